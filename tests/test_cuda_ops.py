@@ -1,0 +1,311 @@
+"""Numerics of every CUDA kernel against the plain-PyTorch fp32 statement of the same op.
+All tests here need a B200; they are skipped on machines without CUDA."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from vlm_training_b200 import ops
+from vlm_training_b200.ops import reference as ref
+
+DEV = "cuda"
+
+
+def _cu():
+    from vlm_training_b200.ops import cuda as cu
+
+    return cu
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV) * scale).to(dtype)
+
+
+def _close(got, want, atol, rtol, what=""):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    assert bool((err <= tol).all()), f"{what}: max err {err.max().item():.4g}, max ref {want.abs().max().item():.4g}, " \
+                                     f"frac bad {(err > tol).float().mean().item():.4g}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (1000, 1152, 1536), (384, 4304, 1152), (8, 16, 8),
+                                   (2048, 4096, 4096), (130, 136, 72)])
+def test_gemm_forward_layout(M, N, K):
+    cu = _cu()
+    a, b = _rand(M, K), _rand(N, K)
+    got = cu._gemm(a, b)
+    want = a.float() @ b.float().t()
+    _close(got, want, atol=0.05 * math.sqrt(K) / 8, rtol=2e-2, what=f"gemm KK {M}x{N}x{K}")
+    cu.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (1000, 1152, 4304), (2048, 4096, 12288)])
+def test_gemm_dgrad_wgrad_layouts(M, N, K):
+    cu = _cu()
+    # dgrad: dX[M,K] = dY[M,N] . W[N,K]   (A K-major, B stored [contraction, out])
+    dy, w, x = _rand(M, N), _rand(N, K), _rand(M, K)
+    got = cu._gemm(dy, w, b_mn=True)
+    _close(got, dy.float() @ w.float(), atol=0.05 * math.sqrt(N) / 8, rtol=2e-2, what="dgrad")
+    # wgrad: dW[N,K] = dY^T . X   (both stored [contraction, out])
+    got = cu._gemm(dy, x, a_mn=True, b_mn=True)
+    _close(got, dy.float().t() @ x.float(), atol=0.05 * math.sqrt(M) / 8, rtol=2e-2, what="wgrad")
+    # fp32 accumulate-into
+    acc = torch.ones(N, K, device=DEV)
+    cu._gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    _close(acc, 1.0 + dy.float().t() @ x.float(), atol=0.05 * math.sqrt(M) / 8, rtol=2e-2, what="wgrad acc")
+    cu.check_status()
+
+
+def test_gemm_bias_and_repeatability():
+    cu = _cu()
+    a, b, bias = _rand(512, 1152), _rand(3456, 1152), _rand(3456)
+    got = cu._gemm(a, b, bias=bias)
+    _close(got, a.float() @ b.float().t() + bias.float(), atol=0.3, rtol=2e-2, what="bias")
+    assert torch.equal(got, cu._gemm(a, b, bias=bias)), "two runs differ"
+
+
+def test_linear_autograd_matches_torch():
+    x = _rand(300, 256, scale=0.5).requires_grad_()
+    w = _rand(512, 256, scale=0.1).requires_grad_()
+    b = _rand(512, scale=0.1).requires_grad_()
+    y = ops.linear(x, w, b)
+    g = _rand(300, 512)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    _close(y, yr, 0.05, 2e-2, "y")
+    _close(x.grad, xr.grad, 0.1, 2e-2, "dx")
+    _close(w.grad, wr.grad, 0.3, 2e-2, "dw")
+    _close(b.grad, br.grad, 0.3, 2e-2, "db")
+
+
+@pytest.mark.parametrize("offset", [False, True])
+@pytest.mark.parametrize("D", [128, 4096, 1152])
+def test_rms_norm_fwd_bwd(D, offset):
+    x = _rand(777, D).requires_grad_()
+    w = _rand(D, scale=0.3).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-6, offset)
+    g = _rand(777, D)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rms_norm(xr, wr, 1e-6, offset)
+    yr.backward(g.float())
+    _close(y, yr, 0.02, 1e-2, "y")
+    _close(x.grad, xr.grad, 0.03, 2e-2, "dx")
+    _close(w.grad, wr.grad, 0.5, 2e-2, "dw")
+
+
+def test_add_rms_norm_fwd_bwd():
+    D = 512
+    x, r = _rand(300, D).requires_grad_(), _rand(300, D).requires_grad_()
+    w = _rand(D, scale=0.3).requires_grad_()
+    y, s = ops.add_rms_norm(x, r, w, 1e-6, False)
+    gy, gs = _rand(300, D), _rand(300, D)
+    torch.autograd.backward([y, s], [gy, gs])
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    sr = xr + rr
+    yr = ref.rms_norm(sr, wr, 1e-6, False)
+    torch.autograd.backward([yr, sr], [gy.float(), gs.float()])
+    _close(y, yr, 0.03, 2e-2, "y")
+    _close(s, sr, 0.03, 1e-2, "sum")
+    _close(x.grad, xr.grad, 0.05, 2e-2, "dx")
+    _close(r.grad, rr.grad, 0.05, 2e-2, "dres")
+    _close(w.grad, wr.grad, 0.5, 2e-2, "dw")
+
+
+def test_layer_norm_fwd_bwd():
+    D = 1152
+    x = _rand(500, D).requires_grad_()
+    w, b = _rand(D, scale=0.5).requires_grad_(), _rand(D, scale=0.5).requires_grad_()
+    y = ops.layer_norm(x, w, b, 1e-6)
+    g = _rand(500, D)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (D,), wr, br, 1e-6)
+    yr.backward(g.float())
+    _close(y, yr, 0.03, 1e-2, "y")
+    _close(x.grad, xr.grad, 0.05, 2e-2, "dx")
+    _close(w.grad, wr.grad, 0.5, 2e-2, "dw")
+    _close(b.grad, br.grad, 0.5, 2e-2, "db")
+
+
+def test_rms_norm_gated_fwd_bwd():
+    D = 128
+    x, z = _rand(1000, D).requires_grad_(), _rand(1000, D).requires_grad_()
+    w = _rand(D, scale=0.5).requires_grad_()
+    y = ops.rms_norm_gated(x, z, w, 1e-6)
+    g = _rand(1000, D)
+    y.backward(g)
+    xr, zr, wr = (t.detach().float().requires_grad_() for t in (x, z, w))
+    yr = ref.rms_norm_gated(xr, zr, wr, 1e-6)
+    yr.backward(g.float())
+    _close(y, yr, 0.03, 2e-2, "y")
+    _close(x.grad, xr.grad, 0.05, 2e-2, "dx")
+    _close(z.grad, zr.grad, 0.05, 2e-2, "dz")
+    _close(w.grad, wr.grad, 0.6, 2e-2, "dw")
+
+
+def test_swiglu_sigmoid_mul_gelu():
+    gu = _rand(257, 2 * 768).requires_grad_()
+    y = ops.swiglu(gu)
+    g = _rand(257, 768)
+    y.backward(g)
+    gr = gu.detach().float().requires_grad_()
+    a, b = gr.chunk(2, -1)
+    yr = torch.nn.functional.silu(a) * b
+    yr.backward(g.float())
+    _close(y, yr, 0.02, 1e-2, "swiglu")
+    _close(gu.grad, gr.grad, 0.03, 2e-2, "swiglu grad")
+
+    x, gt = _rand(100, 512).requires_grad_(), _rand(100, 512).requires_grad_()
+    y = ops.sigmoid_mul(x, gt)
+    g = _rand(100, 512)
+    y.backward(g)
+    xr, gtr = x.detach().float().requires_grad_(), gt.detach().float().requires_grad_()
+    (xr * torch.sigmoid(gtr)).backward(g.float())
+    _close(x.grad, xr.grad, 0.02, 2e-2, "sigmul dx")
+    _close(gt.grad, gtr.grad, 0.02, 2e-2, "sigmul dgate")
+
+    cu = _cu()
+    for approx in ("tanh", "none"):
+        x = _rand(64, 1024).requires_grad_()
+        y = cu.gelu(x, approx)
+        y.backward(g := _rand(64, 1024))
+        xr = x.detach().float().requires_grad_()
+        yr = torch.nn.functional.gelu(xr, approximate=approx)
+        yr.backward(g.float())
+        _close(y, yr, 0.02, 1e-2, f"gelu {approx}")
+        _close(x.grad, xr.grad, 0.03, 2e-2, f"gelu grad {approx}")
+
+
+@pytest.mark.parametrize("D,R,gated,offset", [(128, 128, False, False), (256, 64, True, True), (64, 64, False, False),
+                                              (32, 32, False, False), (64, 16, True, True)])
+def test_qkv_norm_rope_fwd_bwd(D, R, gated, offset):
+    T, n_q, n_kv = 193, 4, 2
+    W = (n_q * (2 if gated else 1) + 2 * n_kv) * D
+    qkv = _rand(T, W).requires_grad_()
+    qw, kw = _rand(D, scale=0.3).requires_grad_(), _rand(D, scale=0.3).requires_grad_()
+    ang = torch.rand(T, R // 2, device=DEV) * 6.28
+    emb = torch.cat((ang, ang), -1)
+    cos, sin = emb.cos(), emb.sin()
+    outs = ops.qkv_norm_rope(qkv, n_q, n_kv, D, qw, kw, cos, sin, 1e-6, offset, gated)
+    grads = [_rand(*o.shape) for o in outs if o is not None]
+    torch.autograd.backward([o for o in outs if o is not None], grads)
+    import vlm_training_b200.ops as O
+
+    qkvr, qwr, kwr = (t.detach().float().requires_grad_() for t in (qkv, qw, kw))
+    O._FORCE_REF = True
+    try:
+        outs_r = ops.qkv_norm_rope(qkvr, n_q, n_kv, D, qwr, kwr, cos, sin, 1e-6, offset, gated)
+    finally:
+        O._FORCE_REF = False
+    torch.autograd.backward([o for o in outs_r if o is not None], [g.float() for g in grads])
+    for name, a, b in zip("qkvg", outs, outs_r):
+        if a is not None:
+            _close(a, b, 0.03, 2e-2, name)
+    _close(qkv.grad, qkvr.grad, 0.06, 3e-2, "dqkv")
+    _close(qw.grad, qwr.grad, 0.8, 3e-2, "dqw")
+    _close(kw.grad, kwr.grad, 0.8, 3e-2, "dkw")
+
+
+def test_rope_vision_fwd_bwd():
+    S, H, D = 300, 4, 72
+    qkv = _rand(S, 3, H, D).requires_grad_()
+    ang = torch.rand(S, D // 2, device=DEV) * 6.28
+    emb = torch.cat((ang, ang), -1)
+    cos, sin = emb.cos(), emb.sin()
+    q, k, v = qkv.unbind(1)
+    qo, ko = ops.rope_vision(q, k, cos, sin)
+    gq, gk = _rand(S, H, D), _rand(S, H, D)
+    torch.autograd.backward([qo, ko], [gq, gk])
+    qr = qkv.detach().float().requires_grad_()
+    q2, k2, _ = qr.unbind(1)
+    qo_r, ko_r = ref.apply_rope(q2, cos, sin), ref.apply_rope(k2, cos, sin)
+    torch.autograd.backward([qo_r, ko_r], [gq.float(), gk.float()])
+    _close(qo, qo_r, 0.02, 1e-2, "q")
+    _close(ko, ko_r, 0.02, 1e-2, "k")
+    _close(qkv.grad, qr.grad, 0.03, 2e-2, "dqkv")
+
+
+def test_gdn_gates_and_conv():
+    T, H, C = 500, 16, 512
+    proj = _rand(T, C + 2 * H).requires_grad_()
+    A_log, dt_bias = _rand(H, scale=0.5).requires_grad_(), _rand(H).requires_grad_()
+    x, a, b = proj.split([C, H, H], -1)
+    g, beta = ops.gdn_gates(a, b, A_log, dt_bias)
+    cu_seq = torch.tensor([0, 100, 101, 350, 500], device=DEV, dtype=torch.int32)
+    seq_idx = ref.seq_idx_from_cu(cu_seq, T)
+    w = _rand(C, 4, scale=0.5).requires_grad_()
+    y = ops.causal_conv1d_silu(x, w, seq_idx)
+    gg, gb, gy = torch.randn(T, H, device=DEV), _rand(T, H), _rand(T, C)
+    torch.autograd.backward([g, beta, y], [gg, gb, gy])
+
+    pr, Ar, dr, wr = (t.detach().float().requires_grad_() for t in (proj, A_log, dt_bias, w))
+    xr, ar, br = pr.split([C, H, H], -1)
+    g_r = -Ar.exp() * torch.nn.functional.softplus(ar + dr)
+    beta_r = torch.sigmoid(br)
+    y_r = ref.causal_conv1d_silu(xr, wr, seq_idx)
+    torch.autograd.backward([g_r, beta_r, y_r], [gg, gb.float(), gy.float()])
+    _close(g, g_r, 0.02, 1e-2, "g")
+    _close(beta, beta_r, 0.01, 1e-2, "beta")
+    _close(y, y_r, 0.03, 2e-2, "conv y")
+    _close(proj.grad, pr.grad, 0.06, 3e-2, "dproj")
+    _close(w.grad, wr.grad, 1.0, 3e-2, "dconv w")
+    _close(A_log.grad, Ar.grad, 2.0, 3e-2, "dA_log")
+    _close(dt_bias.grad, dr.grad, 2.0, 3e-2, "ddt_bias")
+
+
+def test_rows_scatter_add():
+    x = _rand(1000, 256).requires_grad_()
+    idx = torch.randperm(1000, device=DEV)[:300].sort().values
+    src = _rand(300, 256).requires_grad_()
+    for fn, rfn in ((ops.scatter_rows, ref.scatter_rows), (ops.add_rows, ref.add_rows)):
+        x.grad = src.grad = None
+        y = fn(x, idx, src)
+        g = _rand(1000, 256)
+        y.backward(g)
+        xr, sr = x.detach().float().requires_grad_(), src.detach().float().requires_grad_()
+        yr = rfn(xr, idx, sr)
+        yr.backward(g.float())
+        _close(y, yr, 0.02, 1e-2, "y")
+        _close(x.grad, xr.grad, 1e-3, 1e-3, "dx")
+        _close(src.grad, sr.grad, 1e-3, 1e-3, "dsrc")
+
+
+@pytest.mark.parametrize("T,H,V,chunk", [(700, 256, 5000, 256), (1024, 512, 151936, 512)])
+def test_linear_cross_entropy(T, H, V, chunk):
+    h = _rand(T, H, scale=0.5).requires_grad_()
+    w = _rand(V, H, scale=0.05).requires_grad_()
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    tgt[::7] = -100
+    loss_sum, n = ops.linear_cross_entropy(h, w, tgt, chunk)
+    (loss_sum / n).backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    logits = (hr @ wr.t()).to(torch.bfloat16).float()  # the kernel sees bf16 logits
+    lr = torch.nn.functional.cross_entropy(logits, tgt, ignore_index=-100)
+    lr.backward()
+    assert int(n) == int((tgt != -100).sum())
+    assert abs((loss_sum / n).item() - lr.item()) < 2e-2, ((loss_sum / n).item(), lr.item())
+    _close(h.grad, hr.grad, 2e-4, 5e-2, "dh")
+    _close(w.grad, wr.grad, 2e-4, 5e-2, "dw")
+
+
+def test_adamw_matches_torch():
+    cu = _cu()
+    n = 100_003
+    p0 = torch.randn(n, device=DEV)
+    master, m, v = p0.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    param = p0.to(torch.bfloat16)
+    pr = p0.clone().requires_grad_()
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in range(1, 4):
+        g = torch.randn(n, device=DEV).to(torch.bfloat16)
+        cu.adamw_step_(g, master, m, v, param, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+        pr.grad = g.float()
+        opt.step()
+    torch.testing.assert_close(master, pr.detach(), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(param.float(), pr.detach().to(torch.bfloat16).float(), atol=1e-2, rtol=1e-2)

@@ -1,0 +1,909 @@
+// Bandwidth-bound fused kernels (bf16 I/O, fp32 math): RMSNorm (+residual, offset form),
+// LayerNorm, gated RMSNorm, SwiGLU, sigmoid gating, GELU, fused per-head QK-norm + rotary +
+// layout split of the fused qkv projection, ViT rotary, Gated-DeltaNet gate prep, depthwise
+// causal conv1d + SiLU over packed rows, row scatter / row add for vision features.
+//
+// Conventions: one warp per row for the row-reduction kernels, 16-byte vector accesses,
+// weight-gradient partial sums written per block (reduced by the caller) so results are
+// bit-reproducible run to run.
+#include "elementwise.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const bf162* p = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  bf162* p = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float ldw(const bf16* w, int i) { return __bfloat162float(w[i]); }
+__device__ __forceinline__ float ldw(const float* w, int i) { return w[i]; }
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = kWarpsPerBlock * 32;
+
+// ----------------------------------------------------------------------------------- RMSNorm forward
+// y = x * rstd * (w or 1+w);  optional residual: r = x + res is written out and normalised.
+template <typename WT>
+__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const WT* __restrict__ w,
+                                   bf16* __restrict__ y, bf16* __restrict__ r_out, float* __restrict__ rstd, int rows, int D,
+                                   float eps, int offset) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
+    const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * D) : nullptr;
+    uint4* ro = r_out ? reinterpret_cast<uint4*>(r_out + (size_t)row * D) : nullptr;
+    float ss = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+      if (rr) {
+        float g[8];
+        unpack8(rr[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += g[i];
+        uint4 pk = pack8(f);
+        ro[v] = pk;
+        unpack8(pk, f);  // normalise the rounded residual stream, as the unfused sequence does
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / (float)D + eps);
+    if (lane == 0 && rstd) rstd[row] = rs;
+    const uint4* src = rr ? reinterpret_cast<const uint4*>(r_out + (size_t)row * D) : xr;
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * D);
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8];
+      unpack8(src[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float wv = ldw(w, v * 8 + i);
+        f[i] = f[i] * rs * (offset ? 1.f + wv : wv);
+      }
+      yr[v] = pack8(f);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------- RMSNorm backward
+// dx = rstd * (g - xhat * mean(g * xhat)) (+ dres),  g = dy * w';   dw_partial[block] += dy * xhat
+template <typename WT>
+__global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const WT* __restrict__ w,
+                                   const float* __restrict__ rstd, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                                   float* __restrict__ dw_partial, int rows, int D, int offset) {
+  extern __shared__ float sm_dw[];  // [kWarpsPerBlock][D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  float* my_dw = sm_dw + (size_t)warp * D;
+  for (int i = lane; i < D; i += 32) my_dw[i] = 0.f;
+  __syncwarp();
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
+    const float rs = rstd[row];
+    float dot = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float xf[8], gf[8];
+      unpack8(xr[v], xf);
+      unpack8(gr[v], gf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float wv = ldw(w, v * 8 + i);
+        wv = offset ? 1.f + wv : wv;
+        const float xh = xf[i] * rs;
+        dot += gf[i] * wv * xh;
+        my_dw[v * 8 + i] += gf[i] * xh;
+      }
+    }
+    dot = warp_sum(dot) / (float)D;
+    const uint4* dr = dres ? reinterpret_cast<const uint4*>(dres + (size_t)row * D) : nullptr;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * D);
+    for (int v = lane; v < nvec; v += 32) {
+      float xf[8], gf[8], o[8];
+      unpack8(xr[v], xf);
+      unpack8(gr[v], gf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float wv = ldw(w, v * 8 + i);
+        wv = offset ? 1.f + wv : wv;
+        o[i] = rs * (gf[i] * wv - xf[i] * rs * dot);
+      }
+      if (dr) {
+        float e[8];
+        unpack8(dr[v], e);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += e[i];
+      }
+      dxr[v] = pack8(o);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kWarpsPerBlock; ++wi) s += sm_dw[(size_t)wi * D + i];
+    dw_partial[(size_t)blockIdx.x * D + i] = s;
+  }
+}
+
+// ----------------------------------------------------------------------------------- LayerNorm
+__global__ void layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
+                                     bf16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int rows, int D,
+                                     float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
+    float s = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += f[i];
+    }
+    const float mu = warp_sum(s) / (float)D;
+    float ss = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float d = f[i] - mu; ss += d * d; }
+    }
+    const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * D);
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = (f[i] - mu) * rs * ldw(w, v * 8 + i) + (b ? ldw(b, v * 8 + i) : 0.f);
+      yr[v] = pack8(f);
+    }
+  }
+}
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * w; partial dw, db per block
+__global__ void layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                     const float* __restrict__ mean, const float* __restrict__ rstd, bf16* __restrict__ dx,
+                                     float* __restrict__ dw_partial, float* __restrict__ db_partial, int rows, int D) {
+  extern __shared__ float sm_acc[];  // [kWarpsPerBlock][2][D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  float* my_dw = sm_acc + (size_t)warp * 2 * D;
+  float* my_db = my_dw + D;
+  for (int i = lane; i < 2 * D; i += 32) my_dw[i] = 0.f;
+  __syncwarp();
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float xf[8], gf[8];
+      unpack8(xr[v], xf);
+      unpack8(gr[v], gf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (xf[i] - mu) * rs;
+        const float g = gf[i] * ldw(w, v * 8 + i);
+        s1 += g;
+        s2 += g * xh;
+        my_dw[v * 8 + i] += gf[i] * xh;
+        my_db[v * 8 + i] += gf[i];
+      }
+    }
+    s1 = warp_sum(s1) / (float)D;
+    s2 = warp_sum(s2) / (float)D;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * D);
+    for (int v = lane; v < nvec; v += 32) {
+      float xf[8], gf[8], o[8];
+      unpack8(xr[v], xf);
+      unpack8(gr[v], gf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (xf[i] - mu) * rs;
+        o[i] = rs * (gf[i] * ldw(w, v * 8 + i) - s1 - xh * s2);
+      }
+      dxr[v] = pack8(o);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float a = 0.f, c = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kWarpsPerBlock; ++wi) { a += sm_acc[(size_t)wi * 2 * D + i]; c += sm_acc[(size_t)wi * 2 * D + D + i]; }
+    dw_partial[(size_t)blockIdx.x * D + i] = a;
+    db_partial[(size_t)blockIdx.x * D + i] = c;
+  }
+}
+
+// ----------------------------------------------------------------------------------- gated RMSNorm (GDN output)
+// y = x * rstd * w * z * sigmoid(z), rows of D (<= 256), one warp per row
+__global__ void rmsnorm_gated_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, const bf16* __restrict__ w,
+                                         bf16* __restrict__ y, float* __restrict__ rstd, int rows, int D, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) { const float f = __bfloat162float(x[(size_t)row * D + i]); ss += f * f; }
+    const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+    if (lane == 0) rstd[row] = rs;
+    for (int i = lane; i < D; i += 32) {
+      const float f = __bfloat162float(x[(size_t)row * D + i]);
+      const float zz = __bfloat162float(z[(size_t)row * D + i]);
+      y[(size_t)row * D + i] = __float2bfloat16(f * rs * ldw(w, i) * zz * sigmoidf_(zz));
+    }
+  }
+}
+__global__ void rmsnorm_gated_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ z,
+                                         const bf16* __restrict__ w, const float* __restrict__ rstd, bf16* __restrict__ dx,
+                                         bf16* __restrict__ dz, float* __restrict__ dw_partial, int rows, int D) {
+  extern __shared__ float sm_dw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* my_dw = sm_dw + (size_t)warp * D;
+  for (int i = lane; i < D; i += 32) my_dw[i] = 0.f;
+  __syncwarp();
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+    const float rs = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const size_t o = (size_t)row * D + i;
+      const float xh = __bfloat162float(x[o]) * rs, zz = __bfloat162float(z[o]), g = __bfloat162float(dy[o]);
+      const float sg = sigmoidf_(zz), act = zz * sg;
+      const float gn = g * act;  // grad wrt normalised*weight
+      dot += gn * ldw(w, i) * xh;
+      my_dw[i] += gn * xh;
+      dz[o] = __float2bfloat16(g * xh * ldw(w, i) * (sg + act * (1.f - sg)));
+    }
+    dot = warp_sum(dot) / (float)D;
+    for (int i = lane; i < D; i += 32) {
+      const size_t o = (size_t)row * D + i;
+      const float xh = __bfloat162float(x[o]) * rs, zz = __bfloat162float(z[o]), g = __bfloat162float(dy[o]);
+      const float gn = g * zz * sigmoidf_(zz);
+      dx[o] = __float2bfloat16(rs * (gn * ldw(w, i) - xh * dot));
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kWarpsPerBlock; ++wi) s += sm_dw[(size_t)wi * D + i];
+    dw_partial[(size_t)blockIdx.x * D + i] = s;
+  }
+}
+
+// ----------------------------------------------------------------------------------- SwiGLU
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long rows, int I) {
+  const long nvec = rows * (I >> 3);
+  const int vper = I >> 3;
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
+    const long row = v / vper;
+    const int c = (int)(v - row * vper);
+    const uint4* base = reinterpret_cast<const uint4*>(gu + row * 2 * (long)I);
+    float g[8], u[8], o[8];
+    unpack8(base[c], g);
+    unpack8(base[vper + c], u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = g[i] * sigmoidf_(g[i]) * u[i];
+    reinterpret_cast<uint4*>(out)[v] = pack8(o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu, bf16* __restrict__ dgu, long rows,
+                                  int I) {
+  const long nvec = rows * (I >> 3);
+  const int vper = I >> 3;
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
+    const long row = v / vper;
+    const int c = (int)(v - row * vper);
+    const uint4* base = reinterpret_cast<const uint4*>(gu + row * 2 * (long)I);
+    uint4* obase = reinterpret_cast<uint4*>(dgu + row * 2 * (long)I);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(base[c], g);
+    unpack8(base[vper + c], u);
+    unpack8(reinterpret_cast<const uint4*>(dout)[v], d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float s = sigmoidf_(g[i]);
+      const float silu = g[i] * s;
+      du[i] = d[i] * silu;
+      dg[i] = d[i] * u[i] * (s + silu * (1.f - s));
+    }
+    obase[c] = pack8(dg);
+    obase[vper + c] = pack8(du);
+  }
+}
+
+// ----------------------------------------------------------------------------------- x * sigmoid(gate)
+__global__ void sigmoid_mul_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gate, bf16* __restrict__ out, long n8) {
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < n8; v += (long)gridDim.x * blockDim.x) {
+    float a[8], g[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[v], a);
+    unpack8(reinterpret_cast<const uint4*>(gate)[v], g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] *= sigmoidf_(g[i]);
+    reinterpret_cast<uint4*>(out)[v] = pack8(a);
+  }
+}
+__global__ void sigmoid_mul_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ x, const bf16* __restrict__ gate,
+                                       bf16* __restrict__ dx, bf16* __restrict__ dgate, long n8) {
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < n8; v += (long)gridDim.x * blockDim.x) {
+    float a[8], g[8], d[8], o1[8], o2[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[v], a);
+    unpack8(reinterpret_cast<const uint4*>(gate)[v], g);
+    unpack8(reinterpret_cast<const uint4*>(dout)[v], d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float s = sigmoidf_(g[i]);
+      o1[i] = d[i] * s;
+      o2[i] = d[i] * a[i] * s * (1.f - s);
+    }
+    reinterpret_cast<uint4*>(dx)[v] = pack8(o1);
+    reinterpret_cast<uint4*>(dgate)[v] = pack8(o2);
+  }
+}
+
+// ----------------------------------------------------------------------------------- GELU
+__device__ __forceinline__ float gelu_f(float x, int tanh_approx) {
+  if (tanh_approx) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.f + tanhf(u));
+  }
+  return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+}
+__device__ __forceinline__ float gelu_grad_f(float x, int tanh_approx) {
+  if (tanh_approx) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    const float t = tanhf(u);
+    const float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x * x);
+    return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+  }
+  const float cdf = 0.5f * (1.f + erff(x * 0.7071067811865476f));
+  return cdf + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+__global__ void gelu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long n8, int tanh_approx) {
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < n8; v += (long)gridDim.x * blockDim.x) {
+    float a[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[v], a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = gelu_f(a[i], tanh_approx);
+    reinterpret_cast<uint4*>(y)[v] = pack8(a);
+  }
+}
+__global__ void gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx, long n8,
+                                int tanh_approx) {
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < n8; v += (long)gridDim.x * blockDim.x) {
+    float a[8], d[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[v], a);
+    unpack8(reinterpret_cast<const uint4*>(dy)[v], d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d[i] *= gelu_grad_f(a[i], tanh_approx);
+    reinterpret_cast<uint4*>(dx)[v] = pack8(d);
+  }
+}
+
+// ----------------------------------------------------------------------------------- fused qkv split + QK-norm + rotary
+// One warp per (token, head slot).  Head slots: [0, n_q) q heads, [n_q, n_q+n_kv) k heads,
+// [n_q+n_kv, n_q+2 n_kv) v heads.  Lane owns E = D/32 consecutive channels; the rotate-half
+// partner of channel j (< R/2) is j + R/2, held by lane + (R/2)/E.
+template <int E>
+__global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                                         const float* __restrict__ cosv, const float* __restrict__ sinv, bf16* __restrict__ q,
+                                         bf16* __restrict__ k, bf16* __restrict__ v, bf16* __restrict__ gate,
+                                         float* __restrict__ rstd, int T, int n_q, int n_kv, int R, float eps, int offset,
+                                         int gated, int has_norm) {
+  constexpr int D = E * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = n_q + 2 * n_kv;
+  const int qstride = gated ? 2 * D : D;
+  const int W = n_q * qstride + 2 * n_kv * D;
+  const long total = (long)T * slots;
+  const int half = R >> 1;
+  const int plane = half / E;  // partner lane distance
+  for (long item = blockIdx.x * (long)kWarpsPerBlock + warp; item < total; item += (long)gridDim.x * kWarpsPerBlock) {
+    const int t = (int)(item / slots);
+    const int s = (int)(item - (long)t * slots);
+    const bf16* row = qkv + (size_t)t * W;
+    const bf16* src;
+    bf16* dst;
+    const bf16* wn = nullptr;
+    int kind;  // 0 q, 1 k, 2 v
+    if (s < n_q) { src = row + s * qstride; dst = q + ((size_t)t * n_q + s) * D; wn = qw; kind = 0; }
+    else if (s < n_q + n_kv) { const int h = s - n_q; src = row + n_q * qstride + h * D; dst = k + ((size_t)t * n_kv + h) * D; wn = kw; kind = 1; }
+    else { const int h = s - n_q - n_kv; src = row + n_q * qstride + n_kv * D + h * D; dst = v + ((size_t)t * n_kv + h) * D; kind = 2; }
+    float f[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) f[i] = __bfloat162float(src[lane * E + i]);
+    if (kind == 2) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) dst[lane * E + i] = src[lane * E + i];
+      continue;
+    }
+    if (kind == 0 && gated) {
+      bf16* gd = gate + ((size_t)t * n_q + s) * D;
+#pragma unroll
+      for (int i = 0; i < E; ++i) gd[lane * E + i] = src[D + lane * E + i];
+    }
+    if (has_norm) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < E; ++i) ss += f[i] * f[i];
+      const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+      if (lane == 0) rstd[(size_t)t * (n_q + n_kv) + s] = rs;
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        const float wv = ldw(wn, lane * E + i);
+        // round to bf16 between norm and rotary like the unfused sequence of ops
+        f[i] = __bfloat162float(__float2bfloat16(f[i] * rs * (offset ? 1.f + wv : wv)));
+      }
+    }
+    // rotary on channels [0, R)
+    float o[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const int j = lane * E + i;
+      const float partner = __shfl_xor_sync(0xffffffffu, f[i], plane);
+      if (j < R) {
+        const float c = cosv[(size_t)t * R + j], sn = sinv[(size_t)t * R + j];
+        o[i] = f[i] * c + (j < half ? -partner : partner) * sn;
+      } else {
+        o[i] = f[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < E; ++i) dst[lane * E + i] = __float2bfloat16(o[i]);
+  }
+}
+
+template <int E>
+__global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* __restrict__ dk, const bf16* __restrict__ dv,
+                                         const bf16* __restrict__ dgate, const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
+                                         const bf16* __restrict__ kw, const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                         const float* __restrict__ rstd, bf16* __restrict__ dqkv, float* __restrict__ dw_partial,
+                                         int T, int n_q, int n_kv, int R, int offset, int gated, int has_norm) {
+  constexpr int D = E * 32;
+  __shared__ float sm_dw[kWarpsPerBlock][2][D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = n_q + 2 * n_kv;
+  const int qstride = gated ? 2 * D : D;
+  const int W = n_q * qstride + 2 * n_kv * D;
+  const long total = (long)T * slots;
+  const int half = R >> 1;
+  const int plane = half / E;
+  float acc_q[E], acc_k[E];
+#pragma unroll
+  for (int i = 0; i < E; ++i) acc_q[i] = acc_k[i] = 0.f;
+  for (long item = blockIdx.x * (long)kWarpsPerBlock + warp; item < total; item += (long)gridDim.x * kWarpsPerBlock) {
+    const int t = (int)(item / slots);
+    const int s = (int)(item - (long)t * slots);
+    const bf16* row = qkv + (size_t)t * W;
+    bf16* drow = dqkv + (size_t)t * W;
+    int kind, off;
+    const bf16* g;
+    const bf16* wn = nullptr;
+    if (s < n_q) { kind = 0; off = s * qstride; g = dq + ((size_t)t * n_q + s) * D; wn = qw; }
+    else if (s < n_q + n_kv) { kind = 1; const int h = s - n_q; off = n_q * qstride + h * D; g = dk + ((size_t)t * n_kv + h) * D; wn = kw; }
+    else { kind = 2; const int h = s - n_q - n_kv; off = n_q * qstride + n_kv * D + h * D; g = dv + ((size_t)t * n_kv + h) * D; }
+    if (kind == 2) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) drow[off + lane * E + i] = g[lane * E + i];
+      continue;
+    }
+    if (kind == 0 && gated) {
+      const bf16* gg = dgate + ((size_t)t * n_q + s) * D;
+#pragma unroll
+      for (int i = 0; i < E; ++i) drow[off + D + lane * E + i] = gg[lane * E + i];
+    }
+    // rotary transpose: dn[j] = do[j] c[j] + (j < half ? do[j+half] s[j+half] : -do[j-half] s[j-half])
+    float dn[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const int j = lane * E + i;
+      const float d = __bfloat162float(g[j]);
+      float ds = 0.f;
+      if (j < R) ds = d * sinv[(size_t)t * R + j];
+      const float partner = __shfl_xor_sync(0xffffffffu, ds, plane);
+      if (j < R) dn[i] = d * cosv[(size_t)t * R + j] + (j < half ? partner : -partner);
+      else dn[i] = d;
+    }
+    if (!has_norm) {
+#pragma unroll
+      for (int i = 0; i < E; ++i) drow[off + lane * E + i] = __float2bfloat16(dn[i]);
+      continue;
+    }
+    const float rs = rstd[(size_t)t * (n_q + n_kv) + s];
+    float xh[E], dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float wv0 = ldw(wn, lane * E + i);
+      const float wv = offset ? 1.f + wv0 : wv0;
+      xh[i] = __bfloat162float(row[off + lane * E + i]) * rs;
+      dot += dn[i] * wv * xh[i];
+      if (kind == 0) acc_q[i] += dn[i] * xh[i]; else acc_k[i] += dn[i] * xh[i];
+    }
+    dot = warp_sum(dot) / (float)D;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float wv0 = ldw(wn, lane * E + i);
+      const float wv = offset ? 1.f + wv0 : wv0;
+      drow[off + lane * E + i] = __float2bfloat16(rs * (dn[i] * wv - xh[i] * dot));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < E; ++i) { sm_dw[warp][0][lane * E + i] = acc_q[i]; sm_dw[warp][1][lane * E + i] = acc_k[i]; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+    float sacc = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kWarpsPerBlock; ++wi) sacc += sm_dw[wi][i / D][i % D];
+    dw_partial[(size_t)blockIdx.x * 2 * D + i] = sacc;
+  }
+}
+
+// ----------------------------------------------------------------------------------- ViT rotary (any even D, strided input)
+// x [S, H, D] with strides (ss, hs, 1) -> contiguous out; cos/sin [S, D] fp32; transpose=1 gives the backward map.
+__global__ void rope_generic_kernel(const bf16* __restrict__ x, long ss, long hs, const float* __restrict__ cosv,
+                                    const float* __restrict__ sinv, bf16* __restrict__ out, long oss, long ohs, int S, int H, int D,
+                                    int transpose) {
+  const int half = D >> 1;
+  const long total = (long)S * H * half;
+  for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int j = (int)(idx % half);
+    const long sh = idx / half;
+    const int h = (int)(sh % H);
+    const long s = sh / H;
+    const bf16* p = x + s * ss + h * hs;
+    const float a = __bfloat162float(p[j]), b = __bfloat162float(p[j + half]);
+    const float c0 = cosv[s * D + j], c1 = cosv[s * D + j + half], s0 = sinv[s * D + j], s1 = sinv[s * D + j + half];
+    float o0, o1;
+    if (!transpose) { o0 = a * c0 - b * s0; o1 = b * c1 + a * s1; }
+    else { o0 = a * c0 + b * s1; o1 = b * c1 - a * s0; }
+    bf16* q = out + s * oss + h * ohs;
+    q[j] = __float2bfloat16(o0);
+    q[j + half] = __float2bfloat16(o1);
+  }
+}
+
+// ----------------------------------------------------------------------------------- GDN gate prep
+// g = -exp(A_log) * softplus(a + dt_bias) (fp32 out), beta = sigmoid(b) (bf16 out); a,b strided rows
+__global__ void gdn_gates_fwd_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, long row_stride,
+                                     const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ g,
+                                     bf16* __restrict__ beta, long T, int H) {
+  const long n = T * H;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / H;
+    const int h = (int)(i - t * H);
+    const float av = __bfloat162float(a[t * row_stride + h]) + dt_bias[h];
+    const float sp = av > 20.f ? av : log1pf(__expf(av));
+    g[i] = -__expf(A_log[h]) * sp;
+    beta[i] = __float2bfloat16(sigmoidf_(__bfloat162float(b[t * row_stride + h])));
+  }
+}
+// da = dg * (-exp(A_log)) * sigmoid(a + dt_bias); db = dbeta * beta (1-beta);
+// dA_log[h] += dg * g ; ddt_bias[h] += da  (per-block partials, H <= 256)
+__global__ void gdn_gates_bwd_kernel(const float* __restrict__ dg, const bf16* __restrict__ dbeta, const bf16* __restrict__ a,
+                                     const bf16* __restrict__ b, long row_stride, const float* __restrict__ A_log,
+                                     const float* __restrict__ dt_bias, bf16* __restrict__ da, bf16* __restrict__ db,
+                                     long out_stride, float* __restrict__ partial, long T, int H) {
+  extern __shared__ float sm[];  // [2][H]
+  for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) sm[i] = 0.f;
+  __syncthreads();
+  const long n = T * H;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / H;
+    const int h = (int)(i - t * H);
+    const float av = __bfloat162float(a[t * row_stride + h]) + dt_bias[h];
+    const float sp = av > 20.f ? av : log1pf(__expf(av));
+    const float eA = __expf(A_log[h]);
+    const float dgi = dg[i];
+    const float dav = dgi * (-eA) * sigmoidf_(av);
+    const float bt = sigmoidf_(__bfloat162float(b[t * row_stride + h]));
+    da[t * out_stride + h] = __float2bfloat16(dav);
+    db[t * out_stride + h] = __float2bfloat16(__bfloat162float(dbeta[i]) * bt * (1.f - bt));
+    atomicAdd(&sm[h], dgi * (-eA) * sp);
+    atomicAdd(&sm[H + h], dav);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) partial[(size_t)blockIdx.x * 2 * H + i] = sm[i];
+}
+
+// ----------------------------------------------------------------------------------- depthwise causal conv1d + SiLU (packed rows)
+// x [T, C] (row stride xs), w [C, K] fp32/bf16, seq_idx [T]; y[t,c] = silu(sum_j w[c,j] x[t-(K-1)+j, c]) within a document
+template <int K>
+__global__ void conv1d_silu_fwd_kernel(const bf16* __restrict__ x, long xs, const bf16* __restrict__ w, const int* __restrict__ seq_idx,
+                                       bf16* __restrict__ y, long ys, int T, int C) {
+  const int c8 = C >> 3;
+  const long total = (long)T * c8;
+  for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / c8);
+    const int c = (int)(idx - (long)t * c8) * 8;
+    const int doc = seq_idx[t];
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int ts = t - (K - 1) + j;
+      if (ts < 0 || seq_idx[ts] != doc) continue;
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + (long)ts * xs + c), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i] * __bfloat162float(w[(c + i) * K + j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = acc[i] * sigmoidf_(acc[i]);
+    *reinterpret_cast<uint4*>(y + (long)t * ys + c) = pack8(acc);
+  }
+}
+// dx[t,c] = sum_j w[c,j] * dpre[t+(K-1)-j, c] (same document), dpre = dy * silu'(pre); dw partial per block.
+// pre is recomputed from x.  Each block covers a contiguous range of tokens for a slab of 8*blockDim.x... channels.
+template <int K>
+__global__ void conv1d_silu_bwd_kernel(const bf16* __restrict__ dy, long dys, const bf16* __restrict__ x, long xs,
+                                       const bf16* __restrict__ w, const int* __restrict__ seq_idx, bf16* __restrict__ dx, long dxs,
+                                       float* __restrict__ dw_partial, int T, int C, int t_per_block) {
+  // thread -> one channel; block.y slab of tokens
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int t0 = blockIdx.y * t_per_block;
+  const int t1 = min(T, t0 + t_per_block);
+  float wv[K], dwacc[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) { wv[j] = __bfloat162float(w[c * K + j]); dwacc[j] = 0.f; }
+  // sliding windows: xw holds x[t-(K-1)..t]; dpre of tokens t..t+K-1 needed for dx[t] -> compute dpre on the fly
+  // by recomputing pre for up to K-1 tokens ahead (cheap: K=4).
+  auto pre_at = [&](int t) -> float {
+    const int doc = seq_idx[t];
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int ts = t - (K - 1) + j;
+      if (ts >= 0 && seq_idx[ts] == doc) acc += __bfloat162float(x[(long)ts * xs + c]) * wv[j];
+    }
+    return acc;
+  };
+  auto dpre_at = [&](int t) -> float {
+    const float p = pre_at(t);
+    const float s = sigmoidf_(p);
+    return __bfloat162float(dy[(long)t * dys + c]) * (s + p * s * (1.f - s));
+  };
+  for (int t = t0; t < t1; ++t) {
+    const int doc = seq_idx[t];
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int tt = t + (K - 1) - j;  // output token that used x[t] with tap j
+      if (tt < T && seq_idx[tt] == doc) acc += wv[j] * dpre_at(tt);
+    }
+    dx[(long)t * dxs + c] = __float2bfloat16(acc);
+    // dw[c,j] += dpre[t] * x[t-(K-1)+j]
+    const float dp = dpre_at(t);
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int ts = t - (K - 1) + j;
+      if (ts >= 0 && seq_idx[ts] == doc) dwacc[j] += dp * __bfloat162float(x[(long)ts * xs + c]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < K; ++j) dw_partial[((size_t)blockIdx.y * C + c) * K + j] = dwacc[j];
+}
+
+// ----------------------------------------------------------------------------------- row scatter / row add
+// out[index[i], :] (=|+=) src[i, :]   (index rows are unique)
+__global__ void rows_update_kernel(bf16* __restrict__ out, const long* __restrict__ index, const bf16* __restrict__ src, long n_rows,
+                                   int D, int add) {
+  const int vper = D >> 3;
+  const long total = n_rows * vper;
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < total; v += (long)gridDim.x * blockDim.x) {
+    const long i = v / vper;
+    const int c = (int)(v - i * vper);
+    uint4* dst = reinterpret_cast<uint4*>(out + index[i] * (long)D) + c;
+    uint4 s = reinterpret_cast<const uint4*>(src + i * (long)D)[c];
+    if (add) {
+      float a[8], b[8];
+      unpack8(*dst, a);
+      unpack8(s, b);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) a[k] += b[k];
+      s = pack8(a);
+    }
+    *dst = s;
+  }
+}
+// dst[i, :] = src[index[i], :]
+__global__ void rows_gather_kernel(bf16* __restrict__ dst, const long* __restrict__ index, const bf16* __restrict__ src, long n_rows,
+                                   int D) {
+  const int vper = D >> 3;
+  const long total = n_rows * vper;
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < total; v += (long)gridDim.x * blockDim.x) {
+    const long i = v / vper;
+    const int c = (int)(v - i * vper);
+    reinterpret_cast<uint4*>(dst + i * (long)D)[c] = reinterpret_cast<const uint4*>(src + index[i] * (long)D)[c];
+  }
+}
+
+inline int grid_for(long work_items, int per_block, int cap) {
+  long g = (work_items + per_block - 1) / per_block;
+  if (g < 1) g = 1;
+  return (int)(g < cap ? g : cap);
+}
+
+}  // namespace
+
+// ===================================================================================== launchers
+#define BF(p) reinterpret_cast<const bf16*>(p)
+#define BFM(p) reinterpret_cast<bf16*>(p)
+
+extern "C" {
+
+int vlmt_norm_blocks(int rows) { return grid_for(rows, kWarpsPerBlock, 148 * 4); }
+
+void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32, void* y, void* r_out, float* rstd, int rows, int D,
+                      float eps, int offset, cudaStream_t st) {
+  const int grid = grid_for(rows, kWarpsPerBlock, 148 * 8);
+  if (w_fp32)
+    rmsnorm_fwd_kernel<float><<<grid, kThreads, 0, st>>>(BF(x), BF(res), (const float*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset);
+  else
+    rmsnorm_fwd_kernel<bf16><<<grid, kThreads, 0, st>>>(BF(x), BF(res), BF(w), BFM(y), BFM(r_out), rstd, rows, D, eps, offset);
+}
+
+int vlmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, int w_fp32, const float* rstd, const void* dres, void* dx,
+                     float* dw_partial, int rows, int D, int offset, cudaStream_t st) {
+  const int grid = vlmt_norm_blocks(rows);
+  const size_t smem = (size_t)kWarpsPerBlock * D * sizeof(float);
+  if (w_fp32) {
+    auto k = rmsnorm_bwd_kernel<float>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<grid, kThreads, smem, st>>>(BF(dy), BF(x), (const float*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset);
+  } else {
+    auto k = rmsnorm_bwd_kernel<bf16>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<grid, kThreads, smem, st>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset);
+  }
+  return grid;
+}
+
+void vlmt_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D, float eps,
+                        cudaStream_t st) {
+  layernorm_fwd_kernel<<<grid_for(rows, kWarpsPerBlock, 148 * 8), kThreads, 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps);
+}
+int vlmt_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx, float* dw_partial,
+                       float* db_partial, int rows, int D, cudaStream_t st) {
+  const int grid = vlmt_norm_blocks(rows);
+  const size_t smem = (size_t)kWarpsPerBlock * 2 * D * sizeof(float);
+  cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  layernorm_bwd_kernel<<<grid, kThreads, smem, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D);
+  return grid;
+}
+
+void vlmt_rmsnorm_gated_fwd(const void* x, const void* z, const void* w, void* y, float* rstd, int rows, int D, float eps, cudaStream_t st) {
+  rmsnorm_gated_fwd_kernel<<<grid_for(rows, kWarpsPerBlock, 148 * 16), kThreads, 0, st>>>(BF(x), BF(z), BF(w), BFM(y), rstd, rows, D, eps);
+}
+int vlmt_rmsnorm_gated_bwd(const void* dy, const void* x, const void* z, const void* w, const float* rstd, void* dx, void* dz,
+                           float* dw_partial, int rows, int D, cudaStream_t st) {
+  const int grid = vlmt_norm_blocks(rows);
+  rmsnorm_gated_bwd_kernel<<<grid, kThreads, (size_t)kWarpsPerBlock * D * sizeof(float), st>>>(BF(dy), BF(x), BF(z), BF(w), rstd, BFM(dx),
+                                                                                            BFM(dz), dw_partial, rows, D);
+  return grid;
+}
+
+void vlmt_swiglu_fwd(const void* gu, void* out, long rows, int I, cudaStream_t st) {
+  swiglu_fwd_kernel<<<grid_for(rows * (I >> 3), 256, 148 * 16), 256, 0, st>>>(BF(gu), BFM(out), rows, I);
+}
+void vlmt_swiglu_bwd(const void* dout, const void* gu, void* dgu, long rows, int I, cudaStream_t st) {
+  swiglu_bwd_kernel<<<grid_for(rows * (I >> 3), 256, 148 * 16), 256, 0, st>>>(BF(dout), BF(gu), BFM(dgu), rows, I);
+}
+void vlmt_sigmoid_mul_fwd(const void* x, const void* gate, void* out, long n, cudaStream_t st) {
+  sigmoid_mul_fwd_kernel<<<grid_for(n >> 3, 256, 148 * 16), 256, 0, st>>>(BF(x), BF(gate), BFM(out), n >> 3);
+}
+void vlmt_sigmoid_mul_bwd(const void* dout, const void* x, const void* gate, void* dx, void* dgate, long n, cudaStream_t st) {
+  sigmoid_mul_bwd_kernel<<<grid_for(n >> 3, 256, 148 * 16), 256, 0, st>>>(BF(dout), BF(x), BF(gate), BFM(dx), BFM(dgate), n >> 3);
+}
+void vlmt_gelu_fwd(const void* x, void* y, long n, int tanh_approx, cudaStream_t st) {
+  gelu_fwd_kernel<<<grid_for(n >> 3, 256, 148 * 16), 256, 0, st>>>(BF(x), BFM(y), n >> 3, tanh_approx);
+}
+void vlmt_gelu_bwd(const void* dy, const void* x, void* dx, long n, int tanh_approx, cudaStream_t st) {
+  gelu_bwd_kernel<<<grid_for(n >> 3, 256, 148 * 16), 256, 0, st>>>(BF(dy), BF(x), BFM(dx), n >> 3, tanh_approx);
+}
+
+int vlmt_qkv_blocks(long items) { return grid_for(items, kWarpsPerBlock, 148 * 8); }
+
+int vlmt_qkv_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, const float* cosv, const float* sinv, void* q, void* k,
+                           void* v, void* gate, float* rstd, int T, int n_q, int n_kv, int D, int R, float eps, int offset, int gated,
+                           int has_norm, cudaStream_t st) {
+  const int E = D / 32;
+  if (D % 32 || R > D || (R / 2) % E || (((R / 2) / E) & ((R / 2) / E - 1)) || (R / 2) / E >= 32) return -1;
+  const int grid = vlmt_qkv_blocks((long)T * (n_q + 2 * n_kv));
+#define LAUNCH(E_)                                                                                                              \
+  qkv_norm_rope_fwd_kernel<E_><<<grid, kThreads, 0, st>>>(BF(qkv), BF(qw), BF(kw), cosv, sinv, BFM(q), BFM(k), BFM(v), BFM(gate), \
+                                                          rstd, T, n_q, n_kv, R, eps, offset, gated, has_norm)
+  switch (E) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 4: LAUNCH(4); break;
+    case 8: LAUNCH(8); break;
+    default: return -2;
+  }
+#undef LAUNCH
+  return 0;
+}
+int vlmt_qkv_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* dgate, const void* qkv, const void* qw,
+                           const void* kw, const float* cosv, const float* sinv, const float* rstd, void* dqkv, float* dw_partial,
+                           int T, int n_q, int n_kv, int D, int R, int offset, int gated, int has_norm, cudaStream_t st) {
+  const int E = D / 32;
+  const int grid = vlmt_qkv_blocks((long)T * (n_q + 2 * n_kv));
+#define LAUNCH(E_)                                                                                                               \
+  qkv_norm_rope_bwd_kernel<E_><<<grid, kThreads, 0, st>>>(BF(dq), BF(dk), BF(dv), BF(dgate), BF(qkv), BF(qw), BF(kw), cosv, sinv, \
+                                                          rstd, BFM(dqkv), dw_partial, T, n_q, n_kv, R, offset, gated, has_norm)
+  switch (E) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 4: LAUNCH(4); break;
+    case 8: LAUNCH(8); break;
+    default: return -2;
+  }
+#undef LAUNCH
+  return grid;
+}
+
+void vlmt_rope_generic(const void* x, long ss, long hs, const float* cosv, const float* sinv, void* out, long oss, long ohs, int S, int H,
+                       int D, int transpose, cudaStream_t st) {
+  rope_generic_kernel<<<grid_for((long)S * H * (D / 2), 256, 148 * 16), 256, 0, st>>>(BF(x), ss, hs, cosv, sinv, BFM(out), oss, ohs, S, H, D,
+                                                                                    transpose);
+}
+
+void vlmt_gdn_gates_fwd(const void* a, const void* b, long row_stride, const float* A_log, const float* dt_bias, float* g, void* beta,
+                        long T, int H, cudaStream_t st) {
+  gdn_gates_fwd_kernel<<<grid_for(T * H, 256, 148 * 8), 256, 0, st>>>(BF(a), BF(b), row_stride, A_log, dt_bias, g, BFM(beta), T, H);
+}
+int vlmt_gdn_gates_bwd(const float* dg, const void* dbeta, const void* a, const void* b, long row_stride, const float* A_log,
+                       const float* dt_bias, void* da, void* db, long out_stride, float* partial, long T, int H, cudaStream_t st) {
+  const int grid = grid_for(T * H, 256, 148 * 2);
+  gdn_gates_bwd_kernel<<<grid, 256, 2 * H * sizeof(float), st>>>(dg, BF(dbeta), BF(a), BF(b), row_stride, A_log, dt_bias, BFM(da), BFM(db),
+                                                               out_stride, partial, T, H);
+  return grid;
+}
+
+int vlmt_conv1d_silu_fwd(const void* x, long xs, const void* w, const int* seq_idx, void* y, long ys, int T, int C, int K, cudaStream_t st) {
+  if (K != 4 || (C & 7)) return -1;
+  conv1d_silu_fwd_kernel<4><<<grid_for((long)T * (C >> 3), 256, 148 * 16), 256, 0, st>>>(BF(x), xs, BF(w), seq_idx, BFM(y), ys, T, C);
+  return 0;
+}
+int vlmt_conv1d_bwd_slabs(int T) { return (T + 255) / 256; }
+int vlmt_conv1d_silu_bwd(const void* dy, long dys, const void* x, long xs, const void* w, const int* seq_idx, void* dx, long dxs,
+                         float* dw_partial, int T, int C, int K, cudaStream_t st) {
+  if (K != 4) return -1;
+  dim3 grid((C + 127) / 128, vlmt_conv1d_bwd_slabs(T));
+  conv1d_silu_bwd_kernel<4><<<grid, 128, 0, st>>>(BF(dy), dys, BF(x), xs, BF(w), seq_idx, BFM(dx), dxs, dw_partial, T, C, 256);
+  return 0;
+}
+
+void vlmt_rows_update(void* out, const long* index, const void* src, long n_rows, int D, int add, cudaStream_t st) {
+  if (n_rows == 0) return;
+  rows_update_kernel<<<grid_for(n_rows * (D >> 3), 256, 148 * 16), 256, 0, st>>>(BFM(out), index, BF(src), n_rows, D, add);
+}
+void vlmt_rows_gather(void* dst, const long* index, const void* src, long n_rows, int D, cudaStream_t st) {
+  if (n_rows == 0) return;
+  rows_gather_kernel<<<grid_for(n_rows * (D >> 3), 256, 148 * 16), 256, 0, st>>>(BFM(dst), index, BF(src), n_rows, D);
+}
+
+}  // extern "C"

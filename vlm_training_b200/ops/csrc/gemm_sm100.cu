@@ -1,0 +1,351 @@
+// Persistent bf16 GEMM for sm_100a:  D[M,N] (+)= A(M,K) * B(N,K)^T  with fp32 accumulation.
+//
+//   warp 0      TMA producer: per-CTA tiled loads (128-byte swizzle) into a 4-stage smem ring
+//   warp 1      allocates TMEM, one lane issues tcgen05.mma (128 x BN x 16) into one of two
+//               accumulator buffers, commits to the ring's "empty" barriers and to "tmem_full"
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one row per thread), apply
+//               bias / GELU / accumulate, convert to bf16, store
+//
+// Operand layouts (bf16):
+//   A K-major : A stored [M, K] row-major      (activations in a forward linear, dY in dgrad)
+//   A MN-major: A stored [K, M] row-major      (dY in wgrad: contraction over tokens)
+//   B K-major : B stored [N, K] row-major      (weights W[out,in] in a forward linear)
+//   B MN-major: B stored [K, N] row-major      (W in dgrad, X in wgrad)
+// so one kernel covers forward (K,K), dgrad (K,MN) and wgrad (MN,MN) without transposes.
+//
+// The tile loop is static round-robin over a grouped raster (16 M-tiles per group) so the
+// 148 concurrently resident tiles share A and B panels in L2.
+#include "sm100.cuh"
+#include "gemm_sm100.h"
+
+#include <cuda_runtime.h>
+#include <mutex>
+#include <stdio.h>
+
+namespace {
+using namespace sm100;
+
+constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // + barriers + slack for 1024-B alignment
+};
+
+struct Params {
+  int M, N, K;
+  int ldd;             // row stride of D in elements
+  __nv_bfloat16* D;
+  const __nv_bfloat16* bias;  // [N] or null
+  float* Dacc32;       // optional fp32 destination (wgrad into fp32 main grads) or null
+  int epilogue;        // GemmEpilogue
+  int accumulate;      // D += result
+  int* status;
+};
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.f + tanhf(u));
+}
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + erff(x * 0.7071067811865476f)); }
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsz = min(GROUP_M, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int TMEM_COLS = 2 * BN;  // 256 or 512: a power of two >= 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) tmem_alloc<TMEM_COLS>(tmem_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn; tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);               // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)                                    // boxes {64 m, 64 k}
+              tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + 64 * j, k0);
+          }
+          if (!B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)                                   // boxes {64 k, 128 n}
+              tma_load_2d(sb + j * 16384, &tmap_b, &full_bar[stage], k0, n0 + 128 * j);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)                                    // boxes {64 n, 64 k}
+              tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + 64 * j, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      int tm, tn; tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+          }
+          if (p.epilogue == GEMM_EPI_GELU_TANH) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_f(v[i]);
+          } else if (p.epilogue == GEMM_EPI_GELU_ERF) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = gelu_erf_f(v[i]);
+          }
+          if (p.Dacc32 != nullptr) {
+            float* dst = p.Dacc32 + (size_t)row * p.ldd + col0;
+            if (col0 + 32 <= p.N && (p.ldd & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = p.accumulate ? *reinterpret_cast<float4*>(dst + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                o.x += v[i]; o.y += v[i + 1]; o.z += v[i + 2]; o.w += v[i + 3];
+                *reinterpret_cast<float4*>(dst + i) = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = (p.accumulate ? dst[i] : 0.f) + v[i];
+            }
+          } else {
+            __nv_bfloat16* dst = p.D + (size_t)row * p.ldd + col0;
+            if (col0 + 32 <= p.N && (p.ldd & 7) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                if (p.accumulate) {
+                  uint4 old = *reinterpret_cast<const uint4*>(dst + i);
+                  const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(o2[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
+                }
+                uint4 pk;
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                *reinterpret_cast<uint4*>(dst + i) = pk;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
+                float o = p.accumulate ? __bfloat162float(dst[i]) : 0.f;
+                dst[i] = __float2bfloat16(o + v[i]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the smem goes away
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<TMEM_COLS>(tmem_base);
+  }
+}
+
+// -------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+}  // namespace
+
+extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  // The encode call is a driver-API entry point and needs a current context on the calling thread.
+  // Threads that only ever used the runtime API lazily (autograd workers) may not have bound the
+  // primary context yet; cudaSetDevice on the current device binds it.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -4;
+    ctx_bound = true;
+  }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int num_sms, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, NUM_THREADS, L::kTotal, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K,
+                              int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate,
+                              int* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7)) return -2;  // TMA needs 16-byte row strides
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn_major) r = vlmt_make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, 128);
+  else r = vlmt_make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
+  if (r) return 1000 + r;
+  const bool bn256 = N > 128;
+  if (!b_mn_major) r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, 128);
+  else r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
+  if (r) return 2000 + r;
+  Params p;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd;
+  p.D = reinterpret_cast<__nv_bfloat16*>(D);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.Dacc32 = Dacc32;
+  p.epilogue = epilogue; p.accumulate = accumulate; p.status = status;
+#define DISPATCH(BN_)                                                                                     \
+  do {                                                                                                    \
+    if (!a_mn_major && !b_mn_major) return launch_variant<BN_, false, false>(ta, tb, p, num_sms, stream); \
+    if (!a_mn_major && b_mn_major) return launch_variant<BN_, false, true>(ta, tb, p, num_sms, stream);   \
+    if (a_mn_major && b_mn_major) return launch_variant<BN_, true, true>(ta, tb, p, num_sms, stream);     \
+    return launch_variant<BN_, true, false>(ta, tb, p, num_sms, stream);                                  \
+  } while (0)
+  if (bn256) DISPATCH(256);
+  DISPATCH(128);
+#undef DISPATCH
+}

@@ -1,0 +1,24 @@
+// C entry points of the tcgen05 GEMM (gemm_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum GemmEpilogue { GEMM_EPI_NONE = 0, GEMM_EPI_GELU_TANH = 1, GEMM_EPI_GELU_ERF = 2 };
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// D[M,N] (+)= A(M,K) * B(N,K)^T (+ bias[N]) (-> GELU), bf16 in, fp32 accumulate.
+// a_mn_major: A is stored [K, M] (lda = M-stride);  else [M, K].
+// b_mn_major: B is stored [K, N];                    else [N, K].
+// Dacc32 != null: write/accumulate fp32 results there instead of bf16 D.
+// Returns 0 or a CUDA / encode error code; device-side timeouts land in *status.
+int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K, int lda,
+                   int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate, int* status, int num_sms,
+                   cudaStream_t stream);
+// 2-D bf16 tensor map with 128-byte swizzle; `out_map` points at 128 bytes (CUtensorMap).
+int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                           uint32_t box_inner, uint32_t box_outer);
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,170 @@
+// Cross-entropy over one chunk of logits (forward loss + in-place gradient) and the fused
+// AdamW update on flat fp32 master weights with a bf16 parameter write-back.
+#include "loss_optim.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const bf162* p = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  bf162* p = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// One block per row.  Pass 1: online (max, sum-exp) over the row; pass 2: overwrite the row with
+// grad_scale * (softmax - onehot) (zeros when the target is ignore_index).  loss[row] = lse - logit[target].
+constexpr int CE_THREADS = 512;
+__global__ void __launch_bounds__(CE_THREADS)
+ce_fwd_bwd_kernel(bf16* __restrict__ logits, long ld, const long* __restrict__ targets, float* __restrict__ loss, float grad_scale,
+                  int V, long ignore_index) {
+  __shared__ float s_m[CE_THREADS / 32], s_s[CE_THREADS / 32];
+  __shared__ float s_max, s_lse;
+  const long row = blockIdx.x;
+  bf16* lr = logits + row * ld;
+  const long tgt = targets[row];
+  const int nvec = V >> 3;
+  const bool vec_ok = ((ld & 7) == 0) && ((V & 7) == 0);
+  float m = -INFINITY, s = 0.f;
+  auto upd = [&](float x) {
+    if (x > m) { s = s * __expf(m - x) + 1.f; m = x; }
+    else s += __expf(x - m);
+  };
+  if (vec_ok) {
+    const uint4* lv = reinterpret_cast<const uint4*>(lr);
+    for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+      float f[8];
+      unpack8(lv[v], f);
+      float lm = f[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) lm = fmaxf(lm, f[i]);
+      if (lm > m) { s *= __expf(m - lm); m = lm; }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += __expf(f[i] - m);
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += CE_THREADS) upd(__bfloat162float(lr[i]));
+  }
+  // warp then block reduction of (m, s)
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float nm = fmaxf(m, om);
+    s = (m == -INFINITY ? 0.f : s * __expf(m - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+    m = nm;
+  }
+  if ((threadIdx.x & 31) == 0) { s_m[threadIdx.x >> 5] = m; s_s[threadIdx.x >> 5] = s; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float M = s_m[0], S = s_s[0];
+    for (int w = 1; w < CE_THREADS / 32; ++w) {
+      const float nm = fmaxf(M, s_m[w]);
+      S = (M == -INFINITY ? 0.f : S * __expf(M - nm)) + (s_m[w] == -INFINITY ? 0.f : s_s[w] * __expf(s_m[w] - nm));
+      M = nm;
+    }
+    s_max = M;
+    s_lse = M + logf(S);
+    const bool valid = tgt != ignore_index && tgt >= 0 && tgt < V;
+    loss[row] = valid ? (s_lse - __bfloat162float(lr[tgt])) : 0.f;
+  }
+  __syncthreads();
+  const float lse = s_lse;
+  const bool valid = tgt != ignore_index && tgt >= 0 && tgt < V;
+  const float sc = valid ? grad_scale : 0.f;
+  if (vec_ok) {
+    uint4* lv = reinterpret_cast<uint4*>(lr);
+    for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+      float f[8];
+      unpack8(lv[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p = __expf(f[i] - lse);
+        f[i] = sc * (p - ((long)(v * 8 + i) == tgt ? 1.f : 0.f));
+      }
+      lv[v] = pack8(f);
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += CE_THREADS) {
+      const float p = __expf(__bfloat162float(lr[i]) - lse);
+      lr[i] = __float2bfloat16(sc * (p - ((long)i == tgt ? 1.f : 0.f)));
+    }
+  }
+}
+
+// AdamW on a flat range: grads bf16 (or fp32), master/m/v fp32, bf16 parameter written back.
+//   m = b1 m + (1-b1) g ; v = b2 v + (1-b2) g^2 ; p = p (1 - lr wd) - lr * (m / bc1) / (sqrt(v / bc2) + eps)
+template <typename GT>
+__global__ void adamw_kernel(const GT* __restrict__ grad, float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                             bf16* __restrict__ param, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                             float grad_scale) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float g;
+    if constexpr (sizeof(GT) == 2) g = __bfloat162float(grad[i]) * grad_scale; else g = (float)grad[i] * grad_scale;
+    float mi = b1 * m[i] + (1.f - b1) * g;
+    float vi = b2 * v[i] + (1.f - b2) * g * g;
+    float p = master[i] * (1.f - lr * wd);
+    p -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    m[i] = mi; v[i] = vi; master[i] = p;
+    if (param) param[i] = __float2bfloat16(p);
+  }
+}
+
+// sum of squares of a flat bf16/fp32 range -> out[0] (atomic; used for gradient clipping)
+template <typename GT>
+__global__ void sumsq_kernel(const GT* __restrict__ x, long n, float* __restrict__ out) {
+  float acc = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float f;
+    if constexpr (sizeof(GT) == 2) f = __bfloat162float(x[i]); else f = (float)x[i];
+    acc += f * f;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ float sm[32];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sm[w];
+    atomicAdd(out, t);
+  }
+}
+}  // namespace
+
+extern "C" {
+void vlmt_ce_fwd_bwd(void* logits, long ld, const long* targets, float* loss, float grad_scale, int rows, int V, long ignore_index,
+                     cudaStream_t st) {
+  if (rows <= 0) return;
+  ce_fwd_bwd_kernel<<<rows, CE_THREADS, 0, st>>>(reinterpret_cast<bf16*>(logits), ld, targets, loss, grad_scale, V, ignore_index);
+}
+void vlmt_adamw(const void* grad, int grad_fp32, float* master, float* m, float* v, void* param, long n, float lr, float b1, float b2,
+                float eps, float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
+  if (n <= 0) return;
+  long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (grad_fp32)
+    adamw_kernel<float><<<(int)blocks, 256, 0, st>>>((const float*)grad, master, m, v, reinterpret_cast<bf16*>(param), n, lr, b1, b2, eps, wd,
+                                                     bc1, bc2, grad_scale);
+  else
+    adamw_kernel<bf16><<<(int)blocks, 256, 0, st>>>((const bf16*)grad, master, m, v, reinterpret_cast<bf16*>(param), n, lr, b1, b2, eps, wd,
+                                                    bc1, bc2, grad_scale);
+}
+void vlmt_sumsq(const void* x, int fp32, long n, float* out, cudaStream_t st) {
+  if (n <= 0) return;
+  long blocks = (n + 1023) / 1024;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (fp32) sumsq_kernel<float><<<(int)blocks, 256, 0, st>>>((const float*)x, n, out);
+  else sumsq_kernel<bf16><<<(int)blocks, 256, 0, st>>>((const bf16*)x, n, out);
+}
+}

@@ -1,0 +1,15 @@
+// C entry points of the cross-entropy and AdamW kernels (loss_optim.cu).
+#pragma once
+#include <cuda_runtime.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+// In place: logits[rows, V] -> grad_scale * (softmax - onehot); loss[row] = lse - logit[target] (0 if ignored).
+void vlmt_ce_fwd_bwd(void* logits, long ld, const long* targets, float* loss, float grad_scale, int rows, int V, long ignore_index,
+                     cudaStream_t st);
+void vlmt_adamw(const void* grad, int grad_fp32, float* master, float* m, float* v, void* param, long n, float lr, float b1, float b2,
+                float eps, float wd, float bc1, float bc2, float grad_scale, cudaStream_t st);
+void vlmt_sumsq(const void* x, int fp32, long n, float* out, cudaStream_t st);
+#ifdef __cplusplus
+}
+#endif
