@@ -1,0 +1,99 @@
+"""Host-side batch pipeline: a background thread pulls rows from a dataset iterator, pins
+them, and the training thread issues the host→device copies (non-blocking, from pinned
+memory) and builds the :class:`BatchPlan` from the host metadata.
+
+The reference pulls from an energon loader with two worker processes and then syncs with the
+GPU several times per step to derive ``max_seqlen`` / position ids (reference:
+train/train_qwen.py:403-442, models/qwen3_vl/model.py:674-679,765); here everything the
+forward needs is already on the host when the batch arrives.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+
+import numpy as np
+import torch
+
+from ..models.causal_lm import BatchPlan
+from ..models.vision import VisionPlan
+
+_TENSOR_KEYS = ("input_ids", "labels", "cu_seqlens", "pixel_values", "image_grid_thw", "attention_mask", "mm_token_type_ids")
+
+
+class PrefetchLoader:
+    def __init__(self, dataset, depth: int = 2, pin: bool = True):
+        self.dataset = iter(dataset)
+        self.pin = pin and torch.cuda.is_available()
+        self.q: queue.Queue = queue.Queue(maxsize=depth)
+        self._stop = False
+        self.thread = threading.Thread(target=self._work, daemon=True)
+        self.thread.start()
+
+    def _work(self):
+        try:
+            while not self._stop:
+                batch = next(self.dataset)
+                if self.pin:
+                    for k in _TENSOR_KEYS:
+                        if k in batch and torch.is_tensor(batch[k]):
+                            batch[k] = batch[k].pin_memory()
+                self.q.put(batch)
+        except StopIteration:
+            self.q.put(None)
+        except Exception as exc:  # surface worker failures in the training thread
+            self.q.put(exc)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        item = self.q.get()
+        if item is None:
+            raise StopIteration
+        if isinstance(item, Exception):
+            raise item
+        return item
+
+    def close(self):
+        self._stop = True
+
+
+def batch_nbytes(batch: dict) -> int:
+    """Bytes of one batch that cross host→device (tensors + host-built plan tables)."""
+    n = 0
+    for k in ("input_ids", "labels", "cu_seqlens", "pixel_values", "image_grid_thw"):
+        if k in batch and torch.is_tensor(batch[k]):
+            n += batch[k].numel() * batch[k].element_size()
+    for v in batch.get("host", {}).values():
+        if isinstance(v, np.ndarray):
+            n += v.nbytes
+    return n
+
+
+def to_device(batch: dict, cfg, device, pixel_dtype=torch.bfloat16) -> dict:
+    """Copy one batch to ``device`` and assemble the model call's keyword arguments.
+    As in the reference trainer, ``attention_mask`` becomes ``cu_seqlens`` (train/train_qwen.py:420)."""
+    nb = device.type == "cuda"
+    ids = batch["input_ids"].to(device, non_blocking=nb)
+    labels = batch["labels"].to(device, non_blocking=nb)
+    cu = batch["cu_seqlens"].to(device=device, dtype=torch.int32, non_blocking=nb)
+    host = batch.get("host")
+    grids = batch.get("image_grid_thw")
+    kwargs = {"input_ids": ids, "labels": labels, "attention_mask": cu}
+    if host is None:
+        plan = BatchPlan.build(cfg, batch["input_ids"], batch["cu_seqlens"], grids if "pixel_values" in batch else None, device)
+    else:
+        t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=dt, non_blocking=nb)
+        plan = BatchPlan(cu, int(host["max_seqlen"]), t(host["position_ids"], torch.int64))
+        if "seq_idx" in host:
+            plan.seq_idx = t(host["seq_idx"], torch.int32)
+        if "image_rows" in host:
+            plan.image_rows = t(host["image_rows"], torch.int64)
+            plan.image_rows_host = host["image_rows"]
+            plan.vision = VisionPlan.build(grids.tolist(), cfg.vision, device)
+    if "pixel_values" in batch:
+        kwargs["pixel_values"] = batch["pixel_values"].to(device=device, dtype=pixel_dtype, non_blocking=nb)
+        kwargs["image_grid_thw"] = grids
+    kwargs["batch_plan"] = plan
+    return kwargs

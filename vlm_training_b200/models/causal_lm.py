@@ -54,6 +54,14 @@ class BatchPlan:
     image_rows: torch.Tensor | None = None  # int64 rows of the packed sequence that hold image tokens
     vision: VisionPlan | None = None
     extras: dict = field(default_factory=dict)
+    image_rows_host: np.ndarray | None = None
+
+    def local_image_rows(self, lo: int, hi: int, device):
+        """(indices into the vision features, row indices local to the token shard [lo, hi))."""
+        rows = self.image_rows_host
+        sel = np.flatnonzero((rows >= lo) & (rows < hi))
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=torch.int64, non_blocking=True)
+        return t(sel), t(rows[sel] - lo)
 
     @staticmethod
     def build(cfg: ModelConfig, input_ids, cu_seqlens, grids, device, need_seq_idx: bool | None = None) -> "BatchPlan":
@@ -78,6 +86,7 @@ class BatchPlan:
         if grids_l:
             rows = np.flatnonzero(ids == cfg.image_token_id)
             plan.image_rows = t(rows, torch.int64)
+            plan.image_rows_host = rows
             plan.vision = VisionPlan.build(grids_l, cfg.vision, device)
         return plan
 
@@ -126,13 +135,24 @@ class _CausalLMBase(nn.Module):
         dev = dec.embed_tokens.weight.device
         if batch_plan is None:
             batch_plan = BatchPlan.build(cfg, ids, attention_mask, image_grid_thw if pixel_values is not None else None, dev)
-        x = ops.embedding(ids, dec.embed_tokens.weight)
+        tp = getattr(self, "tp", None)
+        sp = tp is not None and tp.enabled and tp.sequence_parallel
+        lo, hi = 0, T
+        if sp:
+            if T % tp.size:
+                raise ValueError(f"sequence parallelism needs the row length ({T}) divisible by tp={tp.size}")
+            lo, hi = tp.rank * (T // tp.size), (tp.rank + 1) * (T // tp.size)
+        x = ops.embedding(ids[lo:hi], dec.embed_tokens.weight)
         deepstack = None
         if pixel_values is not None and self.visual is not None:
             merged, deep = self.visual(pixel_values, image_grid_thw, batch_plan.vision)
             rows = batch_plan.image_rows
             if rows.numel() != merged.shape[0]:
                 raise ValueError(f"{rows.numel()} image tokens in the row but the vision tower produced {merged.shape[0]}")
+            if sp:
+                # keep the image tokens that fall in this rank's token shard (selection built on the host)
+                sel, local_rows = batch_plan.local_image_rows(lo, hi, dev)
+                merged, deep, rows = merged[sel], [d[sel] for d in deep], local_rows
             x = ops.scatter_rows(x, rows, merged)
             deepstack = [(rows, d) for d in deep]
         inv_freq = self._inv_freq(dev)
@@ -142,12 +162,22 @@ class _CausalLMBase(nn.Module):
         want_logits = return_logits if return_logits is not None else labels is None
         logits = None
         if want_logits:
-            logits = ops.linear(x, self.output_weight()).unsqueeze(0)
+            logits = ops.linear(x, self.output_weight())
+            if sp:
+                from ..parallel.tp_comm import gather_rows
+
+                logits = gather_rows(logits, tp)
+            logits = logits.unsqueeze(0)
         if labels is None:
             return logits
         lab = labels.reshape(-1)
         targets = torch.cat((lab[1:], lab.new_full((1,), -100)))  # next-token shift over the whole row
-        loss_sum, n_valid = self._loss(x, targets)
+        loss_sum, n_valid = self._loss(x, targets[lo:hi])
+        if sp:
+            from ..parallel.tp_comm import _ReduceFromTP
+
+            loss_sum = _ReduceFromTP.apply(loss_sum.reshape(1), tp).reshape(())
+            n_valid = (targets != -100).sum()
         loss = loss_sum / n_valid.to(loss_sum.dtype)
         return CausalLMOutput(loss=loss, logits=logits, loss_sum=loss_sum, n_valid=n_valid)
 

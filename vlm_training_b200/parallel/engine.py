@@ -1,0 +1,431 @@
+"""Sharded data-parallel engine: flat parameter / gradient buffers, bucketed gradient
+reduction overlapped with backward, optimizer state sharded across the data-parallel
+ranks, fused AdamW on fp32 master weights, and the parameter all-gather that feeds
+the next forward.
+
+It fills the role of FSDP2 (`fully_shard`) and DDP (`replicate`) in the reference
+(reference: train/infra.py:250-346, train/train_qwen.py:195-200, 273-328) with a
+layout chosen for 180 GB GPUs on NVSwitch:
+
+* bf16 parameters stay whole on every rank between steps (no per-layer re-gather
+  in forward or backward); what is sharded is everything that is 12 of the 16 bytes
+  per parameter: fp32 master weights and both Adam moments.
+* gradients are reduced ONCE per optimizer step (after the last micro-batch), bucket
+  by bucket while backward is still running, by reduce-scatter (``fsdp``) or
+  all-reduce (``ddp``).
+* the update is one fused kernel per bucket segment on the local shard, writing the
+  bf16 parameter shard straight into the flat parameter buffer, followed by an
+  all-gather on the communication stream; the next forward waits per bucket, so the
+  gather of late buckets overlaps the first layers.
+* with ``fused_comm`` the three steps (reduce-scatter, AdamW, all-gather) run as ONE
+  kernel over NVLink peer memory (see :mod:`vlm_training_b200.parallel.fused`).
+
+Two reduction domains exist under tensor parallelism: parameters that are split
+across TP ranks reduce over the data-parallel group only; parameters replicated
+across TP ranks reduce over the whole (dp x tp) world, because with sequence
+parallelism every TP rank holds a partial gradient for them.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+ALIGN = 6720  # lcm(1..8) * 8 elements: every shard boundary for dp <= 8 stays 16-byte aligned
+
+
+@dataclass
+class GroupSpec:
+    """One optimizer parameter group (learning rate multiplier is applied by the scheduler)."""
+
+    name: str
+    params: list
+    lr: float
+    weight_decay: float = 0.0
+    base_lr: float = 0.0
+
+    def __post_init__(self):
+        self.base_lr = self.lr
+
+
+@dataclass
+class _Segment:
+    start: int
+    end: int
+    group: int
+
+
+@dataclass
+class _Bucket:
+    start: int  # offsets into the domain's flat buffers (elements)
+    end: int
+    params: list = field(default_factory=list)
+    segments: list = field(default_factory=list)
+    pending: int = 0
+    reduced: bool = False
+    gather_event: object = None
+    reduce_event: object = None
+
+
+class _Domain:
+    """Flat buffers + process group for one reduction domain."""
+
+    def __init__(self, name, entries, group, grad_scale, shard, device, param_dtype, bucket_elems, state_dtype,
+                 symmetric=False):
+        self.name, self.group, self.shard, self.device = name, group, shard, device
+        self.size = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if (group is not None and dist.is_initialized()) else 0
+        self.grad_scale = grad_scale
+        unit = math.lcm(ALIGN, 8 * self.size)
+        # ---- layout: buckets of whole parameters, each padded to `unit`
+        self.buckets: list[_Bucket] = []
+        off = 0
+        cur = _Bucket(start=0, end=0)
+        self.slots = []  # (param, offset, numel, group_idx)
+        for p, gi in entries:
+            n = p.numel()
+            if cur.params and (off - cur.start) + n > bucket_elems:
+                off = _round_up(off, unit)
+                cur.end = off
+                self.buckets.append(cur)
+                cur = _Bucket(start=off, end=off)
+            self.slots.append((p, off, n, gi))
+            if cur.segments and cur.segments[-1].group == gi:
+                cur.segments[-1].end = off + n
+            else:
+                cur.segments.append(_Segment(off, off + n, gi))
+            cur.params.append(p)
+            off += n
+        off = _round_up(off, unit)
+        cur.end = off
+        if cur.params:
+            self.buckets.append(cur)
+        self.total = off
+        # ---- buffers
+        alloc = _symmetric_empty if symmetric else (lambda n, dt, dev, grp: torch.zeros(n, dtype=dt, device=dev))
+        self.flat_param = alloc(self.total, param_dtype, device, group)
+        self.flat_grad = alloc(self.total, param_dtype, device, group)
+        self.flat_grad.zero_()
+        with torch.no_grad():
+            for p, o, n, _ in self.slots:
+                self.flat_param[o:o + n].copy_(p.detach().reshape(-1))
+                p.data = self.flat_param[o:o + n].view(p.shape)
+                p.grad = self.flat_grad[o:o + n].view(p.shape)
+        self.param_bucket = {}
+        for b in self.buckets:
+            for p in b.params:
+                self.param_bucket[p] = b
+        # ---- optimizer state on the local shard of every bucket
+        self.master, self.exp_avg, self.exp_avg_sq = [], [], []
+        for b in self.buckets:
+            lo, hi = self.shard_range(b)
+            self.master.append(self.flat_param[lo:hi].float().clone())
+            self.exp_avg.append(torch.zeros(hi - lo, dtype=state_dtype, device=device))
+            self.exp_avg_sq.append(torch.zeros(hi - lo, dtype=state_dtype, device=device))
+
+    def shard_range(self, b: _Bucket):
+        if not self.shard or self.size == 1:
+            return b.start, b.end
+        n = (b.end - b.start) // self.size
+        return b.start + self.rank * n, b.start + (self.rank + 1) * n
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def _symmetric_empty(n, dtype, device, group):
+    from .symm import symmetric_zeros
+
+    return symmetric_zeros(n, dtype, device, group)
+
+
+class ShardedOptimizerEngine(torch.optim.Optimizer):
+    """Owns the model's trainable parameters as flat buffers and performs
+    gradient synchronisation + AdamW + parameter redistribution.
+
+    ``step()`` = finish gradient reduction → (optional clip) → fused AdamW on shards →
+    all-gather parameters.  ``zero_grad()`` clears the flat gradient buffers.
+    ``param_groups`` mimics ``torch.optim.Optimizer.param_groups`` enough for
+    ``LambdaLR`` (keys ``lr`` / ``initial_lr``)."""
+
+    def __init__(self, model, groups: list[GroupSpec], *, dp_group=None, world_group=None, tp_size: int = 1,
+                 mode: str = "fsdp", betas=(0.9, 0.999), eps: float = 1e-8, max_grad_norm: float | None = None,
+                 bucket_mb: float = 256.0, state_dtype=torch.float32, fused_comm: bool = False, overlap: bool = True):
+        pgs = [{"params": list(g.params), "lr": g.lr, "weight_decay": g.weight_decay, "name": g.name} for g in groups]
+        super().__init__(pgs, defaults={"lr": groups[0].lr, "weight_decay": 0.0})
+        self.model = model
+        self.groups = groups
+        self.betas, self.eps, self.max_grad_norm = betas, eps, max_grad_norm
+        self.mode = mode
+        self.step_count = 0
+        self.fused_comm = fused_comm
+        self.overlap = overlap
+        params = [p for g in groups for p in g.params]
+        if not params:
+            raise ValueError("no trainable parameters")
+        device = params[0].device
+        self.device = device
+        self.is_cuda = device.type == "cuda"
+        pdtype = params[0].dtype
+        group_of = {p: gi for gi, g in enumerate(groups) for p in g.params}
+        dp_size = dist.get_world_size(dp_group) if (dist.is_initialized() and dp_group is not None) else (
+            dist.get_world_size() if dist.is_initialized() and tp_size == 1 else 1)
+        self.dp_size = dp_size
+        shard = mode == "fsdp"
+        bucket_elems = int(bucket_mb * (1 << 20) / params[0].element_size())
+        # parameter order = registration order (≈ forward order): late buckets finish first in backward
+        ordered = [p for p in model.parameters() if p in group_of]
+        sharded = [(p, group_of[p]) for p in ordered if getattr(p, "_tp_sharded", False)]
+        replicated = [(p, group_of[p]) for p in ordered if not getattr(p, "_tp_sharded", False)]
+        self.domains: list[_Domain] = []
+        symmetric = fused_comm and self.is_cuda and dist.is_initialized()
+        if tp_size > 1:
+            if sharded:
+                self.domains.append(_Domain("tp_sharded", sharded, dp_group, 1.0 / dp_size, shard, device, pdtype,
+                                            bucket_elems, state_dtype, symmetric))
+            if replicated:
+                with torch.no_grad():
+                    self._identical = [p for p, _ in replicated if getattr(p, "_tp_grad", "partial") == "identical"]
+                self.domains.append(_Domain("tp_replicated", replicated, world_group, 1.0 / dp_size, shard, device, pdtype,
+                                            bucket_elems, state_dtype, symmetric))
+            self._identical_scale = 1.0 / tp_size
+        else:
+            self._identical = []
+            self.domains.append(_Domain("all", replicated + sharded, dp_group if dp_group is not None else world_group,
+                                        1.0 / dp_size, shard, device, pdtype, bucket_elems, state_dtype, symmetric))
+        self.comm_stream = torch.cuda.Stream(device=device) if self.is_cuda else None
+        self._hooks = []
+        self._sync_grads = True
+        if self.is_cuda and overlap and dist.is_initialized():
+            self._install_hooks()
+        if self.is_cuda:
+            self._install_forward_waits()
+        self._clip_buf = torch.zeros(1, dtype=torch.float32, device=device)
+        self.last_grad_norm = None
+
+    # ------------------------------------------------------------------ torch.optim surface
+    def zero_grad(self, set_to_none: bool = False):
+        for d in self.domains:
+            d.flat_grad.zero_()
+            for b in d.buckets:
+                b.pending = len(b.params)
+                b.reduced = False
+                b.reduce_event = None
+
+    def set_requires_gradient_sync(self, flag: bool):
+        """False on all but the last micro-batch of an accumulation window."""
+        self._sync_grads = flag
+
+    # ------------------------------------------------------------------ overlap plumbing
+    def _install_hooks(self):
+        for d in self.domains:
+            for b in d.buckets:
+                b.pending = len(b.params)
+                for p in b.params:
+                    self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(d, b)))
+
+    def _make_hook(self, d, b):
+        def hook(_p):
+            if not self._sync_grads:
+                return
+            b.pending -= 1
+            if b.pending == 0 and not b.reduced:
+                self._reduce_bucket(d, b)
+        return hook
+
+    def _install_forward_waits(self):
+        """Before a module's forward, wait for the all-gather of the buckets that hold its parameters."""
+        engine = self
+
+        def pre_hook(mod, _args):
+            for p in mod._parameters.values():
+                if p is None:
+                    continue
+                for d in engine.domains:
+                    b = d.param_bucket.get(p)
+                    if b is not None and b.gather_event is not None:
+                        torch.cuda.current_stream().wait_event(b.gather_event)
+                        b.gather_event = None
+        for mod in self.model.modules():
+            if any(p is not None for p in mod._parameters.values()):
+                self._hooks.append(mod.register_forward_pre_hook(pre_hook))
+
+    def wait_all_gathers(self):
+        if not self.is_cuda:
+            return
+        for d in self.domains:
+            for b in d.buckets:
+                if b.gather_event is not None:
+                    torch.cuda.current_stream().wait_event(b.gather_event)
+                    b.gather_event = None
+
+    # ------------------------------------------------------------------ gradient reduction
+    def _reduce_bucket(self, d: _Domain, b: _Bucket):
+        b.reduced = True
+        if d.size == 1 or not dist.is_initialized():
+            return
+        g = d.flat_grad[b.start:b.end]
+        if self._identical and d.name == "tp_replicated":
+            for p in b.params:
+                if getattr(p, "_tp_grad", "partial") == "identical":
+                    p.grad.mul_(self._identical_scale)
+        if self.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                self._collective_reduce(d, b, g)
+                b.reduce_event = torch.cuda.Event()
+                b.reduce_event.record(self.comm_stream)
+        else:
+            self._collective_reduce(d, b, g)
+
+    def _collective_reduce(self, d, b, g):
+        if d.shard and g.is_cuda:
+            lo, hi = d.shard_range(b)
+            dist.reduce_scatter_tensor(d.flat_grad[lo:hi], g, op=dist.ReduceOp.SUM, group=d.group)
+        else:
+            # ddp mode, and gloo (which has no reduce-scatter): all-reduce the bucket
+            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=d.group)
+
+    def finish_grad_sync(self):
+        for d in self.domains:
+            for b in d.buckets:
+                if not b.reduced:
+                    self._reduce_bucket(d, b)
+        if self.is_cuda:
+            for d in self.domains:
+                for b in d.buckets:
+                    if b.reduce_event is not None:
+                        torch.cuda.current_stream().wait_event(b.reduce_event)
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self, closure=None):
+        self.step_count += 1
+        if self.fused_comm and self.is_cuda and dist.is_initialized() and self.max_grad_norm is None:
+            from .fused import fused_reduce_adamw_gather
+
+            if fused_reduce_adamw_gather(self):
+                return
+        self.finish_grad_sync()
+        clip = 1.0
+        if self.max_grad_norm is not None:
+            clip = self._clip_coefficient()
+        b1, b2 = self.betas
+        for d in self.domains:
+            for bi, b in enumerate(d.buckets):
+                lo, hi = d.shard_range(b)
+                for seg in b.segments:
+                    s, e = max(seg.start, lo), min(seg.end, hi)
+                    if e <= s:
+                        continue
+                    pg = self.param_groups[seg.group]
+                    self._adamw(d, bi, s - lo, e - lo, d.flat_grad[s:e], d.flat_param[s:e], pg["lr"], pg["weight_decay"],
+                                b1, b2, d.grad_scale * clip)
+                self._gather_bucket(d, b)
+
+    def _adamw(self, d, bi, s, e, grad, param, lr, wd, b1, b2, grad_scale):
+        master, m, v = d.master[bi][s:e], d.exp_avg[bi][s:e], d.exp_avg_sq[bi][s:e]
+        if self.is_cuda and m.dtype == torch.float32 and param.dtype == torch.bfloat16:
+            from ..ops import cuda as cu
+
+            cu.adamw_step_(grad, master, m, v, param, lr, b1, b2, self.eps, wd, self.step_count, grad_scale)
+            return
+        g = grad.float() * grad_scale
+        mf, vf = m.float(), v.float()
+        mf.mul_(b1).add_(g, alpha=1 - b1)
+        vf.mul_(b2).addcmul_(g, g, value=1 - b2)
+        bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+        master.mul_(1 - lr * wd)
+        master.addcdiv_(mf / bc1, (vf / bc2).sqrt_().add_(self.eps), value=-lr)
+        m.copy_(mf)
+        v.copy_(vf)
+        param.copy_(master)
+
+    def _gather_bucket(self, d: _Domain, b: _Bucket):
+        if not d.shard or d.size == 1 or not dist.is_initialized():
+            return
+        lo, hi = d.shard_range(b)
+        if self.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                dist.all_gather_into_tensor(d.flat_param[b.start:b.end], d.flat_param[lo:hi], group=d.group)
+                b.gather_event = torch.cuda.Event()
+                b.gather_event.record(self.comm_stream)
+        else:
+            shard = d.flat_param[lo:hi].clone()
+            dist.all_gather_into_tensor(d.flat_param[b.start:b.end], shard, group=d.group)
+
+    def _clip_coefficient(self) -> float:
+        """Global gradient norm over every reduced shard (each element counted once) → clip factor."""
+        self._clip_buf.zero_()
+        for d in self.domains:
+            for b in d.buckets:
+                lo, hi = d.shard_range(b)
+                g = d.flat_grad[lo:hi]
+                if self.is_cuda and g.dtype in (torch.bfloat16, torch.float32):
+                    from ..ops import cuda as cu
+
+                    part = torch.zeros(1, dtype=torch.float32, device=self.device)
+                    cu.sumsq_(g, part)
+                else:
+                    part = g.float().pow(2).sum().reshape(1)
+                self._clip_buf += part * (d.grad_scale ** 2) / (1 if d.shard else d.size)
+        if dist.is_initialized():
+            dist.all_reduce(self._clip_buf)
+            if self.domains[0].name == "tp_sharded":
+                pass  # shards are disjoint across the world in both domains: a plain sum is exact
+        norm = float(self._clip_buf.sqrt().item())
+        self.last_grad_norm = norm
+        return min(1.0, self.max_grad_norm / (norm + 1e-6))
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self) -> dict:
+        out = {"step": self.step_count, "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
+        for d in self.domains:
+            out[d.name] = {
+                "master": torch.cat(d.master), "exp_avg": torch.cat(d.exp_avg), "exp_avg_sq": torch.cat(d.exp_avg_sq),
+                "layout": {"total": d.total, "size": d.size, "rank": d.rank, "shard": d.shard,
+                           "buckets": [(b.start, b.end) for b in d.buckets]}}
+        return out
+
+    def load_state_dict(self, state: dict):
+        self.step_count = int(state["step"])
+        for pg, saved in zip(self.param_groups, state["param_groups"]):
+            pg.update({k: v for k, v in saved.items() if k in ("lr", "initial_lr", "weight_decay")})
+        for d in self.domains:
+            s = state[d.name]
+            for name, dst in (("master", d.master), ("exp_avg", d.exp_avg), ("exp_avg_sq", d.exp_avg_sq)):
+                off = 0
+                for t in dst:
+                    t.copy_(s[name][off:off + t.numel()])
+                    off += t.numel()
+            # parameters follow the master copy
+            for bi, b in enumerate(d.buckets):
+                lo, hi = d.shard_range(b)
+                d.flat_param[lo:hi].copy_(d.master[bi])
+                self._gather_bucket(d, b)
+        self.wait_all_gathers()
+
+    def resync_master_from_params(self):
+        """Re-read the master weights from the (bf16) parameters, e.g. after loading a model checkpoint."""
+        with torch.no_grad():
+            for d in self.domains:
+                for bi, b in enumerate(d.buckets):
+                    lo, hi = d.shard_range(b)
+                    d.master[bi].copy_(d.flat_param[lo:hi])
+
+    def memory_bytes(self) -> dict:
+        tot = {"param": 0, "grad": 0, "optimizer": 0}
+        for d in self.domains:
+            tot["param"] += d.flat_param.numel() * d.flat_param.element_size()
+            tot["grad"] += d.flat_grad.numel() * d.flat_grad.element_size()
+            for t in d.master + d.exp_avg + d.exp_avg_sq:
+                tot["optimizer"] += t.numel() * t.element_size()
+        return tot
