@@ -84,7 +84,7 @@ def test_linear_autograd_matches_torch():
 
 
 @pytest.mark.parametrize("offset", [False, True])
-@pytest.mark.parametrize("D", [128, 4096, 1152])
+@pytest.mark.parametrize("D", [128, 4096, 1152, 8192])
 def test_rms_norm_fwd_bwd(D, offset):
     x = _rand(777, D).requires_grad_()
     w = _rand(D, scale=0.3).requires_grad_()
@@ -117,8 +117,8 @@ def test_add_rms_norm_fwd_bwd():
     _close(w.grad, wr.grad, 0.5, 2e-2, "dw")
 
 
-def test_layer_norm_fwd_bwd():
-    D = 1152
+@pytest.mark.parametrize("D", [1152, 4608])
+def test_layer_norm_fwd_bwd(D):
     x = _rand(500, D).requires_grad_()
     w, b = _rand(D, scale=0.5).requires_grad_(), _rand(D, scale=0.5).requires_grad_()
     y = ops.layer_norm(x, w, b, 1e-6)

@@ -20,9 +20,22 @@ def _gen(device, seed: int) -> torch.Generator:
     return g
 
 
+_CUDA_GENS = {}
+
+
 def _normal_(p: torch.Tensor, std: float, gen: torch.Generator):
-    # draw on the CPU in fp32 so the values do not depend on device or dtype
     with torch.no_grad():
+        if p.is_cuda:
+            # large models are initialised in place on the GPU; the device generator is seeded from the
+            # host generator so every rank (same seed, same GPU type) draws the same values
+            key = (p.device, id(gen))
+            if key not in _CUDA_GENS:
+                g = torch.Generator(device=p.device)
+                g.manual_seed(int(torch.randint(0, 2 ** 31 - 1, (1,), generator=gen)))
+                _CUDA_GENS[key] = g
+            p.normal_(0.0, std, generator=_CUDA_GENS[key])
+            return
+        # CPU: draw in fp32 chunks so the values do not depend on the parameter dtype
         chunk = 1 << 24
         flat = p.view(-1)
         for s in range(0, flat.numel(), chunk):

@@ -337,6 +337,7 @@ Tensor status() { return status_tensor(); }
 torch::Tensor vlmt_status_tensor() { return status_tensor(); }
 
 void bind_attention(pybind11::module_& m);
+void bind_comm(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
@@ -366,4 +367,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq_", &sumsq_);
   m.def("status", &status);
   bind_attention(m);
+  bind_comm(m);
 }

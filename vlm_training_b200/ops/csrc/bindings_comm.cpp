@@ -1,0 +1,44 @@
+// Bindings of the fused collective kernels.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "comm_kernels.h"
+
+using torch::Tensor;
+
+// state tensors are the local shard (fp32); `state_off` is the element offset of `lo` inside them
+static void fused_rs_adamw_ag(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, int64_t grad_mc,
+                              int64_t param_mc, int64_t world, int64_t lo, int64_t hi, Tensor& master, Tensor& m, Tensor& v,
+                              int64_t state_off, double lr, double b1, double b2, double eps, double wd, double bc1, double bc2,
+                              double grad_scale) {
+  TORCH_CHECK((int64_t)grad_ptrs.size() == world && (int64_t)param_ptrs.size() == world);
+  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(lo % 8 == 0 && hi % 8 == 0 && state_off % 8 == 0, "shard segment must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(master.device());
+  void* g[16];
+  void* p[16];
+  TORCH_CHECK(world <= 16);
+  for (int i = 0; i < world; ++i) { g[i] = reinterpret_cast<void*>(grad_ptrs[i]); p[i] = reinterpret_cast<void*>(param_ptrs[i]); }
+  int r = vlmt_fused_rs_adamw_ag(g, p, reinterpret_cast<void*>(grad_mc), reinterpret_cast<void*>(param_mc), (int)world, lo, hi,
+                                 master.data_ptr<float>() + state_off, m.data_ptr<float>() + state_off, v.data_ptr<float>() + state_off,
+                                 (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, (float)bc1, (float)bc2, (float)grad_scale,
+                                 at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_fused_rs_adamw_ag failed with code ", r);
+}
+
+static void peer_sum_rows(const std::vector<int64_t>& partial_ptrs, int64_t row0, const c10::optional<Tensor>& residual, Tensor& out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  void* p[16];
+  const int world = (int)partial_ptrs.size();
+  TORCH_CHECK(world <= 16 && out.is_contiguous() && out.scalar_type() == at::kBFloat16);
+  for (int i = 0; i < world; ++i) p[i] = reinterpret_cast<void*>(partial_ptrs[i]);
+  int r = vlmt_peer_sum_rows(p, world, row0, out.size(0), (int)out.size(1), residual.has_value() ? residual->data_ptr() : nullptr,
+                             out.data_ptr(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_peer_sum_rows failed with code ", r);
+}
+
+void bind_comm(pybind11::module_& m) {
+  m.def("fused_rs_adamw_ag", &fused_rs_adamw_ag);
+  m.def("peer_sum_rows", &peer_sum_rows);
+}

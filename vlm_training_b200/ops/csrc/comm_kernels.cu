@@ -1,0 +1,175 @@
+// Collectives fused with their adjacent compute, over NVLink / NVSwitch peer memory.
+//
+// fused_rs_adamw_ag: ONE kernel per bucket does gradient reduce-scatter + fp32 AdamW + parameter
+// all-gather.  Every rank owns a contiguous shard [lo, hi) of the bucket.  For its shard it
+//   1. reads the bf16 gradients of ALL ranks (plain 16-byte peer loads, or one multimem.ld_reduce
+//      through the switch when a multicast mapping is available) and sums them in fp32,
+//   2. updates its fp32 master weights and Adam moments (local HBM),
+//   3. stores the new bf16 parameters into the flat parameter buffer of EVERY rank
+//      (peer stores, or one multimem.st).
+// Gradient bytes cross NVLink once, parameter bytes once; nothing is staged.  The kernel contains
+// no waits: the caller orders it after all ranks have finished writing their gradients and
+// before any rank reads parameters (two tiny NCCL collectives on the communication stream).
+//
+// peer_sum_rows: out[r, :] = sum over ranks of partial_rank[r, :] for the rows a rank owns
+// (tensor-parallel reduce-scatter), optionally fused with a residual add.
+#include "comm_kernels.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+constexpr int MAX_PEERS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_PEERS];
+};
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const bf162* p = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  bf162* p = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ uint4 ld_peer_16B(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+// sum of 8 bf16 over all devices of the multicast group, accumulated in fp32 inside the switch
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_ptr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_16B(void* mc_ptr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+struct AdamArgs {
+  float lr, b1, b2, eps, wd, bc1, bc2, grad_scale;
+};
+
+// elements [lo, hi) of the bucket-relative flat buffers; lo, hi multiples of 8
+template <bool MULTIMEM>
+__global__ void fused_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, void* grad_mc, void* param_mc, int world, long lo, long hi,
+                                         float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, AdamArgs a) {
+  const long nvec = (hi - lo) >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    const long e = lo + (i << 3);
+    float g[8];
+    if (MULTIMEM) {
+      unpack8(multimem_ld_reduce_bf16x8(reinterpret_cast<const bf16*>(grad_mc) + e), g);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        float t[8];
+        unpack8(ld_peer_16B(reinterpret_cast<const bf16*>(grads.p[r]) + e), t);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] += t[k];
+      }
+    }
+    const long s = i << 3;  // offset into the local shard state
+    float pm[8], mm[8], vv[8];
+    {
+      const float4* p4 = reinterpret_cast<const float4*>(master + s);
+      const float4* m4 = reinterpret_cast<const float4*>(m + s);
+      const float4* v4 = reinterpret_cast<const float4*>(v + s);
+      float4 x0 = p4[0], x1 = p4[1], y0 = m4[0], y1 = m4[1], z0 = v4[0], z1 = v4[1];
+      pm[0] = x0.x; pm[1] = x0.y; pm[2] = x0.z; pm[3] = x0.w; pm[4] = x1.x; pm[5] = x1.y; pm[6] = x1.z; pm[7] = x1.w;
+      mm[0] = y0.x; mm[1] = y0.y; mm[2] = y0.z; mm[3] = y0.w; mm[4] = y1.x; mm[5] = y1.y; mm[6] = y1.z; mm[7] = y1.w;
+      vv[0] = z0.x; vv[1] = z0.y; vv[2] = z0.z; vv[3] = z0.w; vv[4] = z1.x; vv[5] = z1.y; vv[6] = z1.z; vv[7] = z1.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = g[k] * a.grad_scale;
+      mm[k] = a.b1 * mm[k] + (1.f - a.b1) * gk;
+      vv[k] = a.b2 * vv[k] + (1.f - a.b2) * gk * gk;
+      float p = pm[k] * (1.f - a.lr * a.wd);
+      p -= a.lr * (mm[k] / a.bc1) / (sqrtf(vv[k] / a.bc2) + a.eps);
+      pm[k] = p;
+    }
+    {
+      float4* p4 = reinterpret_cast<float4*>(master + s);
+      float4* m4 = reinterpret_cast<float4*>(m + s);
+      float4* v4 = reinterpret_cast<float4*>(v + s);
+      p4[0] = make_float4(pm[0], pm[1], pm[2], pm[3]); p4[1] = make_float4(pm[4], pm[5], pm[6], pm[7]);
+      m4[0] = make_float4(mm[0], mm[1], mm[2], mm[3]); m4[1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+      v4[0] = make_float4(vv[0], vv[1], vv[2], vv[3]); v4[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    }
+    const uint4 packed = pack8(pm);
+    if (MULTIMEM) {
+      multimem_st_16B(reinterpret_cast<bf16*>(param_mc) + e, packed);
+    } else {
+      for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(params.p[r]) + e) = packed;
+    }
+  }
+}
+
+// out[row, :] = (residual ? residual[row, :] : 0) + sum_r partial_r[row0 + row, :]   (bf16, fp32 accumulation)
+__global__ void peer_sum_rows_kernel(PeerPtrs partials, int world, long row0, long rows, int D, const bf16* __restrict__ residual,
+                                     bf16* __restrict__ out) {
+  const int vper = D >> 3;
+  const long nvec = rows * vper;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / vper;
+    const int c = (int)(i - row * vper);
+    float acc[8];
+    if (residual) unpack8(reinterpret_cast<const uint4*>(residual + row * D)[c], acc);
+    else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    }
+    for (int r = 0; r < world; ++r) {
+      float t[8];
+      unpack8(ld_peer_16B(reinterpret_cast<const bf16*>(partials.p[r]) + (row0 + row) * D + c * 8), t);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += t[k];
+    }
+    reinterpret_cast<uint4*>(out + row * D)[c] = pack8(acc);
+  }
+}
+}  // namespace
+
+extern "C" {
+int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* grad_mc, void* param_mc, int world, long lo, long hi,
+                           float* master, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                           float grad_scale, cudaStream_t st) {
+  if (world > MAX_PEERS) return -1;
+  if ((lo & 7) || (hi & 7)) return -2;
+  if (hi <= lo) return 0;
+  PeerPtrs g, p;
+  for (int r = 0; r < world; ++r) { g.p[r] = grad_ptrs[r]; p.p[r] = param_ptrs[r]; }
+  AdamArgs a{lr, b1, b2, eps, wd, bc1, bc2, grad_scale};
+  long blocks = (((hi - lo) >> 3) + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (grad_mc && param_mc)
+    fused_rs_adamw_ag_kernel<true><<<(int)blocks, 256, 0, st>>>(g, p, grad_mc, param_mc, world, lo, hi, master, m, v, a);
+  else
+    fused_rs_adamw_ag_kernel<false><<<(int)blocks, 256, 0, st>>>(g, p, nullptr, nullptr, world, lo, hi, master, m, v, a);
+  return (int)cudaGetLastError();
+}
+int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st) {
+  if (world > MAX_PEERS || (D & 7)) return -1;
+  if (rows <= 0) return 0;
+  PeerPtrs p;
+  for (int r = 0; r < world; ++r) p.p[r] = partial_ptrs[r];
+  long blocks = (rows * (D >> 3) + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  peer_sum_rows_kernel<<<(int)blocks, 256, 0, st>>>(p, world, row0, rows, D, reinterpret_cast<const bf16*>(residual),
+                                                    reinterpret_cast<bf16*>(out));
+  return (int)cudaGetLastError();
+}
+}

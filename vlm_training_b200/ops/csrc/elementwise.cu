@@ -95,11 +95,12 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __re
                                    float* __restrict__ dw_partial, int rows, int D, int offset) {
   extern __shared__ float sm_dw[];  // [kWarpsPerBlock][D]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
   const int nvec = D >> 3;
   float* my_dw = sm_dw + (size_t)warp * D;
   for (int i = lane; i < D; i += 32) my_dw[i] = 0.f;
   __syncwarp();
-  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+  for (int row = blockIdx.x * nwarps + warp; row < rows; row += gridDim.x * nwarps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
     const float rs = rstd[row];
@@ -142,8 +143,7 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __re
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float s = 0.f;
-#pragma unroll
-    for (int wi = 0; wi < kWarpsPerBlock; ++wi) s += sm_dw[(size_t)wi * D + i];
+for (int wi = 0; wi < nwarps; ++wi) s += sm_dw[(size_t)wi * D + i];
     dw_partial[(size_t)blockIdx.x * D + i] = s;
   }
 }
@@ -190,12 +190,13 @@ __global__ void layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __
                                      float* __restrict__ dw_partial, float* __restrict__ db_partial, int rows, int D) {
   extern __shared__ float sm_acc[];  // [kWarpsPerBlock][2][D]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
   const int nvec = D >> 3;
   float* my_dw = sm_acc + (size_t)warp * 2 * D;
   float* my_db = my_dw + D;
   for (int i = lane; i < 2 * D; i += 32) my_dw[i] = 0.f;
   __syncwarp();
-  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+  for (int row = blockIdx.x * nwarps + warp; row < rows; row += gridDim.x * nwarps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * D);
     const float mu = mean[row], rs = rstd[row];
@@ -232,8 +233,7 @@ __global__ void layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float a = 0.f, c = 0.f;
-#pragma unroll
-    for (int wi = 0; wi < kWarpsPerBlock; ++wi) { a += sm_acc[(size_t)wi * 2 * D + i]; c += sm_acc[(size_t)wi * 2 * D + D + i]; }
+for (int wi = 0; wi < nwarps; ++wi) { a += sm_acc[(size_t)wi * 2 * D + i]; c += sm_acc[(size_t)wi * 2 * D + D + i]; }
     dw_partial[(size_t)blockIdx.x * D + i] = a;
     db_partial[(size_t)blockIdx.x * D + i] = c;
   }
@@ -261,10 +261,11 @@ __global__ void rmsnorm_gated_bwd_kernel(const bf16* __restrict__ dy, const bf16
                                          bf16* __restrict__ dz, float* __restrict__ dw_partial, int rows, int D) {
   extern __shared__ float sm_dw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
   float* my_dw = sm_dw + (size_t)warp * D;
   for (int i = lane; i < D; i += 32) my_dw[i] = 0.f;
   __syncwarp();
-  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < rows; row += gridDim.x * kWarpsPerBlock) {
+  for (int row = blockIdx.x * nwarps + warp; row < rows; row += gridDim.x * nwarps) {
     const float rs = rstd[row];
     float dot = 0.f;
     for (int i = lane; i < D; i += 32) {
@@ -287,8 +288,7 @@ __global__ void rmsnorm_gated_bwd_kernel(const bf16* __restrict__ dy, const bf16
   __syncthreads();
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float s = 0.f;
-#pragma unroll
-    for (int wi = 0; wi < kWarpsPerBlock; ++wi) s += sm_dw[(size_t)wi * D + i];
+for (int wi = 0; wi < nwarps; ++wi) s += sm_dw[(size_t)wi * D + i];
     dw_partial[(size_t)blockIdx.x * D + i] = s;
   }
 }
@@ -757,6 +757,13 @@ extern "C" {
 
 int vlmt_norm_blocks(int rows) { return grid_for(rows, kWarpsPerBlock, 148 * 4); }
 
+// warps per block of the backward norm kernels: each warp owns `floats_per_warp` fp32 accumulators in smem
+static int bwd_warps(size_t floats_per_warp) {
+  int w = (int)((200 * 1024) / (floats_per_warp * sizeof(float)));
+  if (w > kWarpsPerBlock) w = kWarpsPerBlock;
+  return w < 1 ? 0 : w;
+}
+
 void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32, void* y, void* r_out, float* rstd, int rows, int D,
                       float eps, int offset, cudaStream_t st) {
   const int grid = grid_for(rows, kWarpsPerBlock, 148 * 8);
@@ -769,15 +776,18 @@ void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32,
 int vlmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, int w_fp32, const float* rstd, const void* dres, void* dx,
                      float* dw_partial, int rows, int D, int offset, cudaStream_t st) {
   const int grid = vlmt_norm_blocks(rows);
-  const size_t smem = (size_t)kWarpsPerBlock * D * sizeof(float);
+  const int nw = bwd_warps(D);
+  if (nw == 0) return -1;
+  const size_t smem = (size_t)nw * D * sizeof(float);
+  const int kThreadsDyn = nw * 32;
   if (w_fp32) {
     auto k = rmsnorm_bwd_kernel<float>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<grid, kThreads, smem, st>>>(BF(dy), BF(x), (const float*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset);
+    k<<<grid, kThreadsDyn, smem, st>>>(BF(dy), BF(x), (const float*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset);
   } else {
     auto k = rmsnorm_bwd_kernel<bf16>;
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<grid, kThreads, smem, st>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset);
+    k<<<grid, kThreadsDyn, smem, st>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset);
   }
   return grid;
 }
@@ -789,9 +799,11 @@ void vlmt_layernorm_fwd(const void* x, const void* w, const void* b, void* y, fl
 int vlmt_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx, float* dw_partial,
                        float* db_partial, int rows, int D, cudaStream_t st) {
   const int grid = vlmt_norm_blocks(rows);
-  const size_t smem = (size_t)kWarpsPerBlock * 2 * D * sizeof(float);
+  const int nw = bwd_warps(2 * (size_t)D);
+  if (nw == 0) return -1;
+  const size_t smem = (size_t)nw * 2 * D * sizeof(float);
   cudaFuncSetAttribute(layernorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  layernorm_bwd_kernel<<<grid, kThreads, smem, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D);
+  layernorm_bwd_kernel<<<grid, nw * 32, smem, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D);
   return grid;
 }
 

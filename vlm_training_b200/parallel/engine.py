@@ -86,6 +86,7 @@ class _Domain:
         self.slots = []  # (param, offset, numel, group_idx)
         for p, gi in entries:
             n = p.numel()
+            off = _round_up(off, 8)  # every parameter starts on a 16-byte boundary (bf16)
             if cur.params and (off - cur.start) + n > bucket_elems:
                 off = _round_up(off, unit)
                 cur.end = off

@@ -68,7 +68,7 @@ class Trainer:
             mcfg = ModelConfig.preset(cfg.model.preset)
             if cfg.model.dsa:
                 mcfg.text.dsa, mcfg.text.dsa_topk = True, cfg.model.dsa_topk
-            model = cls.from_config(mcfg, dtype=dtype, device="cpu", init=False)
+            model = cls.from_config(mcfg, dtype=dtype, device=self.device, init=False)
             init_normal_(model, 0.02, seed=t.seed)
         self.model_config = mcfg
         self.seq_len = int(cfg.data.seq_len)
