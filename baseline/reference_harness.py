@@ -141,12 +141,15 @@ def run(args):
     optimizer = torch.optim.AdamW(groups, lr=2e-6, foreach=True, weight_decay=0.01)
 
     spec = SyntheticSpec(kind="vlm", seq_len=args.seq_len, vocab_size=t.vocab_size, seed=42)
-    data = iter(SyntheticDataset(spec, ours, dp_rank=dp_rank, dp_size=dp_size))
+    # rows are produced and pinned by a background thread, like the reference's loader workers
+    # (num_workers=2, reference: train/train_qwen.py:239-250); the timed loop only does the H2D copies
+    from vlm_training_b200.data.loader import PrefetchLoader
+
+    data = PrefetchLoader(SyntheticDataset(spec, ours, dp_rank=dp_rank, dp_size=dp_size), depth=3)
 
     def host_batch():
         b = next(data)
-        return {k: (b[k].pin_memory() if torch.is_tensor(b[k]) else b[k]) for k in
-                ("input_ids", "labels", "cu_seqlens", "pixel_values", "image_grid_thw")}
+        return {k: b[k] for k in ("input_ids", "labels", "cu_seqlens", "pixel_values", "image_grid_thw")}
 
     def to_dev(b):
         return {"input_ids": b["input_ids"].to(dev, non_blocking=True).unsqueeze(0),

@@ -43,6 +43,8 @@ def parse():
     ap.add_argument("--no-sp", action="store_true")
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the number of decoder layers (result is not a bench value)")
+    ap.add_argument("--opt-state", default="auto", choices=["auto", "fp32", "bf16"])
+    ap.add_argument("--vit-ac", default="auto", choices=["auto", "off", "full"])
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file (not a bench run)")
     return ap.parse_args()
@@ -73,6 +75,10 @@ class ClockSampler:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
         self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
         sm = sorted(int(float(r[0])) for r in self.rows if r and r[0].replace(".", "").isdigit())
         mx = [int(float(r[1])) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
         reasons = set()
@@ -98,7 +104,10 @@ def build_config(args, world: int):
     t.lr_llm, t.lr_mlp, t.lr_vit, t.weight_decay = 2e-6, 1e-5, 1e-6, 0.01
     t.total_steps, t.warmup_steps, t.save_steps = 10 ** 9, 50, 0
     t.ce_chunk_size = args.ce_chunk
-    t.ac_mode = args.ac if args.ac != "auto" else ("full" if world == 1 else "off")
+    t.ac_mode = args.ac if args.ac != "auto" else "off"
+    # one GPU holds the whole 8.8 B-parameter model: bf16 Adam moments (fp32 master weights kept) leave room
+    # for the decoder's activations without recomputation; with >= 2 GPUs the state is sharded and stays fp32
+    t.optimizer_state_dtype = args.opt_state if args.opt_state != "auto" else ("bf16" if world == 1 else "fp32")
     t.fused_comm = os.environ.get("VLMT_FUSED_COMM", "1") == "1"
     t.output_dir = "/tmp/vlmt_bench"
     cfg.data.synthetic = "vlm" if "vl" in args.model else "text-loguniform"
@@ -126,8 +135,9 @@ def run_ours(args):
         mc._PRESETS[args.model] = fewer
     cfg = build_config(args, world)
     tr = Trainer(cfg)
-    if cfg.training.ac_mode != "off" and tr.model.visual is not None:
-        tr.model.visual.ac_mode = "full"
+    vit_ac = args.vit_ac if args.vit_ac != "auto" else ("full" if world == 1 else "off")
+    if tr.model.visual is not None:
+        tr.model.visual.ac_mode = vit_ac
     from vlm_training_b200.ops import cuda as cu
 
     dev = tr.device
@@ -231,7 +241,7 @@ def run_ours(args):
             "mfu_vs_measured_sustained": value * flops_tok / n / tr.peak_flops,
             "config": {"model": args.model, "global_batch": int(round(global_tokens / args.seq_len)), "seq_len": args.seq_len,
                        "parallelism": f"fsdp{tr.mesh.dp}xtp{tr.mesh.tp}" + ("+sp" if cfg.training.sequence_parallel else ""),
-                       "ac_mode": cfg.training.ac_mode, "optimizer": "AdamW, fp32 master + fp32 moments, sharded over dp",
+                       "ac_mode": cfg.training.ac_mode, "optimizer": f"AdamW, fp32 master + {cfg.training.optimizer_state_dtype} moments, sharded over dp", "vit_ac": vit_ac,
                        "l2": "not flushed: every step streams >17 GB of weights, far above the 126 MB L2",
                        "layers_override": args.layers or None, "ce_chunk": args.ce_chunk},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem, "final_loss": float(loss.item()),

@@ -309,3 +309,55 @@ def test_adamw_matches_torch():
         opt.step()
     torch.testing.assert_close(master, pr.detach(), atol=1e-5, rtol=1e-5)
     torch.testing.assert_close(param.float(), pr.detach().to(torch.bfloat16).float(), atol=1e-2, rtol=1e-2)
+
+
+def test_norm_linear_and_swiglu_linear_match_unfused():
+    """The memory-saving fused forms must give the same values and gradients as the unfused sequence."""
+    T, H, N, I = 300, 512, 768, 1024
+    x, r = _rand(T, H).requires_grad_(), _rand(T, H).requires_grad_()
+    nw, w = _rand(H, scale=0.3).requires_grad_(), _rand(N, H, scale=0.05).requires_grad_()
+    y, s = ops.rms_norm_linear(x, nw, w, 1e-6, False, r)
+    gy, gs = _rand(T, N), _rand(T, H)
+    torch.autograd.backward([y, s], [gy, gs])
+    xr, rr, nwr, wr = (t.detach().float().requires_grad_() for t in (x, r, nw, w))
+    sr = xr + rr
+    yr = torch.nn.functional.linear(ref.rms_norm(sr, nwr, 1e-6, False), wr)
+    torch.autograd.backward([yr, sr], [gy.float(), gs.float()])
+    _close(y, yr, 0.05, 2e-2, "y")
+    _close(x.grad, xr.grad, 0.05, 3e-2, "dx")
+    _close(r.grad, rr.grad, 0.05, 3e-2, "dres")
+    _close(nw.grad, nwr.grad, 0.5, 3e-2, "dnorm_w")
+    _close(w.grad, wr.grad, 0.3, 3e-2, "dw")
+
+    gu = _rand(T, 2 * I).requires_grad_()
+    wd = _rand(H, I, scale=0.05).requires_grad_()
+    y = ops.swiglu_linear(gu, wd)
+    g = _rand(T, H)
+    y.backward(g)
+    gur, wdr = gu.detach().float().requires_grad_(), wd.detach().float().requires_grad_()
+    a, b = gur.chunk(2, -1)
+    yr = torch.nn.functional.linear(torch.nn.functional.silu(a) * b, wdr)
+    yr.backward(g.float())
+    _close(y, yr, 0.05, 2e-2, "swiglu_linear y")
+    _close(gu.grad, gur.grad, 0.05, 3e-2, "dgate_up")
+    _close(wd.grad, wdr.grad, 0.3, 3e-2, "dw_down")
+
+
+def test_adamw_bf16_moments_close_to_fp32():
+    cu = _cu()
+    n = 50_000
+    p0 = torch.randn(n, device=DEV)
+    ma, m32, v32 = p0.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    mb, m16, v16 = p0.clone(), torch.zeros(n, device=DEV, dtype=torch.bfloat16), torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+    pa, pb = p0.bfloat16(), p0.bfloat16()
+    for step in range(1, 6):
+        g = torch.randn(n, device=DEV).bfloat16()
+        cu.adamw_step_(g, ma, m32, v32, pa, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
+        cu.adamw_step_(g, mb, m16, v16, pb, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
+    torch.testing.assert_close(ma, mb, atol=2e-4, rtol=1e-3)
+
+
+def test_bias_colsum():
+    cu = _cu()
+    x = _rand(3000, 1152)
+    torch.testing.assert_close(cu._C.colsum(x), x.float().sum(0), atol=1e-2, rtol=1e-3)

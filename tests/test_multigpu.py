@@ -1,0 +1,59 @@
+"""Multi-GPU checks (2 GPUs of one node, NCCL): tensor parallelism with sequence parallelism against a
+single-GPU run, and the one-kernel reduce-scatter+AdamW+all-gather path against the NCCL path.
+Each case runs as torchrun child processes; nothing here waits on a flag inside a kernel."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r"""
+import json, os, sys
+sys.path.insert(0, {root!r})
+import torch
+from vlm_training_b200.config import ConfigManager, Config
+from vlm_training_b200.train.trainer import Trainer
+cfg = ConfigManager(Config).parse_args(sys.argv[1:])
+tr = Trainer(cfg)
+hist = tr.train()
+if tr.rank == 0:
+    os.makedirs(cfg.training.output_dir, exist_ok=True)
+    json.dump([m["train/loss"] for m in hist], open(os.path.join(cfg.training.output_dir, "losses.json"), "w"))
+if torch.distributed.is_initialized():
+    torch.distributed.destroy_process_group()
+"""
+
+
+def _run(tmp_path, nproc, extra, port, env_extra=None):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER.format(root=ROOT))
+    out = tmp_path / f"out_{port}"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(script), "--model.model_name", "Qwen3-VL-tiny", "--model.preset", "tiny-qwen3-vl-gpu",
+           "--model.train_vit", "true", "--training.output_dir", str(out), "--training.total_steps", "4", "--training.warmup_steps", "0",
+           "--training.save_steps", "0", "--training.lr_llm", "1e-3", "--training.lr_mlp", "1e-3", "--training.lr_vit", "1e-3",
+           "--training.scheduler_type", "cosine", "--training.data_parallel", "fsdp", "--data.synthetic", "vlm",
+           "--data.seq_len", "2048", "--wandb.mode", "disabled"] + extra
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env.update(env_extra or {})
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return json.load(open(out / "losses.json"))
+
+
+def test_tp2_sp_matches_one_gpu(tmp_path):
+    one = _run(tmp_path, 1, [], 29701)
+    tp2 = _run(tmp_path, 2, ["--training.tp_size", "2", "--training.sequence_parallel", "true", "--training.fused_comm", "false"], 29702)
+    assert tp2 == pytest.approx(one, rel=3e-2, abs=3e-2)
+
+
+def test_fused_optimizer_matches_nccl(tmp_path):
+    nccl = _run(tmp_path, 2, ["--training.fused_comm", "false"], 29703)
+    fused = _run(tmp_path, 2, ["--training.fused_comm", "true"], 29704, {"VLMT_NO_MULTIMEM": "1"})
+    assert fused == pytest.approx(nccl, rel=2e-3, abs=2e-3)
+    assert fused[-1] < fused[0]

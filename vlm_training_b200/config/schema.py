@@ -95,6 +95,8 @@ class TrainingSection:
     sequence_parallel: bool = False
     ce_chunk_size: int = 1024
     fp32_master: bool = True
+    # storage type of the Adam moments ("fp32" | "bf16"); master weights stay fp32 either way
+    optimizer_state_dtype: str = "fp32"
     # gradient clipping is off unless asked for: the reference never clips
     # although it carries max_grad_norm (reference: train/train_qwen.py:534-605)
     clip_grad: bool = False

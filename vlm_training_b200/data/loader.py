@@ -30,6 +30,15 @@ class PrefetchLoader:
         self.thread = threading.Thread(target=self._work, daemon=True)
         self.thread.start()
 
+    def _put(self, item) -> bool:
+        while not self._stop:
+            try:
+                self.q.put(item, timeout=0.1)
+                return True
+            except queue.Full:
+                continue
+        return False
+
     def _work(self):
         try:
             while not self._stop:
@@ -38,11 +47,12 @@ class PrefetchLoader:
                     for k in _TENSOR_KEYS:
                         if k in batch and torch.is_tensor(batch[k]):
                             batch[k] = batch[k].pin_memory()
-                self.q.put(batch)
+                if not self._put(batch):
+                    return
         except StopIteration:
-            self.q.put(None)
+            self._put(None)
         except Exception as exc:  # surface worker failures in the training thread
-            self.q.put(exc)
+            self._put(exc)
 
     def __iter__(self):
         return self
@@ -56,7 +66,15 @@ class PrefetchLoader:
         return item
 
     def close(self):
+        """Stop the worker and wait for it, so no thread touches CUDA (pinned allocations) during interpreter exit."""
         self._stop = True
+        try:
+            while True:
+                self.q.get_nowait()
+        except queue.Empty:
+            pass
+        if self.thread.is_alive() and threading.current_thread() is not self.thread:
+            self.thread.join(timeout=30)
 
 
 def batch_nbytes(batch: dict) -> int:
@@ -86,6 +104,7 @@ def to_device(batch: dict, cfg, device, pixel_dtype=torch.bfloat16) -> dict:
     else:
         t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=dt, non_blocking=nb)
         plan = BatchPlan(cu, int(host["max_seqlen"]), t(host["position_ids"], torch.int64))
+        plan.extras["cu_host"] = batch["cu_seqlens"].tolist()
         if "seq_idx" in host:
             plan.seq_idx = t(host["seq_idx"], torch.int32)
         if "image_rows" in host:

@@ -61,6 +61,12 @@ def text_row(rng: np.random.Generator, spec: SyntheticSpec) -> dict:
     return {"input_ids": ids, "labels": labels, "cu_seqlens": np.asarray(cu, dtype=np.int32)}
 
 
+def _text_vocab(spec: SyntheticSpec, cfg: ModelConfig) -> int:
+    """Random text ids stay below every special (vision) token id and inside the vocabulary."""
+    return max(1, min(spec.vocab_size, cfg.text.vocab_size, cfg.image_token_id, cfg.video_token_id,
+                      cfg.vision_start_token_id, cfg.vision_end_token_id))
+
+
 def _vlm_sample(rng, spec: SyntheticSpec, cfg: ModelConfig, budget: int):
     """Token ids / labels / grids of one multimodal sample that fits in ``budget`` tokens, or None."""
     merge = cfg.vision.spatial_merge_size
@@ -88,7 +94,7 @@ def _vlm_sample(rng, spec: SyntheticSpec, cfg: ModelConfig, budget: int):
     seg = np.diff(np.concatenate(([0], cuts, [want - 4 * n_seg]))) + 4
     ids, labels = [], []
     for i in range(n_seg):
-        t = rng.integers(0, min(spec.vocab_size, 151000), size=int(seg[i]), dtype=np.int64)
+        t = rng.integers(0, _text_vocab(spec, cfg), size=int(seg[i]), dtype=np.int64)
         ids.append(t)
         labels.append(t.copy())
         if i < len(grids):
@@ -109,7 +115,7 @@ def vlm_row(rng: np.random.Generator, spec: SyntheticSpec, cfg: ModelConfig) -> 
         room = L - cu[-1]
         s = _vlm_sample(rng, spec, cfg, room) if room >= 64 + 2 + 16 else None
         if s is None:
-            t = rng.integers(0, min(spec.vocab_size, 151000), size=room, dtype=np.int64)
+            t = rng.integers(0, _text_vocab(spec, cfg), size=room, dtype=np.int64)
             lab = t.copy()
             lab[0] = -100
             ids_all.append(t)

@@ -81,6 +81,7 @@ class BatchPlan:
         else:
             pos = positions.doc_position_ids(cu, T)[None]
         plan = BatchPlan(t(cu, torch.int32), mx, t(pos, torch.int64))
+        plan.extras["cu_host"] = cu.tolist()
         if need_seq_idx if need_seq_idx is not None else cfg.text.is_hybrid:
             plan.seq_idx = t(positions.seq_idx(cu, T), torch.int32)
         if grids_l:
@@ -133,6 +134,8 @@ class _CausalLMBase(nn.Module):
             raise ValueError("one packed row per call: the batch dimension must be 1")
         dec = self.decoder
         dev = dec.embed_tokens.weight.device
+        if cfg.vision is not None and max(cfg.image_token_id, cfg.vision_start_token_id, cfg.vision_end_token_id) >= cfg.text.vocab_size:
+            raise ValueError("the vision token ids lie outside the vocabulary; an embedding lookup with them would be out of range")
         if batch_plan is None:
             batch_plan = BatchPlan.build(cfg, ids, attention_mask, image_grid_thw if pixel_values is not None else None, dev)
         tp = getattr(self, "tp", None)

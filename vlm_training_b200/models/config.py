@@ -221,6 +221,17 @@ def _tiny_qwen3_vl() -> ModelConfig:
                             num_position_embeddings=64, out_hidden_size=128, deepstack_visual_indexes=[0, 1, 2]))
 
 
+def _tiny_qwen3_vl_gpu() -> ModelConfig:
+    """Small VLM whose shapes fit the CUDA kernels' tiles (head dims 64 / 72-style padding, dims multiple of 8)."""
+    return ModelConfig(
+        family="qwen3_vl",
+        text=TextConfig(vocab_size=8192, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+                        num_attention_heads=8, num_key_value_heads=4, head_dim=64, mrope_section=[12, 10, 10]),
+        vision=VisionConfig(depth=3, hidden_size=288, intermediate_size=576, num_heads=4, patch_size=16,
+                            num_position_embeddings=256, out_hidden_size=512, deepstack_visual_indexes=[0, 1, 2]),
+        image_token_id=8000, video_token_id=8001, vision_start_token_id=8002, vision_end_token_id=8003)
+
+
 def _qwen3_5_dense() -> ModelConfig:
     n = 32
     return ModelConfig(family="qwen3_5", vision=None, text=TextConfig(
@@ -263,6 +274,7 @@ _PRESETS = {
     "qwen3-8b": _qwen3_8b,
     "qwen3-vl-8b": _qwen3_vl_8b,
     "tiny-qwen3-vl": _tiny_qwen3_vl,
+    "tiny-qwen3-vl-gpu": _tiny_qwen3_vl_gpu,
     "qwen3.5-dense": _qwen3_5_dense,
     "qwen3.5-moe": _qwen3_5_moe,
     "tiny-qwen3.5": _tiny_qwen3_5,

@@ -137,7 +137,17 @@ class SwiGLUMLP(nn.Module):
         expose_fused(self, "gate_up")
 
     def forward(self, x):
+        if not self.down_proj.tp.enabled:
+            return ops.swiglu_linear(self.gate_up(x), self.down_proj.weight)
         return self.down_proj(ops.swiglu(self.gate_up(x)))
+
+    def forward_prenorm(self, x, residual, norm: "RMSNorm"):
+        """``r = x + residual; mlp(norm(r))`` → ``(out, r)`` with the norm fused into the gate/up projection."""
+        if self.gate_up.tp.enabled:
+            h, r = ops.add_rms_norm(x, residual, norm.weight, norm.eps, norm.offset)
+            return self.forward(h), r
+        gu, r = ops.rms_norm_linear(x, norm.weight, self.gate_up.weight, norm.eps, norm.offset, residual)
+        return ops.swiglu_linear(gu, self.down_proj.weight), r
 
 
 # ----------------------------------------------------------------------------- attention
@@ -165,8 +175,14 @@ class SelfAttention(nn.Module):
             self.idx_k = Linear(cfg.hidden_size, cfg.dsa_index_dim)
             self.idx_w = Linear(cfg.hidden_size, cfg.dsa_index_heads)
 
-    def forward(self, x, ctx: RowContext):
-        qkv = self.qkv(x)
+    def forward(self, x, ctx: RowContext, prenorm: "RMSNorm | None" = None):
+        """``prenorm``: apply this RMSNorm to ``x`` first, fused into the qkv projection where possible."""
+        if prenorm is not None and not self.qkv.tp.enabled and not self.cfg.dsa:
+            qkv = ops.rms_norm_linear(x, prenorm.weight, self.qkv.weight, prenorm.eps, prenorm.offset)
+        else:
+            if prenorm is not None:
+                x = prenorm(x)
+            qkv = self.qkv(x)
         T = qkv.shape[0]
         q, k, v, gate = ops.qkv_norm_rope(qkv, self.n_q, self.n_kv, self.head_dim, self.q_norm.weight,
                                           self.k_norm.weight, ctx.cos, ctx.sin, self.cfg.rms_norm_eps,
@@ -238,7 +254,7 @@ class GatedDeltaNet(nn.Module):
             rep = self.n_v // self.n_k
             q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
         g, beta = ops.gdn_gates(a, b, self.A_log, self.dt_bias)
-        o = ops.gated_delta_rule(q, k, v, g, beta, ctx.cu_seqlens, None, 64)
+        o = ops.gated_delta_rule(q, k, v, g, beta, ctx.cu_seqlens, None, 64, cu_host=ctx.extras.get("cu_host"))
         o = self.norm(o.reshape(T * self.n_v, self.d_v), z.reshape(T * self.n_v, self.d_v))
         return self.out_proj(o.reshape(T, self.value_dim))
 
@@ -304,8 +320,13 @@ class DecoderLayer(nn.Module):
         self.mlp = SparseMoeBlock(cfg) if cfg.num_experts > 0 else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size)
 
     def forward(self, x, ctx: RowContext):
-        h = self.input_layernorm(x)
-        h = self.linear_attn(h, ctx) if self.layer_type == "linear_attention" else self.self_attn(h, ctx)
+        if self.layer_type == "linear_attention":
+            h = self.linear_attn(self.input_layernorm(x), ctx)
+        else:
+            h = self.self_attn(x, ctx, prenorm=self.input_layernorm)
+        if isinstance(self.mlp, SwiGLUMLP):
+            out, x = self.mlp.forward_prenorm(h, x, self.post_attention_layernorm)
+            return x + out
         h, x = ops.add_rms_norm(h, x, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps,
                                 self.post_attention_layernorm.offset)
         return x + self.mlp(h)

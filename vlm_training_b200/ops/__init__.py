@@ -73,6 +73,25 @@ def linear_gelu(x, weight, bias, approximate: str = "tanh"):
     return ref.gelu_tanh(y) if approximate == "tanh" else ref.gelu_erf(y)
 
 
+def rms_norm_linear(x, norm_weight, weight, eps: float = 1e-6, offset: bool = False, residual=None):
+    """``linear(rms_norm(x + residual), weight)``; returns ``y`` or ``(y, x + residual)``.  On CUDA the normalised
+    activation is not kept for backward (it is recomputed), which removes one ``[T, H]`` tensor per use."""
+    if _use_cuda(x):
+        return _cu().rms_norm_linear(x, norm_weight, weight, eps, offset, residual)
+    if residual is None:
+        return ref.linear(ref.rms_norm(x, norm_weight, eps, offset), weight)
+    r = x + residual
+    return ref.linear(ref.rms_norm(r, norm_weight, eps, offset), weight), r
+
+
+def swiglu_linear(gate_up, weight):
+    """``linear(silu(gate) * up, weight)`` for a fused ``[T, 2I]`` input; on CUDA only ``gate_up`` is kept for backward."""
+    if _use_cuda(gate_up):
+        return _cu().swiglu_linear(gate_up, weight)
+    g, u = gate_up.chunk(2, dim=-1)
+    return ref.linear(ref.swiglu(g, u), weight)
+
+
 # --- activations -------------------------------------------------------------
 def swiglu(gate_up):
     """``silu(gate) * up`` for a fused ``[..., 2I]`` tensor laid out ``[gate | up]``."""
@@ -119,18 +138,26 @@ def qkv_norm_rope(qkv, n_q: int, n_kv: int, head_dim: int, q_weight, k_weight, c
     return q, k, v, gate
 
 
-def rope_vision(q, k, cos, sin):
+def rope_vision(q, k, cos, sin, pad_to=None):
     """fp32 rotate-half rotary on ViT q,k ``[S, H, D]`` with ``cos/sin [S, D]``
-    (reference: models/qwen3_vl/model.py:385-394)."""
+    (reference: models/qwen3_vl/model.py:385-394).  ``pad_to`` appends zero channels up to that width."""
     if _use_cuda(q):
-        return _cu().rope_vision(q, k, cos, sin)
-    return ref.apply_rope(q, cos, sin), ref.apply_rope(k, cos, sin)
+        return _cu().rope_vision(q, k, cos, sin, pad_to)
+    q, k = ref.apply_rope(q, cos, sin), ref.apply_rope(k, cos, sin)
+    if pad_to and pad_to > q.shape[-1]:
+        pad = (0, pad_to - q.shape[-1])
+        q, k = torch.nn.functional.pad(q, pad), torch.nn.functional.pad(k, pad)
+    return q, k
 
 
 # --- attention ---------------------------------------------------------------
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: float | None = None):
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: float | None = None,
+                     valid_dim: int | None = None):
+    """``valid_dim``: the inputs carry zero padding beyond this many channels (see ``rope_vision(pad_to=...)``)."""
     if _use_cuda(q):
-        return _cu().attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        return _cu().attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale, valid_dim)
+    if scale is None and valid_dim:
+        scale = valid_dim ** -0.5
     return ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
 
 
@@ -163,9 +190,10 @@ def gdn_gates(a, b, A_log, dt_bias):
     return g, torch.sigmoid(b.float()).to(b.dtype)
 
 
-def gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale: float | None = None, chunk: int = 64):
+def gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale: float | None = None, chunk: int = 64, cu_host=None):
+    """``cu_host``: the same boundaries as a host sequence (saves a device sync when given)."""
     if _use_cuda(q):
-        return _cu().gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale, chunk)
+        return _cu().gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale, chunk, cu_host)
     return ref.gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale, chunk)
 
 

@@ -60,6 +60,7 @@ struct FwdParams {
   int n_docs, T, Hq, Hkv;
   float scale_log2;   // softmax scale * log2(e)
   int causal;
+  int d_eff;          // channels that can be non-zero (multiple of 16, <= D): MMAs skip the zero padding beyond it
   int* status;
 };
 
@@ -157,7 +158,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(BM, D, false, true);
+      const uint32_t idesc_pv = make_idesc_bf16(BM, p.d_eff, false, true);
       const uint32_t sQ = smem_u32(smem + L::offQ);
       auto issue_S = [&](int j) -> bool {
         const int s = j & 1;
@@ -168,6 +169,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t sK = smem_u32(smem + L::offK + s * L::kKV);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk * 16 >= p.d_eff) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + S_COL + s * BN, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
         }
@@ -280,11 +282,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t pv_addr = tmem_base + PV_COL + pb * D + lane_addr;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t rr[32];
-          tmem_ld_32x32(pv_addr + c * 32, rr);
-          tmem_ld_wait();
+          if (c * 32 < p.d_eff) {  // columns at and beyond d_eff were never written by the MMA: leave those outputs at zero
+            uint32_t rr[32];
+            tmem_ld_32x32(pv_addr + c * 32, rr);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < p.d_eff) o[c * 32 + i] = o[c * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -300,11 +305,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t pv_addr = tmem_base + PV_COL + pb * D + lane_addr;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t rr[32];
-          tmem_ld_32x32(pv_addr + c * 32, rr);
-          tmem_ld_wait();
+          if (c * 32 < p.d_eff) {  // columns at and beyond d_eff were never written by the MMA: leave those outputs at zero
+            uint32_t rr[32];
+            tmem_ld_32x32(pv_addr + c * 32, rr);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < p.d_eff) o[c * 32 + i] = o[c * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
+          }
         }
       } else {
         ok = false;
@@ -364,6 +372,7 @@ struct BwdParams {
   int n_docs, T, Hq, Hkv;
   float scale, scale_log2;
   int causal;
+  int d_eff;
   int* status;
 };
 
@@ -450,7 +459,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S = Q K^T, dP = dO V^T
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, true, true);       // dV = P^T dO, dK = dS^T Q
+      const uint32_t idesc_g = make_idesc_bf16(128, p.d_eff, true, true);     // dV = P^T dO, dK = dS^T Q
       const uint32_t sK = smem_u32(smem + L::offA), sV = smem_u32(smem + L::offB);
       const uint32_t sQ = smem_u32(smem + L::offC), sdO = smem_u32(smem + L::offD);
       const uint32_t sP = smem_u32(smem + L::offP), sDS = smem_u32(smem + L::offDS);
@@ -461,11 +470,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk * 16 >= p.d_eff) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + S_COL, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk * 16 >= p.d_eff) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + DP_COL, make_smem_desc(sdO + off, 16, 1024), make_smem_desc(sV + off, 16, 1024), idesc_s, kk != 0);
         }
@@ -551,8 +562,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t rr[32];
-            tmem_ld_32x32(tmem_base + col + lane_addr + c * 32, rr);
-            tmem_ld_wait();
+            if (c * 32 < p.d_eff) {
+              tmem_ld_32x32(tmem_base + col + lane_addr + c * 32, rr);
+              tmem_ld_wait();
+            }
+#pragma unroll
+            for (int u = 0; u < 32; ++u) if (c * 32 + u >= p.d_eff) rr[u] = 0u;
             if (kvi < ti.doc_len) {
               __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * D + c * 32;
 #pragma unroll
@@ -648,7 +663,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, false, true);  // dQ = dS K : A K-major [q][kv], B = K [kv][d] MN-major
+      const uint32_t idesc_q = make_idesc_bf16(128, p.d_eff, false, true);  // dQ = dS K : A K-major [q][kv], B = K [kv][d] MN-major
       const uint32_t sQ = smem_u32(smem + L::offA), sdO = smem_u32(smem + L::offB);
       const uint32_t sK = smem_u32(smem + L::offC), sV = smem_u32(smem + L::offD);
       const uint32_t sDS = smem_u32(smem + L::offDS);
@@ -659,11 +674,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk * 16 >= p.d_eff) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + S_COL, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk * 16 >= p.d_eff) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + DP_COL, make_smem_desc(sdO + off, 16, 1024), make_smem_desc(sV + off, 16, 1024), idesc_s, kk != 0);
         }
@@ -728,8 +745,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t rr[32];
-        tmem_ld_32x32(tmem_base + DQ_COL + lane_addr + c * 32, rr);
-        tmem_ld_wait();
+        if (c * 32 < p.d_eff) {
+          tmem_ld_32x32(tmem_base + DQ_COL + lane_addr + c * 32, rr);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int u = 0; u < 32; ++u) if (c * 32 + u >= p.d_eff) rr[u] = 0u;
         if (row_ok && J > 0) {
           __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * D + c * 32;
 #pragma unroll
@@ -772,7 +793,7 @@ int set_smem(K kern, int bytes) {
 }  // namespace
 
 extern "C" int vlmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu, int n_docs, int T, int Hq,
-                             int Hkv, int D, long ldq, long ldk, long ldv, float scale, int causal, int* status, cudaStream_t st) {
+                             int Hkv, int D, int d_eff, long ldq, long ldk, long ldv, float scale, int causal, int* status, cudaStream_t st) {
   if (T <= 0 || n_docs <= 0) return 0;
   CUtensorMap tq, tk, tv;
   int r;
@@ -782,6 +803,7 @@ extern "C" int vlmt_attn_fwd(const void* q, const void* k, const void* v, void* 
   FwdParams p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o); p.LSE = lse; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
+  p.d_eff = (d_eff <= 0 || d_eff > D) ? D : ((d_eff + 15) / 16) * 16;
   dim3 grid(T / BM + n_docs + 1, Hq);
   if (D == 128) {
     if ((r = set_smem(attn_fwd_kernel<128>, FwdSmem<128>::kTotal))) return r;
@@ -796,7 +818,7 @@ extern "C" int vlmt_attn_fwd(const void* q, const void* k, const void* v, void* 
 }
 
 extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse, float* delta,
-                             void* dq, void* dk, void* dv, const int* cu, int n_docs, int T, int Hq, int Hkv, int D, float scale,
+                             void* dq, void* dk, void* dv, const int* cu, int n_docs, int T, int Hq, int Hkv, int D, int d_eff, float scale,
                              int causal, int* status, cudaStream_t st) {
   if (T <= 0 || n_docs <= 0) return 0;
   {
@@ -814,6 +836,7 @@ extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, con
   p.dQ = reinterpret_cast<__nv_bfloat16*>(dq); p.dK = reinterpret_cast<__nv_bfloat16*>(dk); p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   p.LSE = lse; p.delta = delta; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
+  p.d_eff = (d_eff <= 0 || d_eff > D) ? D : ((d_eff + 15) / 16) * 16;
   dim3 grid_kv(T / BN + n_docs + 1, Hkv), grid_q(T / BM + n_docs + 1, Hq);
   if (D == 128) {
     if ((r = set_smem(attn_bwd_dkdv_kernel<128>, BwdSmem<128>::kTotal))) return r;

@@ -316,17 +316,29 @@ Tensor ce_fwd_bwd_(Tensor& logits, const Tensor& targets, double grad_scale, int
 }
 void adamw_(const Tensor& grad, Tensor& master, Tensor& m, Tensor& v, c10::optional<Tensor> param, double lr, double b1, double b2,
             double eps, double wd, int64_t step, double grad_scale) {
-  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == v.scalar_type());
+  TORCH_CHECK(m.scalar_type() == at::kFloat || m.scalar_type() == at::kBFloat16, "Adam moments must be fp32 or bf16");
   TORCH_CHECK(grad.is_contiguous() && master.is_contiguous() && m.is_contiguous() && v.is_contiguous());
   c10::cuda::CUDAGuard guard(master.device());
   const double bc1 = 1.0 - std::pow(b1, (double)step), bc2 = 1.0 - std::pow(b2, (double)step);
-  vlmt_adamw(grad.data_ptr(), grad.scalar_type() == at::kFloat, master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
-             param.has_value() ? param->data_ptr() : nullptr, master.numel(), (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
+  vlmt_adamw(grad.data_ptr(), grad.scalar_type() == at::kFloat, master.data_ptr<float>(), m.data_ptr(), v.data_ptr(),
+             m.scalar_type() == at::kBFloat16, param.has_value() ? param->data_ptr() : nullptr, master.numel(), (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
              (float)bc1, (float)bc2, (float)grad_scale, cur_stream());
 }
 void sumsq_(const Tensor& x, Tensor& out) {
   c10::cuda::CUDAGuard guard(x.device());
   vlmt_sumsq(x.data_ptr(), x.scalar_type() == at::kFloat, x.numel(), out.data_ptr<float>(), cur_stream());
+}
+
+// column sums of a 2-D bf16 tensor in fp32 (bias gradients)
+Tensor colsum(const Tensor& x) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 2 == 0);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = x.size(0), cols = x.size(1);
+  Tensor partial = torch::empty({vlmt_colsum_slabs(rows), cols}, x.options().dtype(torch::kFloat));
+  vlmt_colsum(x.data_ptr(), x.stride(0), rows, cols, partial.data_ptr<float>(), cur_stream());
+  return partial.sum(0);
 }
 
 Tensor status() { return status_tensor(); }
@@ -365,6 +377,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_fwd_bwd_", &ce_fwd_bwd_);
   m.def("adamw_", &adamw_);
   m.def("sumsq_", &sumsq_);
+  m.def("colsum", &colsum);
   m.def("status", &status);
   bind_attention(m);
   bind_comm(m);

@@ -34,7 +34,9 @@ struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kOutOffset = STAGES * kStageBytes;          // epilogue staging: 4 warps x 2 buffers x [32 rows][128 B]
+  static constexpr int kOutBytes = 4 * 2 * 4096;
+  static constexpr int kBarOffset = kOutOffset + kOutBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // + barriers + slack for 1024-B alignment
 };
 
@@ -46,6 +48,7 @@ struct Params {
   float* Dacc32;       // optional fp32 destination (wgrad into fp32 main grads) or null
   int epilogue;        // GemmEpilogue
   int accumulate;      // D += result
+  int tma_store;       // bf16 output goes through smem staging + TMA stores (coalesced, clipped at the edges)
   int* status;
 };
 
@@ -68,7 +71,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_d, Params p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -178,6 +182,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const bool row_ok = row < p.M;
+      if (p.tma_store) {
+        // 64-column slabs: TMEM -> registers -> (bias / GELU) -> bf16 -> swizzled smem -> one TMA store per slab and warp
+        uint8_t* stage = smem + L::kOutOffset + q * 8192;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= p.N) break;
+          uint8_t* buf = stage + (c & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();  // the store issued two slabs ago has finished reading this buffer
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 64 + h * 32, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) if (col0 + h * 32 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + h * 32 + i]);
+            }
+            if (p.epilogue == GEMM_EPI_GELU_TANH) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_f(v[i]);
+            } else if (p.epilogue == GEMM_EPI_GELU_ERF) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = gelu_erf_f(v[i]);
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              uint4 pk;
+              __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(v[t * 8 + 2 * j], v[t * 8 + 2 * j + 1]);
+              const int ci = h * 4 + t;
+              *reinterpret_cast<uint4*>(buf + lane * 128 + ((ci ^ (lane & 7)) << 4)) = pk;
+            }
+          }
+          fence_async_proxy();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_d, buf, col0, tm * BM + q * 32);
+            tma_store_commit();
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -237,6 +288,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -244,6 +296,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 
   // ---------------------------------------------------------------- teardown
+  if (warp >= 2 && lane == 0 && p.tma_store) tma_store_wait<0>();
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {
@@ -302,7 +355,8 @@ extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t 
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int num_sms, cudaStream_t stream) {
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Params& p, int num_sms,
+                          cudaStream_t stream) {
   using L = SmemLayout<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
@@ -313,7 +367,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Pa
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, L::kTotal, stream>>>(ta, tb, p);
+  kern<<<grid, NUM_THREADS, L::kTotal, stream>>>(ta, tb, td, p);
   return (int)cudaGetLastError();
 }
 
@@ -333,6 +387,12 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
   else r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
   if (r) return 2000 + r;
   Params p;
+  CUtensorMap td = ta;  // placeholder when the direct-store epilogue is used
+  p.tma_store = 0;
+  if (Dacc32 == nullptr && !accumulate && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
+    r = vlmt_make_tmap_2d_bf16(&td, D, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * 2, 64, 32);
+    if (r == 0) p.tma_store = 1;
+  }
   p.M = M; p.N = N; p.K = K; p.ldd = ldd;
   p.D = reinterpret_cast<__nv_bfloat16*>(D);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
@@ -340,10 +400,10 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
   p.epilogue = epilogue; p.accumulate = accumulate; p.status = status;
 #define DISPATCH(BN_)                                                                                     \
   do {                                                                                                    \
-    if (!a_mn_major && !b_mn_major) return launch_variant<BN_, false, false>(ta, tb, p, num_sms, stream); \
-    if (!a_mn_major && b_mn_major) return launch_variant<BN_, false, true>(ta, tb, p, num_sms, stream);   \
-    if (a_mn_major && b_mn_major) return launch_variant<BN_, true, true>(ta, tb, p, num_sms, stream);     \
-    return launch_variant<BN_, true, false>(ta, tb, p, num_sms, stream);                                  \
+    if (!a_mn_major && !b_mn_major) return launch_variant<BN_, false, false>(ta, tb, td, p, num_sms, stream); \
+    if (!a_mn_major && b_mn_major) return launch_variant<BN_, false, true>(ta, tb, td, p, num_sms, stream);   \
+    if (a_mn_major && b_mn_major) return launch_variant<BN_, true, true>(ta, tb, td, p, num_sms, stream);     \
+    return launch_variant<BN_, true, false>(ta, tb, td, p, num_sms, stream);                                  \
   } while (0)
   if (bn256) DISPATCH(256);
   DISPATCH(128);

@@ -104,20 +104,41 @@ ce_fwd_bwd_kernel(bf16* __restrict__ logits, long ld, const long* __restrict__ t
 
 // AdamW on a flat range: grads bf16 (or fp32), master/m/v fp32, bf16 parameter written back.
 //   m = b1 m + (1-b1) g ; v = b2 v + (1-b2) g^2 ; p = p (1 - lr wd) - lr * (m / bc1) / (sqrt(v / bc2) + eps)
-template <typename GT>
-__global__ void adamw_kernel(const GT* __restrict__ grad, float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+__device__ __forceinline__ float ld_state(const float* p, long i) { return p[i]; }
+__device__ __forceinline__ float ld_state(const bf16* p, long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void st_state(float* p, long i, float x) { p[i] = x; }
+__device__ __forceinline__ void st_state(bf16* p, long i, float x) { p[i] = __float2bfloat16(x); }
+
+// GT: gradient type (bf16 / float); MT: moment storage type (float, or bf16 to halve the optimizer state)
+template <typename GT, typename MT>
+__global__ void adamw_kernel(const GT* __restrict__ grad, float* __restrict__ master, MT* __restrict__ m, MT* __restrict__ v,
                              bf16* __restrict__ param, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                              float grad_scale) {
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
     float g;
     if constexpr (sizeof(GT) == 2) g = __bfloat162float(grad[i]) * grad_scale; else g = (float)grad[i] * grad_scale;
-    float mi = b1 * m[i] + (1.f - b1) * g;
-    float vi = b2 * v[i] + (1.f - b2) * g * g;
+    float mi = b1 * ld_state(m, i) + (1.f - b1) * g;
+    float vi = b2 * ld_state(v, i) + (1.f - b2) * g * g;
     float p = master[i] * (1.f - lr * wd);
     p -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-    m[i] = mi; v[i] = vi; master[i] = p;
+    st_state(m, i, mi); st_state(v, i, vi); master[i] = p;
     if (param) param[i] = __float2bfloat16(p);
   }
+}
+
+// out[c] = sum_r x[r, c]  (bf16 in, fp32 accumulate): one thread per column pair inside a row slab, partials per slab
+__global__ void colsum_kernel(const bf16* __restrict__ x, long ld, int rows, int cols, float* __restrict__ partial, int rows_per_slab) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= cols) return;
+  const int r0 = blockIdx.y * rows_per_slab;
+  const int r1 = min(rows, r0 + rows_per_slab);
+  float a0 = 0.f, a1 = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(x + (long)r * ld + c));
+    a0 += f.x; a1 += f.y;
+  }
+  partial[(long)blockIdx.y * cols + c] = a0;
+  partial[(long)blockIdx.y * cols + c + 1] = a1;
 }
 
 // sum of squares of a flat bf16/fp32 range -> out[0] (atomic; used for gradient clipping)
@@ -148,17 +169,22 @@ void vlmt_ce_fwd_bwd(void* logits, long ld, const long* targets, float* loss, fl
   if (rows <= 0) return;
   ce_fwd_bwd_kernel<<<rows, CE_THREADS, 0, st>>>(reinterpret_cast<bf16*>(logits), ld, targets, loss, grad_scale, V, ignore_index);
 }
-void vlmt_adamw(const void* grad, int grad_fp32, float* master, float* m, float* v, void* param, long n, float lr, float b1, float b2,
-                float eps, float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
+void vlmt_adamw(const void* grad, int grad_fp32, float* master, void* m, void* v, int state_bf16, void* param, long n, float lr, float b1,
+                float b2, float eps, float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
   if (n <= 0) return;
   long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  if (grad_fp32)
-    adamw_kernel<float><<<(int)blocks, 256, 0, st>>>((const float*)grad, master, m, v, reinterpret_cast<bf16*>(param), n, lr, b1, b2, eps, wd,
-                                                     bc1, bc2, grad_scale);
-  else
-    adamw_kernel<bf16><<<(int)blocks, 256, 0, st>>>((const bf16*)grad, master, m, v, reinterpret_cast<bf16*>(param), n, lr, b1, b2, eps, wd,
-                                                    bc1, bc2, grad_scale);
+  bf16* pp = reinterpret_cast<bf16*>(param);
+#define LAUNCH(GT, MT) adamw_kernel<GT, MT><<<(int)blocks, 256, 0, st>>>((const GT*)grad, master, (MT*)m, (MT*)v, pp, n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale)
+  if (grad_fp32) { if (state_bf16) LAUNCH(float, bf16); else LAUNCH(float, float); }
+  else { if (state_bf16) LAUNCH(bf16, bf16); else LAUNCH(bf16, float); }
+#undef LAUNCH
+}
+int vlmt_colsum_slabs(int rows) { int s = (rows + 511) / 512; return s < 1 ? 1 : s; }
+void vlmt_colsum(const void* x, long ld, int rows, int cols, float* partial, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return;
+  dim3 grid((cols / 2 + 127) / 128, vlmt_colsum_slabs(rows));
+  colsum_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const bf16*>(x), ld, rows, cols, partial, 512);
 }
 void vlmt_sumsq(const void* x, int fp32, long n, float* out, cudaStream_t st) {
   if (n <= 0) return;

@@ -97,7 +97,8 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = _gemm(dy2, x2, a_mn=True, b_mn=True)  # dW[N,K] = dY^T[N,M] . X[M,K]
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy.dtype)
+            db = _C.colsum(dy2).to(dy.dtype) if dy2.shape[1] % 2 == 0 else dy2.float().sum(0).to(dy.dtype)
+            _tick()
         return dx, dw, db, None
 
 
@@ -272,6 +273,90 @@ def sigmoid_mul(x, gate):
     return _SigmoidMul.apply(x, gate)
 
 
+class _NormLinear(torch.autograd.Function):
+    """``(x [+ residual]) → RMSNorm → linear`` that keeps only the un-normalised stream and ``rstd`` for backward;
+    the normalised activation (the GEMM's A operand) is recomputed in backward by one cheap elementwise pass
+    instead of being stored — 2 x T x H bytes less per use."""
+
+    @staticmethod
+    def forward(ctx, x, residual, norm_w, w, eps, offset):
+        xc = x.contiguous()
+        if residual is None:
+            h, rstd = _C.rmsnorm_fwd(xc, None, norm_w, eps, offset)
+            r = xc
+        else:
+            h, rstd, r = _C.rmsnorm_fwd(xc, residual.contiguous(), norm_w, eps, offset)
+        wc = _as_gemm_operand(w)
+        y = _gemm(h, wc)
+        _tick()
+        ctx.save_for_backward(r, norm_w, rstd, wc)
+        ctx.cfg = (eps, offset, residual is not None)
+        if residual is None:
+            return y
+        return y, r
+
+    @staticmethod
+    def backward(ctx, dy, dr=None):
+        r, norm_w, rstd, w = ctx.saved_tensors
+        eps, offset, has_res = ctx.cfg
+        dy2 = _as_gemm_operand(dy)
+        h = _C.rmsnorm_fwd(r, None, norm_w, eps, offset)[0]  # recompute the normalised activation
+        dw = _gemm(dy2, h, a_mn=True, b_mn=True)
+        del h
+        dh = _gemm(dy2, w, b_mn=True)
+        dx, dnw = _C.rmsnorm_bwd(dh, r, norm_w, rstd, dr.contiguous() if dr is not None else None, offset)
+        _tick(3)
+        dnw = dnw.to(norm_w.dtype)
+        if has_res:
+            return dx, dx, dnw, dw, None, None
+        return dx, None, dnw, dw, None, None
+
+
+def rms_norm_linear(x, norm_weight, weight, eps=1e-6, offset=False, residual=None):
+    """``linear(rms_norm(x + residual))``; returns ``y`` or ``(y, x + residual)``."""
+    ok = x.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and not _small_or_odd(x, weight) and x.dim() == 2
+    if not ok:
+        if residual is None:
+            return linear(rms_norm(x, norm_weight, eps, offset), weight)
+        h, r = add_rms_norm(x, residual, norm_weight, eps, offset)
+        return linear(h, weight), r
+    return _NormLinear.apply(x, residual, norm_weight, weight, eps, offset)
+
+
+class _SwiGLULinear(torch.autograd.Function):
+    """``linear(silu(gate) * up)`` that stores only ``gate_up``; the activation is recomputed in backward."""
+
+    @staticmethod
+    def forward(ctx, gate_up, w):
+        guc = gate_up.contiguous()
+        act = _C.swiglu_fwd(guc)
+        wc = _as_gemm_operand(w)
+        y = _gemm(act, wc)
+        _tick()
+        ctx.save_for_backward(guc, wc)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        gu, w = ctx.saved_tensors
+        dy2 = _as_gemm_operand(dy)
+        act = _C.swiglu_fwd(gu)
+        dw = _gemm(dy2, act, a_mn=True, b_mn=True)
+        del act
+        dact = _gemm(dy2, w, b_mn=True)
+        dgu = _C.swiglu_bwd(dact, gu)
+        _tick(2)
+        return dgu, dw
+
+
+def swiglu_linear(gate_up, weight):
+    ok = (gate_up.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and gate_up.dim() == 2 and gate_up.shape[-1] % 16 == 0
+          and not _small_or_odd(gate_up[:, : gate_up.shape[-1] // 2], weight))
+    if not ok:
+        return linear(swiglu(gate_up), weight)
+    return _SwiGLULinear.apply(gate_up, weight)
+
+
 # ------------------------------------------------------------------------------- qkv prep
 class _QKVNormRope(torch.autograd.Function):
     @staticmethod
@@ -324,9 +409,11 @@ class _RopeGeneric(torch.autograd.Function):
         return _C.rope_generic(dy[..., :ctx.d], cos, sin, True, ctx.d), None, None, None
 
 
-def rope_vision(q, k, cos, sin):
+def rope_vision(q, k, cos, sin, pad_to=None):
+    """``pad_to``: emit ``[S, H, pad_to]`` with zeros behind the rotated channels (the attention kernel's tile width)."""
     cos, sin = cos.float().contiguous(), sin.float().contiguous()
-    return _RopeGeneric.apply(q, cos, sin, q.shape[-1]), _RopeGeneric.apply(k, cos, sin, k.shape[-1])
+    d_out = pad_to or q.shape[-1]
+    return _RopeGeneric.apply(q, cos, sin, d_out), _RopeGeneric.apply(k, cos, sin, d_out)
 
 
 # ------------------------------------------------------------------------------- attention
@@ -338,47 +425,47 @@ def _pad_heads(t, d_to):
 
 class _AttentionVarlen(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale, d_eff):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse = _C.attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        o, lse = _C.attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale, d_eff)
         ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
-        ctx.cfg = (max_seqlen, causal, scale)
+        ctx.cfg = (max_seqlen, causal, scale, d_eff)
         _tick()
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse, cu = ctx.saved_tensors
-        max_seqlen, causal, scale = ctx.cfg
-        dq, dk, dv = _C.attn_bwd(do.contiguous(), q, k, v, o, lse, cu, max_seqlen, causal, scale)
+        max_seqlen, causal, scale, d_eff = ctx.cfg
+        dq, dk, dv = _C.attn_bwd(do.contiguous(), q, k, v, o, lse, cu, max_seqlen, causal, scale, d_eff)
         _tick(3)
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None
 
 
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None):
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None, valid_dim=None):
+    """``valid_dim``: q/k/v are zero-padded beyond this many channels (they were padded to the kernel's tile
+    width by the caller); the output keeps the padded width."""
     D = q.shape[-1]
-    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    scale = scale if scale is not None else 1.0 / math.sqrt(valid_dim or D)
     if q.dtype != torch.bfloat16:
         return ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
     if not hasattr(_C, "attn_fwd"):
         raise RuntimeError("the attention kernel is not part of this build of the extension")
     cu = cu_seqlens.to(torch.int32)
     if D in (64, 128):
-        return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale))
+        return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale), int(valid_dim or D))
     if D < 128:
-        # pad the head dim with zeros to the kernel's tile width (ViT head_dim 72)
+        # pad the head dim with zeros to the kernel's tile width (ViT head_dim 72); the MMAs skip the padding
         o = _AttentionVarlen.apply(_pad_heads(q, 128), _pad_heads(k, 128), _pad_heads(v, 128), cu, int(max_seqlen),
-                                   bool(causal), float(scale))
+                                   bool(causal), float(scale), D)
         return o[..., :D]
-    if D == 256:
-        return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale))
     raise NotImplementedError(f"attention head_dim {D}")
 
 
 def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None):
-    if not hasattr(_C, "dsa_attn_fwd"):
-        return ref.dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale)
-    raise NotImplementedError
+    from .dsa_cuda import dsa_attention_cuda
+
+    return dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale)
 
 
 # ------------------------------------------------------------------------------- loss
@@ -482,12 +569,17 @@ def gdn_gates(a, b, A_log, dt_bias):
     return _GdnGates.apply(a, b, A_log, dt_bias)
 
 
-def gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale=None, chunk=64):
+def gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale=None, chunk=64, cu_host=None):
     if hasattr(_C, "gdn_chunk_fwd"):
         from .gdn_cuda import gated_delta_rule_cuda
 
         return gated_delta_rule_cuda(q, k, v, g, beta, cu_seqlens, scale, chunk)
-    raise RuntimeError("the gated-delta-rule kernel is not part of this build of the extension")
+    # batched formulation on library GEMMs (no dedicated recurrence kernel in this build)
+    from .gdn_batched import gated_delta_rule_batched
+
+    if cu_host is None:
+        cu_host = cu_seqlens.tolist()  # one device sync; pass cu_host to avoid it
+    return gated_delta_rule_batched(q, k, v, g, beta, cu_host, scale, chunk)
 
 
 # ------------------------------------------------------------------------------- MoE
@@ -496,11 +588,9 @@ def moe_router(logits, top_k, renorm=True):
 
 
 def moe_experts(x, gate_up, down, weights, experts):
-    if hasattr(_C, "moe_grouped_gemm"):
-        from .moe_cuda import moe_experts_cuda
+    from .moe_cuda import moe_experts_cuda
 
-        return moe_experts_cuda(x, gate_up, down, weights, experts)
-    raise RuntimeError("the grouped expert GEMM is not part of this build of the extension")
+    return moe_experts_cuda(x, gate_up, down, weights, experts)
 
 
 # ------------------------------------------------------------------------------- rows

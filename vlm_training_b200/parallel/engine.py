@@ -331,7 +331,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
 
     def _adamw(self, d, bi, s, e, grad, param, lr, wd, b1, b2, grad_scale):
         master, m, v = d.master[bi][s:e], d.exp_avg[bi][s:e], d.exp_avg_sq[bi][s:e]
-        if self.is_cuda and m.dtype == torch.float32 and param.dtype == torch.bfloat16:
+        if self.is_cuda and param.dtype == torch.bfloat16:
             from ..ops import cuda as cu
 
             cu.adamw_step_(grad, master, m, v, param, lr, b1, b2, self.eps, wd, self.step_count, grad_scale)
