@@ -79,6 +79,15 @@ def run(args):
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)  # the reference always initialises NCCL (train/train_qwen.py:79)
     tp = args.tp if args.tp else (1 if world == 1 else 2)
+    note = None
+    if tp > 1 and os.environ.get("REF_FORCE_TP", "0") != "1":
+        # The reference's Qwen3-VL tensor-parallel plan does not run with its own Qwen3-VL model: q/k come out of the
+        # column-parallel projections as DTensors while cos/sin stay plain tensors, and `apply_rope` raises
+        # "aten.mul.Tensor got mixed torch.Tensor and DTensor" (train/infra.py:432-452 prepares a `hidden_states`
+        # keyword the model never passes; observed on 2 GPUs).  The reference's working multi-GPU layout for this
+        # model is FSDP over all ranks, which is what is measured instead.
+        note = "reference TP plan for Qwen3-VL fails (mixed Tensor/DTensor in apply_rope); measured with its FSDP-only layout"
+        tp = 1
 
     class TrainingArgs:
         tp_size = tp
@@ -230,6 +239,6 @@ def run(args):
             "impl": "reference", "tokens_per_sec_per_gpu": value / world,
             "config": {"model": args.model, "global_batch": dp_size, "seq_len": args.seq_len, "parallelism": f"fsdp{dp_size}xtp{tp}",
                        "ac_mode": ac_mode, "compile": compiled, "optimizer": "torch AdamW foreach on bf16 parameters",
-                       "layers_override": args.layers or None},
+                       "layers_override": args.layers or None, "note": note},
             "clocks": clocks, "e2e": e2e, "gpu_launches": 0, "peak_mem_gib": peak, "final_loss": float(loss.item())}))
     dist.destroy_process_group()

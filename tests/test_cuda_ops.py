@@ -361,3 +361,28 @@ def test_bias_colsum():
     cu = _cu()
     x = _rand(3000, 1152)
     torch.testing.assert_close(cu._C.colsum(x), x.float().sum(0), atol=1e-2, rtol=1e-3)
+
+
+def test_layer_norm_linear_and_gelu_linear_match_unfused():
+    T, H, N = 500, 1152, 4304
+    x = _rand(T, H).requires_grad_()
+    lw, lb = _rand(H, scale=0.5).requires_grad_(), _rand(H, scale=0.5).requires_grad_()
+    w, b = _rand(N, H, scale=0.03).requires_grad_(), _rand(N, scale=0.1).requires_grad_()
+    w2, b2 = _rand(H, N, scale=0.03).requires_grad_(), _rand(H, scale=0.1).requires_grad_()
+    pre = ops.layer_norm_linear(x, lw, lb, w, b, 1e-6)
+    y = ops.gelu_linear(pre, w2, b2, "tanh")
+    g = _rand(T, H)
+    y.backward(g)
+    xr, lwr, lbr, wr, br, w2r, b2r = (t.detach().float().requires_grad_() for t in (x, lw, lb, w, b, w2, b2))
+    pr = torch.nn.functional.linear(torch.nn.functional.layer_norm(xr, (H,), lwr, lbr, 1e-6), wr, br)
+    yr = torch.nn.functional.linear(torch.nn.functional.gelu(pr, approximate="tanh"), w2r, b2r)
+    yr.backward(g.float())
+    _close(pre, pr, 0.05, 2e-2, "pre")
+    _close(y, yr, 0.06, 3e-2, "y")
+    _close(x.grad, xr.grad, 0.06, 4e-2, "dx")
+    _close(w.grad, wr.grad, 0.4, 4e-2, "dw1")
+    _close(w2.grad, w2r.grad, 0.4, 4e-2, "dw2")
+    _close(b.grad, br.grad, 0.5, 4e-2, "db1")
+    _close(b2.grad, b2r.grad, 0.5, 4e-2, "db2")
+    _close(lw.grad, lwr.grad, 1.0, 4e-2, "dln_w")
+    _close(lb.grad, lbr.grad, 1.0, 4e-2, "dln_b")

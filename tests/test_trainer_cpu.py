@@ -53,7 +53,7 @@ def test_single_process_loss_decreases(tmp_path, monkeypatch):
 
     class Same:
         def __next__(self):
-            return dict(fixed)
+            return fixed
 
         def close(self):
             pass
@@ -109,16 +109,18 @@ torch.distributed.destroy_process_group() if torch.distributed.is_initialized() 
 """
 
 
-def _run_ranks(tmp_path, nproc, extra, port):
+def _run_ranks(tmp_path, nproc, extra, port, preset="tiny-qwen3", synthetic="text-uniform", seq_len="256"):
     script = tmp_path / "worker.py"
     script.write_text(WORKER.format(root=ROOT))
     out = tmp_path / f"out{nproc}"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(script),
-           "--model.model_name", "Qwen3-tiny", "--model.preset", "tiny-qwen3", "--training.device", "cpu",
+           "--model.model_name", "Qwen3-VL-tiny" if "vl" in preset else "Qwen3-tiny", "--model.preset", preset,
+           "--model.train_vit", "true", "--training.device", "cpu",
            "--training.bfloat16", "false", "--training.output_dir", str(out), "--training.total_steps", "4",
            "--training.warmup_steps", "0", "--training.save_steps", "0", "--training.lr_llm", "3e-4",
-           "--training.scheduler_type", "cosine", "--data.synthetic", "text-uniform", "--data.seq_len", "256",
+           "--training.scheduler_type", "cosine", "--data.synthetic", synthetic, "--data.seq_len", seq_len,
+           "--training.lr_mlp", "3e-4", "--training.lr_vit", "3e-4",
            "--data.doc_len_min", "16", "--data.doc_len_max", "128", "--wandb.mode", "disabled"] + extra
     env = dict(os.environ, OMP_NUM_THREADS="2")
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
@@ -143,3 +145,15 @@ def test_tp2_sequence_parallel_matches_single_rank(tmp_path):
     tp2_nosp = _run_ranks(tmp_path, 2, ["--training.tp_size", "2"], 29625)
     assert tp2 == pytest.approx(one, rel=2e-4, abs=2e-4)
     assert tp2_nosp == pytest.approx(one, rel=2e-4, abs=2e-4)
+
+
+@pytest.mark.slow
+def test_vlm_tp2_image_parallel_vit_matches_single_rank(tmp_path):
+    """Under TP the vision tower runs image-parallel and its features are exchanged; with and without sequence
+    parallelism the losses must follow the single-rank run (fp32, gloo)."""
+    kw = dict(preset="tiny-qwen3-vl-gpu", synthetic="vlm", seq_len="1024")
+    one = _run_ranks(tmp_path, 1, [], 29626, **kw)
+    sp = _run_ranks(tmp_path, 2, ["--training.tp_size", "2", "--training.sequence_parallel", "true"], 29627, **kw)
+    nosp = _run_ranks(tmp_path, 2, ["--training.tp_size", "2"], 29628, **kw)
+    assert sp == pytest.approx(one, rel=5e-4, abs=5e-4)
+    assert nosp == pytest.approx(one, rel=5e-4, abs=5e-4)

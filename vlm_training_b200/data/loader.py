@@ -22,9 +22,17 @@ _TENSOR_KEYS = ("input_ids", "labels", "cu_seqlens", "pixel_values", "image_grid
 
 
 class PrefetchLoader:
-    def __init__(self, dataset, depth: int = 2, pin: bool = True):
+    """``transfer``: optional ``batch -> kwargs`` callable (see :func:`to_device`) run by the worker thread on its own
+    CUDA stream, so the host→device copies and the plan construction of step n+1 overlap step n; ``__next__`` then
+    returns the device-side kwargs and makes the consumer's stream wait for the copies."""
+
+    def __init__(self, dataset, depth: int = 2, pin: bool = True, transfer=None, device=None):
         self.dataset = iter(dataset)
         self.pin = pin and torch.cuda.is_available()
+        self.transfer = transfer
+        self.device = device
+        self.stream = torch.cuda.Stream(device=device) if (transfer is not None and device is not None
+                                                            and torch.device(device).type == "cuda") else None
         self.q: queue.Queue = queue.Queue(maxsize=depth)
         self._stop = False
         self.thread = threading.Thread(target=self._work, daemon=True)
@@ -47,6 +55,17 @@ class PrefetchLoader:
                     for k in _TENSOR_KEYS:
                         if k in batch and torch.is_tensor(batch[k]):
                             batch[k] = batch[k].pin_memory()
+                if self.transfer is not None:
+                    meta = {"n_tokens": int(batch["input_ids"].numel()), "n_label": int((batch["labels"] != -100).sum()),
+                            "n_docs": int(batch["cu_seqlens"].numel()) - 1, "h2d_bytes": batch_nbytes(batch)}
+                    if self.stream is not None:
+                        with torch.cuda.stream(self.stream):
+                            kwargs = self.transfer(batch)
+                            ev = torch.cuda.Event()
+                            ev.record(self.stream)
+                    else:
+                        kwargs, ev = self.transfer(batch), None
+                    batch = {"kwargs": kwargs, "event": ev, "meta": meta, "host_batch": batch}
                 if not self._put(batch):
                     return
         except StopIteration:
@@ -63,6 +82,11 @@ class PrefetchLoader:
             raise StopIteration
         if isinstance(item, Exception):
             raise item
+        if self.transfer is not None and item.get("event") is not None:
+            cur = torch.cuda.current_stream()
+            cur.wait_event(item["event"])
+            for t in _tensors_of(item["kwargs"]):
+                t.record_stream(cur)  # allocated on the loader's stream, consumed on the training stream
         return item
 
     def close(self):
@@ -75,6 +99,21 @@ class PrefetchLoader:
             pass
         if self.thread.is_alive() and threading.current_thread() is not self.thread:
             self.thread.join(timeout=30)
+
+
+def _tensors_of(obj):
+    if torch.is_tensor(obj):
+        if obj.is_cuda:
+            yield obj
+    elif isinstance(obj, dict):
+        for v in obj.values():
+            yield from _tensors_of(v)
+    elif isinstance(obj, (list, tuple)):
+        for v in obj:
+            yield from _tensors_of(v)
+    elif hasattr(obj, "__dataclass_fields__"):
+        for name in obj.__dataclass_fields__:
+            yield from _tensors_of(getattr(obj, name))
 
 
 def batch_nbytes(batch: dict) -> int:

@@ -148,7 +148,10 @@ class _CausalLMBase(nn.Module):
         x = ops.embedding(ids[lo:hi], dec.embed_tokens.weight)
         deepstack = None
         if pixel_values is not None and self.visual is not None:
-            merged, deep = self.visual(pixel_values, image_grid_thw, batch_plan.vision)
+            if tp is not None and tp.enabled:
+                merged, deep = self._vision_image_parallel(pixel_values, image_grid_thw, tp, dev)
+            else:
+                merged, deep = self.visual(pixel_values, image_grid_thw, batch_plan.vision)
             rows = batch_plan.image_rows
             if rows.numel() != merged.shape[0]:
                 raise ValueError(f"{rows.numel()} image tokens in the row but the vision tower produced {merged.shape[0]}")
@@ -183,6 +186,36 @@ class _CausalLMBase(nn.Module):
             n_valid = (targets != -100).sum()
         loss = loss_sum / n_valid.to(loss_sum.dtype)
         return CausalLMOutput(loss=loss, logits=logits, loss_sum=loss_sum, n_valid=n_valid)
+
+    def _vision_image_parallel(self, pixel_values, image_grid_thw, tp, dev):
+        """The vision tower is replicated across the tensor-parallel group (as in the reference,
+        train/infra.py:382-383) but its WORK is not: every rank encodes a contiguous share of the row's images
+        and the merged / DeepStack features are exchanged with one uneven all-gather (the backward of which
+        routes each feature's gradient back to the rank that produced it)."""
+        from ..parallel.tp_comm import gather_uneven
+
+        grids = image_grid_thw.tolist() if torch.is_tensor(image_grid_thw) else list(image_grid_thw)
+        merge2 = self.config.vision.spatial_merge_size ** 2
+        ranges = positions.split_images(grids, tp.size)
+        patches = [sum(t * h * w for t, h, w in grids[lo:hi]) for lo, hi in ranges]
+        lo, hi = ranges[tp.rank]
+        p0 = sum(patches[: tp.rank])
+        if hi > lo:
+            plan = VisionPlan.build(grids[lo:hi], self.config.vision, dev)
+            merged, deep = self.visual(pixel_values[p0:p0 + patches[tp.rank]], None, plan)
+            feats = torch.cat([merged] + list(deep), dim=-1)
+        else:
+            n_out = 1 + len(self.config.vision.deepstack_visual_indexes)
+            # a rank without images still takes part in the exchange; its tower gradients stay zero in the flat buffer
+            feats = pixel_values.new_zeros((0, n_out * self.config.vision.out_hidden_size),
+                                           dtype=self.decoder.embed_tokens.weight.dtype)
+            if torch.is_grad_enabled():
+                feats.requires_grad_()  # keeps the exchange's backward collective in this rank's autograd graph too
+        sizes = [p // merge2 for p in patches]
+        allf = gather_uneven(feats, sizes, tp, grad_identical=not tp.sequence_parallel)
+        H = self.config.vision.out_hidden_size
+        chunks = allf.split(H, dim=-1)
+        return chunks[0], list(chunks[1:])
 
     def _run_decoder(self, x, ctx, deepstack, batch_plan):
         return self.decoder.run_layers(x, ctx, deepstack)

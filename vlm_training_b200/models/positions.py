@@ -152,3 +152,19 @@ def vision_pos_embed_plan(grids, num_grid_per_side: int, merge: int = 2) -> tupl
 def num_image_tokens(grids, merge: int = 2) -> int:
     g = np.asarray(grids, dtype=np.int64).reshape(-1, 3)
     return int((g[:, 0] * (g[:, 1] // merge) * (g[:, 2] // merge)).sum())
+
+
+def split_images(grids, parts: int) -> list[tuple[int, int]]:
+    """Contiguous ranges of images ``[(lo, hi), ...]`` (one per part) with roughly equal patch counts, so the
+    vision tower can run image-parallel and the concatenation of the parts keeps the original image order."""
+    g = np.asarray(grids, dtype=np.int64).reshape(-1, 3)
+    w = g[:, 0] * g[:, 1] * g[:, 2]
+    total = int(w.sum())
+    csum = np.concatenate(([0], np.cumsum(w)))
+    cuts = [0]
+    for p in range(1, parts):
+        target = total * p / parts
+        j = int(np.argmin(np.abs(csum - target)))
+        cuts.append(max(j, cuts[-1]))
+    cuts.append(len(g))
+    return [(cuts[i], cuts[i + 1]) for i in range(parts)]

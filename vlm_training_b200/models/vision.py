@@ -72,9 +72,13 @@ class VisionAttention(nn.Module):
         self.qkv = Linear(cfg.hidden_size, 3 * cfg.hidden_size, bias=True)
         self.proj = Linear(cfg.hidden_size, cfg.hidden_size, bias=True)
 
-    def forward(self, x, plan: VisionPlan):
+    def forward(self, x, plan: VisionPlan, prenorm: "nn.LayerNorm | None" = None):
         S = x.shape[0]
-        qkv = self.qkv(x).view(S, 3, self.n_heads, self.head_dim)
+        if prenorm is not None:
+            qkv = ops.layer_norm_linear(x, prenorm.weight, prenorm.bias, self.qkv.weight, self.qkv.bias, prenorm.eps)
+        else:
+            qkv = self.qkv(x)
+        qkv = qkv.view(S, 3, self.n_heads, self.head_dim)
         q, k, v = qkv.unbind(1)
         D = self.head_dim
         if x.is_cuda and D not in (64, 128) and D < 128:
@@ -96,8 +100,12 @@ class VisionMLP(nn.Module):
         self.linear_fc2 = Linear(cfg.intermediate_size, cfg.hidden_size, bias=True)
         self.approx = "tanh" if "tanh" in cfg.hidden_act else "none"
 
-    def forward(self, x):
-        return self.linear_fc2(ops.linear_gelu(x, self.linear_fc1.weight, self.linear_fc1.bias, self.approx))
+    def forward(self, x, prenorm: "nn.LayerNorm | None" = None):
+        if prenorm is not None:
+            pre = ops.layer_norm_linear(x, prenorm.weight, prenorm.bias, self.linear_fc1.weight, self.linear_fc1.bias, prenorm.eps)
+        else:
+            pre = ops.linear(x, self.linear_fc1.weight, self.linear_fc1.bias)
+        return ops.gelu_linear(pre, self.linear_fc2.weight, self.linear_fc2.bias, self.approx)
 
 
 class VisionBlock(nn.Module):
@@ -109,8 +117,8 @@ class VisionBlock(nn.Module):
         self.mlp = VisionMLP(cfg)
 
     def forward(self, x, plan: VisionPlan):
-        x = x + self.attn(ops.layer_norm(x, self.norm1.weight, self.norm1.bias, self.norm1.eps), plan)
-        return x + self.mlp(ops.layer_norm(x, self.norm2.weight, self.norm2.bias, self.norm2.eps))
+        x = x + self.attn(x, plan, prenorm=self.norm1)
+        return x + self.mlp(x, prenorm=self.norm2)
 
 
 class PatchMerger(nn.Module):
@@ -131,7 +139,8 @@ class PatchMerger(nn.Module):
             x = ops.layer_norm(x.view(-1, self.merged), self.norm.weight, self.norm.bias, self.norm.eps)
         else:
             x = ops.layer_norm(x, self.norm.weight, self.norm.bias, self.norm.eps).view(-1, self.merged)
-        return self.linear_fc2(ops.linear_gelu(x, self.linear_fc1.weight, self.linear_fc1.bias, "none"))
+        pre = ops.linear(x, self.linear_fc1.weight, self.linear_fc1.bias)
+        return ops.gelu_linear(pre, self.linear_fc2.weight, self.linear_fc2.bias, "none")
 
 
 class VisionModel(nn.Module):

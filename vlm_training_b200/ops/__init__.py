@@ -84,6 +84,21 @@ def rms_norm_linear(x, norm_weight, weight, eps: float = 1e-6, offset: bool = Fa
     return ref.linear(ref.rms_norm(r, norm_weight, eps, offset), weight), r
 
 
+def layer_norm_linear(x, ln_weight, ln_bias, weight, bias=None, eps: float = 1e-6):
+    """``linear(layer_norm(x), weight, bias)``; on CUDA the normalised activation is recomputed in backward."""
+    if _use_cuda(x):
+        return _cu().layer_norm_linear(x, ln_weight, ln_bias, weight, bias, eps)
+    return ref.linear(ref.layer_norm(x, ln_weight, ln_bias, eps), weight, bias)
+
+
+def gelu_linear(pre, weight, bias=None, approximate: str = "tanh"):
+    """``linear(gelu(pre), weight, bias)``; on CUDA only ``pre`` is kept for backward."""
+    if _use_cuda(pre):
+        return _cu().gelu_linear(pre, weight, bias, approximate)
+    act = ref.gelu_tanh(pre) if approximate == "tanh" else ref.gelu_erf(pre)
+    return ref.linear(act, weight, bias)
+
+
 def swiglu_linear(gate_up, weight):
     """``linear(silu(gate) * up, weight)`` for a fused ``[T, 2I]`` input; on CUDA only ``gate_up`` is kept for backward."""
     if _use_cuda(gate_up):

@@ -323,6 +323,81 @@ def rms_norm_linear(x, norm_weight, weight, eps=1e-6, offset=False, residual=Non
     return _NormLinear.apply(x, residual, norm_weight, weight, eps, offset)
 
 
+class _LNLinear(torch.autograd.Function):
+    """``linear(layer_norm(x))`` keeping ``x`` and the row statistics; the normalised activation is recomputed in backward."""
+
+    @staticmethod
+    def forward(ctx, x, ln_w, ln_b, w, b, eps):
+        xc = x.contiguous()
+        h, mean, rstd = _C.layernorm_fwd(xc, ln_w, ln_b, eps)
+        wc = _as_gemm_operand(w)
+        y = _gemm(h, wc, bias=b)
+        _tick()
+        ctx.save_for_backward(xc, ln_w, ln_b, mean, rstd, wc)
+        ctx.eps, ctx.has_bias = eps, b is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, ln_w, ln_b, mean, rstd, w = ctx.saved_tensors
+        dy2 = _as_gemm_operand(dy)
+        h = _C.layernorm_fwd(x, ln_w, ln_b, ctx.eps)[0]
+        dw = _gemm(dy2, h, a_mn=True, b_mn=True)
+        del h
+        dh = _gemm(dy2, w, b_mn=True)
+        dx, dlw, dlb = _C.layernorm_bwd(dh, x, ln_w, mean, rstd)
+        db = None
+        if ctx.has_bias:
+            db = _C.colsum(dy2).to(dy.dtype) if dy2.shape[1] % 2 == 0 else dy2.float().sum(0).to(dy.dtype)
+        _tick(4)
+        return dx, dlw.to(ln_w.dtype), dlb.to(ln_w.dtype) if ln_b is not None else None, dw, db, None
+
+
+def layer_norm_linear(x, ln_weight, ln_bias, weight, bias=None, eps=1e-6):
+    ok = x.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and x.dim() == 2 and not _small_or_odd(x, weight)
+    if not ok:
+        return linear(layer_norm(x, ln_weight, ln_bias, eps), weight, bias)
+    return _LNLinear.apply(x, ln_weight, ln_bias, weight, bias, eps)
+
+
+class _GeluLinear(torch.autograd.Function):
+    """``linear(gelu(pre))`` keeping only ``pre``; the activation is recomputed in backward."""
+
+    @staticmethod
+    def forward(ctx, pre, w, b, tanh_approx):
+        pc = pre.contiguous()
+        act = _C.gelu_fwd(pc, tanh_approx)
+        wc = _as_gemm_operand(w)
+        y = _gemm(act, wc, bias=b)
+        _tick()
+        ctx.save_for_backward(pc, wc)
+        ctx.tanh_approx, ctx.has_bias = tanh_approx, b is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        pre, w = ctx.saved_tensors
+        dy2 = _as_gemm_operand(dy)
+        act = _C.gelu_fwd(pre, ctx.tanh_approx)
+        dw = _gemm(dy2, act, a_mn=True, b_mn=True)
+        del act
+        dact = _gemm(dy2, w, b_mn=True)
+        dpre = _C.gelu_bwd(dact, pre, ctx.tanh_approx)
+        db = None
+        if ctx.has_bias:
+            db = _C.colsum(dy2).to(dy.dtype) if dy2.shape[1] % 2 == 0 else dy2.float().sum(0).to(dy.dtype)
+        _tick(3)
+        return dpre, dw, db, None
+
+
+def gelu_linear(pre, weight, bias=None, approximate="tanh"):
+    ok = (pre.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and pre.dim() == 2 and pre.numel() % 8 == 0
+          and not _small_or_odd(pre, weight))
+    if not ok:
+        return linear(gelu(pre, approximate), weight, bias)
+    return _GeluLinear.apply(pre, weight, bias, approximate == "tanh")
+
+
 class _SwiGLULinear(torch.autograd.Function):
     """``linear(silu(gate) * up)`` that stores only ``gate_up``; the activation is recomputed in backward."""
 
@@ -442,6 +517,13 @@ class _AttentionVarlen(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+def _mma_width(valid: int, padded: int) -> int:
+    """Channels the attention MMAs cover.  Skipping zero padding (e.g. 80 of 128 for head_dim 72) was measured
+    SLOWER on B200 than full-width MMAs (N = 80 is an inefficient instruction shape), so only padding of at least
+    half the tile is skipped (N = 64)."""
+    return 64 if valid <= 64 < padded else padded
+
+
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None, valid_dim=None):
     """``valid_dim``: q/k/v are zero-padded beyond this many channels (they were padded to the kernel's tile
     width by the caller); the output keeps the padded width."""
@@ -453,11 +535,11 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None, v
         raise RuntimeError("the attention kernel is not part of this build of the extension")
     cu = cu_seqlens.to(torch.int32)
     if D in (64, 128):
-        return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale), int(valid_dim or D))
+        return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale), _mma_width(valid_dim or D, D))
     if D < 128:
         # pad the head dim with zeros to the kernel's tile width (ViT head_dim 72); the MMAs skip the padding
         o = _AttentionVarlen.apply(_pad_heads(q, 128), _pad_heads(k, 128), _pad_heads(v, 128), cu, int(max_seqlen),
-                                   bool(causal), float(scale), D)
+                                   bool(causal), float(scale), _mma_width(D, 128))
         return o[..., :D]
     raise NotImplementedError(f"attention head_dim {D}")
 

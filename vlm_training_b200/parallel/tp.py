@@ -139,6 +139,10 @@ def apply_tp(model, mesh, sequence_parallel: bool = False, backend: str = "dist"
         elif isinstance(layer.mlp, SparseMoeBlock):
             _mlp(layer.mlp.shared_expert, ctx)
     grad_kind = "partial" if sequence_parallel else "identical"
+    if model.visual is not None:
+        # the tower runs image-parallel over the group: each rank sees only its share of the images
+        for p in model.visual.parameters():
+            p._tp_grad = "partial"
     for p in model.parameters():
         if not getattr(p, "_tp_sharded", False):
             p._tp_sharded = False

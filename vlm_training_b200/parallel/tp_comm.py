@@ -143,3 +143,43 @@ def gather_rows(x, ctx: TPContext):
 
 def slice_rows(x, ctx: TPContext):
     return _SliceRows.apply(x, ctx) if ctx.enabled else x
+
+
+class _GatherUneven(torch.autograd.Function):
+    """All-gather row blocks of different sizes (sizes known on every rank): forward pads each rank's block to the
+    largest size, gathers, and drops the padding; backward sums every rank's gradient for the local block
+    (reduce-scatter on the padded layout).  Used to share vision features produced image-parallel across the
+    tensor-parallel group."""
+
+    @staticmethod
+    def forward(fctx, x, sizes, ctx, grad_identical=False):
+        fctx.tp, fctx.sizes, fctx.grad_identical = ctx, sizes, grad_identical
+        mx = max(sizes)
+        pad = x.new_zeros((mx,) + tuple(x.shape[1:]))
+        pad[: x.shape[0]].copy_(x)
+        out = x.new_empty((mx * ctx.size,) + tuple(x.shape[1:]))
+        dist.all_gather_into_tensor(out, pad, group=ctx.group)
+        parts = [out[r * mx: r * mx + sizes[r]] for r in range(ctx.size)]
+        return torch.cat(parts, 0)
+
+    @staticmethod
+    def backward(fctx, g):
+        ctx, sizes = fctx.tp, fctx.sizes
+        if fctx.grad_identical:
+            # every rank already holds the complete gradient (replicated consumers): keep the local block
+            o = sum(sizes[: ctx.rank])
+            return g[o:o + sizes[ctx.rank]].contiguous(), None, None, None
+        mx = max(sizes)
+        padded = g.new_zeros((mx * ctx.size,) + tuple(g.shape[1:]))
+        o = 0
+        for r, n in enumerate(sizes):
+            padded[r * mx: r * mx + n].copy_(g[o:o + n])
+            o += n
+        mine = _reduce_scatter_rows(padded, ctx)
+        return mine[: sizes[ctx.rank]].contiguous(), None, None, None
+
+
+def gather_uneven(x, sizes, ctx: TPContext, grad_identical: bool = False):
+    """``grad_identical``: the consumers of the gathered tensor are replicated over the group, so each rank's
+    gradient is already the full one (no sum in backward)."""
+    return _GatherUneven.apply(x, list(sizes), ctx, grad_identical) if ctx.enabled else x

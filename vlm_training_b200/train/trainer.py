@@ -140,7 +140,9 @@ class Trainer:
             from ..data.task_encoders import build_dataset
 
             ds = build_dataset(d, self.cfg.training, self.model_config, dp_rank=self.mesh.dp_rank, dp_size=self.mesh.dp)
-        return PrefetchLoader(ds, depth=max(2, d.num_workers))
+        pixel_dtype = next(self.model.parameters()).dtype
+        transfer = lambda b: to_device(b, self.model_config, self.device, pixel_dtype=pixel_dtype)
+        return PrefetchLoader(ds, depth=max(2, d.num_workers), transfer=transfer, device=self.device)
 
     # ------------------------------------------------------------------ data
     def batch_generator(self):
@@ -151,15 +153,16 @@ class Trainer:
                 batch = next(self.loader)
             except StopIteration:
                 return
-            n_tokens = int(batch["input_ids"].numel())
-            cu = batch["cu_seqlens"]
-            n_label = int((batch["labels"] != -100).sum())
-            self._window["tokens"] += n_tokens
-            self._window["label_tokens"] += n_label
-            self._window["samples"] += int(cu.numel()) - 1
-            self._window["h2d_bytes"] += batch_nbytes(batch)
-            kwargs = to_device(batch, self.model_config, self.device,
-                               pixel_dtype=next(self.model.parameters()).dtype)
+            if "kwargs" in batch:  # the loader thread already copied the batch to the device
+                meta, kwargs = batch["meta"], batch["kwargs"]
+            else:
+                meta = {"n_tokens": int(batch["input_ids"].numel()), "n_label": int((batch["labels"] != -100).sum()),
+                        "n_docs": int(batch["cu_seqlens"].numel()) - 1, "h2d_bytes": batch_nbytes(batch)}
+                kwargs = to_device(batch, self.model_config, self.device, pixel_dtype=next(self.model.parameters()).dtype)
+            self._window["tokens"] += meta["n_tokens"]
+            self._window["label_tokens"] += meta["n_label"]
+            self._window["samples"] += meta["n_docs"]
+            self._window["h2d_bytes"] += meta["h2d_bytes"]
             self._window["data_time"] += time.perf_counter() - t0
             yield kwargs
 
