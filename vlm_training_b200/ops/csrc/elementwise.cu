@@ -7,6 +7,7 @@
 // weight-gradient partial sums written per block (reduced by the caller) so results are
 // bit-reproducible run to run.
 #include "elementwise.h"
+#include "no_alloc_entry.h"
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -919,3 +920,78 @@ void vlmt_rows_gather(void* dst, const long* index, const void* src, long n_rows
 }
 
 }  // extern "C"
+
+
+// ===================================================================================== allocation-free variant
+// RMSNorm backward whose per-block partial weight gradients live in a fixed array of the library image instead of
+// a caller-provided scratch tensor (contract: no_alloc_entry.h).  Nothing above this line is changed by it.
+#include <mutex>
+#include <stdio.h>
+
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[VLMT_NOALLOC_MAX_BLOCKS * VLMT_NOALLOC_MAX_D];
+
+namespace {
+// dw[c] = sum over the `blocks` partial rows written by the backward kernel (every slot read here was written by it)
+__global__ void static_scratch_colsum_kernel(const float* __restrict__ partial, float* __restrict__ dw, int blocks, int D) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float s = 0.f;
+  for (int b = 0; b < blocks; ++b) s += partial[(size_t)b * D + c];
+  dw[c] = s;
+}
+
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mutex;
+
+// Device address of the scratch array on the CURRENT device (looked up once per device; in host code the array's name
+// is only a handle for this lookup, never a pointer a kernel may use).
+float* scratch_for_current_device(int* err) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) { *err = VLMT_NOALLOC_ERR_SYMBOL; return nullptr; }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_rmsnorm_bwd_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      fprintf(stderr, "vlmt_rmsnorm_bwd_static: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
+      *err = VLMT_NOALLOC_ERR_SYMBOL;
+      return nullptr;
+    }
+    g_scratch_addr[dev] = ptr;
+  }
+  return g_scratch_addr[dev];
+}
+}  // namespace
+
+extern "C" int vlmt_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, int w_fp32, const float* rstd, const void* dres,
+                                       void* dx, float* dw, int rows, int D, int offset, cudaStream_t st) {
+  if (D <= 0 || (D & 7) || D > VLMT_NOALLOC_MAX_D) {
+    fprintf(stderr, "vlmt_rmsnorm_bwd_static: D = %d is not supported (need a multiple of 8, at most %d: the built-in scratch "
+                    "holds %d x %d floats)\n", D, VLMT_NOALLOC_MAX_D, VLMT_NOALLOC_MAX_BLOCKS, VLMT_NOALLOC_MAX_D);
+    return VLMT_NOALLOC_ERR_SIZE;
+  }
+  if (rows <= 0) return 0;
+  int err = 0;
+  float* scratch = scratch_for_current_device(&err);
+  if (scratch == nullptr) return err;
+  const int nw = bwd_warps(D);
+  if (nw == 0) return VLMT_NOALLOC_ERR_SIZE;
+  int grid = (rows + nw - 1) / nw;
+  if (grid > VLMT_NOALLOC_MAX_BLOCKS) grid = VLMT_NOALLOC_MAX_BLOCKS;
+  const size_t smem = (size_t)nw * D * sizeof(float);
+  if (w_fp32) {
+    auto k = rmsnorm_bwd_kernel<float>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<grid, nw * 32, smem, st>>>(BF(dy), BF(x), (const float*)w, rstd, BF(dres), BFM(dx), scratch, rows, D, offset);
+  } else {
+    auto k = rmsnorm_bwd_kernel<bf16>;
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<grid, nw * 32, smem, st>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx), scratch, rows, D, offset);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  static_scratch_colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, dw, grid, D);
+  return (int)cudaGetLastError();
+}
