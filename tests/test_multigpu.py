@@ -24,6 +24,10 @@ hist = tr.train()
 if tr.rank == 0:
     os.makedirs(cfg.training.output_dir, exist_ok=True)
     json.dump([m["train/loss"] for m in hist], open(os.path.join(cfg.training.output_dir, "losses.json"), "w"))
+    # a sample of updated weights: Adam hides a wrong gradient SCALE, but a wrongly weighted sum flips update signs
+    probe = torch.cat([p.detach().float().flatten()[:512] for n, p in tr.model.named_parameters()
+                       if n.endswith("down_proj.weight") or n.endswith("lm_head.weight") or "merger.linear_fc2.weight" in n])
+    json.dump(probe.tolist(), open(os.path.join(cfg.training.output_dir, "probe.json"), "w"))
 if torch.distributed.is_initialized():
     torch.distributed.destroy_process_group()
 """
@@ -39,10 +43,11 @@ def _run(tmp_path, nproc, extra, port, env_extra=None):
            "--training.save_steps", "0", "--training.lr_llm", "1e-3", "--training.lr_mlp", "1e-3", "--training.lr_vit", "1e-3",
            "--training.scheduler_type", "cosine", "--training.data_parallel", "fsdp", "--data.synthetic", "vlm",
            "--data.seq_len", "2048", "--wandb.mode", "disabled"] + extra
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", VLMT_PG_TIMEOUT_S="120")
     env.update(env_extra or {})
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    _run.last_probe = json.load(open(out / "probe.json"))
     return json.load(open(out / "losses.json"))
 
 
@@ -50,10 +55,19 @@ def test_tp2_sp_matches_one_gpu(tmp_path):
     one = _run(tmp_path, 1, [], 29701)
     tp2 = _run(tmp_path, 2, ["--training.tp_size", "2", "--training.sequence_parallel", "true", "--training.fused_comm", "false"], 29702)
     assert tp2 == pytest.approx(one, rel=3e-2, abs=3e-2)
+    # the same run with the layer collectives and the optimizer step on our own NVLink kernels (plain peer loads)
+    p2p = _run(tmp_path, 2, ["--training.tp_size", "2", "--training.sequence_parallel", "true", "--training.fused_comm", "true"], 29705,
+               {"VLMT_NO_MULTIMEM": "1"})
+    assert p2p == pytest.approx(tp2, rel=2e-2, abs=2e-2)
 
 
 def test_fused_optimizer_matches_nccl(tmp_path):
     nccl = _run(tmp_path, 2, ["--training.fused_comm", "false"], 29703)
+    probe_nccl = torch.tensor(_run.last_probe)
     fused = _run(tmp_path, 2, ["--training.fused_comm", "true"], 29704, {"VLMT_NO_MULTIMEM": "1"})
+    probe_fused = torch.tensor(_run.last_probe)
     assert fused == pytest.approx(nccl, rel=2e-3, abs=2e-3)
     assert fused[-1] < fused[0]
+    # weights after 4 steps at lr 1e-3: a flipped update sign shows as a ~2e-3 difference
+    frac_off = ((probe_fused - probe_nccl).abs() > 5e-4).float().mean().item()
+    assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ between the fused and the NCCL optimizer step"

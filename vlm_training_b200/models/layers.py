@@ -20,7 +20,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from ..parallel.tp_comm import TPContext, column_input, row_output
+from ..parallel.tp_comm import TPContext, column_input, row_linear, row_output
 from .config import TextConfig
 
 _NO_TP = TPContext()
@@ -64,8 +64,7 @@ class Linear(nn.Module):
         if self.parallel == "column":
             return ops.linear(column_input(x, self.tp), self.weight, self.bias)
         if self.parallel == "row":
-            y = ops.linear(x, self.weight, None)
-            y = row_output(y, self.tp)
+            y = row_linear(x, self.weight, self.tp)
             return y if self.bias is None else y + self.bias
         return ops.linear(x, self.weight, self.bias)
 

@@ -220,8 +220,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kv0 = j * BN;
       const bool need_mask = (kv0 + BN > ti.doc_len) || (p.causal && kv0 + BN - 1 > ti.q0);
       const int limit = p.causal ? min(ti.doc_len - 1, qi) : ti.doc_len - 1;  // last visible key (local index)
-      // pass 1: row max
-      float mx = m;
+      // pass 1: row max of the raw scores (the softmax scale is positive, so it commutes with max)
+      float mx_raw = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t rr[32];
@@ -229,12 +229,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) { const float x = __uint_as_float(rr[i]) * p.scale_log2; if (kv0 + c * 32 + i <= limit) mx = fmaxf(mx, x); }
+          for (int i = 0; i < 32; ++i) if (kv0 + c * 32 + i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(rr[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(rr[i]) * p.scale_log2);
+          for (int i = 0; i < 32; ++i) mx_raw = fmaxf(mx_raw, __uint_as_float(rr[i]));
         }
       }
+      const float mx = fmaxf(m, mx_raw * p.scale_log2);
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
       m = mx;
@@ -242,6 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // pass 2: probabilities -> smem (bf16), row sum
       uint8_t* sP = smem + L::offP + b * L::kP;
       float rowsum = 0.f;
+      const float neg_m = -m_use;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t rr[32];
@@ -250,21 +252,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         float pr[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(rr[i]) * p.scale_log2 - m_use);
+          float e = exp2f(fmaf(__uint_as_float(rr[i]), p.scale_log2, neg_m));
           if (need_mask && kv0 + c * 32 + i > limit) e = 0.f;
           pr[i] = e;
+          rowsum += e;
         }
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           uint4 pk;
           __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            p2[u] = __floats2bfloat162_rn(pr[t * 8 + 2 * u], pr[t * 8 + 2 * u + 1]);
-            // sum what the tensor core will actually see (bf16-rounded), keeps O / l consistent
-            const float2 back = __bfloat1622float2(p2[u]);
-            rowsum += back.x + back.y;
-          }
+          for (int u = 0; u < 4; ++u) p2[u] = __floats2bfloat162_rn(pr[t * 8 + 2 * u], pr[t * 8 + 2 * u + 1]);
           st_swizzled_16B(sP, r, c * 32 + t * 8, pk);
         }
       }
@@ -376,23 +374,37 @@ struct BwdParams {
   int* status;
 };
 
-// Shared layout of both backward kernels: four [128 x D] operand tiles + two [128 x 128] bf16 tiles (P, dS)
+// Backward tiles.  Both kernels work on a 128-row "stationary" tile (keys for dK/dV, queries for dQ) and stream
+// 64-row tiles of the other operand, so that S and dP take only 64 TMEM columns each and can be double-buffered:
+// the tensor core computes S/dP of step i+1 while the CUDA cores turn step i into P / dS, and the accumulation MMAs
+// of step i overlap the CUDA-core work of step i+1.
+constexpr int BS = 64;  // rows of the streamed tile
+
 template <int D>
 struct BwdSmem {
-  static constexpr int kTile = 128 * D * 2;
-  static constexpr int kSq = 128 * 128 * 2;
-  static constexpr int offA = 0;              // dkdv: K_j   | dq: Q_i
-  static constexpr int offB = offA + kTile;   // dkdv: V_j   | dq: dO_i
-  static constexpr int offC = offB + kTile;   // dkdv: Q_i   | dq: K_j
-  static constexpr int offD = offC + kTile;   // dkdv: dO_i  | dq: V_j
-  static constexpr int offP = offD + kTile;
-  static constexpr int offDS = offP + kSq;
-  static constexpr int offBar = offDS + kSq;
+  static constexpr int kBig = 128 * D * 2;     // stationary [128 x D] tile
+  static constexpr int kSmall = BS * D * 2;    // streamed [64 x D] tile
+  static constexpr int kSq = 128 * BS * 2;     // [128 x 64] bf16 tile (P^T / dS^T / dS)
+  static constexpr int offA = 0;                       // dkdv: K_j   | dq: Q_i
+  static constexpr int offB = offA + kBig;             // dkdv: V_j   | dq: dO_i
+  static constexpr int offC = offB + kBig;             // 2 stages: dkdv Q_i  | dq K_j
+  static constexpr int offD = offC + 2 * kSmall;       // 2 stages: dkdv dO_i | dq V_j
+  static constexpr int offP = offD + 2 * kSmall;       // 2 buffers (dkdv: P^T)
+  static constexpr int offDS = offP + 2 * kSq;         // 2 buffers (dS^T / dS)
+  static constexpr int offStat = offDS + 2 * kSq;      // per compute warp: (lse2[64], delta[64]) floats
+  static constexpr int offBar = offStat + 4 * 128 * 4;
   static constexpr int kTotal = offBar + 256 + 1024;
 };
 
-// dK_j, dV_j for one key tile and one kv head: loop over the GQA group's query heads and the query tiles
-// that can see this key tile.  TMEM: S | dP | dV | dK (4 x 128 columns for D = 128).
+// 16 bytes of row r, column col (multiple of 8, < 64) of a [rows x 64] bf16 tile with 128-byte rows and 128-byte swizzle
+__device__ __forceinline__ void st_sw64_16B(uint8_t* tile, int r, int col, uint4 v) {
+  *reinterpret_cast<uint4*>(tile + r * 128 + (((col >> 3) ^ (r & 7)) << 4)) = v;
+}
+
+// dK_j, dV_j for one 128-key tile and one kv head.  Everything is computed transposed (rows = keys):
+//   S^T = K Q^T, dP^T = V dO^T  (M = 128 keys, N = 64 queries)   ->  P^T, dS^T (thread = key row)
+//   dV += P^T dO,  dK += dS^T Q  (A = [128 keys x 64 queries] K-major, B = the [64 x D] query-side tile read MN-major)
+// TMEM columns: S^T[2] 0/64, dP^T[2] 128/192, dV 256, dK 256 + D.
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -402,30 +414,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
-  uint64_t* kv_full = bars;        // K_j and V_j landed
-  uint64_t* qdo_full = bars + 1;   // Q_i and dO_i landed
-  uint64_t* qdo_empty = bars + 2;  // all MMAs reading Q_i / dO_i done
-  uint64_t* sdp_full = bars + 3;   // S and dP computed
-  uint64_t* pds_full = bars + 4;   // P and dS written to smem (4 warps)
-  uint64_t* acc_done = bars + 5;   // final dV/dK accumulation done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* kv_full = bars;          // 1
+  uint64_t* qdo_full = bars + 1;     // 2
+  uint64_t* qdo_empty = bars + 3;    // 2
+  uint64_t* sdp_full = bars + 5;     // 2
+  uint64_t* sdp_empty = bars + 7;    // 2 (4 warps)
+  uint64_t* pds_full = bars + 9;     // 2 (4 warps)
+  uint64_t* pds_empty = bars + 11;   // 2
+  uint64_t* acc_done = bars + 13;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stat = reinterpret_cast<float*>(smem + L::offStat);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const TileInfo ti = find_tile(p.cu, p.n_docs, blockIdx.x, BN);
+  const TileInfo ti = find_tile(p.cu, p.n_docs, blockIdx.x, 128);
   if (!ti.valid) return;
   const int hkv = blockIdx.y;
   const int group = p.Hq / p.Hkv;
-  const int k0 = ti.q0;  // first key row of the tile (local)
-  const int n_qblk = (ti.doc_len + BM - 1) / BM;
-  const int i_first = p.causal ? k0 / BM : 0;
+  const int k0 = ti.q0;  // first key row of the tile (local to the document)
+  const int n_qblk = (ti.doc_len + BS - 1) / BS;
+  const int i_first = p.causal ? k0 / BS : 0;
   const int n_iter = (n_qblk - i_first) * group;
   constexpr int TMEM_COLS = 512;
-  constexpr int S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4); mbar_init(acc_done, 1);
+    mbar_init(kv_full, 1); mbar_init(acc_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 4);
+      mbar_init(&pds_full[i], 4); mbar_init(&pds_empty[i], 1);
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -438,122 +456,144 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 0) {
     if (lane == 0) {
       const int krow = ti.doc_start + k0;
-      mbar_expect_tx(kv_full, 2 * L::kTile);
+      mbar_expect_tx(kv_full, 2 * L::kBig);
 #pragma unroll
       for (int b = 0; b < DB; ++b) {
         tma_load_2d(smem + L::offA + b * 16384, &tmK, kv_full, hkv * D + 64 * b, krow);
         tma_load_2d(smem + L::offB + b * 16384, &tmV, kv_full, hkv * D + 64 * b, krow);
       }
       for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1;
         const int i = i_first + it / group, hq = hkv * group + it % group;
-        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
-        const int qrow = ti.doc_start + i * BM;
-        mbar_expect_tx(qdo_full, 2 * L::kTile);
+        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        const int qrow = ti.doc_start + i * BS;
+        mbar_expect_tx(&qdo_full[st], 2 * L::kSmall);
 #pragma unroll
         for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + b * 16384, &tmQ, qdo_full, hq * D + 64 * b, qrow);
-          tma_load_2d(smem + L::offD + b * 16384, &tmdO, qdo_full, hq * D + 64 * b, qrow);
+          tma_load_2d(smem + L::offC + st * L::kSmall + b * 8192, &tmQ, &qdo_full[st], hq * D + 64 * b, qrow);
+          tma_load_2d(smem + L::offD + st * L::kSmall + b * 8192, &tmdO, &qdo_full[st], hq * D + 64 * b, qrow);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S = Q K^T, dP = dO V^T
-      const uint32_t idesc_g = make_idesc_bf16(128, p.d_eff, true, true);     // dV = P^T dO, dK = dS^T Q
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, BS, false, false);   // [128 keys] x [64 queries], contraction over d
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);      // [128 keys] x [D], contraction over 64 queries
       const uint32_t sK = smem_u32(smem + L::offA), sV = smem_u32(smem + L::offB);
-      const uint32_t sQ = smem_u32(smem + L::offC), sdO = smem_u32(smem + L::offD);
-      const uint32_t sP = smem_u32(smem + L::offP), sDS = smem_u32(smem + L::offDS);
+      auto issue_sdp = [&](int it) -> bool {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&qdo_full[st], ph, abort_flag, p.status, kErrTimeoutFull)) return false;
+        if (!mbar_wait(&sdp_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
+        tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + L::offC + st * L::kSmall), sdO = smem_u32(smem + L::offD + st * L::kSmall);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32, offq = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + ST_COL + st * BS, make_smem_desc(sK + offk, 16, 1024), make_smem_desc(sQ + offq, 16, 1024), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32, offq = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + DPT_COL + st * BS, make_smem_desc(sV + offk, 16, 1024), make_smem_desc(sdO + offq, 16, 1024), idesc_s, kk != 0);
+        }
+        umma_commit(&sdp_full[st]);
+        return true;
+      };
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kErrTimeoutFull);
+      if (ok && n_iter > 0) ok = issue_sdp(0);
       for (int it = 0; it < n_iter && ok; ++it) {
-        const uint32_t ph = it & 1;
-        if (!mbar_wait(qdo_full, ph, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+        if (it + 1 < n_iter) { ok = issue_sdp(it + 1); if (!ok) break; }
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&pds_full[st], ph, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + L::offC + st * L::kSmall), sdO = smem_u32(smem + L::offD + st * L::kSmall);
+        const uint32_t sPT = smem_u32(smem + L::offP + st * L::kSq), sDST = smem_u32(smem + L::offDS + st * L::kSq);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          if (kk * 16 >= p.d_eff) break;
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + S_COL, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
-        }
+        for (int kk = 0; kk < BS / 16; ++kk)
+          umma_bf16(tmem_base + DV_COL, make_smem_desc(sPT + kk * 32, 16, 1024), make_smem_desc(sdO + kk * 2048, 8192, 1024), idesc_g,
+                    (it | kk) != 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          if (kk * 16 >= p.d_eff) break;
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + DP_COL, make_smem_desc(sdO + off, 16, 1024), make_smem_desc(sV + off, 16, 1024), idesc_s, kk != 0);
-        }
-        umma_commit(sdp_full);
-        if (!mbar_wait(pds_full, ph, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
-        tc_fence_after();
-        // contraction over the 128 query rows: P / dS are [q][kv] tiles read as MN-major A (M = kv),
-        // dO / Q are [q][d] tiles read as MN-major B (N = d)
-#pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk) {
-          umma_bf16(tmem_base + DV_COL, make_smem_desc(sP + kk * 2048, 16384, 1024), make_smem_desc(sdO + kk * 2048, 16384, 1024),
-                    idesc_g, (it | kk) != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk) {
-          umma_bf16(tmem_base + DK_COL, make_smem_desc(sDS + kk * 2048, 16384, 1024), make_smem_desc(sQ + kk * 2048, 16384, 1024),
-                    idesc_g, (it | kk) != 0);
-        }
-        umma_commit(qdo_empty);
+        for (int kk = 0; kk < BS / 16; ++kk)
+          umma_bf16(tmem_base + DK_COL, make_smem_desc(sDST + kk * 32, 16, 1024), make_smem_desc(sQ + kk * 2048, 8192, 1024), idesc_g,
+                    (it | kk) != 0);
+        umma_commit(&qdo_empty[st]);
+        umma_commit(&pds_empty[st]);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
     const int q = warp & 3;
-    const int r = q * 32 + lane;  // query row within the tile
+    const int r = q * 32 + lane;           // key row of the tile owned by this thread
+    const int kvi = k0 + r;                // key index local to the document
+    const bool key_ok = kvi < ti.doc_len;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
       const int i = i_first + it / group, hq = hkv * group + it % group;
-      const uint32_t ph = it & 1;
-      const int qi = i * BM + r;
-      const bool row_ok = qi < ti.doc_len;
-      const size_t tok = (size_t)ti.doc_start + (row_ok ? qi : 0);
-      const float lse2 = row_ok ? p.LSE[(size_t)hq * p.T + tok] * kLog2e : 0.f;
-      const float dl = row_ok ? p.delta[(size_t)hq * p.T + tok] : 0.f;
-      if (!mbar_wait(sdp_full, ph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      const int q0 = i * BS;
+      // per-query statistics of this step -> this warp's own smem copy (warp-local, so no block barrier is involved)
+      float* wstat = stat + q * 128;
+      __syncwarp();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qc = lane + 32 * h;
+        const int qq = q0 + qc;
+        const bool qok = qq < ti.doc_len;
+        const size_t tok = (size_t)ti.doc_start + (qok ? qq : 0);
+        wstat[qc] = qok ? p.LSE[(size_t)hq * p.T + tok] * kLog2e : INFINITY;  // +inf -> exp2(-inf) = 0 for padded queries
+        wstat[64 + qc] = qok ? p.delta[(size_t)hq * p.T + tok] : 0.f;
+      }
+      __syncwarp();
+      if (!mbar_wait(&sdp_full[st], ph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      // the previous iteration's dV/dK MMAs (which read sP / sDS) completed before S/dP of this one were
-      // committed: tcgen05 MMAs of one CTA execute in issue order, so the buffers are free to overwrite
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      const float* lse2 = wstat;
+      const float* dl = wstat + 64;
+      float pr[BS], ds[BS];
+#pragma unroll
+      for (int c = 0; c < BS / 32; ++c) {
         uint32_t sr[32], dr[32];
-        tmem_ld_32x32(tmem_base + S_COL + lane_addr + c * 32, sr);
-        tmem_ld_32x32(tmem_base + DP_COL + lane_addr + c * 32, dr);
+        tmem_ld_32x32(tmem_base + ST_COL + st * BS + lane_addr + c * 32, sr);
+        tmem_ld_32x32(tmem_base + DPT_COL + st * BS + lane_addr + c * 32, dr);
         tmem_ld_wait();
-        float pr[32], ds[32];
 #pragma unroll
         for (int u = 0; u < 32; ++u) {
-          const int kv = k0 + c * 32 + u;
-          const bool vis = row_ok && kv < ti.doc_len && (!p.causal || kv <= qi);
-          const float pv = vis ? exp2f(__uint_as_float(sr[u]) * p.scale_log2 - lse2) : 0.f;
-          pr[u] = pv;
-          ds[u] = pv * (__uint_as_float(dr[u]) - dl) * p.scale;
-        }
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          uint4 a, b;
-          __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a);
-          __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            a2[u] = __floats2bfloat162_rn(pr[t * 8 + 2 * u], pr[t * 8 + 2 * u + 1]);
-            b2[u] = __floats2bfloat162_rn(ds[t * 8 + 2 * u], ds[t * 8 + 2 * u + 1]);
-          }
-          st_swizzled_16B(smem + L::offP, r, c * 32 + t * 8, a);
-          st_swizzled_16B(smem + L::offDS, r, c * 32 + t * 8, b);
+          const int qc = c * 32 + u;
+          const bool vis = key_ok && (!p.causal || kvi <= q0 + qc);
+          const float pv = vis ? exp2f(fmaf(__uint_as_float(sr[u]), p.scale_log2, -lse2[qc])) : 0.f;
+          pr[qc] = pv;
+          ds[qc] = pv * (__uint_as_float(dr[u]) - dl[qc]) * p.scale;
         }
       }
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sdp_empty[st]);
+      if (!mbar_wait(&pds_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+      uint8_t* sPT = smem + L::offP + st * L::kSq;
+      uint8_t* sDST = smem + L::offDS + st * L::kSq;
+#pragma unroll
+      for (int t = 0; t < BS / 8; ++t) {
+        uint4 a, b;
+        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a);
+        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          a2[u] = __floats2bfloat162_rn(pr[t * 8 + 2 * u], pr[t * 8 + 2 * u + 1]);
+          b2[u] = __floats2bfloat162_rn(ds[t * 8 + 2 * u], ds[t * 8 + 2 * u + 1]);
+        }
+        st_sw64_16B(sPT, r, t * 8, a);
+        st_sw64_16B(sDST, r, t * 8, b);
+      }
       fence_async_proxy();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
+      if (lane == 0) mbar_arrive(&pds_full[st]);
     }
     // epilogue: thread r owns key row k0 + r of dV and dK
     if (ok && mbar_wait(acc_done, 0, abort_flag, p.status, kErrTimeoutTmemFull)) {
       tc_fence_after();
-      const int kvi = k0 + r;
       if (n_iter > 0) {
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
@@ -562,13 +602,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t rr[32];
-            if (c * 32 < p.d_eff) {
-              tmem_ld_32x32(tmem_base + col + lane_addr + c * 32, rr);
-              tmem_ld_wait();
-            }
-#pragma unroll
-            for (int u = 0; u < 32; ++u) if (c * 32 + u >= p.d_eff) rr[u] = 0u;
-            if (kvi < ti.doc_len) {
+            tmem_ld_32x32(tmem_base + col + lane_addr + c * 32, rr);
+            tmem_ld_wait();
+            if (key_ok) {
               __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * D + c * 32;
 #pragma unroll
               for (int t = 0; t < 4; ++t) {
@@ -599,7 +635,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
 }
 
-// dQ_i for one query tile and head: loop over the key tiles it can see.  TMEM: S | dP | dQ.
+// dQ_i for one 128-query tile and head, streaming 64-key tiles.  TMEM: S[2] 0/64, dP[2] 128/192, dQ 256.
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -609,13 +645,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
-  uint64_t* qdo_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* ds_full = bars + 4;
-  uint64_t* acc_done = bars + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* qdo_full = bars;         // 1
+  uint64_t* kv_full = bars + 1;      // 2
+  uint64_t* kv_empty = bars + 3;     // 2
+  uint64_t* sdp_full = bars + 5;     // 2
+  uint64_t* sdp_empty = bars + 7;    // 2 (4 warps)
+  uint64_t* ds_full = bars + 9;      // 2 (4 warps)
+  uint64_t* ds_empty = bars + 11;    // 2
+  uint64_t* acc_done = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -624,13 +662,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int hq = blockIdx.y;
   const int hkv = hq / (p.Hq / p.Hkv);
   const int kv_end = p.causal ? min(ti.doc_len, ti.q0 + BM) : ti.doc_len;
-  const int J = (kv_end + BN - 1) / BN;
+  const int J = (kv_end + BS - 1) / BS;
   constexpr int TMEM_COLS = 512;
   constexpr int S_COL = 0, DP_COL = 128, DQ_COL = 256;
 
   if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1); mbar_init(kv_full, 1); mbar_init(kv_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 4); mbar_init(acc_done, 1);
+    mbar_init(qdo_full, 1); mbar_init(acc_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 4);
+      mbar_init(&ds_full[i], 4); mbar_init(&ds_empty[i], 1);
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -643,57 +684,65 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       const int qrow = ti.doc_start + ti.q0;
-      mbar_expect_tx(qdo_full, 2 * L::kTile);
+      mbar_expect_tx(qdo_full, 2 * L::kBig);
 #pragma unroll
       for (int b = 0; b < DB; ++b) {
         tma_load_2d(smem + L::offA + b * 16384, &tmQ, qdo_full, hq * D + 64 * b, qrow);
         tma_load_2d(smem + L::offB + b * 16384, &tmdO, qdo_full, hq * D + 64 * b, qrow);
       }
       for (int j = 0; j < J; ++j) {
-        if (!mbar_wait(kv_empty, (j & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
-        const int krow = ti.doc_start + j * BN;
-        mbar_expect_tx(kv_full, 2 * L::kTile);
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        const int krow = ti.doc_start + j * BS;
+        mbar_expect_tx(&kv_full[st], 2 * L::kSmall);
 #pragma unroll
         for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + b * 16384, &tmK, kv_full, hkv * D + 64 * b, krow);
-          tma_load_2d(smem + L::offD + b * 16384, &tmV, kv_full, hkv * D + 64 * b, krow);
+          tma_load_2d(smem + L::offC + st * L::kSmall + b * 8192, &tmK, &kv_full[st], hkv * D + 64 * b, krow);
+          tma_load_2d(smem + L::offD + st * L::kSmall + b * 8192, &tmV, &kv_full[st], hkv * D + 64 * b, krow);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      const uint32_t idesc_q = make_idesc_bf16(128, p.d_eff, false, true);  // dQ = dS K : A K-major [q][kv], B = K [kv][d] MN-major
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, BS, false, false);
+      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, false, true);  // dQ = dS K: A [128 q x 64 kv] K-major, B = K_j [64 kv x D] MN-major
       const uint32_t sQ = smem_u32(smem + L::offA), sdO = smem_u32(smem + L::offB);
-      const uint32_t sK = smem_u32(smem + L::offC), sV = smem_u32(smem + L::offD);
-      const uint32_t sDS = smem_u32(smem + L::offDS);
+      auto issue_sdp = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&kv_full[st], ph, abort_flag, p.status, kErrTimeoutFull)) return false;
+        if (!mbar_wait(&sdp_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
+        tc_fence_after();
+        const uint32_t sK = smem_u32(smem + L::offC + st * L::kSmall), sV = smem_u32(smem + L::offD + st * L::kSmall);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t offq = (kk >> 2) * 16384 + (kk & 3) * 32, offk = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + S_COL + st * BS, make_smem_desc(sQ + offq, 16, 1024), make_smem_desc(sK + offk, 16, 1024), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t offq = (kk >> 2) * 16384 + (kk & 3) * 32, offk = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + DP_COL + st * BS, make_smem_desc(sdO + offq, 16, 1024), make_smem_desc(sV + offk, 16, 1024), idesc_s, kk != 0);
+        }
+        umma_commit(&sdp_full[st]);
+        return true;
+      };
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, kErrTimeoutFull);
+      if (ok && J > 0) ok = issue_sdp(0);
       for (int j = 0; j < J && ok; ++j) {
-        const uint32_t ph = j & 1;
-        if (!mbar_wait(kv_full, ph, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+        if (j + 1 < J) { ok = issue_sdp(j + 1); if (!ok) break; }
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&ds_full[st], ph, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t sK = smem_u32(smem + L::offC + st * L::kSmall);
+        const uint32_t sDS = smem_u32(smem + L::offDS + st * L::kSq);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          if (kk * 16 >= p.d_eff) break;
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + S_COL, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          if (kk * 16 >= p.d_eff) break;
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + DP_COL, make_smem_desc(sdO + off, 16, 1024), make_smem_desc(sV + off, 16, 1024), idesc_s, kk != 0);
-        }
-        umma_commit(sdp_full);
-        if (!mbar_wait(ds_full, ph, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t adesc = make_smem_desc(sDS + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sK + kk * 2048, 16384, 1024);
-          umma_bf16(tmem_base + DQ_COL, adesc, bdesc, idesc_q, (j | kk) != 0);
-        }
-        umma_commit(kv_empty);
+        for (int kk = 0; kk < BS / 16; ++kk)
+          umma_bf16(tmem_base + DQ_COL, make_smem_desc(sDS + kk * 32, 16, 1024), make_smem_desc(sK + kk * 2048, 8192, 1024), idesc_q,
+                    (j | kk) != 0);
+        umma_commit(&kv_empty[st]);
+        umma_commit(&ds_empty[st]);
       }
       if (ok) umma_commit(acc_done);
     }
@@ -708,49 +757,50 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float dl = row_ok ? p.delta[(size_t)hq * p.T + tok] : 0.f;
     bool ok = true;
     for (int j = 0; j < J && ok; ++j) {
-      const uint32_t ph = j & 1;
-      if (!mbar_wait(sdp_full, ph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&sdp_full[st], ph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      const int kv0 = j * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      const int kv0 = j * BS;
+      float ds[BS];
+#pragma unroll
+      for (int c = 0; c < BS / 32; ++c) {
         uint32_t sr[32], dr[32];
-        tmem_ld_32x32(tmem_base + S_COL + lane_addr + c * 32, sr);
-        tmem_ld_32x32(tmem_base + DP_COL + lane_addr + c * 32, dr);
+        tmem_ld_32x32(tmem_base + S_COL + st * BS + lane_addr + c * 32, sr);
+        tmem_ld_32x32(tmem_base + DP_COL + st * BS + lane_addr + c * 32, dr);
         tmem_ld_wait();
-        float ds[32];
 #pragma unroll
         for (int u = 0; u < 32; ++u) {
           const int kv = kv0 + c * 32 + u;
           const bool vis = row_ok && kv < ti.doc_len && (!p.causal || kv <= qi);
-          const float pv = vis ? exp2f(__uint_as_float(sr[u]) * p.scale_log2 - lse2) : 0.f;
-          ds[u] = pv * (__uint_as_float(dr[u]) - dl) * p.scale;
-        }
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          uint4 b;
-          __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) b2[u] = __floats2bfloat162_rn(ds[t * 8 + 2 * u], ds[t * 8 + 2 * u + 1]);
-          st_swizzled_16B(smem + L::offDS, r, c * 32 + t * 8, b);
+          const float pv = vis ? exp2f(fmaf(__uint_as_float(sr[u]), p.scale_log2, -lse2)) : 0.f;
+          ds[c * 32 + u] = pv * (__uint_as_float(dr[u]) - dl) * p.scale;
         }
       }
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sdp_empty[st]);
+      if (!mbar_wait(&ds_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+      uint8_t* sDS = smem + L::offDS + st * L::kSq;
+#pragma unroll
+      for (int t = 0; t < BS / 8; ++t) {
+        uint4 b;
+        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) b2[u] = __floats2bfloat162_rn(ds[t * 8 + 2 * u], ds[t * 8 + 2 * u + 1]);
+        st_sw64_16B(sDS, r, t * 8, b);
+      }
       fence_async_proxy();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(&ds_full[st]);
     }
     if (ok && mbar_wait(acc_done, 0, abort_flag, p.status, kErrTimeoutTmemFull)) {
       tc_fence_after();
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t rr[32];
-        if (c * 32 < p.d_eff) {
-          tmem_ld_32x32(tmem_base + DQ_COL + lane_addr + c * 32, rr);
-          tmem_ld_wait();
-        }
-#pragma unroll
-        for (int u = 0; u < 32; ++u) if (c * 32 + u >= p.d_eff) rr[u] = 0u;
+        tmem_ld_32x32(tmem_base + DQ_COL + lane_addr + c * 32, rr);
+        tmem_ld_wait();
         if (row_ok && J > 0) {
           __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * D + c * 32;
 #pragma unroll
@@ -781,8 +831,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // tensor map over a [T, H*D] bf16 activation with row stride `ld` elements, boxes of {64 channels, 128 tokens}
-int make_act_tmap(CUtensorMap* m, const void* base, int T, int HD, long ld) {
-  return vlmt_make_tmap_2d_bf16(m, base, (uint64_t)HD, (uint64_t)T, (uint64_t)ld * 2, 64, 128);
+int make_act_tmap(CUtensorMap* m, const void* base, int T, int HD, long ld, int box_rows = 128) {
+  return vlmt_make_tmap_2d_bf16(m, base, (uint64_t)HD, (uint64_t)T, (uint64_t)ld * 2, 64, (uint32_t)box_rows);
 }
 
 template <typename K>
@@ -826,12 +876,17 @@ extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, con
     attn_delta_kernel<<<(warps * 32 + 255) / 256, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
                                                                 reinterpret_cast<const __nv_bfloat16*>(o), delta, T, Hq, D);
   }
-  CUtensorMap tq, tk, tv, tdo;
+  // 128-row boxes for the stationary tiles, 64-row boxes for the streamed ones
+  CUtensorMap tq, tk, tv, tdo, tq64, tk64, tv64, tdo64;
   int r;
   if ((r = make_act_tmap(&tq, q, T, Hq * D, (long)Hq * D))) return 1000 + r;
   if ((r = make_act_tmap(&tk, k, T, Hkv * D, (long)Hkv * D))) return 2000 + r;
   if ((r = make_act_tmap(&tv, v, T, Hkv * D, (long)Hkv * D))) return 3000 + r;
   if ((r = make_act_tmap(&tdo, dout, T, Hq * D, (long)Hq * D))) return 4000 + r;
+  if ((r = make_act_tmap(&tq64, q, T, Hq * D, (long)Hq * D, 64))) return 5000 + r;
+  if ((r = make_act_tmap(&tk64, k, T, Hkv * D, (long)Hkv * D, 64))) return 6000 + r;
+  if ((r = make_act_tmap(&tv64, v, T, Hkv * D, (long)Hkv * D, 64))) return 7000 + r;
+  if ((r = make_act_tmap(&tdo64, dout, T, Hq * D, (long)Hq * D, 64))) return 8000 + r;
   BwdParams p;
   p.dQ = reinterpret_cast<__nv_bfloat16*>(dq); p.dK = reinterpret_cast<__nv_bfloat16*>(dk); p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   p.LSE = lse; p.delta = delta; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
@@ -841,13 +896,13 @@ extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, con
   if (D == 128) {
     if ((r = set_smem(attn_bwd_dkdv_kernel<128>, BwdSmem<128>::kTotal))) return r;
     if ((r = set_smem(attn_bwd_dq_kernel<128>, BwdSmem<128>::kTotal))) return r;
-    attn_bwd_dkdv_kernel<128><<<grid_kv, ATT_THREADS, BwdSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
-    attn_bwd_dq_kernel<128><<<grid_q, ATT_THREADS, BwdSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_dkdv_kernel<128><<<grid_kv, ATT_THREADS, BwdSmem<128>::kTotal, st>>>(tq64, tk, tv, tdo64, p);
+    attn_bwd_dq_kernel<128><<<grid_q, ATT_THREADS, BwdSmem<128>::kTotal, st>>>(tq, tk64, tv64, tdo, p);
   } else if (D == 64) {
     if ((r = set_smem(attn_bwd_dkdv_kernel<64>, BwdSmem<64>::kTotal))) return r;
     if ((r = set_smem(attn_bwd_dq_kernel<64>, BwdSmem<64>::kTotal))) return r;
-    attn_bwd_dkdv_kernel<64><<<grid_kv, ATT_THREADS, BwdSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
-    attn_bwd_dq_kernel<64><<<grid_q, ATT_THREADS, BwdSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_dkdv_kernel<64><<<grid_kv, ATT_THREADS, BwdSmem<64>::kTotal, st>>>(tq64, tk, tv, tdo64, p);
+    attn_bwd_dq_kernel<64><<<grid_q, ATT_THREADS, BwdSmem<64>::kTotal, st>>>(tq, tk64, tv64, tdo, p);
   } else {
     return -10;
   }

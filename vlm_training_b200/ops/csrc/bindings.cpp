@@ -58,6 +58,21 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, c
   TORCH_CHECK(r == 0, "vlmt_gemm_bf16 failed with code ", r);
 }
 
+// y-partials of a row-parallel linear pushed to their owners: rows [o*R, (o+1)*R) of a @ b^T go to dst_ptrs[o]
+void gemm_rs_push(const Tensor& a, const Tensor& b, const std::vector<int64_t>& dst_ptrs, int64_t rows_per_rank) {
+  check_bf16(a, "a"); check_bf16(b, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1));
+  c10::cuda::CUDAGuard guard(a.device());
+  void* dst[8];
+  TORCH_CHECK(dst_ptrs.size() <= 8);
+  for (size_t i = 0; i < dst_ptrs.size(); ++i) dst[i] = reinterpret_cast<void*>(dst_ptrs[i]);
+  Tensor st = status_tensor();
+  const int M = a.size(0), N = b.size(0), K = a.size(1);
+  int r = vlmt_gemm_bf16_rs_push(a.data_ptr(), b.data_ptr(), dst, (int)dst_ptrs.size(), (int)rows_per_rank, M, N, K, (int)a.stride(0),
+                                 (int)b.stride(0), N, st.data_ptr<int>(), num_sms(), cur_stream());
+  TORCH_CHECK(r == 0, "vlmt_gemm_bf16_rs_push failed with code ", r);
+}
+
 // ------------------------------------------------------------------ norms
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& res, const Tensor& w, double eps, bool offset) {
   check_bf16(x, "x"); check_contig(x, "x");
@@ -353,6 +368,7 @@ void bind_comm(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("gemm_rs_push", &gemm_rs_push);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("layernorm_fwd", &layernorm_fwd);

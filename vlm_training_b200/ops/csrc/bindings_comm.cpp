@@ -38,7 +38,61 @@ static void peer_sum_rows(const std::vector<int64_t>& partial_ptrs, int64_t row0
   TORCH_CHECK(r == 0, "vlmt_peer_sum_rows failed with code ", r);
 }
 
+Tensor vlmt_status_tensor();
+
+static void fill_ptrs(const std::vector<int64_t>& v, void** out) {
+  TORCH_CHECK(v.size() <= 16);
+  for (size_t i = 0; i < v.size(); ++i) out[i] = reinterpret_cast<void*>(v[i]);
+}
+static void signal_peers(const std::vector<int64_t>& flag_ptrs, int64_t my_rank, int64_t epoch) {
+  void* f[16];
+  fill_ptrs(flag_ptrs, f);
+  int r = vlmt_signal_peers(f, (int)flag_ptrs.size(), (int)my_rank, (int)epoch, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_signal_peers failed with code ", r);
+}
+// flag arrays are addressed as (base pointer, element offset) so one symmetric tensor can hold many flag rows
+static void signal_peers_at(const std::vector<int64_t>& flag_ptrs, int64_t elem_offset, int64_t my_rank, int64_t epoch) {
+  void* f[16];
+  TORCH_CHECK(flag_ptrs.size() <= 16);
+  for (size_t i = 0; i < flag_ptrs.size(); ++i) f[i] = reinterpret_cast<void*>(flag_ptrs[i] + elem_offset * 4);
+  int r = vlmt_signal_peers(f, (int)flag_ptrs.size(), (int)my_rank, (int)epoch, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_signal_peers failed with code ", r);
+}
+static void wait_flags(int64_t my_flags, int64_t elem_offset, int64_t world, int64_t epoch, int64_t skip_rank) {
+  Tensor st = vlmt_status_tensor();
+  int r = vlmt_wait_flags(reinterpret_cast<const int*>(my_flags) + elem_offset, (int)world, (int)epoch, (int)skip_rank, st.data_ptr<int>(),
+                          at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_wait_flags failed with code ", r);
+}
+static void pull_gather(const std::vector<int64_t>& slot_ptrs, Tensor& out, int64_t n_per_rank, int64_t my_flags, int64_t epoch) {
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(out.device());
+  void* s[16];
+  fill_ptrs(slot_ptrs, s);
+  Tensor st = vlmt_status_tensor();
+  int r = vlmt_pull_gather(s, out.data_ptr(), n_per_rank, (int)slot_ptrs.size(), reinterpret_cast<const int*>(my_flags), (int)epoch,
+                           st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_pull_gather failed with code ", r);
+}
+static void pull_reduce(const std::vector<int64_t>& slot_ptrs, Tensor& out, const c10::optional<Tensor>& residual, int64_t n_per_rank,
+                        int64_t my_rank, int64_t my_flags, int64_t epoch) {
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(out.device());
+  void* s[16];
+  fill_ptrs(slot_ptrs, s);
+  Tensor st = vlmt_status_tensor();
+  int r = vlmt_pull_reduce(s, out.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr, n_per_rank, (int)slot_ptrs.size(),
+                           (int)my_rank, reinterpret_cast<const int*>(my_flags), (int)epoch, st.data_ptr<int>(),
+                           at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_pull_reduce failed with code ", r);
+}
+
 void bind_comm(pybind11::module_& m) {
+  m.def("signal_peers", &signal_peers);
+  m.def("signal_peers_at", &signal_peers_at);
+  m.def("wait_flags", &wait_flags);
+  m.def("pull_gather", &pull_gather);
+  m.def("pull_reduce", &pull_reduce);
   m.def("fused_rs_adamw_ag", &fused_rs_adamw_ag);
   m.def("peer_sum_rows", &peer_sum_rows);
 }

@@ -141,9 +141,136 @@ __global__ void peer_sum_rows_kernel(PeerPtrs partials, int world, long row0, lo
     reinterpret_cast<uint4*>(out + row * D)[c] = pack8(acc);
   }
 }
+// ------------------------------------------------------------------------------------ signalled P2P collectives
+// Protocol (per process group, collectives numbered 1, 2, ... in program order, identical on every rank):
+//   every rank copies its contribution into slot (e % n_slots) of its symmetric staging buffer, then `signal`
+//   stores e into flag[my_rank] on EVERY rank (release, system scope); the pull kernel of collective e first
+//   waits (bounded, ~1 s) until all of its own flag[r] >= e, then reads the peers' slots directly over NVLink.
+// A slot is reused n_slots collectives later, by which time every peer has issued (in stream order, after its
+// pull) the signals of the collectives in between, so no extra "done" handshake is needed.
+constexpr unsigned long long kFlagWaitNs = 1000000000ull;
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long gtimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// block-wide: returns false (and records status 100 + rank of the missing peer) when a peer's signal did not arrive in time
+// `skip` (a rank or -1): that rank's flag is not waited for.  A rank must not wait in one kernel for a signal that a
+// SEPARATE launch on the same GPU still has to store (nothing guarantees that the two launches run concurrently);
+// its own readiness is established by stream order instead.
+__device__ bool wait_all_flags(const int* my_flags, int world, int epoch, int* status, int skip = -1) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) {
+    ok = 1;
+    const unsigned long long t0 = gtimer_ns();
+    for (int r = 0; r < world && ok; ++r) {
+      if (r == skip) continue;
+      unsigned spins = 0;
+      while (ld_acquire_sys(my_flags + r) < epoch) {
+        if ((++spins & 0xff) == 0 && gtimer_ns() - t0 > kFlagWaitNs) {
+          atomicCAS(status, 0, 100 + r);
+          ok = 0;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+__global__ void signal_peers_kernel(PeerPtrs flag_ptrs, int world, int my_rank, int epoch) {
+  if ((int)threadIdx.x < world) {
+    __threadfence_system();  // everything this stream wrote before (the staging copy) is visible system-wide first
+    st_release_sys(reinterpret_cast<int*>(flag_ptrs.p[threadIdx.x]) + my_rank, epoch);
+  }
+}
+
+// stand-alone wait: later kernels of the stream start only after every rank stored `epoch` (or the wait timed out)
+__global__ void wait_flags_kernel(const int* my_flags, int world, int epoch, int* status, int skip) {
+  wait_all_flags(my_flags, world, epoch, status, skip);
+}
+
+// all-gather: out[r * n : (r + 1) * n] = slot of rank r   (n elements per rank, multiple of 8)
+__global__ void pull_gather_kernel(PeerPtrs slots, bf16* __restrict__ out, long n, int world, const int* my_flags, int epoch,
+                                   int* status) {
+  if (!wait_all_flags(my_flags, world, epoch, status)) return;
+  const long nvec = n >> 3;
+  const long total = nvec * world;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / nvec);
+    const long v = i - (long)r * nvec;
+    reinterpret_cast<uint4*>(out)[i] = ld_peer_16B(reinterpret_cast<const uint4*>(slots.p[r]) + v);
+  }
+}
+
+// reduce-scatter: out[0:n] = (residual) + sum_r slot_r[me * n : (me + 1) * n]   (own slot included; fp32 accumulation)
+// With `pushed` the producers already stored their blocks into THIS rank's slot (block r from rank r): slots.p[r] then
+// points at local memory and the reads stay on this GPU.
+__global__ void pull_reduce_kernel(PeerPtrs slots, bf16* __restrict__ out, const bf16* __restrict__ residual, long n, int world,
+                                   int my_rank, const int* my_flags, int epoch, int* status) {
+  if (!wait_all_flags(my_flags, world, epoch, status)) return;
+  const long nvec = n >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float acc[8];
+    if (residual) unpack8(reinterpret_cast<const uint4*>(residual)[i], acc);
+    else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    }
+    for (int r = 0; r < world; ++r) {
+      float t[8];
+      unpack8(ld_peer_16B(reinterpret_cast<const uint4*>(slots.p[r]) + (long)my_rank * nvec + i), t);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += t[k];
+    }
+    reinterpret_cast<uint4*>(out)[i] = pack8(acc);
+  }
+}
 }  // namespace
 
 extern "C" {
+int vlmt_signal_peers(void* const* flag_ptrs, int world, int my_rank, int epoch, cudaStream_t st) {
+  if (world > MAX_PEERS) return -1;
+  PeerPtrs f;
+  for (int r = 0; r < world; ++r) f.p[r] = flag_ptrs[r];
+  signal_peers_kernel<<<1, 32, 0, st>>>(f, world, my_rank, epoch);
+  return (int)cudaGetLastError();
+}
+int vlmt_wait_flags(const int* my_flags, int world, int epoch, int skip_rank, int* status, cudaStream_t st) {
+  wait_flags_kernel<<<1, 32, 0, st>>>(my_flags, world, epoch, status, skip_rank);
+  return (int)cudaGetLastError();
+}
+int vlmt_pull_gather(void* const* slot_ptrs, void* out, long n_per_rank, int world, const int* my_flags, int epoch, int* status,
+                     cudaStream_t st) {
+  if (world > MAX_PEERS || (n_per_rank & 7)) return -1;
+  PeerPtrs s;
+  for (int r = 0; r < world; ++r) s.p[r] = slot_ptrs[r];
+  long blocks = ((n_per_rank >> 3) * world + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  pull_gather_kernel<<<(int)blocks, 256, 0, st>>>(s, reinterpret_cast<bf16*>(out), n_per_rank, world, my_flags, epoch, status);
+  return (int)cudaGetLastError();
+}
+int vlmt_pull_reduce(void* const* slot_ptrs, void* out, const void* residual, long n_per_rank, int world, int my_rank,
+                     const int* my_flags, int epoch, int* status, cudaStream_t st) {
+  if (world > MAX_PEERS || (n_per_rank & 7)) return -1;
+  PeerPtrs s;
+  for (int r = 0; r < world; ++r) s.p[r] = slot_ptrs[r];
+  long blocks = ((n_per_rank >> 3) + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  pull_reduce_kernel<<<(int)blocks, 256, 0, st>>>(s, reinterpret_cast<bf16*>(out), reinterpret_cast<const bf16*>(residual), n_per_rank,
+                                                  world, my_rank, my_flags, epoch, status);
+  return (int)cudaGetLastError();
+}
 int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* grad_mc, void* param_mc, int world, long lo, long hi,
                            float* master, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                            float grad_scale, cudaStream_t st) {

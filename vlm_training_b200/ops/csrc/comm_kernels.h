@@ -13,6 +13,18 @@ int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void
                            float grad_scale, cudaStream_t st);
 // out[rows, D] = residual + sum over ranks of partial_r[row0 : row0 + rows, :]
 int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st);
+// Signalled peer-to-peer collectives over symmetric staging slots (protocol: comm_kernels.cu).
+// flag_ptrs[r]: address of rank r's int32 flag array (length >= world); my_flags: this rank's own array.
+int vlmt_signal_peers(void* const* flag_ptrs, int world, int my_rank, int epoch, cudaStream_t st);
+// one-block kernel that returns once my_flags[r] >= epoch for every r < world except skip_rank (-1: none);
+// bounded wait, status word on timeout
+int vlmt_wait_flags(const int* my_flags, int world, int epoch, int skip_rank, int* status, cudaStream_t st);
+// out[r*n:(r+1)*n] = rank r's slot (bf16 elements); waits (bounded) for every rank's signal `epoch`
+int vlmt_pull_gather(void* const* slot_ptrs, void* out, long n_per_rank, int world, const int* my_flags, int epoch, int* status,
+                     cudaStream_t st);
+// out[0:n] = residual + sum_r slot_r[me*n:(me+1)*n]
+int vlmt_pull_reduce(void* const* slot_ptrs, void* out, const void* residual, long n_per_rank, int world, int my_rank,
+                     const int* my_flags, int epoch, int* status, cudaStream_t st);
 #ifdef __cplusplus
 }
 #endif

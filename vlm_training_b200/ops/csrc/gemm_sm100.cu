@@ -49,6 +49,10 @@ struct Params {
   int epilogue;        // GemmEpilogue
   int accumulate;      // D += result
   int tma_store;       // bf16 output goes through smem staging + TMA stores (coalesced, clipped at the edges)
+  // GEMM -> reduce-scatter: output rows are owned by ranks in blocks of rs_rows; the tile for owner o is stored straight
+  // into rs_dst[o] (a buffer in rank o's memory, reached over NVLink), so the transfer overlaps the remaining tiles
+  int rs_world, rs_rows;
+  __nv_bfloat16* rs_dst[8];
   int* status;
 };
 
@@ -263,7 +267,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = (p.accumulate ? dst[i] : 0.f) + v[i];
             }
           } else {
-            __nv_bfloat16* dst = p.D + (size_t)row * p.ldd + col0;
+            __nv_bfloat16* dst;
+            if (p.rs_world > 0) {
+              const int owner = row / p.rs_rows;
+              dst = p.rs_dst[owner] + (size_t)(row - owner * p.rs_rows) * p.ldd + col0;
+            } else {
+              dst = p.D + (size_t)row * p.ldd + col0;
+            }
             if (col0 + 32 <= p.N && (p.ldd & 7) == 0) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
@@ -371,6 +381,10 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
   return (int)cudaGetLastError();
 }
 
+// destination set of the next vlmt_gemm_bf16 call (consumed by vlmt_gemm_bf16_rs_push)
+static thread_local int g_rs_world = 0, g_rs_rows = 0;
+static thread_local void* g_rs_dst[8];
+
 extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K,
                               int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate,
                               int* status, int num_sms, cudaStream_t stream) {
@@ -389,7 +403,12 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
   Params p;
   CUtensorMap td = ta;  // placeholder when the direct-store epilogue is used
   p.tma_store = 0;
-  if (Dacc32 == nullptr && !accumulate && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
+  p.rs_world = 0; p.rs_rows = 0;
+  if (g_rs_world > 0) {
+    p.rs_world = g_rs_world; p.rs_rows = g_rs_rows;
+    for (int i = 0; i < g_rs_world; ++i) p.rs_dst[i] = reinterpret_cast<__nv_bfloat16*>(g_rs_dst[i]);
+  }
+  if (g_rs_world == 0 && Dacc32 == nullptr && !accumulate && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
     r = vlmt_make_tmap_2d_bf16(&td, D, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * 2, 64, 32);
     if (r == 0) p.tma_store = 1;
   }
@@ -408,4 +427,17 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
   if (bn256) DISPATCH(256);
   DISPATCH(128);
 #undef DISPATCH
+}
+
+
+// D rows [o * rows_per_rank, (o + 1) * rows_per_rank) are written to dst[o] (row stride ldd) instead of a local D:
+// the producer half of a tensor-parallel GEMM -> reduce-scatter (the consumer sums the `world` partial blocks it received).
+extern "C" int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const* dst, int world, int rows_per_rank, int M, int N, int K,
+                                      int lda, int ldb, int ldd, int* status, int num_sms, cudaStream_t stream) {
+  if (world < 1 || world > 8 || rows_per_rank % BM != 0 || rows_per_rank * world != M) return -20;
+  g_rs_world = world; g_rs_rows = rows_per_rank;
+  for (int i = 0; i < world; ++i) g_rs_dst[i] = dst[i];
+  int r = vlmt_gemm_bf16(A, B, dst[0], nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, 0, GEMM_EPI_NONE, 0, status, num_sms, stream);
+  g_rs_world = 0;
+  return r;
 }

@@ -16,6 +16,10 @@ extern "C" {
 int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K, int lda,
                    int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate, int* status, int num_sms,
                    cudaStream_t stream);
+// Same GEMM (A K-major, B K-major) whose output rows go to `world` destinations: rows owned by rank o
+// (blocks of rows_per_rank, a multiple of 128) are stored into dst[o], typically peer memory.
+int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const* dst, int world, int rows_per_rank, int M, int N, int K, int lda,
+                           int ldb, int ldd, int* status, int num_sms, cudaStream_t stream);
 // 2-D bf16 tensor map with 128-byte swizzle; `out_map` points at 128 bytes (CUtensorMap).
 int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer);

@@ -521,6 +521,9 @@ def _mma_width(valid: int, padded: int) -> int:
     """Channels the attention MMAs cover.  Skipping zero padding (e.g. 80 of 128 for head_dim 72) was measured
     SLOWER on B200 than full-width MMAs (N = 80 is an inefficient instruction shape), so only padding of at least
     half the tile is skipped (N = 64)."""
+    forced = os.environ.get("VLMT_ATTN_MMA_WIDTH")
+    if forced:
+        return max(min(int(forced), padded), (valid + 15) // 16 * 16)
     return 64 if valid <= 64 < padded else padded
 
 

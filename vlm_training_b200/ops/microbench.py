@@ -1,0 +1,212 @@
+"""Per-kernel micro-benchmarks (CUDA-event timing, L2 flushed between iterations) and roofline fractions.
+
+    python -m vlm_training_b200.ops.microbench gemm --m 8192 --n 6144 --k 4096 [--layout fwd|dgrad|wgrad]
+    python -m vlm_training_b200.ops.microbench attention --tokens 8192 --docs 1 [--backward]
+    python -m vlm_training_b200.ops.microbench rmsnorm | swiglu | qkv_rope | ce | adamw
+    python -m vlm_training_b200.ops.microbench all            # the table used in the roofline report
+
+Each line is JSON: algorithmic FLOPs / bytes, median milliseconds, achieved rate, and the fraction of the
+measured peak (``MEASURED_PEAKS.json`` in the working directory when present: burst cuBLAS bf16 rate and
+STREAM-style copy bandwidth; otherwise 1.59 PFLOP/s and 6.65 TB/s).  ``--iters 1 --warmup 0 --no-flush`` gives
+a run small enough to put under a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+
+def peaks() -> dict:
+    for path in (os.environ.get("VLMT_MEASURED_PEAKS", ""), "MEASURED_PEAKS.json"):
+        if path and os.path.exists(path):
+            with open(path) as fh:
+                d = json.load(fh)
+            return {"tflops": float(d["bf16_tflops"]), "gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "gbs": 6650.0, "source": "fallback"}
+
+
+class Timer:
+    def __init__(self, iters: int, warmup: int, flush: bool):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+
+    def __call__(self, fn) -> float:
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(self.iters):
+            if self.flush is not None:
+                self.flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+
+def _report(name, shape, ms, flops=None, nbytes=None):
+    pk = peaks()
+    out = {"kernel": name, "shape": shape, "ms": round(ms, 4)}
+    if flops is not None:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out["frac_of_" + pk["source"] + "_gemm_peak"] = round(flops / ms / 1e9 / pk["tflops"], 3)
+    if nbytes is not None:
+        out["gbs"] = round(nbytes / ms / 1e6, 1)
+        out["frac_of_" + pk["source"] + "_copy_bw"] = round(nbytes / ms / 1e6 / pk["gbs"], 3)
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def _r(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+def bench_gemm(t: Timer, m, n, k, layout="fwd"):
+    from . import cuda as cu
+
+    if layout == "fwd":
+        a, b = _r(m, k), _r(n, k)
+        fn = lambda: cu._gemm(a, b)
+    elif layout == "dgrad":  # dX[m,n] = dY[m,k] W[k,n]
+        a, b = _r(m, k), _r(k, n)
+        fn = lambda: cu._gemm(a, b, b_mn=True)
+    else:  # wgrad: dW[m,n] = dY[k,m]^T X[k,n]
+        a, b = _r(k, m), _r(k, n)
+        fn = lambda: cu._gemm(a, b, a_mn=True, b_mn=True)
+    return _report(f"gemm_{layout}", [m, n, k], t(fn), flops=2.0 * m * n * k)
+
+
+def bench_attention(t: Timer, tokens, docs, hq=32, hkv=8, d=128, causal=True, backward=False):
+    from .. import ops
+
+    lens = [tokens // docs] * docs
+    cu_seq = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    q, k, v = (_r(tokens, h, d).requires_grad_() for h in (hq, hkv, hkv))
+    g = _r(tokens, hq, d)
+    fl = sum(4.0 * L * L * d * hq * (0.5 if causal else 1.0) for L in lens)
+    if not backward:
+        with torch.no_grad():
+            ms = t(lambda: ops.attention_varlen(q, k, v, cu_seq, max(lens), causal, None))
+        return _report("attention_fwd", [tokens, docs, hq, hkv, d, int(causal)], ms, flops=fl)
+
+    def fb():
+        ops.attention_varlen(q, k, v, cu_seq, max(lens), causal, None).backward(g)
+    return _report("attention_fwd_bwd", [tokens, docs, hq, hkv, d, int(causal)], t(fb), flops=3.5 * fl)
+
+
+def bench_rmsnorm(t: Timer, rows=8192, dim=4096):
+    from . import cuda as cu
+
+    x, w = _r(rows, dim), _r(dim)
+    ms = t(lambda: cu._C.rmsnorm_fwd(x, None, w, 1e-6, False))
+    _report("rmsnorm_fwd", [rows, dim], ms, nbytes=2.0 * rows * dim * 2)
+    y, rstd = cu._C.rmsnorm_fwd(x, None, w, 1e-6, False)
+    ms = t(lambda: cu._C.rmsnorm_bwd(y, x, w, rstd, None, False))
+    return _report("rmsnorm_bwd", [rows, dim], ms, nbytes=3.0 * rows * dim * 2)
+
+
+def bench_swiglu(t: Timer, rows=8192, inter=12288):
+    from . import cuda as cu
+
+    gu = _r(rows, 2 * inter)
+    ms = t(lambda: cu._C.swiglu_fwd(gu))
+    _report("swiglu_fwd", [rows, inter], ms, nbytes=3.0 * rows * inter * 2)
+    d = _r(rows, inter)
+    ms = t(lambda: cu._C.swiglu_bwd(d, gu))
+    return _report("swiglu_bwd", [rows, inter], ms, nbytes=5.0 * rows * inter * 2)
+
+
+def bench_qkv_rope(t: Timer, tokens=8192, hq=32, hkv=8, d=128):
+    from . import cuda as cu
+
+    qkv = _r(tokens, (hq + 2 * hkv) * d)
+    w = _r(d)
+    ang = torch.rand(tokens, d // 2, device="cuda")
+    emb = torch.cat((ang, ang), -1)
+    cos, sin = emb.cos().contiguous(), emb.sin().contiguous()
+    ms = t(lambda: cu._C.qkv_norm_rope_fwd(qkv, hq, hkv, d, w, w, cos, sin, 1e-6, False, False))
+    return _report("qkv_norm_rope_fwd", [tokens, hq, hkv, d], ms, nbytes=2.0 * qkv.numel() * 2)
+
+
+def bench_ce(t: Timer, tokens=4096, hidden=4096, vocab=151936):
+    from . import cuda as cu
+
+    logits = _r(tokens, vocab)
+    tgt = torch.randint(0, vocab, (tokens,), device="cuda")
+    ms = t(lambda: cu._C.ce_fwd_bwd_(logits, tgt, 1.0, -100))
+    return _report("ce_softmax_grad", [tokens, vocab], ms, nbytes=2.0 * tokens * vocab * 2)
+
+
+def bench_adamw(t: Timer, n=1 << 28):
+    from . import cuda as cu
+
+    g = torch.randn(n, device="cuda").bfloat16()
+    p = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    master, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    ms = t(lambda: cu._C.adamw_(g, master, m, v, p, 1e-4, 0.9, 0.999, 1e-8, 0.01, 1, 1.0))
+    return _report("adamw_fp32_state", [n], ms, nbytes=n * (2 + 12 + 12 + 2.0))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "all"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--docs", type=int, default=1)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--non-causal", action="store_true")
+    ap.add_argument("--backward", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args(argv)
+    t = Timer(a.iters, a.warmup, not a.no_flush)
+    if a.what == "gemm":
+        bench_gemm(t, a.m, a.n, a.k, a.layout)
+    elif a.what == "attention":
+        bench_attention(t, a.tokens, a.docs, d=a.head_dim, causal=not a.non_causal, backward=a.backward)
+    elif a.what == "rmsnorm":
+        bench_rmsnorm(t)
+    elif a.what == "swiglu":
+        bench_swiglu(t)
+    elif a.what == "qkv_rope":
+        bench_qkv_rope(t)
+    elif a.what == "ce":
+        bench_ce(t)
+    elif a.what == "adamw":
+        bench_adamw(t)
+    else:
+        for layout in ("fwd", "dgrad", "wgrad"):
+            bench_gemm(t, 8192, 6144, 4096, layout)
+            bench_gemm(t, 8192, 24576, 4096, layout)
+            bench_gemm(t, 8192, 4096, 12288, layout)
+        bench_gemm(t, 28672, 3456, 1152, "fwd")
+        bench_gemm(t, 28672, 4304, 1152, "fwd")
+        bench_gemm(t, 4096, 151936, 4096, "fwd")
+        for docs in (1, 4, 16):
+            bench_attention(t, 8192, docs)
+            bench_attention(t, 8192, docs, backward=True)
+        bench_attention(t, 16384, 8, hq=16, hkv=16, d=128, causal=False)
+        bench_rmsnorm(t)
+        bench_swiglu(t)
+        bench_qkv_rope(t)
+        bench_ce(t)
+        bench_adamw(t)
+    from . import cuda as cu
+
+    cu.check_status()
+
+
+if __name__ == "__main__":
+    main()

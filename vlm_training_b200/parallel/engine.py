@@ -200,6 +200,12 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         self.comm_stream = torch.cuda.Stream(device=device) if self.is_cuda else None
         self._hooks = []
         self._sync_grads = True
+        self._fused = None
+        if symmetric and max_grad_norm is None:
+            from . import fused
+
+            if fused.usable(self):
+                self._fused = fused.FusedStepState(self)
         if self.is_cuda and overlap and dist.is_initialized():
             self._install_hooks()
         if self.is_cuda:
@@ -234,7 +240,12 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                 return
             b.pending -= 1
             if b.pending == 0 and not b.reduced:
-                self._reduce_bucket(d, b)
+                if self._fused is not None:
+                    from . import fused
+
+                    fused.process_bucket(self, d, d.buckets.index(b))
+                else:
+                    self._reduce_bucket(d, b)
         return hook
 
     def _install_forward_waits(self):
@@ -306,12 +317,13 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self, closure=None):
-        self.step_count += 1
-        if self.fused_comm and self.is_cuda and dist.is_initialized() and self.max_grad_norm is None:
-            from .fused import fused_reduce_adamw_gather
+        if self._fused is not None:
+            from . import fused
 
-            if fused_reduce_adamw_gather(self):
-                return
+            fused.finish_step(self)  # buckets not reached by the hooks + the all-ranks-done round
+            self.step_count += 1
+            return
+        self.step_count += 1
         self.finish_grad_sync()
         clip = 1.0
         if self.max_grad_norm is not None:

@@ -1,16 +1,23 @@
-"""One-kernel NVLink paths used by the sharded optimizer engine and tensor parallelism.
+"""One-kernel NVLink path of the sharded optimizer engine.
 
-``fused_reduce_adamw_gather`` replaces, per bucket, the sequence
-``reduce_scatter(grads) → AdamW(shard) → all_gather(params)`` (three passes over HBM and
-two NCCL kernels) by a single kernel that pulls the gradient shard from every peer (or one
-in-switch ``multimem.ld_reduce``), updates the fp32 state and pushes the bf16 parameters to
-every peer (``vlm_training_b200/ops/csrc/comm_kernels.cu``).  It needs the engine's flat
-buffers to live in symmetric memory (``fused_comm=True``).
+Per bucket, ``reduce_scatter(grads) → AdamW(shard) → all_gather(params)`` (three passes over HBM and two NCCL
+kernels) becomes a single kernel that pulls the gradient shard from every peer (or one in-switch
+``multimem.ld_reduce``), updates the fp32 state and pushes the bf16 parameters to every peer
+(``ops/csrc/comm_kernels.cu``).  The engine's flat buffers live in symmetric memory for this.
 
-Ordering: a rank may start a bucket only after EVERY rank has finished writing that bucket's
-gradients, and nobody may read parameters until every rank's pushes have landed.  Both
-conditions are established with a one-element NCCL all-reduce on the communication stream —
-no spin-waits in our own kernels.
+The kernel for a bucket is launched from the autograd hook of the bucket's last gradient, so it overlaps the rest
+of backward.  Ordering is by flags in symmetric memory, one row of ``world`` int32 per bucket, written with the
+optimizer step number:
+
+* when a rank has produced all gradients of bucket ``b`` it stores the step number into ``flag[b][rank]`` on every
+  rank (``signal`` — on its own stream, so a signal never queues behind a wait);
+* a rank's fused kernel for ``b`` is preceded by a one-block wait kernel that returns once ``flag[b][r] >= step`` for
+  all OTHER ranks ``r`` (its own gradients are ordered by the stream; a kernel never waits for a separate launch on its
+  own GPU): then every peer's gradients of ``b`` are final AND every peer is done reading the old parameters of ``b``;
+* after its last bucket a rank signals row ``DONE``; before the next forward (and before gradients are cleared) every
+  rank waits for all ``DONE`` signals: all pushes have landed and nobody still reads this step's gradients.
+
+Every wait is bounded (about a second) and reports through the status word instead of hanging.
 """
 from __future__ import annotations
 
@@ -20,61 +27,118 @@ import torch.distributed as dist
 from . import symm
 
 
-def fused_reduce_adamw_gather(engine) -> bool:
-    """Run the optimizer step through the fused kernel.  Returns False when the engine's buffers
-    are not symmetric (the caller then takes the NCCL path)."""
+class FusedStepState:
+    """Flags, streams and per-step bookkeeping of one engine."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        dev = engine.device
+        self.signal_stream = torch.cuda.Stream(device=dev)
+        self.domains = []
+        for d in engine.domains:
+            info = {"domain": d, "flags": None}
+            if d.size > 1:
+                rows = len(d.buckets) + 1  # + DONE row
+                d_flags = symm.symmetric_zeros(rows * d.size, torch.int32, dev, d.group)
+                info.update(flags=d_flags, flag_ptrs=symm.peer_ptrs(d_flags), done_row=len(d.buckets),
+                            g_ptrs=symm.peer_ptrs(d.flat_grad), p_ptrs=symm.peer_ptrs(d.flat_param),
+                            g_mc=symm.multicast_ptr(d.flat_grad), p_mc=symm.multicast_ptr(d.flat_param))
+            self.domains.append(info)
+        torch.cuda.synchronize(dev)
+        for d in engine.domains:
+            if d.size > 1:
+                dist.barrier(group=d.group)
+        self.step = 0          # number of the optimizer step whose buckets are being processed
+        self.processed = set()
+
+    def info_of(self, d):
+        for info in self.domains:
+            if info["domain"] is d:
+                return info
+        raise KeyError
+
+
+def usable(engine) -> bool:
+    return all(d.size == 1 or symm.handle_of(d.flat_grad) is not None for d in engine.domains)
+
+
+def begin_step(engine):
+    st: FusedStepState = engine._fused
+    if st.step != engine.step_count + 1:
+        st.step = engine.step_count + 1
+        st.processed = set()
+
+
+def process_bucket(engine, d, bi: int):
+    """Signal 'my gradients of bucket bi are final', then (after every rank's signal) run the fused kernel on it."""
     from ..ops import cuda as cu
 
-    domains = [d for d in engine.domains]
-    if any(d.size > 1 and symm.handle_of(d.flat_grad) is None for d in domains):
-        return False
+    st: FusedStepState = engine._fused
+    begin_step(engine)
+    key = (id(d), bi)
+    if key in st.processed:
+        return
+    st.processed.add(key)
+    info = st.info_of(d)
+    b = d.buckets[bi]
+    b.reduced = True
+    step = st.step
     b1, b2 = engine.betas
-    step = engine.step_count
     bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+    if engine._identical and d.name == "tp_replicated":
+        for p in b.params:
+            if getattr(p, "_tp_grad", "partial") == "identical":
+                p.grad.mul_(engine._identical_scale)
     cur = torch.cuda.current_stream()
-    comm = engine.comm_stream
-    token = engine.__dict__.setdefault("_sync_token", torch.zeros(1, device=engine.device))
-    # every rank's backward (all gradient writes) must be complete before anyone pulls
     ev = torch.cuda.Event()
     ev.record(cur)
-    with torch.cuda.stream(comm):
-        comm.wait_event(ev)
-        for d in domains:
+    world = d.size
+    if world > 1:
+        with torch.cuda.stream(st.signal_stream):
+            st.signal_stream.wait_event(ev)
+            cu._C.signal_peers_at(info["flag_ptrs"], bi * world, d.rank, step)
+    esz = d.flat_grad.element_size()
+    with torch.cuda.stream(engine.comm_stream):
+        engine.comm_stream.wait_event(ev)
+        if world > 1:
+            cu._C.wait_flags(info["flags"].data_ptr(), bi * world, world, step, d.rank)  # own readiness: stream order
+            g_ptrs, p_ptrs, g_mc, p_mc = info["g_ptrs"], info["p_ptrs"], info["g_mc"], info["p_mc"]
+        else:
+            g_ptrs, p_ptrs, g_mc, p_mc = [d.flat_grad.data_ptr()], [d.flat_param.data_ptr()], 0, 0
+        lo, hi = d.shard_range(b)
+        for seg in b.segments:
+            s, e = max(seg.start, lo), min(seg.end, hi)
+            if e <= s:
+                continue
+            # parameters start on 8-element boundaries; a segment's tail may not end on one: the padding behind it
+            # holds zero gradients, so rounding the end up is harmless
+            e = min(hi, (e + 7) // 8 * 8)
+            pg = engine.param_groups[seg.group]
+            cu._C.fused_rs_adamw_ag(
+                [p + b.start * esz for p in g_ptrs], [p + b.start * esz for p in p_ptrs],
+                (g_mc + b.start * esz) if g_mc else 0, (p_mc + b.start * esz) if p_mc else 0,
+                world, s - b.start, e - b.start, d.master[bi], d.exp_avg[bi], d.exp_avg_sq[bi], s - lo,
+                pg["lr"], b1, b2, engine.eps, pg["weight_decay"], bc1, bc2, d.grad_scale)
+            cu._tick()
+
+
+def finish_step(engine):
+    """Process whatever the hooks did not reach, then the DONE round; returns with the current stream ordered after it."""
+    from ..ops import cuda as cu
+
+    st: FusedStepState = engine._fused
+    begin_step(engine)
+    for d in engine.domains:
+        for bi in range(len(d.buckets)):
+            process_bucket(engine, d, bi)
+    step = st.step
+    with torch.cuda.stream(engine.comm_stream):
+        for info in st.domains:
+            d = info["domain"]
             if d.size > 1:
-                dist.all_reduce(token, group=d.group)
-        for d in domains:
-            world = d.size
-            if world > 1:
-                g_ptrs, p_ptrs = symm.peer_ptrs(d.flat_grad), symm.peer_ptrs(d.flat_param)
-                g_mc, p_mc = symm.multicast_ptr(d.flat_grad), symm.multicast_ptr(d.flat_param)
-            else:
-                g_ptrs, p_ptrs, g_mc, p_mc = [d.flat_grad.data_ptr()], [d.flat_param.data_ptr()], 0, 0
-            esz = d.flat_grad.element_size()
-            for bi, b in enumerate(d.buckets):
-                if engine._identical and d.name == "tp_replicated":
-                    for p in b.params:
-                        if getattr(p, "_tp_grad", "partial") == "identical":
-                            p.grad.mul_(engine._identical_scale)
-                lo, hi = d.shard_range(b)
-                for seg in b.segments:
-                    s, e = max(seg.start, lo), min(seg.end, hi)
-                    if e <= s:
-                        continue
-                    # parameters start on 8-element boundaries; a segment's tail may not end on one: the padding
-                    # behind it holds zero gradients, so rounding the end up is harmless
-                    e = min(hi, (e + 7) // 8 * 8)
-                    pg = engine.param_groups[seg.group]
-                    cu._C.fused_rs_adamw_ag(
-                        [p + b.start * esz for p in g_ptrs], [p + b.start * esz for p in p_ptrs],
-                        (g_mc + b.start * esz) if g_mc else 0, (p_mc + b.start * esz) if p_mc else 0,
-                        world, s - b.start, e - b.start, d.master[bi], d.exp_avg[bi], d.exp_avg_sq[bi], s - lo,
-                        pg["lr"], b1, b2, engine.eps, pg["weight_decay"], bc1, bc2, d.grad_scale)
-                    cu._tick()
-                b.reduced = True
-        for d in domains:
-            if d.size > 1:
-                dist.all_reduce(token, group=d.group)  # all pushes have landed everywhere
+                row = info["done_row"] * d.size
+                cu._C.signal_peers_at(info["flag_ptrs"], row, d.rank, step)   # after all my fused kernels (same stream)
+                cu._C.wait_flags(info["flags"].data_ptr(), row, d.size, step, d.rank)
         done = torch.cuda.Event()
-        done.record(comm)
-    cur.wait_event(done)
-    return True
+        done.record(engine.comm_stream)
+    torch.cuda.current_stream().wait_event(done)

@@ -12,6 +12,7 @@ import torch.distributed as dist
 def init_distributed(backend: str = "auto", device: str = "auto", timeout_s: int = 1800):
     """Initialise torch.distributed from the torchrun environment (RANK / WORLD_SIZE /
     LOCAL_RANK / MASTER_*); a no-op for single-process runs.  Returns (rank, world, device)."""
+    timeout_s = int(os.environ.get("VLMT_PG_TIMEOUT_S", timeout_s))  # short in tests: a lost rank ends the job quickly
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -1,0 +1,108 @@
+"""Tensor-parallel collectives as our own NVLink kernels (no NCCL on the layer path).
+
+For the 32-64 MB messages of sequence-parallel TP on two ranks NCCL picks its low-latency ring protocol and
+moves ~120 GB/s; a plain peer-to-peer pull over NVSwitch moves the same bytes several times faster.  Each
+collective is: copy the contribution into a slot of this rank's symmetric staging buffer → ``signal`` (store the
+collective's sequence number into every peer's flag array, release/system scope) → one pull kernel that waits
+(bounded) for all signals and then reads the peers' slots directly (``ops/csrc/comm_kernels.cu``).  The
+reduce-scatter kernel accumulates in fp32 and can add a residual in the same pass.
+
+A waiting kernel gives up after about a second and writes a status word (read by ``ops.cuda.check_status``)
+instead of spinning forever, so a rank that left shows up as a Python exception on the survivors.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import symm
+
+
+class P2PComm:
+    N_SLOTS = 4
+
+    def __init__(self, group, device, slot_elems: int = 1 << 25):
+        self.group, self.device = group, device
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.epoch = 0
+        self.slot_elems = 0
+        self.flags = symm.symmetric_zeros(64, torch.int32, device, group)
+        self.flag_ptrs = symm.peer_ptrs(self.flags)
+        self._alloc(slot_elems)
+
+    def _alloc(self, slot_elems: int):
+        slot_elems = (slot_elems + 1023) // 1024 * 1024
+        self.staging = symm.symmetric_zeros(self.N_SLOTS * slot_elems, torch.bfloat16, self.device, self.group)
+        self.slot_elems = slot_elems
+        self.staging_ptrs = symm.peer_ptrs(self.staging)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # every rank's buffers are zeroed and mapped before the first signal
+
+    def _slot(self, n: int):
+        if n > self.slot_elems:
+            self._alloc(n)
+        self.epoch += 1
+        s = self.epoch % self.N_SLOTS
+        off = s * self.slot_elems
+        return self.epoch, self.staging[off:off + n], [p + off * 2 for p in self.staging_ptrs]
+
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        from ..ops import cuda as cu
+
+        x = x.contiguous()
+        n = x.numel()
+        e, slot, ptrs = self._slot(n)
+        slot.copy_(x.view(-1))
+        cu._C.signal_peers(self.flag_ptrs, self.rank, e)
+        out = x.new_empty((x.shape[0] * self.world,) + tuple(x.shape[1:]))
+        cu._C.pull_gather(ptrs, out, n, self.flags.data_ptr(), e)
+        cu._tick(2)
+        return out
+
+    def reduce_scatter_rows(self, y: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        from ..ops import cuda as cu
+
+        y = y.contiguous()
+        n = y.numel()
+        assert y.shape[0] % self.world == 0
+        e, slot, ptrs = self._slot(n)
+        slot.copy_(y.view(-1))
+        cu._C.signal_peers(self.flag_ptrs, self.rank, e)
+        out = y.new_empty((y.shape[0] // self.world,) + tuple(y.shape[1:]))
+        cu._C.pull_reduce(ptrs, out, residual.contiguous() if residual is not None else None, n // self.world, self.rank,
+                          self.flags.data_ptr(), e)
+        cu._tick(2)
+        return out
+
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``reduce_scatter_rows(x @ w.T)`` with the collective fused into the GEMM: the tcgen05 GEMM's epilogue stores each
+        output tile directly into the staging slot of the rank that owns those rows (peer stores over NVLink, overlapping
+        the remaining tiles); after the signal round every rank sums the ``world`` partial blocks it received — local
+        reads only — and adds ``residual`` in the same pass."""
+        from ..ops import cuda as cu
+
+        M, N = x.shape[0], w.shape[0]
+        rows = M // self.world
+        n = M * N
+        e, _slot, ptrs = self._slot(n)
+        block = rows * N * 2  # bytes of one [rows, N] partial block
+        dst = [p + self.rank * block for p in ptrs]  # on rank o: block `my rank` of its slot
+        cu._C.gemm_rs_push(x, w, dst, rows)
+        cu._C.signal_peers(self.flag_ptrs, self.rank, e)
+        out = x.new_empty((rows, N))
+        mine = ptrs[self.rank]
+        local = [mine + (r - self.rank) * block for r in range(self.world)]  # kernel adds rank * block: block r of my slot
+        cu._C.pull_reduce(local, out, residual.contiguous() if residual is not None else None, rows * N, self.rank,
+                          self.flags.data_ptr(), e)
+        cu._tick(3)
+        return out
+
+    def gemm_rs_usable(self, x, w) -> bool:
+        return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and x.shape[0] % (128 * self.world) == 0 and w.shape[0] % 8 == 0 and x.shape[1] % 8 == 0)
+
+
+def usable(x: torch.Tensor, ctx) -> bool:
+    return (getattr(ctx, "p2p", None) is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % (8 * ctx.size) == 0)

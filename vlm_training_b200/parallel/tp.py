@@ -128,6 +128,10 @@ def apply_tp(model, mesh, sequence_parallel: bool = False, backend: str = "dist"
     if model.config.text.tie_word_embeddings:
         raise ValueError("tensor parallelism with tied word embeddings is not supported")  # as the reference refuses
     ctx = TPContext(group=mesh.tp_group, size=mesh.tp, rank=mesh.tp_rank, sequence_parallel=sequence_parallel, backend=backend)
+    if backend == "p2p":
+        from .p2p import P2PComm
+
+        ctx.p2p = P2PComm(mesh.tp_group, mesh.device)
     dec = model.decoder
     for layer in dec.layers:
         if hasattr(layer, "self_attn"):

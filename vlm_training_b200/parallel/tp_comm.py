@@ -28,6 +28,7 @@ class TPContext:
     rank: int = 0
     sequence_parallel: bool = False
     backend: str = "dist"
+    p2p: object = None  # parallel.p2p.P2PComm when the layer collectives run as our own NVLink kernels
 
     @property
     def enabled(self) -> bool:
@@ -35,6 +36,8 @@ class TPContext:
 
 
 def _all_gather_rows(x, ctx: TPContext):
+    if ctx.p2p is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+        return ctx.p2p.all_gather_rows(x)
     x = x.contiguous()
     out = x.new_empty((x.shape[0] * ctx.size,) + tuple(x.shape[1:]))
     dist.all_gather_into_tensor(out, x, group=ctx.group)
@@ -42,6 +45,9 @@ def _all_gather_rows(x, ctx: TPContext):
 
 
 def _reduce_scatter_rows(x, ctx: TPContext):
+    if ctx.p2p is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % (8 * ctx.size) == 0 \
+            and x.shape[0] % ctx.size == 0:
+        return ctx.p2p.reduce_scatter_rows(x)
     x = x.contiguous()
     assert x.shape[0] % ctx.size == 0, "token count must divide by the tensor-parallel size"
     out = x.new_empty((x.shape[0] // ctx.size,) + tuple(x.shape[1:]))
@@ -157,8 +163,7 @@ class _GatherUneven(torch.autograd.Function):
         mx = max(sizes)
         pad = x.new_zeros((mx,) + tuple(x.shape[1:]))
         pad[: x.shape[0]].copy_(x)
-        out = x.new_empty((mx * ctx.size,) + tuple(x.shape[1:]))
-        dist.all_gather_into_tensor(out, pad, group=ctx.group)
+        out = _all_gather_rows(pad, ctx)
         parts = [out[r * mx: r * mx + sizes[r]] for r in range(ctx.size)]
         return torch.cat(parts, 0)
 
@@ -183,3 +188,34 @@ def gather_uneven(x, sizes, ctx: TPContext, grad_identical: bool = False):
     """``grad_identical``: the consumers of the gathered tensor are replicated over the group, so each rank's
     gradient is already the full one (no sum in backward)."""
     return _GatherUneven.apply(x, list(sizes), ctx, grad_identical) if ctx.enabled else x
+
+
+class _RowLinearReduceScatter(torch.autograd.Function):
+    """Row-parallel linear whose reduce-scatter is fused into the GEMM epilogue (sequence-parallel output
+    ``[T/tp, out]``).  Backward: all-gather ``dy`` (peer pull), then the usual dgrad / wgrad GEMMs."""
+
+    @staticmethod
+    def forward(fctx, x, w, ctx):
+        fctx.tp = ctx
+        fctx.save_for_backward(x, w)
+        return ctx.p2p.gemm_reduce_scatter(x, w)
+
+    @staticmethod
+    def backward(fctx, dy):
+        from ..ops import cuda as cu
+
+        x, w = fctx.saved_tensors
+        dy_full = _all_gather_rows(dy.contiguous(), fctx.tp)
+        dx = cu._gemm(dy_full, w, b_mn=True) if fctx.needs_input_grad[0] else None
+        dw = cu._gemm(dy_full, x, a_mn=True, b_mn=True) if fctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+def row_linear(x, weight, ctx: TPContext):
+    """``row_output(linear(x, weight))``; on the peer-to-peer backend with sequence parallelism the collective runs
+    inside the GEMM kernel's epilogue."""
+    if ctx.enabled and ctx.sequence_parallel and ctx.p2p is not None and ctx.p2p.gemm_rs_usable(x, weight):
+        return _RowLinearReduceScatter.apply(x, weight, ctx)
+    from .. import ops
+
+    return row_output(ops.linear(x, weight, None), ctx)

@@ -89,7 +89,8 @@ class Trainer:
         model.ce_chunk_size = t.ce_chunk_size
         set_model(model, cfg.model.train_llm, cfg.model.train_mlp, cfg.model.train_vit)
         # ---------------- parallelism (order matters: TP → AC → data parallel)
-        self.tp_ctx = apply_tp(model, self.mesh, sequence_parallel=t.sequence_parallel)
+        tp_backend = "p2p" if (t.fused_comm and self.device.type == "cuda" and t.tp_size > 1) else "dist"
+        self.tp_ctx = apply_tp(model, self.mesh, sequence_parallel=t.sequence_parallel, backend=tp_backend)
         apply_ac(model, t.ac_mode)
         self.model = model
         self.optimizer = self.create_optimizer()
