@@ -28,6 +28,8 @@ CASES = [
     ([513, 127, 129], 4, 1, 64, True),
     ([196, 196, 1024], 4, 4, 72, False),   # ViT: head_dim 72 is zero-padded to the kernel tile
     ([700], 8, 2, 128, False),
+    ([1500, 260, 40], 2, 1, 128, True),
+    ([900, 130], 2, 2, 64, False),
 ]
 
 
@@ -67,3 +69,31 @@ def test_attention_is_repeatable():
         outs.append((o.detach().clone(), q.grad.clone(), k.grad.clone(), v.grad.clone()))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_growing_scores(causal):
+    """Scores that keep growing along the keys make the running row max jump by far more than the lazy-rescale
+    threshold several times per row, so the in-TMEM rescale of the output accumulator is exercised."""
+    from vlm_training_b200.ops import cuda as cu
+
+    torch.manual_seed(1)
+    lens, Hq, Hkv, D = [1100, 300], 2, 1, 128
+    T = sum(lens)
+    cu_seq = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ramp = torch.linspace(0.2, 6.0, T, device=DEV)[:, None, None]
+    base = torch.randn(1, 1, D, device=DEV)
+    q = (base + 0.3 * torch.randn(T, Hq, D, device=DEV)).bfloat16().requires_grad_()
+    k = (ramp * (base + 0.3 * torch.randn(T, Hkv, D, device=DEV))).bfloat16().requires_grad_()
+    v = torch.randn(T, Hkv, D, device=DEV).bfloat16().requires_grad_()
+    o = ops.attention_varlen(q, k, v, cu_seq, max(lens), causal, None)
+    g = torch.randn(T, Hq, D, device=DEV).bfloat16()
+    o.backward(g)
+    cu.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    o_r = ref.attention_varlen(qr, kr, vr, cu_seq, max(lens), causal, None)
+    o_r.backward(g.float())
+    _close(o, o_r, 0.03, 3e-2, "out")
+    _close(q.grad, qr.grad, 0.08, 5e-2, "dq")
+    _close(k.grad, kr.grad, 0.08, 5e-2, "dk")
+    _close(v.grad, vr.grad, 0.08, 5e-2, "dv")

@@ -1,18 +1,23 @@
 // Varlen (packed-row) flash attention for sm_100a on tcgen05 tensor cores with TMEM accumulators.
 //
-// Forward: one CTA per (128-query tile of one document, query head).
-//   warp 0      TMA: Q once, then K_j / V_j tiles through 2-stage rings
-//   warp 1      MMA issuer: S_j = Q K_j^T into one of two TMEM S buffers (issued one tile ahead),
-//               PV_j = P_j V_j into one of two TMEM PV buffers
-//   warps 2..5  softmax: one query row per thread (tcgen05.ld gives a thread its whole row, so
-//               row max / row sum need no shuffles), P_j written as bf16 into swizzled smem for
-//               the second MMA, running output kept in registers and rescaled as PV tiles arrive
-// Backward: `attn_bwd_dkdv` (one CTA per key tile and kv head, loops over the query tiles and the
-// query heads of the GQA group) and `attn_bwd_dq` (one CTA per query tile and head) recompute
-// S and dP = dO V^T on the tensor cores; no atomics, results are bit-reproducible.
+// All three kernels use ten warps: warp 0 issues TMA loads, one thread of warp 1 issues every MMA, warps 2..9 do
+// the CUDA-core work between the MMAs (two warps per scheduler, so one warp's latencies hide behind the other).
+// Probabilities and score gradients go back to the tensor core through tensor memory (they overwrite the fp32
+// scores they were computed from and are read as the A operand of the next MMA), never through shared memory.
 //
-// Documents are [cu_seqlens[i], cu_seqlens[i+1]); tiles never mix documents: keys past the end of
-// the document (and, with `causal`, keys after the query) are masked to -inf before the softmax.
+// Forward: one CTA per (256 queries of one document = two 128-row tiles, query head).  Warps 2..5 own tile 0 and
+//   warps 6..9 tile 1, one query row per thread (tcgen05.ld gives a thread its whole row: row max and row sum need
+//   no shuffles).  The MMA thread alternates between the tiles - P0.V, S0', P1.V, S1' - so the tensor core works
+//   on one tile while the softmax of the other runs.  O accumulates in TMEM; it is rescaled only when a row's
+//   running max grows by more than 2^8 (the stale max is used meanwhile, which only changes the common scale
+//   of P and l).
+// Backward: `attn_bwd_dkdv` (one CTA per 128-key tile and kv head; loops over 64-query tiles and the query heads of
+//   the GQA group) and `attn_bwd_dq` (one CTA per 128-query tile and head; loops over 64-key tiles) recompute
+//   S and dP = dO V^T on the tensor cores; each compute thread handles half of a 64-wide row.  No atomics:
+//   results are bit-reproducible.
+//
+// Documents are [cu_seqlens[i], cu_seqlens[i+1]); tiles never mix documents: keys past the end of the document
+// (and, with `causal`, keys after the query) are masked before the softmax.
 #include "attention_sm100.h"
 #include "sm100.cuh"
 
@@ -23,16 +28,17 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128, BN = 128;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;  // TMA warp, MMA warp, 8 compute warps
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 struct TileInfo {
-  int doc_start, doc_len, q0;  // q0: first query row of the tile, local to the document
+  int doc_start, doc_len, q0;  // q0: first row of the tile, local to the document
   bool valid;
 };
 
-// Linear tile id -> (document, query block).  Tiles are numbered document by document.
+// Linear tile id -> (document, block of `block_rows` rows).  Tiles are numbered document by document.
 __device__ __forceinline__ TileInfo find_tile(const int* __restrict__ cu, int n_docs, int tile, int block_rows) {
   TileInfo ti;
   ti.valid = false;
@@ -53,6 +59,8 @@ __device__ __forceinline__ TileInfo find_tile(const int* __restrict__ cu, int n_
   return ti;
 }
 
+__device__ __forceinline__ uint32_t (&as32(uint32_t* p))[32] { return *reinterpret_cast<uint32_t(*)[32]>(p); }
+
 struct FwdParams {
   __nv_bfloat16* O;   // [T, Hq, D]
   float* LSE;         // [Hq, T]
@@ -60,30 +68,19 @@ struct FwdParams {
   int n_docs, T, Hq, Hkv;
   float scale_log2;   // softmax scale * log2(e)
   int causal;
-  int d_eff;          // channels that can be non-zero (multiple of 16, <= D): MMAs skip the zero padding beyond it
   int* status;
 };
 
 template <int D>
 struct FwdSmem {
-  static constexpr int kQ = BM * D * 2;
+  static constexpr int kQ = BM * D * 2;    // one query tile
   static constexpr int kKV = BN * D * 2;
-  static constexpr int kP = BM * BN * 2;
-  static constexpr int offQ = 0;
-  static constexpr int offK = offQ + kQ;          // 2 stages
-  static constexpr int offV = offK + 2 * kKV;     // 2 stages
-  static constexpr int offP = offV + 2 * kKV;     // 2 buffers
-  static constexpr int offBar = offP + 2 * kP;
+  static constexpr int offQ = 0;               // 2 tiles
+  static constexpr int offK = offQ + 2 * kQ;   // 2 stages
+  static constexpr int offV = offK + 2 * kKV;  // 2 stages
+  static constexpr int offBar = offV + 2 * kKV;
   static constexpr int kTotal = offBar + 256 + 1024;
 };
-
-// write 8 packed bf16 (16 B) of row r, logical column col (multiple of 8) into a [128 x 128] bf16 tile stored
-// as two 64-column blocks of [128 rows][128 B] with the 128-byte swizzle
-__device__ __forceinline__ void st_swizzled_16B(uint8_t* tile, int r, int col, uint4 v) {
-  const int block = col >> 6;
-  const int ci = (col & 63) >> 3;
-  *reinterpret_cast<uint4*>(tile + block * 16384 + r * 128 + ((ci ^ (r & 7)) << 4)) = v;
-}
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -95,35 +92,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
   uint64_t* q_full = bars;            // 1
-  uint64_t* k_full = bars + 1;        // 2
+  uint64_t* k_full = bars + 1;        // 2 stages
   uint64_t* k_empty = bars + 3;       // 2
   uint64_t* v_full = bars + 5;        // 2
   uint64_t* v_empty = bars + 7;       // 2
-  uint64_t* s_full = bars + 9;        // 2
-  uint64_t* s_empty = bars + 11;      // 2
-  uint64_t* p_full = bars + 13;       // 2
-  uint64_t* p_empty = bars + 15;      // 2
-  uint64_t* pv_full = bars + 17;      // 2
-  uint64_t* pv_empty = bars + 19;     // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* s_full = bars + 9;        // per query tile
+  uint64_t* p_full = bars + 11;       // per query tile (4 warps)
+  uint64_t* o_done = bars + 13;       // per query tile: last P.V finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const TileInfo ti = find_tile(p.cu, p.n_docs, blockIdx.x, BM);
+  const TileInfo ti = find_tile(p.cu, p.n_docs, blockIdx.x, 2 * BM);
   if (!ti.valid) return;  // uniform for the whole CTA
   const int hq = blockIdx.y;
   const int hkv = hq / (p.Hq / p.Hkv);
-  const int kv_end = p.causal ? min(ti.doc_len, ti.q0 + BM) : ti.doc_len;
-  const int J = (kv_end + BN - 1) / BN;
+  // key tiles visible to query tile t (rows q0 + 128 t ...): none if the tile starts beyond the document
+  int Jt[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qs = ti.q0 + t * BM;
+    const int kv_end = qs >= ti.doc_len ? 0 : (p.causal ? min(ti.doc_len, qs + BM) : ti.doc_len);
+    Jt[t] = (kv_end + BN - 1) / BN;
+  }
+  const int J = max(Jt[0], Jt[1]);
   constexpr int TMEM_COLS = 512;
-  constexpr int S_COL = 0, PV_COL = 256;
+  constexpr int S_COL = 0, O_COL = 256;  // S_t at 128 t, O_t at 256 + D t
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1);
-      mbar_init(&pv_full[i], 1); mbar_init(&pv_empty[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_done[i], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -138,9 +138,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 0) {
     if (lane == 0) {
       const int row0 = ti.doc_start + ti.q0;
-      mbar_expect_tx(q_full, L::kQ);
+      mbar_expect_tx(q_full, 2 * L::kQ);
 #pragma unroll
-      for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offQ + b * 16384, &tmQ, q_full, hq * D + 64 * b, row0);
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offQ + t * L::kQ + b * 16384, &tmQ, q_full, hq * D + 64 * b, row0 + t * BM);
       for (int j = 0; j < J; ++j) {
         const int s = j & 1;
         const uint32_t ph = ((j >> 1) & 1) ^ 1;
@@ -158,177 +160,149 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, false, false);
-      const uint32_t idesc_pv = make_idesc_bf16(BM, p.d_eff, false, true);
-      const uint32_t sQ = smem_u32(smem + L::offQ);
-      auto issue_S = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort_flag, p.status, kErrTimeoutFull)) return false;
-        if (!mbar_wait(&s_empty[s], ph ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
-        tc_fence_after();
-        const uint32_t sK = smem_u32(smem + L::offK + s * L::kKV);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(BM, D, false, true);
+      // S_t(j) = Q_t K_j^T.  It overwrites P_t(j-1), whose consumer P_t(j-1).V was issued earlier by this thread.
+      auto issue_S = [&](int t, int j) {
+        const uint32_t sQ = smem_u32(smem + L::offQ + t * L::kQ);
+        const uint32_t sK = smem_u32(smem + L::offK + (j & 1) * L::kKV);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          if (kk * 16 >= p.d_eff) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + S_COL + s * BN, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
+          umma_bf16(tmem_base + S_COL + t * BN, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
         }
-        umma_commit(&s_full[s]);
-        umma_commit(&k_empty[s]);
-        return true;
+        umma_commit(&s_full[t]);
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kErrTimeoutFull);
-      if (ok && J > 0) ok = issue_S(0);
-      for (int j = 0; j < J && ok; ++j) {
-        if (j + 1 < J) { ok = issue_S(j + 1); if (!ok) break; }
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&p_full[b], ph, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
-        if (!mbar_wait(&v_full[b], ph, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
-        if (!mbar_wait(&pv_empty[b], ph ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sP = smem_u32(smem + L::offP + b * L::kP);
-        const uint32_t sV = smem_u32(smem + L::offV + b * L::kKV);
+      if (ok && J > 0) {
+        ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
+        if (ok) {
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t adesc = make_smem_desc(sP + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sV + kk * 2048, 16384, 1024);
-          umma_bf16(tmem_base + PV_COL + b * D, adesc, bdesc, idesc_pv, kk != 0);
+          for (int t = 0; t < 2; ++t) if (Jt[t] > 0) issue_S(t, 0);
+          umma_commit(&k_empty[0]);
         }
-        umma_commit(&pv_full[b]);
-        umma_commit(&v_empty[b]);
-        umma_commit(&p_empty[b]);
+      }
+      for (int j = 0; j < J && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&v_full[s], ph, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+        if (j + 1 < J && !mbar_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+        const uint32_t sV = smem_u32(smem + L::offV + s * L::kKV);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j >= Jt[t]) continue;
+          if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)  // A = P_t: 128 lanes x 8 columns of packed bf16 pairs per 16 keys
+            umma_bf16_ts(tmem_base + O_COL + t * D, tmem_base + S_COL + t * BN + kk * 8, make_smem_desc(sV + kk * 2048, 16384, 1024),
+                         idesc_pv, (j | kk) != 0);
+          if (j + 1 < Jt[t]) issue_S(t, j + 1);
+          else umma_commit(&o_done[t]);
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[s]);
+        if (j + 1 < J) umma_commit(&k_empty[s ^ 1]);  // K_{j+1} is free once every S_t(j+1) issued above has run
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax / output warps
-    const int q = warp & 3;
+    // ------------------------------------------------------------------ softmax warps
+    const int t = (warp - 2) >> 2;         // query tile of this warp
+    const int q = warp & 3;                // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;           // row of the tile owned by this thread
-    const int qi = ti.q0 + r;              // query index local to the document
+    const int qi = ti.q0 + t * BM + r;     // query index local to the document
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    const uint32_t s_addr = tmem_base + S_COL + t * BN + lane_addr;
+    const uint32_t o_addr = tmem_base + O_COL + t * D + lane_addr;
+    const int Jm = Jt[t];
+    float m_used = 0.f, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < J && ok; ++j) {
-      const int b = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&s_full[b], ph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+    for (int j = 0; j < Jm && ok; ++j) {
+      if (!mbar_wait(&s_full[t], j & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_addr = tmem_base + S_COL + b * BN + lane_addr;
+      uint32_t s[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32(s_addr + c * 32, as32(&s[c * 32]));
+      tmem_ld_wait();
       const int kv0 = j * BN;
-      const bool need_mask = (kv0 + BN > ti.doc_len) || (p.causal && kv0 + BN - 1 > ti.q0);
-      const int limit = p.causal ? min(ti.doc_len - 1, qi) : ti.doc_len - 1;  // last visible key (local index)
-      // pass 1: row max of the raw scores (the softmax scale is positive, so it commutes with max)
-      float mx_raw = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(s_addr + c * 32, rr);
-        tmem_ld_wait();
-        if (need_mask) {
+      const bool need_mask = (kv0 + BN > ti.doc_len) || (p.causal && kv0 + BN - 1 > ti.q0 + t * BM);
+      if (need_mask) {
+        const int limit = (p.causal ? min(ti.doc_len - 1, qi) : ti.doc_len - 1) - kv0;  // last visible column of this tile
 #pragma unroll
-          for (int i = 0; i < 32; ++i) if (kv0 + c * 32 + i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(rr[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx_raw = fmaxf(mx_raw, __uint_as_float(rr[i]));
-        }
+        for (int i = 0; i < BN; ++i) if (i > limit) s[i] = 0xff800000u;  // -inf
       }
-      const float mx = fmaxf(m, mx_raw * p.scale_log2);
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
-      m = mx;
-      if (!mbar_wait(&p_empty[b], ph ^ 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
-      // pass 2: probabilities -> smem (bf16), row sum
-      uint8_t* sP = smem + L::offP + b * L::kP;
-      float rowsum = 0.f;
-      const float neg_m = -m_use;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(s_addr + c * 32, rr);
-        tmem_ld_wait();
-        float pr[32];
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(fmaf(__uint_as_float(rr[i]), p.scale_log2, neg_m));
-          if (need_mask && kv0 + c * 32 + i > limit) e = 0.f;
-          pr[i] = e;
-          rowsum += e;
-        }
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          uint4 pk;
-          __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) p2[u] = __floats2bfloat162_rn(pr[t * 8 + 2 * u], pr[t * 8 + 2 * u + 1]);
-          st_swizzled_16B(sP, r, c * 32 + t * 8, pk);
-        }
+      for (int i = 0; i < BN; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[i]));     mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
       }
-      tc_fence_before();
-      fence_async_proxy();
-      __syncwarp();
-      if (lane == 0) { mbar_arrive(&s_empty[b]); mbar_arrive(&p_full[b]); }
-      l = l * alpha + rowsum;
-      // fold in the previous tile's P.V while the tensor core works on this one
-      if (j > 0) {
-        const int pb = (j - 1) & 1;
-        const uint32_t pph = ((j - 1) >> 1) & 1;
-        if (!mbar_wait(&pv_full[pb], pph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t pv_addr = tmem_base + PV_COL + pb * D + lane_addr;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          if (c * 32 < p.d_eff) {  // columns at and beyond d_eff were never written by the MMA: leave those outputs at zero
-            uint32_t rr[32];
-            tmem_ld_32x32(pv_addr + c * 32, rr);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c * 32 + i < p.d_eff) o[c * 32 + i] = o[c * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&pv_empty[pb]);
-      }
-      alpha_pending = alpha;
-    }
-    if (ok && J > 0) {
-      const int pb = (J - 1) & 1;
-      const uint32_t pph = ((J - 1) >> 1) & 1;
-      if (mbar_wait(&pv_full[pb], pph, abort_flag, p.status, kErrTimeoutTmemFull)) {
-        tc_fence_after();
-        const uint32_t pv_addr = tmem_base + PV_COL + pb * D + lane_addr;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          if (c * 32 < p.d_eff) {  // columns at and beyond d_eff were never written by the MMA: leave those outputs at zero
-            uint32_t rr[32];
-            tmem_ld_32x32(pv_addr + c * 32, rr);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c * 32 + i < p.d_eff) o[c * 32 + i] = o[c * 32 + i] * alpha_pending + __uint_as_float(rr[i]);
-          }
-        }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // the scale is positive: it commutes with max
+      if (j == 0) {
+        m_used = (mx == -INFINITY) ? 0.f : mx;
       } else {
-        ok = false;
+        // S_t(j) was issued after P_t(j-1).V, so O_t is complete here and the tensor core does not touch it
+        // before this warp publishes P_t(j).
+        const bool grow = mx > m_used + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? ex2_approx(m_used - mx) : 1.f;
+          if (grow) m_used = mx;
+          l *= alpha;
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_addr + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, o);
+          }
+        }
       }
+      const float neg_m = -m_used;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float e0 = ex2_approx(fmaf(__uint_as_float(s[c * 32 + 2 * i]), p.scale_log2, neg_m));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
+          sum0 += e0;
+          sum1 += e1;
+          pk[i] = pack_bf16x2(e0, e1);
+        }
+        tmem_st_32x16(s_addr + c * 16, pk);  // P_t over the first 64 columns of S_t (every score is in registers already)
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+      l += sum0 + sum1;
     }
-    if (ok && qi < ti.doc_len) {
+    if (ok && Jm > 0 && mbar_wait(&o_done[t], 0, abort_flag, p.status, kErrTimeoutTmemFull)) {
+      tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const size_t tok = (size_t)(ti.doc_start + qi);
       __nv_bfloat16* dst = p.O + (tok * p.Hq + hq) * D;
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
-        uint4 pk;
-        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(o_addr + c * 32, o);
+        tmem_ld_wait();
+        if (qi < ti.doc_len) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) p2[u] = __floats2bfloat162_rn(o[i + 2 * u] * inv, o[i + 2 * u + 1] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = pk;
+          for (int u = 0; u < 4; ++u) {
+            uint4 pk;
+            pk.x = pack_bf16x2(__uint_as_float(o[u * 8 + 0]) * inv, __uint_as_float(o[u * 8 + 1]) * inv);
+            pk.y = pack_bf16x2(__uint_as_float(o[u * 8 + 2]) * inv, __uint_as_float(o[u * 8 + 3]) * inv);
+            pk.z = pack_bf16x2(__uint_as_float(o[u * 8 + 4]) * inv, __uint_as_float(o[u * 8 + 5]) * inv);
+            pk.w = pack_bf16x2(__uint_as_float(o[u * 8 + 6]) * inv, __uint_as_float(o[u * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + u * 8) = pk;
+          }
+        }
       }
-      p.LSE[(size_t)hq * p.T + tok] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
+      if (qi < ti.doc_len) p.LSE[(size_t)hq * p.T + tok] = l > 0.f ? (m_used + log2f(l)) * kLn2 : -INFINITY;
     }
   }
 
@@ -370,40 +344,38 @@ struct BwdParams {
   int n_docs, T, Hq, Hkv;
   float scale, scale_log2;
   int causal;
-  int d_eff;
   int* status;
 };
 
-// Backward tiles.  Both kernels work on a 128-row "stationary" tile (keys for dK/dV, queries for dQ) and stream
-// 64-row tiles of the other operand, so that S and dP take only 64 TMEM columns each and can be double-buffered:
-// the tensor core computes S/dP of step i+1 while the CUDA cores turn step i into P / dS, and the accumulation MMAs
-// of step i overlap the CUDA-core work of step i+1.
-constexpr int BS = 64;  // rows of the streamed tile
+// Backward tiles.  Both kernels keep a 128-row "stationary" tile (keys for dK/dV, queries for dQ) in shared memory and
+// stream 64-row tiles of the other operand through a 3-stage ring, so that S and dP take 64 TMEM columns each and are
+// double-buffered: the tensor core computes S/dP of step i+1 while the compute warps turn step i into P / dS, and the
+// accumulation MMAs of step i overlap the CUDA-core work of step i+1.  P / dS are written as packed bf16 over the
+// fp32 scores they came from and are read from tensor memory as the A operand.
+constexpr int BS = 64;   // rows of the streamed tile
+constexpr int NST = 3;   // stages of the streamed ring
 
 template <int D>
 struct BwdSmem {
   static constexpr int kBig = 128 * D * 2;     // stationary [128 x D] tile
   static constexpr int kSmall = BS * D * 2;    // streamed [64 x D] tile
-  static constexpr int kSq = 128 * BS * 2;     // [128 x 64] bf16 tile (P^T / dS^T / dS)
-  static constexpr int offA = 0;                       // dkdv: K_j   | dq: Q_i
-  static constexpr int offB = offA + kBig;             // dkdv: V_j   | dq: dO_i
-  static constexpr int offC = offB + kBig;             // 2 stages: dkdv Q_i  | dq K_j
-  static constexpr int offD = offC + 2 * kSmall;       // 2 stages: dkdv dO_i | dq V_j
-  static constexpr int offP = offD + 2 * kSmall;       // 2 buffers (dkdv: P^T)
-  static constexpr int offDS = offP + 2 * kSq;         // 2 buffers (dS^T / dS)
-  static constexpr int offStat = offDS + 2 * kSq;      // per compute warp: (lse2[64], delta[64]) floats
-  static constexpr int offBar = offStat + 4 * 128 * 4;
+  static constexpr int offA = 0;                        // dkdv: K_j   | dq: Q_i
+  static constexpr int offB = offA + kBig;              // dkdv: V_j   | dq: dO_i
+  static constexpr int offC = offB + kBig;              // NST stages: dkdv Q_i  | dq K_j
+  static constexpr int offD = offC + NST * kSmall;      // NST stages: dkdv dO_i | dq V_j
+  static constexpr int offStat = offD + NST * kSmall;   // per compute warp: lse2[32], delta[32] floats
+  static constexpr int offBar = offStat + 8 * 64 * 4;
   static constexpr int kTotal = offBar + 256 + 1024;
 };
 
-// 16 bytes of row r, column col (multiple of 8, < 64) of a [rows x 64] bf16 tile with 128-byte rows and 128-byte swizzle
-__device__ __forceinline__ void st_sw64_16B(uint8_t* tile, int r, int col, uint4 v) {
-  *reinterpret_cast<uint4*>(tile + r * 128 + (((col >> 3) ^ (r & 7)) << 4)) = v;
-}
+// Column of the packed-bf16 A operand inside a 64-column fp32 buffer for k-step kk (16 rows of the streamed tile):
+// the warps of column half h write their 32 values as 16 packed words at column 32 h, so no warp overwrites scores
+// that the other half has not read yet.
+__device__ __forceinline__ constexpr int packed_col(int kk) { return (kk >> 1) * 32 + (kk & 1) * 8; }
 
 // dK_j, dV_j for one 128-key tile and one kv head.  Everything is computed transposed (rows = keys):
-//   S^T = K Q^T, dP^T = V dO^T  (M = 128 keys, N = 64 queries)   ->  P^T, dS^T (thread = key row)
-//   dV += P^T dO,  dK += dS^T Q  (A = [128 keys x 64 queries] K-major, B = the [64 x D] query-side tile read MN-major)
+//   S^T = K Q^T, dP^T = V dO^T  (M = 128 keys, N = 64 queries)   ->  P^T, dS^T (thread = key row, half of the queries)
+//   dV += P^T dO,  dK += dS^T Q  (A = [128 keys x 64 queries] from TMEM, B = the [64 x D] query-side tile read MN-major)
 // TMEM columns: S^T[2] 0/64, dP^T[2] 128/192, dV 256, dK 256 + D.
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -415,13 +387,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
   uint64_t* kv_full = bars;          // 1
-  uint64_t* qdo_full = bars + 1;     // 2
-  uint64_t* qdo_empty = bars + 3;    // 2
-  uint64_t* sdp_full = bars + 5;     // 2
-  uint64_t* sdp_empty = bars + 7;    // 2 (4 warps)
-  uint64_t* pds_full = bars + 9;     // 2 (4 warps)
-  uint64_t* pds_empty = bars + 11;   // 2
-  uint64_t* acc_done = bars + 13;    // 1
+  uint64_t* acc_done = bars + 1;     // 1
+  uint64_t* qdo_full = bars + 2;     // NST
+  uint64_t* qdo_empty = bars + 5;    // NST
+  uint64_t* sdp_full = bars + 8;     // 2
+  uint64_t* pds_full = bars + 10;    // 2 (8 warps)
+  uint64_t* buf_free = bars + 12;    // 2: the accumulation MMAs that read P^T / dS^T of this buffer have finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stat = reinterpret_cast<float*>(smem + L::offStat);
@@ -440,10 +411,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(acc_done, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 4);
-      mbar_init(&pds_full[i], 4); mbar_init(&pds_empty[i], 1);
-    }
+    for (int i = 0; i < NST; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&pds_full[i], 8); mbar_init(&buf_free[i], 1); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -462,17 +431,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tma_load_2d(smem + L::offA + b * 16384, &tmK, kv_full, hkv * D + 64 * b, krow);
         tma_load_2d(smem + L::offB + b * 16384, &tmV, kv_full, hkv * D + 64 * b, krow);
       }
+      int sg = 0;
+      uint32_t ph = 1;
       for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1;
         const int i = i_first + it / group, hq = hkv * group + it % group;
-        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        if (!mbar_wait(&qdo_empty[sg], ph, abort_flag, p.status, kErrTimeoutEmpty)) break;
         const int qrow = ti.doc_start + i * BS;
-        mbar_expect_tx(&qdo_full[st], 2 * L::kSmall);
+        mbar_expect_tx(&qdo_full[sg], 2 * L::kSmall);
 #pragma unroll
         for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + st * L::kSmall + b * 8192, &tmQ, &qdo_full[st], hq * D + 64 * b, qrow);
-          tma_load_2d(smem + L::offD + st * L::kSmall + b * 8192, &tmdO, &qdo_full[st], hq * D + 64 * b, qrow);
+          tma_load_2d(smem + L::offC + sg * L::kSmall + b * 8192, &tmQ, &qdo_full[sg], hq * D + 64 * b, qrow);
+          tma_load_2d(smem + L::offD + sg * L::kSmall + b * 8192, &tmdO, &qdo_full[sg], hq * D + 64 * b, qrow);
         }
+        if (++sg == NST) { sg = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -481,117 +452,108 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);      // [128 keys] x [D], contraction over 64 queries
       const uint32_t sK = smem_u32(smem + L::offA), sV = smem_u32(smem + L::offB);
       auto issue_sdp = [&](int it) -> bool {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&qdo_full[st], ph, abort_flag, p.status, kErrTimeoutFull)) return false;
-        if (!mbar_wait(&sdp_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
+        const int sg = it % NST, b = it & 1;
+        if (!mbar_wait(&qdo_full[sg], (it / NST) & 1, abort_flag, p.status, kErrTimeoutFull)) return false;
+        if (!mbar_wait(&buf_free[b], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
         tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + L::offC + st * L::kSmall), sdO = smem_u32(smem + L::offD + st * L::kSmall);
+        const uint32_t sQ = smem_u32(smem + L::offC + sg * L::kSmall), sdO = smem_u32(smem + L::offD + sg * L::kSmall);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32, offq = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + ST_COL + st * BS, make_smem_desc(sK + offk, 16, 1024), make_smem_desc(sQ + offq, 16, 1024), idesc_s, kk != 0);
+          umma_bf16(tmem_base + ST_COL + b * BS, make_smem_desc(sK + offk, 16, 1024), make_smem_desc(sQ + offq, 16, 1024), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32, offq = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + DPT_COL + st * BS, make_smem_desc(sV + offk, 16, 1024), make_smem_desc(sdO + offq, 16, 1024), idesc_s, kk != 0);
+          umma_bf16(tmem_base + DPT_COL + b * BS, make_smem_desc(sV + offk, 16, 1024), make_smem_desc(sdO + offq, 16, 1024), idesc_s, kk != 0);
         }
-        umma_commit(&sdp_full[st]);
+        umma_commit(&sdp_full[b]);
         return true;
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kErrTimeoutFull);
       if (ok && n_iter > 0) ok = issue_sdp(0);
       for (int it = 0; it < n_iter && ok; ++it) {
         if (it + 1 < n_iter) { ok = issue_sdp(it + 1); if (!ok) break; }
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&pds_full[st], ph, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+        const int sg = it % NST, b = it & 1;
+        if (!mbar_wait(&pds_full[b], (it >> 1) & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + L::offC + st * L::kSmall), sdO = smem_u32(smem + L::offD + st * L::kSmall);
-        const uint32_t sPT = smem_u32(smem + L::offP + st * L::kSq), sDST = smem_u32(smem + L::offDS + st * L::kSq);
+        const uint32_t sQ = smem_u32(smem + L::offC + sg * L::kSmall), sdO = smem_u32(smem + L::offD + sg * L::kSmall);
 #pragma unroll
         for (int kk = 0; kk < BS / 16; ++kk)
-          umma_bf16(tmem_base + DV_COL, make_smem_desc(sPT + kk * 32, 16, 1024), make_smem_desc(sdO + kk * 2048, 8192, 1024), idesc_g,
-                    (it | kk) != 0);
+          umma_bf16_ts(tmem_base + DV_COL, tmem_base + ST_COL + b * BS + packed_col(kk), make_smem_desc(sdO + kk * 2048, 8192, 1024), idesc_g,
+                       (it | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < BS / 16; ++kk)
-          umma_bf16(tmem_base + DK_COL, make_smem_desc(sDST + kk * 32, 16, 1024), make_smem_desc(sQ + kk * 2048, 8192, 1024), idesc_g,
-                    (it | kk) != 0);
-        umma_commit(&qdo_empty[st]);
-        umma_commit(&pds_empty[st]);
+          umma_bf16_ts(tmem_base + DK_COL, tmem_base + DPT_COL + b * BS + packed_col(kk), make_smem_desc(sQ + kk * 2048, 8192, 1024), idesc_g,
+                       (it | kk) != 0);
+        umma_commit(&qdo_empty[sg]);
+        umma_commit(&buf_free[b]);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
-    const int q = warp & 3;
+    const int cw = warp - 2;
+    const int ch = cw >> 2;                // column half: queries [32 ch, 32 ch + 32) of the streamed tile
+    const int q = warp & 3;                // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;           // key row of the tile owned by this thread
     const int kvi = k0 + r;                // key index local to the document
     const bool key_ok = kvi < ti.doc_len;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    float* wstat = stat + cw * 64;
+    // per-query statistics: lane l fetches those of query 32 ch + l one step ahead
+    auto fetch = [&](int it, float& l2, float& dl) {
+      const int i = i_first + it / group, hq = hkv * group + it % group;
+      const int qq = i * BS + ch * 32 + lane;
+      const bool qok = qq < ti.doc_len;
+      const size_t idx = (size_t)hq * p.T + ti.doc_start + (qok ? qq : 0);
+      l2 = qok ? p.LSE[idx] * kLog2e : INFINITY;  // +inf -> exp2(-inf) = 0 for queries beyond the document
+      dl = qok ? p.delta[idx] : 0.f;
+    };
+    float nl2 = 0.f, ndl = 0.f;
+    if (n_iter > 0) fetch(0, nl2, ndl);
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int st = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
-      const int i = i_first + it / group, hq = hkv * group + it % group;
-      const int q0 = i * BS;
-      // per-query statistics of this step -> this warp's own smem copy (warp-local, so no block barrier is involved)
-      float* wstat = stat + q * 128;
+      const int b = it & 1;
+      const int q0 = (i_first + it / group) * BS + ch * 32;   // first query of this thread's columns
       __syncwarp();
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int qc = lane + 32 * h;
-        const int qq = q0 + qc;
-        const bool qok = qq < ti.doc_len;
-        const size_t tok = (size_t)ti.doc_start + (qok ? qq : 0);
-        wstat[qc] = qok ? p.LSE[(size_t)hq * p.T + tok] * kLog2e : INFINITY;  // +inf -> exp2(-inf) = 0 for padded queries
-        wstat[64 + qc] = qok ? p.delta[(size_t)hq * p.T + tok] : 0.f;
-      }
+      wstat[lane] = nl2;
+      wstat[32 + lane] = ndl;
       __syncwarp();
-      if (!mbar_wait(&sdp_full[st], ph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      if (it + 1 < n_iter) fetch(it + 1, nl2, ndl);
+      if (!mbar_wait(&sdp_full[b], (it >> 1) & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      const float* lse2 = wstat;
-      const float* dl = wstat + 64;
-      float pr[BS], ds[BS];
+      uint32_t sr[32], dr[32];
+      tmem_ld_32x32(tmem_base + ST_COL + b * BS + ch * 32 + lane_addr, sr);
+      tmem_ld_32x32(tmem_base + DPT_COL + b * BS + ch * 32 + lane_addr, dr);
+      tmem_ld_wait();
+      // masked: keys beyond the document, or (causal) keys after the query
+      const bool need_mask = (k0 + 128 > ti.doc_len) || (p.causal && k0 + 127 > q0);
+      uint32_t pp[16], dd[16];
 #pragma unroll
-      for (int c = 0; c < BS / 32; ++c) {
-        uint32_t sr[32], dr[32];
-        tmem_ld_32x32(tmem_base + ST_COL + st * BS + lane_addr + c * 32, sr);
-        tmem_ld_32x32(tmem_base + DPT_COL + st * BS + lane_addr + c * 32, dr);
-        tmem_ld_wait();
+      for (int u4 = 0; u4 < 8; ++u4) {
+        const float4 l4 = reinterpret_cast<const float4*>(wstat)[u4];
+        const float4 d4 = reinterpret_cast<const float4*>(wstat + 32)[u4];
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dls[4] = {d4.x, d4.y, d4.z, d4.w};
+        float pv[4], dsv[4];
 #pragma unroll
-        for (int u = 0; u < 32; ++u) {
-          const int qc = c * 32 + u;
-          const bool vis = key_ok && (!p.causal || kvi <= q0 + qc);
-          const float pv = vis ? exp2f(fmaf(__uint_as_float(sr[u]), p.scale_log2, -lse2[qc])) : 0.f;
-          pr[qc] = pv;
-          ds[qc] = pv * (__uint_as_float(dr[u]) - dl[qc]) * p.scale;
+        for (int e = 0; e < 4; ++e) {
+          const int u = u4 * 4 + e;
+          float x = fmaf(__uint_as_float(sr[u]), p.scale_log2, -ls[e]);
+          if (need_mask && !(key_ok && (!p.causal || kvi <= q0 + u))) x = -INFINITY;
+          pv[e] = ex2_approx(x);
+          dsv[e] = pv[e] * (__uint_as_float(dr[u]) - dls[e]);
         }
+        pp[u4 * 2] = pack_bf16x2(pv[0], pv[1]);  pp[u4 * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+        dd[u4 * 2] = pack_bf16x2(dsv[0], dsv[1]); dd[u4 * 2 + 1] = pack_bf16x2(dsv[2], dsv[3]);
       }
+      tmem_st_32x16(tmem_base + ST_COL + b * BS + ch * 32 + lane_addr, pp);
+      tmem_st_32x16(tmem_base + DPT_COL + b * BS + ch * 32 + lane_addr, dd);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sdp_empty[st]);
-      if (!mbar_wait(&pds_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
-      uint8_t* sPT = smem + L::offP + st * L::kSq;
-      uint8_t* sDST = smem + L::offDS + st * L::kSq;
-#pragma unroll
-      for (int t = 0; t < BS / 8; ++t) {
-        uint4 a, b;
-        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&a);
-        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          a2[u] = __floats2bfloat162_rn(pr[t * 8 + 2 * u], pr[t * 8 + 2 * u + 1]);
-          b2[u] = __floats2bfloat162_rn(ds[t * 8 + 2 * u], ds[t * 8 + 2 * u + 1]);
-        }
-        st_sw64_16B(sPT, r, t * 8, a);
-        st_sw64_16B(sDST, r, t * 8, b);
-      }
-      fence_async_proxy();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&pds_full[st]);
+      if (lane == 0) mbar_arrive(&pds_full[b]);
     }
-    // epilogue: thread r owns key row k0 + r of dV and dK
+    // epilogue: thread (r, ch) owns channels [ch D/2, (ch+1) D/2) of key row k0 + r of dV and dK (dK carries the softmax scale)
     if (ok && mbar_wait(acc_done, 0, abort_flag, p.status, kErrTimeoutTmemFull)) {
       tc_fence_after();
       if (n_iter > 0) {
@@ -599,20 +561,22 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int which = 0; which < 2; ++which) {
           __nv_bfloat16* base = which == 0 ? p.dV : p.dK;
           const int col = which == 0 ? DV_COL : DK_COL;
+          const float f = which == 0 ? 1.f : p.scale;
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = 0; c < D / 64; ++c) {
+            const int c0 = ch * (D / 2) + c * 32;
             uint32_t rr[32];
-            tmem_ld_32x32(tmem_base + col + lane_addr + c * 32, rr);
+            tmem_ld_32x32(tmem_base + col + lane_addr + c0, rr);
             tmem_ld_wait();
             if (key_ok) {
-              __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * D + c * 32;
+              __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * D + c0;
 #pragma unroll
               for (int t = 0; t < 4; ++t) {
                 uint4 pk;
-                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                  p2[u] = __floats2bfloat162_rn(__uint_as_float(rr[t * 8 + 2 * u]), __uint_as_float(rr[t * 8 + 2 * u + 1]));
+                pk.x = pack_bf16x2(__uint_as_float(rr[t * 8 + 0]) * f, __uint_as_float(rr[t * 8 + 1]) * f);
+                pk.y = pack_bf16x2(__uint_as_float(rr[t * 8 + 2]) * f, __uint_as_float(rr[t * 8 + 3]) * f);
+                pk.z = pack_bf16x2(__uint_as_float(rr[t * 8 + 4]) * f, __uint_as_float(rr[t * 8 + 5]) * f);
+                pk.w = pack_bf16x2(__uint_as_float(rr[t * 8 + 6]) * f, __uint_as_float(rr[t * 8 + 7]) * f);
                 *reinterpret_cast<uint4*>(dst + t * 8) = pk;
               }
             }
@@ -646,13 +610,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
   uint64_t* qdo_full = bars;         // 1
-  uint64_t* kv_full = bars + 1;      // 2
-  uint64_t* kv_empty = bars + 3;     // 2
-  uint64_t* sdp_full = bars + 5;     // 2
-  uint64_t* sdp_empty = bars + 7;    // 2 (4 warps)
-  uint64_t* ds_full = bars + 9;      // 2 (4 warps)
-  uint64_t* ds_empty = bars + 11;    // 2
-  uint64_t* acc_done = bars + 13;
+  uint64_t* acc_done = bars + 1;     // 1
+  uint64_t* kv_full = bars + 2;      // NST
+  uint64_t* kv_empty = bars + 5;     // NST
+  uint64_t* sdp_full = bars + 8;     // 2
+  uint64_t* ds_full = bars + 10;     // 2 (8 warps)
+  uint64_t* buf_free = bars + 12;    // 2
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -668,10 +631,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1); mbar_init(acc_done, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&sdp_full[i], 1); mbar_init(&sdp_empty[i], 4);
-      mbar_init(&ds_full[i], 4); mbar_init(&ds_empty[i], 1);
-    }
+    for (int i = 0; i < NST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&ds_full[i], 8); mbar_init(&buf_free[i], 1); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -690,126 +651,120 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_2d(smem + L::offA + b * 16384, &tmQ, qdo_full, hq * D + 64 * b, qrow);
         tma_load_2d(smem + L::offB + b * 16384, &tmdO, qdo_full, hq * D + 64 * b, qrow);
       }
+      int sg = 0;
+      uint32_t ph = 1;
       for (int j = 0; j < J; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        if (!mbar_wait(&kv_empty[sg], ph, abort_flag, p.status, kErrTimeoutEmpty)) break;
         const int krow = ti.doc_start + j * BS;
-        mbar_expect_tx(&kv_full[st], 2 * L::kSmall);
+        mbar_expect_tx(&kv_full[sg], 2 * L::kSmall);
 #pragma unroll
         for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + st * L::kSmall + b * 8192, &tmK, &kv_full[st], hkv * D + 64 * b, krow);
-          tma_load_2d(smem + L::offD + st * L::kSmall + b * 8192, &tmV, &kv_full[st], hkv * D + 64 * b, krow);
+          tma_load_2d(smem + L::offC + sg * L::kSmall + b * 8192, &tmK, &kv_full[sg], hkv * D + 64 * b, krow);
+          tma_load_2d(smem + L::offD + sg * L::kSmall + b * 8192, &tmV, &kv_full[sg], hkv * D + 64 * b, krow);
         }
+        if (++sg == NST) { sg = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, BS, false, false);
-      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, false, true);  // dQ = dS K: A [128 q x 64 kv] K-major, B = K_j [64 kv x D] MN-major
+      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, false, true);  // dQ = dS K: A [128 q x 64 kv] from TMEM, B = K_j [64 kv x D] MN-major
       const uint32_t sQ = smem_u32(smem + L::offA), sdO = smem_u32(smem + L::offB);
       auto issue_sdp = [&](int j) -> bool {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&kv_full[st], ph, abort_flag, p.status, kErrTimeoutFull)) return false;
-        if (!mbar_wait(&sdp_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
+        const int sg = j % NST, b = j & 1;
+        if (!mbar_wait(&kv_full[sg], (j / NST) & 1, abort_flag, p.status, kErrTimeoutFull)) return false;
+        if (!mbar_wait(&buf_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + L::offC + st * L::kSmall), sV = smem_u32(smem + L::offD + st * L::kSmall);
+        const uint32_t sK = smem_u32(smem + L::offC + sg * L::kSmall), sV = smem_u32(smem + L::offD + sg * L::kSmall);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t offq = (kk >> 2) * 16384 + (kk & 3) * 32, offk = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + S_COL + st * BS, make_smem_desc(sQ + offq, 16, 1024), make_smem_desc(sK + offk, 16, 1024), idesc_s, kk != 0);
+          umma_bf16(tmem_base + S_COL + b * BS, make_smem_desc(sQ + offq, 16, 1024), make_smem_desc(sK + offk, 16, 1024), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t offq = (kk >> 2) * 16384 + (kk & 3) * 32, offk = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + DP_COL + st * BS, make_smem_desc(sdO + offq, 16, 1024), make_smem_desc(sV + offk, 16, 1024), idesc_s, kk != 0);
+          umma_bf16(tmem_base + DP_COL + b * BS, make_smem_desc(sdO + offq, 16, 1024), make_smem_desc(sV + offk, 16, 1024), idesc_s, kk != 0);
         }
-        umma_commit(&sdp_full[st]);
+        umma_commit(&sdp_full[b]);
         return true;
       };
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, kErrTimeoutFull);
       if (ok && J > 0) ok = issue_sdp(0);
       for (int j = 0; j < J && ok; ++j) {
         if (j + 1 < J) { ok = issue_sdp(j + 1); if (!ok) break; }
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&ds_full[st], ph, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+        const int sg = j % NST, b = j & 1;
+        if (!mbar_wait(&ds_full[b], (j >> 1) & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + L::offC + st * L::kSmall);
-        const uint32_t sDS = smem_u32(smem + L::offDS + st * L::kSq);
+        const uint32_t sK = smem_u32(smem + L::offC + sg * L::kSmall);
 #pragma unroll
         for (int kk = 0; kk < BS / 16; ++kk)
-          umma_bf16(tmem_base + DQ_COL, make_smem_desc(sDS + kk * 32, 16, 1024), make_smem_desc(sK + kk * 2048, 8192, 1024), idesc_q,
-                    (j | kk) != 0);
-        umma_commit(&kv_empty[st]);
-        umma_commit(&ds_empty[st]);
+          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + DP_COL + b * BS + packed_col(kk), make_smem_desc(sK + kk * 2048, 8192, 1024), idesc_q,
+                       (j | kk) != 0);
+        umma_commit(&kv_empty[sg]);
+        umma_commit(&buf_free[b]);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
+    const int ch = (warp - 2) >> 2;        // column half: keys [32 ch, 32 ch + 32) of the streamed tile
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const int qi = ti.q0 + r;
     const bool row_ok = qi < ti.doc_len;
     const size_t tok = (size_t)ti.doc_start + (row_ok ? qi : 0);
-    const float lse2 = row_ok ? p.LSE[(size_t)hq * p.T + tok] * kLog2e : 0.f;
+    const float neg_lse2 = row_ok ? -p.LSE[(size_t)hq * p.T + tok] * kLog2e : 0.f;
     const float dl = row_ok ? p.delta[(size_t)hq * p.T + tok] : 0.f;
     bool ok = true;
     for (int j = 0; j < J && ok; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&sdp_full[st], ph, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      const int b = j & 1;
+      if (!mbar_wait(&sdp_full[b], (j >> 1) & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      const int kv0 = j * BS;
-      float ds[BS];
+      uint32_t sr[32], dr[32];
+      tmem_ld_32x32(tmem_base + S_COL + b * BS + ch * 32 + lane_addr, sr);
+      tmem_ld_32x32(tmem_base + DP_COL + b * BS + ch * 32 + lane_addr, dr);
+      tmem_ld_wait();
+      const int kv0 = j * BS + ch * 32;
+      const bool need_mask = (j * BS + BS > ti.doc_len) || (ti.q0 + BM > ti.doc_len) || (p.causal && j * BS + BS - 1 > ti.q0);
+      uint32_t dd[16];
 #pragma unroll
-      for (int c = 0; c < BS / 32; ++c) {
-        uint32_t sr[32], dr[32];
-        tmem_ld_32x32(tmem_base + S_COL + st * BS + lane_addr + c * 32, sr);
-        tmem_ld_32x32(tmem_base + DP_COL + st * BS + lane_addr + c * 32, dr);
-        tmem_ld_wait();
+      for (int u2 = 0; u2 < 16; ++u2) {
+        float dsv[2];
 #pragma unroll
-        for (int u = 0; u < 32; ++u) {
-          const int kv = kv0 + c * 32 + u;
-          const bool vis = row_ok && kv < ti.doc_len && (!p.causal || kv <= qi);
-          const float pv = vis ? exp2f(fmaf(__uint_as_float(sr[u]), p.scale_log2, -lse2)) : 0.f;
-          ds[c * 32 + u] = pv * (__uint_as_float(dr[u]) - dl) * p.scale;
+        for (int e = 0; e < 2; ++e) {
+          const int u = u2 * 2 + e;
+          float x = fmaf(__uint_as_float(sr[u]), p.scale_log2, neg_lse2);
+          if (need_mask && !(row_ok && kv0 + u < ti.doc_len && (!p.causal || kv0 + u <= qi))) x = -INFINITY;
+          dsv[e] = ex2_approx(x) * (__uint_as_float(dr[u]) - dl);
         }
+        dd[u2] = pack_bf16x2(dsv[0], dsv[1]);
       }
+      tmem_st_32x16(tmem_base + DP_COL + b * BS + ch * 32 + lane_addr, dd);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sdp_empty[st]);
-      if (!mbar_wait(&ds_empty[st], ph ^ 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
-      uint8_t* sDS = smem + L::offDS + st * L::kSq;
-#pragma unroll
-      for (int t = 0; t < BS / 8; ++t) {
-        uint4 b;
-        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&b);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) b2[u] = __floats2bfloat162_rn(ds[t * 8 + 2 * u], ds[t * 8 + 2 * u + 1]);
-        st_sw64_16B(sDS, r, t * 8, b);
-      }
-      fence_async_proxy();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_full[st]);
+      if (lane == 0) mbar_arrive(&ds_full[b]);
     }
+    // epilogue: thread (r, ch) owns channels [ch D/2, (ch+1) D/2) of query row q0 + r (dQ carries the softmax scale)
     if (ok && mbar_wait(acc_done, 0, abort_flag, p.status, kErrTimeoutTmemFull)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
+        const int c0 = ch * (D / 2) + c * 32;
         uint32_t rr[32];
-        tmem_ld_32x32(tmem_base + DQ_COL + lane_addr + c * 32, rr);
+        tmem_ld_32x32(tmem_base + DQ_COL + lane_addr + c0, rr);
         tmem_ld_wait();
         if (row_ok && J > 0) {
-          __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * D + c * 32;
+          __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * D + c0;
+          const float f = p.scale;
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             uint4 pk;
-            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              p2[u] = __floats2bfloat162_rn(__uint_as_float(rr[t * 8 + 2 * u]), __uint_as_float(rr[t * 8 + 2 * u + 1]));
+            pk.x = pack_bf16x2(__uint_as_float(rr[t * 8 + 0]) * f, __uint_as_float(rr[t * 8 + 1]) * f);
+            pk.y = pack_bf16x2(__uint_as_float(rr[t * 8 + 2]) * f, __uint_as_float(rr[t * 8 + 3]) * f);
+            pk.z = pack_bf16x2(__uint_as_float(rr[t * 8 + 4]) * f, __uint_as_float(rr[t * 8 + 5]) * f);
+            pk.w = pack_bf16x2(__uint_as_float(rr[t * 8 + 6]) * f, __uint_as_float(rr[t * 8 + 7]) * f);
             *reinterpret_cast<uint4*>(dst + t * 8) = pk;
           }
         }
@@ -853,8 +808,8 @@ extern "C" int vlmt_attn_fwd(const void* q, const void* k, const void* v, void* 
   FwdParams p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o); p.LSE = lse; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
-  p.d_eff = (d_eff <= 0 || d_eff > D) ? D : ((d_eff + 15) / 16) * 16;
-  dim3 grid(T / BM + n_docs + 1, Hq);
+  (void)d_eff;
+  dim3 grid(T / (2 * BM) + n_docs + 1, Hq);
   if (D == 128) {
     if ((r = set_smem(attn_fwd_kernel<128>, FwdSmem<128>::kTotal))) return r;
     attn_fwd_kernel<128><<<grid, ATT_THREADS, FwdSmem<128>::kTotal, st>>>(tq, tk, tv, p);
@@ -891,7 +846,7 @@ extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, con
   p.dQ = reinterpret_cast<__nv_bfloat16*>(dq); p.dK = reinterpret_cast<__nv_bfloat16*>(dk); p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   p.LSE = lse; p.delta = delta; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
-  p.d_eff = (d_eff <= 0 || d_eff > D) ? D : ((d_eff + 15) / 16) * 16;
+  (void)d_eff;
   dim3 grid_kv(T / BN + n_docs + 1, Hkv), grid_q(T / BM + n_docs + 1, Hq);
   if (D == 128) {
     if ((r = set_smem(attn_bwd_dkdv_kernel<128>, BwdSmem<128>::kTotal))) return r;

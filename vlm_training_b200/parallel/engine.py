@@ -179,10 +179,20 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         bucket_elems = int(bucket_mb * (1 << 20) / params[0].element_size())
         # parameter order = registration order (≈ forward order): late buckets finish first in backward
         ordered = [p for p in model.parameters() if p in group_of]
+        experts = [(p, group_of[p]) for p in ordered if getattr(p, "_ep_sharded", False)]
+        ordered = [p for p in ordered if not getattr(p, "_ep_sharded", False)]
         sharded = [(p, group_of[p]) for p in ordered if getattr(p, "_tp_sharded", False)]
         replicated = [(p, group_of[p]) for p in ordered if not getattr(p, "_tp_sharded", False)]
         self.domains: list[_Domain] = []
         symmetric = fused_comm and self.is_cuda and dist.is_initialized()
+        if experts:
+            # expert-parallel parameters: each rank owns different experts, whose gradients already hold the
+            # contributions of every rank of the all-to-all group; they are summed only over the ranks that own
+            # the same experts (none when ep_size equals the data-parallel size)
+            ep = getattr(model, "_ep_ctx", None)
+            rep_group = ep.replica_group if (ep is not None and ep.replica_size > 1) else None
+            self.domains.append(_Domain("ep_experts", experts, rep_group, 1.0 / dp_size, shard and rep_group is not None, device,
+                                        pdtype, bucket_elems, state_dtype, False))
         if tp_size > 1:
             if sharded:
                 self.domains.append(_Domain("tp_sharded", sharded, dp_group, 1.0 / dp_size, shard, device, pdtype,

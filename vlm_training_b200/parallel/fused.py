@@ -59,6 +59,8 @@ class FusedStepState:
 
 
 def usable(engine) -> bool:
+    if any(d.name == "ep_experts" for d in engine.domains):
+        return False  # expert-parallel parameters take the plain path
     return all(d.size == 1 or symm.handle_of(d.flat_grad) is not None for d in engine.domains)
 
 

@@ -122,8 +122,17 @@ def load_model_state(model, state: dict):
     tp = getattr(model, "tp", None)
     target = model.state_dict()
     meta = _param_meta(model) if tp is not None and tp.enabled else {}
+    ep = getattr(model, "_ep_ctx", None)
+    ep_keys = {}
+    if ep is not None and ep.size > 1:  # expert-parallel parameters: state_dict() shows gathered copies, not the parameters
+        ep_keys = {n: p for n, p in model.named_parameters() if getattr(p, "_ep_sharded", False)}
     with torch.no_grad():
+        for k, p in ep_keys.items():
+            n = ep.local_experts
+            p.copy_(state[k][ep.rank * n:(ep.rank + 1) * n].to(p.dtype))
         for k, dst in target.items():
+            if k in ep_keys:
+                continue
             src = state[k]
             if k in meta:
                 dim, splits = meta[k]
@@ -165,6 +174,9 @@ def optimizer_state_for_dcp(engine, tp_rank: int = 0) -> dict:
            "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in engine.param_groups]}
     for d in engine.domains:
         prefix = d.name if d.name != "tp_sharded" else f"tp_sharded.tp{tp_rank}"
+        if d.name == "ep_experts":  # every expert-parallel rank owns different experts
+            ep = getattr(engine.model, "_ep_ctx", None)
+            prefix = f"ep_experts.ep{ep.rank if ep is not None else 0}"
         entry = {}
         for name, bufs in (("master", d.master), ("exp_avg", d.exp_avg), ("exp_avg_sq", d.exp_avg_sq)):
             for bi, t in enumerate(bufs):

@@ -91,6 +91,10 @@ class Trainer:
         # ---------------- parallelism (order matters: TP → AC → data parallel)
         tp_backend = "p2p" if (t.fused_comm and self.device.type == "cuda" and t.tp_size > 1) else "dist"
         self.tp_ctx = apply_tp(model, self.mesh, sequence_parallel=t.sequence_parallel, backend=tp_backend)
+        if t.ep_size > 1:
+            from ..parallel.ep import apply_ep
+
+            self.ep_ctx = apply_ep(model, self.mesh, t.ep_size)
         apply_ac(model, t.ac_mode)
         self.model = model
         self.optimizer = self.create_optimizer()
