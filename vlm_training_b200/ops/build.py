@@ -25,6 +25,7 @@ EXT_NAME = "_C"
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+NVCC_FLAGS += os.environ.get("VLMT_NVCC_EXTRA", "").split()  # e.g. -DVLMT_ATTN_TRACE for the in-kernel timeline dump
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wno-deprecated-declarations"]
 
 

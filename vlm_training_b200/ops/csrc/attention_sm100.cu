@@ -24,6 +24,10 @@
 #include <cuda_bf16.h>
 #include <math.h>
 
+#include <cstdio>
+#include <cstdlib>
+#include <type_traits>
+
 namespace {
 using namespace sm100;
 
@@ -162,13 +166,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(BM, D, false, true);
       // S_t(j) = Q_t K_j^T.  It overwrites P_t(j-1), whose consumer P_t(j-1).V was issued earlier by this thread.
+      const SmemDesc dQ0 = make_desc(smem_u32(smem + L::offQ), 16, 1024);
+      const SmemDesc dK0 = make_desc(smem_u32(smem + L::offK), 16, 1024);
+      const SmemDesc dV0 = make_desc(smem_u32(smem + L::offV), 16384, 1024);
       auto issue_S = [&](int t, int j) {
-        const uint32_t sQ = smem_u32(smem + L::offQ + t * L::kQ);
-        const uint32_t sK = smem_u32(smem + L::offK + (j & 1) * L::kKV);
+        const SmemDesc a = desc_off(dQ0, t * L::kQ), b = desc_off(dK0, (j & 1) * L::kKV);
+        const uint32_t d = tmem_base + S_COL + t * BN;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + S_COL + t * BN, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, kk != 0);
+          if (kk == 0) umma_ss<0>(d, a, b, idesc_s); else umma_ss<1>(d, desc_off(a, off), desc_off(b, off), idesc_s);
         }
         umma_commit(&s_full[t]);
       };
@@ -187,16 +194,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&v_full[s], ph, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
         if (j + 1 < J && !mbar_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
-        const uint32_t sV = smem_u32(smem + L::offV + s * L::kKV);
+        const SmemDesc dV = desc_off(dV0, s * L::kKV);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j >= Jt[t]) continue;
           if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
           tc_fence_after();
+          const uint32_t dO = tmem_base + O_COL + t * D, aP = tmem_base + S_COL + t * BN;
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk)  // A = P_t: 128 lanes x 8 columns of packed bf16 pairs per 16 keys
-            umma_bf16_ts(tmem_base + O_COL + t * D, tmem_base + S_COL + t * BN + kk * 8, make_smem_desc(sV + kk * 2048, 16384, 1024),
-                         idesc_pv, (j | kk) != 0);
+          for (int kk = 0; kk < BN / 16; ++kk) {  // A = P_t: 128 lanes x 8 columns of packed bf16 pairs per 16 keys
+            if (kk == 0) umma_ts<2>(dO, aP, dV, idesc_pv, (uint32_t)j); else umma_ts<1>(dO, aP + kk * 8, desc_off(dV, kk * 2048), idesc_pv);
+          }
           if (j + 1 < Jt[t]) issue_S(t, j + 1);
           else umma_commit(&o_done[t]);
         }
@@ -345,40 +353,51 @@ struct BwdParams {
   float scale, scale_log2;
   int causal;
   int* status;
+  long long* trace;  // timeline dump of CTA (0,0) (only with -DVLMT_ATTN_TRACE; nullptr otherwise)
 };
 
-// Backward tiles.  Both kernels keep a 128-row "stationary" tile (keys for dK/dV, queries for dQ) in shared memory and
-// stream 64-row tiles of the other operand through a 3-stage ring, so that S and dP take 64 TMEM columns each and are
-// double-buffered: the tensor core computes S/dP of step i+1 while the compute warps turn step i into P / dS, and the
-// accumulation MMAs of step i overlap the CUDA-core work of step i+1.  P / dS are written as packed bf16 over the
-// fp32 scores they came from and are read from tensor memory as the A operand.
-constexpr int BS = 64;   // rows of the streamed tile
-constexpr int NST = 3;   // stages of the streamed ring
+#ifdef VLMT_ATTN_TRACE
+#define TRACE(slot, j) do { if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && (j) < 256) p.trace[(j) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot, j) do { } while (0)
+#endif
+
+// Backward.  Measured on B200 (in-kernel clock64 timeline, build with -DVLMT_ATTN_TRACE): one tcgen05.mma of shape
+// 128 x N x 16 occupies the tensor core for about max(N / 2, 70) cycles whether its A operand comes from shared or from
+// tensor memory, so MMAs narrower than N = 128 waste the pipe.  Both kernels therefore work on 128 x 128 score tiles
+// (every MMA has N = 128 or N = D) and hide the CUDA-core work by splitting it in two phases per tile:
+//   phase a:  P  = exp2(S * scale - lse)          (special-function-unit bound: 16 ex2 per clock per SM)
+//   phase b:  dS = P * (dP - delta)               (needs dP, short)
+// so that the tensor core computes dP (and the accumulations of the previous tile) while phase a runs.  P / dS are
+// written as packed bf16 over the fp32 scores and are read from tensor memory as the A operand of the next MMA.
+constexpr int NCW = 8;       // compute warps; a thread owns one row of the 128-row tile and 64 of its 128 columns
+constexpr int CPT = 64;      // columns per thread
+
+// A-operand column of k-step kk (16 streamed rows) inside a 128-column buffer: the warps that own columns
+// [64 g, 64 g + 64) write their 64 values as 32 packed words at column 64 g, so no warp overwrites scores that the
+// other group has not read yet.
+__device__ __forceinline__ constexpr int packed_col(int kk) { return (kk >> 2) * 64 + (kk & 3) * 8; }
 
 template <int D>
 struct BwdSmem {
-  static constexpr int kBig = 128 * D * 2;     // stationary [128 x D] tile
-  static constexpr int kSmall = BS * D * 2;    // streamed [64 x D] tile
-  static constexpr int offA = 0;                        // dkdv: K_j   | dq: Q_i
-  static constexpr int offB = offA + kBig;              // dkdv: V_j   | dq: dO_i
-  static constexpr int offC = offB + kBig;              // NST stages: dkdv Q_i  | dq K_j
-  static constexpr int offD = offC + NST * kSmall;      // NST stages: dkdv dO_i | dq V_j
-  static constexpr int offStat = offD + NST * kSmall;   // per compute warp: lse2[32], delta[32] floats
-  static constexpr int offBar = offStat + 8 * 64 * 4;
+  static constexpr int kTile = 128 * D * 2;    // one [128 x D] tile
+  static constexpr int offA = 0;                     // dkdv: K_j   | dq: Q_i
+  static constexpr int offB = offA + kTile;          // dkdv: V_j   | dq: dO_i
+  static constexpr int offC = offB + kTile;          // 2 stages: dkdv Q_i  | dq K_j
+  static constexpr int offD = offC + 2 * kTile;      // 2 stages: dkdv dO_i | dq V_j
+  static constexpr int offStat = offD + 2 * kTile;   // per compute warp: -lse2[64], -delta[64] (dkdv only)
+  static constexpr int offBar = offStat + NCW * 128 * 4;
   static constexpr int kTotal = offBar + 256 + 1024;
 };
 
-// Column of the packed-bf16 A operand inside a 64-column fp32 buffer for k-step kk (16 rows of the streamed tile):
-// the warps of column half h write their 32 values as 16 packed words at column 32 h, so no warp overwrites scores
-// that the other half has not read yet.
-__device__ __forceinline__ constexpr int packed_col(int kk) { return (kk >> 1) * 32 + (kk & 1) * 8; }
-
-// dK_j, dV_j for one 128-key tile and one kv head.  Everything is computed transposed (rows = keys):
-//   S^T = K Q^T, dP^T = V dO^T  (M = 128 keys, N = 64 queries)   ->  P^T, dS^T (thread = key row, half of the queries)
-//   dV += P^T dO,  dK += dS^T Q  (A = [128 keys x 64 queries] from TMEM, B = the [64 x D] query-side tile read MN-major)
-// TMEM columns: S^T[2] 0/64, dP^T[2] 128/192, dV 256, dK 256 + D.
+// ------------------------------------------------------------------------------------------------ dK / dV
+// One CTA per 128-key tile and kv head; loops over 128-query tiles and the query heads of the GQA group.
+// Everything is computed transposed (rows = keys):
+//   S^T = K Q^T -> X,  dP^T = V dO^T -> Y        (M = 128 keys, N = 128 queries)
+//   dV += P^T dO (A = X),  dK += dS^T Q (A = Y)   (B = the [128 x D] query-side tile read MN-major)
+// TMEM columns: X 0, Y 128, dV 256, dK 256 + D.  Tensor-core order: dV(i), S^T(i+1), dK(i), dP^T(i+1).
 template <int D>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(64 + 32 * NCW, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
   using L = BwdSmem<D>;
@@ -388,12 +407,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
   uint64_t* kv_full = bars;          // 1
   uint64_t* acc_done = bars + 1;     // 1
-  uint64_t* qdo_full = bars + 2;     // NST
-  uint64_t* qdo_empty = bars + 5;    // NST
-  uint64_t* sdp_full = bars + 8;     // 2
-  uint64_t* pds_full = bars + 10;    // 2 (8 warps)
-  uint64_t* buf_free = bars + 12;    // 2: the accumulation MMAs that read P^T / dS^T of this buffer have finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* qdo_full = bars + 2;     // 2
+  uint64_t* qdo_empty = bars + 4;    // 2
+  uint64_t* s_full = bars + 6;       // S^T(i) is in X
+  uint64_t* dp_full = bars + 7;      // dP^T(i) is in Y
+  uint64_t* p_full = bars + 8;       // NCW warps: P^T(i) is in X
+  uint64_t* ds_full = bars + 9;      // NCW warps: dS^T(i) is in Y
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stat = reinterpret_cast<float*>(smem + L::offStat);
 
@@ -403,16 +423,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int hkv = blockIdx.y;
   const int group = p.Hq / p.Hkv;
   const int k0 = ti.q0;  // first key row of the tile (local to the document)
-  const int n_qblk = (ti.doc_len + BS - 1) / BS;
-  const int i_first = p.causal ? k0 / BS : 0;
+  const int n_qblk = (ti.doc_len + 127) / 128;
+  const int i_first = p.causal ? k0 / 128 : 0;
   const int n_iter = (n_qblk - i_first) * group;
   constexpr int TMEM_COLS = 512;
-  constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  constexpr int X_COL = 0, Y_COL = 128, DV_COL = 256, DK_COL = 256 + D;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(acc_done, 1);
-    for (int i = 0; i < NST; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&pds_full[i], 8); mbar_init(&buf_free[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    mbar_init(s_full, 1); mbar_init(dp_full, 1); mbar_init(p_full, NCW); mbar_init(ds_full, NCW);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -425,153 +445,189 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 0) {
     if (lane == 0) {
       const int krow = ti.doc_start + k0;
-      mbar_expect_tx(kv_full, 2 * L::kBig);
+      mbar_expect_tx(kv_full, 2 * L::kTile);
 #pragma unroll
       for (int b = 0; b < DB; ++b) {
         tma_load_2d(smem + L::offA + b * 16384, &tmK, kv_full, hkv * D + 64 * b, krow);
         tma_load_2d(smem + L::offB + b * 16384, &tmV, kv_full, hkv * D + 64 * b, krow);
       }
-      int sg = 0;
-      uint32_t ph = 1;
       for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1;
         const int i = i_first + it / group, hq = hkv * group + it % group;
-        if (!mbar_wait(&qdo_empty[sg], ph, abort_flag, p.status, kErrTimeoutEmpty)) break;
-        const int qrow = ti.doc_start + i * BS;
-        mbar_expect_tx(&qdo_full[sg], 2 * L::kSmall);
+        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        const int qrow = ti.doc_start + i * 128;
+        mbar_expect_tx(&qdo_full[st], 2 * L::kTile);
 #pragma unroll
         for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + sg * L::kSmall + b * 8192, &tmQ, &qdo_full[sg], hq * D + 64 * b, qrow);
-          tma_load_2d(smem + L::offD + sg * L::kSmall + b * 8192, &tmdO, &qdo_full[sg], hq * D + 64 * b, qrow);
+          tma_load_2d(smem + L::offC + st * L::kTile + b * 16384, &tmQ, &qdo_full[st], hq * D + 64 * b, qrow);
+          tma_load_2d(smem + L::offD + st * L::kTile + b * 16384, &tmdO, &qdo_full[st], hq * D + 64 * b, qrow);
         }
-        if (++sg == NST) { sg = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, BS, false, false);   // [128 keys] x [64 queries], contraction over d
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);      // [128 keys] x [D], contraction over 64 queries
-      const uint32_t sK = smem_u32(smem + L::offA), sV = smem_u32(smem + L::offB);
-      auto issue_sdp = [&](int it) -> bool {
-        const int sg = it % NST, b = it & 1;
-        if (!mbar_wait(&qdo_full[sg], (it / NST) & 1, abort_flag, p.status, kErrTimeoutFull)) return false;
-        if (!mbar_wait(&buf_free[b], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
-        tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + L::offC + sg * L::kSmall), sdO = smem_u32(smem + L::offD + sg * L::kSmall);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // [128 keys] x [128 queries], contraction over d
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);       // [128 keys] x [D], contraction over 128 queries
+      const SmemDesc dK = make_desc(smem_u32(smem + L::offA), 16, 1024), dV = make_desc(smem_u32(smem + L::offB), 16, 1024);
+      const SmemDesc dQk = make_desc(smem_u32(smem + L::offC), 16, 1024), dOk = make_desc(smem_u32(smem + L::offD), 16, 1024);         // K-major views
+      const SmemDesc dQm = make_desc(smem_u32(smem + L::offC), 16384, 1024), dOm = make_desc(smem_u32(smem + L::offD), 16384, 1024);   // MN-major views
+      const uint32_t tX = tmem_base + X_COL, tY = tmem_base + Y_COL;
+      auto issue_score = [&](uint32_t dst, SmemDesc a, SmemDesc bq) {  // dst = a (stationary) x bq^T (streamed), both K-major
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32, offq = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + ST_COL + b * BS, make_smem_desc(sK + offk, 16, 1024), make_smem_desc(sQ + offq, 16, 1024), idesc_s, kk != 0);
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          if (kk == 0) umma_ss<0>(dst, a, bq, idesc_s); else umma_ss<1>(dst, desc_off(a, off), desc_off(bq, off), idesc_s);
         }
+      };
+      auto issue_acc = [&](uint32_t dst, uint32_t a_tmem, SmemDesc bm, uint32_t acc) {  // dst += a_tmem [128 x 128] x bm [128 x D]
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32, offq = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + DPT_COL + b * BS, make_smem_desc(sV + offk, 16, 1024), make_smem_desc(sdO + offq, 16, 1024), idesc_s, kk != 0);
+        for (int kk = 0; kk < 8; ++kk) {
+          if (kk == 0) umma_ts<2>(dst, a_tmem, bm, idesc_g, acc); else umma_ts<1>(dst, a_tmem + packed_col(kk), desc_off(bm, kk * 2048), idesc_g);
         }
-        umma_commit(&sdp_full[b]);
-        return true;
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kErrTimeoutFull);
-      if (ok && n_iter > 0) ok = issue_sdp(0);
+      if (ok && n_iter > 0) {
+        ok = mbar_wait(&qdo_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
+        if (ok) {
+          tc_fence_after();
+          issue_score(tX, dK, dQk);
+          umma_commit(s_full);
+          issue_score(tY, dV, dOk);
+          umma_commit(dp_full);
+        }
+      }
       for (int it = 0; it < n_iter && ok; ++it) {
-        if (it + 1 < n_iter) { ok = issue_sdp(it + 1); if (!ok) break; }
-        const int sg = it % NST, b = it & 1;
-        if (!mbar_wait(&pds_full[b], (it >> 1) & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+        const int st = it & 1, nx = st ^ 1;
+        const bool more = it + 1 < n_iter;
+        if (!mbar_wait(p_full, it & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sQ = smem_u32(smem + L::offC + sg * L::kSmall), sdO = smem_u32(smem + L::offD + sg * L::kSmall);
-#pragma unroll
-        for (int kk = 0; kk < BS / 16; ++kk)
-          umma_bf16_ts(tmem_base + DV_COL, tmem_base + ST_COL + b * BS + packed_col(kk), make_smem_desc(sdO + kk * 2048, 8192, 1024), idesc_g,
-                       (it | kk) != 0);
-#pragma unroll
-        for (int kk = 0; kk < BS / 16; ++kk)
-          umma_bf16_ts(tmem_base + DK_COL, tmem_base + DPT_COL + b * BS + packed_col(kk), make_smem_desc(sQ + kk * 2048, 8192, 1024), idesc_g,
-                       (it | kk) != 0);
-        umma_commit(&qdo_empty[sg]);
-        umma_commit(&buf_free[b]);
+        issue_acc(tmem_base + DV_COL, tX, desc_off(dOm, st * L::kTile), (uint32_t)it);
+        if (more) {
+          if (!mbar_wait(&qdo_full[nx], ((it + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          issue_score(tX, dK, desc_off(dQk, nx * L::kTile));   // runs after dV(it), which read X
+          umma_commit(s_full);
+        }
+        if (!mbar_wait(ds_full, it & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+        tc_fence_after();
+        issue_acc(tmem_base + DK_COL, tY, desc_off(dQm, st * L::kTile), (uint32_t)it);
+        umma_commit(&qdo_empty[st]);
+        if (more) {
+          issue_score(tY, dV, desc_off(dOk, nx * L::kTile));   // runs after dK(it), which read Y
+          umma_commit(dp_full);
+        }
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
     const int cw = warp - 2;
-    const int ch = cw >> 2;                // column half: queries [32 ch, 32 ch + 32) of the streamed tile
+    const int cq = cw >> 2;                // column group: queries [64 cq, 64 cq + 64) of the streamed tile
     const int q = warp & 3;                // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;           // key row of the tile owned by this thread
     const int kvi = k0 + r;                // key index local to the document
     const bool key_ok = kvi < ti.doc_len;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float* wstat = stat + cw * 64;
-    // per-query statistics: lane l fetches those of query 32 ch + l one step ahead
-    auto fetch = [&](int it, float& l2, float& dl) {
+    const uint32_t tX = tmem_base + X_COL + cq * CPT + lane_addr, tY = tmem_base + Y_COL + cq * CPT + lane_addr;
+    float* wstat = stat + cw * 128;
+    // per-query statistics: lane l fetches those of queries 64 cq + l and 64 cq + 32 + l one step ahead
+    auto fetch = [&](int it, float (&v)[4]) {
       const int i = i_first + it / group, hq = hkv * group + it % group;
-      const int qq = i * BS + ch * 32 + lane;
-      const bool qok = qq < ti.doc_len;
-      const size_t idx = (size_t)hq * p.T + ti.doc_start + (qok ? qq : 0);
-      l2 = qok ? p.LSE[idx] * kLog2e : INFINITY;  // +inf -> exp2(-inf) = 0 for queries beyond the document
-      dl = qok ? p.delta[idx] : 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qq = i * 128 + cq * CPT + h * 32 + lane;
+        const bool qok = qq < ti.doc_len;
+        const size_t idx = (size_t)hq * p.T + ti.doc_start + (qok ? qq : 0);
+        v[h] = qok ? -p.LSE[idx] * kLog2e : -INFINITY;  // -inf -> exp2(-inf) = 0 for queries beyond the document
+        v[2 + h] = qok ? -p.delta[idx] : 0.f;
+      }
     };
-    float nl2 = 0.f, ndl = 0.f;
-    if (n_iter > 0) fetch(0, nl2, ndl);
+    float nxt[4] = {0.f, 0.f, 0.f, 0.f};
+    if (n_iter > 0) fetch(0, nxt);
+    const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int b = it & 1;
-      const int q0 = (i_first + it / group) * BS + ch * 32;   // first query of this thread's columns
+      const int q0 = (i_first + it / group) * 128 + cq * CPT;   // first query of this thread's columns
       __syncwarp();
-      wstat[lane] = nl2;
-      wstat[32 + lane] = ndl;
+      wstat[lane] = nxt[0]; wstat[32 + lane] = nxt[1]; wstat[64 + lane] = nxt[2]; wstat[96 + lane] = nxt[3];
       __syncwarp();
-      if (it + 1 < n_iter) fetch(it + 1, nl2, ndl);
-      if (!mbar_wait(&sdp_full[b], (it >> 1) & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      if (it + 1 < n_iter) fetch(it + 1, nxt);
+      // ---- phase a: P^T = exp2(S^T * scale - lse)
+      if (!mbar_wait(s_full, it & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sr[32], dr[32];
-      tmem_ld_32x32(tmem_base + ST_COL + b * BS + ch * 32 + lane_addr, sr);
-      tmem_ld_32x32(tmem_base + DPT_COL + b * BS + ch * 32 + lane_addr, dr);
-      tmem_ld_wait();
-      // masked: keys beyond the document, or (causal) keys after the query
+      // masked: keys beyond the document, or (causal) keys after the query.  Column c is visible iff c >= cmin.
       const bool need_mask = (k0 + 128 > ti.doc_len) || (p.causal && k0 + 127 > q0);
-      uint32_t pp[16], dd[16];
+      const int cmin = !key_ok ? (1 << 30) : (p.causal ? kvi - q0 : -(1 << 30));
+      float pr[CPT];
 #pragma unroll
-      for (int u4 = 0; u4 < 8; ++u4) {
-        const float4 l4 = reinterpret_cast<const float4*>(wstat)[u4];
-        const float4 d4 = reinterpret_cast<const float4*>(wstat + 32)[u4];
-        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dls[4] = {d4.x, d4.y, d4.z, d4.w};
-        float pv[4], dsv[4];
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sr[32];
+        tmem_ld_32x32(tX + c * 32, sr);
+        tmem_ld_wait();
+        auto body = [&](auto masked) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int u = u4 * 4 + e;
-          float x = fmaf(__uint_as_float(sr[u]), p.scale_log2, -ls[e]);
-          if (need_mask && !(key_ok && (!p.causal || kvi <= q0 + u))) x = -INFINITY;
-          pv[e] = ex2_approx(x);
-          dsv[e] = pv[e] * (__uint_as_float(dr[u]) - dls[e]);
-        }
-        pp[u4 * 2] = pack_bf16x2(pv[0], pv[1]);  pp[u4 * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
-        dd[u4 * 2] = pack_bf16x2(dsv[0], dsv[1]); dd[u4 * 2 + 1] = pack_bf16x2(dsv[2], dsv[3]);
+          for (int u = 0; u < 32; u += 2) {
+            const float2 l2 = *reinterpret_cast<const float2*>(wstat + c * 32 + u);
+            float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[u]), __uint_as_float(sr[u + 1])), sc2, l2);
+            if (decltype(masked)::value) {
+              if (c * 32 + u < cmin) x.x = -INFINITY;
+              if (c * 32 + u + 1 < cmin) x.y = -INFINITY;
+            }
+            pr[c * 32 + u] = ex2_approx(x.x);
+            pr[c * 32 + u + 1] = ex2_approx(x.y);
+          }
+        };
+        if (need_mask) body(std::true_type{}); else body(std::false_type{});
+        uint32_t pk[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) pk[u] = pack_bf16x2(pr[c * 32 + 2 * u], pr[c * 32 + 2 * u + 1]);
+        tmem_st_32x16(tX + c * 16, pk);   // packed P^T over this thread's own columns
       }
-      tmem_st_32x16(tmem_base + ST_COL + b * BS + ch * 32 + lane_addr, pp);
-      tmem_st_32x16(tmem_base + DPT_COL + b * BS + ch * 32 + lane_addr, dd);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&pds_full[b]);
+      if (lane == 0) mbar_arrive(p_full);
+      // ---- phase b: dS^T = P^T * (dP^T - delta)
+      if (!mbar_wait(dp_full, it & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dr[32];
+        tmem_ld_32x32(tY + c * 32, dr);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int u = 0; u < 32; u += 2) {
+          const float2 d2 = *reinterpret_cast<const float2*>(wstat + 64 + c * 32 + u);
+          const float2 ds = __fmul2_rn(make_float2(pr[c * 32 + u], pr[c * 32 + u + 1]),
+                                       __fadd2_rn(make_float2(__uint_as_float(dr[u]), __uint_as_float(dr[u + 1])), d2));
+          pk[u >> 1] = pack_bf16x2(ds.x, ds.y);
+        }
+        tmem_st_32x16(tY + c * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
     }
-    // epilogue: thread (r, ch) owns channels [ch D/2, (ch+1) D/2) of key row k0 + r of dV and dK (dK carries the softmax scale)
+    // epilogue: thread (r, cq) owns D / 2 channels of key row k0 + r of dV and dK (dK carries the softmax scale)
     if (ok && mbar_wait(acc_done, 0, abort_flag, p.status, kErrTimeoutTmemFull)) {
       tc_fence_after();
       if (n_iter > 0) {
+        constexpr int CH = D / 2;
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           __nv_bfloat16* base = which == 0 ? p.dV : p.dK;
           const int col = which == 0 ? DV_COL : DK_COL;
           const float f = which == 0 ? 1.f : p.scale;
 #pragma unroll 1
-          for (int c = 0; c < D / 64; ++c) {
-            const int c0 = ch * (D / 2) + c * 32;
-            uint32_t rr[32];
-            tmem_ld_32x32(tmem_base + col + lane_addr + c0, rr);
+          for (int c = 0; c < CH / 16; ++c) {
+            const int c0 = cq * CH + c * 16;
+            uint32_t rr[16];
+            tmem_ld_32x16(tmem_base + col + lane_addr + c0, rr);
             tmem_ld_wait();
             if (key_ok) {
               __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * D + c0;
 #pragma unroll
-              for (int t = 0; t < 4; ++t) {
+              for (int t = 0; t < 2; ++t) {
                 uint4 pk;
                 pk.x = pack_bf16x2(__uint_as_float(rr[t * 8 + 0]) * f, __uint_as_float(rr[t * 8 + 1]) * f);
                 pk.y = pack_bf16x2(__uint_as_float(rr[t * 8 + 2]) * f, __uint_as_float(rr[t * 8 + 3]) * f);
@@ -599,9 +655,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
 }
 
-// dQ_i for one 128-query tile and head, streaming 64-key tiles.  TMEM: S[2] 0/64, dP[2] 128/192, dQ 256.
+// ------------------------------------------------------------------------------------------------ dQ
+// One CTA per 128-query tile and head, streaming 128-key tiles.
+// TMEM: S[2] 0/128 (double-buffered, so phase a of step j+1 can start while step j finishes), dP 256, dQ 384.
+// Tensor-core order: S(j+1), dQ(j), dP(j+1).
 template <int D>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(64 + 32 * NCW, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
   using L = BwdSmem<D>;
@@ -611,12 +670,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
   uint64_t* qdo_full = bars;         // 1
   uint64_t* acc_done = bars + 1;     // 1
-  uint64_t* kv_full = bars + 2;      // NST
-  uint64_t* kv_empty = bars + 5;     // NST
-  uint64_t* sdp_full = bars + 8;     // 2
-  uint64_t* ds_full = bars + 10;     // 2 (8 warps)
-  uint64_t* buf_free = bars + 12;    // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* kv_full = bars + 2;      // 2
+  uint64_t* kv_empty = bars + 4;     // 2
+  uint64_t* s_full = bars + 6;       // 2
+  uint64_t* s_free = bars + 8;       // 2 (NCW warps): the scores of this buffer are in registers
+  uint64_t* dp_full = bars + 10;     // 1
+  uint64_t* ds_full = bars + 11;     // 1 (NCW warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -625,14 +685,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int hq = blockIdx.y;
   const int hkv = hq / (p.Hq / p.Hkv);
   const int kv_end = p.causal ? min(ti.doc_len, ti.q0 + BM) : ti.doc_len;
-  const int J = (kv_end + BS - 1) / BS;
+  const int J = (kv_end + BN - 1) / BN;
   constexpr int TMEM_COLS = 512;
-  constexpr int S_COL = 0, DP_COL = 128, DQ_COL = 256;
+  constexpr int S_COL = 0, DP_COL = 256, DQ_COL = 384;
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1); mbar_init(acc_done, 1);
-    for (int i = 0; i < NST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&ds_full[i], 8); mbar_init(&buf_free[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); mbar_init(&s_free[i], NCW);
+    }
+    mbar_init(dp_full, 1); mbar_init(ds_full, NCW);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -645,69 +707,81 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       const int qrow = ti.doc_start + ti.q0;
-      mbar_expect_tx(qdo_full, 2 * L::kBig);
+      mbar_expect_tx(qdo_full, 2 * L::kTile);
 #pragma unroll
       for (int b = 0; b < DB; ++b) {
         tma_load_2d(smem + L::offA + b * 16384, &tmQ, qdo_full, hq * D + 64 * b, qrow);
         tma_load_2d(smem + L::offB + b * 16384, &tmdO, qdo_full, hq * D + 64 * b, qrow);
       }
-      int sg = 0;
-      uint32_t ph = 1;
       for (int j = 0; j < J; ++j) {
-        if (!mbar_wait(&kv_empty[sg], ph, abort_flag, p.status, kErrTimeoutEmpty)) break;
-        const int krow = ti.doc_start + j * BS;
-        mbar_expect_tx(&kv_full[sg], 2 * L::kSmall);
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        const int krow = ti.doc_start + j * BN;
+        mbar_expect_tx(&kv_full[st], 2 * L::kTile);
 #pragma unroll
         for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + sg * L::kSmall + b * 8192, &tmK, &kv_full[sg], hkv * D + 64 * b, krow);
-          tma_load_2d(smem + L::offD + sg * L::kSmall + b * 8192, &tmV, &kv_full[sg], hkv * D + 64 * b, krow);
+          tma_load_2d(smem + L::offC + st * L::kTile + b * 16384, &tmK, &kv_full[st], hkv * D + 64 * b, krow);
+          tma_load_2d(smem + L::offD + st * L::kTile + b * 16384, &tmV, &kv_full[st], hkv * D + 64 * b, krow);
         }
-        if (++sg == NST) { sg = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, BS, false, false);
-      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, false, true);  // dQ = dS K: A [128 q x 64 kv] from TMEM, B = K_j [64 kv x D] MN-major
-      const uint32_t sQ = smem_u32(smem + L::offA), sdO = smem_u32(smem + L::offB);
-      auto issue_sdp = [&](int j) -> bool {
-        const int sg = j % NST, b = j & 1;
-        if (!mbar_wait(&kv_full[sg], (j / NST) & 1, abort_flag, p.status, kErrTimeoutFull)) return false;
-        if (!mbar_wait(&buf_free[b], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) return false;
-        tc_fence_after();
-        const uint32_t sK = smem_u32(smem + L::offC + sg * L::kSmall), sV = smem_u32(smem + L::offD + sg * L::kSmall);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, false, true);  // dQ = dS K: A [128 q x 128 kv] from TMEM, B = K_j [128 kv x D] MN-major
+      const SmemDesc dQ = make_desc(smem_u32(smem + L::offA), 16, 1024), dO = make_desc(smem_u32(smem + L::offB), 16, 1024);
+      const SmemDesc dKk = make_desc(smem_u32(smem + L::offC), 16, 1024), dVk = make_desc(smem_u32(smem + L::offD), 16, 1024);   // K-major views
+      const SmemDesc dKm = make_desc(smem_u32(smem + L::offC), 16384, 1024);                                                     // MN-major view
+      auto issue_score = [&](uint32_t dst, SmemDesc a, SmemDesc bk) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offq = (kk >> 2) * 16384 + (kk & 3) * 32, offk = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + S_COL + b * BS, make_smem_desc(sQ + offq, 16, 1024), make_smem_desc(sK + offk, 16, 1024), idesc_s, kk != 0);
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          if (kk == 0) umma_ss<0>(dst, a, bk, idesc_s); else umma_ss<1>(dst, desc_off(a, off), desc_off(bk, off), idesc_s);
         }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offq = (kk >> 2) * 16384 + (kk & 3) * 32, offk = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + DP_COL + b * BS, make_smem_desc(sdO + offq, 16, 1024), make_smem_desc(sV + offk, 16, 1024), idesc_s, kk != 0);
-        }
-        umma_commit(&sdp_full[b]);
-        return true;
       };
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, kErrTimeoutFull);
-      if (ok && J > 0) ok = issue_sdp(0);
+      if (ok && J > 0) {
+        ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
+        if (ok) {
+          tc_fence_after();
+          issue_score(tmem_base + S_COL, dQ, dKk);
+          umma_commit(&s_full[0]);
+          issue_score(tmem_base + DP_COL, dO, dVk);
+          umma_commit(dp_full);
+        }
+      }
       for (int j = 0; j < J && ok; ++j) {
-        if (j + 1 < J) { ok = issue_sdp(j + 1); if (!ok) break; }
-        const int sg = j % NST, b = j & 1;
-        if (!mbar_wait(&ds_full[b], (j >> 1) & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+        TRACE(0, j);
+        const int st = j & 1, nx = st ^ 1;
+        const bool more = j + 1 < J;
+        if (more) {
+          if (!mbar_wait(&kv_full[nx], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          if (!mbar_wait(&s_free[nx], (((j + 1) >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) { ok = false; break; }
+          tc_fence_after();
+          issue_score(tmem_base + S_COL + nx * BN, dQ, desc_off(dKk, nx * L::kTile));
+          umma_commit(&s_full[nx]);
+        }
+        TRACE(1, j);
+        if (!mbar_wait(ds_full, j & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
+        TRACE(2, j);
         tc_fence_after();
-        const uint32_t sK = smem_u32(smem + L::offC + sg * L::kSmall);
+        const SmemDesc k = desc_off(dKm, st * L::kTile);
 #pragma unroll
-        for (int kk = 0; kk < BS / 16; ++kk)
-          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + DP_COL + b * BS + packed_col(kk), make_smem_desc(sK + kk * 2048, 8192, 1024), idesc_q,
-                       (j | kk) != 0);
-        umma_commit(&kv_empty[sg]);
-        umma_commit(&buf_free[b]);
+        for (int kk = 0; kk < 8; ++kk) {
+          if (kk == 0) umma_ts<2>(tmem_base + DQ_COL, tmem_base + DP_COL, k, idesc_q, (uint32_t)j);
+          else umma_ts<1>(tmem_base + DQ_COL, tmem_base + DP_COL + packed_col(kk), desc_off(k, kk * 2048), idesc_q);
+        }
+        umma_commit(&kv_empty[st]);
+        if (more) {
+          issue_score(tmem_base + DP_COL, dO, desc_off(dVk, nx * L::kTile));   // runs after dQ(j), which read the dP buffer
+          umma_commit(dp_full);
+        }
+        TRACE(3, j);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
-    const int ch = (warp - 2) >> 2;        // column half: keys [32 ch, 32 ch + 32) of the streamed tile
+    const int cq = (warp - 2) >> 2;        // column group: keys [64 cq, 64 cq + 64) of the streamed tile
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
@@ -715,51 +789,83 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const bool row_ok = qi < ti.doc_len;
     const size_t tok = (size_t)ti.doc_start + (row_ok ? qi : 0);
     const float neg_lse2 = row_ok ? -p.LSE[(size_t)hq * p.T + tok] * kLog2e : 0.f;
-    const float dl = row_ok ? p.delta[(size_t)hq * p.T + tok] : 0.f;
+    const float neg_dl = row_ok ? -p.delta[(size_t)hq * p.T + tok] : 0.f;
+    const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(neg_lse2, neg_lse2), nd2 = make_float2(neg_dl, neg_dl);
+    // last visible key (local index) of this row; -1 for rows beyond the document
+    const int last = !row_ok ? -1 : (p.causal ? min(ti.doc_len - 1, qi) : ti.doc_len - 1);
+    const uint32_t tDP = tmem_base + DP_COL + cq * CPT + lane_addr;
     bool ok = true;
     for (int j = 0; j < J && ok; ++j) {
       const int b = j & 1;
-      if (!mbar_wait(&sdp_full[b], (j >> 1) & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      // ---- phase a: P = exp2(S * scale - lse), kept in registers
+      if (threadIdx.x == 64) TRACE(8, j);
+      if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      if (threadIdx.x == 64) TRACE(9, j);
       tc_fence_after();
-      uint32_t sr[32], dr[32];
-      tmem_ld_32x32(tmem_base + S_COL + b * BS + ch * 32 + lane_addr, sr);
-      tmem_ld_32x32(tmem_base + DP_COL + b * BS + ch * 32 + lane_addr, dr);
+      const bool need_mask = (j * BN + BN > ti.doc_len) || (ti.q0 + BM > ti.doc_len) || (p.causal && j * BN + BN - 1 > ti.q0);
+      const int umax = last - (j * BN + cq * CPT);   // columns u <= umax are visible
+      float pr[CPT];
+      uint32_t sr[CPT];
+      tmem_ld_32x32(tmem_base + S_COL + b * BN + cq * CPT + lane_addr, as32(&sr[0]));
+      tmem_ld_32x32(tmem_base + S_COL + b * BN + cq * CPT + 32 + lane_addr, as32(&sr[32]));
       tmem_ld_wait();
-      const int kv0 = j * BS + ch * 32;
-      const bool need_mask = (j * BS + BS > ti.doc_len) || (ti.q0 + BM > ti.doc_len) || (p.causal && j * BS + BS - 1 > ti.q0);
-      uint32_t dd[16];
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[b]);
+      if (threadIdx.x == 64) TRACE(10, j);
+      auto body = [&](auto masked) {
 #pragma unroll
-      for (int u2 = 0; u2 < 16; ++u2) {
-        float dsv[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int u = u2 * 2 + e;
-          float x = fmaf(__uint_as_float(sr[u]), p.scale_log2, neg_lse2);
-          if (need_mask && !(row_ok && kv0 + u < ti.doc_len && (!p.causal || kv0 + u <= qi))) x = -INFINITY;
-          dsv[e] = ex2_approx(x) * (__uint_as_float(dr[u]) - dl);
+        for (int u = 0; u < CPT; u += 2) {
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[u]), __uint_as_float(sr[u + 1])), sc2, nl2);
+          if (decltype(masked)::value) {
+            if (u > umax) x.x = -INFINITY;
+            if (u + 1 > umax) x.y = -INFINITY;
+          }
+          pr[u] = ex2_approx(x.x);
+          pr[u + 1] = ex2_approx(x.y);
         }
-        dd[u2] = pack_bf16x2(dsv[0], dsv[1]);
+      };
+      if (need_mask) body(std::true_type{}); else body(std::false_type{});
+      if (threadIdx.x == 64) TRACE(11, j);
+      // ---- phase b: dS = P * (dP - delta)
+      if (!mbar_wait(dp_full, j & 1, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      if (threadIdx.x == 64) TRACE(12, j);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dr[32];
+        tmem_ld_32x32(tDP + c * 32, dr);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int u = 0; u < 32; u += 2) {
+          const float2 ds = __fmul2_rn(make_float2(pr[c * 32 + u], pr[c * 32 + u + 1]),
+                                       __fadd2_rn(make_float2(__uint_as_float(dr[u]), __uint_as_float(dr[u + 1])), nd2));
+          pk[u >> 1] = pack_bf16x2(ds.x, ds.y);
+        }
+        tmem_st_32x16(tDP + c * 16, pk);   // packed dS over this thread's own (already read) columns
       }
-      tmem_st_32x16(tmem_base + DP_COL + b * BS + ch * 32 + lane_addr, dd);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_full[b]);
+      if (lane == 0) mbar_arrive(ds_full);
+      if (threadIdx.x == 64) TRACE(13, j);
     }
-    // epilogue: thread (r, ch) owns channels [ch D/2, (ch+1) D/2) of query row q0 + r (dQ carries the softmax scale)
+    // epilogue: thread (r, cq) owns D / 2 channels of query row q0 + r (dQ carries the softmax scale)
     if (ok && mbar_wait(acc_done, 0, abort_flag, p.status, kErrTimeoutTmemFull)) {
       tc_fence_after();
+      constexpr int CH = D / 2;
 #pragma unroll 1
-      for (int c = 0; c < D / 64; ++c) {
-        const int c0 = ch * (D / 2) + c * 32;
-        uint32_t rr[32];
-        tmem_ld_32x32(tmem_base + DQ_COL + lane_addr + c0, rr);
+      for (int c = 0; c < CH / 16; ++c) {
+        const int c0 = cq * CH + c * 16;
+        uint32_t rr[16];
+        tmem_ld_32x16(tmem_base + DQ_COL + lane_addr + c0, rr);
         tmem_ld_wait();
         if (row_ok && J > 0) {
           __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * D + c0;
           const float f = p.scale;
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
+          for (int t = 0; t < 2; ++t) {
             uint4 pk;
             pk.x = pack_bf16x2(__uint_as_float(rr[t * 8 + 0]) * f, __uint_as_float(rr[t * 8 + 1]) * f);
             pk.y = pack_bf16x2(__uint_as_float(rr[t * 8 + 2]) * f, __uint_as_float(rr[t * 8 + 3]) * f);
@@ -831,35 +937,55 @@ extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, con
     attn_delta_kernel<<<(warps * 32 + 255) / 256, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
                                                                 reinterpret_cast<const __nv_bfloat16*>(o), delta, T, Hq, D);
   }
-  // 128-row boxes for the stationary tiles, 64-row boxes for the streamed ones
-  CUtensorMap tq, tk, tv, tdo, tq64, tk64, tv64, tdo64;
+  CUtensorMap tq, tk, tv, tdo;
   int r;
   if ((r = make_act_tmap(&tq, q, T, Hq * D, (long)Hq * D))) return 1000 + r;
   if ((r = make_act_tmap(&tk, k, T, Hkv * D, (long)Hkv * D))) return 2000 + r;
   if ((r = make_act_tmap(&tv, v, T, Hkv * D, (long)Hkv * D))) return 3000 + r;
   if ((r = make_act_tmap(&tdo, dout, T, Hq * D, (long)Hq * D))) return 4000 + r;
-  if ((r = make_act_tmap(&tq64, q, T, Hq * D, (long)Hq * D, 64))) return 5000 + r;
-  if ((r = make_act_tmap(&tk64, k, T, Hkv * D, (long)Hkv * D, 64))) return 6000 + r;
-  if ((r = make_act_tmap(&tv64, v, T, Hkv * D, (long)Hkv * D, 64))) return 7000 + r;
-  if ((r = make_act_tmap(&tdo64, dout, T, Hq * D, (long)Hq * D, 64))) return 8000 + r;
   BwdParams p;
   p.dQ = reinterpret_cast<__nv_bfloat16*>(dq); p.dK = reinterpret_cast<__nv_bfloat16*>(dk); p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   p.LSE = lse; p.delta = delta; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
+  p.trace = nullptr;
   (void)d_eff;
+#ifdef VLMT_ATTN_TRACE
+  static long long* trace_buf = nullptr;
+  if (!trace_buf) cudaMalloc(&trace_buf, 256 * 16 * sizeof(long long));
+  cudaMemset(trace_buf, 0, 256 * 16 * sizeof(long long));
+  p.trace = trace_buf;
+#endif
   dim3 grid_kv(T / BN + n_docs + 1, Hkv), grid_q(T / BM + n_docs + 1, Hq);
-  if (D == 128) {
-    if ((r = set_smem(attn_bwd_dkdv_kernel<128>, BwdSmem<128>::kTotal))) return r;
-    if ((r = set_smem(attn_bwd_dq_kernel<128>, BwdSmem<128>::kTotal))) return r;
-    attn_bwd_dkdv_kernel<128><<<grid_kv, ATT_THREADS, BwdSmem<128>::kTotal, st>>>(tq64, tk, tv, tdo64, p);
-    attn_bwd_dq_kernel<128><<<grid_q, ATT_THREADS, BwdSmem<128>::kTotal, st>>>(tq, tk64, tv64, tdo, p);
-  } else if (D == 64) {
-    if ((r = set_smem(attn_bwd_dkdv_kernel<64>, BwdSmem<64>::kTotal))) return r;
-    if ((r = set_smem(attn_bwd_dq_kernel<64>, BwdSmem<64>::kTotal))) return r;
-    attn_bwd_dkdv_kernel<64><<<grid_kv, ATT_THREADS, BwdSmem<64>::kTotal, st>>>(tq64, tk, tv, tdo64, p);
-    attn_bwd_dq_kernel<64><<<grid_q, ATT_THREADS, BwdSmem<64>::kTotal, st>>>(tq, tk64, tv64, tdo, p);
-  } else {
-    return -10;
+  auto launch = [&](auto dtag) -> int {
+    constexpr int Dh = decltype(dtag)::value;
+    int rr;
+    if ((rr = set_smem(attn_bwd_dkdv_kernel<Dh>, BwdSmem<Dh>::kTotal))) return rr;
+    if ((rr = set_smem(attn_bwd_dq_kernel<Dh>, BwdSmem<Dh>::kTotal))) return rr;
+    attn_bwd_dkdv_kernel<Dh><<<grid_kv, 64 + 32 * NCW, BwdSmem<Dh>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_dq_kernel<Dh><<<grid_q, 64 + 32 * NCW, BwdSmem<Dh>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    return 0;
+  };
+  if (D == 128) r = launch(std::integral_constant<int, 128>{});
+  else if (D == 64) r = launch(std::integral_constant<int, 64>{});
+  else return -10;
+  if (r) return r;
+#ifdef VLMT_ATTN_TRACE
+  {
+    static int dumps = 0;
+    cudaStreamSynchronize(st);
+    static long long host[256 * 16];
+    cudaMemcpy(host, p.trace, sizeof(host), cudaMemcpyDeviceToHost);
+    if (dumps++ == 2) {
+      const long long t0 = host[0];
+      for (int j = 0; j < 256 && host[j * 16]; ++j) {
+        fprintf(stderr, "TRACE j=%d mma:", j);
+        for (int k = 0; k < 4; ++k) fprintf(stderr, " %lld", host[j * 16 + k] - t0);
+        fprintf(stderr, " | cw:");
+        for (int k = 8; k < 14; ++k) fprintf(stderr, " %lld", host[j * 16 + k] - t0);
+        fprintf(stderr, "\n");
+      }
+    }
   }
+#endif
   return (int)cudaGetLastError();
 }

@@ -163,6 +163,21 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+// N consecutive 32-bit columns of this thread's TMEM lane
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(N == 16 || N == 32, "16 or 32 columns");
+  if constexpr (N == 32) tmem_ld_32x32(taddr, r); else tmem_ld_32x16(taddr, r);
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[N]) {
+  static_assert(N == 8 || N == 16, "8 or 16 columns");
+  if constexpr (N == 16) tmem_st_32x16(taddr, r); else tmem_st_32x8(taddr, r);
+}
 // 2^x on the special-function unit (denormal results flush to zero; -inf gives 0)
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -196,6 +211,47 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- lean MMA issue
+// The thread that issues the MMAs is a single instruction stream: with small tiles (N = 64 or 128) one MMA is only
+// 32-64 tensor-pipe cycles, so every extra instruction per MMA shows up as an idle tensor pipe.  These helpers keep
+// the descriptor as two 32-bit halves (advancing it is one 32-bit add on the address field) and take the accumulate
+// flag as a compile-time constant where it is one.
+struct SmemDesc { uint32_t lo, hi; };
+__device__ __forceinline__ SmemDesc make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  SmemDesc d;
+  d.lo = ((smem_addr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+  d.hi = ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);  // version 1 (bit 46), 128-byte swizzle (bits 61-63)
+  return d;
+}
+__device__ __forceinline__ SmemDesc desc_off(SmemDesc d, uint32_t bytes) { d.lo += bytes >> 4; return d; }
+
+// ACC: 0 = overwrite D, 1 = accumulate into D, 2 = `flag` decides at run time
+template <int ACC>
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, SmemDesc a, SmemDesc b, uint32_t idesc, uint32_t flag = 0) {
+  if constexpr (ACC == 2) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+                 ::"r"(tmem_d), "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(flag) : "memory");
+  } else {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+                 ::"r"(tmem_d), "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi), "r"(idesc), "n"(ACC) : "memory");
+  }
+}
+// A operand from tensor memory
+template <int ACC>
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, SmemDesc b, uint32_t idesc, uint32_t flag = 0) {
+  if constexpr (ACC == 2) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(flag) : "memory");
+  } else {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "r"(b.lo), "r"(b.hi), "r"(idesc), "n"(ACC) : "memory");
+  }
 }
 
 }  // namespace sm100
