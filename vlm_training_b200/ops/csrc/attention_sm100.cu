@@ -241,9 +241,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < BN; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(s[i]));     mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      for (int i = 0; i < BN; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // the scale is positive: it commutes with max
       if (j == 0) {
@@ -378,17 +380,30 @@ constexpr int CPT = 64;      // columns per thread
 // other group has not read yet.
 __device__ __forceinline__ constexpr int packed_col(int kk) { return (kk >> 2) * 64 + (kk & 3) * 8; }
 
+// Shared memory: two stationary [128 x D] tiles and two TMA rings for the streamed tiles.  The ring whose tiles are
+// needed until the END of a step (Q for dK, K for dQ) has three stages, the other (dO / V, free after the first half of
+// the step) two: a load is then issued about one whole step before its first use, which hides the TMA latency
+// (about 1600 cycles for a 32 KB tile; with two stages each the tensor core idled on the loads).
 template <int D>
 struct BwdSmem {
   static constexpr int kTile = 128 * D * 2;    // one [128 x D] tile
   static constexpr int offA = 0;                     // dkdv: K_j   | dq: Q_i
   static constexpr int offB = offA + kTile;          // dkdv: V_j   | dq: dO_i
-  static constexpr int offC = offB + kTile;          // 2 stages: dkdv Q_i  | dq K_j
-  static constexpr int offD = offC + 2 * kTile;      // 2 stages: dkdv dO_i | dq V_j
-  static constexpr int offStat = offD + 2 * kTile;   // per compute warp: -lse2[64], -delta[64] (dkdv only)
-  static constexpr int offBar = offStat + NCW * 128 * 4;
-  static constexpr int kTotal = offBar + 256 + 1024;
+  static constexpr int offC = offB + kTile;          // 3 stages: dkdv Q_i  | dq K_j
+  static constexpr int offD = offC + 3 * kTile;      // 2 stages: dkdv dO_i | dq V_j
+  static constexpr int offStat = offD + 2 * kTile;   // dkdv: per column group and step parity: -lse2[64], -delta[64]
+  static constexpr int offBar = offStat + 2 * 2 * 128 * 4;
+  static constexpr int kSlack = 512;                 // room for rounding the dynamic shared memory base up to 1024 bytes
+  static constexpr int kTotal = offBar + 256 + kSlack;
 };
+
+// Round the dynamic shared memory base up to 1024 bytes (TMA 128-byte swizzle atoms); returns nullptr if that needs more
+// than the slack the launch reserved (the base is 1024-aligned in practice, so this does not happen).
+template <int kSlack>
+__device__ __forceinline__ uint8_t* align_smem(uint8_t* raw) {
+  uint8_t* a = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  return (a - raw) <= kSlack ? a : nullptr;
+}
 
 // ------------------------------------------------------------------------------------------------ dK / dV
 // One CTA per 128-key tile and kv head; loops over 128-query tiles and the query heads of the GQA group.
@@ -403,17 +418,20 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   using L = BwdSmem<D>;
   constexpr int DB = D / 64;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = align_smem<L::kSlack>(smem_raw);
+  if (smem == nullptr) { if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrTimeoutOther); return; }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
   uint64_t* kv_full = bars;          // 1
   uint64_t* acc_done = bars + 1;     // 1
-  uint64_t* qdo_full = bars + 2;     // 2
-  uint64_t* qdo_empty = bars + 4;    // 2
-  uint64_t* s_full = bars + 6;       // S^T(i) is in X
-  uint64_t* dp_full = bars + 7;      // dP^T(i) is in Y
-  uint64_t* p_full = bars + 8;       // NCW warps: P^T(i) is in X
-  uint64_t* ds_full = bars + 9;      // NCW warps: dS^T(i) is in Y
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* q_full = bars + 2;       // 3
+  uint64_t* q_empty = bars + 5;      // 3
+  uint64_t* do_full = bars + 8;      // 2
+  uint64_t* do_empty = bars + 10;    // 2
+  uint64_t* s_full = bars + 12;      // S^T(i) is in X
+  uint64_t* dp_full = bars + 13;     // dP^T(i) is in Y
+  uint64_t* p_full = bars + 14;      // NCW warps: P^T(i) is in X
+  uint64_t* ds_full = bars + 15;     // NCW warps: dS^T(i) is in Y
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stat = reinterpret_cast<float*>(smem + L::offStat);
 
@@ -431,7 +449,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(acc_done, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    for (int i = 0; i < 3; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&do_full[i], 1); mbar_init(&do_empty[i], 1); }
     mbar_init(s_full, 1); mbar_init(dp_full, 1); mbar_init(p_full, NCW); mbar_init(ds_full, NCW);
     *abort_flag = 0;
     fence_mbar_init();
@@ -451,17 +470,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tma_load_2d(smem + L::offA + b * 16384, &tmK, kv_full, hkv * D + 64 * b, krow);
         tma_load_2d(smem + L::offB + b * 16384, &tmV, kv_full, hkv * D + 64 * b, krow);
       }
+      int qs = 0;             // stage / phase of the Q ring (3 stages) ; the dO ring (2 stages) follows `it`
+      uint32_t qph = 1;
       for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1;
+        const int ds = it & 1;
         const int i = i_first + it / group, hq = hkv * group + it % group;
-        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
         const int qrow = ti.doc_start + i * 128;
-        mbar_expect_tx(&qdo_full[st], 2 * L::kTile);
+        if (!mbar_wait(&q_empty[qs], qph, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        mbar_expect_tx(&q_full[qs], L::kTile);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + st * L::kTile + b * 16384, &tmQ, &qdo_full[st], hq * D + 64 * b, qrow);
-          tma_load_2d(smem + L::offD + st * L::kTile + b * 16384, &tmdO, &qdo_full[st], hq * D + 64 * b, qrow);
-        }
+        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offC + qs * L::kTile + b * 16384, &tmQ, &q_full[qs], hq * D + 64 * b, qrow);
+        if (!mbar_wait(&do_empty[ds], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        mbar_expect_tx(&do_full[ds], L::kTile);
+#pragma unroll
+        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offD + ds * L::kTile + b * 16384, &tmdO, &do_full[ds], hq * D + 64 * b, qrow);
+        if (++qs == 3) { qs = 0; qph ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -487,34 +510,46 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kErrTimeoutFull);
       if (ok && n_iter > 0) {
-        ok = mbar_wait(&qdo_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
+        ok = mbar_wait(&q_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
         if (ok) {
           tc_fence_after();
           issue_score(tX, dK, dQk);
           umma_commit(s_full);
+          ok = mbar_wait(&do_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
+        }
+        if (ok) {
+          tc_fence_after();
           issue_score(tY, dV, dOk);
           umma_commit(dp_full);
         }
       }
+      int qs = 0, qn = 1;     // Q-ring stage of step `it` and of step `it + 1`
+      uint32_t qn_ph = 0;     // phase of q_full[qn] for step it + 1
       for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it & 1, nx = st ^ 1;
+        const int ds = it & 1, dn = ds ^ 1;
         const bool more = it + 1 < n_iter;
         if (!mbar_wait(p_full, it & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         tc_fence_after();
-        issue_acc(tmem_base + DV_COL, tX, desc_off(dOm, st * L::kTile), (uint32_t)it);
+        issue_acc(tmem_base + DV_COL, tX, desc_off(dOm, ds * L::kTile), (uint32_t)it);
+        umma_commit(&do_empty[ds]);                          // dO_i was last read by dV(i)
         if (more) {
-          if (!mbar_wait(&qdo_full[nx], ((it + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
-          issue_score(tX, dK, desc_off(dQk, nx * L::kTile));   // runs after dV(it), which read X
+          if (!mbar_wait(&q_full[qn], qn_ph, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_score(tX, dK, desc_off(dQk, qn * L::kTile));   // runs after dV(it), which read X
           umma_commit(s_full);
         }
         if (!mbar_wait(ds_full, it & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         tc_fence_after();
-        issue_acc(tmem_base + DK_COL, tY, desc_off(dQm, st * L::kTile), (uint32_t)it);
-        umma_commit(&qdo_empty[st]);
+        issue_acc(tmem_base + DK_COL, tY, desc_off(dQm, qs * L::kTile), (uint32_t)it);
+        umma_commit(&q_empty[qs]);                           // Q_i was last read by dK(i)
         if (more) {
-          issue_score(tY, dV, desc_off(dOk, nx * L::kTile));   // runs after dK(it), which read Y
+          if (!mbar_wait(&do_full[dn], ((it + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_score(tY, dV, desc_off(dOk, dn * L::kTile));   // runs after dK(it), which read Y
           umma_commit(dp_full);
         }
+        qs = qn;
+        if (++qn == 3) { qn = 0; qn_ph ^= 1; }
       }
       if (ok) umma_commit(acc_done);
     }
@@ -527,7 +562,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const bool key_ok = kvi < ti.doc_len;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t tX = tmem_base + X_COL + cq * CPT + lane_addr, tY = tmem_base + Y_COL + cq * CPT + lane_addr;
-    float* wstat = stat + cw * 128;
+    // every warp of a column group writes the same values into the group's area (no cross-warp ordering needed);
+    // two areas alternate by step parity so that a warp one phase ahead never overwrites what a slower warp still reads
     // per-query statistics: lane l fetches those of queries 64 cq + l and 64 cq + 32 + l one step ahead
     auto fetch = [&](int it, float (&v)[4]) {
       const int i = i_first + it / group, hq = hkv * group + it % group;
@@ -546,7 +582,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int q0 = (i_first + it / group) * 128 + cq * CPT;   // first query of this thread's columns
-      __syncwarp();
+      float* wstat = stat + (cq * 2 + (it & 1)) * 128;
       wstat[lane] = nxt[0]; wstat[32 + lane] = nxt[1]; wstat[64 + lane] = nxt[2]; wstat[96 + lane] = nxt[3];
       __syncwarp();
       if (it + 1 < n_iter) fetch(it + 1, nxt);
@@ -666,17 +702,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   using L = BwdSmem<D>;
   constexpr int DB = D / 64;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = align_smem<L::kSlack>(smem_raw);
+  if (smem == nullptr) { if (threadIdx.x == 0) atomicCAS(p.status, 0, kErrTimeoutOther); return; }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::offBar);
   uint64_t* qdo_full = bars;         // 1
   uint64_t* acc_done = bars + 1;     // 1
-  uint64_t* kv_full = bars + 2;      // 2
-  uint64_t* kv_empty = bars + 4;     // 2
-  uint64_t* s_full = bars + 6;       // 2
-  uint64_t* s_free = bars + 8;       // 2 (NCW warps): the scores of this buffer are in registers
-  uint64_t* dp_full = bars + 10;     // 1
-  uint64_t* ds_full = bars + 11;     // 1 (NCW warps)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* k_full = bars + 2;       // 3
+  uint64_t* k_empty = bars + 5;      // 3
+  uint64_t* v_full = bars + 8;       // 2
+  uint64_t* v_empty = bars + 10;     // 2
+  uint64_t* s_full = bars + 12;      // 2
+  uint64_t* s_free = bars + 14;      // 2 (NCW warps): the scores of this buffer are in registers
+  uint64_t* dp_full = bars + 16;     // 1
+  uint64_t* ds_full = bars + 17;     // 1 (NCW warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -691,8 +730,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1); mbar_init(acc_done, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); mbar_init(&s_free[i], NCW);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&s_full[i], 1); mbar_init(&s_free[i], NCW);
     }
     mbar_init(dp_full, 1); mbar_init(ds_full, NCW);
     *abort_flag = 0;
@@ -713,16 +753,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_2d(smem + L::offA + b * 16384, &tmQ, qdo_full, hq * D + 64 * b, qrow);
         tma_load_2d(smem + L::offB + b * 16384, &tmdO, qdo_full, hq * D + 64 * b, qrow);
       }
+      int ks = 0;             // stage / phase of the K ring (3 stages); the V ring (2 stages) follows j
+      uint32_t kph = 1;
       for (int j = 0; j < J; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        const int vs = j & 1;
         const int krow = ti.doc_start + j * BN;
-        mbar_expect_tx(&kv_full[st], 2 * L::kTile);
+        if (!mbar_wait(&k_empty[ks], kph, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        mbar_expect_tx(&k_full[ks], L::kTile);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + L::offC + st * L::kTile + b * 16384, &tmK, &kv_full[st], hkv * D + 64 * b, krow);
-          tma_load_2d(smem + L::offD + st * L::kTile + b * 16384, &tmV, &kv_full[st], hkv * D + 64 * b, krow);
-        }
+        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offC + ks * L::kTile + b * 16384, &tmK, &k_full[ks], hkv * D + 64 * b, krow);
+        if (!mbar_wait(&v_empty[vs], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
+        mbar_expect_tx(&v_full[vs], L::kTile);
+#pragma unroll
+        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offD + vs * L::kTile + b * 16384, &tmV, &v_full[vs], hkv * D + 64 * b, krow);
+        if (++ks == 3) { ks = 0; kph ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -741,41 +785,53 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, kErrTimeoutFull);
       if (ok && J > 0) {
-        ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
+        ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
         if (ok) {
           tc_fence_after();
           issue_score(tmem_base + S_COL, dQ, dKk);
           umma_commit(&s_full[0]);
+          ok = mbar_wait(&v_full[0], 0, abort_flag, p.status, kErrTimeoutFull);
+        }
+        if (ok) {
+          tc_fence_after();
           issue_score(tmem_base + DP_COL, dO, dVk);
           umma_commit(dp_full);
+          umma_commit(&v_empty[0]);
         }
       }
+      int ks = 0, kn = 1;     // K-ring stage of step j and of step j + 1
+      uint32_t kn_ph = 0;     // phase of k_full[kn] for step j + 1
       for (int j = 0; j < J && ok; ++j) {
         TRACE(0, j);
-        const int st = j & 1, nx = st ^ 1;
+        const int nb = (j + 1) & 1;
         const bool more = j + 1 < J;
         if (more) {
-          if (!mbar_wait(&kv_full[nx], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
-          if (!mbar_wait(&s_free[nx], (((j + 1) >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) { ok = false; break; }
+          if (!mbar_wait(&k_full[kn], kn_ph, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          if (!mbar_wait(&s_free[nb], (((j + 1) >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) { ok = false; break; }
           tc_fence_after();
-          issue_score(tmem_base + S_COL + nx * BN, dQ, desc_off(dKk, nx * L::kTile));
-          umma_commit(&s_full[nx]);
+          issue_score(tmem_base + S_COL + nb * BN, dQ, desc_off(dKk, kn * L::kTile));
+          umma_commit(&s_full[nb]);
         }
         TRACE(1, j);
         if (!mbar_wait(ds_full, j & 1, abort_flag, p.status, kErrTimeoutOther)) { ok = false; break; }
         TRACE(2, j);
         tc_fence_after();
-        const SmemDesc k = desc_off(dKm, st * L::kTile);
+        const SmemDesc k = desc_off(dKm, ks * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           if (kk == 0) umma_ts<2>(tmem_base + DQ_COL, tmem_base + DP_COL, k, idesc_q, (uint32_t)j);
           else umma_ts<1>(tmem_base + DQ_COL, tmem_base + DP_COL + packed_col(kk), desc_off(k, kk * 2048), idesc_q);
         }
-        umma_commit(&kv_empty[st]);
+        umma_commit(&k_empty[ks]);                          // K_j was last read by dQ(j)
         if (more) {
-          issue_score(tmem_base + DP_COL, dO, desc_off(dVk, nx * L::kTile));   // runs after dQ(j), which read the dP buffer
+          if (!mbar_wait(&v_full[nb], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          tc_fence_after();
+          issue_score(tmem_base + DP_COL, dO, desc_off(dVk, nb * L::kTile));   // runs after dQ(j), which read the dP buffer
           umma_commit(dp_full);
+          umma_commit(&v_empty[nb]);                        // V_{j+1} is only read by dP(j+1)
         }
+        ks = kn;
+        if (++kn == 3) { kn = 0; kn_ph ^= 1; }
         TRACE(3, j);
       }
       if (ok) umma_commit(acc_done);
