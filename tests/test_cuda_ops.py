@@ -311,6 +311,34 @@ def test_adamw_matches_torch():
     torch.testing.assert_close(param.float(), pr.detach().to(torch.bfloat16).float(), atol=1e-2, rtol=1e-2)
 
 
+def test_adamw_clears_gradient_and_handles_unaligned_ranges():
+    """``zero_grad=True`` leaves the consumed gradient range at zero; a range that does not start on a 16-byte boundary
+    takes the scalar path and must give the same update as the vector path."""
+    cu = _cu()
+    n = 40_000
+    big = torch.randn(n + 8, device=DEV)
+    g_all = torch.randn(n + 8, device=DEV).to(torch.bfloat16)
+    outs = []
+    for off in (0, 1):   # aligned / unaligned views of the same data
+        master = big[off:off + n].clone()
+        m, v = torch.zeros(n + 8, device=DEV)[off:off + n], torch.zeros(n + 8, device=DEV)[off:off + n]
+        gbuf = g_all.clone()
+        g = gbuf[off:off + n]
+        pbuf = torch.zeros(n + 8, device=DEV, dtype=torch.bfloat16)
+        mbuf = torch.empty(n + 8, device=DEV)
+        mview = mbuf[off:off + n]
+        mview.copy_(master)
+        cu.adamw_step_(g, mview, m, v, pbuf[off:off + n], 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 0.5, zero_grad=True)
+        assert float(g.float().abs().max()) == 0.0
+        if off == 1:
+            assert float(gbuf[0].float().abs()) == float(g_all[0].float().abs())   # outside the range: untouched
+        outs.append((mview.clone(), g_all[off:off + n].clone(), big[off:off + n].clone()))
+    for mview, g_in, p0 in outs:
+        gf = g_in.float() * 0.5
+        want = p0 * (1 - 1e-2 * 0.1) - 1e-2 * ((0.1 * gf) / (1 - 0.9)) / (((0.05 * gf * gf) / (1 - 0.95)).sqrt() + 1e-8)
+        torch.testing.assert_close(mview, want, atol=1e-5, rtol=1e-5)
+
+
 def test_norm_linear_and_swiglu_linear_match_unfused():
     """The memory-saving fused forms must give the same values and gradients as the unfused sequence."""
     T, H, N, I = 300, 512, 768, 1024

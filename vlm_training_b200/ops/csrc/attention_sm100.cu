@@ -4,6 +4,8 @@
 // the CUDA-core work between the MMAs (two warps per scheduler, so one warp's latencies hide behind the other).
 // Probabilities and score gradients go back to the tensor core through tensor memory (they overwrite the fp32
 // scores they were computed from and are read as the A operand of the next MMA), never through shared memory.
+// Every MMA has N = 128 (or N = head dim): narrower MMAs occupy the tensor core for about 70 cycles whatever
+// their size (measured), so they would waste it.
 //
 // Forward: one CTA per (256 queries of one document = two 128-row tiles, query head).  Warps 2..5 own tile 0 and
 //   warps 6..9 tile 1, one query row per thread (tcgen05.ld gives a thread its whole row: row max and row sum need
@@ -11,13 +13,17 @@
 //   on one tile while the softmax of the other runs.  O accumulates in TMEM; it is rescaled only when a row's
 //   running max grows by more than 2^8 (the stale max is used meanwhile, which only changes the common scale
 //   of P and l).
-// Backward: `attn_bwd_dkdv` (one CTA per 128-key tile and kv head; loops over 64-query tiles and the query heads of
-//   the GQA group) and `attn_bwd_dq` (one CTA per 128-query tile and head; loops over 64-key tiles) recompute
-//   S and dP = dO V^T on the tensor cores; each compute thread handles half of a 64-wide row.  No atomics:
-//   results are bit-reproducible.
+// Backward: `attn_bwd_dkdv` (one CTA per 128-key tile and kv head; loops over 128-query tiles and the query heads
+//   of the GQA group) and `attn_bwd_dq` (one CTA per 128-query tile and head; loops over 128-key tiles) recompute
+//   S and dP = dO V^T on the tensor cores; each compute thread handles half of a 128-wide row in two phases
+//   (P = exp2(S - lse), then dS = P (dP - delta)) so that the exp2 phase overlaps the dP and accumulation MMAs.
+//   No atomics: results are bit-reproducible.
 //
 // Documents are [cu_seqlens[i], cu_seqlens[i+1]); tiles never mix documents: keys past the end of the document
 // (and, with `causal`, keys after the query) are masked before the softmax.
+//
+// Building with -DVLMT_ATTN_TRACE records clock64 stamps of the MMA thread and of one compute warp of CTA (0,0) of
+// the dQ kernel and prints them after the third backward call (a timeline tool; no effect on regular builds).
 #include "attention_sm100.h"
 #include "sm100.cuh"
 

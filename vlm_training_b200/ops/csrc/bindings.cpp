@@ -329,8 +329,8 @@ Tensor ce_fwd_bwd_(Tensor& logits, const Tensor& targets, double grad_scale, int
                   (int)logits.size(0), (int)logits.size(1), ignore_index, cur_stream());
   return loss;
 }
-void adamw_(const Tensor& grad, Tensor& master, Tensor& m, Tensor& v, c10::optional<Tensor> param, double lr, double b1, double b2,
-            double eps, double wd, int64_t step, double grad_scale) {
+void adamw_(Tensor& grad, Tensor& master, Tensor& m, Tensor& v, c10::optional<Tensor> param, double lr, double b1, double b2,
+            double eps, double wd, int64_t step, double grad_scale, bool zero_grad) {
   TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == v.scalar_type());
   TORCH_CHECK(m.scalar_type() == at::kFloat || m.scalar_type() == at::kBFloat16, "Adam moments must be fp32 or bf16");
   TORCH_CHECK(grad.is_contiguous() && master.is_contiguous() && m.is_contiguous() && v.is_contiguous());
@@ -338,7 +338,7 @@ void adamw_(const Tensor& grad, Tensor& master, Tensor& m, Tensor& v, c10::optio
   const double bc1 = 1.0 - std::pow(b1, (double)step), bc2 = 1.0 - std::pow(b2, (double)step);
   vlmt_adamw(grad.data_ptr(), grad.scalar_type() == at::kFloat, master.data_ptr<float>(), m.data_ptr(), v.data_ptr(),
              m.scalar_type() == at::kBFloat16, param.has_value() ? param->data_ptr() : nullptr, master.numel(), (float)lr, (float)b1, (float)b2, (float)eps, (float)wd,
-             (float)bc1, (float)bc2, (float)grad_scale, cur_stream());
+             (float)bc1, (float)bc2, (float)grad_scale, zero_grad ? 1 : 0, cur_stream());
 }
 void sumsq_(const Tensor& x, Tensor& out) {
   c10::cuda::CUDAGuard guard(x.device());

@@ -240,6 +240,368 @@ for (int wi = 0; wi < nwarps; ++wi) { a += sm_acc[(size_t)wi * 2 * D + i]; c += 
   }
 }
 
+// ----------------------------------------------------------------------------------- row-tile norm kernels
+// The kernels above give a warp a whole row (re-reading it for every pass and, in backward, accumulating the weight
+// gradient through shared memory); they measured 16-40 % of copy bandwidth.  The row-tile forms below are used whenever
+// D <= 8192: a block of 256 threads works on kRR rows at a time, every thread owns the same VPT 8-element column
+// groups of every row, so the rows stay in registers between the passes, the weights are loaded once per thread, and
+// the weight gradient of a thread's columns accumulates in its own registers (no shared memory, no cross-warp sum).
+constexpr int kRT = 256;  // threads per block
+constexpr int kRR = 4;    // rows in flight per block
+
+// Sum K per-thread values over the block; every thread gets the totals.  `sm` holds 2 x K x 8 floats and is used
+// alternately (`parity`), which makes one __syncthreads per call sufficient.
+template <int K>
+__device__ __forceinline__ void block_sum(float (&v)[K], float* sm, int& parity) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* buf = sm + parity * K * 8;
+#pragma unroll
+  for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) buf[k * 8 + warp] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kRT / 32; ++w) t += buf[k * 8 + w];
+    v[k] = t;
+  }
+  parity ^= 1;
+}
+__device__ __forceinline__ void ld_w8(const bf16* w, int v, float (&f)[8]) { unpack8(reinterpret_cast<const uint4*>(w)[v], f); }
+__device__ __forceinline__ void ld_w8(const float* w, int v, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(w)[2 * v], b = reinterpret_cast<const float4*>(w)[2 * v + 1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+template <typename WT, int VPT>
+__global__ void __launch_bounds__(kRT) rmsnorm_fwd_tile_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                              const WT* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ r_out,
+                                                              float* __restrict__ rstd, int rows, int D, float eps, int offset) {
+  __shared__ float sm[2 * kRR * 8];
+  const int nvec = D >> 3;
+  float wv[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kRT;
+    if (v < nvec) {
+      ld_w8(w, v, wv[k]);
+      if (offset) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wv[k][i] += 1.f;
+      }
+    }
+  }
+  int parity = 0;
+  const int n_groups = (rows + kRR - 1) / kRR;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    uint4 xv[kRR][VPT];
+    float ss[kRR];
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      ss[r] = 0.f;
+      const int row = g * kRR + r;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (row < rows && v < nvec) {
+          const size_t o = (size_t)row * nvec + v;
+          uint4 u = reinterpret_cast<const uint4*>(x)[o];
+          float f[8];
+          unpack8(u, f);
+          if (res) {
+            float e[8];
+            unpack8(reinterpret_cast<const uint4*>(res)[o], e);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] += e[i];
+            u = pack8(f);
+            reinterpret_cast<uint4*>(r_out)[o] = u;
+            unpack8(u, f);  // normalise the rounded residual stream, as the unfused sequence does
+          }
+          xv[r][k] = u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss[r] += f[i] * f[i];
+        }
+      }
+    }
+    block_sum<kRR>(ss, sm, parity);
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      const int row = g * kRR + r;
+      if (row >= rows) continue;
+      const float rs = rsqrtf(ss[r] / (float)D + eps);
+      if (threadIdx.x == 0 && rstd) rstd[row] = rs;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (v < nvec) {
+          float f[8];
+          unpack8(xv[r][k], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = f[i] * rs * wv[k][i];
+          reinterpret_cast<uint4*>(y)[(size_t)row * nvec + v] = pack8(f);
+        }
+      }
+    }
+  }
+}
+
+template <typename WT, int VPT>
+__global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                              const WT* __restrict__ w, const float* __restrict__ rstd,
+                                                              const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                                                              float* __restrict__ dw_partial, int rows, int D, int offset) {
+  __shared__ float sm[2 * kRR * 8];
+  const int nvec = D >> 3;
+  float wv[VPT][8], dw[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kRT;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dw[k][i] = 0.f;
+    if (v < nvec) {
+      ld_w8(w, v, wv[k]);
+      if (offset) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wv[k][i] += 1.f;
+      }
+    }
+  }
+  int parity = 0;
+  const int n_groups = (rows + kRR - 1) / kRR;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    uint4 xv[kRR][VPT], gv[kRR][VPT];
+    float dot[kRR], rs[kRR];
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      dot[r] = 0.f;
+      const int row = g * kRR + r;
+      rs[r] = row < rows ? rstd[row] : 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (row < rows && v < nvec) {
+          const size_t o = (size_t)row * nvec + v;
+          xv[r][k] = reinterpret_cast<const uint4*>(x)[o];
+          gv[r][k] = reinterpret_cast<const uint4*>(dy)[o];
+          float xf[8], gf[8];
+          unpack8(xv[r][k], xf);
+          unpack8(gv[r][k], gf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float xh = xf[i] * rs[r];
+            dot[r] += gf[i] * wv[k][i] * xh;
+            dw[k][i] += gf[i] * xh;
+          }
+        }
+      }
+    }
+    block_sum<kRR>(dot, sm, parity);
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      const int row = g * kRR + r;
+      if (row >= rows) continue;
+      const float dt = dot[r] / (float)D;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (v < nvec) {
+          const size_t o = (size_t)row * nvec + v;
+          float xf[8], gf[8], out[8];
+          unpack8(xv[r][k], xf);
+          unpack8(gv[r][k], gf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) out[i] = rs[r] * (gf[i] * wv[k][i] - xf[i] * rs[r] * dt);
+          if (dres) {
+            float e[8];
+            unpack8(reinterpret_cast<const uint4*>(dres)[o], e);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) out[i] += e[i];
+          }
+          reinterpret_cast<uint4*>(dx)[o] = pack8(out);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kRT;
+    if (v < nvec) {
+      float4* dst = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * D + (size_t)v * 8);
+      dst[0] = make_float4(dw[k][0], dw[k][1], dw[k][2], dw[k][3]);
+      dst[1] = make_float4(dw[k][4], dw[k][5], dw[k][6], dw[k][7]);
+    }
+  }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                                const bf16* __restrict__ b, bf16* __restrict__ y,
+                                                                float* __restrict__ mean, float* __restrict__ rstd, int rows, int D,
+                                                                float eps) {
+  __shared__ float sm[2 * kRR * 8];
+  const int nvec = D >> 3;
+  float wv[VPT][8], bv[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kRT;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bv[k][i] = 0.f;
+    if (v < nvec) {
+      ld_w8(w, v, wv[k]);
+      if (b) ld_w8(b, v, bv[k]);
+    }
+  }
+  int parity = 0;
+  const int n_groups = (rows + kRR - 1) / kRR;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    uint4 xv[kRR][VPT];
+    float s[kRR];
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      s[r] = 0.f;
+      const int row = g * kRR + r;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (row < rows && v < nvec) {
+          xv[r][k] = reinterpret_cast<const uint4*>(x)[(size_t)row * nvec + v];
+          float f[8];
+          unpack8(xv[r][k], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s[r] += f[i];
+        }
+      }
+    }
+    block_sum<kRR>(s, sm, parity);
+    float ss[kRR];
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      s[r] /= (float)D;  // mean
+      ss[r] = 0.f;
+      const int row = g * kRR + r;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (row < rows && v < nvec) {
+          float f[8];
+          unpack8(xv[r][k], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { const float d = f[i] - s[r]; ss[r] += d * d; }
+        }
+      }
+    }
+    block_sum<kRR>(ss, sm, parity);
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      const int row = g * kRR + r;
+      if (row >= rows) continue;
+      const float mu = s[r], rs = rsqrtf(ss[r] / (float)D + eps);
+      if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (v < nvec) {
+          float f[8];
+          unpack8(xv[r][k], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = (f[i] - mu) * rs * wv[k][i] + bv[k][i];
+          reinterpret_cast<uint4*>(y)[(size_t)row * nvec + v] = pack8(f);
+        }
+      }
+    }
+  }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                const bf16* __restrict__ w, const float* __restrict__ mean,
+                                                                const float* __restrict__ rstd, bf16* __restrict__ dx,
+                                                                float* __restrict__ dw_partial, float* __restrict__ db_partial, int rows,
+                                                                int D) {
+  __shared__ float sm[2 * 2 * kRR * 8];
+  const int nvec = D >> 3;
+  float wv[VPT][8], dw[VPT][8], db[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kRT;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dw[k][i] = 0.f; db[k][i] = 0.f; }
+    if (v < nvec) ld_w8(w, v, wv[k]);
+  }
+  int parity = 0;
+  const int n_groups = (rows + kRR - 1) / kRR;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    uint4 xv[kRR][VPT], gv[kRR][VPT];
+    float s12[2 * kRR], mu[kRR], rs[kRR];
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      s12[2 * r] = s12[2 * r + 1] = 0.f;
+      const int row = g * kRR + r;
+      mu[r] = row < rows ? mean[row] : 0.f;
+      rs[r] = row < rows ? rstd[row] : 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (row < rows && v < nvec) {
+          const size_t o = (size_t)row * nvec + v;
+          xv[r][k] = reinterpret_cast<const uint4*>(x)[o];
+          gv[r][k] = reinterpret_cast<const uint4*>(dy)[o];
+          float xf[8], gf[8];
+          unpack8(xv[r][k], xf);
+          unpack8(gv[r][k], gf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float xh = (xf[i] - mu[r]) * rs[r];
+            const float gw = gf[i] * wv[k][i];
+            s12[2 * r] += gw;
+            s12[2 * r + 1] += gw * xh;
+            dw[k][i] += gf[i] * xh;
+            db[k][i] += gf[i];
+          }
+        }
+      }
+    }
+    block_sum<2 * kRR>(s12, sm, parity);
+#pragma unroll
+    for (int r = 0; r < kRR; ++r) {
+      const int row = g * kRR + r;
+      if (row >= rows) continue;
+      const float s1 = s12[2 * r] / (float)D, s2 = s12[2 * r + 1] / (float)D;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int v = threadIdx.x + k * kRT;
+        if (v < nvec) {
+          float xf[8], gf[8], out[8];
+          unpack8(xv[r][k], xf);
+          unpack8(gv[r][k], gf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float xh = (xf[i] - mu[r]) * rs[r];
+            out[i] = rs[r] * (gf[i] * wv[k][i] - s1 - xh * s2);
+          }
+          reinterpret_cast<uint4*>(dx)[(size_t)row * nvec + v] = pack8(out);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * kRT;
+    if (v < nvec) {
+      float4* d1 = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * D + (size_t)v * 8);
+      float4* d2 = reinterpret_cast<float4*>(db_partial + (size_t)blockIdx.x * D + (size_t)v * 8);
+      d1[0] = make_float4(dw[k][0], dw[k][1], dw[k][2], dw[k][3]);
+      d1[1] = make_float4(dw[k][4], dw[k][5], dw[k][6], dw[k][7]);
+      d2[0] = make_float4(db[k][0], db[k][1], db[k][2], db[k][3]);
+      d2[1] = make_float4(db[k][4], db[k][5], db[k][6], db[k][7]);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------------- gated RMSNorm (GDN output)
 // y = x * rstd * w * z * sigmoid(z), rows of D (<= 256), one warp per row
 __global__ void rmsnorm_gated_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, const bf16* __restrict__ w,
@@ -407,6 +769,55 @@ __global__ void gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restr
 // One warp per (token, head slot).  Head slots: [0, n_q) q heads, [n_q, n_q+n_kv) k heads,
 // [n_q+n_kv, n_q+2 n_kv) v heads.  Lane owns E = D/32 consecutive channels; the rotate-half
 // partner of channel j (< R/2) is j + R/2, held by lane + (R/2)/E.
+// E consecutive bf16 (E = 1, 2, 4, 8; the address is E*2-byte aligned) <-> floats, as one memory access
+template <int E> struct VecE;
+template <> struct VecE<1> { using T = unsigned short; };
+template <> struct VecE<2> { using T = uint32_t; };
+template <> struct VecE<4> { using T = uint2; };
+template <> struct VecE<8> { using T = uint4; };
+template <int E>
+__device__ __forceinline__ void ldE(const bf16* p, float (&f)[E]) {
+  const typename VecE<E>::T raw = *reinterpret_cast<const typename VecE<E>::T*>(p);
+  const bf16* h = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+  for (int i = 0; i < E; ++i) f[i] = __bfloat162float(h[i]);
+}
+template <int E>
+__device__ __forceinline__ void stE(bf16* p, const float (&f)[E]) {
+  typename VecE<E>::T raw;
+  bf16* h = reinterpret_cast<bf16*>(&raw);
+#pragma unroll
+  for (int i = 0; i < E; ++i) h[i] = __float2bfloat16(f[i]);
+  *reinterpret_cast<typename VecE<E>::T*>(p) = raw;
+}
+template <int E>
+__device__ __forceinline__ void cpE(bf16* dst, const bf16* src) {
+  *reinterpret_cast<typename VecE<E>::T*>(dst) = *reinterpret_cast<const typename VecE<E>::T*>(src);
+}
+// E consecutive floats starting at p[j] when the whole group lies below `limit`, else zeros (j, limit multiples of E
+// when `vec`; element-wise otherwise)
+template <int E>
+__device__ __forceinline__ void ldF(const float* p, int j, int limit, bool vec, float (&f)[E]) {
+  if (vec && E >= 2) {
+    if (j < limit) {
+      if constexpr (E == 2) { const float2 a = *reinterpret_cast<const float2*>(p + j); f[0] = a.x; f[1] = a.y; }
+      else {
+#pragma unroll
+        for (int q4 = 0; q4 < E / 4; ++q4) {
+          const float4 a = *reinterpret_cast<const float4*>(p + j + 4 * q4);
+          f[4 * q4] = a.x; f[4 * q4 + 1] = a.y; f[4 * q4 + 2] = a.z; f[4 * q4 + 3] = a.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < E; ++i) f[i] = 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < E; ++i) f[i] = (j + i < limit) ? p[j + i] : 0.f;
+  }
+}
+
 template <int E>
 __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
                                          const float* __restrict__ cosv, const float* __restrict__ sinv, bf16* __restrict__ q,
@@ -421,6 +832,7 @@ __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf1
   const long total = (long)T * slots;
   const int half = R >> 1;
   const int plane = half / E;  // partner lane distance
+  const bool vec_cs = (R % E) == 0 && (R % 4) == 0;  // a lane's E angles are all inside or all outside [0, R), 16-byte aligned rows
   for (long item = blockIdx.x * (long)kWarpsPerBlock + warp; item < total; item += (long)gridDim.x * kWarpsPerBlock) {
     const int t = (int)(item / slots);
     const int s = (int)(item - (long)t * slots);
@@ -432,47 +844,38 @@ __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf1
     if (s < n_q) { src = row + s * qstride; dst = q + ((size_t)t * n_q + s) * D; wn = qw; kind = 0; }
     else if (s < n_q + n_kv) { const int h = s - n_q; src = row + n_q * qstride + h * D; dst = k + ((size_t)t * n_kv + h) * D; wn = kw; kind = 1; }
     else { const int h = s - n_q - n_kv; src = row + n_q * qstride + n_kv * D + h * D; dst = v + ((size_t)t * n_kv + h) * D; kind = 2; }
-    float f[E];
-#pragma unroll
-    for (int i = 0; i < E; ++i) f[i] = __bfloat162float(src[lane * E + i]);
     if (kind == 2) {
-#pragma unroll
-      for (int i = 0; i < E; ++i) dst[lane * E + i] = src[lane * E + i];
+      cpE<E>(dst + lane * E, src + lane * E);
       continue;
     }
-    if (kind == 0 && gated) {
-      bf16* gd = gate + ((size_t)t * n_q + s) * D;
-#pragma unroll
-      for (int i = 0; i < E; ++i) gd[lane * E + i] = src[D + lane * E + i];
-    }
+    float f[E];
+    ldE<E>(src + lane * E, f);
+    if (kind == 0 && gated) cpE<E>(gate + ((size_t)t * n_q + s) * D + lane * E, src + D + lane * E);
     if (has_norm) {
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < E; ++i) ss += f[i] * f[i];
       const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
       if (lane == 0) rstd[(size_t)t * (n_q + n_kv) + s] = rs;
+      float wv[E];
+      ldE<E>(wn + lane * E, wv);
 #pragma unroll
       for (int i = 0; i < E; ++i) {
-        const float wv = ldw(wn, lane * E + i);
         // round to bf16 between norm and rotary like the unfused sequence of ops
-        f[i] = __bfloat162float(__float2bfloat16(f[i] * rs * (offset ? 1.f + wv : wv)));
+        f[i] = __bfloat162float(__float2bfloat16(f[i] * rs * (offset ? 1.f + wv[i] : wv[i])));
       }
     }
     // rotary on channels [0, R)
-    float o[E];
+    float c[E], sn[E], o[E];
+    ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
+    ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
 #pragma unroll
     for (int i = 0; i < E; ++i) {
       const int j = lane * E + i;
       const float partner = __shfl_xor_sync(0xffffffffu, f[i], plane);
-      if (j < R) {
-        const float c = cosv[(size_t)t * R + j], sn = sinv[(size_t)t * R + j];
-        o[i] = f[i] * c + (j < half ? -partner : partner) * sn;
-      } else {
-        o[i] = f[i];
-      }
+      o[i] = j < R ? f[i] * c[i] + (j < half ? -partner : partner) * sn[i] : f[i];
     }
-#pragma unroll
-    for (int i = 0; i < E; ++i) dst[lane * E + i] = __float2bfloat16(o[i]);
+    stE<E>(dst + lane * E, o);
   }
 }
 
@@ -491,6 +894,7 @@ __global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16
   const long total = (long)T * slots;
   const int half = R >> 1;
   const int plane = half / E;
+  const bool vec_cs = (R % E) == 0 && (R % 4) == 0;
   float acc_q[E], acc_k[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) acc_q[i] = acc_k[i] = 0.f;
@@ -506,49 +910,42 @@ __global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16
     else if (s < n_q + n_kv) { kind = 1; const int h = s - n_q; off = n_q * qstride + h * D; g = dk + ((size_t)t * n_kv + h) * D; wn = kw; }
     else { kind = 2; const int h = s - n_q - n_kv; off = n_q * qstride + n_kv * D + h * D; g = dv + ((size_t)t * n_kv + h) * D; }
     if (kind == 2) {
-#pragma unroll
-      for (int i = 0; i < E; ++i) drow[off + lane * E + i] = g[lane * E + i];
+      cpE<E>(drow + off + lane * E, g + lane * E);
       continue;
     }
-    if (kind == 0 && gated) {
-      const bf16* gg = dgate + ((size_t)t * n_q + s) * D;
-#pragma unroll
-      for (int i = 0; i < E; ++i) drow[off + D + lane * E + i] = gg[lane * E + i];
-    }
+    if (kind == 0 && gated) cpE<E>(drow + off + D + lane * E, dgate + ((size_t)t * n_q + s) * D + lane * E);
     // rotary transpose: dn[j] = do[j] c[j] + (j < half ? do[j+half] s[j+half] : -do[j-half] s[j-half])
-    float dn[E];
+    float d[E], c[E], sn[E], dn[E];
+    ldE<E>(g + lane * E, d);
+    ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
+    ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
 #pragma unroll
     for (int i = 0; i < E; ++i) {
       const int j = lane * E + i;
-      const float d = __bfloat162float(g[j]);
-      float ds = 0.f;
-      if (j < R) ds = d * sinv[(size_t)t * R + j];
+      const float ds = d[i] * sn[i];  // sn is zero beyond R
       const float partner = __shfl_xor_sync(0xffffffffu, ds, plane);
-      if (j < R) dn[i] = d * cosv[(size_t)t * R + j] + (j < half ? partner : -partner);
-      else dn[i] = d;
+      dn[i] = j < R ? d[i] * c[i] + (j < half ? partner : -partner) : d[i];
     }
     if (!has_norm) {
-#pragma unroll
-      for (int i = 0; i < E; ++i) drow[off + lane * E + i] = __float2bfloat16(dn[i]);
+      stE<E>(drow + off + lane * E, dn);
       continue;
     }
     const float rs = rstd[(size_t)t * (n_q + n_kv) + s];
-    float xh[E], dot = 0.f;
+    float xh[E], wv[E], dot = 0.f;
+    ldE<E>(row + off + lane * E, xh);
+    ldE<E>(wn + lane * E, wv);
 #pragma unroll
     for (int i = 0; i < E; ++i) {
-      const float wv0 = ldw(wn, lane * E + i);
-      const float wv = offset ? 1.f + wv0 : wv0;
-      xh[i] = __bfloat162float(row[off + lane * E + i]) * rs;
-      dot += dn[i] * wv * xh[i];
+      if (offset) wv[i] += 1.f;
+      xh[i] *= rs;
+      dot += dn[i] * wv[i] * xh[i];
       if (kind == 0) acc_q[i] += dn[i] * xh[i]; else acc_k[i] += dn[i] * xh[i];
     }
     dot = warp_sum(dot) / (float)D;
+    float out[E];
 #pragma unroll
-    for (int i = 0; i < E; ++i) {
-      const float wv0 = ldw(wn, lane * E + i);
-      const float wv = offset ? 1.f + wv0 : wv0;
-      drow[off + lane * E + i] = __float2bfloat16(rs * (dn[i] * wv - xh[i] * dot));
-    }
+    for (int i = 0; i < E; ++i) out[i] = rs * (dn[i] * wv[i] - xh[i] * dot);
+    stE<E>(drow + off + lane * E, out);
   }
 #pragma unroll
   for (int i = 0; i < E; ++i) { sm_dw[warp][0][lane * E + i] = acc_q[i]; sm_dw[warp][1][lane * E + i] = acc_k[i]; }
@@ -563,6 +960,36 @@ __global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16
 
 // ----------------------------------------------------------------------------------- ViT rotary (any even D, strided input)
 // x [S, H, D] with strides (ss, hs, 1) -> contiguous out; cos/sin [S, D] fp32; transpose=1 gives the backward map.
+// the same rotation on groups of 4 channels (8-byte bf16 accesses, 16-byte angle loads): needs D/2, every stride and
+// every base address to be multiples of 4 elements
+__global__ void rope_generic_vec4_kernel(const bf16* __restrict__ x, long ss, long hs, const float* __restrict__ cosv,
+                                         const float* __restrict__ sinv, bf16* __restrict__ out, long oss, long ohs, int S, int H, int D,
+                                         int transpose) {
+  const int half = D >> 1, hq = half >> 2;
+  const long total = (long)S * H * hq;
+  for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int j = (int)(idx % hq) * 4;
+    const long sh = idx / hq;
+    const int h = (int)(sh % H);
+    const long s = sh / H;
+    const bf16* p = x + s * ss + h * hs;
+    float a[4], b[4], o0[4], o1[4];
+    ldE<4>(p + j, a);
+    ldE<4>(p + j + half, b);
+    const float4 c0 = *reinterpret_cast<const float4*>(cosv + s * D + j), c1 = *reinterpret_cast<const float4*>(cosv + s * D + j + half);
+    const float4 s0 = *reinterpret_cast<const float4*>(sinv + s * D + j), s1 = *reinterpret_cast<const float4*>(sinv + s * D + j + half);
+    const float c0v[4] = {c0.x, c0.y, c0.z, c0.w}, c1v[4] = {c1.x, c1.y, c1.z, c1.w};
+    const float s0v[4] = {s0.x, s0.y, s0.z, s0.w}, s1v[4] = {s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (!transpose) { o0[i] = a[i] * c0v[i] - b[i] * s0v[i]; o1[i] = b[i] * c1v[i] + a[i] * s1v[i]; }
+      else { o0[i] = a[i] * c0v[i] + b[i] * s1v[i]; o1[i] = b[i] * c1v[i] - a[i] * s0v[i]; }
+    }
+    bf16* q = out + s * oss + h * ohs;
+    stE<4>(q + j, o0);
+    stE<4>(q + j + half, o1);
+  }
+}
 __global__ void rope_generic_kernel(const bf16* __restrict__ x, long ss, long hs, const float* __restrict__ cosv,
                                     const float* __restrict__ sinv, bf16* __restrict__ out, long oss, long ohs, int S, int H, int D,
                                     int transpose) {
@@ -765,8 +1192,26 @@ static int bwd_warps(size_t floats_per_warp) {
   return w < 1 ? 0 : w;
 }
 
+// column groups per thread of the row-tile kernels (0: D is too wide for them)
+static int tile_vpt(int D) {
+  const int nvec = D >> 3;
+  if ((D & 7) || nvec > 4 * kRT) return 0;
+  return nvec <= kRT ? 1 : (nvec <= 2 * kRT ? 2 : 4);
+}
+#define TILE_DISPATCH(VPT, CALL1, CALL2, CALL4) do { if ((VPT) == 1) { CALL1; } else if ((VPT) == 2) { CALL2; } else { CALL4; } } while (0)
+
 void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32, void* y, void* r_out, float* rstd, int rows, int D,
                       float eps, int offset, cudaStream_t st) {
+  if (rows <= 0) return;
+  const int vpt = tile_vpt(D);
+  if (vpt) {
+    const int grid = grid_for(rows, kRR, 148 * 4);
+#define RF(WT, V) rmsnorm_fwd_tile_kernel<WT, V><<<grid, kRT, 0, st>>>(BF(x), BF(res), (const WT*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset)
+    if (w_fp32) TILE_DISPATCH(vpt, RF(float, 1), RF(float, 2), RF(float, 4));
+    else TILE_DISPATCH(vpt, RF(bf16, 1), RF(bf16, 2), RF(bf16, 4));
+#undef RF
+    return;
+  }
   const int grid = grid_for(rows, kWarpsPerBlock, 148 * 8);
   if (w_fp32)
     rmsnorm_fwd_kernel<float><<<grid, kThreads, 0, st>>>(BF(x), BF(res), (const float*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset);
@@ -774,9 +1219,18 @@ void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32,
     rmsnorm_fwd_kernel<bf16><<<grid, kThreads, 0, st>>>(BF(x), BF(res), BF(w), BFM(y), BFM(r_out), rstd, rows, D, eps, offset);
 }
 
+// dw_partial has vlmt_norm_blocks(rows) rows; every one of them is written
 int vlmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, int w_fp32, const float* rstd, const void* dres, void* dx,
                      float* dw_partial, int rows, int D, int offset, cudaStream_t st) {
   const int grid = vlmt_norm_blocks(rows);
+  const int vpt = tile_vpt(D);
+  if (vpt) {
+#define RB(WT, V) rmsnorm_bwd_tile_kernel<WT, V><<<grid, kRT, 0, st>>>(BF(dy), BF(x), (const WT*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset)
+    if (w_fp32) TILE_DISPATCH(vpt, RB(float, 1), RB(float, 2), RB(float, 4));
+    else TILE_DISPATCH(vpt, RB(bf16, 1), RB(bf16, 2), RB(bf16, 4));
+#undef RB
+    return grid;
+  }
   const int nw = bwd_warps(D);
   if (nw == 0) return -1;
   const size_t smem = (size_t)nw * D * sizeof(float);
@@ -795,11 +1249,27 @@ int vlmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, int w_fp32, c
 
 void vlmt_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D, float eps,
                         cudaStream_t st) {
+  if (rows <= 0) return;
+  const int vpt = tile_vpt(D);
+  if (vpt) {
+    const int grid = grid_for(rows, kRR, 148 * 4);
+#define LF(V) layernorm_fwd_tile_kernel<V><<<grid, kRT, 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps)
+    TILE_DISPATCH(vpt, LF(1), LF(2), LF(4));
+#undef LF
+    return;
+  }
   layernorm_fwd_kernel<<<grid_for(rows, kWarpsPerBlock, 148 * 8), kThreads, 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps);
 }
 int vlmt_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx, float* dw_partial,
                        float* db_partial, int rows, int D, cudaStream_t st) {
   const int grid = vlmt_norm_blocks(rows);
+  const int vpt = tile_vpt(D);
+  if (vpt) {
+#define LB(V) layernorm_bwd_tile_kernel<V><<<grid, kRT, 0, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D)
+    TILE_DISPATCH(vpt, LB(1), LB(2), LB(4));
+#undef LB
+    return grid;
+  }
   const int nw = bwd_warps(2 * (size_t)D);
   if (nw == 0) return -1;
   const size_t smem = (size_t)nw * 2 * D * sizeof(float);
@@ -880,6 +1350,14 @@ int vlmt_qkv_norm_rope_bwd(const void* dq, const void* dk, const void* dv, const
 
 void vlmt_rope_generic(const void* x, long ss, long hs, const float* cosv, const float* sinv, void* out, long oss, long ohs, int S, int H,
                        int D, int transpose, cudaStream_t st) {
+  const int half = D / 2;
+  const bool vec4 = half % 4 == 0 && ss % 4 == 0 && hs % 4 == 0 && oss % 4 == 0 && ohs % 4 == 0 && ((uintptr_t)x & 7) == 0 &&
+                    ((uintptr_t)out & 7) == 0 && ((uintptr_t)cosv & 15) == 0 && ((uintptr_t)sinv & 15) == 0;
+  if (vec4) {
+    rope_generic_vec4_kernel<<<grid_for((long)S * H * (half / 4), 256, 148 * 16), 256, 0, st>>>(BF(x), ss, hs, cosv, sinv, BFM(out), oss,
+                                                                                           ohs, S, H, D, transpose);
+    return;
+  }
   rope_generic_kernel<<<grid_for((long)S * H * (D / 2), 256, 148 * 16), 256, 0, st>>>(BF(x), ss, hs, cosv, sinv, BFM(out), oss, ohs, S, H, D,
                                                                                     transpose);
 }

@@ -109,9 +109,10 @@ __device__ __forceinline__ float ld_state(const bf16* p, long i) { return __bflo
 __device__ __forceinline__ void st_state(float* p, long i, float x) { p[i] = x; }
 __device__ __forceinline__ void st_state(bf16* p, long i, float x) { p[i] = __float2bfloat16(x); }
 
-// GT: gradient type (bf16 / float); MT: moment storage type (float, or bf16 to halve the optimizer state)
-template <typename GT, typename MT>
-__global__ void adamw_kernel(const GT* __restrict__ grad, float* __restrict__ master, MT* __restrict__ m, MT* __restrict__ v,
+// GT: gradient type (bf16 / float); MT: moment storage type (float, or bf16 to halve the optimizer state).
+// ZERO: also clear the gradient (saves the separate memset of the gradient buffer before the next step).
+template <typename GT, typename MT, bool ZERO>
+__global__ void adamw_kernel(GT* __restrict__ grad, float* __restrict__ master, MT* __restrict__ m, MT* __restrict__ v,
                              bf16* __restrict__ param, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                              float grad_scale) {
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
@@ -123,6 +124,63 @@ __global__ void adamw_kernel(const GT* __restrict__ grad, float* __restrict__ ma
     p -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
     st_state(m, i, mi); st_state(v, i, vi); master[i] = p;
     if (param) param[i] = __float2bfloat16(p);
+    if constexpr (ZERO) grad[i] = GT(0.f);
+  }
+}
+
+// 8 consecutive values as floats <-> memory (16-byte accesses)
+struct F8 { float x[8]; };
+__device__ __forceinline__ F8 ld8(const float* p) {
+  F8 r;
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  r.x[0] = a.x; r.x[1] = a.y; r.x[2] = a.z; r.x[3] = a.w; r.x[4] = b.x; r.x[5] = b.y; r.x[6] = b.z; r.x[7] = b.w;
+  return r;
+}
+__device__ __forceinline__ F8 ld8(const bf16* p) {
+  F8 r;
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); r.x[2 * i] = f.x; r.x[2 * i + 1] = f.y; }
+  return r;
+}
+__device__ __forceinline__ void st8(float* p, const F8& r) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(r.x[0], r.x[1], r.x[2], r.x[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(r.x[4], r.x[5], r.x[6], r.x[7]);
+}
+__device__ __forceinline__ void st8(bf16* p, const F8& r) {
+  uint4 u;
+  bf162* h = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(r.x[2 * i], r.x[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// The same update on groups of 8 elements with 16-byte loads and stores (all pointers 16-byte aligned, n8 groups).
+template <typename GT, typename MT, bool ZERO>
+__global__ void adamw_vec8_kernel(GT* __restrict__ grad, float* __restrict__ master, MT* __restrict__ m, MT* __restrict__ v,
+                                  bf16* __restrict__ param, long n8, float lr, float b1, float b2, float eps, float wd, float rbc1,
+                                  float rbc2, float grad_scale) {
+  const float decay = 1.f - lr * wd;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const long o = i * 8;
+    const F8 g = ld8(grad + o);
+    F8 mm = ld8(m + o), vv = ld8(v + o), pp = ld8(master + o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = g.x[k] * grad_scale;
+      mm.x[k] = b1 * mm.x[k] + (1.f - b1) * gk;
+      vv.x[k] = b2 * vv.x[k] + (1.f - b2) * gk * gk;
+      pp.x[k] = pp.x[k] * decay - lr * (mm.x[k] * rbc1) / (sqrtf(vv.x[k] * rbc2) + eps);
+    }
+    st8(m + o, mm); st8(v + o, vv); st8(master + o, pp);
+    if (param) st8(param + o, pp);
+    if constexpr (ZERO) {
+      F8 z;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) z.x[k] = 0.f;
+      st8(grad + o, z);
+    }
   }
 }
 
@@ -169,15 +227,33 @@ void vlmt_ce_fwd_bwd(void* logits, long ld, const long* targets, float* loss, fl
   if (rows <= 0) return;
   ce_fwd_bwd_kernel<<<rows, CE_THREADS, 0, st>>>(reinterpret_cast<bf16*>(logits), ld, targets, loss, grad_scale, V, ignore_index);
 }
-void vlmt_adamw(const void* grad, int grad_fp32, float* master, void* m, void* v, int state_bf16, void* param, long n, float lr, float b1,
-                float b2, float eps, float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
+void vlmt_adamw(void* grad, int grad_fp32, float* master, void* m, void* v, int state_bf16, void* param, long n, float lr, float b1,
+                float b2, float eps, float wd, float bc1, float bc2, float grad_scale, int zero_grad, cudaStream_t st) {
   if (n <= 0) return;
-  long blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
   bf16* pp = reinterpret_cast<bf16*>(param);
-#define LAUNCH(GT, MT) adamw_kernel<GT, MT><<<(int)blocks, 256, 0, st>>>((const GT*)grad, master, (MT*)m, (MT*)v, pp, n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale)
-  if (grad_fp32) { if (state_bf16) LAUNCH(float, bf16); else LAUNCH(float, float); }
-  else { if (state_bf16) LAUNCH(bf16, bf16); else LAUNCH(bf16, float); }
+  const uintptr_t bits = (uintptr_t)grad | (uintptr_t)master | (uintptr_t)m | (uintptr_t)v | (uintptr_t)param;
+  const long n8 = (bits & 15) == 0 ? n / 8 : 0;   // groups of 8 handled with 16-byte accesses
+  const long done = n8 * 8;
+#define LAUNCH(GT, MT, Z)                                                                                                         \
+  do {                                                                                                                            \
+    if (n8 > 0) {                                                                                                                 \
+      long blocks = (n8 + 255) / 256;                                                                                             \
+      if (blocks > 148 * 8) blocks = 148 * 8;                                                                                     \
+      adamw_vec8_kernel<GT, MT, Z><<<(int)blocks, 256, 0, st>>>((GT*)grad, master, (MT*)m, (MT*)v, pp, n8, lr, b1, b2, eps, wd,   \
+                                                                 1.f / bc1, 1.f / bc2, grad_scale);                                \
+    }                                                                                                                             \
+    if (done < n) {                                                                                                               \
+      long blocks = (n - done + 255) / 256;                                                                                       \
+      if (blocks > 148 * 16) blocks = 148 * 16;                                                                                   \
+      adamw_kernel<GT, MT, Z><<<(int)blocks, 256, 0, st>>>((GT*)grad + done, master + done, (MT*)m + done, (MT*)v + done,         \
+                                                            pp ? pp + done : nullptr, n - done, lr, b1, b2, eps, wd, bc1, bc2,     \
+                                                            grad_scale);                                                           \
+    }                                                                                                                             \
+  } while (0)
+#define PICK(GT, MT) do { if (zero_grad) LAUNCH(GT, MT, true); else LAUNCH(GT, MT, false); } while (0)
+  if (grad_fp32) { if (state_bf16) PICK(float, bf16); else PICK(float, float); }
+  else { if (state_bf16) PICK(bf16, bf16); else PICK(bf16, float); }
+#undef PICK
 #undef LAUNCH
 }
 int vlmt_colsum_slabs(int rows) { int s = (rows + 511) / 512; return s < 1 ? 1 : s; }

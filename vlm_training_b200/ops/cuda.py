@@ -715,8 +715,10 @@ def add_rows(x, index, src):
 
 
 # ------------------------------------------------------------------------------- optimizer
-def adamw_step_(grad, master, exp_avg, exp_avg_sq, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0):
-    _C.adamw_(grad, master, exp_avg, exp_avg_sq, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale)
+def adamw_step_(grad, master, exp_avg, exp_avg_sq, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+                zero_grad=False):
+    """``zero_grad``: clear ``grad`` after it has been consumed (no separate memset before the next step)."""
+    _C.adamw_(grad, master, exp_avg, exp_avg_sq, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale, zero_grad)
     _tick()
 
 

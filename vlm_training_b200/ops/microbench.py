@@ -151,7 +151,7 @@ def bench_adamw(t: Timer, n=1 << 28):
     g = torch.randn(n, device="cuda").bfloat16()
     p = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
     master, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
-    ms = t(lambda: cu._C.adamw_(g, master, m, v, p, 1e-4, 0.9, 0.999, 1e-8, 0.01, 1, 1.0))
+    ms = t(lambda: cu._C.adamw_(g, master, m, v, p, 1e-4, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, False))
     return _report("adamw_fp32_state", [n], ms, nbytes=n * (2 + 12 + 12 + 2.0))
 
 

@@ -226,7 +226,10 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
     # ------------------------------------------------------------------ torch.optim surface
     def zero_grad(self, set_to_none: bool = False):
         for d in self.domains:
-            d.flat_grad.zero_()
+            if getattr(d, "grads_clean", False):
+                d.grads_clean = False  # the AdamW kernel of the last step() cleared every gradient it consumed
+            else:
+                d.flat_grad.zero_()
             for b in d.buckets:
                 b.pending = len(b.params)
                 b.reduced = False
@@ -350,13 +353,16 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                     self._adamw(d, bi, s - lo, e - lo, d.flat_grad[s:e], d.flat_param[s:e], pg["lr"], pg["weight_decay"],
                                 b1, b2, d.grad_scale * clip)
                 self._gather_bucket(d, b)
+            # on this path every rank's kernel clears the gradients it consumed; when each rank consumes the whole
+            # buffer (one rank, or unsharded data parallelism) the next zero_grad() has nothing left to do
+            d.grads_clean = self.is_cuda and d.flat_param.dtype == torch.bfloat16 and (d.size == 1 or not d.shard)
 
     def _adamw(self, d, bi, s, e, grad, param, lr, wd, b1, b2, grad_scale):
         master, m, v = d.master[bi][s:e], d.exp_avg[bi][s:e], d.exp_avg_sq[bi][s:e]
         if self.is_cuda and param.dtype == torch.bfloat16:
             from ..ops import cuda as cu
 
-            cu.adamw_step_(grad, master, m, v, param, lr, b1, b2, self.eps, wd, self.step_count, grad_scale)
+            cu.adamw_step_(grad, master, m, v, param, lr, b1, b2, self.eps, wd, self.step_count, grad_scale, zero_grad=True)
             return
         g = grad.float() * grad_scale
         mf, vf = m.float(), v.float()
