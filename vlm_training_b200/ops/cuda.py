@@ -43,12 +43,14 @@ def _tick(n: int = 1):
 
 def check_status(raise_on_error: bool = True) -> int:
     """Read (and clear) the device status word that bounded in-kernel waits write on timeout."""
+    from . import status
+
     st = _C.status()
+    if raise_on_error:
+        return status.raise_if_set(st, "a kernel")
     code = int(st[0].item())
     if code != 0:
         st.zero_()
-        if raise_on_error:
-            raise RuntimeError(f"a kernel gave up on a bounded wait (status code {code})")
     return code
 
 
