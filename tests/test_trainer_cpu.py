@@ -157,3 +157,14 @@ def test_vlm_tp2_image_parallel_vit_matches_single_rank(tmp_path):
     nosp = _run_ranks(tmp_path, 2, ["--training.tp_size", "2"], 29628, **kw)
     assert sp == pytest.approx(one, rel=5e-4, abs=5e-4)
     assert nosp == pytest.approx(one, rel=5e-4, abs=5e-4)
+
+
+@pytest.mark.slow
+def test_vlm_dp2_tp2_matches_dp2(tmp_path):
+    """Four ranks as data-parallel 2 x tensor-parallel 2 (two reduction domains in the optimizer engine: parameters split
+    over TP are reduced over the data-parallel group, replicated ones over the world) follow the 2-rank data-parallel run."""
+    kw = dict(preset="tiny-qwen3-vl-gpu", synthetic="vlm", seq_len="1024")
+    dp2 = _run_ranks(tmp_path, 2, ["--training.data_parallel", "fsdp"], 29629, **kw)
+    dp2tp2 = _run_ranks(tmp_path, 4, ["--training.data_parallel", "fsdp", "--training.tp_size", "2",
+                                      "--training.sequence_parallel", "true"], 29630, **kw)
+    assert dp2tp2 == pytest.approx(dp2, rel=5e-4, abs=5e-4)

@@ -131,11 +131,24 @@ def vlm_row(rng: np.random.Generator, spec: SyntheticSpec, cfg: ModelConfig) -> 
     labels = np.concatenate(lab_all)
     grids = np.asarray(grids_all, dtype=np.int64).reshape(-1, 3)
     n_patches = int((grids[:, 0] * grids[:, 1] * grids[:, 2]).sum())
-    pixels = torch.empty(n_patches, cfg.vision.patch_dim, dtype=getattr(torch, spec.pixel_dtype))
-    gen = torch.Generator().manual_seed(int(rng.integers(0, 2 ** 31 - 1)))
-    pixels.normal_(0.0, 1.0, generator=gen)
+    # patches are drawn (with replacement) from a fixed pool of normal(0, 1) patch vectors: drawing 40 M fresh normals
+    # per row costs about a second of host time, more than a training step, and would make the loader the bottleneck
+    pool = _patch_pool(spec.seed, cfg.vision.patch_dim, spec.pixel_dtype)
+    pixels = pool.index_select(0, torch.from_numpy(rng.integers(0, pool.shape[0], size=n_patches)))
     return {"input_ids": ids, "labels": labels, "cu_seqlens": np.asarray(cu, dtype=np.int32),
             "pixel_values": pixels, "image_grid_thw": grids}
+
+
+_POOLS: dict = {}
+_POOL_ROWS = 8192
+
+
+def _patch_pool(seed: int, patch_dim: int, dtype: str) -> torch.Tensor:
+    key = (seed, patch_dim, dtype)
+    if key not in _POOLS:
+        gen = torch.Generator().manual_seed(1000003 * seed + patch_dim)
+        _POOLS[key] = torch.randn(_POOL_ROWS, patch_dim, generator=gen, dtype=torch.float32).to(getattr(torch, dtype))
+    return _POOLS[key]
 
 
 def host_plan(batch: dict, cfg: ModelConfig) -> dict:

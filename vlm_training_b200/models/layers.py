@@ -20,7 +20,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from ..parallel.tp_comm import TPContext, column_input, row_linear, row_output
+from ..parallel.tp_comm import TPContext, column_input, column_linear, row_linear, row_output
 from .config import TextConfig
 
 _NO_TP = TPContext()
@@ -62,7 +62,7 @@ class Linear(nn.Module):
 
     def forward(self, x):
         if self.parallel == "column":
-            return ops.linear(column_input(x, self.tp), self.weight, self.bias)
+            return column_linear(x, self.weight, self.bias, self.tp)
         if self.parallel == "row":
             y = row_linear(x, self.weight, self.tp)
             return y if self.bias is None else y + self.bias

@@ -78,6 +78,7 @@ struct FwdParams {
   int n_docs, T, Hq, Hkv;
   float scale_log2;   // softmax scale * log2(e)
   int causal;
+  int k_steps;        // 16-channel steps of the Q.K contraction (channels beyond 16 * k_steps are zero padding)
   int* status;
 };
 
@@ -180,6 +181,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t d = tmem_base + S_COL + t * BN;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk >= p.k_steps) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           if (kk == 0) umma_ss<0>(d, a, b, idesc_s); else umma_ss<1>(d, desc_off(a, off), desc_off(b, off), idesc_s);
         }
@@ -360,6 +362,7 @@ struct BwdParams {
   int n_docs, T, Hq, Hkv;
   float scale, scale_log2;
   int causal;
+  int k_steps;        // 16-channel steps of the contractions over the head dim (Q.K and dO.V); the rest is zero padding
   int* status;
   long long* trace;  // timeline dump of CTA (0,0) (only with -DVLMT_ATTN_TRACE; nullptr otherwise)
 };
@@ -504,6 +507,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       auto issue_score = [&](uint32_t dst, SmemDesc a, SmemDesc bq) {  // dst = a (stationary) x bq^T (streamed), both K-major
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk >= p.k_steps) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           if (kk == 0) umma_ss<0>(dst, a, bq, idesc_s); else umma_ss<1>(dst, desc_off(a, off), desc_off(bq, off), idesc_s);
         }
@@ -785,6 +789,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       auto issue_score = [&](uint32_t dst, SmemDesc a, SmemDesc bk) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+          if (kk >= p.k_steps) break;
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           if (kk == 0) umma_ss<0>(dst, a, bk, idesc_s); else umma_ss<1>(dst, desc_off(a, off), desc_off(bk, off), idesc_s);
         }
@@ -976,7 +981,7 @@ extern "C" int vlmt_attn_fwd(const void* q, const void* k, const void* v, void* 
   FwdParams p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o); p.LSE = lse; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
-  (void)d_eff;
+  p.k_steps = (d_eff <= 0 || d_eff > D) ? D / 16 : (d_eff + 15) / 16;
   dim3 grid(T / (2 * BM) + n_docs + 1, Hq);
   if (D == 128) {
     if ((r = set_smem(attn_fwd_kernel<128>, FwdSmem<128>::kTotal))) return r;
@@ -1010,7 +1015,7 @@ extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, con
   p.LSE = lse; p.delta = delta; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
   p.trace = nullptr;
-  (void)d_eff;
+  p.k_steps = (d_eff <= 0 || d_eff > D) ? D / 16 : (d_eff + 15) / 16;
 #ifdef VLMT_ATTN_TRACE
   static long long* trace_buf = nullptr;
   if (!trace_buf) cudaMalloc(&trace_buf, 256 * 16 * sizeof(long long));

@@ -88,6 +88,10 @@ static void pull_reduce(const std::vector<int64_t>& slot_ptrs, Tensor& out, cons
 }
 
 void bind_comm(pybind11::module_& m) {
+  m.def("set_flag_wait_ms", [](int64_t ms) {
+    int r = vlmt_set_flag_wait_ms((long)ms);
+    TORCH_CHECK(r == 0, "vlmt_set_flag_wait_ms failed with code ", r);
+  });
   m.def("signal_peers", &signal_peers);
   m.def("signal_peers_at", &signal_peers_at);
   m.def("wait_flags", &wait_flags);

@@ -145,10 +145,13 @@ __global__ void peer_sum_rows_kernel(PeerPtrs partials, int world, long row0, lo
 // Protocol (per process group, collectives numbered 1, 2, ... in program order, identical on every rank):
 //   every rank copies its contribution into slot (e % n_slots) of its symmetric staging buffer, then `signal`
 //   stores e into flag[my_rank] on EVERY rank (release, system scope); the pull kernel of collective e first
-//   waits (bounded, ~1 s) until all of its own flag[r] >= e, then reads the peers' slots directly over NVLink.
+//   waits (bounded, see g_flag_wait_ns) until all of its own flag[r] >= e, then reads the peers' slots directly over NVLink.
 // A slot is reused n_slots collectives later, by which time every peer has issued (in stream order, after its
 // pull) the signals of the collectives in between, so no extra "done" handshake is needed.
-constexpr unsigned long long kFlagWaitNs = 1000000000ull;
+// Wall-clock bound of a flag wait.  Long enough for an ordinary straggler (a rank that saves a checkpoint, a slow data
+// batch, first-step allocation), short enough that a rank that is gone shows up as an error and not as a hung job.
+// Set once per process from the host (environment variable VLMT_FLAG_WAIT_MS, default 20 s).
+__device__ unsigned long long g_flag_wait_ns = 20000000000ull;
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
@@ -176,7 +179,7 @@ __device__ bool wait_all_flags(const int* my_flags, int world, int epoch, int* s
       if (r == skip) continue;
       unsigned spins = 0;
       while (ld_acquire_sys(my_flags + r) < epoch) {
-        if ((++spins & 0xff) == 0 && gtimer_ns() - t0 > kFlagWaitNs) {
+        if ((++spins & 0xff) == 0 && gtimer_ns() - t0 > g_flag_wait_ns) {
           atomicCAS(status, 0, 100 + r);
           ok = 0;
           break;
@@ -204,12 +207,20 @@ __global__ void wait_flags_kernel(const int* my_flags, int world, int epoch, int
 __global__ void pull_gather_kernel(PeerPtrs slots, bf16* __restrict__ out, long n, int world, const int* my_flags, int epoch,
                                    int* status) {
   if (!wait_all_flags(my_flags, world, epoch, status)) return;
+  // Few blocks (two per SM) with four 16-byte loads in flight per thread: enough bytes in flight to fill NVLink, and few
+  // enough registers and threads that the blocks share the SMs with a GEMM running on another stream.
   const long nvec = n >> 3;
-  const long total = nvec * world;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / nvec);
-    const long v = i - (long)r * nvec;
-    reinterpret_cast<uint4*>(out)[i] = ld_peer_16B(reinterpret_cast<const uint4*>(slots.p[r]) + v);
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (int r = 0; r < world; ++r) {
+    const uint4* src = reinterpret_cast<const uint4*>(slots.p[r]);
+    uint4* dst = reinterpret_cast<uint4*>(out) + (long)r * nvec;
+    long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      const uint4 a = ld_peer_16B(src + i), b = ld_peer_16B(src + i + stride), c = ld_peer_16B(src + i + 2 * stride),
+                  d = ld_peer_16B(src + i + 3 * stride);
+      dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+    }
+    for (; i < nvec; i += stride) dst[i] = ld_peer_16B(src + i);
   }
 }
 
@@ -239,6 +250,10 @@ __global__ void pull_reduce_kernel(PeerPtrs slots, bf16* __restrict__ out, const
 }  // namespace
 
 extern "C" {
+int vlmt_set_flag_wait_ms(long ms) {
+  const unsigned long long ns = (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
+  return (int)cudaMemcpyToSymbol(g_flag_wait_ns, &ns, sizeof(ns));
+}
 int vlmt_signal_peers(void* const* flag_ptrs, int world, int my_rank, int epoch, cudaStream_t st) {
   if (world > MAX_PEERS) return -1;
   PeerPtrs f;
@@ -255,8 +270,8 @@ int vlmt_pull_gather(void* const* slot_ptrs, void* out, long n_per_rank, int wor
   if (world > MAX_PEERS || (n_per_rank & 7)) return -1;
   PeerPtrs s;
   for (int r = 0; r < world; ++r) s.p[r] = slot_ptrs[r];
-  long blocks = ((n_per_rank >> 3) * world + 255) / 256;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  long blocks = ((n_per_rank >> 3) + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;
   pull_gather_kernel<<<(int)blocks, 256, 0, st>>>(s, reinterpret_cast<bf16*>(out), n_per_rank, world, my_flags, epoch, status);
   return (int)cudaGetLastError();
 }

@@ -15,6 +15,8 @@ int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void
 int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st);
 // Signalled peer-to-peer collectives over symmetric staging slots (protocol: comm_kernels.cu).
 // flag_ptrs[r]: address of rank r's int32 flag array (length >= world); my_flags: this rank's own array.
+// bound of every flag wait on the current device, in milliseconds (default 20 000)
+int vlmt_set_flag_wait_ms(long ms);
 int vlmt_signal_peers(void* const* flag_ptrs, int world, int my_rank, int epoch, cudaStream_t st);
 // one-block kernel that returns once my_flags[r] >= epoch for every r < world except skip_rank (-1: none);
 // bounded wait, status word on timeout

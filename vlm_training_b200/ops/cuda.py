@@ -520,13 +520,9 @@ class _AttentionVarlen(torch.autograd.Function):
 
 
 def _mma_width(valid: int, padded: int) -> int:
-    """Channels the attention MMAs cover.  Skipping zero padding (e.g. 80 of 128 for head_dim 72) was measured
-    SLOWER on B200 than full-width MMAs (N = 80 is an inefficient instruction shape), so only padding of at least
-    half the tile is skipped (N = 64)."""
-    forced = os.environ.get("VLMT_ATTN_MMA_WIDTH")
-    if forced:
-        return max(min(int(forced), padded), (valid + 15) // 16 * 16)
-    return 64 if valid <= 64 < padded else padded
+    """Channels the head-dim contractions of the attention kernels cover: the padding beyond ``valid`` (rounded up to
+    the MMA's 16-channel step) is skipped."""
+    return min(padded, (valid + 15) // 16 * 16)
 
 
 def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None, valid_dim=None):

@@ -17,7 +17,7 @@ optimizer step number:
 * after its last bucket a rank signals row ``DONE``; before the next forward (and before gradients are cleared) every
   rank waits for all ``DONE`` signals: all pushes have landed and nobody still reads this step's gradients.
 
-Every wait is bounded (about a second) and reports through the status word instead of hanging.
+Every wait is bounded (``VLMT_FLAG_WAIT_MS``, default 20 s) and reports through the status word instead of hanging.
 """
 from __future__ import annotations
 
@@ -34,6 +34,7 @@ class FusedStepState:
         self.engine = engine
         dev = engine.device
         self.signal_stream = torch.cuda.Stream(device=dev)
+        symm.apply_flag_wait_limit()
         self.domains = []
         for d in engine.domains:
             info = {"domain": d, "flags": None}

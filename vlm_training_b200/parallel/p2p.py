@@ -7,7 +7,7 @@ collective's sequence number into every peer's flag array, release/system scope)
 (bounded) for all signals and then reads the peers' slots directly (``ops/csrc/comm_kernels.cu``).  The
 reduce-scatter kernel accumulates in fp32 and can add a residual in the same pass.
 
-A waiting kernel gives up after about a second and writes a status word (read by ``ops.cuda.check_status``)
+A waiting kernel gives up after a bounded time (``VLMT_FLAG_WAIT_MS``, default 20 s) and writes a status word (read by ``ops.cuda.check_status``)
 instead of spinning forever, so a rank that left shows up as a Python exception on the survivors.
 """
 from __future__ import annotations
@@ -29,6 +29,8 @@ class P2PComm:
         self.slot_elems = 0
         self.flags = symm.symmetric_zeros(64, torch.int32, device, group)
         self.flag_ptrs = symm.peer_ptrs(self.flags)
+        self.side = torch.cuda.Stream(device=device)  # pulls that overlap the caller's compute
+        symm.apply_flag_wait_limit()
         self._alloc(slot_elems)
 
     def _alloc(self, slot_elems: int):
@@ -59,6 +61,39 @@ class P2PComm:
         cu._C.pull_gather(ptrs, out, n, self.flags.data_ptr(), e)
         cu._tick(2)
         return out
+
+    def all_gather_rows_async(self, x: torch.Tensor):
+        """Like :meth:`all_gather_rows`, but the pull runs on this object's side stream: returns ``(out, event)``; the
+        caller's stream must wait for ``event`` before it reads rows other than its own (which it still holds in ``x``),
+        and can compute on its own rows meanwhile."""
+        from ..ops import cuda as cu
+
+        x = x.contiguous()
+        n = x.numel()
+        e, slot, ptrs = self._slot(n)
+        slot.copy_(x.view(-1))
+        cu._C.signal_peers(self.flag_ptrs, self.rank, e)
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        out = x.new_empty((x.shape[0] * self.world,) + tuple(x.shape[1:]))
+        out.record_stream(self.side)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)
+            cu._C.pull_gather(ptrs, out, n, self.flags.data_ptr(), e)
+            done = torch.cuda.Event()
+            done.record(self.side)
+        cu._tick(2)
+        return out, done
+
+    def reduce_scatter_begin(self, rows_total: int, width: int):
+        """Reduce-scatter in two halves around the caller's compute: returns ``(buf, finish)``.  The caller writes its
+        ``[rows_total, width]`` partial result into ``buf`` (this rank's staging slot, so no extra copy), calls
+        ``finish.signal()`` as soon as the row blocks of the OTHER ranks are written, goes on to write its own block (and
+        to do unrelated work), and finally calls ``finish.result(residual)``."""
+        n = rows_total * width
+        e, slot, ptrs = self._slot(n)
+        return slot.view(rows_total, width), _ReduceScatterHandle(self, e, ptrs, rows_total // self.world, width)
 
     def reduce_scatter_rows(self, y: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         from ..ops import cuda as cu
@@ -102,6 +137,25 @@ class P2PComm:
     def gemm_rs_usable(self, x, w) -> bool:
         return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and x.shape[0] % (128 * self.world) == 0 and w.shape[0] % 8 == 0 and x.shape[1] % 8 == 0)
+
+
+class _ReduceScatterHandle:
+    def __init__(self, comm: P2PComm, epoch: int, ptrs, rows: int, width: int):
+        self.comm, self.epoch, self.ptrs, self.rows, self.width = comm, epoch, ptrs, rows, width
+
+    def signal(self):
+        from ..ops import cuda as cu
+
+        cu._C.signal_peers(self.comm.flag_ptrs, self.comm.rank, self.epoch)
+
+    def result(self, like: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        from ..ops import cuda as cu
+
+        out = like.new_empty((self.rows, self.width))
+        cu._C.pull_reduce(self.ptrs, out, residual.contiguous() if residual is not None else None, self.rows * self.width,
+                          self.comm.rank, self.comm.flags.data_ptr(), self.epoch)
+        cu._tick(2)
+        return out
 
 
 def usable(x: torch.Tensor, ctx) -> bool:

@@ -52,3 +52,10 @@ def multicast_ptr(t: torch.Tensor) -> int:
             return int(hdl.multicast_ptr)
         except Exception:
             return 0
+
+
+def apply_flag_wait_limit():
+    """Set the bound of the in-kernel flag waits of the current device from ``VLMT_FLAG_WAIT_MS`` (default 20 000)."""
+    from ..ops import cuda as cu
+
+    cu._C.set_flag_wait_ms(int(os.environ.get("VLMT_FLAG_WAIT_MS", "20000")))

@@ -190,6 +190,84 @@ def gather_uneven(x, sizes, ctx: TPContext, grad_identical: bool = False):
     return _GatherUneven.apply(x, list(sizes), ctx, grad_identical) if ctx.enabled else x
 
 
+def _row_blocks(rank: int, size: int, rows: int):
+    """Row ranges of the other ranks' blocks (at most two contiguous ranges) and of this rank's block."""
+    others = []
+    if rank > 0:
+        others.append((0, rank * rows))
+    if rank < size - 1:
+        others.append(((rank + 1) * rows, size * rows))
+    return others, (rank * rows, (rank + 1) * rows)
+
+
+def _gathered_gemm(x_local, w, ctx, b_mn=False):
+    """``all_gather_rows(x_local) @ op(w)`` with the gather overlapped: the product of this rank's own rows needs no
+    communication and runs while the side stream pulls the peers' rows.  Returns ``(y_full, x_full)``."""
+    from ..ops import cuda as cu
+
+    R = x_local.shape[0]
+    x_full, done = ctx.p2p.all_gather_rows_async(x_local)
+    others, (o0, o1) = _row_blocks(ctx.rank, ctx.size, R)
+    n_out = w.shape[1] if b_mn else w.shape[0]
+    y = x_local.new_empty((R * ctx.size, n_out))
+    cu._gemm(x_local, w, b_mn=b_mn, out=y[o0:o1])
+    torch.cuda.current_stream().wait_event(done)
+    for a, b in others:
+        cu._gemm(x_full[a:b], w, b_mn=b_mn, out=y[a:b])
+    return y, x_full
+
+
+class _GatherLinear(torch.autograd.Function):
+    """Column-parallel linear on a sequence-parallel input: ``all_gather_rows(x) @ w.T`` with the collectives overlapped.
+    Forward: own rows first while the peers' rows arrive.  Backward: the input-gradient blocks that belong to the other
+    ranks are computed first and announced, the own block and the weight gradient follow, and the reduce-scatter
+    completes at the end, when the peers' blocks have long been written."""
+
+    @staticmethod
+    def forward(fctx, x, w, ctx):
+        y, x_full = _gathered_gemm(x, w, ctx)
+        fctx.tp = ctx
+        fctx.save_for_backward(x_full, w)
+        return y
+
+    @staticmethod
+    def backward(fctx, dy):
+        from ..ops import cuda as cu
+
+        ctx = fctx.tp
+        x_full, w = fctx.saved_tensors
+        dy = dy.contiguous()
+        T, K = x_full.shape
+        dx = None
+        if fctx.needs_input_grad[0]:
+            buf, handle = ctx.p2p.reduce_scatter_begin(T, K)
+            others, (o0, o1) = _row_blocks(ctx.rank, ctx.size, T // ctx.size)
+            for a, b in others:
+                cu._gemm(dy[a:b], w, b_mn=True, out=buf[a:b])
+            handle.signal()
+            cu._gemm(dy[o0:o1], w, b_mn=True, out=buf[o0:o1])
+        dw = cu._gemm(dy, x_full, a_mn=True, b_mn=True) if fctx.needs_input_grad[1] else None
+        if fctx.needs_input_grad[0]:
+            dx = handle.result(dy)
+        return dx, dw, None
+
+
+def gather_linear_usable(x, weight, bias, ctx: TPContext) -> bool:
+    return (ctx.enabled and ctx.sequence_parallel and ctx.p2p is not None and bias is None and x.is_cuda
+            and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous() and x.shape[0] % 128 == 0
+            and x.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0)
+
+
+def column_linear(x, weight, bias, ctx: TPContext):
+    """``linear(column_input(x), weight, bias)``; on the peer-to-peer backend with sequence parallelism the all-gather
+    is overlapped with the product of the local rows."""
+    if gather_linear_usable(x, weight, bias, ctx):
+        return _GatherLinear.apply(x, weight, ctx)
+    from .. import ops
+
+    return ops.linear(column_input(x, ctx), weight, bias)
+
+
 class _RowLinearReduceScatter(torch.autograd.Function):
     """Row-parallel linear whose reduce-scatter is fused into the GEMM epilogue (sequence-parallel output
     ``[T/tp, out]``).  Backward: all-gather ``dy`` (peer pull), then the usual dgrad / wgrad GEMMs."""
@@ -205,8 +283,10 @@ class _RowLinearReduceScatter(torch.autograd.Function):
         from ..ops import cuda as cu
 
         x, w = fctx.saved_tensors
-        dy_full = _all_gather_rows(dy.contiguous(), fctx.tp)
-        dx = cu._gemm(dy_full, w, b_mn=True) if fctx.needs_input_grad[0] else None
+        if fctx.needs_input_grad[0]:
+            dx, dy_full = _gathered_gemm(dy.contiguous(), w, fctx.tp, b_mn=True)   # gather overlapped with the own rows
+        else:
+            dx, dy_full = None, _all_gather_rows(dy.contiguous(), fctx.tp)
         dw = cu._gemm(dy_full, x, a_mn=True, b_mn=True) if fctx.needs_input_grad[1] else None
         return dx, dw, None
 
