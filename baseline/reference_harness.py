@@ -134,7 +134,10 @@ def run(args):
     if ac_mode != "off":
         apply_ac(model.model.language_model, ACConfig(enabled=True, full=(ac_mode == "full")), model_compile_enabled=False)
     apply_fsdp(ModelType.Qwen3_vl, model, mesh=dp_group)
-    compiled = os.environ.get("REF_COMPILE", "0") == "1"
+    # torch.compile is the reference's default (train/config.py:110) and is applied after FSDP as its trainer does
+    # (train/train_qwen.py:196-209); REF_COMPILE=0 runs it eagerly.  If compilation fails on this box the harness
+    # re-executes itself eagerly and says so in its output.
+    compiled = os.environ.get("REF_COMPILE", "1") == "1"
     if compiled:
         compile_model(model)
     # optimizer exactly as the reference builds it (every non-merger parameter lands in the lr_mlp group)
@@ -188,6 +191,19 @@ def run(args):
 
     try:
         staged = [to_dev(host_batch()) for _ in range(max(2, min(4, args.steps)))]
+        if compiled:
+            try:  # extra untimed steps so that (re)compilation for the row shapes is over before the warm-up proper
+                for i in range(len(staged) + 2):
+                    step(staged[i % len(staged)])
+            except torch.OutOfMemoryError:
+                raise
+            except Exception as exc:
+                sys.stderr.write(f"[reference harness] torch.compile failed ({type(exc).__name__}: {str(exc)[:200]}); "
+                                 "re-running eagerly\n")
+                sys.stderr.flush()
+                os.environ["REF_COMPILE"] = "0"
+                os.environ["REF_COMPILE_FAILED"] = "1"
+                os.execv(sys.executable, [sys.executable] + sys.argv)
         for i in range(args.warmup):
             step(staged[i % len(staged)])
         barrier()
@@ -239,6 +255,8 @@ def run(args):
             "impl": "reference", "tokens_per_sec_per_gpu": value / world,
             "config": {"model": args.model, "global_batch": dp_size, "seq_len": args.seq_len, "parallelism": f"fsdp{dp_size}xtp{tp}",
                        "ac_mode": ac_mode, "compile": compiled, "optimizer": "torch AdamW foreach on bf16 parameters",
-                       "layers_override": args.layers or None, "note": note},
+                       "layers_override": args.layers or None,
+                       "note": "; ".join(x for x in (note, "torch.compile failed on this box, measured eagerly"
+                                                     if os.environ.get("REF_COMPILE_FAILED") == "1" else None) if x) or None},
             "clocks": clocks, "e2e": e2e, "gpu_launches": 0, "peak_mem_gib": peak, "final_loss": float(loss.item())}))
     dist.destroy_process_group()

@@ -30,6 +30,7 @@ CASES = [
     ([700], 8, 2, 128, False),
     ([1500, 260, 40], 2, 1, 128, True),
     ([900, 130], 2, 2, 64, False),
+    ([300, 200], 4, 2, 256, True),         # head dims above 128 take the library path
 ]
 
 

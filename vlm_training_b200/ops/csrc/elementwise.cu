@@ -833,49 +833,72 @@ __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf1
   const int half = R >> 1;
   const int plane = half / E;  // partner lane distance
   const bool vec_cs = (R % E) == 0 && (R % 4) == 0;  // a lane's E angles are all inside or all outside [0, R), 16-byte aligned rows
-  for (long item = blockIdx.x * (long)kWarpsPerBlock + warp; item < total; item += (long)gridDim.x * kWarpsPerBlock) {
-    const int t = (int)(item / slots);
-    const int s = (int)(item - (long)t * slots);
-    const bf16* row = qkv + (size_t)t * W;
-    const bf16* src;
-    bf16* dst;
-    const bf16* wn = nullptr;
-    int kind;  // 0 q, 1 k, 2 v
-    if (s < n_q) { src = row + s * qstride; dst = q + ((size_t)t * n_q + s) * D; wn = qw; kind = 0; }
-    else if (s < n_q + n_kv) { const int h = s - n_q; src = row + n_q * qstride + h * D; dst = k + ((size_t)t * n_kv + h) * D; wn = kw; kind = 1; }
-    else { const int h = s - n_q - n_kv; src = row + n_q * qstride + n_kv * D + h * D; dst = v + ((size_t)t * n_kv + h) * D; kind = 2; }
-    if (kind == 2) {
-      cpE<E>(dst + lane * E, src + lane * E);
-      continue;
-    }
-    float f[E];
-    ldE<E>(src + lane * E, f);
-    if (kind == 0 && gated) cpE<E>(gate + ((size_t)t * n_q + s) * D + lane * E, src + D + lane * E);
-    if (has_norm) {
-      float ss = 0.f;
+  // Four (token, head) items per warp and iteration, all loads first: a single 256-byte item in flight per warp leaves
+  // the kernel latency-bound.
+  constexpr int U = 4;
+  using Raw = typename VecE<E>::T;
+  for (long base = (blockIdx.x * (long)kWarpsPerBlock + warp) * U; base < total; base += (long)gridDim.x * kWarpsPerBlock * U) {
+    const bf16* src[U];
+    bf16* dst[U];
+    const bf16* wn[U];
+    int tt[U], sl[U], kind[U];  // kind: 0 q, 1 k, 2 v, -1 none
+    Raw raw[U], graw[U];
 #pragma unroll
-      for (int i = 0; i < E; ++i) ss += f[i] * f[i];
-      const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
-      if (lane == 0) rstd[(size_t)t * (n_q + n_kv) + s] = rs;
-      float wv[E];
-      ldE<E>(wn + lane * E, wv);
+    for (int u = 0; u < U; ++u) {
+      const long item = base + u;
+      kind[u] = -1;
+      if (item >= total) continue;
+      const int t = (int)(item / slots);
+      const int s = (int)(item - (long)t * slots);
+      const bf16* row = qkv + (size_t)t * W;
+      tt[u] = t; sl[u] = s; wn[u] = nullptr;
+      if (s < n_q) { src[u] = row + s * qstride; dst[u] = q + ((size_t)t * n_q + s) * D; wn[u] = qw; kind[u] = 0; }
+      else if (s < n_q + n_kv) { const int h = s - n_q; src[u] = row + n_q * qstride + h * D; dst[u] = k + ((size_t)t * n_kv + h) * D; wn[u] = kw; kind[u] = 1; }
+      else { const int h = s - n_q - n_kv; src[u] = row + n_q * qstride + n_kv * D + h * D; dst[u] = v + ((size_t)t * n_kv + h) * D; kind[u] = 2; }
+      raw[u] = *reinterpret_cast<const Raw*>(src[u] + lane * E);
+      if (kind[u] == 0 && gated) graw[u] = *reinterpret_cast<const Raw*>(src[u] + D + lane * E);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (kind[u] < 0) continue;
+      if (kind[u] == 2) {
+        *reinterpret_cast<Raw*>(dst[u] + lane * E) = raw[u];
+        continue;
+      }
+      const int t = tt[u], s = sl[u];
+      if (kind[u] == 0 && gated) *reinterpret_cast<Raw*>(gate + ((size_t)t * n_q + s) * D + lane * E) = graw[u];
+      float f[E];
+      {
+        const bf16* h = reinterpret_cast<const bf16*>(&raw[u]);
+#pragma unroll
+        for (int i = 0; i < E; ++i) f[i] = __bfloat162float(h[i]);
+      }
+      if (has_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < E; ++i) ss += f[i] * f[i];
+        const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+        if (lane == 0) rstd[(size_t)t * (n_q + n_kv) + s] = rs;
+        float wv[E];
+        ldE<E>(wn[u] + lane * E, wv);
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+          // round to bf16 between norm and rotary like the unfused sequence of ops
+          f[i] = __bfloat162float(__float2bfloat16(f[i] * rs * (offset ? 1.f + wv[i] : wv[i])));
+        }
+      }
+      // rotary on channels [0, R)
+      float c[E], sn[E], o[E];
+      ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
+      ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
 #pragma unroll
       for (int i = 0; i < E; ++i) {
-        // round to bf16 between norm and rotary like the unfused sequence of ops
-        f[i] = __bfloat162float(__float2bfloat16(f[i] * rs * (offset ? 1.f + wv[i] : wv[i])));
+        const int j = lane * E + i;
+        const float partner = __shfl_xor_sync(0xffffffffu, f[i], plane);
+        o[i] = j < R ? f[i] * c[i] + (j < half ? -partner : partner) * sn[i] : f[i];
       }
+      stE<E>(dst[u] + lane * E, o);
     }
-    // rotary on channels [0, R)
-    float c[E], sn[E], o[E];
-    ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
-    ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
-#pragma unroll
-    for (int i = 0; i < E; ++i) {
-      const int j = lane * E + i;
-      const float partner = __shfl_xor_sync(0xffffffffu, f[i], plane);
-      o[i] = j < R ? f[i] * c[i] + (j < half ? -partner : partner) * sn[i] : f[i];
-    }
-    stE<E>(dst + lane * E, o);
   }
 }
 
@@ -1181,6 +1204,15 @@ inline int grid_for(long work_items, int per_block, int cap) {
 #define BF(p) reinterpret_cast<const bf16*>(p)
 #define BFM(p) reinterpret_cast<bf16*>(p)
 
+// grid of a forward row-tile kernel: one wave of resident blocks (a second, partly filled wave costs a whole pass)
+template <typename K>
+static int tile_grid(K kernel, int rows) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRT, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return grid_for(rows, kRR, sms * per_sm);
+}
 extern "C" {
 
 int vlmt_norm_blocks(int rows) { return grid_for(rows, kWarpsPerBlock, 148 * 4); }
@@ -1205,8 +1237,7 @@ void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32,
   if (rows <= 0) return;
   const int vpt = tile_vpt(D);
   if (vpt) {
-    const int grid = grid_for(rows, kRR, 148 * 4);
-#define RF(WT, V) rmsnorm_fwd_tile_kernel<WT, V><<<grid, kRT, 0, st>>>(BF(x), BF(res), (const WT*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset)
+#define RF(WT, V) rmsnorm_fwd_tile_kernel<WT, V><<<tile_grid(rmsnorm_fwd_tile_kernel<WT, V>, rows), kRT, 0, st>>>(BF(x), BF(res), (const WT*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset)
     if (w_fp32) TILE_DISPATCH(vpt, RF(float, 1), RF(float, 2), RF(float, 4));
     else TILE_DISPATCH(vpt, RF(bf16, 1), RF(bf16, 2), RF(bf16, 4));
 #undef RF
@@ -1252,8 +1283,7 @@ void vlmt_layernorm_fwd(const void* x, const void* w, const void* b, void* y, fl
   if (rows <= 0) return;
   const int vpt = tile_vpt(D);
   if (vpt) {
-    const int grid = grid_for(rows, kRR, 148 * 4);
-#define LF(V) layernorm_fwd_tile_kernel<V><<<grid, kRT, 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps)
+#define LF(V) layernorm_fwd_tile_kernel<V><<<tile_grid(layernorm_fwd_tile_kernel<V>, rows), kRT, 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps)
     TILE_DISPATCH(vpt, LF(1), LF(2), LF(4));
 #undef LF
     return;
@@ -1315,7 +1345,7 @@ int vlmt_qkv_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, cons
                            int has_norm, cudaStream_t st) {
   const int E = D / 32;
   if (D % 32 || R > D || (R / 2) % E || (((R / 2) / E) & ((R / 2) / E - 1)) || (R / 2) / E >= 32) return -1;
-  const int grid = vlmt_qkv_blocks((long)T * (n_q + 2 * n_kv));
+  const int grid = vlmt_qkv_blocks(((long)T * (n_q + 2 * n_kv) + 3) / 4);  // four items per warp and iteration
 #define LAUNCH(E_)                                                                                                              \
   qkv_norm_rope_fwd_kernel<E_><<<grid, kThreads, 0, st>>>(BF(qkv), BF(qw), BF(kw), cosv, sinv, BFM(q), BFM(k), BFM(v), BFM(gate), \
                                                           rstd, T, n_q, n_kv, R, eps, offset, gated, has_norm)

@@ -542,7 +542,13 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None, v
         o = _AttentionVarlen.apply(_pad_heads(q, 128), _pad_heads(k, 128), _pad_heads(v, 128), cu, int(max_seqlen),
                                    bool(causal), float(scale), _mma_width(D, 128))
         return o[..., :D]
-    raise NotImplementedError(f"attention head_dim {D}")
+    # head dims above 128 (Qwen3.5 full-attention layers use 256) exceed the tensor-memory budget of the kernels above
+    # (two 128-row score tiles plus two output accumulators of D columns each); they run through torch's library
+    # varlen attention until a single-tile variant exists
+    from torch.nn.attention.varlen import varlen_attn
+
+    return varlen_attn(q, k, v, cu, cu, int(max_seqlen), int(max_seqlen), scale=float(scale),
+                       window_size=(-1, 0) if causal else (-1, -1))
 
 
 def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None):

@@ -162,6 +162,7 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
+    ap.add_argument("--rows", type=int, default=8192, help="rows / tokens of the row-wise kernels (rmsnorm, swiglu, qkv_rope)")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--docs", type=int, default=1)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -177,11 +178,11 @@ def main(argv=None):
     elif a.what == "attention":
         bench_attention(t, a.tokens, a.docs, d=a.head_dim, causal=not a.non_causal, backward=a.backward)
     elif a.what == "rmsnorm":
-        bench_rmsnorm(t)
+        bench_rmsnorm(t, rows=a.rows)
     elif a.what == "swiglu":
-        bench_swiglu(t)
+        bench_swiglu(t, rows=a.rows)
     elif a.what == "qkv_rope":
-        bench_qkv_rope(t)
+        bench_qkv_rope(t, tokens=a.rows)
     elif a.what == "ce":
         bench_ce(t)
     elif a.what == "adamw":
