@@ -94,7 +94,8 @@ def build_config(args, world: int):
     from vlm_training_b200.config import Config
 
     cfg = Config()
-    cfg.model.model_name, cfg.model.preset = "Qwen3-VL-8B", args.model
+    name = "Qwen3-VL-8B" if "vl" in args.model else ("Qwen3.5-9B" if "3.5" in args.model else "Qwen3-8B")
+    cfg.model.model_name, cfg.model.preset = name, args.model
     cfg.model.train_llm = cfg.model.train_mlp = cfg.model.train_vit = True
     t = cfg.training
     tp = args.tp if args.tp else (1 if world == 1 else 2)
@@ -235,10 +236,11 @@ def run_ours(args):
     if rank == 0:
         n = world
         line = {
-            "metric": "tokens/sec (whole job), Qwen3-VL-8B-shaped VLM training step", "value": value, "unit": "tokens/s",
+            "metric": f"tokens/sec (whole job), {cfg.model.model_name}-shaped {'VLM ' if cfg.data.synthetic == 'vlm' else ''}training step", "value": value, "unit": "tokens/s",
             "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (value / n / BASELINE_TOKENS_PER_SEC_PER_GPU) if BASELINE_TOKENS_PER_SEC_PER_GPU else None,
-            "dtype": "bf16", "data": "synthetic packed multimodal rows, random-init weights", "impl": "ours",
+            "dtype": "bf16", "data": ("synthetic packed multimodal rows" if cfg.data.synthetic == "vlm" else "synthetic packed text rows")
+                                     + ", random-init weights", "impl": "ours",
             "tokens_per_sec_per_gpu": value / n,
             "mfu_vs_measured_sustained": value * flops_tok / n / tr.peak_flops,
             "config": {"model": args.model, "global_batch": int(round(global_tokens / args.seq_len)), "seq_len": args.seq_len,

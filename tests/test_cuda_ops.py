@@ -414,3 +414,31 @@ def test_layer_norm_linear_and_gelu_linear_match_unfused():
     _close(b2.grad, b2r.grad, 0.5, 4e-2, "db2")
     _close(lw.grad, lwr.grad, 1.0, 4e-2, "dln_w")
     _close(lb.grad, lbr.grad, 1.0, 4e-2, "dln_b")
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(300, 256, 128, 8, 2), (1000, 512, 256, 16, 4), (40, 128, 64, 8, 2)])
+def test_moe_experts_grouped_gemm(T, H, I, E, k):
+    """All experts in one grouped-GEMM launch per projection (some experts get no tokens) against the per-expert
+    fp32 statement: outputs and the gradients of tokens, routing weights and both expert weight tensors."""
+    cu = _cu()
+    torch.manual_seed(0)
+    x = _rand(T, H).requires_grad_()
+    gate_up = _rand(E, 2 * I, H, scale=0.05).requires_grad_()
+    down = _rand(E, H, I, scale=0.05).requires_grad_()
+    logits = torch.randn(T, E, device=DEV)
+    logits[:, E - 2:] = -1e9                      # the last two experts stay empty
+    w, idx = ops.moe_router(logits, k, True)
+    w = w.detach().to(torch.bfloat16).requires_grad_()
+    out = ops.moe_experts(x, gate_up, down, w, idx)
+    g = _rand(T, H)
+    out.backward(g)
+    cu.check_status()
+    xr, gur, dr, wr = (t.detach().float().requires_grad_() for t in (x, gate_up, down, w))
+    out_r = ref.moe_experts(xr, gur, dr, wr, idx)
+    out_r.backward(g.float())
+    _close(out, out_r, 0.03, 3e-2, "out")
+    _close(x.grad, xr.grad, 0.03, 3e-2, "dx")
+    _close(w.grad, wr.grad, 0.5, 5e-2, "dw_routing")   # a dot product of two bf16 rows of H elements
+    _close(gate_up.grad, gur.grad, 0.3, 5e-2, "dgate_up")   # bf16 products summed over an expert's rows
+    _close(down.grad, dr.grad, 0.3, 5e-2, "ddown")
+    assert float(gate_up.grad[E - 1].abs().max()) == 0.0 and float(down.grad[E - 2].abs().max()) == 0.0

@@ -48,14 +48,15 @@ def _draw_len(rng: np.random.Generator, spec: SyntheticSpec) -> int:
     return int(round(math.exp(rng.uniform(math.log(lo), math.log(hi)))))
 
 
-def text_row(rng: np.random.Generator, spec: SyntheticSpec) -> dict:
+def text_row(rng: np.random.Generator, spec: SyntheticSpec, vocab: int | None = None) -> dict:
     """One packed row of exactly ``seq_len`` tokens: documents are drawn until the row
-    is full and the last one is cut to fit."""
+    is full and the last one is cut to fit.  ``vocab``: ids are drawn below it (models with vision token ids pass the
+    smallest special id so that text rows hold no image tokens)."""
     L = spec.seq_len
     cu = [0]
     while cu[-1] < L:
         cu.append(min(L, cu[-1] + max(1, _draw_len(rng, spec))))
-    ids = rng.integers(0, spec.vocab_size, size=L, dtype=np.int64)
+    ids = rng.integers(0, vocab or spec.vocab_size, size=L, dtype=np.int64)
     labels = ids.copy()
     labels[np.asarray(cu[:-1])] = -100
     return {"input_ids": ids, "labels": labels, "cu_seqlens": np.asarray(cu, dtype=np.int32)}
@@ -183,7 +184,8 @@ class SyntheticDataset:
         return self
 
     def __next__(self) -> dict:
-        row = vlm_row(self.rng, self.spec, self.cfg) if self.spec.kind == "vlm" else text_row(self.rng, self.spec)
+        row = vlm_row(self.rng, self.spec, self.cfg) if self.spec.kind == "vlm" else text_row(self.rng, self.spec,
+                                                                                                 _text_vocab(self.spec, self.cfg))
         host = host_plan(row, self.cfg)
         ids = torch.from_numpy(row["input_ids"])
         batch = {

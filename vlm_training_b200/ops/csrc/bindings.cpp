@@ -73,6 +73,32 @@ void gemm_rs_push(const Tensor& a, const Tensor& b, const std::vector<int64_t>& 
   TORCH_CHECK(r == 0, "vlmt_gemm_bf16_rs_push failed with code ", r);
 }
 
+// grouped GEMM over padded row groups (see gemm_sm100.h); prefix: int32 device tensor [groups + 1]
+void gemm_grouped(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& prefix, int64_t mode, bool b_mn) {
+  check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(out, "out");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1);
+  TORCH_CHECK(prefix.scalar_type() == at::kInt && prefix.is_cuda() && prefix.is_contiguous());
+  c10::cuda::CUDAGuard guard(a.device());
+  const int groups = (int)prefix.numel() - 1;
+  int M, N, K;
+  bool a_mn = false;
+  if (mode == 1) {           // out[cap, N] = a[cap, K] x B_g
+    M = a.size(0); K = a.size(1);
+    N = b_mn ? b.size(1) : b.size(0) / groups;
+    TORCH_CHECK((b_mn ? b.size(0) / groups : b.size(1)) == K, "contraction sizes differ");
+    TORCH_CHECK(out.size(0) == M && out.size(1) == N, "bad output shape");
+  } else {                   // out[g * M + m, n] = sum_rows a[row, m] b[row, n]
+    a_mn = true; b_mn = true;
+    K = a.size(0); M = a.size(1); N = b.size(1);
+    TORCH_CHECK(b.size(0) == K && out.size(0) == (int64_t)M * groups && out.size(1) == N, "bad shapes");
+  }
+  Tensor st = status_tensor();
+  int r = vlmt_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), prefix.data_ptr<int>(), groups, (int)mode, M, N, K,
+                                 (int)a.stride(0), (int)b.stride(0), (int)out.stride(0), a_mn, b_mn, st.data_ptr<int>(), num_sms(),
+                                 cur_stream());
+  TORCH_CHECK(r == 0, "vlmt_gemm_bf16_grouped failed with code ", r);
+}
+
 // ------------------------------------------------------------------ norms
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& res, const Tensor& w, double eps, bool offset) {
   check_bf16(x, "x"); check_contig(x, "x");
@@ -369,6 +395,7 @@ void bind_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_rs_push", &gemm_rs_push);
+  m.def("gemm_grouped", &gemm_grouped);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("layernorm_fwd", &layernorm_fwd);

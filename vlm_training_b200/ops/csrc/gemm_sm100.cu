@@ -53,8 +53,26 @@ struct Params {
   // into rs_dst[o] (a buffer in rank o's memory, reached over NVLink), so the transfer overlaps the remaining tiles
   int rs_world, rs_rows;
   __nv_bfloat16* rs_dst[8];
+  // Grouped GEMM (one launch for all experts of a MoE layer).  Rows of every group are padded to whole 128-row tiles
+  // and laid out back to back; grp_prefix[g] (device memory, G + 1 ints) is the first tile of group g.
+  //   grp_mode 1 (forward / dgrad): groups partition the M dimension; group g multiplies its rows with its own B
+  //                                 (B rows g * grp_b_rows ...).  The number of M tiles is read from grp_prefix[G].
+  //   grp_mode 2 (wgrad):           groups partition the K dimension (the padded rows); group g produces its own
+  //                                 [M, N] output at D rows g * M ...; an empty group writes zeros.
+  const int* grp_prefix;
+  int grp_count, grp_mode, grp_b_rows;
   int* status;
 };
+
+// group that owns M tile `tm`: largest g with prefix[g] <= tm
+__device__ __forceinline__ int group_of_tile(const int* __restrict__ prefix, int G, int tm) {
+  int lo = 0, hi = G - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (prefix[mid] <= tm) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
 
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
@@ -88,9 +106,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_m = p.grp_mode == 1 ? p.grp_prefix[p.grp_count] : (p.M + BM - 1) / BM;
+  const int tiles_per_group = tiles_m * tiles_n;                       // grp_mode 2: one [M, N] output per group
+  const int num_tiles = p.grp_mode == 2 ? tiles_per_group * p.grp_count : tiles_per_group;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int m_limit = p.grp_mode == 1 ? tiles_m * BM : p.M;           // rows that exist
   constexpr int TMEM_COLS = 2 * BN;  // 256 or 512: a power of two >= 32
 
   if (threadIdx.x == 0) {
@@ -113,9 +134,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn; tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        int tm, tn, kb_lo = 0, kb_hi = num_kb, b_row = 0;
+        if (p.grp_mode == 2) {
+          const int g = tile / tiles_per_group;
+          tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
+          kb_lo = p.grp_prefix[g] * (BM / BK);
+          kb_hi = p.grp_prefix[g + 1] * (BM / BK);
+        } else {
+          tile_coords(tile, tiles_m, tiles_n, tm, tn);
+          if (p.grp_mode == 1) b_row = group_of_tile(p.grp_prefix, p.grp_count, tm) * p.grp_b_rows;
+        }
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
@@ -131,11 +161,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (!B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 128; ++j)                                   // boxes {64 k, 128 n}
-              tma_load_2d(sb + j * 16384, &tmap_b, &full_bar[stage], k0, n0 + 128 * j);
+              tma_load_2d(sb + j * 16384, &tmap_b, &full_bar[stage], k0, b_row + n0 + 128 * j);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)                                    // boxes {64 n, 64 k}
-              tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + 64 * j, k0);
+              tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + 64 * j, b_row + k0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -154,7 +184,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb_lo = 0, kb_hi = num_kb;
+        if (p.grp_mode == 2) {
+          const int g = tile / tiles_per_group;
+          kb_lo = p.grp_prefix[g] * (BM / BK);
+          kb_hi = p.grp_prefix[g + 1] * (BM / BK);
+        }
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
@@ -163,7 +199,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, ((kb - kb_lo) | k) != 0);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -177,7 +213,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
-      int tm, tn; tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      int tm, tn, d_row0 = 0;
+      bool empty_group = false;   // grp_mode 2: no rows for this group, the accumulator was never written -> zeros
+      if (p.grp_mode == 2) {
+        const int g = tile / tiles_per_group;
+        tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
+        d_row0 = g * p.M;
+        empty_group = p.grp_prefix[g + 1] == p.grp_prefix[g];
+      } else {
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      }
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
@@ -185,7 +230,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      const bool row_ok = row < p.M;
+      const bool row_ok = row < m_limit;
       if (p.tma_store) {
         // 64-column slabs: TMEM -> registers -> (bias / GELU) -> bf16 -> swizzled smem -> one TMA store per slab and warp
         uint8_t* stage = smem + L::kOutOffset + q * 8192;
@@ -203,7 +248,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tmem_ld_wait();
             float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 32; ++i) v[i] = empty_group ? 0.f : __uint_as_float(r[i]);
             if (p.bias != nullptr) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) if (col0 + h * 32 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + h * 32 + i]);
@@ -228,7 +273,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           fence_async_proxy();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_d, buf, col0, tm * BM + q * 32);
+            tma_store_2d(&tmap_d, buf, col0, d_row0 + tm * BM + q * 32);
             tma_store_commit();
           }
         }
@@ -375,8 +420,8 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < num_sms ? tiles : num_sms;
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.grp_mode == 2 ? p.grp_count : 1);
+  const int grid = tiles < num_sms ? tiles : num_sms;   // grp_mode 1: p.M is the row capacity, an upper bound
   kern<<<grid, NUM_THREADS, L::kTotal, stream>>>(ta, tb, td, p);
   return (int)cudaGetLastError();
 }
@@ -384,6 +429,9 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
 // destination set of the next vlmt_gemm_bf16 call (consumed by vlmt_gemm_bf16_rs_push)
 static thread_local int g_rs_world = 0, g_rs_rows = 0;
 static thread_local void* g_rs_dst[8];
+// group table of the next vlmt_gemm_bf16 call (set by vlmt_gemm_bf16_grouped)
+static thread_local const int* g_grp_prefix = nullptr;
+static thread_local int g_grp_count = 0, g_grp_mode = 0, g_grp_b_rows = 0;
 
 extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K,
                               int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate,
@@ -397,8 +445,9 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
   else r = vlmt_make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
   if (r) return 1000 + r;
   const bool bn256 = N > 128;
-  if (!b_mn_major) r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, 128);
-  else r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
+  const uint64_t b_groups = g_grp_mode == 1 ? (uint64_t)g_grp_count : 1;   // grouped forward / dgrad: one B per group, stacked along the rows
+  if (!b_mn_major) r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N * b_groups, (uint64_t)ldb * 2, 64, 128);
+  else r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K * b_groups, (uint64_t)ldb * 2, 64, 64);
   if (r) return 2000 + r;
   Params p;
   CUtensorMap td = ta;  // placeholder when the direct-store epilogue is used
@@ -409,10 +458,13 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
     for (int i = 0; i < g_rs_world; ++i) p.rs_dst[i] = reinterpret_cast<__nv_bfloat16*>(g_rs_dst[i]);
   }
   if (g_rs_world == 0 && Dacc32 == nullptr && !accumulate && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
-    r = vlmt_make_tmap_2d_bf16(&td, D, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * 2, 64, 32);
+    const uint64_t d_rows = g_grp_mode == 2 ? (uint64_t)M * g_grp_count : (uint64_t)M;
+    r = vlmt_make_tmap_2d_bf16(&td, D, (uint64_t)N, d_rows, (uint64_t)ldd * 2, 64, 32);
     if (r == 0) p.tma_store = 1;
   }
   p.M = M; p.N = N; p.K = K; p.ldd = ldd;
+  p.grp_prefix = g_grp_prefix; p.grp_count = g_grp_count; p.grp_mode = g_grp_mode; p.grp_b_rows = g_grp_b_rows;
+  if (p.grp_mode == 2 && !p.tma_store) return -30;  // grouped wgrad writes through the TMA-store epilogue only
   p.D = reinterpret_cast<__nv_bfloat16*>(D);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.Dacc32 = Dacc32;
@@ -439,5 +491,26 @@ extern "C" int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const*
   for (int i = 0; i < world; ++i) g_rs_dst[i] = dst[i];
   int r = vlmt_gemm_bf16(A, B, dst[0], nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, 0, GEMM_EPI_NONE, 0, status, num_sms, stream);
   g_rs_world = 0;
+  return r;
+}
+
+
+// One launch for all groups (experts).  `prefix` (device, G + 1 ints): first 128-row tile of every group in the padded
+// row layout.
+//   mode 1: D[rows, N] = A[rows, K] x B_g  with A K-major [row_capacity, K]; B K-major [G * N, K] (forward) or
+//           MN-major [G * K, N] (dgrad); M = row capacity (tiles beyond prefix[G] are not touched).
+//   mode 2: D_g[M, N] = sum over the rows of group g of A[row, M]^T B[row, N]  (A, B MN-major, K = row capacity);
+//           D is [G * M, N]; needs M % 128 == 0 and a 16-byte aligned D.
+extern "C" int vlmt_gemm_bf16_grouped(const void* A, const void* B, void* D, const int* prefix, int groups, int mode, int M, int N, int K,
+                                      int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int* status, int num_sms,
+                                      cudaStream_t stream) {
+  if (groups < 1 || (mode != 1 && mode != 2) || prefix == nullptr) return -31;
+  if (mode == 1 && a_mn_major) return -32;
+  if (mode == 2 && (!a_mn_major || !b_mn_major || (M % BM) != 0)) return -33;
+  g_grp_prefix = prefix; g_grp_count = groups; g_grp_mode = mode;
+  g_grp_b_rows = mode == 1 ? (b_mn_major ? K : N) : 0;
+  int r = vlmt_gemm_bf16(A, B, D, nullptr, nullptr, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, GEMM_EPI_NONE, 0, status, num_sms,
+                         stream);
+  g_grp_prefix = nullptr; g_grp_count = 0; g_grp_mode = 0; g_grp_b_rows = 0;
   return r;
 }

@@ -20,6 +20,12 @@ int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const v
 // (blocks of rows_per_rank, a multiple of 128) are stored into dst[o], typically peer memory.
 int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const* dst, int world, int rows_per_rank, int M, int N, int K, int lda,
                            int ldb, int ldd, int* status, int num_sms, cudaStream_t stream);
+// One launch for all groups (the experts of a MoE layer); `prefix` (device memory, groups + 1 ints) gives the first
+// 128-row tile of every group in the padded row layout.  mode 1: forward / dgrad, groups partition the M dimension
+// (M = row capacity) and every group has its own B (stacked along B's rows); mode 2: wgrad, groups partition the
+// contraction over the rows (K = row capacity) and every group writes its own [M, N] block of D.
+int vlmt_gemm_bf16_grouped(const void* A, const void* B, void* D, const int* prefix, int groups, int mode, int M, int N, int K, int lda,
+                           int ldb, int ldd, int a_mn_major, int b_mn_major, int* status, int num_sms, cudaStream_t stream);
 // 2-D bf16 tensor map with 128-byte swizzle; `out_map` points at 128 bytes (CUtensorMap).
 int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer);

@@ -2,7 +2,7 @@
 
     python -m vlm_training_b200.ops.microbench gemm --m 8192 --n 6144 --k 4096 [--layout fwd|dgrad|wgrad]
     python -m vlm_training_b200.ops.microbench attention --tokens 8192 --docs 1 [--backward]
-    python -m vlm_training_b200.ops.microbench rmsnorm | swiglu | qkv_rope | ce | adamw
+    python -m vlm_training_b200.ops.microbench rmsnorm | swiglu | qkv_rope | ce | adamw | moe
     python -m vlm_training_b200.ops.microbench all            # the table used in the roofline report
 
 Each line is JSON: algorithmic FLOPs / bytes, median milliseconds, achieved rate, and the fraction of the
@@ -155,9 +155,26 @@ def bench_adamw(t: Timer, n=1 << 28):
     return _report("adamw_fp32_state", [n], ms, nbytes=n * (2 + 12 + 12 + 2.0))
 
 
+def bench_moe(t: Timer, tokens=16384, hidden=2048, inter=512, experts=256, topk=8):
+    """Routed experts of one MoE layer (grouped GEMMs, forward + backward) with a random router."""
+    from .. import ops
+
+    x = _r(tokens, hidden).requires_grad_()
+    gate_up = _r(experts, 2 * inter, hidden, scale=0.02).requires_grad_()
+    down = _r(experts, hidden, inter, scale=0.02).requires_grad_()
+    w, idx = ops.moe_router(torch.randn(tokens, experts, device="cuda"), topk, True)
+    w = w.to(torch.bfloat16)
+    g = _r(tokens, hidden)
+
+    def fb():
+        ops.moe_experts(x, gate_up, down, w, idx).backward(g)
+    flops = 3.0 * tokens * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden)
+    return _report("moe_experts_fwd_bwd", [tokens, hidden, inter, experts, topk], t(fb), flops=flops)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -187,6 +204,8 @@ def main(argv=None):
         bench_ce(t)
     elif a.what == "adamw":
         bench_adamw(t)
+    elif a.what == "moe":
+        bench_moe(t)
     else:
         for layout in ("fwd", "dgrad", "wgrad"):
             bench_gemm(t, 8192, 6144, 4096, layout)
@@ -204,6 +223,7 @@ def main(argv=None):
         bench_qkv_rope(t)
         bench_ce(t)
         bench_adamw(t)
+        bench_moe(t)
     from . import cuda as cu
 
     cu.check_status()
