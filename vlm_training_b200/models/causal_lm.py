@@ -196,13 +196,17 @@ class _CausalLMBase(nn.Module):
 
         grids = image_grid_thw.tolist() if torch.is_tensor(image_grid_thw) else list(image_grid_thw)
         merge2 = self.config.vision.spatial_merge_size ** 2
-        ranges = positions.split_images(grids, tp.size)
-        patches = [sum(t * h * w for t, h, w in grids[lo:hi]) for lo, hi in ranges]
-        lo, hi = ranges[tp.rank]
-        p0 = sum(patches[: tp.rank])
-        if hi > lo:
-            plan = VisionPlan.build(grids[lo:hi], self.config.vision, dev)
-            merged, deep = self.visual(pixel_values[p0:p0 + patches[tp.rank]], None, plan)
+        assign = positions.assign_images(grids, tp.size)          # image indices per rank, balanced by cost
+        n_patch = [t * h * w for t, h, w in grids]
+        p_off = [0]
+        for n in n_patch:
+            p_off.append(p_off[-1] + n)
+        mine = assign[tp.rank]
+        if mine:
+            plan = VisionPlan.build([grids[i] for i in mine], self.config.vision, dev)
+            pix = torch.cat([pixel_values[p_off[i]:p_off[i + 1]] for i in mine], 0) if len(mine) > 1 else \
+                pixel_values[p_off[mine[0]]:p_off[mine[0] + 1]]
+            merged, deep = self.visual(pix, None, plan)
             feats = torch.cat([merged] + list(deep), dim=-1)
         else:
             n_out = 1 + len(self.config.vision.deepstack_visual_indexes)
@@ -211,8 +215,18 @@ class _CausalLMBase(nn.Module):
                                            dtype=self.decoder.embed_tokens.weight.dtype)
             if torch.is_grad_enabled():
                 feats.requires_grad_()  # keeps the exchange's backward collective in this rank's autograd graph too
-        sizes = [p // merge2 for p in patches]
+        sizes = [sum(n_patch[i] for i in ix) // merge2 for ix in assign]
         allf = gather_uneven(feats, sizes, tp, grad_identical=not tp.sequence_parallel)
+        # the gathered rows are rank-major; put the images back in their order of appearance in the row
+        tok_of = [n // merge2 for n in n_patch]
+        start_in_gather, pos = {}, 0
+        for ix in assign:
+            for i in ix:
+                start_in_gather[i] = pos
+                pos += tok_of[i]
+        if [i for ix in assign for i in ix] != list(range(len(grids))):
+            order = np.concatenate([np.arange(start_in_gather[i], start_in_gather[i] + tok_of[i]) for i in range(len(grids))])
+            allf = allf.index_select(0, torch.from_numpy(order).to(dev, non_blocking=True))
         H = self.config.vision.out_hidden_size
         chunks = allf.split(H, dim=-1)
         return chunks[0], list(chunks[1:])
