@@ -59,17 +59,17 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, c
 }
 
 // y-partials of a row-parallel linear pushed to their owners: rows [o*R, (o+1)*R) of a @ b^T go to dst_ptrs[o]
-void gemm_rs_push(const Tensor& a, const Tensor& b, const std::vector<int64_t>& dst_ptrs, int64_t rows_per_rank) {
+void gemm_rs_push(const Tensor& a, const Tensor& b, const std::vector<int64_t>& dst_ptrs, int64_t rows_per_rank, bool b_mn) {
   check_bf16(a, "a"); check_bf16(b, "b");
-  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1));
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == (b_mn ? b.size(0) : b.size(1)));
   c10::cuda::CUDAGuard guard(a.device());
   void* dst[8];
   TORCH_CHECK(dst_ptrs.size() <= 8);
   for (size_t i = 0; i < dst_ptrs.size(); ++i) dst[i] = reinterpret_cast<void*>(dst_ptrs[i]);
   Tensor st = status_tensor();
-  const int M = a.size(0), N = b.size(0), K = a.size(1);
+  const int M = a.size(0), N = b_mn ? b.size(1) : b.size(0), K = a.size(1);
   int r = vlmt_gemm_bf16_rs_push(a.data_ptr(), b.data_ptr(), dst, (int)dst_ptrs.size(), (int)rows_per_rank, M, N, K, (int)a.stride(0),
-                                 (int)b.stride(0), N, st.data_ptr<int>(), num_sms(), cur_stream());
+                                 (int)b.stride(0), N, b_mn ? 1 : 0, st.data_ptr<int>(), num_sms(), cur_stream());
   TORCH_CHECK(r == 0, "vlmt_gemm_bf16_rs_push failed with code ", r);
 }
 

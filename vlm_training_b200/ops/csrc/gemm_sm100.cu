@@ -53,6 +53,7 @@ struct Params {
   // into rs_dst[o] (a buffer in rank o's memory, reached over NVLink), so the transfer overlaps the remaining tiles
   int rs_world, rs_rows;
   __nv_bfloat16* rs_dst[8];
+  const CUtensorMap* rs_maps;  // device memory: one tensor map per owner over its [rs_rows, N] destination block (TMA-store epilogue)
   // Grouped GEMM (one launch for all experts of a MoE layer).  Rows of every group are padded to whole 128-row tiles
   // and laid out back to back; grp_prefix[g] (device memory, G + 1 ints) is the first tile of group g.
   //   grp_mode 1 (forward / dgrad): groups partition the M dimension; group g multiplies its rows with its own B
@@ -195,11 +196,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
+          const SmemDesc a0 = A_MN ? make_desc(sa, 8192, 1024) : make_desc(sa, 16, 1024);
+          const SmemDesc b0 = B_MN ? make_desc(sb, 8192, 1024) : make_desc(sb, 16, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, ((kb - kb_lo) | k) != 0);
+            const SmemDesc ad = desc_off(a0, A_MN ? k * 2048 : k * 32), bd = desc_off(b0, B_MN ? k * 2048 : k * 32);
+            if (k == 0) umma_ss<2>(d_tmem, ad, bd, idesc, (uint32_t)(kb - kb_lo));   // the first k-block of a tile overwrites
+            else umma_ss<1>(d_tmem, ad, bd, idesc);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -273,7 +276,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           fence_async_proxy();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_d, buf, col0, d_row0 + tm * BM + q * 32);
+            if (p.rs_world > 0) {  // the tile's rows belong to one owner (rs_rows is a multiple of the tile height)
+              const int owner = (tm * BM) / p.rs_rows;
+              tma_store_2d(&p.rs_maps[owner], buf, col0, tm * BM - owner * p.rs_rows + q * 32);
+            } else {
+              tma_store_2d(&tmap_d, buf, col0, d_row0 + tm * BM + q * 32);
+            }
             tma_store_commit();
           }
         }
@@ -426,6 +434,32 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
   return (int)cudaGetLastError();
 }
 
+// Tensor maps of reduce-scatter destinations live in device memory (the kernel picks one per tile).  A destination
+// set is one of a few staging slots, so the maps are built once per (pointers, shape) and kept for the process.
+#include <map>
+#include <vector>
+static const CUtensorMap* rs_maps_for(void* const* dst, int world, int rows, int N, int ldd) {
+  static thread_local std::map<std::vector<uint64_t>, CUtensorMap*> cache;
+  std::vector<uint64_t> key;
+  for (int i = 0; i < world; ++i) key.push_back(reinterpret_cast<uint64_t>(dst[i]));
+  key.push_back((uint64_t)rows); key.push_back((uint64_t)N); key.push_back((uint64_t)ldd);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  key.push_back((uint64_t)dev);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  CUtensorMap host[8];
+  for (int i = 0; i < world; ++i) {
+    if ((reinterpret_cast<uintptr_t>(dst[i]) & 15) || (ldd & 7)) return nullptr;
+    if (vlmt_make_tmap_2d_bf16(&host[i], dst[i], (uint64_t)N, (uint64_t)rows, (uint64_t)ldd * 2, 64, 32)) return nullptr;
+  }
+  CUtensorMap* devp = nullptr;
+  if (cudaMalloc(&devp, sizeof(CUtensorMap) * 8) != cudaSuccess) return nullptr;
+  if (cudaMemcpy(devp, host, sizeof(CUtensorMap) * world, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+  cache[key] = devp;
+  return devp;
+}
+
 // destination set of the next vlmt_gemm_bf16 call (consumed by vlmt_gemm_bf16_rs_push)
 static thread_local int g_rs_world = 0, g_rs_rows = 0;
 static thread_local void* g_rs_dst[8];
@@ -453,9 +487,16 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
   CUtensorMap td = ta;  // placeholder when the direct-store epilogue is used
   p.tma_store = 0;
   p.rs_world = 0; p.rs_rows = 0;
+  p.rs_maps = nullptr;
   if (g_rs_world > 0) {
     p.rs_world = g_rs_world; p.rs_rows = g_rs_rows;
     for (int i = 0; i < g_rs_world; ++i) p.rs_dst[i] = reinterpret_cast<__nv_bfloat16*>(g_rs_dst[i]);
+    // whole 64-column slabs go out as TMA stores into the owners' memory (large NVLink writes); the per-thread 16-byte
+    // stores of the direct epilogue are kept as the fallback
+    if (Dacc32 == nullptr && !accumulate && !bias && epilogue == GEMM_EPI_NONE) {
+      p.rs_maps = rs_maps_for(g_rs_dst, g_rs_world, g_rs_rows, N, ldd);
+      if (p.rs_maps != nullptr) p.tma_store = 1;
+    }
   }
   if (g_rs_world == 0 && Dacc32 == nullptr && !accumulate && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
     const uint64_t d_rows = g_grp_mode == 2 ? (uint64_t)M * g_grp_count : (uint64_t)M;
@@ -484,12 +525,14 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
 
 // D rows [o * rows_per_rank, (o + 1) * rows_per_rank) are written to dst[o] (row stride ldd) instead of a local D:
 // the producer half of a tensor-parallel GEMM -> reduce-scatter (the consumer sums the `world` partial blocks it received).
+// B is K-major (a row-parallel forward linear) or MN-major (the input gradient of a column-parallel linear).
 extern "C" int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const* dst, int world, int rows_per_rank, int M, int N, int K,
-                                      int lda, int ldb, int ldd, int* status, int num_sms, cudaStream_t stream) {
+                                      int lda, int ldb, int ldd, int b_mn_major, int* status, int num_sms, cudaStream_t stream) {
   if (world < 1 || world > 8 || rows_per_rank % BM != 0 || rows_per_rank * world != M) return -20;
   g_rs_world = world; g_rs_rows = rows_per_rank;
   for (int i = 0; i < world; ++i) g_rs_dst[i] = dst[i];
-  int r = vlmt_gemm_bf16(A, B, dst[0], nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, 0, GEMM_EPI_NONE, 0, status, num_sms, stream);
+  int r = vlmt_gemm_bf16(A, B, dst[0], nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, b_mn_major, GEMM_EPI_NONE, 0, status, num_sms,
+                         stream);
   g_rs_world = 0;
   return r;
 }

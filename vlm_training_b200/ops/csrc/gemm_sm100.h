@@ -16,10 +16,10 @@ extern "C" {
 int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K, int lda,
                    int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate, int* status, int num_sms,
                    cudaStream_t stream);
-// Same GEMM (A K-major, B K-major) whose output rows go to `world` destinations: rows owned by rank o
+// Same GEMM (A K-major; B K-major or MN-major) whose output rows go to `world` destinations: rows owned by rank o
 // (blocks of rows_per_rank, a multiple of 128) are stored into dst[o], typically peer memory.
 int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const* dst, int world, int rows_per_rank, int M, int N, int K, int lda,
-                           int ldb, int ldd, int* status, int num_sms, cudaStream_t stream);
+                           int ldb, int ldd, int b_mn_major, int* status, int num_sms, cudaStream_t stream);
 // One launch for all groups (the experts of a MoE layer); `prefix` (device memory, groups + 1 ints) gives the first
 // 128-row tile of every group in the padded row layout.  mode 1: forward / dgrad, groups partition the M dimension
 // (M = row capacity) and every group has its own B (stacked along B's rows); mode 2: wgrad, groups partition the

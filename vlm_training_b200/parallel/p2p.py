@@ -111,20 +111,22 @@ class P2PComm:
         return out
 
 
-    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """``reduce_scatter_rows(x @ w.T)`` with the collective fused into the GEMM: the tcgen05 GEMM's epilogue stores each
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,
+                            b_mn: bool = False) -> torch.Tensor:
+        """``reduce_scatter_rows(x @ w.T)`` (``x @ w`` with ``b_mn``: the input gradient of a column-parallel linear, ``w``
+        stored ``[out, in]``) with the collective fused into the GEMM: the tcgen05 GEMM's epilogue stores each
         output tile directly into the staging slot of the rank that owns those rows (peer stores over NVLink, overlapping
         the remaining tiles); after the signal round every rank sums the ``world`` partial blocks it received — local
         reads only — and adds ``residual`` in the same pass."""
         from ..ops import cuda as cu
 
-        M, N = x.shape[0], w.shape[0]
+        M, N = x.shape[0], (w.shape[1] if b_mn else w.shape[0])
         rows = M // self.world
         n = M * N
         e, _slot, ptrs = self._slot(n)
         block = rows * N * 2  # bytes of one [rows, N] partial block
         dst = [p + self.rank * block for p in ptrs]  # on rank o: block `my rank` of its slot
-        cu._C.gemm_rs_push(x, w, dst, rows)
+        cu._C.gemm_rs_push(x, w, dst, rows, b_mn)
         cu._C.signal_peers(self.flag_ptrs, self.rank, e)
         out = x.new_empty((rows, N))
         mine = ptrs[self.rank]

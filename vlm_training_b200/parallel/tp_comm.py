@@ -240,14 +240,19 @@ class _GatherLinear(torch.autograd.Function):
         T, K = x_full.shape
         dx = None
         if fctx.needs_input_grad[0]:
-            buf, handle = ctx.p2p.reduce_scatter_begin(T, K)
-            others, (o0, o1) = _row_blocks(ctx.rank, ctx.size, T // ctx.size)
-            for a, b in others:
-                cu._gemm(dy[a:b], w, b_mn=True, out=buf[a:b])
-            handle.signal()
-            cu._gemm(dy[o0:o1], w, b_mn=True, out=buf[o0:o1])
+            if ctx.p2p.gemm_rs_usable(dy, w) and K % 8 == 0:
+                # input gradient with the reduce-scatter inside the GEMM: the epilogue stores every row block into its
+                # owner's memory while the remaining tiles are computed; the final sum reads local memory only
+                dx = ctx.p2p.gemm_reduce_scatter(dy, w, b_mn=True)
+            else:
+                buf, handle = ctx.p2p.reduce_scatter_begin(T, K)
+                others, (o0, o1) = _row_blocks(ctx.rank, ctx.size, T // ctx.size)
+                for a, b in others:
+                    cu._gemm(dy[a:b], w, b_mn=True, out=buf[a:b])
+                handle.signal()
+                cu._gemm(dy[o0:o1], w, b_mn=True, out=buf[o0:o1])
         dw = cu._gemm(dy, x_full, a_mn=True, b_mn=True) if fctx.needs_input_grad[1] else None
-        if fctx.needs_input_grad[0]:
+        if fctx.needs_input_grad[0] and dx is None:
             dx = handle.result(dy)
         return dx, dw, None
 
