@@ -42,6 +42,55 @@ def test_gemm_forward_layout(M, N, K):
     cu.check_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (1000, 1152, 4304), (777, 136, 72)])
+def test_gemm_wgrad_adds_into_bf16_gradient(M, N, K):
+    """bf16 accumulate: the slabs are added by TMA reduce-adds; the previous content of D must survive."""
+    cu = _cu()
+    dy, x = _rand(M, N), _rand(M, K)
+    before = _rand(N, K, scale=3.0)
+    acc = before.clone()
+    cu._gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    want = before.float() + dy.float().t() @ x.float()
+    _close(acc, want, atol=0.05 * math.sqrt(M) / 8 + 0.05, rtol=2e-2, what="wgrad bf16 acc")
+    cu.check_status()
+
+
+def test_linear_wgrad_in_place_into_tagged_gradient():
+    """A parameter tagged by the optimizer engine gets its weight gradient added into ``.grad`` by the GEMM itself:
+    autograd sees ``None``, the ready hook fires once, and activation checkpointing does not change that."""
+    from torch.utils.checkpoint import checkpoint
+
+    cu = _cu()
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(256, 384, bias=False, device=DEV, dtype=torch.bfloat16)
+    norm_w = torch.nn.Parameter(torch.ones(256, device=DEV, dtype=torch.bfloat16))
+    flat = torch.zeros(384 * 256 + 8, device=DEV, dtype=torch.bfloat16)
+    w = lin.weight
+    w.grad = flat[8:].view(384, 256)
+    w._vlmt_grad_in_place = True
+    fired = []
+    w._vlmt_grad_ready = lambda p: fired.append(id(p))
+    x = _rand(512, 256).requires_grad_()
+    g = _rand(512, 384, scale=0.1)
+    want = g.float().t() @ x.detach().float()
+
+    def check(times):
+        _close(flat[8:].view(384, 256), times * want, atol=0.08 * times, rtol=2e-2, what=f"in-place wgrad x{times}")
+        assert float(flat[:8].abs().sum()) == 0.0
+
+    ops.linear(x, w).backward(g)
+    assert fired == [id(w)]
+    check(1)
+    checkpoint(lambda t: ops.linear(t, w), x, use_reentrant=False).backward(g)     # second micro-batch: accumulates
+    assert fired == [id(w)] * 2
+    check(2)
+    y = ops.rms_norm_linear(x, norm_w, w, 1e-6)
+    y.backward(g)
+    assert len(fired) == 3 and norm_w.grad is not None
+    assert x.grad is not None
+    cu.check_status()
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 512, 384), (1000, 1152, 4304), (2048, 4096, 12288)])
 def test_gemm_dgrad_wgrad_layouts(M, N, K):
     cu = _cu()

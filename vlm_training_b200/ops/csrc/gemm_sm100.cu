@@ -279,6 +279,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (p.rs_world > 0) {  // the tile's rows belong to one owner (rs_rows is a multiple of the tile height)
               const int owner = (tm * BM) / p.rs_rows;
               tma_store_2d(&p.rs_maps[owner], buf, col0, tm * BM - owner * p.rs_rows + q * 32);
+            } else if (p.accumulate) {
+              tma_reduce_add_2d(&tmap_d, buf, col0, d_row0 + tm * BM + q * 32);
             } else {
               tma_store_2d(&tmap_d, buf, col0, d_row0 + tm * BM + q * 32);
             }
@@ -498,7 +500,9 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
       if (p.rs_maps != nullptr) p.tma_store = 1;
     }
   }
-  if (g_rs_world == 0 && Dacc32 == nullptr && !accumulate && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
+  // with `accumulate` the slabs go out as TMA reduce-adds (bf16 addition in the memory system), so a weight gradient can
+  // be added straight into the optimizer's gradient buffer without reading it back into the SM
+  if (g_rs_world == 0 && Dacc32 == nullptr && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
     const uint64_t d_rows = g_grp_mode == 2 ? (uint64_t)M * g_grp_count : (uint64_t)M;
     r = vlmt_make_tmap_2d_bf16(&td, D, (uint64_t)N, d_rows, (uint64_t)ldd * 2, 64, 32);
     if (r == 0) p.tma_store = 1;

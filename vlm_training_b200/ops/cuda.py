@@ -76,6 +76,32 @@ def _tma_ok(*ts) -> bool:
     return all(t.shape[-1] % 8 == 0 and t.dtype == torch.bfloat16 for t in ts)
 
 
+_WGRAD_IN_PLACE = os.environ.get("VLMT_WGRAD_IN_PLACE", "1") != "0"
+
+
+def _grad_target(w):
+    """The parameter whose ``.grad`` is a view of the optimizer engine's flat gradient buffer (the engine tags those),
+    else ``None``.  Kept on the autograd context as a plain attribute: under activation checkpointing the tensors that
+    come back from ``saved_tensors`` are detached copies without ``.grad``."""
+    return w if (_WGRAD_IN_PLACE and getattr(w, "_vlmt_grad_in_place", False)) else None
+
+
+def _wgrad(dy2, x2, param=None):
+    """dW[N,K] = dY^T[N,M] . X[M,K].  For a tagged parameter the GEMM adds the product into ``param.grad`` from its
+    epilogue (TMA reduce-add) and autograd gets ``None``: no separate accumulation pass over the gradient, no temporary.
+    The engine's gradient-ready hook is called by hand because autograd has nothing to accumulate."""
+    if param is not None:
+        g = param.grad
+        if (g is not None and g.dtype == torch.bfloat16 and g.dim() == 2 and g.shape == (dy2.shape[1], x2.shape[1])
+                and g.stride(1) == 1 and g.stride(0) % 8 == 0 and g.data_ptr() % 16 == 0):
+            _gemm(dy2, x2, a_mn=True, b_mn=True, out=g, accumulate=True)
+            ready = getattr(param, "_vlmt_grad_ready", None)
+            if ready is not None:
+                ready(param)
+            return None
+    return _gemm(dy2, x2, a_mn=True, b_mn=True)
+
+
 class _Linear(torch.autograd.Function):
     """y = x W^T (+ b).  fwd: (K,K) GEMM; dgrad: (K,MN); wgrad: (MN,MN) — no transposes materialised."""
 
@@ -83,6 +109,7 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, w, b, epilogue):
         x2 = _as_gemm_operand(x.reshape(-1, x.shape[-1]))
         wc = _as_gemm_operand(w)
+        ctx.w_param = _grad_target(w)
         y = _gemm(x2, wc, bias=b, epilogue=epilogue)
         ctx.save_for_backward(x2, wc)
         ctx.has_bias = b is not None
@@ -97,7 +124,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = _gemm(dy2, w, b_mn=True).view(ctx.in_shape)  # dX[M,K] = dY[M,N] . W[N,K]
         if ctx.needs_input_grad[1]:
-            dw = _gemm(dy2, x2, a_mn=True, b_mn=True)  # dW[N,K] = dY^T[N,M] . X[M,K]
+            dw = _wgrad(dy2, x2, ctx.w_param)  # dW[N,K] = dY^T[N,M] . X[M,K]
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _C.colsum(dy2).to(dy.dtype) if dy2.shape[1] % 2 == 0 else dy2.float().sum(0).to(dy.dtype)
             _tick()
@@ -289,6 +316,7 @@ class _NormLinear(torch.autograd.Function):
         else:
             h, rstd, r = _C.rmsnorm_fwd(xc, residual.contiguous(), norm_w, eps, offset)
         wc = _as_gemm_operand(w)
+        ctx.w_param = _grad_target(w)
         y = _gemm(h, wc)
         _tick()
         ctx.save_for_backward(r, norm_w, rstd, wc)
@@ -303,7 +331,7 @@ class _NormLinear(torch.autograd.Function):
         eps, offset, has_res = ctx.cfg
         dy2 = _as_gemm_operand(dy)
         h = _C.rmsnorm_fwd(r, None, norm_w, eps, offset)[0]  # recompute the normalised activation
-        dw = _gemm(dy2, h, a_mn=True, b_mn=True)
+        dw = _wgrad(dy2, h, ctx.w_param)
         del h
         dh = _gemm(dy2, w, b_mn=True)
         dx, dnw = _C.rmsnorm_bwd(dh, r, norm_w, rstd, dr.contiguous() if dr is not None else None, offset)
@@ -333,6 +361,7 @@ class _LNLinear(torch.autograd.Function):
         xc = x.contiguous()
         h, mean, rstd = _C.layernorm_fwd(xc, ln_w, ln_b, eps)
         wc = _as_gemm_operand(w)
+        ctx.w_param = _grad_target(w)
         y = _gemm(h, wc, bias=b)
         _tick()
         ctx.save_for_backward(xc, ln_w, ln_b, mean, rstd, wc)
@@ -344,7 +373,7 @@ class _LNLinear(torch.autograd.Function):
         x, ln_w, ln_b, mean, rstd, w = ctx.saved_tensors
         dy2 = _as_gemm_operand(dy)
         h = _C.layernorm_fwd(x, ln_w, ln_b, ctx.eps)[0]
-        dw = _gemm(dy2, h, a_mn=True, b_mn=True)
+        dw = _wgrad(dy2, h, ctx.w_param)
         del h
         dh = _gemm(dy2, w, b_mn=True)
         dx, dlw, dlb = _C.layernorm_bwd(dh, x, ln_w, mean, rstd)
@@ -370,6 +399,7 @@ class _GeluLinear(torch.autograd.Function):
         pc = pre.contiguous()
         act = _C.gelu_fwd(pc, tanh_approx)
         wc = _as_gemm_operand(w)
+        ctx.w_param = _grad_target(w)
         y = _gemm(act, wc, bias=b)
         _tick()
         ctx.save_for_backward(pc, wc)
@@ -381,7 +411,7 @@ class _GeluLinear(torch.autograd.Function):
         pre, w = ctx.saved_tensors
         dy2 = _as_gemm_operand(dy)
         act = _C.gelu_fwd(pre, ctx.tanh_approx)
-        dw = _gemm(dy2, act, a_mn=True, b_mn=True)
+        dw = _wgrad(dy2, act, ctx.w_param)
         del act
         dact = _gemm(dy2, w, b_mn=True)
         dpre = _C.gelu_bwd(dact, pre, ctx.tanh_approx)
@@ -408,6 +438,7 @@ class _SwiGLULinear(torch.autograd.Function):
         guc = gate_up.contiguous()
         act = _C.swiglu_fwd(guc)
         wc = _as_gemm_operand(w)
+        ctx.w_param = _grad_target(w)
         y = _gemm(act, wc)
         _tick()
         ctx.save_for_backward(guc, wc)
@@ -418,7 +449,7 @@ class _SwiGLULinear(torch.autograd.Function):
         gu, w = ctx.saved_tensors
         dy2 = _as_gemm_operand(dy)
         act = _C.swiglu_fwd(gu)
-        dw = _gemm(dy2, act, a_mn=True, b_mn=True)
+        dw = _wgrad(dy2, act, ctx.w_param)
         del act
         dact = _gemm(dy2, w, b_mn=True)
         dgu = _C.swiglu_bwd(dact, gu)

@@ -64,6 +64,7 @@ class _Bucket:
     params: list = field(default_factory=list)
     segments: list = field(default_factory=list)
     pending: int = 0
+    seen: set = field(default_factory=set)  # ids of the parameters whose gradient has been reported this step
     reduced: bool = False
     gather_event: object = None
     reduce_event: object = None
@@ -114,6 +115,9 @@ class _Domain:
                 self.flat_param[o:o + n].copy_(p.detach().reshape(-1))
                 p.data = self.flat_param[o:o + n].view(p.shape)
                 p.grad = self.flat_grad[o:o + n].view(p.shape)
+                # weight-gradient GEMMs may add into this view directly (ops/cuda.py:_wgrad); valid because every
+                # such parameter enters exactly one linear per forward pass
+                p._vlmt_grad_in_place = True
         self.param_bucket = {}
         for b in self.buckets:
             for p in b.params:
@@ -232,6 +236,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                 d.flat_grad.zero_()
             for b in d.buckets:
                 b.pending = len(b.params)
+                b.seen.clear()
                 b.reduced = False
                 b.reduce_event = None
 
@@ -245,12 +250,19 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
             for b in d.buckets:
                 b.pending = len(b.params)
                 for p in b.params:
-                    self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(d, b)))
+                    hook = self._make_hook(d, b)
+                    p._vlmt_grad_ready = hook
+                    self._hooks.append(p.register_post_accumulate_grad_hook(hook))
 
     def _make_hook(self, d, b):
-        def hook(_p):
+        def hook(p):
             if not self._sync_grads:
                 return
+            # once per parameter and step: a weight-gradient GEMM that adds into the flat buffer itself reports the
+            # parameter by hand (`_vlmt_grad_ready`), and autograd may report it again with nothing to accumulate
+            if id(p) in b.seen:
+                return
+            b.seen.add(id(p))
             b.pending -= 1
             if b.pending == 0 and not b.reduced:
                 if self._fused is not None:

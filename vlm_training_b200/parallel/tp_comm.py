@@ -225,8 +225,11 @@ class _GatherLinear(torch.autograd.Function):
 
     @staticmethod
     def forward(fctx, x, w, ctx):
+        from ..ops import cuda as cu
+
         y, x_full = _gathered_gemm(x, w, ctx)
         fctx.tp = ctx
+        fctx.w_param = cu._grad_target(w)
         fctx.save_for_backward(x_full, w)
         return y
 
@@ -251,7 +254,7 @@ class _GatherLinear(torch.autograd.Function):
                     cu._gemm(dy[a:b], w, b_mn=True, out=buf[a:b])
                 handle.signal()
                 cu._gemm(dy[o0:o1], w, b_mn=True, out=buf[o0:o1])
-        dw = cu._gemm(dy, x_full, a_mn=True, b_mn=True) if fctx.needs_input_grad[1] else None
+        dw = cu._wgrad(dy, x_full, fctx.w_param) if fctx.needs_input_grad[1] else None
         if fctx.needs_input_grad[0] and dx is None:
             dx = handle.result(dy)
         return dx, dw, None
@@ -279,7 +282,10 @@ class _RowLinearReduceScatter(torch.autograd.Function):
 
     @staticmethod
     def forward(fctx, x, w, ctx):
+        from ..ops import cuda as cu
+
         fctx.tp = ctx
+        fctx.w_param = cu._grad_target(w)
         fctx.save_for_backward(x, w)
         return ctx.p2p.gemm_reduce_scatter(x, w)
 
@@ -292,7 +298,7 @@ class _RowLinearReduceScatter(torch.autograd.Function):
             dx, dy_full = _gathered_gemm(dy.contiguous(), w, fctx.tp, b_mn=True)   # gather overlapped with the own rows
         else:
             dx, dy_full = None, _all_gather_rows(dy.contiguous(), fctx.tp)
-        dw = cu._gemm(dy_full, x, a_mn=True, b_mn=True) if fctx.needs_input_grad[1] else None
+        dw = cu._wgrad(dy_full, x, fctx.w_param) if fctx.needs_input_grad[1] else None
         return dx, dw, None
 
 
