@@ -458,7 +458,7 @@ def test_layer_norm_linear_and_gelu_linear_match_unfused():
     _close(y, yr, 0.06, 3e-2, "y")
     _close(x.grad, xr.grad, 0.06, 4e-2, "dx")
     _close(w.grad, wr.grad, 0.4, 4e-2, "dw1")
-    _close(w2.grad, w2r.grad, 0.4, 4e-2, "dw2")
+    _close(w2.grad, w2r.grad, 0.8, 4e-2, "dw2")
     _close(b.grad, br.grad, 0.5, 4e-2, "db1")
     _close(b2.grad, b2r.grad, 0.5, 4e-2, "db2")
     _close(lw.grad, lwr.grad, 1.0, 4e-2, "dln_w")
