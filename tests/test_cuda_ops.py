@@ -491,3 +491,59 @@ def test_moe_experts_grouped_gemm(T, H, I, E, k):
     _close(gate_up.grad, gur.grad, 0.3, 5e-2, "dgate_up")   # bf16 products summed over an expert's rows
     _close(down.grad, dr.grad, 0.3, 5e-2, "ddown")
     assert float(gate_up.grad[E - 1].abs().max()) == 0.0 and float(down.grad[E - 2].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("reverse", [False, True])
+def test_gdn_scan_kernel_matches_loop(reverse):
+    """The tcgen05 scan kernel against the same recurrence as a loop of fp32 tensor operations on the same bf16 inputs."""
+    import numpy as np
+
+    from vlm_training_b200.ops.gdn_scan import scan_torch
+
+    cu = _cu()
+    torch.manual_seed(5)
+    H = 3
+    count = np.array([1, 4, 2, 7], dtype=np.int32)
+    first = np.concatenate(([0], np.cumsum(count)))[:-1].astype(np.int32)
+    N = int(count.sum())
+    x1, x2 = _rand(N, H, 64, 128, scale=0.06), _rand(N, H, 64, 128, scale=0.06)
+    e = _rand(N, H, 64, 128, scale=0.5)
+    decay = torch.rand(N, H, device=DEV) * 0.5 + 0.5
+    ext = _rand(N, H, 128, 128, scale=0.2) if reverse else None
+    ranges = (first, count, torch.from_numpy(np.stack((first, count), 1).copy()).to(DEV))
+    y, states = cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse)
+    torch.cuda.synchronize()
+    cu.check_status()
+    assert y.dtype == torch.bfloat16 and states.dtype == torch.bfloat16
+    y_ref, s_ref = scan_torch(x1, x2, e, decay, ext, first, count, reverse)
+    _close(y, y_ref, atol=0.03, rtol=3e-2, what="scan Y")
+    _close(states, s_ref, atol=0.03, rtol=3e-2, what="scan states")
+    y2, states2 = cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse)       # no atomics: bit-reproducible
+    assert torch.equal(y, y2) and torch.equal(states, states2)
+
+
+def test_gated_delta_rule_scan_path_matches_reference():
+    """Head size 128 takes the scan-kernel path; outputs and all five gradients against the fp32 reference."""
+    torch.manual_seed(11)
+    T, H, D = 700, 2, 128
+    cu_list = [0, 130, 130, 200, 641, 700]
+    cu_t = torch.tensor(cu_list, device=DEV, dtype=torch.int32)
+
+    def mk():
+        q, k, v = _rand(T, H, D), _rand(T, H, D), _rand(T, H, D)
+        g = (-torch.rand(T, H, device=DEV) * 0.3).float()
+        b = torch.rand(T, H, device=DEV).to(torch.bfloat16)
+        return [t.requires_grad_() for t in (q, k, v, g, b)]
+
+    ins = mk()
+    go = _rand(T, H, D, scale=0.5)
+    ins_ref = [t.detach().float().requires_grad_() for t in ins]
+    want = ref.gated_delta_rule(*ins_ref, cu_t)
+    want.backward(go.float())
+    got = ops.gated_delta_rule(*ins, cu_t, None, 64, cu_host=cu_list)
+    got.backward(go)
+    _cu().check_status()
+    _close(got, want, atol=0.03, rtol=4e-2, what="gdn out")
+    for name, a, b in zip("qkvgb", ins, ins_ref):
+        scale = float(b.grad.abs().max())
+        _close(a.grad, b.grad, atol=0.03 * scale + 1e-3, rtol=6e-2, what=f"gdn d{name}")

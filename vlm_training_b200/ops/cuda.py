@@ -689,16 +689,29 @@ def gdn_gates(a, b, A_log, dt_bias):
     return _GdnGates.apply(a, b, A_log, dt_bias)
 
 
+def gdn_scan(x1, x2, e, decay, ext, ranges, reverse):
+    """The chunk-to-chunk scan of :mod:`.gdn_scan` as one tcgen05 kernel launch (``csrc/gdn_scan_sm100.cu``):
+    bf16 operands ``[chunks, heads, 64, 128]``.  Other shapes run the tensor-operation loop."""
+    if x1.dtype == torch.bfloat16 and x1.shape[2:] == (64, 128) and e.shape[3] == 128:
+        y, states = _C.gdn_scan(x1, x2, e, decay.float().contiguous(), ext.to(torch.bfloat16) if ext is not None else None,
+                                ranges[2], reverse)
+        _tick()
+        return y, states
+    from .gdn_scan import scan_torch
+
+    return scan_torch(x1, x2, e, decay, ext, ranges[0], ranges[1], reverse)
+
+
 def gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale=None, chunk=64, cu_host=None):
-    if hasattr(_C, "gdn_chunk_fwd"):
-        from .gdn_cuda import gated_delta_rule_cuda
-
-        return gated_delta_rule_cuda(q, k, v, g, beta, cu_seqlens, scale, chunk)
-    # batched formulation on library GEMMs (no dedicated recurrence kernel in this build)
-    from .gdn_batched import gated_delta_rule_batched
-
     if cu_host is None:
         cu_host = cu_seqlens.tolist()  # one device sync; pass cu_host to avoid it
+    if q.shape[-1] == 128 and v.shape[-1] == 128 and chunk == 64 and os.environ.get("VLMT_GDN_SCAN", "1") != "0":
+        from .gdn_scan import gated_delta_rule_scan
+
+        return gated_delta_rule_scan(q, k, v, g, beta, cu_host, scale, chunk)
+    # other head sizes: the recurrence as batched library operations, one step per chunk position
+    from .gdn_batched import gated_delta_rule_batched
+
     return gated_delta_rule_batched(q, k, v, g, beta, cu_host, scale, chunk)
 
 
