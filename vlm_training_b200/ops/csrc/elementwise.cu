@@ -1080,82 +1080,149 @@ __global__ void gdn_gates_bwd_kernel(const float* __restrict__ dg, const bf16* _
 
 // ----------------------------------------------------------------------------------- depthwise causal conv1d + SiLU (packed rows)
 // x [T, C] (row stride xs), w [C, K] fp32/bf16, seq_idx [T]; y[t,c] = silu(sum_j w[c,j] x[t-(K-1)+j, c]) within a document
+// Sliding-window form: a thread owns 8 channels and walks `rows_per_thread` consecutive tokens, keeping the last K-1
+// input rows and its K x 8 weights in registers, so every input row and weight is read once (plus K-1 rows of overlap
+// per walk).  seq_idx is non-decreasing, so row t-k belongs to token t's document iff seq_idx[t-k] == seq_idx[t].
 template <int K>
 __global__ void conv1d_silu_fwd_kernel(const bf16* __restrict__ x, long xs, const bf16* __restrict__ w, const int* __restrict__ seq_idx,
-                                       bf16* __restrict__ y, long ys, int T, int C) {
-  const int c8 = C >> 3;
-  const long total = (long)T * c8;
-  for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-    const int t = (int)(idx / c8);
-    const int c = (int)(idx - (long)t * c8) * 8;
-    const int doc = seq_idx[t];
+                                       bf16* __restrict__ y, long ys, int T, int C, int rows_per_thread) {
+  static_assert(K == 4, "window code below is written for K = 4");
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int t0 = blockIdx.y * rows_per_thread;
+  const int t1 = min(T, t0 + rows_per_thread);
+  float wv[K][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint2 w4 = *reinterpret_cast<const uint2*>(w + (long)(c + i) * K);   // K = 4 bf16 = 8 bytes
+    wv[0][i] = __uint_as_float(w4.x << 16); wv[1][i] = __uint_as_float(w4.x & 0xffff0000u);
+    wv[2][i] = __uint_as_float(w4.y << 16); wv[3][i] = __uint_as_float(w4.y & 0xffff0000u);
+  }
+  float x1[8], x2[8], x3[8];   // rows t-1, t-2, t-3
+  int d1 = -1, d2 = -1, d3 = -1;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) x1[i] = x2[i] = x3[i] = 0.f;
+  if (t0 - 1 >= 0) { d1 = seq_idx[t0 - 1]; unpack8(*reinterpret_cast<const uint4*>(x + (long)(t0 - 1) * xs + c), x1); }
+  if (t0 - 2 >= 0) { d2 = seq_idx[t0 - 2]; unpack8(*reinterpret_cast<const uint4*>(x + (long)(t0 - 2) * xs + c), x2); }
+  if (t0 - 3 >= 0) { d3 = seq_idx[t0 - 3]; unpack8(*reinterpret_cast<const uint4*>(x + (long)(t0 - 3) * xs + c), x3); }
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t) {
+    float x0[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + (long)t * xs + c), x0);
+    const int d0 = seq_idx[t];
+    const float m1 = d1 == d0 ? 1.f : 0.f, m2 = d2 == d0 ? 1.f : 0.f, m3 = d3 == d0 ? 1.f : 0.f;
     float acc[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const int ts = t - (K - 1) + j;
-      if (ts < 0 || seq_idx[ts] != doc) continue;
-      float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(x + (long)ts * xs + c), f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += f[i] * __bfloat162float(w[(c + i) * K + j]);
+    for (int i = 0; i < 8; ++i) {
+      float a = x0[i] * wv[3][i];
+      a = fmaf(m1 * x1[i], wv[2][i], a);
+      a = fmaf(m2 * x2[i], wv[1][i], a);
+      a = fmaf(m3 * x3[i], wv[0][i], a);
+      acc[i] = a * sigmoidf_(a);
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = acc[i] * sigmoidf_(acc[i]);
     *reinterpret_cast<uint4*>(y + (long)t * ys + c) = pack8(acc);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { x3[i] = x2[i]; x2[i] = x1[i]; x1[i] = x0[i]; }
+    d3 = d2; d2 = d1; d1 = d0;
   }
 }
-// dx[t,c] = sum_j w[c,j] * dpre[t+(K-1)-j, c] (same document), dpre = dy * silu'(pre); dw partial per block.
-// pre is recomputed from x.  Each block covers a contiguous range of tokens for a slab of 8*blockDim.x... channels.
+// dx[t,c] = sum_j w[c,j] * dpre[t+(K-1)-j, c] (same document), dpre = dy * silu'(pre), pre recomputed from x;
+// dw[c,j] = sum_t dpre[t,c] x[t-(K-1)+j, c].  A thread owns 4 channels and walks one slab of tokens [t0, t1) plus K-1
+// tokens of lookahead (their dpre is needed for the slab's last dx rows; they do not count toward dw): at token t it
+// forms dpre[t] from the sliding input window and then emits dx[t-(K-1)] from the sliding dpre window.
 template <int K>
 __global__ void conv1d_silu_bwd_kernel(const bf16* __restrict__ dy, long dys, const bf16* __restrict__ x, long xs,
                                        const bf16* __restrict__ w, const int* __restrict__ seq_idx, bf16* __restrict__ dx, long dxs,
                                        float* __restrict__ dw_partial, int T, int C, int t_per_block) {
-  // thread -> one channel; block.y slab of tokens
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  static_assert(K == 4, "window code below is written for K = 4");
+  constexpr int V = 4;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
   if (c >= C) return;
   const int t0 = blockIdx.y * t_per_block;
   const int t1 = min(T, t0 + t_per_block);
-  float wv[K], dwacc[K];
+  float wv[K][V], dwacc[K][V];
 #pragma unroll
-  for (int j = 0; j < K; ++j) { wv[j] = __bfloat162float(w[c * K + j]); dwacc[j] = 0.f; }
-  // sliding windows: xw holds x[t-(K-1)..t]; dpre of tokens t..t+K-1 needed for dx[t] -> compute dpre on the fly
-  // by recomputing pre for up to K-1 tokens ahead (cheap: K=4).
-  auto pre_at = [&](int t) -> float {
-    const int doc = seq_idx[t];
-    float acc = 0.f;
+  for (int i = 0; i < V; ++i) {
+    const uint2 w4 = *reinterpret_cast<const uint2*>(w + (long)(c + i) * K);
+    wv[0][i] = __uint_as_float(w4.x << 16); wv[1][i] = __uint_as_float(w4.x & 0xffff0000u);
+    wv[2][i] = __uint_as_float(w4.y << 16); wv[3][i] = __uint_as_float(w4.y & 0xffff0000u);
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const int ts = t - (K - 1) + j;
-      if (ts >= 0 && seq_idx[ts] == doc) acc += __bfloat162float(x[(long)ts * xs + c]) * wv[j];
-    }
-    return acc;
+    for (int j = 0; j < K; ++j) dwacc[j][i] = 0.f;
+  }
+  auto ld4 = [&](const bf16* ptr, float (&f)[V]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(ptr);
+    f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+    f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
   };
-  auto dpre_at = [&](int t) -> float {
-    const float p = pre_at(t);
-    const float s = sigmoidf_(p);
-    return __bfloat162float(dy[(long)t * dys + c]) * (s + p * s * (1.f - s));
-  };
-  for (int t = t0; t < t1; ++t) {
-    const int doc = seq_idx[t];
-    float acc = 0.f;
+  float x1[V], x2[V], x3[V];          // input rows t-1, t-2, t-3
+  float p1[V], p2[V], p3[V];          // dpre of tokens t-1, t-2, t-3
+  int d1 = -1, d2 = -1, d3 = -1;      // their documents (-1: no such token)
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const int tt = t + (K - 1) - j;  // output token that used x[t] with tap j
-      if (tt < T && seq_idx[tt] == doc) acc += wv[j] * dpre_at(tt);
-    }
-    dx[(long)t * dxs + c] = __float2bfloat16(acc);
-    // dw[c,j] += dpre[t] * x[t-(K-1)+j]
-    const float dp = dpre_at(t);
+  for (int i = 0; i < V; ++i) x1[i] = x2[i] = x3[i] = p1[i] = p2[i] = p3[i] = 0.f;
+  // input rows before the slab are needed for pre[t0 ...]; dpre of tokens before the slab is never needed (dx looks ahead)
+  if (t0 - 1 >= 0) { d1 = seq_idx[t0 - 1]; ld4(x + (long)(t0 - 1) * xs + c, x1); }
+  if (t0 - 2 >= 0) { d2 = seq_idx[t0 - 2]; ld4(x + (long)(t0 - 2) * xs + c, x2); }
+  if (t0 - 3 >= 0) { d3 = seq_idx[t0 - 3]; ld4(x + (long)(t0 - 3) * xs + c, x3); }
+  const int t_end = t1 + (K - 1);
+#pragma unroll 2
+  for (int t = t0; t < t_end; ++t) {
+    float x0[V], p0[V];
+    int d0 = -2;                       // beyond the last token: matches no document
+    if (t < T) {
+      float g[V];
+      ld4(x + (long)t * xs + c, x0);
+      ld4(dy + (long)t * dys + c, g);
+      d0 = seq_idx[t];
+      const float m1 = d1 == d0 ? 1.f : 0.f, m2 = d2 == d0 ? 1.f : 0.f, m3 = d3 == d0 ? 1.f : 0.f;
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const int ts = t - (K - 1) + j;
-      if (ts >= 0 && seq_idx[ts] == doc) dwacc[j] += dp * __bfloat162float(x[(long)ts * xs + c]);
+      for (int i = 0; i < V; ++i) {
+        float a = x0[i] * wv[3][i];
+        a = fmaf(m1 * x1[i], wv[2][i], a);
+        a = fmaf(m2 * x2[i], wv[1][i], a);
+        a = fmaf(m3 * x3[i], wv[0][i], a);
+        const float sg = sigmoidf_(a);
+        p0[i] = g[i] * (sg + a * sg * (1.f - sg));
+      }
+      if (t < t1) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          dwacc[3][i] = fmaf(p0[i], x0[i], dwacc[3][i]);
+          dwacc[2][i] = fmaf(p0[i], m1 * x1[i], dwacc[2][i]);
+          dwacc[1][i] = fmaf(p0[i], m2 * x2[i], dwacc[1][i]);
+          dwacc[0][i] = fmaf(p0[i], m3 * x3[i], dwacc[0][i]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) { x0[i] = 0.f; p0[i] = 0.f; }
     }
+    // dx of token s = t - 3: taps j = 3, 2, 1, 0 meet dpre of tokens s, s+1, s+2, s+3 = t-3, t-2, t-1, t
+    const int sidx = t - (K - 1);
+    if (sidx >= t0) {
+      const float n2 = d2 == d3 ? 1.f : 0.f, n1 = d1 == d3 ? 1.f : 0.f, n0 = d0 == d3 ? 1.f : 0.f;
+      float o[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float a = wv[3][i] * p3[i];
+        a = fmaf(n2 * wv[2][i], p2[i], a);
+        a = fmaf(n1 * wv[1][i], p1[i], a);
+        a = fmaf(n0 * wv[0][i], p0[i], a);
+        o[i] = a;
+      }
+      uint2 pk;
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+      pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dx + (long)sidx * dxs + c) = pk;
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) { x3[i] = x2[i]; x2[i] = x1[i]; x1[i] = x0[i]; p3[i] = p2[i]; p2[i] = p1[i]; p1[i] = p0[i]; }
+    d3 = d2; d2 = d1; d1 = d0;
   }
 #pragma unroll
-  for (int j = 0; j < K; ++j) dw_partial[((size_t)blockIdx.y * C + c) * K + j] = dwacc[j];
+  for (int i = 0; i < V; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) dw_partial[((size_t)blockIdx.y * C + c + i) * K + j] = dwacc[j][i];
 }
 
 // ----------------------------------------------------------------------------------- row scatter / row add
@@ -1406,14 +1473,16 @@ int vlmt_gdn_gates_bwd(const float* dg, const void* dbeta, const void* a, const 
 
 int vlmt_conv1d_silu_fwd(const void* x, long xs, const void* w, const int* seq_idx, void* y, long ys, int T, int C, int K, cudaStream_t st) {
   if (K != 4 || (C & 7)) return -1;
-  conv1d_silu_fwd_kernel<4><<<grid_for((long)T * (C >> 3), 256, 148 * 16), 256, 0, st>>>(BF(x), xs, BF(w), seq_idx, BFM(y), ys, T, C);
+  const int rows = 64;
+  dim3 grid(((C >> 3) + 127) / 128, (T + rows - 1) / rows);
+  conv1d_silu_fwd_kernel<4><<<grid, 128, 0, st>>>(BF(x), xs, BF(w), seq_idx, BFM(y), ys, T, C, rows);
   return 0;
 }
 int vlmt_conv1d_bwd_slabs(int T) { return (T + 255) / 256; }
 int vlmt_conv1d_silu_bwd(const void* dy, long dys, const void* x, long xs, const void* w, const int* seq_idx, void* dx, long dxs,
                          float* dw_partial, int T, int C, int K, cudaStream_t st) {
-  if (K != 4) return -1;
-  dim3 grid((C + 127) / 128, vlmt_conv1d_bwd_slabs(T));
+  if (K != 4 || (C & 3)) return -1;
+  dim3 grid(((C >> 2) + 127) / 128, vlmt_conv1d_bwd_slabs(T));
   conv1d_silu_bwd_kernel<4><<<grid, 128, 0, st>>>(BF(dy), dys, BF(x), xs, BF(w), seq_idx, BFM(dx), dxs, dw_partial, T, C, 256);
   return 0;
 }

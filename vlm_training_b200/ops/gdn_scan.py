@@ -142,14 +142,14 @@ def gated_delta_rule_scan(q, k, v, g, beta, cu_host, scale=None, chunk: int = CH
     kb = kf * bf.unsqueeze(-1)
     vb = vf * bf.unsqueeze(-1)
     dec = gc.unsqueeze(-1) - gc.unsqueeze(-2)  # [N, H, C, C]: gc_i - gc_j
-    strict = torch.ones(chunk, chunk, dtype=torch.bool, device=dev).tril(-1)
     incl = torch.ones(chunk, chunk, dtype=torch.bool, device=dev).tril(0)
-    A = (kb @ kf.transpose(-1, -2)) * dec.masked_fill(~strict, float("-inf")).exp()
+    decay_incl = dec.masked_fill(~incl, float("-inf")).exp()      # exp(gc_i - gc_j) for j <= i, else 0
+    A = (kb @ kf.transpose(-1, -2)) * decay_incl.tril(-1)
     eye = torch.eye(chunk, device=dev, dtype=torch.float32)
     Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A).contiguous(), upper=False)
     w = Tm @ (kb * gc.exp().unsqueeze(-1))
     u = Tm @ vb
-    P = (qf @ kf.transpose(-1, -2)) * dec.masked_fill(~incl, float("-inf")).exp()
+    P = (qf @ kf.transpose(-1, -2)) * decay_incl
     qg = qf * gc.exp().unsqueeze(-1)
     last = gc[..., -1]
     kdec = kf * (last.unsqueeze(-1) - gc).exp().unsqueeze(-1)

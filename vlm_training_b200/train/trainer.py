@@ -54,6 +54,11 @@ class Trainer:
         logger.info(f"{self.mesh}")
         self.debug = bool(os.environ.get("DEBUG"))
         set_determinism(t.seed)  # one seed for every rank: weights are drawn identically without a broadcast
+        if self.device.type == "cuda":
+            # float32 library matmuls (the intra-chunk part of the gated delta rule) may use TF32 tensor cores, as in
+            # the reference trainer (train/train_qwen.py:65-66)
+            torch.backends.cuda.matmul.allow_tf32 = True
+            torch.backends.cudnn.allow_tf32 = True
         self.wandb = self._init_wandb()
 
         # ---------------- model
