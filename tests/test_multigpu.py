@@ -71,3 +71,15 @@ def test_fused_optimizer_matches_nccl(tmp_path):
     # weights after 4 steps at lr 1e-3: a flipped update sign shows as a ~2e-3 difference
     frac_off = ((probe_fused - probe_nccl).abs() > 5e-4).float().mean().item()
     assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ between the fused and the NCCL optimizer step"
+
+
+def test_in_place_weight_gradients_match_autograd_accumulation(tmp_path):
+    """Data parallel over 2 GPUs with bucketed overlap: weight-gradient GEMMs that add straight into the flat gradient
+    buffer (and report the parameter to the bucket logic by hand) against gradients accumulated by autograd."""
+    base = _run(tmp_path, 2, ["--training.fused_comm", "true"], 29706, {"VLMT_NO_MULTIMEM": "1", "VLMT_WGRAD_IN_PLACE": "0"})
+    probe_base = torch.tensor(_run.last_probe)
+    inplace = _run(tmp_path, 2, ["--training.fused_comm", "true"], 29707, {"VLMT_NO_MULTIMEM": "1", "VLMT_WGRAD_IN_PLACE": "1"})
+    probe_in = torch.tensor(_run.last_probe)
+    assert inplace == pytest.approx(base, rel=2e-3, abs=2e-3)
+    frac_off = ((probe_in - probe_base).abs() > 5e-4).float().mean().item()
+    assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ"
