@@ -3,6 +3,7 @@
     python -m vlm_training_b200.ops.microbench gemm --m 8192 --n 6144 --k 4096 [--layout fwd|dgrad|wgrad]
     python -m vlm_training_b200.ops.microbench attention --tokens 8192 --docs 1 [--backward]
     python -m vlm_training_b200.ops.microbench rmsnorm | swiglu | qkv_rope | ce | adamw | moe
+    python -m vlm_training_b200.ops.microbench gdn_scan --tokens 16384 --docs 1 [--backward]   |   conv1d [--backward]
     python -m vlm_training_b200.ops.microbench all            # the table used in the roofline report
 
 Each line is JSON: algorithmic FLOPs / bytes, median milliseconds, achieved rate, and the fraction of the
@@ -172,9 +173,49 @@ def bench_moe(t: Timer, tokens=16384, hidden=2048, inter=512, experts=256, topk=
     return _report("moe_experts_fwd_bwd", [tokens, hidden, inter, experts, topk], t(fb), flops=flops)
 
 
+def bench_gdn_scan(t: Timer, tokens=16384, docs=1, heads=32, reverse=False):
+    """The chunk-to-chunk scan of the gated delta rule: ``tokens / 64`` chunks split evenly over ``docs`` documents."""
+    import numpy as np
+
+    from . import cuda as cu
+
+    n = tokens // 64
+    per = n // docs
+    first = (np.arange(docs) * per).astype(np.int32)
+    count = np.full(docs, per, dtype=np.int32)
+    ranges = (first, count, torch.from_numpy(np.stack((first, count), 1).copy()).cuda())
+    x1, x2 = _r(n, heads, 64, 128, scale=0.05), _r(n, heads, 64, 128, scale=0.05)
+    e = _r(n, heads, 64, 128, scale=0.5)
+    decay = torch.rand(n, heads, device="cuda") * 0.3 + 0.7
+    ext = _r(n, heads, 128, 128, scale=0.1) if reverse else None
+    ms = t(lambda: cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse))
+    nbytes = 2.0 * n * heads * (4 * 64 * 128 + (2 if reverse else 1) * 128 * 128)   # 3 operand tiles in, Y and states out (+ ext in)
+    out = _report("gdn_scan_bwd" if reverse else "gdn_scan_fwd", [tokens, docs, heads], ms, nbytes=nbytes)
+    print(json.dumps({"kernel": "gdn_scan", "us_per_chunk_step": round(ms * 1e3 / per, 3)}))
+    return out
+
+
+def bench_conv1d(t: Timer, tokens=16384, channels=8192, backward=False):
+    from .. import ops
+    from . import reference as ref
+
+    x = _r(tokens, channels).requires_grad_()
+    w = _r(channels, 4, scale=0.5).requires_grad_()
+    cu_seq = torch.tensor([0, tokens // 3, tokens], device="cuda", dtype=torch.int32)
+    seq_idx = ref.seq_idx_from_cu(cu_seq, tokens)
+    g = _r(tokens, channels)
+    if backward:
+        y = ops.causal_conv1d_silu(x, w, seq_idx)
+        ms = t(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True))
+        return _report("conv1d_silu_bwd", [tokens, channels], ms, nbytes=2.0 * tokens * channels * 3)
+    with torch.no_grad():
+        ms = t(lambda: ops.causal_conv1d_silu(x, w, seq_idx))
+    return _report("conv1d_silu_fwd", [tokens, channels], ms, nbytes=2.0 * tokens * channels * 2)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "conv1d", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -206,6 +247,10 @@ def main(argv=None):
         bench_adamw(t)
     elif a.what == "moe":
         bench_moe(t)
+    elif a.what == "gdn_scan":
+        bench_gdn_scan(t, a.tokens, a.docs, reverse=a.backward)
+    elif a.what == "conv1d":
+        bench_conv1d(t, a.tokens, backward=a.backward)
     else:
         for layout in ("fwd", "dgrad", "wgrad"):
             bench_gemm(t, 8192, 6144, 4096, layout)
@@ -224,6 +269,11 @@ def main(argv=None):
         bench_ce(t)
         bench_adamw(t)
         bench_moe(t)
+        for docs in (1, 16):
+            bench_gdn_scan(t, 16384, docs)
+            bench_gdn_scan(t, 16384, docs, reverse=True)
+        bench_conv1d(t)
+        bench_conv1d(t, backward=True)
     from . import cuda as cu
 
     cu.check_status()
