@@ -493,8 +493,8 @@ def test_moe_experts_grouped_gemm(T, H, I, E, k):
     assert float(gate_up.grad[E - 1].abs().max()) == 0.0 and float(down.grad[E - 2].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("reverse", [False, True])
-def test_gdn_scan_kernel_matches_loop(reverse):
+@pytest.mark.parametrize("reverse,head_major", [(False, False), (True, False), (False, True), (True, True)])
+def test_gdn_scan_kernel_matches_loop(reverse, head_major):
     """The tcgen05 scan kernel against the same recurrence as a loop of fp32 tensor operations on the same bf16 inputs."""
     import numpy as np
 
@@ -511,14 +511,17 @@ def test_gdn_scan_kernel_matches_loop(reverse):
     decay = torch.rand(N, H, device=DEV) * 0.5 + 0.5
     ext = _rand(N, H, 128, 128, scale=0.2) if reverse else None
     ranges = (first, count, torch.from_numpy(np.stack((first, count), 1).copy()).to(DEV))
-    y, states = cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse)
+    if head_major:   # the same data in [H, N, ...] order
+        x1, x2, e, decay = (t.transpose(0, 1).contiguous() for t in (x1, x2, e, decay))
+        ext = ext.transpose(0, 1).contiguous() if ext is not None else None
+    y, states = cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse, head_major)
     torch.cuda.synchronize()
     cu.check_status()
     assert y.dtype == torch.bfloat16 and states.dtype == torch.bfloat16
-    y_ref, s_ref = scan_torch(x1, x2, e, decay, ext, first, count, reverse)
+    y_ref, s_ref = scan_torch(x1, x2, e, decay, ext, first, count, reverse, head_major)
     _close(y, y_ref, atol=0.03, rtol=3e-2, what="scan Y")
     _close(states, s_ref, atol=0.03, rtol=3e-2, what="scan states")
-    y2, states2 = cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse)       # no atomics: bit-reproducible
+    y2, states2 = cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse, head_major)       # no atomics: bit-reproducible
     assert torch.equal(y, y2) and torch.equal(states, states2)
 
 

@@ -102,17 +102,17 @@ void gemm_grouped(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& p
 
 // chunk-to-chunk scan of the gated delta rule (gdn_scan_sm100.h); ranges: int32 device tensor [n_docs, 2]
 std::vector<Tensor> gdn_scan(const Tensor& x1, const Tensor& x2, const Tensor& e, const Tensor& decay, const c10::optional<Tensor>& ext,
-                             const Tensor& ranges, bool reverse) {
+                             const Tensor& ranges, bool reverse, bool head_major) {
   check_bf16(x1, "x1"); check_bf16(x2, "x2"); check_bf16(e, "e");
   check_contig(x1, "x1"); check_contig(x2, "x2"); check_contig(e, "e"); check_contig(decay, "decay");
   TORCH_CHECK(x1.dim() == 4 && x1.size(2) == 64 && x1.size(3) == 128 && x2.sizes() == x1.sizes() && e.sizes() == x1.sizes(),
-              "gdn_scan: operands must be [chunks, heads, 64, 128]");
-  TORCH_CHECK(decay.scalar_type() == at::kFloat && decay.numel() == x1.size(0) * x1.size(1), "gdn_scan: decay must be fp32 [chunks, heads]");
+              "gdn_scan: operands must be [chunks, heads, 64, 128] (or [heads, chunks, 64, 128])");
+  TORCH_CHECK(decay.scalar_type() == at::kFloat && decay.numel() == x1.size(0) * x1.size(1), "gdn_scan: decay must be fp32, one value per (chunk, head)");
   TORCH_CHECK(ranges.scalar_type() == at::kInt && ranges.is_cuda() && ranges.is_contiguous() && ranges.dim() == 2 && ranges.size(1) == 2);
   c10::cuda::CUDAGuard guard(x1.device());
-  const int N = (int)x1.size(0), H = (int)x1.size(1);
+  const int N = (int)x1.size(head_major ? 1 : 0), H = (int)x1.size(head_major ? 0 : 1);
   Tensor y = at::empty_like(e);
-  Tensor states = at::empty({N, H, 128, 128}, x1.options());
+  Tensor states = at::empty({x1.size(0), x1.size(1), 128, 128}, x1.options());
   const void* extp = nullptr;
   if (ext.has_value()) {
     check_bf16(*ext, "ext"); check_contig(*ext, "ext");
@@ -121,7 +121,7 @@ std::vector<Tensor> gdn_scan(const Tensor& x1, const Tensor& x2, const Tensor& e
   }
   Tensor st = status_tensor();
   int r = vlmt_gdn_scan(x1.data_ptr(), x2.data_ptr(), e.data_ptr(), decay.data_ptr<float>(), extp, y.data_ptr(), states.data_ptr(),
-                        ranges.data_ptr<int>(), (int)ranges.size(0), N, H, reverse ? 1 : 0, st.data_ptr<int>(), cur_stream());
+                        ranges.data_ptr<int>(), (int)ranges.size(0), N, H, head_major ? 1 : 0, reverse ? 1 : 0, st.data_ptr<int>(), cur_stream());
   TORCH_CHECK(r == 0, "vlmt_gdn_scan failed with code ", r);
   return {y, states};
 }

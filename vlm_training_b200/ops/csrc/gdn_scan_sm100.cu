@@ -48,6 +48,7 @@ struct Params {
   __nv_bfloat16* states;        // [N, H, DV, DK]
   const int2* ranges;           // per document: first chunk, chunk count
   int H;
+  int cs, hs;                   // tile index of (chunk c, head h) = c * cs + h * hs: [N, H] or [H, N] tile order
   int* status;
 };
 
@@ -69,11 +70,12 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int2 range = p.ranges[blockIdx.x];
-  const int h = blockIdx.y, H = p.H;
+  const int h = blockIdx.y;
   const int n_steps = range.y;
   if (n_steps <= 0) return;  // uniform for the CTA
   // chunk visited at step n
   auto chunk_of = [&](int n) { return REVERSE ? range.x + n_steps - 1 - n : range.x + n; };
+  auto tile_of = [&](int chunk) { return chunk * p.cs + h * p.hs; };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
@@ -94,7 +96,7 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         const int s = n & 1;
         const uint32_t ph = ((n >> 1) & 1) ^ 1;
         if (!mbar_wait(&x_empty[s], ph, abort_flag, p.status, kErrTimeoutEmpty)) break;
-        const int row = (chunk_of(n) * H + h) * C;
+        const int row = tile_of(chunk_of(n)) * C;
         uint8_t* st = smem + s * kStage;
         mbar_expect_tx(&x_full[s], kStage);
 #pragma unroll
@@ -138,7 +140,7 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t acc = tmem_base + ACC_COL + lane_addr, a1 = tmem_base + A1_COL + lane_addr, yacc = tmem_base + Y_COL + lane_addr;
     constexpr float s1 = REVERSE ? 1.f : -1.f, s2 = REVERSE ? -1.f : 1.f;
-    auto state_row = [&](int chunk) { return ((size_t)(chunk * H + h) * DV + dv) * DK; };
+    auto state_row = [&](int chunk) { return ((size_t)tile_of(chunk) * DV + dv) * DK; };
 
     // ---- prologue: Z = 0 entering the first step; ACC = ext[first]
     {
@@ -196,7 +198,7 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         tmem_ld_wait();
         const uint8_t* et = smem + s * kStage + 2 * kTile + (dv >> 6) * 8192;
         const int ci = (dv & 63) >> 3, ce = (dv & 7) * 2;
-        __nv_bfloat16* yrow = p.Y + ((size_t)(c * H + h) * C) * DV + dv;
+        __nv_bfloat16* yrow = p.Y + ((size_t)tile_of(c) * C) * DV + dv;
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < C; i += 2) {
@@ -217,7 +219,7 @@ gdn_scan_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       }
       if (!has_next) break;
       // ---- new state: store it, repack it, prepare ACC for the next step
-      const float dn = p.decay[cn * H + h];
+      const float dn = p.decay[tile_of(cn)];
       uint4 ex[16];
       if (REVERSE && p.ext != nullptr) {   // independent of the recurrence: in flight while the second product runs
         const uint4* er = reinterpret_cast<const uint4*>(p.ext + state_row(cn));
@@ -290,7 +292,7 @@ int launch(const CUtensorMap& t1, const CUtensorMap& t2, const CUtensorMap& te, 
 }  // namespace
 
 extern "C" int vlmt_gdn_scan(const void* x1, const void* x2, const void* e, const float* decay, const void* ext, void* y,
-                             void* states, const int* ranges, int n_docs, int n_chunks, int H, int reverse, int* status,
+                             void* states, const int* ranges, int n_docs, int n_chunks, int H, int head_major, int reverse, int* status,
                              cudaStream_t stream) {
   if (n_docs <= 0 || n_chunks <= 0) return 0;
   const uint64_t rows = (uint64_t)n_chunks * H * C;
@@ -306,6 +308,8 @@ extern "C" int vlmt_gdn_scan(const void* x1, const void* x2, const void* e, cons
   p.states = reinterpret_cast<__nv_bfloat16*>(states);
   p.ranges = reinterpret_cast<const int2*>(ranges);
   p.H = H;
+  p.cs = head_major ? 1 : H;
+  p.hs = head_major ? n_chunks : 1;
   p.status = status;
   return reverse ? launch<true>(t1, t2, te, p, n_docs, stream) : launch<false>(t1, t2, te, p, n_docs, stream);
 }

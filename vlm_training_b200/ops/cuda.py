@@ -689,17 +689,18 @@ def gdn_gates(a, b, A_log, dt_bias):
     return _GdnGates.apply(a, b, A_log, dt_bias)
 
 
-def gdn_scan(x1, x2, e, decay, ext, ranges, reverse):
+def gdn_scan(x1, x2, e, decay, ext, ranges, reverse, head_major=False):
     """The chunk-to-chunk scan of :mod:`.gdn_scan` as one tcgen05 kernel launch (``csrc/gdn_scan_sm100.cu``):
-    bf16 operands ``[chunks, heads, 64, 128]``.  Other shapes run the tensor-operation loop."""
+    bf16 operands ``[chunks, heads, 64, 128]`` (``head_major``: ``[heads, chunks, 64, 128]``).  Other shapes run the
+    tensor-operation loop."""
     if x1.dtype == torch.bfloat16 and x1.shape[2:] == (64, 128) and e.shape[3] == 128:
         y, states = _C.gdn_scan(x1, x2, e, decay.float().contiguous(), ext.to(torch.bfloat16) if ext is not None else None,
-                                ranges[2], reverse)
+                                ranges[2], reverse, head_major)
         _tick()
         return y, states
     from .gdn_scan import scan_torch
 
-    return scan_torch(x1, x2, e, decay, ext, ranges[0], ranges[1], reverse)
+    return scan_torch(x1, x2, e, decay, ext, ranges[0], ranges[1], reverse, head_major)
 
 
 def gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale=None, chunk=64, cu_host=None):

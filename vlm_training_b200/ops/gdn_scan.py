@@ -50,10 +50,15 @@ def doc_chunk_ranges(cu_host, chunk: int = CHUNK):
     return dst, int(n_per.sum()), first_all[keep].astype(np.int32), n_per[keep].astype(np.int32)
 
 
-def scan_torch(x1, x2, e, decay, ext, first, count, reverse: bool):
+def scan_torch(x1, x2, e, decay, ext, first, count, reverse: bool, head_major: bool = False):
     """The scan as a loop of tensor operations (CPU, and the statement the kernel is tested against).
-    ``x1, x2 [N,H,C,Dk]``, ``e [N,H,C,Dv]``, ``decay [N,H]``, ``ext [N,H,Dv,Dk]`` or ``None``.
+    ``x1, x2 [N,H,C,Dk]``, ``e [N,H,C,Dv]``, ``decay [N,H]``, ``ext [N,H,Dv,Dk]`` or ``None``
+    (``head_major``: the first two dimensions exchanged, in and out).
     Returns ``(Y [N,H,C,Dv], states [N,H,Dv,Dk])`` in float32."""
+    if head_major:
+        y, st = scan_torch(x1.transpose(0, 1), x2.transpose(0, 1), e.transpose(0, 1), decay.transpose(0, 1),
+                           ext.transpose(0, 1) if ext is not None else None, first, count, reverse)
+        return y.transpose(0, 1).contiguous(), st.transpose(0, 1).contiguous()
     N, H, C, Dk = x1.shape
     Dv = e.shape[-1]
     s1, s2 = (1.0, -1.0) if reverse else (-1.0, 1.0)
@@ -77,13 +82,13 @@ def _scan_impl(x1, x2, e, decay, ext, ranges, reverse):
     if x1.is_cuda:
         from . import cuda as cu
 
-        return cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse)
+        return cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse, head_major=True)
     first, count = ranges[0], ranges[1]
-    return scan_torch(x1, x2, e, decay, ext, first, count, reverse)
+    return scan_torch(x1, x2, e, decay, ext, first, count, reverse, head_major=True)
 
 
 class _Scan(torch.autograd.Function):
-    """``(w, u, kdec, decay) -> (S_all^T [N,H,Dv,Dk], vnew [N,H,C,Dv])``.
+    """``(w, u, kdec, decay) -> (S_all^T [H,N,Dv,Dk], vnew [H,N,C,Dv])``; all tensors head-major ``[H, N, ...]``.
 
     Backward, with ``G_c`` the gradient with respect to the state entering chunk ``c + 1`` accumulated over everything
     that follows it: ``dvnew_c = dvnew_ext_c + kdec_c G_c``, ``G_{c-1} = dS_ext_c + decay_c G_c - w_c^T dvnew_c`` (the
@@ -128,15 +133,18 @@ def gated_delta_rule_scan(q, k, v, g, beta, cu_host, scale=None, chunk: int = CH
     dst = torch.from_numpy(dst_np).to(dev, non_blocking=True)
     ranges = (first, count, torch.from_numpy(np.stack((first, count), 1).copy()).to(dev, non_blocking=True))
 
-    def pad(x):  # [T, H, ...] -> [n_slots, H, chunk, ...]; padding rows are zero and have no effect
-        out = x.new_zeros((n_slots * chunk,) + tuple(x.shape[1:]))
-        out = out.index_copy(0, dst, x[:Tc])
-        return out.view(n_slots, chunk, *x.shape[1:]).transpose(1, 2)
+    # Head-major padded layout [H, n_slots, chunk, ...]: one index_copy per tensor writes it contiguously, so the batched
+    # products below never re-copy a transposed view.  Padding rows are zero and have no effect.
+    def pad(x):  # [T, H, ...] -> [H, n_slots, chunk, ...]
+        xt = x[:Tc].transpose(0, 1)
+        out = xt.new_zeros((H, n_slots * chunk) + tuple(x.shape[2:]))
+        out.index_copy_(1, dst, xt)
+        return out.view(H, n_slots, chunk, *x.shape[2:])
 
-    qf = pad(l2norm(q) * scale)
-    kf = pad(l2norm(k))
-    vf = pad(v.float())
-    gf = pad(g.float())        # [N, H, C]
+    qf = l2norm(pad(q)) * scale
+    kf = l2norm(pad(k))
+    vf = pad(v).float()
+    gf = pad(g.float())        # [H, N, C]
     bf = pad(beta.float())
     gc = gf.cumsum(-1)
     kb = kf * bf.unsqueeze(-1)
@@ -155,9 +163,8 @@ def gated_delta_rule_scan(q, k, v, g, beta, cu_host, scale=None, chunk: int = CH
     kdec = kf * (last.unsqueeze(-1) - gc).exp().unsqueeze(-1)
     states, vnew = _Scan.apply(w.to(work_dtype).contiguous(), u.to(work_dtype).contiguous(),
                                kdec.to(work_dtype).contiguous(), last.exp().contiguous(), ranges)
-    o = qg.to(work_dtype) @ states.transpose(-1, -2) + P.to(work_dtype) @ vnew      # [N, H, C, Dv]
-    o = o.transpose(1, 2).reshape(n_slots * chunk, H, Dv)
-    out = o.index_select(0, dst)
+    o = qg.to(work_dtype) @ states.transpose(-1, -2) + P.to(work_dtype) @ vnew      # [H, N, C, Dv]
+    out = o.reshape(H, n_slots * chunk, Dv).index_select(1, dst).transpose(0, 1)     # [Tc, H, Dv]
     if Tc < T:
         out = torch.cat((out, out.new_zeros(T - Tc, H, Dv)), 0)
     return out.to(v.dtype)

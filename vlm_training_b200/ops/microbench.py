@@ -188,7 +188,7 @@ def bench_gdn_scan(t: Timer, tokens=16384, docs=1, heads=32, reverse=False):
     e = _r(n, heads, 64, 128, scale=0.5)
     decay = torch.rand(n, heads, device="cuda") * 0.3 + 0.7
     ext = _r(n, heads, 128, 128, scale=0.1) if reverse else None
-    ms = t(lambda: cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse))
+    ms = t(lambda: cu.gdn_scan(x1, x2, e, decay, ext, ranges, reverse, False))
     nbytes = 2.0 * n * heads * (4 * 64 * 128 + (2 if reverse else 1) * 128 * 128)   # 3 operand tiles in, Y and states out (+ ext in)
     out = _report("gdn_scan_bwd" if reverse else "gdn_scan_fwd", [tokens, docs, heads], ms, nbytes=nbytes)
     print(json.dumps({"kernel": "gdn_scan", "us_per_chunk_step": round(ms * 1e3 / per, 3)}))
