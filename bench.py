@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--ac", default="auto", choices=["auto", "off", "full", "sac"])
     ap.add_argument("--tp", type=int, default=0, help="0 = 1 for one GPU, 2 otherwise")
     ap.add_argument("--no-sp", action="store_true")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel group size (MoE models; data parallel only, tp = 1)")
     ap.add_argument("--ce-chunk", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the number of decoder layers (result is not a bench value)")
     ap.add_argument("--opt-state", default="auto", choices=["auto", "fp32", "bf16"])
@@ -94,11 +95,13 @@ def build_config(args, world: int):
     from vlm_training_b200.config import Config
 
     cfg = Config()
-    name = "Qwen3-VL-8B" if "vl" in args.model else ("Qwen3.5-9B" if "3.5" in args.model else "Qwen3-8B")
+    name = "Qwen3-VL-8B" if "vl" in args.model else ("Qwen3.5-35B-A3B" if "moe" in args.model else
+                                                      ("Qwen3.5-9B" if "3.5" in args.model else "Qwen3-8B"))
     cfg.model.model_name, cfg.model.preset = name, args.model
     cfg.model.train_llm = cfg.model.train_mlp = cfg.model.train_vit = True
     t = cfg.training
-    tp = args.tp if args.tp else (1 if world == 1 else 2)
+    tp = args.tp if args.tp else (1 if (world == 1 or args.ep > 1) else 2)
+    t.ep_size = args.ep
     t.tp_size, t.sequence_parallel = tp, (tp > 1 and not args.no_sp)
     t.data_parallel = "fsdp"
     t.bfloat16, t.device = True, "cuda"
@@ -126,14 +129,17 @@ def run_ours(args):
     from vlm_training_b200.train.trainer import Trainer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.layers:
+    if args.layers or "moe" in args.model:
         base = mc._PRESETS[args.model]
 
-        def fewer():
+        def adjusted():
             c = base()
-            c.text.num_hidden_layers = args.layers
+            if args.layers:
+                c.text.num_hidden_layers = args.layers
+            if "moe" in args.model:
+                c.vision = None   # text rows only: the vision tower of this preset would hold parameters that never get a gradient
             return c
-        mc._PRESETS[args.model] = fewer
+        mc._PRESETS[args.model] = adjusted
     cfg = build_config(args, world)
     tr = Trainer(cfg)
     # activations of the vision tower are kept (no recomputation): on one GPU the step then peaks at about 155 of
@@ -244,7 +250,8 @@ def run_ours(args):
             "tokens_per_sec_per_gpu": value / n,
             "mfu_vs_measured_sustained": value * flops_tok / n / tr.peak_flops,
             "config": {"model": args.model, "global_batch": int(round(global_tokens / args.seq_len)), "seq_len": args.seq_len,
-                       "parallelism": f"fsdp{tr.mesh.dp}xtp{tr.mesh.tp}" + ("+sp" if cfg.training.sequence_parallel else ""),
+                       "parallelism": f"fsdp{tr.mesh.dp}xtp{tr.mesh.tp}" + ("+sp" if cfg.training.sequence_parallel else "")
+                                      + (f"+ep{args.ep}" if args.ep > 1 else ""),
                        "ac_mode": cfg.training.ac_mode, "optimizer": f"AdamW, fp32 master + {cfg.training.optimizer_state_dtype} moments, sharded over dp", "vit_ac": vit_ac,
                        "l2": "not flushed: every step streams >17 GB of weights, far above the 126 MB L2",
                        "layers_override": args.layers or None, "ce_chunk": args.ce_chunk},
