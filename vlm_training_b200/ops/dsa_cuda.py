@@ -11,10 +11,29 @@ from __future__ import annotations
 import math
 
 import torch
+import torch.utils.checkpoint as _ckpt
 
 from . import cuda as cu
 
 _QBLOCK = 1024
+
+
+def _block_attention(qb, kd, vd, sel, valid, scale, rep):
+    """Softmax attention of one query block over its selected keys: ``qb [B,Hq,D]``, ``kd, vd [L,Hkv,D]``,
+    ``sel, valid [B,kk]``.  Differentiable with respect to ``qb``, ``kd`` and ``vd``."""
+    B, Hq, D = qb.shape
+    Hkv = kd.shape[1]
+    # head-major float32 copies of the document's keys / values (small), gathered straight into the [Hkv, B, kk, D]
+    # layout the batched products want: one write of the gathered block, no permuted re-copies
+    kt = kd.float().transpose(0, 1).contiguous()
+    vt = vd.float().transpose(0, 1).contiguous()
+    kg = kt[:, sel]                                             # [Hkv, B, kk, D]
+    vg = vt[:, sel]
+    q4 = qb.float().view(B, Hkv, rep, D).transpose(0, 1)         # [Hkv, B, rep, D]
+    att = torch.matmul(q4, kg.transpose(-1, -2)) * scale         # [Hkv, B, rep, kk]
+    att = att.masked_fill(~valid[None, :, None, :], float("-inf")).softmax(-1)
+    out = torch.matmul(att, vg)                                  # [Hkv, B, rep, D]
+    return out.transpose(0, 1).reshape(B, Hq, D)
 
 
 def dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None):
@@ -40,20 +59,20 @@ def dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=Non
         for b0 in range(0, L, _QBLOCK):
             b1 = min(L, b0 + _QBLOCK)
             n_keys = b1  # causal: keys [0, b1)
-            sc = torch.einsum("thd,sd->ths", idx_q[s + b0:s + b1].float(), ik[:n_keys]).relu_()
-            sc = (sc * idx_w[s + b0:s + b1].float().unsqueeze(-1)).sum(1)  # [B, n_keys]
-            qpos = torch.arange(b0, b1, device=q.device).unsqueeze(1)
-            kpos = torch.arange(n_keys, device=q.device).unsqueeze(0)
-            sc = sc.masked_fill(kpos > qpos, float("-inf"))
-            kk = min(topk, n_keys)
-            sel = sc.topk(kk, dim=-1).indices  # [B, kk]
-            valid = sel <= qpos  # picks that were -inf (fewer than kk causal keys) are masked out
-            kg = kd[sel].float()  # [B, kk, Hkv, D]
-            vg = vd[sel].float()
-            qb = q[s + b0:s + b1].float().view(b1 - b0, Hkv, rep, D)
-            att = torch.einsum("bgrd,bkgd->bgrk", qb, kg) * scale
-            att = att.masked_fill(~valid[:, None, None, :], float("-inf")).softmax(-1)
-            doc_out.append(torch.einsum("bgrk,bkgd->bgrd", att, vg).reshape(b1 - b0, Hq, D))
+            with torch.no_grad():  # the selection is an index set: nothing of it is kept for backward
+                sc = torch.einsum("thd,sd->ths", idx_q[s + b0:s + b1].float(), ik[:n_keys]).relu_()
+                sc = (sc * idx_w[s + b0:s + b1].float().unsqueeze(-1)).sum(1)  # [B, n_keys]
+                qpos = torch.arange(b0, b1, device=q.device).unsqueeze(1)
+                kpos = torch.arange(n_keys, device=q.device).unsqueeze(0)
+                sc = sc.masked_fill(kpos > qpos, float("-inf"))
+                kk = min(topk, n_keys)
+                sel = sc.topk(kk, dim=-1).indices  # [B, kk]
+                valid = sel <= qpos  # picks that were -inf (fewer than kk causal keys) are masked out
+                del sc
+            # the gathered keys / values of a block are 2 x B x kk x Hkv x D floats (gigabytes at topk 2048): they are
+            # rebuilt in backward instead of being kept, so a long document costs one block of them at a time
+            doc_out.append(_ckpt.checkpoint(_block_attention, q[s + b0:s + b1], kd, vd, sel, valid, scale, rep,
+                                            use_reentrant=False))
         outs.append(torch.cat(doc_out, 0).to(q.dtype))
     if bounds[-1] < T:
         outs.append(q.new_zeros(T - bounds[-1], Hq, D))
