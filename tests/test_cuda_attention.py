@@ -98,3 +98,41 @@ def test_attention_growing_scores(causal):
     _close(q.grad, qr.grad, 0.08, 5e-2, "dq")
     _close(k.grad, kr.grad, 0.08, 5e-2, "dk")
     _close(v.grad, vr.grad, 0.08, 5e-2, "dv")
+
+
+@pytest.mark.parametrize("D,Hkv,rep,L,B,kk", [(256, 2, 8, 700, 96, 300), (64, 2, 2, 300, 50, 64), (128, 1, 4, 513, 33, 2048)])
+def test_dsa_selected_attention_kernels(D, Hkv, rep, L, B, kk):
+    """Selected-key attention kernels (forward and backward) against the gathered dense softmax in float32."""
+    from vlm_training_b200.ops import dsa_cuda
+
+    torch.manual_seed(2)
+    kk = min(kk, L)
+    q = (torch.randn(B, Hkv * rep, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    k = (torch.randn(L, Hkv, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    v = torch.randn(L, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    sel = torch.stack([torch.randperm(L, device="cuda")[:kk] for _ in range(B)])
+    valid = torch.rand(B, kk, device="cuda") > 0.3
+    valid[:, 0] = True
+    valid[1] = False                       # a query without any key: zero output, zero gradients
+    scale = D ** -0.5
+    go = torch.randn(B, Hkv * rep, D, device="cuda").to(torch.bfloat16)
+    sel32 = torch.where(valid, sel, -1).to(torch.int32)
+    got = dsa_cuda._SelectedAttention.apply(q, k, v, sel32, scale)
+    got.backward(go)
+    grads = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    v2 = valid.clone()
+    v2[1, 0] = True                        # the tensor form cannot softmax an empty row; row 1 is compared separately
+    want = dsa_cuda._block_attention(q, k, v, sel, v2, scale, rep)
+    mask = torch.ones(B, 1, 1, device="cuda")
+    mask[1] = 0
+    (want * mask).backward(go.float())
+    assert float(got[1].abs().max()) == 0.0
+    torch.testing.assert_close(got.float() * mask, want * mask, atol=2e-2, rtol=2e-2)
+    for name, a, t in zip("qkv", grads, (q, k, v)):
+        ref = t.grad.float()
+        tol = 2e-2 * float(ref.abs().max()) + 1e-3
+        assert float((a.float() - ref).abs().max()) <= tol, (name, float((a.float() - ref).abs().max()), tol)
+    a2 = dsa_cuda._SelectedAttention.apply(q, k, v, sel32, scale)
+    assert torch.equal(a2, got)

@@ -1,0 +1,257 @@
+// Sparse (selected-key) attention for DSA: every query attends to its own list of up to `kk` key rows.
+//
+// One CTA per (query, kv head): the `REP` query heads that share the kv head are processed together, so every selected
+// key / value row is read once per CTA.  Each query has its own key set, so there is no tile shared between queries to
+// put on the tensor cores (M would be REP = 8); the kernel is a CUDA-core kernel bound by the gathered reads:
+//   phase 1  thread <-> key:  s[j][h] = scale * q[h] . K[sel[j]]           (16-byte key loads, q broadcast from smem)
+//   phase 2  warp   <-> head: m[h], l[h], p = exp(s - m)                    (scores stay in shared memory)
+//   phase 3  thread <-> dim:  o[h][d] = sum_j p[j][h] V[sel[j]][d] / l[h]   (coalesced value loads)
+// The backward kernel recomputes p from the saved log-sum-exp, forms dS in phase 1 (thread <-> key, second pass over
+// the value row for dP) and accumulates dQ in registers and dK / dV with float atomics in phase 2 (thread <-> dim).
+// sel[j] < 0 marks an unused slot.  No waits on other CTAs anywhere.
+#include "dsa_attention.h"
+
+#include <cuda_bf16.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int THREADS = 256;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// dot products of one key (or value) row with the REP rows of `a_s` ([REP][D] floats in shared memory)
+template <int D, int REP>
+__device__ __forceinline__ void row_dots(const __nv_bfloat16* __restrict__ row, const float* __restrict__ a_s, float (&acc)[REP]) {
+#pragma unroll
+  for (int h = 0; h < REP; ++h) acc[h] = 0.f;
+#pragma unroll 4
+  for (int c = 0; c < D / 8; ++c) {
+    float kf[8];
+    unpack8(*reinterpret_cast<const uint4*>(row + c * 8), kf);
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      const float4 a0 = *reinterpret_cast<const float4*>(a_s + h * D + c * 8);
+      const float4 a1 = *reinterpret_cast<const float4*>(a_s + h * D + c * 8 + 4);
+      acc[h] += kf[0] * a0.x + kf[1] * a0.y + kf[2] * a0.z + kf[3] * a0.w + kf[4] * a1.x + kf[5] * a1.y + kf[6] * a1.z + kf[7] * a1.w;
+    }
+  }
+}
+
+struct Params {
+  const __nv_bfloat16* q;    // [B, Hkv * REP, D]
+  const __nv_bfloat16* k;    // [L, Hkv, D]
+  const __nv_bfloat16* v;    // [L, Hkv, D]
+  const int* sel;            // [B, kk], -1 = unused
+  __nv_bfloat16* o;          // [B, Hkv * REP, D]
+  float* lse;                // [B, Hkv * REP]  natural-log sum-exp of the scaled scores
+  const __nv_bfloat16* d_o;  // backward only
+  float* dq;                 // [B, Hkv * REP, D]
+  float* dk;                 // [L, Hkv, D] accumulated with atomics
+  float* dv;
+  int B, Hkv, kk;
+  float scale;
+};
+
+template <int D, int REP>
+__global__ void __launch_bounds__(THREADS) dsa_fwd_kernel(Params p) {
+  extern __shared__ float smem[];
+  float* q_s = smem;                       // [REP][D]
+  float* s_s = q_s + REP * D;              // [kk][REP]
+  float* ml_s = s_s + (size_t)p.kk * REP;  // [2][REP]: max, 1 / sum
+  int* sel_s = reinterpret_cast<int*>(ml_s + 2 * REP);  // [kk]
+  const int b = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int Hq = p.Hkv * REP;
+  const __nv_bfloat16* qrow = p.q + ((size_t)b * Hq + g * REP) * D;
+  for (int i = tid; i < REP * D; i += THREADS) q_s[i] = __bfloat162float(qrow[i]);
+  for (int j = tid; j < p.kk; j += THREADS) sel_s[j] = p.sel[(size_t)b * p.kk + j];
+  __syncthreads();
+  // ---- phase 1
+  for (int j = tid; j < p.kk; j += THREADS) {
+    const int idx = sel_s[j];
+    float acc[REP];
+    if (idx >= 0) {
+      row_dots<D, REP>(p.k + ((size_t)idx * p.Hkv + g) * D, q_s, acc);
+#pragma unroll
+      for (int h = 0; h < REP; ++h) s_s[j * REP + h] = acc[h] * p.scale;
+    } else {
+#pragma unroll
+      for (int h = 0; h < REP; ++h) s_s[j * REP + h] = -INFINITY;
+    }
+  }
+  __syncthreads();
+  // ---- phase 2: warp h owns head h
+  for (int h = warp; h < REP; h += THREADS / 32) {
+    float m = -INFINITY;
+    for (int j = lane; j < p.kk; j += 32) m = fmaxf(m, s_s[j * REP + h]);
+    m = warp_max(m);
+    const float mm = m == -INFINITY ? 0.f : m;
+    float l = 0.f;
+    for (int j = lane; j < p.kk; j += 32) {
+      const float e = __expf(s_s[j * REP + h] - mm);
+      s_s[j * REP + h] = e;
+      l += e;
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      ml_s[h] = mm;
+      ml_s[REP + h] = l > 0.f ? 1.f / l : 0.f;
+      p.lse[(size_t)b * Hq + g * REP + h] = l > 0.f ? mm + logf(l) : -INFINITY;
+    }
+  }
+  __syncthreads();
+  // ---- phase 3: thread <-> dim (threads beyond D idle for small heads)
+  if (tid < D) {
+    float acc[REP];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) acc[h] = 0.f;
+    for (int j = 0; j < p.kk; ++j) {
+      const int idx = sel_s[j];
+      if (idx < 0) continue;
+      const float vv = __bfloat162float(p.v[((size_t)idx * p.Hkv + g) * D + tid]);
+#pragma unroll
+      for (int h = 0; h < REP; ++h) acc[h] = fmaf(s_s[j * REP + h], vv, acc[h]);
+    }
+#pragma unroll
+    for (int h = 0; h < REP; ++h) p.o[((size_t)b * Hq + g * REP + h) * D + tid] = __float2bfloat16(acc[h] * ml_s[REP + h]);
+  }
+}
+
+template <int D, int REP>
+__global__ void __launch_bounds__(THREADS) dsa_bwd_kernel(Params p) {
+  extern __shared__ float smem[];
+  float* q_s = smem;                        // [REP][D]
+  float* do_s = q_s + REP * D;              // [REP][D]
+  float* p_s = do_s + REP * D;              // [kk][REP]  probabilities
+  float* ds_s = p_s + (size_t)p.kk * REP;   // [kk][REP]  gradient of the raw (unscaled) scores
+  float* st_s = ds_s + (size_t)p.kk * REP;  // [2][REP]: lse, delta
+  int* sel_s = reinterpret_cast<int*>(st_s + 2 * REP);
+  const int b = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int Hq = p.Hkv * REP;
+  const size_t row0 = ((size_t)b * Hq + g * REP) * D;
+  for (int i = tid; i < REP * D; i += THREADS) {
+    q_s[i] = __bfloat162float(p.q[row0 + i]);
+    do_s[i] = __bfloat162float(p.d_o[row0 + i]);
+  }
+  for (int j = tid; j < p.kk; j += THREADS) sel_s[j] = p.sel[(size_t)b * p.kk + j];
+  __syncthreads();
+  // delta[h] = sum_d dO[h][d] O[h][d]
+  for (int h = warp; h < REP; h += THREADS / 32) {
+    float acc = 0.f;
+    for (int d = lane; d < D; d += 32) acc += do_s[h * D + d] * __bfloat162float(p.o[row0 + (size_t)h * D + d]);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      st_s[h] = p.lse[(size_t)b * Hq + g * REP + h];
+      st_s[REP + h] = acc;
+    }
+  }
+  __syncthreads();
+  // ---- phase 1: thread <-> key: p, dS
+  for (int j = tid; j < p.kk; j += THREADS) {
+    const int idx = sel_s[j];
+    if (idx >= 0) {
+      float sc[REP], dp[REP];
+      row_dots<D, REP>(p.k + ((size_t)idx * p.Hkv + g) * D, q_s, sc);
+      row_dots<D, REP>(p.v + ((size_t)idx * p.Hkv + g) * D, do_s, dp);
+#pragma unroll
+      for (int h = 0; h < REP; ++h) {
+        const float lse = st_s[h];
+        const float pr = lse == -INFINITY ? 0.f : __expf(sc[h] * p.scale - lse);
+        p_s[j * REP + h] = pr;
+        ds_s[j * REP + h] = pr * (dp[h] - st_s[REP + h]) * p.scale;
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < REP; ++h) { p_s[j * REP + h] = 0.f; ds_s[j * REP + h] = 0.f; }
+    }
+  }
+  __syncthreads();
+  // ---- phase 2: thread <-> dim: dQ in registers, dK / dV with atomics
+  if (tid < D) {
+    float dq[REP], qv[REP], dov[REP];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) { dq[h] = 0.f; qv[h] = q_s[h * D + tid]; dov[h] = do_s[h * D + tid]; }
+    for (int j = 0; j < p.kk; ++j) {
+      const int idx = sel_s[j];
+      if (idx < 0) continue;
+      const size_t off = ((size_t)idx * p.Hkv + g) * D + tid;
+      const float kv = __bfloat162float(p.k[off]);
+      float dk = 0.f, dv = 0.f;
+#pragma unroll
+      for (int h = 0; h < REP; ++h) {
+        const float ds = ds_s[j * REP + h];
+        dq[h] = fmaf(ds, kv, dq[h]);
+        dk = fmaf(ds, qv[h], dk);
+        dv = fmaf(p_s[j * REP + h], dov[h], dv);
+      }
+      atomicAdd(p.dk + off, dk);
+      atomicAdd(p.dv + off, dv);
+    }
+#pragma unroll
+    for (int h = 0; h < REP; ++h) p.dq[row0 + (size_t)h * D + tid] = dq[h];
+  }
+}
+
+template <int D, int REP>
+int launch(const Params& p, bool backward, cudaStream_t st) {
+  const size_t smem = backward ? sizeof(float) * (2 * REP * D + 2 * (size_t)p.kk * REP + 2 * REP) + sizeof(int) * p.kk
+                               : sizeof(float) * (REP * D + (size_t)p.kk * REP + 2 * REP) + sizeof(int) * p.kk;
+  if (smem > 200 * 1024) return -3;
+  dim3 grid(p.B, p.Hkv);
+  if (backward) {
+    if (cudaFuncSetAttribute(dsa_bwd_kernel<D, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -4;
+    dsa_bwd_kernel<D, REP><<<grid, THREADS, smem, st>>>(p);
+  } else {
+    if (cudaFuncSetAttribute(dsa_fwd_kernel<D, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -4;
+    dsa_fwd_kernel<D, REP><<<grid, THREADS, smem, st>>>(p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int dispatch(const Params& p, int D, int rep, bool backward, cudaStream_t st) {
+  if (D == 256 && rep == 8) return launch<256, 8>(p, backward, st);
+  if (D == 128 && rep == 4) return launch<128, 4>(p, backward, st);
+  if (D == 64 && rep == 2) return launch<64, 2>(p, backward, st);
+  return -2;
+}
+}  // namespace
+
+extern "C" int vlmt_dsa_supported(int D, int rep) { return (D == 256 && rep == 8) || (D == 128 && rep == 4) || (D == 64 && rep == 2); }
+
+extern "C" int vlmt_dsa_fwd(const void* q, const void* k, const void* v, const int* sel, void* o, float* lse, int B, int Hkv, int rep,
+                            int D, int kk, float scale, cudaStream_t st) {
+  if (B <= 0 || kk <= 0) return 0;
+  Params p{};
+  p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v; p.sel = sel;
+  p.o = (__nv_bfloat16*)o; p.lse = lse; p.B = B; p.Hkv = Hkv; p.kk = kk; p.scale = scale;
+  return dispatch(p, D, rep, false, st);
+}
+
+extern "C" int vlmt_dsa_bwd(const void* q, const void* k, const void* v, const int* sel, const void* o, const float* lse, const void* d_o,
+                            float* dq, float* dk, float* dv, int B, int Hkv, int rep, int D, int kk, float scale, cudaStream_t st) {
+  if (B <= 0 || kk <= 0) return 0;
+  Params p{};
+  p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v; p.sel = sel;
+  p.o = (__nv_bfloat16*)const_cast<void*>(o); p.lse = const_cast<float*>(lse); p.d_o = (const __nv_bfloat16*)d_o;
+  p.dq = dq; p.dk = dk; p.dv = dv; p.B = B; p.Hkv = Hkv; p.kk = kk; p.scale = scale;
+  return dispatch(p, D, rep, true, st);
+}

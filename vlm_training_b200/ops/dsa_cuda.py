@@ -3,12 +3,15 @@
 Indexer scores → per-query top-k key selection → attention restricted to the selected keys.  This build
 computes the selection with batched library kernels per document (scores by one GEMM per indexer head
 block, ``topk``) in query blocks so the ``[L, L]`` score matrix is never larger than ``block x L``, and
-runs the attention over the selected keys as a gathered dense softmax in the same blocks.  Documents no
-longer than ``topk`` take the dense tcgen05 attention kernel directly (the selection keeps every causal key).
+runs the attention over the selected keys in the same blocks: with the CUDA kernels of ``csrc/dsa_attention.cu``
+(one CTA per query and kv head reads each selected key / value row once for the query heads that share it) for the
+supported head shapes, else as a gathered dense softmax of tensor operations.  Documents no longer than ``topk``
+take the dense tcgen05 attention kernel directly (the selection keeps every causal key).
 """
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.utils.checkpoint as _ckpt
@@ -16,6 +19,35 @@ import torch.utils.checkpoint as _ckpt
 from . import cuda as cu
 
 _QBLOCK = 1024
+
+
+class _SelectedAttention(torch.autograd.Function):
+    """Attention of a query block over per-query key lists, as the CUDA kernels of ``csrc/dsa_attention.cu``.
+    ``sel`` is int32 ``[B, kk]`` with -1 in unused slots.  The key / value gradients of the whole document come back as
+    float32 (atomics accumulate them), autograd sums the blocks' contributions."""
+
+    @staticmethod
+    def forward(ctx, qb, kd, vd, sel, scale):
+        qb, kd, vd = qb.contiguous(), kd.contiguous(), vd.contiguous()
+        o, lse = cu._C.dsa_fwd(qb, kd, vd, sel, scale)
+        cu._tick()
+        ctx.save_for_backward(qb, kd, vd, sel, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        qb, kd, vd, sel, o, lse = ctx.saved_tensors
+        dk = torch.zeros(kd.shape, dtype=torch.float32, device=kd.device)
+        dv = torch.zeros(vd.shape, dtype=torch.float32, device=vd.device)
+        dq = cu._C.dsa_bwd(d_o.contiguous(), qb, kd, vd, sel, o, lse, dk, dv, ctx.scale)
+        cu._tick()
+        return dq.to(qb.dtype), dk.to(kd.dtype), dv.to(vd.dtype), None, None
+
+
+def _native(q, k) -> bool:
+    return (hasattr(cu._C, "dsa_fwd") and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+            and cu._C.dsa_supported(q.shape[-1], q.shape[1] // k.shape[1]) and os.environ.get("VLMT_DSA_NATIVE", "0") != "0")
 
 
 def _block_attention(qb, kd, vd, sel, valid, scale, rep):
@@ -42,6 +74,7 @@ def dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=Non
     rep = Hq // Hkv
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     bounds = cu_seqlens.tolist()
+    native = _native(q, k)
     if max(b - a for a, b in zip(bounds[:-1], bounds[1:])) <= topk:
         return cu.attention_varlen(q, k, v, cu_seqlens, 0, True, scale)
     outs = []
@@ -71,8 +104,12 @@ def dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=Non
                 del sc
             # the gathered keys / values of a block are 2 x B x kk x Hkv x D floats (gigabytes at topk 2048): they are
             # rebuilt in backward instead of being kept, so a long document costs one block of them at a time
-            doc_out.append(_ckpt.checkpoint(_block_attention, q[s + b0:s + b1], kd, vd, sel, valid, scale, rep,
-                                            use_reentrant=False))
+            if native:
+                sel32 = torch.where(valid, sel, -1).to(torch.int32)
+                doc_out.append(_SelectedAttention.apply(q[s + b0:s + b1], kd, vd, sel32, scale))
+            else:
+                doc_out.append(_ckpt.checkpoint(_block_attention, q[s + b0:s + b1], kd, vd, sel, valid, scale, rep,
+                                                use_reentrant=False))
         outs.append(torch.cat(doc_out, 0).to(q.dtype))
     if bounds[-1] < T:
         outs.append(q.new_zeros(T - bounds[-1], Hq, D))
