@@ -47,7 +47,7 @@ class _SelectedAttention(torch.autograd.Function):
 
 def _native(q, k) -> bool:
     return (hasattr(cu._C, "dsa_fwd") and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
-            and cu._C.dsa_supported(q.shape[-1], q.shape[1] // k.shape[1]) and os.environ.get("VLMT_DSA_NATIVE", "0") != "0")
+            and cu._C.dsa_supported(q.shape[-1], q.shape[1] // k.shape[1]) and os.environ.get("VLMT_DSA_NATIVE", "1") != "0")
 
 
 def _block_attention(qb, kd, vd, sel, valid, scale, rep):
