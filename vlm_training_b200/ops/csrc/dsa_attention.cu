@@ -44,15 +44,21 @@ template <int D, int REP>
 __device__ __forceinline__ void row_dots(const __nv_bfloat16* __restrict__ row, const float* __restrict__ a_s, float (&acc)[REP]) {
 #pragma unroll
   for (int h = 0; h < REP; ++h) acc[h] = 0.f;
-#pragma unroll 4
-  for (int c = 0; c < D / 8; ++c) {
-    float kf[8];
-    unpack8(*reinterpret_cast<const uint4*>(row + c * 8), kf);
+  // 8 chunks (128 bytes of the row) are loaded before they are used, so a thread keeps 8 gathered loads in flight
+  for (int c0 = 0; c0 < D / 8; c0 += 8) {
+    uint4 raw[8];
 #pragma unroll
-    for (int h = 0; h < REP; ++h) {
-      const float4 a0 = *reinterpret_cast<const float4*>(a_s + h * D + c * 8);
-      const float4 a1 = *reinterpret_cast<const float4*>(a_s + h * D + c * 8 + 4);
-      acc[h] += kf[0] * a0.x + kf[1] * a0.y + kf[2] * a0.z + kf[3] * a0.w + kf[4] * a1.x + kf[5] * a1.y + kf[6] * a1.z + kf[7] * a1.w;
+    for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(row + (c0 + u) * 8);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      float kf[8];
+      unpack8(raw[u], kf);
+#pragma unroll
+      for (int h = 0; h < REP; ++h) {
+        const float4 a0 = *reinterpret_cast<const float4*>(a_s + h * D + (c0 + u) * 8);
+        const float4 a1 = *reinterpret_cast<const float4*>(a_s + h * D + (c0 + u) * 8 + 4);
+        acc[h] += kf[0] * a0.x + kf[1] * a0.y + kf[2] * a0.z + kf[3] * a0.w + kf[4] * a1.x + kf[5] * a1.y + kf[6] * a1.z + kf[7] * a1.w;
+      }
     }
   }
 }
@@ -124,12 +130,23 @@ __global__ void __launch_bounds__(THREADS) dsa_fwd_kernel(Params p) {
     float acc[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) acc[h] = 0.f;
-    for (int j = 0; j < p.kk; ++j) {
-      const int idx = sel_s[j];
-      if (idx < 0) continue;
-      const float vv = __bfloat162float(p.v[((size_t)idx * p.Hkv + g) * D + tid]);
+    // 8 value rows in flight per thread; an unused slot reads row 0 with probability 0
+    constexpr int U = 8;
+    for (int j0 = 0; j0 < p.kk; j0 += U) {
+      float vv[U];
 #pragma unroll
-      for (int h = 0; h < REP; ++h) acc[h] = fmaf(s_s[j * REP + h], vv, acc[h]);
+      for (int u = 0; u < U; ++u) {
+        const int j = j0 + u;
+        const int idx = j < p.kk ? max(sel_s[j], 0) : 0;
+        vv[u] = __bfloat162float(p.v[((size_t)idx * p.Hkv + g) * D + tid]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (j0 + u < p.kk) {
+#pragma unroll
+          for (int h = 0; h < REP; ++h) acc[h] = fmaf(s_s[(j0 + u) * REP + h], vv[u], acc[h]);
+        }
+      }
     }
 #pragma unroll
     for (int h = 0; h < REP; ++h) p.o[((size_t)b * Hq + g * REP + h) * D + tid] = __float2bfloat16(acc[h] * ml_s[REP + h]);
@@ -190,21 +207,32 @@ __global__ void __launch_bounds__(THREADS) dsa_bwd_kernel(Params p) {
     float dq[REP], qv[REP], dov[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) { dq[h] = 0.f; qv[h] = q_s[h * D + tid]; dov[h] = do_s[h * D + tid]; }
-    for (int j = 0; j < p.kk; ++j) {
-      const int idx = sel_s[j];
-      if (idx < 0) continue;
-      const size_t off = ((size_t)idx * p.Hkv + g) * D + tid;
-      const float kv = __bfloat162float(p.k[off]);
-      float dk = 0.f, dv = 0.f;
+    constexpr int U = 8;
+    for (int j0 = 0; j0 < p.kk; j0 += U) {
+      float kv[U];
+      int idxs[U];
 #pragma unroll
-      for (int h = 0; h < REP; ++h) {
-        const float ds = ds_s[j * REP + h];
-        dq[h] = fmaf(ds, kv, dq[h]);
-        dk = fmaf(ds, qv[h], dk);
-        dv = fmaf(p_s[j * REP + h], dov[h], dv);
+      for (int u = 0; u < U; ++u) {
+        const int j = j0 + u;
+        idxs[u] = j < p.kk ? sel_s[j] : -1;
+        kv[u] = __bfloat162float(p.k[((size_t)max(idxs[u], 0) * p.Hkv + g) * D + tid]);
       }
-      atomicAdd(p.dk + off, dk);
-      atomicAdd(p.dv + off, dv);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (idxs[u] < 0) continue;
+        const int j = j0 + u;
+        float dk = 0.f, dv = 0.f;
+#pragma unroll
+        for (int h = 0; h < REP; ++h) {
+          const float ds = ds_s[j * REP + h];
+          dq[h] = fmaf(ds, kv[u], dq[h]);
+          dk = fmaf(ds, qv[h], dk);
+          dv = fmaf(p_s[j * REP + h], dov[h], dv);
+        }
+        const size_t off = ((size_t)idxs[u] * p.Hkv + g) * D + tid;
+        atomicAdd(p.dk + off, dk);
+        atomicAdd(p.dv + off, dv);
+      }
     }
 #pragma unroll
     for (int h = 0; h < REP; ++h) p.dq[row0 + (size_t)h * D + tid] = dq[h];
