@@ -3,7 +3,7 @@
     python -m vlm_training_b200.ops.microbench gemm --m 8192 --n 6144 --k 4096 [--layout fwd|dgrad|wgrad]
     python -m vlm_training_b200.ops.microbench attention --tokens 8192 --docs 1 [--backward]
     python -m vlm_training_b200.ops.microbench rmsnorm | swiglu | qkv_rope | ce | adamw | moe
-    python -m vlm_training_b200.ops.microbench gdn_scan --tokens 16384 --docs 1 [--backward]   |   conv1d [--backward]
+    python -m vlm_training_b200.ops.microbench gdn_scan --tokens 16384 --docs 1 [--backward]   |   conv1d [--backward]   |   dsa [--backward]
     python -m vlm_training_b200.ops.microbench all            # the table used in the roofline report
 
 Each line is JSON: algorithmic FLOPs / bytes, median milliseconds, achieved rate, and the fraction of the
@@ -213,9 +213,28 @@ def bench_conv1d(t: Timer, tokens=16384, channels=8192, backward=False):
     return _report("conv1d_silu_fwd", [tokens, channels], ms, nbytes=2.0 * tokens * channels * 2)
 
 
+def bench_dsa(t: Timer, queries=1024, keys=16384, topk=2048, hkv=2, rep=8, d=256, backward=False):
+    """Selected-key attention of one query block: every query reads its own ``topk`` rows of a ``keys``-row document."""
+    from . import dsa_cuda
+
+    q = _r(queries, hkv * rep, d, scale=0.5).requires_grad_()
+    k = _r(keys, hkv, d, scale=0.5).requires_grad_()
+    v = _r(keys, hkv, d).requires_grad_()
+    sel = torch.rand(queries, keys, device="cuda").topk(topk, dim=-1).indices.to(torch.int32)
+    g = _r(queries, hkv * rep, d)
+    gathered = 2.0 * queries * hkv * topk * d * 2     # key and value rows read by the forward pass
+    if backward:
+        o = dsa_cuda._SelectedAttention.apply(q, k, v, sel, d ** -0.5)
+        ms = t(lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True))
+        return _report("dsa_selected_attention_bwd", [queries, keys, topk, hkv, rep, d], ms, nbytes=2.0 * gathered)
+    with torch.no_grad():
+        ms = t(lambda: dsa_cuda._SelectedAttention.apply(q, k, v, sel, d ** -0.5))
+    return _report("dsa_selected_attention_fwd", [queries, keys, topk, hkv, rep, d], ms, nbytes=gathered)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "conv1d", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "conv1d", "dsa", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -251,6 +270,8 @@ def main(argv=None):
         bench_gdn_scan(t, a.tokens, a.docs, reverse=a.backward)
     elif a.what == "conv1d":
         bench_conv1d(t, a.tokens, backward=a.backward)
+    elif a.what == "dsa":
+        bench_dsa(t, backward=a.backward)
     else:
         for layout in ("fwd", "dgrad", "wgrad"):
             bench_gemm(t, 8192, 6144, 4096, layout)
@@ -274,6 +295,8 @@ def main(argv=None):
             bench_gdn_scan(t, 16384, docs, reverse=True)
         bench_conv1d(t)
         bench_conv1d(t, backward=True)
+        bench_dsa(t)
+        bench_dsa(t, backward=True)
     from . import cuda as cu
 
     cu.check_status()
