@@ -3,7 +3,7 @@
 // One CTA per (query, kv head): the `REP` query heads that share the kv head are processed together, so every selected
 // key / value row is read once per CTA.  Each query has its own key set, so there is no tile shared between queries to
 // put on the tensor cores (M would be REP = 8); the kernel is a CUDA-core kernel bound by the gathered reads:
-//   phase 1  thread <-> key:  s[j][h] = scale * q[h] . K[sel[j]]           (16-byte key loads, q broadcast from smem)
+//   phase 1  thread <-> key:  s[j][h] = scale * q[h] . K[sel[j]]           (two keys per thread, q broadcast from smem)
 //   phase 2  warp   <-> head: m[h], l[h], p = exp(s - m)                    (scores stay in shared memory)
 //   phase 3  thread <-> dim:  o[h][d] = sum_j p[j][h] V[sel[j]][d] / l[h]   (coalesced value loads)
 // The backward kernel recomputes p from the saved log-sum-exp, forms dS in phase 1 (thread <-> key, second pass over
@@ -39,25 +39,32 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// dot products of one key (or value) row with the REP rows of `a_s` ([REP][D] floats in shared memory)
+// dot products of two key (or value) rows with the REP rows of `a_s` ([REP][D] floats in shared memory): every
+// shared-memory read of `a_s` feeds both rows (the kernels are bound by the shared-memory pipe, so pairing the rows
+// halves its load per key); 4 x 16 bytes of each row are loaded before they are used
 template <int D, int REP>
-__device__ __forceinline__ void row_dots(const __nv_bfloat16* __restrict__ row, const float* __restrict__ a_s, float (&acc)[REP]) {
+__device__ __forceinline__ void row_dots2(const __nv_bfloat16* __restrict__ r0, const __nv_bfloat16* __restrict__ r1,
+                                          const float* __restrict__ a_s, float (&acc0)[REP], float (&acc1)[REP]) {
 #pragma unroll
-  for (int h = 0; h < REP; ++h) acc[h] = 0.f;
-  // 8 chunks (128 bytes of the row) are loaded before they are used, so a thread keeps 8 gathered loads in flight
-  for (int c0 = 0; c0 < D / 8; c0 += 8) {
-    uint4 raw[8];
+  for (int h = 0; h < REP; ++h) { acc0[h] = 0.f; acc1[h] = 0.f; }
+  for (int c0 = 0; c0 < D / 8; c0 += 4) {
+    uint4 raw0[4], raw1[4];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(row + (c0 + u) * 8);
+    for (int u = 0; u < 4; ++u) {
+      raw0[u] = *reinterpret_cast<const uint4*>(r0 + (c0 + u) * 8);
+      raw1[u] = *reinterpret_cast<const uint4*>(r1 + (c0 + u) * 8);
+    }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      float kf[8];
-      unpack8(raw[u], kf);
+    for (int u = 0; u < 4; ++u) {
+      float k0[8], k1[8];
+      unpack8(raw0[u], k0);
+      unpack8(raw1[u], k1);
 #pragma unroll
       for (int h = 0; h < REP; ++h) {
         const float4 a0 = *reinterpret_cast<const float4*>(a_s + h * D + (c0 + u) * 8);
         const float4 a1 = *reinterpret_cast<const float4*>(a_s + h * D + (c0 + u) * 8 + 4);
-        acc[h] += kf[0] * a0.x + kf[1] * a0.y + kf[2] * a0.z + kf[3] * a0.w + kf[4] * a1.x + kf[5] * a1.y + kf[6] * a1.z + kf[7] * a1.w;
+        acc0[h] += k0[0] * a0.x + k0[1] * a0.y + k0[2] * a0.z + k0[3] * a0.w + k0[4] * a1.x + k0[5] * a1.y + k0[6] * a1.z + k0[7] * a1.w;
+        acc1[h] += k1[0] * a0.x + k1[1] * a0.y + k1[2] * a0.z + k1[3] * a0.w + k1[4] * a1.x + k1[5] * a1.y + k1[6] * a1.z + k1[7] * a1.w;
       }
     }
   }
@@ -91,17 +98,17 @@ __global__ void __launch_bounds__(THREADS) dsa_fwd_kernel(Params p) {
   for (int i = tid; i < REP * D; i += THREADS) q_s[i] = __bfloat162float(qrow[i]);
   for (int j = tid; j < p.kk; j += THREADS) sel_s[j] = p.sel[(size_t)b * p.kk + j];
   __syncthreads();
-  // ---- phase 1
-  for (int j = tid; j < p.kk; j += THREADS) {
-    const int idx = sel_s[j];
-    float acc[REP];
-    if (idx >= 0) {
-      row_dots<D, REP>(p.k + ((size_t)idx * p.Hkv + g) * D, q_s, acc);
+  // ---- phase 1: two keys per thread and pass (an unused or missing slot reads row 0 and is overwritten with -inf)
+  for (int j = tid; j < p.kk; j += 2 * THREADS) {
+    const int j1 = j + THREADS;
+    const int i0 = sel_s[j], i1 = j1 < p.kk ? sel_s[j1] : -1;
+    float a0[REP], a1[REP];
+    row_dots2<D, REP>(p.k + ((size_t)max(i0, 0) * p.Hkv + g) * D, p.k + ((size_t)max(i1, 0) * p.Hkv + g) * D, q_s, a0, a1);
 #pragma unroll
-      for (int h = 0; h < REP; ++h) s_s[j * REP + h] = acc[h] * p.scale;
-    } else {
+    for (int h = 0; h < REP; ++h) s_s[j * REP + h] = i0 >= 0 ? a0[h] * p.scale : -INFINITY;
+    if (j1 < p.kk) {
 #pragma unroll
-      for (int h = 0; h < REP; ++h) s_s[j * REP + h] = -INFINITY;
+      for (int h = 0; h < REP; ++h) s_s[j1 * REP + h] = i1 >= 0 ? a1[h] * p.scale : -INFINITY;
     }
   }
   __syncthreads();
@@ -182,23 +189,29 @@ __global__ void __launch_bounds__(THREADS) dsa_bwd_kernel(Params p) {
     }
   }
   __syncthreads();
-  // ---- phase 1: thread <-> key: p, dS
-  for (int j = tid; j < p.kk; j += THREADS) {
-    const int idx = sel_s[j];
-    if (idx >= 0) {
-      float sc[REP], dp[REP];
-      row_dots<D, REP>(p.k + ((size_t)idx * p.Hkv + g) * D, q_s, sc);
-      row_dots<D, REP>(p.v + ((size_t)idx * p.Hkv + g) * D, do_s, dp);
+  // ---- phase 1: thread <-> key (two keys per pass): p, dS
+  for (int j = tid; j < p.kk; j += 2 * THREADS) {
+    const int j1 = j + THREADS;
+    const int i0 = sel_s[j], i1 = j1 < p.kk ? sel_s[j1] : -1;
+    const size_t o0 = ((size_t)max(i0, 0) * p.Hkv + g) * D, o1 = ((size_t)max(i1, 0) * p.Hkv + g) * D;
+    float sc0[REP], sc1[REP], dp0[REP], dp1[REP];
+    row_dots2<D, REP>(p.k + o0, p.k + o1, q_s, sc0, sc1);
+    row_dots2<D, REP>(p.v + o0, p.v + o1, do_s, dp0, dp1);
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      const float lse = st_s[h];
+      const float pr = (i0 < 0 || lse == -INFINITY) ? 0.f : __expf(sc0[h] * p.scale - lse);
+      p_s[j * REP + h] = pr;
+      ds_s[j * REP + h] = pr * (dp0[h] - st_s[REP + h]) * p.scale;
+    }
+    if (j1 < p.kk) {
 #pragma unroll
       for (int h = 0; h < REP; ++h) {
         const float lse = st_s[h];
-        const float pr = lse == -INFINITY ? 0.f : __expf(sc[h] * p.scale - lse);
-        p_s[j * REP + h] = pr;
-        ds_s[j * REP + h] = pr * (dp[h] - st_s[REP + h]) * p.scale;
+        const float pr = (i1 < 0 || lse == -INFINITY) ? 0.f : __expf(sc1[h] * p.scale - lse);
+        p_s[j1 * REP + h] = pr;
+        ds_s[j1 * REP + h] = pr * (dp1[h] - st_s[REP + h]) * p.scale;
       }
-    } else {
-#pragma unroll
-      for (int h = 0; h < REP; ++h) { p_s[j * REP + h] = 0.f; ds_s[j * REP + h] = 0.f; }
     }
   }
   __syncthreads();
