@@ -318,17 +318,35 @@ class DecoderLayer(nn.Module):
             self.self_attn = SelfAttention(cfg)
         self.mlp = SparseMoeBlock(cfg) if cfg.num_experts > 0 else SwiGLUMLP(cfg.hidden_size, cfg.intermediate_size)
 
-    def forward(self, x, ctx: RowContext):
+    def mixer_half(self, x, ctx: RowContext):
+        """Token mixer on the normalised input (attention or Gated DeltaNet); the residual add happens in the MLP half."""
         if self.layer_type == "linear_attention":
-            h = self.linear_attn(self.input_layernorm(x), ctx)
-        else:
-            h = self.self_attn(x, ctx, prenorm=self.input_layernorm)
+            return self.linear_attn(self.input_layernorm(x), ctx)
+        return self.self_attn(x, ctx, prenorm=self.input_layernorm)
+
+    def mlp_half(self, h, x):
+        """``r = x + h; r + mlp(norm(r))``."""
         if isinstance(self.mlp, SwiGLUMLP):
             out, x = self.mlp.forward_prenorm(h, x, self.post_attention_layernorm)
             return x + out
         h, x = ops.add_rms_norm(h, x, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps,
                                 self.post_attention_layernorm.offset)
         return x + self.mlp(h)
+
+    def forward(self, x, ctx: RowContext):
+        return self.mlp_half(self.mixer_half(x, ctx), x)
+
+    def forward_sac(self, x, ctx: RowContext):
+        """Selective activation checkpointing: the mixer half runs under plain autograd, so what its ops saved (the
+        projections' inputs, attention output and log-sum-exp, the scan states) stays and the expensive attention /
+        recurrence is not run twice; the MLP half, whose ``[T, 2 I]`` activations are the largest tensors of the
+        layer, is recomputed in backward (the reference's ``sac`` keeps matmul outputs and recomputes the elementwise
+        work, reference: train/infra.py:161-170,222-223; here the custom ops already decide what they keep, so the
+        split is by sub-block)."""
+        from torch.utils.checkpoint import checkpoint
+
+        h = self.mixer_half(x, ctx)
+        return checkpoint(self.mlp_half, h, x, use_reentrant=False)
 
 
 class Decoder(nn.Module):

@@ -129,6 +129,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return out
 
 
-if __name__ == "__main__":
+def main():
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,10 +1,11 @@
 """Activation checkpointing for decoder / ViT blocks.
 
 ``full`` recomputes the whole block in backward; ``sac`` keeps the block's
-attention half (whose recompute is the expensive part) and recomputes only the
-MLP half, whose activations are the largest (reference policy names:
-train/infra.py:155-234 — there "sac" saves matmul outputs; here the custom ops
-decide what they save, so the split is by sub-block).
+mixer half (attention / Gated DeltaNet, whose recompute is the expensive part)
+and recomputes only the MLP half, whose activations are the largest
+(``DecoderLayer.forward_sac``; reference policy names: train/infra.py:155-234 —
+there "sac" saves matmul outputs; here the custom ops decide what they save, so
+the split is by sub-block).
 """
 from __future__ import annotations
 
@@ -15,10 +16,10 @@ from torch.utils.checkpoint import checkpoint
 def checkpoint_layer(layer, x, ctx, mode: str):
     if mode == "full":
         return checkpoint(layer, x, ctx, use_reentrant=False)
-    if mode == "sac" and hasattr(layer, "forward_sac"):
-        return layer.forward_sac(x, ctx)
     if mode == "sac":
-        return checkpoint(layer, x, ctx, use_reentrant=False)
+        if not hasattr(layer, "forward_sac"):
+            raise ValueError(f"ac_mode 'sac' needs a block with a forward_sac method; {type(layer).__name__} has none")
+        return layer.forward_sac(x, ctx)
     return layer(x, ctx)
 
 
