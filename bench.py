@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -224,19 +225,27 @@ def run_ours(args):
         tr._window = {"tokens": 0, "label_tokens": 0, "samples": 0, "micro": 0, "data_time": 0.0, "h2d_bytes": 0}
         for _ in range(2):
             tr.train_step(data_it)
+        tr.flush_metrics()
         barrier()
-        h2d = 0
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
+        got = []
         for _ in range(args.steps):
-            m = tr.train_step(data_it)  # H2D from pinned memory + one loss read-back per step
-            h2d += int(m["perf/h2d_bytes"])
+            # every step: H2D of its batch from pinned memory, and a D2H copy of its loss / reductions / status word;
+            # the host reads step k's numbers when step k + 1 has been enqueued, so the device never waits for it
+            m = tr.train_step(data_it)
+            if m is not None:
+                got.append(m)
+        got.append(tr.flush_metrics())  # the last step's numbers: all K read-backs end inside the timed region
         e1.record()
         barrier()
+        assert len(got) == args.steps and all(math.isfinite(m["train/loss"]) for m in got), "a step's loss did not reach the host"
         ms_e2e = max_over_ranks(e0.elapsed_time(e1))
         e2e = {"value": global_tokens * args.steps / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-               "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": 4}
+               "h2d_bytes_per_step": sum(int(m["perf/h2d_bytes"]) for m in got) // args.steps,
+               "d2h_bytes_per_step": sum(int(m["perf/d2h_bytes"]) for m in got) // args.steps,
+               "losses": [round(float(m["train/loss"]), 4) for m in got[-4:]]}
     tr.end_run()
     flops_tok = tr.flops_per_token * tr.mesh.tp  # whole-model FLOPs per token
     if rank == 0:

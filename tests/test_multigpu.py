@@ -83,3 +83,61 @@ def test_in_place_weight_gradients_match_autograd_accumulation(tmp_path):
     assert inplace == pytest.approx(base, rel=2e-3, abs=2e-3)
     frac_off = ((probe_in - probe_base).abs() > 5e-4).float().mean().item()
     assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ"
+
+
+PRIMITIVES = r"""
+import os, sys
+sys.path.insert(0, {root!r})
+import torch
+import torch.distributed as dist
+from vlm_training_b200.parallel.mesh import init_distributed
+from vlm_training_b200.parallel.p2p import P2PComm
+from vlm_training_b200.ops import cuda as cu
+
+rank, world, dev = init_distributed("nccl", "cuda")
+comm = P2PComm(dist.group.WORLD, dev, slot_elems=1 << 22)
+torch.manual_seed(1234)                      # same stream of numbers on every rank
+site = object()
+worst = 0.0
+for it, (R, K, N) in enumerate([(256, 512, 384), (1024, 1024, 2048), (256, 512, 384), (128, 256, 136), (1024, 1024, 2048)]):
+    x_all = (torch.randn(world * R, K, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()          # forward layout [out, in]
+    w_t = (torch.randn(K, N, device=dev) * 0.05).bfloat16()        # dgrad layout: stored [in, out] = [K, N]
+    x_loc = x_all[rank * R:(rank + 1) * R].contiguous()
+    comm.begin_microbatch()
+    for b_mn, wt in ((False, w), (True, w_t)):
+        for use_site in (True, False):
+            y, x_full = comm.gemm_all_gather(x_loc, wt, b_mn=b_mn, site=site if use_site else None)
+            ref = x_all.float() @ (wt.float() if b_mn else wt.float().t())
+            torch.cuda.synchronize()
+            assert torch.equal(x_full, x_all), f"gathered rows differ (it {{it}}, b_mn {{b_mn}}, site {{use_site}})"
+            err = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+            worst = max(worst, err)
+            assert err < 2e-2, f"gemm_all_gather: relative error {{err}} (it {{it}}, b_mn {{b_mn}})"
+    # GEMM -> reduce-scatter with the same operands: every rank holds a partial product of the full rows
+    part = (torch.randn(world * R, K, device=dev) * 0.5 + rank).bfloat16()
+    out = comm.gemm_reduce_scatter(part, w)
+    gathered = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(gathered, part)
+    ref = sum(g.float() @ w.float().t() for g in gathered)[rank * R:(rank + 1) * R]
+    torch.cuda.synchronize()
+    err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
+    assert err < 2e-2, f"gemm_reduce_scatter: relative error {{err}}"
+cu.check_status()
+print(f"rank {{rank}} PRIMITIVES OK worst {{worst:.2e}}", flush=True)
+dist.destroy_process_group()
+"""
+
+
+def test_fused_gemm_collectives_match_torch(tmp_path):
+    """The all-gather -> GEMM kernel (own rows from the local source, peers' rows gated by their flags, forward and
+    input-gradient layouts, persistent site buffer and ring slot, repeated so slots and buffers are reused) and the
+    GEMM -> reduce-scatter kernel against fp32 matmuls of the gathered operands."""
+    script = tmp_path / "prims.py"
+    script.write_text(PRIMITIVES.format(root=ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29711", str(script)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", VLMT_NO_MULTIMEM="1", VLMT_PG_TIMEOUT_S="120", VLMT_FLAG_WAIT_MS="5000")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count("PRIMITIVES OK") == 2, res.stdout[-2000:]

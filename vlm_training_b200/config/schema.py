@@ -108,6 +108,12 @@ class TrainingSection:
     backend: str = "auto"  # "auto" | "nccl" | "gloo"
     device: str = "auto"  # "auto" | "cuda" | "cpu"
     log_every: int = 1
+    # on a GPU, read a step's loss / reductions / device status one step later from pinned memory instead of
+    # stalling the host on them (metrics of step k are returned by the call that runs step k + 1)
+    async_metrics: bool = True
+    # "DEBUG" runs: first and last optimizer step of the cProfile window (reference: train/train_qwen.py:667-694)
+    cprofile_start: int = 50
+    cprofile_stop: int = 65
 
 
 @dataclass

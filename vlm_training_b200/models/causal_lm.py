@@ -140,6 +140,9 @@ class _CausalLMBase(nn.Module):
             batch_plan = BatchPlan.build(cfg, ids, attention_mask, image_grid_thw if pixel_values is not None else None, dev)
         tp = getattr(self, "tp", None)
         sp = tp is not None and tp.enabled and tp.sequence_parallel
+        if tp is not None and tp.p2p is not None and torch.is_grad_enabled():
+            # peers store this pass's gathered activations into buffers that the previous backward pass still read
+            tp.p2p.begin_microbatch()
         lo, hi = 0, T
         if sp:
             if T % tp.size:

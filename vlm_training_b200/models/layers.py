@@ -62,7 +62,7 @@ class Linear(nn.Module):
 
     def forward(self, x):
         if self.parallel == "column":
-            return column_linear(x, self.weight, self.bias, self.tp)
+            return column_linear(x, self.weight, self.bias, self.tp, site=self)
         if self.parallel == "row":
             y = row_linear(x, self.weight, self.tp)
             return y if self.bias is None else y + self.bias

@@ -74,6 +74,37 @@ void gemm_rs_push(const Tensor& a, const Tensor& b, const std::vector<int64_t>& 
   TORCH_CHECK(r == 0, "vlmt_gemm_bf16_rs_push failed with code ", r);
 }
 
+// all-gather fused into the GEMM: out[world * R, N] = gather(x_local) @ op(b); x_full is this rank's [world * R, K] gathered
+// buffer (symmetric memory; full_ptrs[r] is its address on rank r), flag_ptrs[r] rank r's flag array, flags_elem_offset the
+// row of the flag arrays that this collective uses
+void gemm_ag(const Tensor& x_local, Tensor& x_full, const Tensor& b, Tensor& out, const std::vector<int64_t>& full_ptrs,
+             const std::vector<int64_t>& flag_ptrs, int64_t flags_elem_offset, Tensor& counter, int64_t epoch, int64_t rank, bool b_mn) {
+  check_bf16(x_local, "x_local"); check_bf16(x_full, "x_full"); check_bf16(b, "b"); check_bf16(out, "out");
+  check_contig(x_local, "x_local"); check_contig(x_full, "x_full");
+  TORCH_CHECK(x_local.dim() == 2 && x_full.dim() == 2 && b.dim() == 2 && out.dim() == 2 && b.stride(1) == 1 && out.stride(1) == 1);
+  const int world = (int)full_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && flag_ptrs.size() == full_ptrs.size() && rank >= 0 && rank < world);
+  const int R = x_local.size(0), K = x_local.size(1);
+  const int N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK(x_full.size(0) == (int64_t)R * world && x_full.size(1) == K && (b_mn ? b.size(0) : b.size(1)) == K, "gemm_ag: bad shapes");
+  TORCH_CHECK(out.size(0) == x_full.size(0) && out.size(1) == N, "gemm_ag: bad output shape");
+  TORCH_CHECK(full_ptrs[rank] == reinterpret_cast<int64_t>(x_full.data_ptr()), "gemm_ag: full_ptrs[rank] must be x_full");
+  TORCH_CHECK(counter.scalar_type() == at::kInt && counter.is_cuda() && counter.numel() >= 1);
+  c10::cuda::CUDAGuard guard(x_local.device());
+  void* full[8];
+  void* flg[8];
+  for (int i = 0; i < world; ++i) {
+    full[i] = reinterpret_cast<void*>(full_ptrs[i]);
+    flg[i] = reinterpret_cast<void*>(flag_ptrs[i] + flags_elem_offset * 4);
+  }
+  Tensor st = status_tensor();
+  int r = vlmt_gemm_bf16_ag(x_local.data_ptr(), x_full.data_ptr(), b.data_ptr(), out.data_ptr(), full, flg,
+                            reinterpret_cast<const int*>(flag_ptrs[rank] + flags_elem_offset * 4),
+                            reinterpret_cast<unsigned*>(counter.data_ptr<int>()), (int)epoch, world, (int)rank, R, N, K, (int)b.stride(0),
+                            (int)out.stride(0), b_mn ? 1 : 0, st.data_ptr<int>(), num_sms(), cur_stream());
+  TORCH_CHECK(r == 0, "vlmt_gemm_bf16_ag failed with code ", r);
+}
+
 // grouped GEMM over padded row groups (see gemm_sm100.h); prefix: int32 device tensor [groups + 1]
 void gemm_grouped(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& prefix, int64_t mode, bool b_mn) {
   check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(out, "out");
@@ -422,6 +453,11 @@ void bind_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_rs_push", &gemm_rs_push);
+  m.def("gemm_ag", &gemm_ag);
+  m.def("gemm_set_flag_wait_ms", [](int64_t ms) {
+    int r = vlmt_gemm_set_flag_wait_ms((long)ms);
+    TORCH_CHECK(r == 0, "vlmt_gemm_set_flag_wait_ms failed with code ", r);
+  });
   m.def("gemm_grouped", &gemm_grouped);
   m.def("gdn_scan", &gdn_scan);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

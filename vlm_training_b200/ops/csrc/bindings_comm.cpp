@@ -7,6 +7,8 @@
 
 using torch::Tensor;
 
+Tensor vlmt_status_tensor();
+
 // state tensors are the local shard (fp32); `state_off` is the element offset of `lo` inside them
 static void fused_rs_adamw_ag(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, int64_t grad_mc,
                               int64_t param_mc, int64_t world, int64_t lo, int64_t hi, Tensor& master, Tensor& m, Tensor& v,
@@ -23,7 +25,7 @@ static void fused_rs_adamw_ag(const std::vector<int64_t>& grad_ptrs, const std::
   int r = vlmt_fused_rs_adamw_ag(g, p, reinterpret_cast<void*>(grad_mc), reinterpret_cast<void*>(param_mc), (int)world, lo, hi,
                                  master.data_ptr<float>() + state_off, m.data_ptr<float>() + state_off, v.data_ptr<float>() + state_off,
                                  (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, (float)bc1, (float)bc2, (float)grad_scale,
-                                 at::cuda::getCurrentCUDAStream().stream());
+                                 vlmt_status_tensor().data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(r == 0, "vlmt_fused_rs_adamw_ag failed with code ", r);
 }
 
@@ -37,8 +39,6 @@ static void peer_sum_rows(const std::vector<int64_t>& partial_ptrs, int64_t row0
                              out.data_ptr(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(r == 0, "vlmt_peer_sum_rows failed with code ", r);
 }
-
-Tensor vlmt_status_tensor();
 
 static void fill_ptrs(const std::vector<int64_t>& v, void** out) {
   TORCH_CHECK(v.size() <= 16);

@@ -8,8 +8,10 @@
 //   3. stores the new bf16 parameters into the flat parameter buffer of EVERY rank
 //      (peer stores, or one multimem.st).
 // Gradient bytes cross NVLink once, parameter bytes once; nothing is staged.  The kernel contains
-// no waits: the caller orders it after all ranks have finished writing their gradients and
-// before any rank reads parameters (two tiny NCCL collectives on the communication stream).
+// no waits: the caller orders it behind a one-block wait kernel on the same stream that returns once every
+// peer's "gradients of this bucket are final" flag has arrived (signal_peers / wait_flags below).  If that
+// wait, or any earlier bounded wait, ran out, the device status word is non-zero and the kernel returns
+// without touching the optimizer state, so a lost peer can never corrupt master weights or moments.
 //
 // peer_sum_rows: out[r, :] = sum over ranks of partial_rank[r, :] for the rows a rank owns
 // (tensor-parallel reduce-scatter), optionally fused with a residual add.
@@ -64,7 +66,9 @@ struct AdamArgs {
 // elements [lo, hi) of the bucket-relative flat buffers; lo, hi multiples of 8
 template <bool MULTIMEM>
 __global__ void fused_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, void* grad_mc, void* param_mc, int world, long lo, long hi,
-                                         float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, AdamArgs a) {
+                                         float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, AdamArgs a,
+                                         const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;  // an earlier wait gave up
   const long nvec = (hi - lo) >> 3;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
     const long e = lo + (i << 3);
@@ -288,7 +292,7 @@ int vlmt_pull_reduce(void* const* slot_ptrs, void* out, const void* residual, lo
 }
 int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* grad_mc, void* param_mc, int world, long lo, long hi,
                            float* master, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                           float grad_scale, cudaStream_t st) {
+                           float grad_scale, const int* status, cudaStream_t st) {
   if (world > MAX_PEERS) return -1;
   if ((lo & 7) || (hi & 7)) return -2;
   if (hi <= lo) return 0;
@@ -298,9 +302,9 @@ int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void
   long blocks = (((hi - lo) >> 3) + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (grad_mc && param_mc)
-    fused_rs_adamw_ag_kernel<true><<<(int)blocks, 256, 0, st>>>(g, p, grad_mc, param_mc, world, lo, hi, master, m, v, a);
+    fused_rs_adamw_ag_kernel<true><<<(int)blocks, 256, 0, st>>>(g, p, grad_mc, param_mc, world, lo, hi, master, m, v, a, status);
   else
-    fused_rs_adamw_ag_kernel<false><<<(int)blocks, 256, 0, st>>>(g, p, nullptr, nullptr, world, lo, hi, master, m, v, a);
+    fused_rs_adamw_ag_kernel<false><<<(int)blocks, 256, 0, st>>>(g, p, nullptr, nullptr, world, lo, hi, master, m, v, a, status);
   return (int)cudaGetLastError();
 }
 int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st) {

@@ -8,9 +8,11 @@ extern "C" {
 // grad_ptrs / param_ptrs: `world` device pointers (one per rank, this rank's own included) to the start of the
 // bucket in each rank's flat buffer.  grad_mc / param_mc: multicast (NVLS) addresses of the same bucket or null.
 // [lo, hi): this rank's shard in elements relative to the bucket start, multiples of 8.
+// status: the device status word (or null); when it is non-zero at kernel start (a bounded wait ran out earlier, e.g. the
+// wait for this bucket's "gradients final" flags) the kernel returns without reading or writing anything.
 int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* grad_mc, void* param_mc, int world, long lo, long hi,
                            float* master, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                           float grad_scale, cudaStream_t st);
+                           float grad_scale, const int* status, cudaStream_t st);
 // out[rows, D] = residual + sum over ranks of partial_r[row0 : row0 + rows, :]
 int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st);
 // Signalled peer-to-peer collectives over symmetric staging slots (protocol: comm_kernels.cu).

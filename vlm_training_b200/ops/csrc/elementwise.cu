@@ -1549,25 +1549,32 @@ extern "C" int vlmt_rmsnorm_bwd_static(const void* dy, const void* x, const void
                     "holds %d x %d floats)\n", D, VLMT_NOALLOC_MAX_D, VLMT_NOALLOC_MAX_BLOCKS, VLMT_NOALLOC_MAX_D);
     return VLMT_NOALLOC_ERR_SIZE;
   }
-  if (rows <= 0) return 0;
   int err = 0;
   float* scratch = scratch_for_current_device(&err);
   if (scratch == nullptr) return err;
+  if (rows <= 0) {
+    // no rows, no partial sums: the column-sum kernel over zero blocks still overwrites dw (an output) with zeros
+    static_scratch_colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, dw, 0, D);
+    return (int)cudaGetLastError();
+  }
   const int nw = bwd_warps(D);
   if (nw == 0) return VLMT_NOALLOC_ERR_SIZE;
   int grid = (rows + nw - 1) / nw;
   if (grid > VLMT_NOALLOC_MAX_BLOCKS) grid = VLMT_NOALLOC_MAX_BLOCKS;
   const size_t smem = (size_t)nw * D * sizeof(float);
+  cudaError_t e;
   if (w_fp32) {
     auto k = rmsnorm_bwd_kernel<float>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
     k<<<grid, nw * 32, smem, st>>>(BF(dy), BF(x), (const float*)w, rstd, BF(dres), BFM(dx), scratch, rows, D, offset);
   } else {
     auto k = rmsnorm_bwd_kernel<bf16>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
     k<<<grid, nw * 32, smem, st>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx), scratch, rows, D, offset);
   }
-  cudaError_t e = cudaGetLastError();
+  e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   static_scratch_colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, dw, grid, D);
   return (int)cudaGetLastError();

@@ -15,6 +15,14 @@
 //
 // The tile loop is static round-robin over a grouped raster (16 M-tiles per group) so the
 // 148 concurrently resident tiles share A and B panels in L2.
+//
+// All-gather fused into the A operand (template flag AG; tensor-parallel column linear on sequence-sharded rows):
+// every rank holds `rows` of the M dimension.  Two extra warps per CTA copy this rank's rows into the gathered
+// buffer of EVERY rank (plain 16-byte stores into peer memory over NVLink) while the MMA pipeline already works on
+// the tiles of the own rows, which it reads from the local source; the last CTA to finish its share stores the
+// collective's number into every peer's flag array.  The TMA producer waits (bounded) for a peer's flag before it
+// loads the first tile of that peer's rows from the LOCAL gathered buffer, so remote rows cross NVLink once and the
+// transfer hides behind the own rows' tiles.
 #include "sm100.cuh"
 #include "gemm_sm100.h"
 
@@ -27,7 +35,12 @@ using namespace sm100;
 
 constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
+constexpr int AG_PUSH_THREADS = 64;   // warps 6 and 7 of the all-gather variant
 constexpr int GROUP_M = 16;
+constexpr int MAX_RANKS = 8;
+
+// wall-clock bound of a wait for a peer's flag inside the GEMM (set with vlmt_gemm_set_flag_wait_ms)
+__device__ unsigned long long g_gemm_flag_wait_ns = 20000000000ull;
 
 template <int BN>
 struct SmemLayout {
@@ -39,6 +52,8 @@ struct SmemLayout {
   static constexpr int kBarOffset = kOutOffset + kOutBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // + barriers + slack for 1024-B alignment
 };
+
+struct RsMaps { CUtensorMap m[MAX_RANKS]; };  // one tensor map per owner over its [rs_rows, N] destination block
 
 struct Params {
   int M, N, K;
@@ -52,8 +67,15 @@ struct Params {
   // GEMM -> reduce-scatter: output rows are owned by ranks in blocks of rs_rows; the tile for owner o is stored straight
   // into rs_dst[o] (a buffer in rank o's memory, reached over NVLink), so the transfer overlaps the remaining tiles
   int rs_world, rs_rows;
-  __nv_bfloat16* rs_dst[8];
-  const CUtensorMap* rs_maps;  // device memory: one tensor map per owner over its [rs_rows, N] destination block (TMA-store epilogue)
+  __nv_bfloat16* rs_dst[MAX_RANKS];
+  // all-gather -> GEMM (AG variant): M = ag_world * ag_rows; this rank's rows come from ag_src (tensor map tmap_a2), the
+  // others from the local gathered buffer (tmap_a) once flags[r] >= ag_epoch
+  int ag_world, ag_rank, ag_rows, ag_epoch;
+  const uint4* ag_src;          // this rank's rows, contiguous [ag_rows, K]
+  uint4* ag_dst[MAX_RANKS];     // the gathered buffer [M, K] of every rank (own included)
+  int* ag_flag_dst[MAX_RANKS];  // flag array of every rank
+  const int* ag_flags;          // this rank's flag array
+  unsigned* ag_counter;         // local: CTAs that have finished their share of the push (reset by the last one)
   // Grouped GEMM (one launch for all experts of a MoE layer).  Rows of every group are padded to whole 128-row tiles
   // and laid out back to back; grp_prefix[g] (device memory, G + 1 ints) is the first tile of group g.
   //   grp_mode 1 (forward / dgrad): groups partition the M dimension; group g multiplies its rows with its own B
@@ -92,10 +114,20 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / gsz;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_s32(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <int BN, bool A_MN, bool B_MN, bool AG>
+__global__ void __launch_bounds__(AG ? NUM_THREADS + AG_PUSH_THREADS : NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const __grid_constant__ CUtensorMap tmap_d, Params p) {
+            const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ CUtensorMap tmap_a2,
+            const __grid_constant__ RsMaps rs_maps, Params p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -122,7 +154,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (AG) tma_prefetch_desc(&tmap_a2);
   }
+  // AG: M tiles are visited starting with this rank's own block, so the peers' rows are needed as late as possible
+  const int ag_rot = AG ? p.ag_rank * (p.ag_rows / BM) : 0;
+  // the MMA thread and the epilogue depend on a producer that may be waiting for a peer: their own bound covers that wait
+  const unsigned long long wait_ns = AG ? kWaitLimitNs + g_gemm_flag_wait_ns : kWaitLimitNs;
   if (warp == 1) tmem_alloc<TMEM_COLS>(tmem_slot);
   tc_fence_before();
   __syncthreads();
@@ -134,6 +171,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      uint32_t ag_ready = 0;  // AG: peers whose flag has been seen
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn, kb_lo = 0, kb_hi = num_kb, b_row = 0;
         if (p.grp_mode == 2) {
@@ -145,7 +183,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tile_coords(tile, tiles_m, tiles_n, tm, tn);
           if (p.grp_mode == 1) b_row = group_of_tile(p.grp_prefix, p.grp_count, tm) * p.grp_b_rows;
         }
+        if (AG) { tm += ag_rot; if (tm >= tiles_m) tm -= tiles_m; }
         const int m0 = tm * BM, n0 = tn * BN;
+        bool own_rows = false;
+        if (AG) {
+          const int owner = m0 / p.ag_rows;
+          own_rows = owner == p.ag_rank;
+          if (!own_rows && !((ag_ready >> owner) & 1u)) {
+            // first tile of this peer's rows: wait until its push has landed in the local gathered buffer
+            const unsigned long long t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_sys_s32(p.ag_flags + owner) < p.ag_epoch) {
+              if ((++spins & 0xff) == 0) {
+                if (*abort_flag) { ok = false; break; }
+                if (globaltimer_ns() - t0 > g_gemm_flag_wait_ns) {
+                  *abort_flag = 1;
+                  atomicCAS(p.status, 0, 100 + owner);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");  // the peer's stores are read through the async proxy (TMA)
+            ag_ready |= 1u << owner;
+          }
+        }
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -153,7 +216,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);               // box {64 k, 128 m}
+            if (AG && own_rows) tma_load_2d(sa, &tmap_a2, &full_bar[stage], k0, m0 - p.ag_rank * p.ag_rows);
+            else tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);          // box {64 k, 128 m}
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)                                    // boxes {64 m, 64 k}
@@ -182,7 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty)) { ok = false; break; }
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty, wait_ns)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         int kb_lo = 0, kb_hi = num_kb;
@@ -192,7 +256,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           kb_hi = p.grp_prefix[g + 1] * (BM / BK);
         }
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrTimeoutFull)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrTimeoutFull, wait_ns)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
@@ -208,6 +272,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else if (AG && warp >= 6) {
+    // ------------------------------------------------------------ all-gather push (warps 6, 7)
+    // this rank's rows -> the gathered buffer of every rank; 16-byte vectors, four loads in flight per thread
+    const long nvec = (long)p.ag_rows * p.K / 8;
+    const long off = (long)p.ag_rank * nvec;
+    const int t = threadIdx.x - NUM_THREADS;
+    const long stride = (long)gridDim.x * AG_PUSH_THREADS;
+    long i = (long)blockIdx.x * AG_PUSH_THREADS + t;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      const uint4 a = p.ag_src[i], b = p.ag_src[i + stride], c = p.ag_src[i + 2 * stride], d = p.ag_src[i + 3 * stride];
+      for (int r = 0; r < p.ag_world; ++r) {
+        uint4* dst = p.ag_dst[r] + off;
+        dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+      }
+    }
+    for (; i < nvec; i += stride) {
+      const uint4 a = p.ag_src[i];
+      for (int r = 0; r < p.ag_world; ++r) p.ag_dst[r][off + i] = a;
+    }
+    __threadfence_system();                                    // this thread's stores are visible system-wide
+    asm volatile("bar.sync 1, %0;" ::"n"(AG_PUSH_THREADS) : "memory");
+    if (t == 0) {
+      const unsigned done = atomicAdd(p.ag_counter, 1u);
+      if (done == gridDim.x - 1) {                             // every CTA's share has been stored
+        *p.ag_counter = 0;                                     // ready for the next launch (stream-ordered)
+        __threadfence_system();
+        for (int r = 0; r < p.ag_world; ++r)
+          if (r != p.ag_rank) st_release_sys_s32(p.ag_flag_dst[r] + p.ag_rank, p.ag_epoch);
       }
     }
   } else {
@@ -226,9 +320,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       } else {
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
       }
+      if (AG) { tm += ag_rot; if (tm >= tiles_m) tm -= tiles_m; }
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kErrTimeoutTmemFull)) { ok = false; break; }
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kErrTimeoutTmemFull, wait_ns)) { ok = false; break; }
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * BN;
@@ -278,7 +373,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (lane == 0) {
             if (p.rs_world > 0) {  // the tile's rows belong to one owner (rs_rows is a multiple of the tile height)
               const int owner = (tm * BM) / p.rs_rows;
-              tma_store_2d(&p.rs_maps[owner], buf, col0, tm * BM - owner * p.rs_rows + q * 32);
+              tma_store_2d(&rs_maps.m[owner], buf, col0, tm * BM - owner * p.rs_rows + q * 32);
             } else if (p.accumulate) {
               tma_reduce_add_2d(&tmap_d, buf, col0, d_row0 + tm * BM + q * 32);
             } else {
@@ -361,7 +456,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 
   // ---------------------------------------------------------------- teardown
-  if (warp >= 2 && lane == 0 && p.tma_store) tma_store_wait<0>();
+  if (warp >= 2 && warp < 6 && lane == 0 && p.tma_store) tma_store_wait<0>();
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {
@@ -396,8 +491,39 @@ EncodeTiledFn get_encode_fn() {
 
 }  // namespace
 
+// Tensor maps are pure functions of (base, shape, stride, box); training re-issues the same few hundred GEMM shapes on the
+// same buffers every step, so the encoded maps are kept per thread and looked up instead of re-encoded.
+#include <unordered_map>
+namespace {
+struct TmapKey {
+  uint64_t base, inner, outer, stride;
+  uint32_t box_inner, box_outer;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box_inner == o.box_inner &&
+           box_outer == o.box_outer;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
+    h ^= (k.inner + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.outer + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.stride + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (((uint64_t)k.box_inner << 32 | k.box_outer) + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    return (size_t)h;
+  }
+};
+}  // namespace
+
 extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                                       uint32_t box_inner, uint32_t box_outer) {
+  static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const TmapKey key{reinterpret_cast<uint64_t>(base), inner, outer, row_stride_bytes, box_inner, box_outer};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *reinterpret_cast<CUtensorMap*>(out_map) = it->second;
+    return 0;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   // The encode call is a driver-API entry point and needs a current context on the calling thread.
@@ -416,14 +542,36 @@ extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t 
   CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) {
+    if (cache.size() > 16384) cache.clear();  // shapes that change every step (variable packing) must not grow it forever
+    cache.emplace(key, *reinterpret_cast<CUtensorMap*>(out_map));
+  }
   return (int)r;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Params& p, int num_sms,
-                          cudaStream_t stream) {
+namespace {
+// Everything one launch needs besides the plain GEMM arguments; passed explicitly down to the launcher.
+struct GemmExtras {
+  // GEMM -> reduce-scatter: output rows owned by rank o (blocks of rs_rows) are stored into rs_dst[o]
+  int rs_world = 0, rs_rows = 0;
+  void* const* rs_dst = nullptr;
+  // grouped GEMM
+  const int* grp_prefix = nullptr;
+  int grp_count = 0, grp_mode = 0, grp_b_rows = 0;
+  // all-gather -> GEMM
+  int ag_world = 0, ag_rank = 0, ag_rows = 0, ag_epoch = 0;
+  const void* ag_src = nullptr;
+  void* const* ag_dst = nullptr;
+  void* const* ag_flag_dst = nullptr;
+  const int* ag_flags = nullptr;
+  unsigned* ag_counter = nullptr;
+};
+
+template <int BN, bool A_MN, bool B_MN, bool AG>
+int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const CUtensorMap& ta2, const RsMaps& rsm,
+                   const Params& p, int num_sms, cudaStream_t stream) {
   using L = SmemLayout<BN>;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, AG>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
@@ -432,46 +580,13 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.grp_mode == 2 ? p.grp_count : 1);
   const int grid = tiles < num_sms ? tiles : num_sms;   // grp_mode 1: p.M is the row capacity, an upper bound
-  kern<<<grid, NUM_THREADS, L::kTotal, stream>>>(ta, tb, td, p);
+  kern<<<grid, AG ? NUM_THREADS + AG_PUSH_THREADS : NUM_THREADS, L::kTotal, stream>>>(ta, tb, td, ta2, rsm, p);
   return (int)cudaGetLastError();
 }
 
-// Tensor maps of reduce-scatter destinations live in device memory (the kernel picks one per tile).  A destination
-// set is one of a few staging slots, so the maps are built once per (pointers, shape) and kept for the process.
-#include <map>
-#include <vector>
-static const CUtensorMap* rs_maps_for(void* const* dst, int world, int rows, int N, int ldd) {
-  static thread_local std::map<std::vector<uint64_t>, CUtensorMap*> cache;
-  std::vector<uint64_t> key;
-  for (int i = 0; i < world; ++i) key.push_back(reinterpret_cast<uint64_t>(dst[i]));
-  key.push_back((uint64_t)rows); key.push_back((uint64_t)N); key.push_back((uint64_t)ldd);
-  int dev = 0;
-  cudaGetDevice(&dev);
-  key.push_back((uint64_t)dev);
-  auto it = cache.find(key);
-  if (it != cache.end()) return it->second;
-  CUtensorMap host[8];
-  for (int i = 0; i < world; ++i) {
-    if ((reinterpret_cast<uintptr_t>(dst[i]) & 15) || (ldd & 7)) return nullptr;
-    if (vlmt_make_tmap_2d_bf16(&host[i], dst[i], (uint64_t)N, (uint64_t)rows, (uint64_t)ldd * 2, 64, 32)) return nullptr;
-  }
-  CUtensorMap* devp = nullptr;
-  if (cudaMalloc(&devp, sizeof(CUtensorMap) * 8) != cudaSuccess) return nullptr;
-  if (cudaMemcpy(devp, host, sizeof(CUtensorMap) * world, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
-  cache[key] = devp;
-  return devp;
-}
-
-// destination set of the next vlmt_gemm_bf16 call (consumed by vlmt_gemm_bf16_rs_push)
-static thread_local int g_rs_world = 0, g_rs_rows = 0;
-static thread_local void* g_rs_dst[8];
-// group table of the next vlmt_gemm_bf16 call (set by vlmt_gemm_bf16_grouped)
-static thread_local const int* g_grp_prefix = nullptr;
-static thread_local int g_grp_count = 0, g_grp_mode = 0, g_grp_b_rows = 0;
-
-extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K,
-                              int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate,
-                              int* status, int num_sms, cudaStream_t stream) {
+int gemm_launch(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K, int lda, int ldb, int ldd,
+                int a_mn_major, int b_mn_major, int epilogue, int accumulate, const GemmExtras& x, int* status, int num_sms,
+                cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7)) return -2;  // TMA needs 16-byte row strides
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
@@ -481,66 +596,98 @@ extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc
   else r = vlmt_make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
   if (r) return 1000 + r;
   const bool bn256 = N > 128;
-  const uint64_t b_groups = g_grp_mode == 1 ? (uint64_t)g_grp_count : 1;   // grouped forward / dgrad: one B per group, stacked along the rows
+  const uint64_t b_groups = x.grp_mode == 1 ? (uint64_t)x.grp_count : 1;   // grouped forward / dgrad: one B per group, stacked along the rows
   if (!b_mn_major) r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N * b_groups, (uint64_t)ldb * 2, 64, 128);
   else r = vlmt_make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K * b_groups, (uint64_t)ldb * 2, 64, 64);
   if (r) return 2000 + r;
   Params p;
-  CUtensorMap td = ta;  // placeholder when the direct-store epilogue is used
+  CUtensorMap td = ta, ta2 = ta;  // placeholders where the direct-store epilogue / a single A source is used
+  static const RsMaps kNoRsMaps = {};
+  RsMaps rsm_local;
+  const RsMaps* rsm = &kNoRsMaps;
   p.tma_store = 0;
   p.rs_world = 0; p.rs_rows = 0;
-  p.rs_maps = nullptr;
-  if (g_rs_world > 0) {
-    p.rs_world = g_rs_world; p.rs_rows = g_rs_rows;
-    for (int i = 0; i < g_rs_world; ++i) p.rs_dst[i] = reinterpret_cast<__nv_bfloat16*>(g_rs_dst[i]);
+  if (x.rs_world > 0) {
+    p.rs_world = x.rs_world; p.rs_rows = x.rs_rows;
+    for (int i = 0; i < x.rs_world; ++i) p.rs_dst[i] = reinterpret_cast<__nv_bfloat16*>(x.rs_dst[i]);
     // whole 64-column slabs go out as TMA stores into the owners' memory (large NVLink writes); the per-thread 16-byte
     // stores of the direct epilogue are kept as the fallback
-    if (Dacc32 == nullptr && !accumulate && !bias && epilogue == GEMM_EPI_NONE) {
-      p.rs_maps = rs_maps_for(g_rs_dst, g_rs_world, g_rs_rows, N, ldd);
-      if (p.rs_maps != nullptr) p.tma_store = 1;
+    if (Dacc32 == nullptr && !accumulate && !bias && epilogue == GEMM_EPI_NONE && (ldd & 7) == 0) {
+      bool maps_ok = true;
+      for (int i = 0; i < x.rs_world && maps_ok; ++i) {
+        if (reinterpret_cast<uintptr_t>(x.rs_dst[i]) & 15) maps_ok = false;
+        else if (vlmt_make_tmap_2d_bf16(&rsm_local.m[i], x.rs_dst[i], (uint64_t)N, (uint64_t)x.rs_rows, (uint64_t)ldd * 2, 64, 32))
+          maps_ok = false;
+      }
+      if (maps_ok) {
+        for (int i = x.rs_world; i < MAX_RANKS; ++i) rsm_local.m[i] = rsm_local.m[0];
+        rsm = &rsm_local;
+        p.tma_store = 1;
+      }
     }
   }
   // with `accumulate` the slabs go out as TMA reduce-adds (bf16 addition in the memory system), so a weight gradient can
   // be added straight into the optimizer's gradient buffer without reading it back into the SM
-  if (g_rs_world == 0 && Dacc32 == nullptr && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
-    const uint64_t d_rows = g_grp_mode == 2 ? (uint64_t)M * g_grp_count : (uint64_t)M;
+  if (x.rs_world == 0 && Dacc32 == nullptr && (ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0) {
+    const uint64_t d_rows = x.grp_mode == 2 ? (uint64_t)M * x.grp_count : (uint64_t)M;
     r = vlmt_make_tmap_2d_bf16(&td, D, (uint64_t)N, d_rows, (uint64_t)ldd * 2, 64, 32);
     if (r == 0) p.tma_store = 1;
   }
   p.M = M; p.N = N; p.K = K; p.ldd = ldd;
-  p.grp_prefix = g_grp_prefix; p.grp_count = g_grp_count; p.grp_mode = g_grp_mode; p.grp_b_rows = g_grp_b_rows;
+  p.grp_prefix = x.grp_prefix; p.grp_count = x.grp_count; p.grp_mode = x.grp_mode; p.grp_b_rows = x.grp_b_rows;
   if (p.grp_mode == 2 && !p.tma_store) return -30;  // grouped wgrad writes through the TMA-store epilogue only
   p.D = reinterpret_cast<__nv_bfloat16*>(D);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.Dacc32 = Dacc32;
   p.epilogue = epilogue; p.accumulate = accumulate; p.status = status;
-#define DISPATCH(BN_)                                                                                     \
-  do {                                                                                                    \
-    if (!a_mn_major && !b_mn_major) return launch_variant<BN_, false, false>(ta, tb, td, p, num_sms, stream); \
-    if (!a_mn_major && b_mn_major) return launch_variant<BN_, false, true>(ta, tb, td, p, num_sms, stream);   \
-    if (a_mn_major && b_mn_major) return launch_variant<BN_, true, true>(ta, tb, td, p, num_sms, stream);     \
-    return launch_variant<BN_, true, false>(ta, tb, td, p, num_sms, stream);                                  \
+  p.ag_world = 0; p.ag_rank = 0; p.ag_rows = 0; p.ag_epoch = 0;
+  p.ag_src = nullptr; p.ag_flags = nullptr; p.ag_counter = nullptr;
+  if (x.ag_world > 0) {
+    if (a_mn_major || !bn256 || x.ag_world > MAX_RANKS || x.ag_rows % BM != 0 || x.ag_rows * x.ag_world != M || (K & 7) ||
+        (reinterpret_cast<uintptr_t>(x.ag_src) & 15))
+      return -40;
+    r = vlmt_make_tmap_2d_bf16(&ta2, x.ag_src, (uint64_t)K, (uint64_t)x.ag_rows, (uint64_t)K * 2, 64, 128);
+    if (r) return 4000 + r;
+    p.ag_world = x.ag_world; p.ag_rank = x.ag_rank; p.ag_rows = x.ag_rows; p.ag_epoch = x.ag_epoch;
+    p.ag_src = reinterpret_cast<const uint4*>(x.ag_src);
+    for (int i = 0; i < x.ag_world; ++i) {
+      p.ag_dst[i] = reinterpret_cast<uint4*>(x.ag_dst[i]);
+      p.ag_flag_dst[i] = reinterpret_cast<int*>(x.ag_flag_dst[i]);
+    }
+    p.ag_flags = x.ag_flags; p.ag_counter = x.ag_counter;
+    if (!b_mn_major) return launch_variant<256, false, false, true>(ta, tb, td, ta2, *rsm, p, num_sms, stream);
+    return launch_variant<256, false, true, true>(ta, tb, td, ta2, *rsm, p, num_sms, stream);
+  }
+#define DISPATCH(BN_)                                                                                                     \
+  do {                                                                                                                    \
+    if (!a_mn_major && !b_mn_major) return launch_variant<BN_, false, false, false>(ta, tb, td, ta2, *rsm, p, num_sms, stream); \
+    if (!a_mn_major && b_mn_major) return launch_variant<BN_, false, true, false>(ta, tb, td, ta2, *rsm, p, num_sms, stream);   \
+    if (a_mn_major && b_mn_major) return launch_variant<BN_, true, true, false>(ta, tb, td, ta2, *rsm, p, num_sms, stream);     \
+    return launch_variant<BN_, true, false, false>(ta, tb, td, ta2, *rsm, p, num_sms, stream);                                  \
   } while (0)
   if (bn256) DISPATCH(256);
   DISPATCH(128);
 #undef DISPATCH
 }
+}  // namespace
 
+extern "C" int vlmt_gemm_bf16(const void* A, const void* B, void* D, float* Dacc32, const void* bias, int M, int N, int K,
+                              int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int epilogue, int accumulate,
+                              int* status, int num_sms, cudaStream_t stream) {
+  return gemm_launch(A, B, D, Dacc32, bias, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, epilogue, accumulate, GemmExtras{}, status,
+                     num_sms, stream);
+}
 
 // D rows [o * rows_per_rank, (o + 1) * rows_per_rank) are written to dst[o] (row stride ldd) instead of a local D:
 // the producer half of a tensor-parallel GEMM -> reduce-scatter (the consumer sums the `world` partial blocks it received).
 // B is K-major (a row-parallel forward linear) or MN-major (the input gradient of a column-parallel linear).
 extern "C" int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const* dst, int world, int rows_per_rank, int M, int N, int K,
                                       int lda, int ldb, int ldd, int b_mn_major, int* status, int num_sms, cudaStream_t stream) {
-  if (world < 1 || world > 8 || rows_per_rank % BM != 0 || rows_per_rank * world != M) return -20;
-  g_rs_world = world; g_rs_rows = rows_per_rank;
-  for (int i = 0; i < world; ++i) g_rs_dst[i] = dst[i];
-  int r = vlmt_gemm_bf16(A, B, dst[0], nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, b_mn_major, GEMM_EPI_NONE, 0, status, num_sms,
-                         stream);
-  g_rs_world = 0;
-  return r;
+  if (world < 1 || world > MAX_RANKS || rows_per_rank % BM != 0 || rows_per_rank * world != M) return -20;
+  GemmExtras x;
+  x.rs_world = world; x.rs_rows = rows_per_rank; x.rs_dst = dst;
+  return gemm_launch(A, B, dst[0], nullptr, nullptr, M, N, K, lda, ldb, ldd, 0, b_mn_major, GEMM_EPI_NONE, 0, x, status, num_sms, stream);
 }
-
 
 // One launch for all groups (experts).  `prefix` (device, G + 1 ints): first 128-row tile of every group in the padded
 // row layout.
@@ -554,10 +701,30 @@ extern "C" int vlmt_gemm_bf16_grouped(const void* A, const void* B, void* D, con
   if (groups < 1 || (mode != 1 && mode != 2) || prefix == nullptr) return -31;
   if (mode == 1 && a_mn_major) return -32;
   if (mode == 2 && (!a_mn_major || !b_mn_major || (M % BM) != 0)) return -33;
-  g_grp_prefix = prefix; g_grp_count = groups; g_grp_mode = mode;
-  g_grp_b_rows = mode == 1 ? (b_mn_major ? K : N) : 0;
-  int r = vlmt_gemm_bf16(A, B, D, nullptr, nullptr, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, GEMM_EPI_NONE, 0, status, num_sms,
-                         stream);
-  g_grp_prefix = nullptr; g_grp_count = 0; g_grp_mode = 0; g_grp_b_rows = 0;
-  return r;
+  GemmExtras x;
+  x.grp_prefix = prefix; x.grp_count = groups; x.grp_mode = mode;
+  x.grp_b_rows = mode == 1 ? (b_mn_major ? K : N) : 0;
+  return gemm_launch(A, B, D, nullptr, nullptr, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, GEMM_EPI_NONE, 0, x, status, num_sms,
+                     stream);
+}
+
+// All-gather fused into the GEMM: D[M, N] = gathered(A) x op(B) with M = world * rows.  This rank's rows `src` [rows, K]
+// (contiguous) are copied by the kernel into gathered[r] + rank * rows * K for every rank r (gathered[rank] is the local
+// buffer `A_full` [M, K], whose peer blocks the kernel reads once flags[r] >= epoch) and the collective's number `epoch`
+// is stored into flag_dst[r][rank] of every peer when the copy is complete.  `counter`: one zero-initialised unsigned in
+// local memory, shared by all launches of a stream.
+extern "C" int vlmt_gemm_bf16_ag(const void* src, void* A_full, const void* B, void* D, void* const* gathered, void* const* flag_dst,
+                                 const int* flags, unsigned* counter, int epoch, int world, int rank, int rows, int N, int K, int ldb,
+                                 int ldd, int b_mn_major, int* status, int num_sms, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || gathered[rank] != A_full) return -41;
+  GemmExtras x;
+  x.ag_world = world; x.ag_rank = rank; x.ag_rows = rows; x.ag_epoch = epoch;
+  x.ag_src = src; x.ag_dst = gathered; x.ag_flag_dst = flag_dst; x.ag_flags = flags; x.ag_counter = counter;
+  return gemm_launch(A_full, B, D, nullptr, nullptr, world * rows, N, K, K, ldb, ldd, 0, b_mn_major, GEMM_EPI_NONE, 0, x, status, num_sms,
+                     stream);
+}
+
+extern "C" int vlmt_gemm_set_flag_wait_ms(long ms) {
+  const unsigned long long ns = (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
+  return (int)cudaMemcpyToSymbol(g_gemm_flag_wait_ns, &ns, sizeof(ns));
 }

@@ -26,6 +26,17 @@ int vlmt_gemm_bf16_rs_push(const void* A, const void* B, void* const* dst, int w
 // contraction over the rows (K = row capacity) and every group writes its own [M, N] block of D.
 int vlmt_gemm_bf16_grouped(const void* A, const void* B, void* D, const int* prefix, int groups, int mode, int M, int N, int K, int lda,
                            int ldb, int ldd, int a_mn_major, int b_mn_major, int* status, int num_sms, cudaStream_t stream);
+// All-gather fused into the GEMM (tensor-parallel column linear on sequence-sharded rows): D[world * rows, N] =
+// gathered(A) x op(B).  The kernel copies this rank's rows `src` [rows, K] (contiguous) into block `rank` of
+// gathered[r] for every rank r (peer stores; gathered[rank] == A_full is the local [world * rows, K] buffer), stores
+// `epoch` into flag_dst[r][rank] of every peer when the copy is complete, computes the tiles of its own rows from `src`
+// meanwhile and reads a peer's block of A_full once flags[peer] >= epoch (bounded wait -> status 100 + peer).
+// counter: one zero-initialised unsigned in local device memory.  B K-major or MN-major; N > 128; rows % 128 == 0.
+int vlmt_gemm_bf16_ag(const void* src, void* A_full, const void* B, void* D, void* const* gathered, void* const* flag_dst,
+                      const int* flags, unsigned* counter, int epoch, int world, int rank, int rows, int N, int K, int ldb, int ldd,
+                      int b_mn_major, int* status, int num_sms, cudaStream_t stream);
+// bound of the in-GEMM wait for a peer's flag on the current device, in milliseconds (default 20 000)
+int vlmt_gemm_set_flag_wait_ms(long ms);
 // 2-D bf16 tensor map with 128-byte swizzle; `out_map` points at 128 bytes (CUtensorMap).
 int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer);

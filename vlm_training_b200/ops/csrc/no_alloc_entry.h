@@ -12,7 +12,8 @@
 //
 // Contract
 //   * dy, x, dx: bf16 [rows, D]; w: bf16 (or fp32 when w_fp32 != 0) [D]; rstd: fp32 [rows];
-//     dres: optional bf16 [rows, D] added to dx (may be null); dw: fp32 [D] OUTPUT (overwritten).
+//     dres: optional bf16 [rows, D] added to dx (may be null); dw: fp32 [D] OUTPUT (overwritten; with
+//     rows <= 0 it is overwritten with zeros).
 //   * D must be a multiple of 8 and at most VLMT_NOALLOC_MAX_D (8192).  Larger D is refused:
 //     the function prints the reason to stderr and returns VLMT_NOALLOC_ERR_SIZE; nothing is launched.
 //   * The scratch is VLMT_NOALLOC_MAX_BLOCKS x VLMT_NOALLOC_MAX_D floats (148 x 8192 x 4 B = 4.6 MiB).

@@ -51,14 +51,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when it gave up (timeout, or another role already
 // raised `*abort_flag`); the caller must then leave its loop.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// `limit_ns`: kernels whose producer may itself wait for another GPU pass a longer bound for the waits that depend on it.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

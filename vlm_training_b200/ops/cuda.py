@@ -41,6 +41,11 @@ def _tick(n: int = 1):
     LAUNCHES["count"] += n
 
 
+def status_word() -> torch.Tensor:
+    """The device status word of the current device (one int32): 0, or the code of the first bounded wait that ran out."""
+    return _C.status()[:1]
+
+
 def check_status(raise_on_error: bool = True) -> int:
     """Read (and clear) the device status word that bounded in-kernel waits write on timeout."""
     from . import status

@@ -188,6 +188,14 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         sharded = [(p, group_of[p]) for p in ordered if getattr(p, "_tp_sharded", False)]
         replicated = [(p, group_of[p]) for p in ordered if not getattr(p, "_tp_sharded", False)]
         self.domains: list[_Domain] = []
+        self.comm_path = "local" if not dist.is_initialized() else "nccl"
+        reason = ""
+        if fused_comm and self.is_cuda and dist.is_initialized():
+            # decided before the buffers are allocated: the one-kernel path needs them in symmetric memory
+            if state_dtype != torch.float32:
+                fused_comm, reason = False, f"the fused kernel keeps fp32 Adam moments, optimizer_state_dtype is {state_dtype}"
+            elif max_grad_norm is not None:
+                fused_comm, reason = False, "gradient clipping needs the global norm before the first update"
         symmetric = fused_comm and self.is_cuda and dist.is_initialized()
         if experts:
             # expert-parallel parameters: each rank owns different experts, whose gradients already hold the
@@ -196,7 +204,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
             ep = getattr(model, "_ep_ctx", None)
             rep_group = ep.replica_group if (ep is not None and ep.replica_size > 1) else None
             self.domains.append(_Domain("ep_experts", experts, rep_group, 1.0 / dp_size, shard and rep_group is not None, device,
-                                        pdtype, bucket_elems, state_dtype, False))
+                                        pdtype, bucket_elems, state_dtype, symmetric and rep_group is not None))
         if tp_size > 1:
             if sharded:
                 self.domains.append(_Domain("tp_sharded", sharded, dp_group, 1.0 / dp_size, shard, device, pdtype,
@@ -215,11 +223,19 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         self._hooks = []
         self._sync_grads = True
         self._fused = None
-        if symmetric and max_grad_norm is None:
+        if symmetric:
             from . import fused
 
-            if fused.usable(self):
+            ok, reason = fused.usable(self)
+            if ok:
                 self._fused = fused.FusedStepState(self)
+                self.comm_path = "fused"
+        if dist.is_initialized() and self.is_cuda:
+            import logging
+
+            logging.getLogger("vlm_training_b200").info(
+                "optimizer step: " + ("reduce-scatter + AdamW + all-gather in one NVLink kernel per bucket" if self._fused is not None
+                                      else f"NCCL reduce-scatter / all-gather around the AdamW kernel ({reason or 'fused_comm is off'})"))
         if self.is_cuda and overlap and dist.is_initialized():
             self._install_hooks()
         if self.is_cuda:

@@ -59,10 +59,15 @@ class FusedStepState:
         raise KeyError
 
 
-def usable(engine) -> bool:
-    if any(d.name == "ep_experts" for d in engine.domains):
-        return False  # expert-parallel parameters take the plain path
-    return all(d.size == 1 or symm.handle_of(d.flat_grad) is not None for d in engine.domains)
+def usable(engine) -> tuple[bool, str]:
+    """Whether the one-kernel path can run this engine, and if not, why (the engine logs the reason and takes the
+    NCCL path)."""
+    for d in engine.domains:
+        if d.exp_avg and d.exp_avg[0].dtype != torch.float32:
+            return False, f"the fused kernel keeps fp32 Adam moments, optimizer_state_dtype is {d.exp_avg[0].dtype}"
+        if d.size > 1 and symm.handle_of(d.flat_grad) is None:
+            return False, f"the buffers of domain '{d.name}' are not in symmetric memory"
+    return True, ""
 
 
 def begin_step(engine):

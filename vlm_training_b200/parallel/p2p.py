@@ -1,11 +1,24 @@
 """Tensor-parallel collectives as our own NVLink kernels (no NCCL on the layer path).
 
 For the 32-64 MB messages of sequence-parallel TP on two ranks NCCL picks its low-latency ring protocol and
-moves ~120 GB/s; a plain peer-to-peer pull over NVSwitch moves the same bytes several times faster.  Each
-collective is: copy the contribution into a slot of this rank's symmetric staging buffer → ``signal`` (store the
-collective's sequence number into every peer's flag array, release/system scope) → one pull kernel that waits
-(bounded) for all signals and then reads the peers' slots directly (``ops/csrc/comm_kernels.cu``).  The
-reduce-scatter kernel accumulates in fp32 and can add a residual in the same pass.
+moves ~120 GB/s; plain peer-to-peer loads and stores over NVSwitch move the same bytes several times faster.
+
+* all-gather -> GEMM (column-parallel linears, and the gather of ``dY`` in the backward of row-parallel ones) is ONE
+  kernel: :meth:`P2PComm.gemm_all_gather` launches the tcgen05 GEMM whose extra warps store this rank's rows into
+  every rank's gathered buffer and signal, while its tiles of the own rows already run; tiles of a peer's rows start
+  when that peer's flag has arrived (``ops/csrc/gemm_sm100.cu``, the ``AG`` variant).
+* GEMM -> reduce-scatter (row-parallel linears, and the input gradient of column-parallel ones) is the GEMM whose
+  epilogue TMA-stores each tile into its owner's memory, followed by a local sum (:meth:`P2PComm.gemm_reduce_scatter`).
+* the remaining collectives (vision features, non-GEMM gathers) are: copy the contribution into a slot of this rank's
+  symmetric staging buffer → ``signal`` (store the collective's sequence number into every peer's flag array,
+  release/system scope) → one pull kernel that waits (bounded) for all signals and then reads the peers' slots
+  directly (``ops/csrc/comm_kernels.cu``).  The reduce-scatter kernel accumulates in fp32 and can add a residual in
+  the same pass.
+
+Collectives are numbered 1, 2, ... in program order (identical on every rank, all on the caller's stream), and flag
+values only grow, so "flag[r] >= e" means rank r has contributed to collective e.  Gathered activations that are kept
+for backward live in one symmetric buffer per call site (``site_buffer``); a peer overwrites it in the next
+micro-batch's forward, which :meth:`P2PComm.begin_microbatch` orders behind this rank's previous backward.
 
 A waiting kernel gives up after a bounded time (``VLMT_FLAG_WAIT_MS``, default 20 s) and writes a status word (read by ``ops.cuda.check_status``)
 instead of spinning forever, so a rank that left shows up as a Python exception on the survivors.
@@ -21,25 +34,39 @@ from . import symm
 class P2PComm:
     N_SLOTS = 4
 
+    FENCE_ROW = 16  # flags[16 + r]: micro-batch fence of rank r; flags[r]: collective number of rank r
+
     def __init__(self, group, device, slot_elems: int = 1 << 25):
         self.group, self.device = group, device
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.epoch = 0
+        self.fence_epoch = 0
         self.slot_elems = 0
+        self.staging = None
         self.flags = symm.symmetric_zeros(64, torch.int32, device, group)
         self.flag_ptrs = symm.peer_ptrs(self.flags)
         self.side = torch.cuda.Stream(device=device)  # pulls that overlap the caller's compute
+        self.ag_counter = torch.zeros(1, dtype=torch.int32, device=device)  # CTAs done with their share of a push
+        self.arena = symm.SymmetricArena(group, device)
+        self.sites = {}  # call site -> (gathered buffer, its address on every rank)
         symm.apply_flag_wait_limit()
         self._alloc(slot_elems)
 
     def _alloc(self, slot_elems: int):
+        """(Re)allocate the staging ring.  Peers may still be reading the old ring or storing into it, so every rank first
+        drains its own stream and meets the others; only then is the old buffer dropped."""
         slot_elems = (slot_elems + 1023) // 1024 * 1024
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        old = self.staging
         self.staging = symm.symmetric_zeros(self.N_SLOTS * slot_elems, torch.bfloat16, self.device, self.group)
         self.slot_elems = slot_elems
         self.staging_ptrs = symm.peer_ptrs(self.staging)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)  # every rank's buffers are zeroed and mapped before the first signal
+        if old is not None:
+            symm.release(old)
 
     def _slot(self, n: int):
         if n > self.slot_elems:
@@ -48,6 +75,53 @@ class P2PComm:
         s = self.epoch % self.N_SLOTS
         off = s * self.slot_elems
         return self.epoch, self.staging[off:off + n], [p + off * 2 for p in self.staging_ptrs]
+
+    def site_buffer(self, site, rows: int, width: int):
+        """The gathered-activation buffer ``[rows, width]`` of one call site (a module), allocated on first use from the
+        symmetric arena and reused by every later step.  All ranks reach their call sites in the same order."""
+        ent = self.sites.get(id(site))
+        if ent is None or ent[0].numel() < rows * width:
+            ent = self.arena.alloc(rows * width)
+            self.sites[id(site)] = ent
+        buf, ptrs = ent
+        return buf[: rows * width].view(rows, width), ptrs
+
+    def begin_microbatch(self):
+        """Order the peers' stores of the coming forward pass behind this rank's previous backward pass: every rank
+        announces "my stream has reached the next micro-batch" and waits (bounded, on the device) for the others."""
+        from ..ops import cuda as cu
+
+        self.fence_epoch += 1
+        cu._C.signal_peers_at(self.flag_ptrs, self.FENCE_ROW, self.rank, self.fence_epoch)
+        cu._C.wait_flags(self.flags.data_ptr(), self.FENCE_ROW, self.world, self.fence_epoch, self.rank)
+        cu._tick(2)
+
+    def gemm_all_gather(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, site=None):
+        """``(all_gather_rows(x_local) @ op(w), all_gather_rows(x_local))`` in one kernel launch (``op(w)`` = ``w.T``, or
+        ``w`` with ``b_mn``).  The gathered rows land in the call site's persistent buffer (``site``: kept for backward)
+        or, without a site, in a slot of the staging ring (valid until three more collectives have been issued)."""
+        from ..ops import cuda as cu
+
+        x_local = x_local.contiguous()
+        R, K = x_local.shape
+        T = R * self.world
+        if site is not None:
+            x_full, ptrs = self.site_buffer(site, T, K)
+            self.epoch += 1
+            e = self.epoch
+        else:
+            e, slot, ptrs = self._slot(T * K)
+            x_full = slot.view(T, K)
+        n_out = w.shape[1] if b_mn else w.shape[0]
+        y = x_local.new_empty((T, n_out))
+        cu._C.gemm_ag(x_local, x_full, w, y, ptrs, self.flag_ptrs, 0, self.ag_counter, e, self.rank, b_mn)
+        cu._tick()
+        return y, x_full
+
+    def gemm_ag_usable(self, x, w, b_mn: bool = False) -> bool:
+        n_out = w.shape[1] if b_mn else w.shape[0]
+        return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] % 128 == 0 and x.shape[1] % 8 == 0
+                and n_out > 128 and n_out % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and self.world <= 8)
 
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         from ..ops import cuda as cu

@@ -54,8 +54,43 @@ def multicast_ptr(t: torch.Tensor) -> int:
             return 0
 
 
+def release(t: torch.Tensor):
+    """Forget the rendezvous handle of a symmetric buffer that is no longer used (the mapping goes away with the last
+    reference to the tensor and its handle)."""
+    _HANDLES.pop(t.data_ptr(), None)
+
+
+class SymmetricArena:
+    """Bump allocator over symmetric memory for buffers that live as long as the model (one per call site that
+    gathers activations).  Every rank of the group must request the same sizes in the same order, so a buffer has the
+    same offset on every rank; memory comes in chunks so that ~70 call sites cost a handful of rendezvous, not 70."""
+
+    def __init__(self, group, device, chunk_bytes: int = 1 << 30):
+        self.group, self.device, self.chunk_bytes = group, device, chunk_bytes
+        self.chunks = []  # (uint8 tensor, peer pointers, bytes used)
+
+    def alloc(self, n: int, dtype=torch.bfloat16):
+        """Returns ``(tensor [n], [address of the same buffer on every rank])``; the buffer is zero-filled."""
+        nbytes = (n * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
+        if not self.chunks or self.chunks[-1][2] + nbytes > self.chunks[-1][0].numel():
+            size = max(self.chunk_bytes, nbytes)
+            buf = symmetric_zeros(size, torch.uint8, self.device, self.group)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)  # zero-filled and mapped on every rank before anybody stores into it
+            self.chunks.append([buf, peer_ptrs(buf), 0])
+        buf, ptrs, used = self.chunks[-1]
+        self.chunks[-1][2] = used + nbytes
+        t = buf[used:used + n * torch.empty((), dtype=dtype).element_size()].view(dtype)
+        return t, [p + used for p in ptrs]
+
+    def bytes_reserved(self) -> int:
+        return sum(c[0].numel() for c in self.chunks)
+
+
 def apply_flag_wait_limit():
     """Set the bound of the in-kernel flag waits of the current device from ``VLMT_FLAG_WAIT_MS`` (default 20 000)."""
     from ..ops import cuda as cu
 
-    cu._C.set_flag_wait_ms(int(os.environ.get("VLMT_FLAG_WAIT_MS", "20000")))
+    ms = int(os.environ.get("VLMT_FLAG_WAIT_MS", "20000"))
+    cu._C.set_flag_wait_ms(ms)
+    cu._C.gemm_set_flag_wait_ms(ms)

@@ -10,7 +10,7 @@ the reference uses (reference: train/infra.py:391-401,438-458).
 Each function is an autograd ``Function`` whose backward is the conjugate
 collective.  ``TPContext.backend`` selects how the bytes move: ``"dist"``
 (torch.distributed: NCCL on GPUs, gloo on CPU) or ``"fused"`` (the one-kernel
-NVLink paths in :mod:`vlm_training_b200.parallel.fused`), which handle the
+NVLink paths of :mod:`vlm_training_b200.parallel.p2p`), which handle the
 collective inside the adjacent GEMM and bypass these functions.
 """
 from __future__ import annotations
@@ -200,11 +200,14 @@ def _row_blocks(rank: int, size: int, rows: int):
     return others, (rank * rows, (rank + 1) * rows)
 
 
-def _gathered_gemm(x_local, w, ctx, b_mn=False):
-    """``all_gather_rows(x_local) @ op(w)`` with the gather overlapped: the product of this rank's own rows needs no
-    communication and runs while the side stream pulls the peers' rows.  Returns ``(y_full, x_full)``."""
+def _gathered_gemm(x_local, w, ctx, b_mn=False, site=None):
+    """``all_gather_rows(x_local) @ op(w)``; returns ``(y_full, x_full)``.  One kernel where the shapes allow it (the
+    all-gather runs inside the GEMM, :meth:`P2PComm.gemm_all_gather`); otherwise the gather is a peer pull on a side
+    stream that overlaps the product of this rank's own rows."""
     from ..ops import cuda as cu
 
+    if ctx.p2p.gemm_ag_usable(x_local, w, b_mn):
+        return ctx.p2p.gemm_all_gather(x_local, w, b_mn=b_mn, site=site)
     R = x_local.shape[0]
     x_full, done = ctx.p2p.all_gather_rows_async(x_local)
     others, (o0, o1) = _row_blocks(ctx.rank, ctx.size, R)
@@ -224,10 +227,10 @@ class _GatherLinear(torch.autograd.Function):
     completes at the end, when the peers' blocks have long been written."""
 
     @staticmethod
-    def forward(fctx, x, w, ctx):
+    def forward(fctx, x, w, ctx, site=None):
         from ..ops import cuda as cu
 
-        y, x_full = _gathered_gemm(x, w, ctx)
+        y, x_full = _gathered_gemm(x, w, ctx, site=site)
         fctx.tp = ctx
         fctx.w_param = cu._grad_target(w)
         fctx.save_for_backward(x_full, w)
@@ -257,7 +260,7 @@ class _GatherLinear(torch.autograd.Function):
         dw = cu._wgrad(dy, x_full, fctx.w_param) if fctx.needs_input_grad[1] else None
         if fctx.needs_input_grad[0] and dx is None:
             dx = handle.result(dy)
-        return dx, dw, None
+        return dx, dw, None, None
 
 
 def gather_linear_usable(x, weight, bias, ctx: TPContext) -> bool:
@@ -266,11 +269,12 @@ def gather_linear_usable(x, weight, bias, ctx: TPContext) -> bool:
             and x.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0)
 
 
-def column_linear(x, weight, bias, ctx: TPContext):
+def column_linear(x, weight, bias, ctx: TPContext, site=None):
     """``linear(column_input(x), weight, bias)``; on the peer-to-peer backend with sequence parallelism the all-gather
-    is overlapped with the product of the local rows."""
+    runs inside the GEMM kernel.  ``site``: the calling module; its gathered input is kept in a persistent symmetric
+    buffer of that site for the backward pass."""
     if gather_linear_usable(x, weight, bias, ctx):
-        return _GatherLinear.apply(x, weight, ctx)
+        return _GatherLinear.apply(x, weight, ctx, site)
     from .. import ops
 
     return ops.linear(column_input(x, ctx), weight, bias)

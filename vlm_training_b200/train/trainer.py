@@ -9,8 +9,10 @@ Differences that are deliberate:
 * device time is measured with CUDA events (the reference reads ``perf_counter`` without
   a device sync, reference: train/train_qwen.py:537,550);
 * gradients are reduced once per optimizer step, not once per micro-batch;
-* no per-step ``.item()`` on the device: token counts come from the host copy of the batch
-  and the loss is read back once per logged step;
+* no host sync inside the step on a GPU: token counts come from the host copy of the batch; the loss, the
+  data-parallel reductions and the device status word of step ``k`` travel to pinned host memory by an
+  asynchronous copy and are read when step ``k + 1`` has been enqueued (``training.async_metrics``), so the
+  metrics of a step are returned one call later and the GPU never idles while the host catches up;
 * three optimizer groups as intended (see :mod:`.optimizer`).
 """
 from __future__ import annotations
@@ -21,6 +23,7 @@ import time
 
 import torch
 import torch.distributed as dist
+from torch.distributed.elastic.multiprocessing.errors import record
 
 from ..config import Config, ModelType, to_flat_dict
 from ..data.loader import PrefetchLoader, batch_nbytes, to_device
@@ -33,7 +36,7 @@ from . import checkpoint as ckpt
 from .flops import get_dense_model_nparams_and_flops, peak_flops
 from .freeze import set_determinism, set_model
 from .logger import colors, init_logger, logger
-from .metrics import PERF_KEYS, gather_perf, reduce_many, topk_report
+from .metrics import PERF_KEYS, gather_perf, topk_report
 from .optimizer import create_optimizer
 from .schedulers import accumulation_pattern, build_scheduler
 
@@ -45,6 +48,7 @@ def select_model_class(model_type: ModelType):
 
 
 class Trainer:
+    @record  # a failure during set-up lands in torchrun's error file (reference: train/train_qwen.py:17,71)
     def __init__(self, cfg: Config):
         self.cfg = cfg
         t = cfg.training
@@ -116,6 +120,12 @@ class Trainer:
         self.samples_seen = 0
         self._window = {"tokens": 0, "label_tokens": 0, "samples": 0, "micro": 0, "data_time": 0.0, "h2d_bytes": 0}
         self._last_log = time.perf_counter()
+        self._pending = None
+        self._cprofile = None
+        self._last_perf = None
+        self._flushed = []  # metrics resolved by a flush (checkpoint, end of run) that no train_step call returned
+        # deferred metrics need pinned memory and events, so they exist on a GPU only
+        self.async_metrics = bool(t.async_metrics) and self.device.type == "cuda"
         logger.info(f"model {cfg.model.model_name or cfg.model.preset}: {self.nparams / 1e9:.3f} B parameters, "
                     f"{self.flops_per_token / 1e9:.2f} GFLOP/token/GPU, mode {t.data_parallel} x tp{t.tp_size}")
 
@@ -211,50 +221,120 @@ class Trainer:
         self.accum_target = next(self.accum_cycle)
         return metrics
 
-    def _finish_step(self) -> dict:
-        t = self.cfg.training
+    def _finish_step(self) -> dict | None:
+        """Close the accumulation window: enqueue the step's reductions and read-back, then return the metrics of the
+        newest step whose numbers have reached the host (this step when metrics are synchronous, the previous one
+        when they are deferred, ``None`` on the first deferred call)."""
         w = self._window
         now = time.perf_counter()
-        wall = now - self._last_log
+        pend = {"window": w, "wall": now - self._last_log, "step": self.global_step,
+                "lr": self.optimizer.param_groups[0]["lr"]}
         self._last_log = now
-        loss_local = float((self._loss_acc / w["micro"]).item())  # the one device→host read of the step
-        if self.device.type == "cuda":
-            self._ev_end.synchronize()
-            step_time = self._ev_start.elapsed_time(self._ev_end) / 1e3
-            fwd_bwd = self._ev_start.elapsed_time(self._ev_fb) / 1e3
-            peak_mem = torch.cuda.max_memory_allocated() / 2 ** 30
+        cuda = self.device.type == "cuda"
+        # the previous step first: its numbers have long arrived, and its timings feed this step's straggler table
+        done = None
+        if self._pending is not None:
+            done, self._pending = self._resolve(self._pending), None
+        loss_local = (self._loss_acc / w["micro"]).double().reshape(1)
+        if cuda:
+            pend.update(ev_start=self._ev_start, ev_fb=self._ev_fb, ev_end=self._ev_end)
+            pend["peak_mem"] = torch.cuda.max_memory_allocated() / 2 ** 30
             torch.cuda.reset_peak_memory_stats()
+        # [loss, tokens, label tokens, samples | loss (max) | device status word | straggler table]: the collectives
+        # run over the data-parallel group (the table over all ranks) with no host read in between
+        counts = torch.tensor([w["tokens"], w["label_tokens"], w["samples"]], dtype=torch.float64)
+        if cuda:
+            counts = counts.pin_memory().to(self.device, non_blocking=True)
+        vec = torch.cat([loss_local, counts])
+        mx = loss_local.clone()
+        n = 1
+        if dist.is_initialized() and self.mesh.dp > 1:
+            dist.all_reduce(vec, op=dist.ReduceOp.SUM, group=self.mesh.dp_group)
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=self.mesh.dp_group)
+            n = self.mesh.dp
+        parts = [vec, mx]
+        if cuda:
+            from ..ops import cuda as cu
+
+            parts.append(cu.status_word().double())
         else:
-            step_time = fwd_bwd = wall
-            peak_mem = 0.0
-        dpg = self.mesh.dp_group
-        loss_mean, loss_max, tok_sum, lab_sum, samp_sum = reduce_many(
-            [loss_local, loss_local, w["tokens"], w["label_tokens"], w["samples"]],
-            ["mean", "max", "sum", "sum", "sum"], group=dpg, device=self.device)
+            parts.append(torch.zeros(1, dtype=torch.float64))
+        want_topk = self.cfg.wandb.log_topk and self.world > 1
+        if want_topk and not self.async_metrics:
+            pend["topk_now"] = True  # synchronous metrics rank the step itself, after its timings are known
+        elif want_topk and self._last_perf is not None:
+            table = torch.tensor(self._last_perf, dtype=torch.float64)
+            if cuda:
+                table = table.pin_memory().to(self.device, non_blocking=True)
+            gathered = torch.empty(self.world * table.numel(), dtype=torch.float64, device=self.device)
+            dist.all_gather_into_tensor(gathered, table)
+            parts.append(gathered)
+        packed = torch.cat(parts)
+        if cuda:
+            host = torch.empty(packed.numel(), dtype=torch.float64, pin_memory=True)
+            host.copy_(packed, non_blocking=True)  # the step's device -> host read
+            pend["ready"] = torch.cuda.Event()
+            pend["ready"].record()
+        else:
+            host = packed
+        pend["host"], pend["dp"] = host, n
+        self._window = {"tokens": 0, "label_tokens": 0, "samples": 0, "micro": 0, "data_time": 0.0, "h2d_bytes": 0}
+        self._pending = pend
+        if not self.async_metrics:
+            return self.flush_metrics()
+        return done
+
+    def flush_metrics(self) -> dict | None:
+        """Wait for the newest step's numbers and return its metrics (``None`` if every step has been reported).
+        Called before a checkpoint is written and at the end of the run; raises if a kernel of the step reported a
+        bounded wait that ran out."""
+        pend, self._pending = self._pending, None
+        return self._resolve(pend) if pend is not None else None
+
+    def _resolve(self, pend: dict) -> dict:
+        w = pend["window"]
+        if "ready" in pend:
+            pend["ready"].synchronize()  # long complete unless this is a flush
+            step_time = pend["ev_start"].elapsed_time(pend["ev_end"]) / 1e3
+            fwd_bwd = pend["ev_start"].elapsed_time(pend["ev_fb"]) / 1e3
+        else:
+            step_time = fwd_bwd = pend["wall"]
+        vals = pend["host"].tolist()
+        loss_sum, tok_sum, lab_sum, samp_sum, loss_max, status = vals[:6]
+        if int(status) != 0:
+            from ..ops import cuda as cu, status as st
+
+            cu.status_word().zero_()
+            raise RuntimeError(f"step {pend['step']}: a kernel gave up on a bounded wait: {st.describe(int(status))} "
+                               f"(status {int(status)}); the optimizer state of this step may be incomplete")
         self.tokens_seen += int(tok_sum)
         self.tokens_seen_assistant += int(lab_sum)
         self.samples_seen += int(samp_sum)
         tps = w["tokens"] / max(step_time, 1e-9)
         tflops = self.flops_per_token * self.seq_len * w["micro"] / max(step_time, 1e-9) / 1e12
         mfu = tflops * 1e12 / self.peak_flops
-        m = {"train/loss": loss_mean, "train/max_loss": loss_max, "train/tokens_seen": self.tokens_seen,
+        m = {"train/loss": loss_sum / pend["dp"], "train/max_loss": loss_max, "train/tokens_seen": self.tokens_seen,
              "train/assistant_tokens_seen": self.tokens_seen_assistant, "train/num_samples": samp_sum,
-             "train/lr": self.optimizer.param_groups[0]["lr"],
+             "train/lr": pend["lr"],
              "train/batch_efficiency": w["tokens"] / max(1, w["micro"] * self.seq_len),
-             "perf/tokens_per_second": tps, "perf/data_time_pct": 100.0 * w["data_time"] / max(wall, 1e-9),
+             "perf/tokens_per_second": tps, "perf/data_time_pct": 100.0 * w["data_time"] / max(pend["wall"], 1e-9),
              "perf/step_time": step_time, "perf/fwd_bwd_time": fwd_bwd, "perf/tflops_per_second": tflops, "perf/mfu": mfu,
-             "perf/peak_mem_gib": peak_mem, "perf/h2d_bytes": w["h2d_bytes"], "step": self.global_step}
-        if self.cfg.wandb.log_topk and self.world > 1:
-            table = gather_perf([tps, step_time, fwd_bwd, tflops, mfu, peak_mem], self.device)
+             "perf/peak_mem_gib": pend.get("peak_mem", 0.0), "perf/h2d_bytes": w["h2d_bytes"],
+             "perf/d2h_bytes": pend["host"].numel() * pend["host"].element_size(), "step": pend["step"]}
+        self._last_perf = [tps, step_time, fwd_bwd, tflops, mfu, pend.get("peak_mem", 0.0)]
+        if pend.get("topk_now"):
+            m.update(topk_report(gather_perf(self._last_perf, self.device), self.cfg.wandb.top_k))
+        elif len(vals) > 6:
+            # deferred metrics: the ranking was gathered with this step's read-back and describes the step before it
+            table = torch.tensor(vals[6:], dtype=torch.float32).view(self.world, len(PERF_KEYS))
             m.update(topk_report(table, self.cfg.wandb.top_k))
         self.log(m)
-        self._window = {"tokens": 0, "label_tokens": 0, "samples": 0, "micro": 0, "data_time": 0.0, "h2d_bytes": 0}
         return m
 
     def log(self, m: dict):
         if self.rank != 0:
             return
-        if self.global_step % max(1, self.cfg.training.log_every) == 0:
+        if m["step"] % max(1, self.cfg.training.log_every) == 0:
             c = colors()
             logger.info(f"{c.cyan}step {m['step']:>6}{c.reset} loss {c.yellow}{m['train/loss']:.4f}{c.reset} "
                         f"tps {m['perf/tokens_per_second']:,.0f} mfu {100 * m['perf/mfu']:.1f}% "
@@ -266,6 +346,9 @@ class Trainer:
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self):
+        m = self.flush_metrics()  # counters are final and the device status word of the last step has been checked
+        if m is not None:
+            self._flushed.append(m)
         return ckpt.save_checkpoint(self.cfg.training.output_dir, self.global_step, self.model, self.optimizer, self.scheduler,
                                     {"tokens_seen": self.tokens_seen, "tokens_seen_assistant": self.tokens_seen_assistant},
                                     tp_rank=self.mesh.tp_rank)
@@ -295,6 +378,7 @@ class Trainer:
         try:
             with prof if prof is not None else _Null():
                 while self.global_step < t.total_steps:
+                    before = self.global_step
                     try:
                         m = self.train_step(data_iterator)
                     except StopIteration:
@@ -305,10 +389,43 @@ class Trainer:
                         prof.step()
                     if m is not None:
                         history.append(m)
+                    if self.global_step != before:  # an optimizer step was taken
+                        self._cprofile_window()
                         self.may_save()
+                    history.extend(self._flushed)
+                    self._flushed.clear()
         finally:
             self.end_run()
+        history.extend(self._flushed)
+        self._flushed.clear()
         return history
+
+    def _cprofile_window(self):
+        """``DEBUG=1``: profile the host side of optimizer steps ``cprofile_start`` .. ``cprofile_stop`` with cProfile
+        and write the 50 most expensive call sites by cumulative time to ``cprofile_rank_{r}.txt`` in the output
+        directory (reference: train/train_qwen.py:607-615,667-694)."""
+        if not self.debug:
+            return
+        t = self.cfg.training
+        if self.global_step == t.cprofile_start and self._cprofile is None:
+            import cProfile
+
+            self._cprofile = cProfile.Profile()
+            self._cprofile.enable()
+        elif self.global_step >= t.cprofile_stop and self._cprofile is not None:
+            self._dump_cprofile()
+
+    def _dump_cprofile(self):
+        import io
+        import pstats
+
+        prof, self._cprofile = self._cprofile, None
+        prof.disable()
+        buf = io.StringIO()
+        pstats.Stats(prof, stream=buf).sort_stats("cumulative").print_stats(50)
+        os.makedirs(self.cfg.training.output_dir, exist_ok=True)
+        with open(os.path.join(self.cfg.training.output_dir, f"cprofile_rank_{self.rank}.txt"), "w") as fh:
+            fh.write(buf.getvalue())
 
     def _profiler(self):
         """``DEBUG=1``: torch profiler (wait 10, warm-up 2, active 2) writing a chrome trace and a
@@ -331,8 +448,15 @@ class Trainer:
 
     def end_run(self):
         self.loader.close()
-        if self.wandb is not None:
-            self.wandb.finish()
+        if self._cprofile is not None:  # the run ended inside the window
+            self._dump_cprofile()
+        try:
+            m = self.flush_metrics()  # also checks the device status word of the last step
+            if m is not None:
+                self._flushed.append(m)
+        finally:
+            if self.wandb is not None:
+                self.wandb.finish()
         if self.device.type == "cuda":
             from ..ops import cuda as cu
 
@@ -347,6 +471,7 @@ class _Null:
         return False
 
 
+@record
 def main(argv=None):
     import sys
 
