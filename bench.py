@@ -110,9 +110,10 @@ def build_config(args, world: int):
     t.total_steps, t.warmup_steps, t.save_steps = 10 ** 9, 50, 0
     t.ce_chunk_size = args.ce_chunk
     t.ac_mode = args.ac if args.ac != "auto" else "off"
-    # one GPU holds the whole 8.8 B-parameter model: bf16 Adam moments (fp32 master weights kept) leave room
-    # for the decoder's activations without recomputation; with >= 2 GPUs the state is sharded and stays fp32
-    t.optimizer_state_dtype = args.opt_state if args.opt_state != "auto" else ("bf16" if world == 1 else "fp32")
+    # bf16 Adam moments (fp32 master weights kept) at every N: on one GPU they leave room for the decoder's activations
+    # of the whole 8.8 B-parameter model without recomputation, and the optimizer pass moves 20 instead of 28 bytes per
+    # parameter; the same precision at every N keeps the scaling curve a like-for-like comparison
+    t.optimizer_state_dtype = args.opt_state if args.opt_state != "auto" else "bf16"
     t.fused_comm = os.environ.get("VLMT_FUSED_COMM", "1") == "1"
     t.output_dir = "/tmp/vlmt_bench"
     cfg.data.synthetic = "vlm" if "vl" in args.model else "text-loguniform"
@@ -197,8 +198,16 @@ def run_ours(args):
             torch.cuda.synchronize()
         if rank == 0:
             os.makedirs(os.path.dirname(os.path.abspath(args.profile)), exist_ok=True)
+            from torch.autograd import DeviceType
+
+            rows = [e for e in prof.key_averages() if e.device_type == DeviceType.CUDA]
+            rows.sort(key=lambda e: -e.self_device_time_total)
+            total = sum(e.self_device_time_total for e in rows)
             with open(args.profile, "w") as fh:
-                fh.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=60, max_name_column_width=90))
+                fh.write(f"kernels of one optimizer step, {world} GPU(s), rank 0: {total / 1e3:.1f} ms of device time\n")
+                fh.write(f"{'ms':>9} {'share':>7} {'calls':>6}  kernel\n")
+                for e in rows[:100]:
+                    fh.write(f"{e.self_device_time_total / 1e3:9.3f} {100 * e.self_device_time_total / max(total, 1):6.2f}% {e.count:6d}  {e.key[:150]}\n")
     torch.cuda.reset_peak_memory_stats()
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     if rank == 0:

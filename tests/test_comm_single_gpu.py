@@ -75,7 +75,7 @@ def test_fused_optimizer_kernel_skips_after_a_failed_wait(short_waits):
     p = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
     master, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
     flags = torch.zeros(8, dtype=torch.int32, device="cuda")
-    args = ([g.data_ptr()], [p.data_ptr()], 0, 0, 1, 0, n, master, m, v, 0, 1e-2, 0.9, 0.999, 1e-8, 0.0, 0.1, 0.001, 1.0)
+    args = ([g.data_ptr()], [p.data_ptr()], 0, 0, 1, 0, n, master, m, v, 0, 1e-2, 0.9, 0.999, 1e-8, 0.0, 0.1, 0.001, 1.0, False)
     cu._C.wait_flags(flags.data_ptr(), 0, 2, 1, 0)
     cu._C.fused_rs_adamw_ag(*args)
     torch.cuda.synchronize()
@@ -84,6 +84,35 @@ def test_fused_optimizer_kernel_skips_after_a_failed_wait(short_waits):
     cu._C.fused_rs_adamw_ag(*args)                        # status clear: the update happens
     torch.cuda.synchronize()
     assert float(m.min()) > 0.0 and float(master.max()) < 0.0
+
+
+@pytest.mark.parametrize("state_dtype", [torch.float32, torch.bfloat16])
+def test_fused_optimizer_kernel_one_rank_matches_adamw(short_waits, state_dtype):
+    """The one-kernel optimizer step on a domain of one rank (no peers): fp32 and bf16 moments against the plain AdamW
+    kernel, and the gradients it consumed are cleared."""
+    cu = short_waits
+    n = 8 * 4096
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    g = torch.randn(n, device="cuda", generator=gen).bfloat16()
+    w0 = torch.randn(n, device="cuda", generator=gen)
+    state = lambda: (w0.clone(), torch.zeros(n, device="cuda", dtype=state_dtype), torch.zeros(n, device="cuda", dtype=state_dtype))
+    m1, a1, b1 = state()
+    m2, a2, b2 = state()
+    p1, p2 = torch.zeros(n, dtype=torch.bfloat16, device="cuda"), torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    g1, g2 = g.clone(), g.clone()
+    for step in (1, 2):
+        bc1, bc2 = 1 - 0.9 ** step, 1 - 0.999 ** step
+        cu._C.fused_rs_adamw_ag([g1.data_ptr()], [p1.data_ptr()], 0, 0, 1, 0, n, m1, a1, b1, 0, 1e-2, 0.9, 0.999, 1e-8, 0.01, bc1, bc2,
+                                0.5, True)
+        cu.adamw_step_(g2, m2, a2, b2, p2, 1e-2, 0.9, 0.999, 1e-8, 0.01, step, 0.5, zero_grad=True)
+        torch.cuda.synchronize()
+        assert float(g1.float().abs().sum()) == 0.0       # consumed gradients are cleared
+        torch.testing.assert_close(m1, m2, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(a1.float(), a2.float(), rtol=1e-2, atol=1e-6)
+        assert torch.equal(p1, m1.bfloat16())
+        g1.copy_(g)
+        g2.copy_(g)
+    assert cu.check_status() == 0
 
 
 @pytest.mark.parametrize("rank", [0, 1])

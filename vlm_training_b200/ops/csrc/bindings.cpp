@@ -452,6 +452,12 @@ void bind_comm(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("memset_zero_", [](Tensor& t) {
+    TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "memset_zero_: a contiguous CUDA tensor is required");
+    c10::cuda::CUDAGuard guard(t.device());
+    cudaError_t e = cudaMemsetAsync(t.data_ptr(), 0, (size_t)t.numel() * t.element_size(), cur_stream());
+    TORCH_CHECK(e == cudaSuccess, "cudaMemsetAsync failed: ", cudaGetErrorString(e));
+  });
   m.def("gemm_rs_push", &gemm_rs_push);
   m.def("gemm_ag", &gemm_ag);
   m.def("gemm_set_flag_wait_ms", [](int64_t ms) {

@@ -9,22 +9,27 @@ using torch::Tensor;
 
 Tensor vlmt_status_tensor();
 
-// state tensors are the local shard (fp32); `state_off` is the element offset of `lo` inside them
+// state tensors are the local shard (master fp32; moments fp32 or bf16); `state_off` is the element offset of `lo` inside them
 static void fused_rs_adamw_ag(const std::vector<int64_t>& grad_ptrs, const std::vector<int64_t>& param_ptrs, int64_t grad_mc,
                               int64_t param_mc, int64_t world, int64_t lo, int64_t hi, Tensor& master, Tensor& m, Tensor& v,
                               int64_t state_off, double lr, double b1, double b2, double eps, double wd, double bc1, double bc2,
-                              double grad_scale) {
+                              double grad_scale, bool zero_own) {
   TORCH_CHECK((int64_t)grad_ptrs.size() == world && (int64_t)param_ptrs.size() == world);
-  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(master.scalar_type() == at::kFloat, "master weights must be float32");
+  TORCH_CHECK(m.scalar_type() == v.scalar_type() && (m.scalar_type() == at::kFloat || m.scalar_type() == at::kBFloat16),
+              "Adam moments must both be float32 or both bfloat16");
   TORCH_CHECK(lo % 8 == 0 && hi % 8 == 0 && state_off % 8 == 0, "shard segment must be 16-byte aligned");
   c10::cuda::CUDAGuard guard(master.device());
   void* g[16];
   void* p[16];
   TORCH_CHECK(world <= 16);
   for (int i = 0; i < world; ++i) { g[i] = reinterpret_cast<void*>(grad_ptrs[i]); p[i] = reinterpret_cast<void*>(param_ptrs[i]); }
+  const bool sb = m.scalar_type() == at::kBFloat16;
+  const int64_t esz = sb ? 2 : 4;
   int r = vlmt_fused_rs_adamw_ag(g, p, reinterpret_cast<void*>(grad_mc), reinterpret_cast<void*>(param_mc), (int)world, lo, hi,
-                                 master.data_ptr<float>() + state_off, m.data_ptr<float>() + state_off, v.data_ptr<float>() + state_off,
-                                 (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, (float)bc1, (float)bc2, (float)grad_scale,
+                                 master.data_ptr<float>() + state_off, static_cast<char*>(m.data_ptr()) + state_off * esz,
+                                 static_cast<char*>(v.data_ptr()) + state_off * esz, sb ? 1 : 0, (float)lr, (float)b1, (float)b2,
+                                 (float)eps, (float)wd, (float)bc1, (float)bc2, (float)grad_scale, zero_own ? 1 : 0,
                                  vlmt_status_tensor().data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(r == 0, "vlmt_fused_rs_adamw_ag failed with code ", r);
 }

@@ -63,11 +63,25 @@ struct AdamArgs {
   float lr, b1, b2, eps, wd, bc1, bc2, grad_scale;
 };
 
-// elements [lo, hi) of the bucket-relative flat buffers; lo, hi multiples of 8
-template <bool MULTIMEM>
+// 8 consecutive Adam moments, stored as fp32 or bf16
+__device__ __forceinline__ void load_state8(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void load_state8(const bf16* p, float (&f)[8]) { unpack8(*reinterpret_cast<const uint4*>(p), f); }
+__device__ __forceinline__ void store_state8(float* p, const float (&f)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+__device__ __forceinline__ void store_state8(bf16* p, const float (&f)[8]) { *reinterpret_cast<uint4*>(p) = pack8(f); }
+
+// elements [lo, hi) of the bucket-relative flat buffers; lo, hi multiples of 8.  ST: storage type of the Adam moments
+// (fp32, or bf16 to save 4 bytes per parameter; master weights are fp32 either way).  zero_own: also clear this rank's
+// copy of the gradients it consumed (world 1: every gradient, so the next step needs no separate clearing pass).
+template <bool MULTIMEM, typename ST>
 __global__ void fused_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, void* grad_mc, void* param_mc, int world, long lo, long hi,
-                                         float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, AdamArgs a,
-                                         const int* __restrict__ status) {
+                                         float* __restrict__ master, ST* __restrict__ m, ST* __restrict__ v, AdamArgs a,
+                                         const int* __restrict__ status, int zero_own) {
   if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;  // an earlier wait gave up
   const long nvec = (hi - lo) >> 3;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
@@ -84,18 +98,13 @@ __global__ void fused_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, void* 
 #pragma unroll
         for (int k = 0; k < 8; ++k) g[k] += t[k];
       }
+      if (zero_own && world == 1) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(grads.p[0]) + e) = make_uint4(0u, 0u, 0u, 0u);
     }
     const long s = i << 3;  // offset into the local shard state
     float pm[8], mm[8], vv[8];
-    {
-      const float4* p4 = reinterpret_cast<const float4*>(master + s);
-      const float4* m4 = reinterpret_cast<const float4*>(m + s);
-      const float4* v4 = reinterpret_cast<const float4*>(v + s);
-      float4 x0 = p4[0], x1 = p4[1], y0 = m4[0], y1 = m4[1], z0 = v4[0], z1 = v4[1];
-      pm[0] = x0.x; pm[1] = x0.y; pm[2] = x0.z; pm[3] = x0.w; pm[4] = x1.x; pm[5] = x1.y; pm[6] = x1.z; pm[7] = x1.w;
-      mm[0] = y0.x; mm[1] = y0.y; mm[2] = y0.z; mm[3] = y0.w; mm[4] = y1.x; mm[5] = y1.y; mm[6] = y1.z; mm[7] = y1.w;
-      vv[0] = z0.x; vv[1] = z0.y; vv[2] = z0.z; vv[3] = z0.w; vv[4] = z1.x; vv[5] = z1.y; vv[6] = z1.z; vv[7] = z1.w;
-    }
+    load_state8(master + s, pm);
+    load_state8(m + s, mm);
+    load_state8(v + s, vv);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const float gk = g[k] * a.grad_scale;
@@ -105,14 +114,9 @@ __global__ void fused_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, void* 
       p -= a.lr * (mm[k] / a.bc1) / (sqrtf(vv[k] / a.bc2) + a.eps);
       pm[k] = p;
     }
-    {
-      float4* p4 = reinterpret_cast<float4*>(master + s);
-      float4* m4 = reinterpret_cast<float4*>(m + s);
-      float4* v4 = reinterpret_cast<float4*>(v + s);
-      p4[0] = make_float4(pm[0], pm[1], pm[2], pm[3]); p4[1] = make_float4(pm[4], pm[5], pm[6], pm[7]);
-      m4[0] = make_float4(mm[0], mm[1], mm[2], mm[3]); m4[1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
-      v4[0] = make_float4(vv[0], vv[1], vv[2], vv[3]); v4[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
-    }
+    store_state8(master + s, pm);
+    store_state8(m + s, mm);
+    store_state8(v + s, vv);
     const uint4 packed = pack8(pm);
     if (MULTIMEM) {
       multimem_st_16B(reinterpret_cast<bf16*>(param_mc) + e, packed);
@@ -291,8 +295,8 @@ int vlmt_pull_reduce(void* const* slot_ptrs, void* out, const void* residual, lo
   return (int)cudaGetLastError();
 }
 int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* grad_mc, void* param_mc, int world, long lo, long hi,
-                           float* master, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                           float grad_scale, const int* status, cudaStream_t st) {
+                           float* master, void* m, void* v, int state_bf16, float lr, float b1, float b2, float eps, float wd, float bc1,
+                           float bc2, float grad_scale, int zero_own, const int* status, cudaStream_t st) {
   if (world > MAX_PEERS) return -1;
   if ((lo & 7) || (hi & 7)) return -2;
   if (hi <= lo) return 0;
@@ -301,10 +305,13 @@ int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void
   AdamArgs a{lr, b1, b2, eps, wd, bc1, bc2, grad_scale};
   long blocks = (((hi - lo) >> 3) + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  if (grad_mc && param_mc)
-    fused_rs_adamw_ag_kernel<true><<<(int)blocks, 256, 0, st>>>(g, p, grad_mc, param_mc, world, lo, hi, master, m, v, a, status);
-  else
-    fused_rs_adamw_ag_kernel<false><<<(int)blocks, 256, 0, st>>>(g, p, nullptr, nullptr, world, lo, hi, master, m, v, a, status);
+  const bool mc = grad_mc && param_mc;
+#define LAUNCH(MC, ST)                                                                                                          \
+  fused_rs_adamw_ag_kernel<MC, ST><<<(int)blocks, 256, 0, st>>>(g, p, mc ? grad_mc : nullptr, mc ? param_mc : nullptr, world, lo, hi, \
+                                                                master, reinterpret_cast<ST*>(m), reinterpret_cast<ST*>(v), a, status, zero_own)
+  if (state_bf16) { if (mc) LAUNCH(true, bf16); else LAUNCH(false, bf16); }
+  else { if (mc) LAUNCH(true, float); else LAUNCH(false, float); }
+#undef LAUNCH
   return (int)cudaGetLastError();
 }
 int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st) {

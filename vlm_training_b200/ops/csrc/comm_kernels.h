@@ -10,9 +10,11 @@ extern "C" {
 // [lo, hi): this rank's shard in elements relative to the bucket start, multiples of 8.
 // status: the device status word (or null); when it is non-zero at kernel start (a bounded wait ran out earlier, e.g. the
 // wait for this bucket's "gradients final" flags) the kernel returns without reading or writing anything.
+// m, v: the Adam moments of the shard, fp32 or (state_bf16 != 0) bf16; master: fp32.
+// zero_own: with world == 1, clear the gradients after they have been consumed.
 int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* grad_mc, void* param_mc, int world, long lo, long hi,
-                           float* master, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                           float grad_scale, const int* status, cudaStream_t st);
+                           float* master, void* m, void* v, int state_bf16, float lr, float b1, float b2, float eps, float wd, float bc1,
+                           float bc2, float grad_scale, int zero_own, const int* status, cudaStream_t st);
 // out[rows, D] = residual + sum over ranks of partial_r[row0 : row0 + rows, :]
 int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st);
 // Signalled peer-to-peer collectives over symmetric staging slots (protocol: comm_kernels.cu).

@@ -776,6 +776,11 @@ def adamw_step_(grad, master, exp_avg, exp_avg_sq, param, lr, beta1, beta2, eps,
     _tick()
 
 
+def memset_zero_(t):
+    """Clear a contiguous tensor with the driver's memset on the current stream (write-only, at memory speed)."""
+    _C.memset_zero_(t)
+
+
 def sumsq_(x, out):
     _C.sumsq_(x, out)
     _tick()

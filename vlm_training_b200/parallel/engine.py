@@ -192,8 +192,8 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         reason = ""
         if fused_comm and self.is_cuda and dist.is_initialized():
             # decided before the buffers are allocated: the one-kernel path needs them in symmetric memory
-            if state_dtype != torch.float32:
-                fused_comm, reason = False, f"the fused kernel keeps fp32 Adam moments, optimizer_state_dtype is {state_dtype}"
+            if state_dtype not in (torch.float32, torch.bfloat16):
+                fused_comm, reason = False, f"the fused kernel keeps fp32 or bf16 Adam moments, optimizer_state_dtype is {state_dtype}"
             elif max_grad_norm is not None:
                 fused_comm, reason = False, "gradient clipping needs the global norm before the first update"
         symmetric = fused_comm and self.is_cuda and dist.is_initialized()
@@ -248,6 +248,10 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         for d in self.domains:
             if getattr(d, "grads_clean", False):
                 d.grads_clean = False  # the AdamW kernel of the last step() cleared every gradient it consumed
+            elif self.is_cuda:
+                from ..ops import cuda as cu
+
+                cu.memset_zero_(d.flat_grad)
             else:
                 d.flat_grad.zero_()
             for b in d.buckets:
