@@ -9,8 +9,10 @@ Layout and contents follow the reference trainer (reference: train/train_qwen.py
 * ``model`` tensors are saved as GLOBAL tensors: tensor-parallel shards are gathered at
   save time and re-split at load time, so a checkpoint loads under any (dp, tp).
 * ``optimizer`` holds the sharded fp32 master weights and Adam moments, one DTensor per
-  bucket (``Shard(0)`` over the reduction group), so DCP re-shards them when the
-  data-parallel size changes.
+  bucket (``Shard(0)`` over the reduction group).  ``optimizer_layout.json`` beside them
+  records where every parameter's state sits; a run with the same layout loads the shards
+  in place, a run with another ``tp_size`` / ``ep_size`` / data-parallel size / bucket size
+  re-assembles the state parameter by parameter (:mod:`.opt_reshard`).
 * Unlike the reference, a failed save or load raises instead of being logged and ignored.
 """
 from __future__ import annotations
@@ -194,7 +196,8 @@ def load_optimizer_state_from_dcp(engine, state: dict, tp_rank: int = 0):
     engine.step_count = int(state["step"])
     for pg, saved in zip(engine.param_groups, state["param_groups"]):
         pg.update({k: v for k, v in saved.items() if k in ("lr", "initial_lr", "weight_decay")})
-    # tensors were loaded in place by DCP (the DTensors wrap the engine's own buffers)
+    # tensors were loaded in place (by DCP through the DTensors that wrap the engine's own buffers, or by the
+    # resharding loader); the bf16 parameters follow the master copy
     with torch.no_grad():
         for d in engine.domains:
             for bi, b in enumerate(d.buckets):
@@ -221,6 +224,10 @@ def save_checkpoint(output_dir: str, step: int, model, engine, scheduler, counte
         os.makedirs(path, exist_ok=True)
     if dist.is_initialized():
         dist.barrier()
+    from . import opt_reshard
+
+    tp = getattr(model, "tp", None)
+    opt_reshard.write_layout(path, engine, tp.size if (tp is not None and tp.enabled) else 1)
     dcp.save(state, checkpoint_id=path, no_dist=not dist.is_initialized())
     logger.info(f"saved checkpoint {path}")
     return path
@@ -234,17 +241,30 @@ def load_checkpoint(output_dir: str, step: int, model, engine, scheduler, tp_ran
         raise FileNotFoundError(f"no complete checkpoint at {path}")
     if dist.is_initialized():
         dist.barrier()
+    from . import opt_reshard
+
     shapes = _global_shapes(model)
     dev = next(model.parameters()).device
     model_buf = {k: torch.empty(shape, dtype=dt, device=dev) for k, (shape, dt) in shapes.items()}
+    tp = getattr(model, "tp", None)
+    saved_layout = opt_reshard.read_layout(path)
+    here = opt_reshard.describe_layout(engine, tp.size if (tp is not None and tp.enabled) else 1)
+    in_place = saved_layout is None or opt_reshard.same_layout(saved_layout, here)
+    opt_state = optimizer_state_for_dcp(engine, tp_rank)
+    if not in_place:
+        # another parallel layout wrote this checkpoint: only the scalars load directly, the tensors are re-assembled
+        opt_state = {"step": opt_state["step"], "param_groups": opt_state["param_groups"]}
     state = {
         "model": model_buf,
-        "optimizer": optimizer_state_for_dcp(engine, tp_rank),
+        "optimizer": opt_state,
         "scheduler": {k: v for k, v in scheduler.state_dict().items() if k != "lr_lambdas"} if scheduler is not None else {},
         "step": 0, "tokens_seen": 0, "tokens_seen_assistant": 0,
     }
     dcp.load(state, checkpoint_id=path, no_dist=not dist.is_initialized())
     load_model_state(model, state["model"])
+    if not in_place:
+        logger.info("the checkpoint was written under another parallel layout: re-assembling the optimizer state per parameter")
+        opt_reshard.load_resharded(path, engine, saved_layout, tp)
     load_optimizer_state_from_dcp(engine, state["optimizer"], tp_rank)
     if scheduler is not None and state["scheduler"]:
         sd = scheduler.state_dict()
