@@ -162,3 +162,50 @@ def test_dcp_to_hf_conversion_roundtrip(tmp_path):
             torch.testing.assert_close(v, want[k])
     finally:
         mc._PRESETS["tiny-qwen3"] = orig
+
+
+def test_energon_items_are_normalised_cooked_and_sharded(monkeypatch):
+    """The energon path end to end on our side, with a stand-in for the (not installed) package: items arrive as batches
+    of one with raw bytes, leave as cooked ``{"image", "messages"}`` samples; rank and worker count reach the loader."""
+    import io
+    import json as _json
+    import sys
+    import types
+
+    from PIL import Image
+
+    from vlm_training_b200.config import Config
+    from vlm_training_b200.data import task_encoders as te
+
+    buf = io.BytesIO()
+    Image.new("RGB", (8, 8), (255, 0, 0)).save(buf, format="PNG")
+    crude = [[{"__key__": f"s{i}", "jpg": buf.getvalue(),
+               "json": _json.dumps({"conversations": [{"from": "human", "value": "<image>\nwhat?"}, {"from": "gpt", "value": f"red {i}"}]}).encode()}]
+             for i in range(3)]
+    seen = {}
+    fake = types.ModuleType("megatron.energon")
+
+    class WorkerConfig:
+        def __init__(self, rank, world_size, num_workers):
+            seen.update(rank=rank, world=world_size, workers=num_workers)
+
+    fake.WorkerConfig = WorkerConfig
+    fake.get_train_dataset = lambda path, **kw: ("dataset", path, kw)
+    fake.get_loader = lambda ds: iter(crude)
+    monkeypatch.setitem(sys.modules, "megatron", types.ModuleType("megatron"))
+    monkeypatch.setitem(sys.modules, "megatron.energon", fake)
+    d = Config().data
+    d.num_workers = 3
+    out = list(te._energon_samples("/data/x", d, rank=1, world=4))
+    assert seen == {"rank": 1, "world": 4, "workers": 3}
+    assert len(out) == 3 and all(set(o) >= {"image", "messages"} for o in out)
+    assert out[0]["image"].size == (8, 8)
+    assert [m["role"] for m in out[2]["messages"]] == ["user", "assistant"]
+    assert out[2]["messages"][0]["content"][0] == {"type": "image"}
+    assert out[2]["messages"][1]["content"][0]["text"] == "red 2"
+    # captions: the cooker follows the sample's fields
+    assert te.pick_cooker({"jpg": None, "txt": "a cat"}) is te.cookers.cook_llava_imagenet
+    import pytest as _pytest
+
+    with _pytest.raises(KeyError):
+        te.pick_cooker({"jpg": None})

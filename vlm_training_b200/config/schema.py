@@ -132,6 +132,8 @@ class DataSection:
     doc_len_min: int = 128
     doc_len_max: int = 8192
     num_workers: int = 2
+    # cooker for crude webdataset samples: "auto" (from the sample's fields) or a name of data.cookers.COOKERS
+    cooker: str = "auto"
 
 
 @dataclass

@@ -5,9 +5,10 @@ Three encoders, selected as in the reference factory (reference: data/task_encod
 number of samples per row); ``batch_size == 0`` → :class:`PackedBatchEncoder` (online packing of a
 buffer of ``packing_buffer_size`` samples).  The encoders are plain Python: ``encode_sample`` works
 on one cooked sample, ``rows(iterable)`` yields batches.  When ``megatron.energon`` is importable,
-``build_dataset`` reads ``data.data_path`` through it (crude webdatasets, rank-sharded); otherwise
-it accepts a ``.jsonl`` / ``.txt`` file of documents for text training and raises a clear error for
-multimodal paths.
+``build_dataset`` reads ``data.data_path`` through it (crude webdatasets, rank-sharded, energon's worker
+processes; every item is normalised, cooked by the cooker that ``data.cooker`` names or the sample's fields
+imply, and then encoded); otherwise it accepts a ``.jsonl`` / ``.txt`` file of documents for text training
+and raises a clear error for multimodal paths.
 """
 from __future__ import annotations
 
@@ -147,14 +148,72 @@ def _read_text_file(path: str, rank: int, world: int):
             yield json.loads(line) if path.endswith(".jsonl") else {"text": line}
 
 
+def pick_cooker(sample: dict, name: str = "auto"):
+    """The cooker for a crude sample: by name (``data.cooker``), or from the sample's fields: ``json`` with a
+    ``conversations`` list → the conversation cooker, ``txt`` → image + caption."""
+    if name != "auto":
+        return cookers.COOKERS[name]
+    js = sample.get("json")
+    if isinstance(js, (bytes, str)):
+        js = json.loads(js)
+    if isinstance(js, dict) and "conversations" in js:
+        return cookers.cook_conversation
+    if "txt" in sample:
+        return cookers.cook_llava_imagenet
+    raise KeyError(f"cannot choose a cooker for a sample with fields {sorted(sample)}; set data.cooker")
+
+
+def normalise_crude(item) -> dict:
+    """One loader item → a plain crude-sample dict: unwraps the batch of one that ``batch_size=1`` produces, turns
+    sample objects into dicts, decodes ``json`` / ``txt`` bytes and opens ``jpg`` / ``png`` bytes with PIL (decoding
+    here, not in the HF processor, keeps the pixel scaling single as in the reference, data/energon_dataloader.py:242-247)."""
+    if isinstance(item, (list, tuple)) and len(item) == 1:
+        item = item[0]
+    if not isinstance(item, dict):
+        item = {k: getattr(item, k) for k in dir(item) if not k.startswith("_") and not callable(getattr(item, k))}
+    out = dict(item)
+    for k in ("json", "txt"):
+        v = out.get(k)
+        if isinstance(v, bytes):
+            v = v.decode("utf-8")
+        if k == "json" and isinstance(v, str):
+            v = json.loads(v)
+        if v is not None:
+            out[k] = v
+    for k in ("jpg", "jpeg", "png"):
+        v = out.get(k)
+        if isinstance(v, bytes):
+            import io
+
+            from PIL import Image
+
+            v = Image.open(io.BytesIO(v)).convert("RGB")
+        if v is not None:
+            out["jpg"] = v
+    return out
+
+
 def _energon_samples(path: str, data_args, rank: int, world: int):
+    """Cooked samples from an energon (crude webdataset) path, sharded over the data-parallel ranks; energon's own
+    loader runs ``data.num_workers`` worker processes (reference: train/train_qwen.py:227-250).  Text datasets pass
+    through uncooked."""
     from megatron.energon import WorkerConfig, get_loader, get_train_dataset  # optional dependency
 
     wc = WorkerConfig(rank=rank, world_size=world, num_workers=data_args.num_workers)
     ds = get_train_dataset(path, batch_size=1, shuffle_buffer_size=data_args.shuffle_buffer_size,
                            max_samples_per_sequence=data_args.max_samples_per_sequence, worker_config=wc, repeat=False)
+    cooker = None
     for item in get_loader(ds):
-        yield item
+        if data_args.text_dataset:
+            yield item[0] if isinstance(item, (list, tuple)) and len(item) == 1 else item
+            continue
+        crude = normalise_crude(item)
+        if "messages" in crude:
+            yield crude
+            continue
+        if cooker is None:
+            cooker = pick_cooker(crude, getattr(data_args, "cooker", "auto"))
+        yield cooker(crude)
 
 
 def build_dataset(data_args, training_args, cfg: ModelConfig, dp_rank: int, dp_size: int):
