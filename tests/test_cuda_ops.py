@@ -493,6 +493,55 @@ def test_moe_experts_grouped_gemm(T, H, I, E, k):
     assert float(gate_up.grad[E - 1].abs().max()) == 0.0 and float(down.grad[E - 2].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("T,E,k,renorm,dtype", [(777, 256, 8, True, torch.float32), (300, 256, 8, False, torch.bfloat16),
+                                                 (64, 8, 2, True, torch.bfloat16), (1000, 100, 4, True, torch.float32)])
+def test_moe_router_kernel(T, E, k, renorm, dtype):
+    """softmax -> top-k -> renormalise in one kernel against the tensor-operation statement, forward and backward."""
+    _cu()
+    torch.manual_seed(1)
+    logits = (torch.randn(T, E, device=DEV) * 2).to(dtype).requires_grad_()
+    w, idx = ops.moe_router(logits, k, renorm)
+    lr = logits.detach().float().requires_grad_()
+    wr, idxr = ref.moe_router(lr, k, renorm)
+    assert idx.dtype == torch.int64 and w.dtype == torch.float32
+    # the same experts (as sets: equal probabilities may be ordered differently) with the same weights
+    assert torch.equal(idx.sort(-1).values, idxr.sort(-1).values)
+    _close(w.gather(1, idx.argsort(-1)), wr.gather(1, idxr.argsort(-1)), 1e-5, 1e-4, "weights")
+    g = torch.randn(T, k, device=DEV)
+    (w.gather(1, idx.argsort(-1)) * g).sum().backward()
+    (wr.gather(1, idxr.argsort(-1)) * g).sum().backward()
+    _close(logits.grad, lr.grad, 2e-3 if dtype == torch.bfloat16 else 1e-5, 2e-2 if dtype == torch.bfloat16 else 1e-3, "dlogits")
+
+
+def test_moe_plan_is_a_stable_sort_by_expert():
+    """Every slot gets the row that a stable sort by expert gives it inside its expert's 128-row tiles; rows that hold no
+    slot are marked -1; run twice: identical placement."""
+    cu = _cu()
+    torch.manual_seed(2)
+    T, k, E = 5000, 8, 256
+    experts = torch.randint(0, E, (T, k), device=DEV)
+    experts[experts == 7] = 8                                   # one empty expert
+    from vlm_training_b200.ops.moe_cuda import MoePlan
+
+    a, b = MoePlan(experts, E, k), MoePlan(experts, E, k)
+    assert torch.equal(a.dest, b.dest) and torch.equal(a.slot_of_row, b.slot_of_row)
+    flat = experts.reshape(-1)
+    counts = torch.bincount(flat, minlength=E)
+    assert torch.equal(a.counts.long(), counts)
+    tiles = (counts + 127) // 128
+    prefix = torch.cat((tiles.new_zeros(1), tiles.cumsum(0)))
+    assert torch.equal(a.prefix.long(), prefix)
+    order = torch.argsort(flat, stable=True)
+    start = counts.cumsum(0) - counts
+    e_sorted = flat[order]
+    want = torch.empty_like(flat)
+    want[order] = prefix[:-1][e_sorted] * 128 + (torch.arange(flat.numel(), device=DEV) - start[e_sorted])
+    assert torch.equal(a.dest.long(), want)
+    rows = a.slot_of_row.long()
+    assert torch.equal(rows[want], torch.arange(flat.numel(), device=DEV)) and int((rows >= 0).sum()) == flat.numel()
+    cu.check_status()
+
+
 @pytest.mark.parametrize("reverse,head_major", [(False, False), (True, False), (False, True), (True, True)])
 def test_gdn_scan_kernel_matches_loop(reverse, head_major):
     """The tcgen05 scan kernel against the same recurrence as a loop of fp32 tensor operations on the same bf16 inputs."""

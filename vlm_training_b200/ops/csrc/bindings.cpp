@@ -449,6 +449,7 @@ torch::Tensor vlmt_status_tensor() { return status_tensor(); }
 
 void bind_attention(pybind11::module_& m);
 void bind_comm(pybind11::module_& m);
+void bind_moe(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
@@ -494,4 +495,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("status", &status);
   bind_attention(m);
   bind_comm(m);
+  bind_moe(m);
 }

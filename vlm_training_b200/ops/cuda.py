@@ -723,7 +723,9 @@ def gated_delta_rule(q, k, v, g, beta, cu_seqlens, scale=None, chunk=64, cu_host
 
 # ------------------------------------------------------------------------------- MoE
 def moe_router(logits, top_k, renorm=True):
-    return ref.moe_router(logits, top_k, renorm)
+    from .moe_cuda import moe_router_cuda
+
+    return moe_router_cuda(logits, top_k, renorm)
 
 
 def moe_experts(x, gate_up, down, weights, experts):
