@@ -141,3 +141,63 @@ def test_fused_gemm_collectives_match_torch(tmp_path):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("PRIMITIVES OK") == 2, res.stdout[-2000:]
+
+
+EP_FUSED = r"""
+import os, sys
+sys.path.insert(0, {root!r})
+import torch
+import torch.distributed as dist
+from vlm_training_b200 import ops
+from vlm_training_b200.parallel.mesh import init_distributed
+from vlm_training_b200.parallel.ep import EPContext, EPFused, ep_moe_experts
+from vlm_training_b200.ops import cuda as cu
+
+rank, world, dev = init_distributed("nccl", "cuda")
+E, H, I, k, T = 16, 256, 128, 4, 1000
+torch.manual_seed(0)
+gate_up = (torch.randn(E, 2 * I, H, device=dev) * 0.05).bfloat16()
+down = (torch.randn(E, H, I, device=dev) * 0.05).bfloat16()
+El = E // world
+ep_nccl = EPContext(group=dist.group.WORLD, size=world, rank=rank, n_experts=E)
+ep_fused = EPContext(group=dist.group.WORLD, size=world, rank=rank, n_experts=E)
+ep_fused.fused = EPFused(ep_fused, dev)
+for it in range(3):                       # several layers' worth of exchanges through the same buffers
+    torch.manual_seed(100 + rank + 10 * it)
+    x = torch.randn(T, H, device=dev).bfloat16()
+    logits = torch.randn(T, E, device=dev)
+    if rank == 1:
+        logits[:, :4] += 2.0              # unbalanced: most of rank 1's tokens go to rank 0's experts
+    logits[:, E - 1] = -1e9               # one expert without tokens
+    w, idx = ops.moe_router(logits, k, True)
+    g = torch.randn(T, H, device=dev).bfloat16()
+    res = []
+    for ep in (ep_nccl, ep_fused):
+        xi = x.clone().requires_grad_()
+        wi = w.clone().requires_grad_()
+        gu = gate_up[rank * El:(rank + 1) * El].clone().requires_grad_()
+        dn = down[rank * El:(rank + 1) * El].clone().requires_grad_()
+        out = ep_moe_experts(xi, gu, dn, wi, idx, ep)
+        out.backward(g)
+        torch.cuda.synchronize()
+        res.append((out.detach().float(), xi.grad.float(), wi.grad.float(), gu.grad.float(), dn.grad.float()))
+    for name, a, b in zip(("out", "dx", "dw_routing", "dgate_up", "ddown"), *res):
+        err = ((a - b).abs().max() / (a.abs().max() + 1e-6)).item()
+        assert err < 3e-2, f"{{name}}: relative error {{err}} (iteration {{it}})"
+cu.check_status()
+print(f"rank {{rank}} EP FUSED OK", flush=True)
+dist.destroy_process_group()
+"""
+
+
+def test_expert_parallel_peer_store_transport_matches_all_to_all(tmp_path):
+    """Expert parallelism on 2 GPUs: dispatch / return by peer stores (device-built plan over all ranks' counts, no host
+    read) against the all-to-all transport: outputs and every gradient."""
+    script = tmp_path / "ep_fused.py"
+    script.write_text(EP_FUSED.format(root=ROOT))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29712", str(script)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", VLMT_NO_MULTIMEM="1", VLMT_PG_TIMEOUT_S="120", VLMT_FLAG_WAIT_MS="5000")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count("EP FUSED OK") == 2, res.stdout[-2000:]

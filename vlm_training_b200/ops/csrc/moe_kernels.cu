@@ -186,10 +186,14 @@ __global__ void moe_plan_scan_kernel(int* __restrict__ hist, int n_blocks, int E
 
 // Pass 3: destination row of every slot = first row of its expert + slots of the same expert in earlier blocks + its
 // stable rank inside the block (warps take turns in slot order; inside a warp the rank comes from match_any).
+// row_base (optional): first row per expert given by the caller (expert parallelism: a row of the OWNER's buffer) instead of
+// prefix[e] * 128.  Rows at or beyond cap_rows are not placed (dest = -1).  slot_of_row may be null.
 __global__ void moe_plan_place_kernel(const int* __restrict__ experts, long n_slots, int E, const int* __restrict__ hist,
-                                      const int* __restrict__ prefix, int* __restrict__ dest, int* __restrict__ slot_of_row) {
+                                      const int* __restrict__ prefix, const int* __restrict__ row_base, long cap_rows,
+                                      int* __restrict__ dest, int* __restrict__ slot_of_row) {
   extern __shared__ int cursor[];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) cursor[e] = prefix[e] * TILE + hist[(size_t)blockIdx.x * E + e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    cursor[e] = (row_base ? row_base[e] : prefix[e] * TILE) + hist[(size_t)blockIdx.x * E + e];
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const long lo = (long)blockIdx.x * PLAN_CHUNK, hi = min(n_slots, lo + PLAN_CHUNK);
@@ -203,8 +207,9 @@ __global__ void moe_plan_place_kernel(const int* __restrict__ experts, long n_sl
         const int rank = __popc(same & ((1u << lane) - 1u));
         if (live) {
           const int row = cursor[e] + rank;
-          dest[s] = row;
-          slot_of_row[row] = (int)s;
+          const bool fits = row < cap_rows;
+          dest[s] = fits ? row : -1;
+          if (fits && slot_of_row != nullptr) slot_of_row[row] = (int)s;
         }
         __syncwarp();
         if (live && rank == 0) cursor[e] += __popc(same);      // one lane per expert advances the cursor
@@ -297,6 +302,124 @@ __global__ void moe_tokens_from_rows_kernel(const bf16* __restrict__ rows, const
     }
   }
 }
+
+// ---------------------------------------------------------------------------------------------------- expert parallelism
+constexpr int EP_MAX_RANKS = 16;
+struct EpPtrs { void* p[EP_MAX_RANKS]; };
+
+// counts[E] of this rank -> row `me` of every rank's count matrix [ep, E]
+__global__ void ep_push_counts_kernel(const int* __restrict__ counts, int E, EpPtrs mats, int ep, int me) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < E * ep; i += gridDim.x * blockDim.x) {
+    const int r = i / E, e = i - r * E;
+    reinterpret_cast<int*>(mats.p[r])[(size_t)me * E + e] = counts[e];
+  }
+}
+
+// One block.  counts_all [ep, E]: row s = slots per expert of source rank s.  Expert e lives on rank e / El; in the owner's
+// buffer the rows of an expert are ordered by source rank, every expert padded to whole 128-row tiles.
+//   row_base[e]      first row (in the owner's buffer) of THIS rank's slots of expert e
+//   prefix_local     [El + 1] tile prefix of this rank's own experts (what the grouped GEMM reads)
+//   tot_local        [El] rows per local expert (all sources)
+// An owner whose rows exceed cap_rows sets status 200 (the sender side then drops the slots that do not fit).
+__global__ void ep_plan_kernel(const int* __restrict__ counts_all, int ep, int E, int me, int cap_rows, int* __restrict__ row_base,
+                               int* __restrict__ prefix_local, int* __restrict__ tot_local, int* __restrict__ status) {
+  extern __shared__ int sh[];       // tot[E] | before[E] | tile_first[E]
+  int* tot = sh;
+  int* before = sh + E;
+  int* tile_first = sh + 2 * E;
+  const int El = E / ep;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int t = 0, b = 0;
+    for (int s = 0; s < ep; ++s) {
+      const int c = counts_all[(size_t)s * E + e];
+      if (s < me) b += c;
+      t += c;
+    }
+    tot[e] = t;
+    before[e] = b;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < ep) {
+    const int o = threadIdx.x;
+    int run = 0;
+    for (int i = 0; i < El; ++i) {
+      const int e = o * El + i;
+      tile_first[e] = run;
+      if (o == me) { prefix_local[i] = run; tot_local[i] = tot[e]; }
+      run += (tot[e] + TILE - 1) / TILE;
+    }
+    if (o == me) prefix_local[El] = run;
+    if ((long)run * TILE > cap_rows) atomicCAS(status, 0, 200);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) row_base[e] = tile_first[e] * TILE + before[e];
+}
+
+// One warp per slot: rows_of_owner[dest[slot], :] = scale[slot] * src[slot / k, :] and src_of_row[dest[slot]] = me * n_slots + slot
+// (peer stores into the memory of the rank that owns the slot's expert).
+__global__ void ep_dispatch_kernel(const bf16* __restrict__ src, const int* __restrict__ experts, const int* __restrict__ dest,
+                                   const float* __restrict__ scale, long n_slots, int k, int H, int El, int me, EpPtrs rows, EpPtrs srcs) {
+  const long slot = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (slot >= n_slots) return;
+  const int row = dest[slot];
+  if (row < 0) return;
+  const int o = experts[slot] / El;
+  const uint4* in = reinterpret_cast<const uint4*>(src + (size_t)(slot / k) * H);
+  uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(rows.p[o]) + (size_t)row * H);
+  const int nvec = H >> 3;
+  if (scale == nullptr) {
+    for (int c = lane; c < nvec; c += 32) out[c] = in[c];
+  } else {
+    const float sc = scale[slot];
+    for (int c = lane; c < nvec; c += 32) {
+      uint4 v = in[c];
+      __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(p[i]);
+        p[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+      }
+      out[c] = v;
+    }
+  }
+  if (lane == 0) reinterpret_cast<int*>(srcs.p[o])[row] = me * (int)n_slots + (int)slot;
+}
+
+// Owner side, after all sources have signalled: padding rows of every local expert's last tile -> zero, src_of_row -> -1.
+// One block per local expert.
+__global__ void ep_zero_padding_kernel(bf16* __restrict__ rows, int* __restrict__ src_of_row, const int* __restrict__ prefix_local,
+                                       const int* __restrict__ tot_local, int H, long cap_rows) {
+  const int e = blockIdx.x;
+  const long first = (long)prefix_local[e] * TILE + tot_local[e];
+  long last = (long)prefix_local[e + 1] * TILE;
+  if (last > cap_rows) last = cap_rows;
+  const int nvec = H >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  for (long r = first + warp; r < last; r += n_warps) {
+    uint4* out = reinterpret_cast<uint4*>(rows + r * H);
+    for (int c = lane; c < nvec; c += 32) out[c] = make_uint4(0u, 0u, 0u, 0u);
+    if (lane == 0) src_of_row[r] = -1;
+  }
+}
+
+// Owner side: every row that holds a slot goes back to its source: back_of_source[slot, :] = y[row, :].  One warp per row.
+__global__ void ep_return_kernel(const bf16* __restrict__ y, const int* __restrict__ src_of_row, const int* __restrict__ prefix_local,
+                                 int El, long n_slots, int H, long cap_rows, EpPtrs backs) {
+  const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  long used = (long)prefix_local[El] * TILE;
+  if (used > cap_rows) used = cap_rows;
+  if (row >= used) return;
+  const int s = src_of_row[row];
+  if (s < 0) return;
+  const int rank = s / (int)n_slots;
+  const long slot = s - (long)rank * n_slots;
+  const uint4* in = reinterpret_cast<const uint4*>(y + row * H);
+  uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(backs.p[rank]) + slot * H);
+  const int nvec = H >> 3;
+  for (int c = lane; c < nvec; c += 32) out[c] = in[c];
+}
 }  // namespace
 
 extern "C" {
@@ -321,18 +444,32 @@ int vlmt_moe_route_bwd(const void* logits, int logits_fp32, const int* experts, 
   return (int)cudaGetLastError();
 }
 int vlmt_moe_plan_blocks(long n_slots) { return (int)((n_slots + PLAN_CHUNK - 1) / PLAN_CHUNK); }
-// hist: scratch of plan_blocks(n_slots) * E ints; slot_of_row: cap_rows ints (set to -1 here); dest: n_slots ints;
-// counts: E ints; prefix: E + 1 ints
-int vlmt_moe_plan(const int* experts, long n_slots, int E, int* hist, int* counts, int* prefix, int* dest, int* slot_of_row, long cap_rows,
-                  cudaStream_t st) {
+// stage 1: hist (scratch of plan_blocks(n_slots) * E ints, left as per-block exclusive prefixes), counts [E], prefix [E + 1]
+int vlmt_moe_plan_count(const int* experts, long n_slots, int E, int* hist, int* counts, int* prefix, cudaStream_t st) {
   if (E > 4096) return -1;
-  cudaError_t e = cudaMemsetAsync(slot_of_row, 0xff, (size_t)cap_rows * sizeof(int), st);
-  if (e != cudaSuccess) return (int)e;
   const int nb = vlmt_moe_plan_blocks(n_slots);
   if (nb > 0) moe_plan_hist_kernel<<<nb, PLAN_THREADS, E * sizeof(int), st>>>(experts, n_slots, E, hist);
   moe_plan_scan_kernel<<<1, 256, E * sizeof(int), st>>>(hist, nb, E, counts, prefix);
-  if (nb > 0) moe_plan_place_kernel<<<nb, PLAN_THREADS, E * sizeof(int), st>>>(experts, n_slots, E, hist, prefix, dest, slot_of_row);
   return (int)cudaGetLastError();
+}
+// stage 2: dest [n_slots]; slot_of_row [cap_rows] (optional; set to -1 first); row_base (optional) replaces prefix * 128
+int vlmt_moe_plan_place(const int* experts, long n_slots, int E, const int* hist, const int* prefix, const int* row_base, int* dest,
+                        int* slot_of_row, long cap_rows, cudaStream_t st) {
+  if (E > 4096) return -1;
+  if (slot_of_row != nullptr) {
+    cudaError_t e = cudaMemsetAsync(slot_of_row, 0xff, (size_t)cap_rows * sizeof(int), st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int nb = vlmt_moe_plan_blocks(n_slots);
+  if (nb > 0)
+    moe_plan_place_kernel<<<nb, PLAN_THREADS, E * sizeof(int), st>>>(experts, n_slots, E, hist, prefix, row_base, cap_rows, dest, slot_of_row);
+  return (int)cudaGetLastError();
+}
+int vlmt_moe_plan(const int* experts, long n_slots, int E, int* hist, int* counts, int* prefix, int* dest, int* slot_of_row, long cap_rows,
+                  cudaStream_t st) {
+  int r = vlmt_moe_plan_count(experts, n_slots, E, hist, counts, prefix, st);
+  if (r) return r;
+  return vlmt_moe_plan_place(experts, n_slots, E, hist, prefix, nullptr, dest, slot_of_row, cap_rows, st);
 }
 int vlmt_moe_rows_from_tokens(const void* src, const int* slot_of_row, const int* prefix, int E, int k, int H, const float* scale, void* rows,
                               long cap_rows, cudaStream_t st) {
@@ -347,6 +484,41 @@ int vlmt_moe_tokens_from_rows(const void* rows, const int* dest, const float* w,
   if (H & 7) return -1;
   if (T <= 0) return 0;
   moe_tokens_from_rows_kernel<<<(T + 7) / 8, 256, 0, st>>>((const bf16*)rows, dest, w, T, k, H, (bf16*)out, (const bf16*)g, dw);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ expert parallelism
+static void fill(EpPtrs& d, void* const* p, int n) { for (int i = 0; i < n; ++i) d.p[i] = p[i]; }
+int vlmt_ep_push_counts(const int* counts, int E, void* const* mats, int ep, int me, cudaStream_t st) {
+  if (ep > EP_MAX_RANKS) return -1;
+  EpPtrs m; fill(m, mats, ep);
+  ep_push_counts_kernel<<<(E * ep + 255) / 256, 256, 0, st>>>(counts, E, m, ep, me);
+  return (int)cudaGetLastError();
+}
+int vlmt_ep_plan(const int* counts_all, int ep, int E, int me, int cap_rows, int* row_base, int* prefix_local, int* tot_local, int* status,
+                 cudaStream_t st) {
+  if (ep > EP_MAX_RANKS || E % ep != 0 || E > 4096) return -1;
+  ep_plan_kernel<<<1, 256, 3 * E * sizeof(int), st>>>(counts_all, ep, E, me, cap_rows, row_base, prefix_local, tot_local, status);
+  return (int)cudaGetLastError();
+}
+int vlmt_ep_dispatch(const void* src, const int* experts, const int* dest, const float* scale, long n_slots, int k, int H, int El, int me,
+                     void* const* rows, void* const* srcs, int ep, cudaStream_t st) {
+  if (ep > EP_MAX_RANKS || (H & 7)) return -1;
+  if (n_slots <= 0) return 0;
+  EpPtrs r, s; fill(r, rows, ep); fill(s, srcs, ep);
+  ep_dispatch_kernel<<<(unsigned)((n_slots + 7) / 8), 256, 0, st>>>((const bf16*)src, experts, dest, scale, n_slots, k, H, El, me, r, s);
+  return (int)cudaGetLastError();
+}
+int vlmt_ep_zero_padding(void* rows, int* src_of_row, const int* prefix_local, const int* tot_local, int El, int H, long cap_rows,
+                         cudaStream_t st) {
+  ep_zero_padding_kernel<<<El, 256, 0, st>>>((bf16*)rows, src_of_row, prefix_local, tot_local, H, cap_rows);
+  return (int)cudaGetLastError();
+}
+int vlmt_ep_return(const void* y, const int* src_of_row, const int* prefix_local, int El, long n_slots, int H, long cap_rows,
+                   void* const* backs, int ep, cudaStream_t st) {
+  if (ep > EP_MAX_RANKS || (H & 7)) return -1;
+  EpPtrs b; fill(b, backs, ep);
+  ep_return_kernel<<<(unsigned)((cap_rows + 7) / 8), 256, 0, st>>>((const bf16*)y, src_of_row, prefix_local, El, n_slots, H, cap_rows, b);
   return (int)cudaGetLastError();
 }
 }

@@ -103,7 +103,7 @@ class Trainer:
         if t.ep_size > 1:
             from ..parallel.ep import apply_ep
 
-            self.ep_ctx = apply_ep(model, self.mesh, t.ep_size)
+            self.ep_ctx = apply_ep(model, self.mesh, t.ep_size, fused=t.fused_comm and self.device.type == "cuda")
         apply_ac(model, t.ac_mode)
         self.model = model
         self.optimizer = self.create_optimizer()
