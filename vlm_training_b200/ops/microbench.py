@@ -2,7 +2,7 @@
 
     python -m vlm_training_b200.ops.microbench gemm --m 8192 --n 6144 --k 4096 [--layout fwd|dgrad|wgrad]
     python -m vlm_training_b200.ops.microbench attention --tokens 8192 --docs 1 [--backward]
-    python -m vlm_training_b200.ops.microbench rmsnorm | swiglu | qkv_rope | ce | adamw | moe
+    python -m vlm_training_b200.ops.microbench rmsnorm | swiglu | qkv_rope | ce | adamw | moe | fused_adamw | gemm_ag
     python -m vlm_training_b200.ops.microbench gdn_scan --tokens 16384 --docs 1 [--backward]   |   conv1d [--backward]   |   dsa [--backward]
     python -m vlm_training_b200.ops.microbench all            # the table used in the roofline report
 
@@ -232,9 +232,44 @@ def bench_dsa(t: Timer, queries=1024, keys=16384, topk=2048, hkv=2, rep=8, d=256
     return _report("dsa_selected_attention_fwd", [queries, keys, topk, hkv, rep, d], ms, nbytes=gathered)
 
 
+def bench_fused_adamw(t: Timer, n=1 << 27, state=torch.float32):
+    """The reduce-scatter + AdamW + all-gather kernel on a domain of one rank (no peers): what it costs when only the
+    memory system limits it; the multi-rank timings are in ``parallel.microbench_comm``."""
+    from . import cuda as cu
+
+    g = _r(n)
+    p = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    master = torch.zeros(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda", dtype=state), torch.zeros(n, device="cuda", dtype=state)
+    fn = lambda: cu._C.fused_rs_adamw_ag([g.data_ptr()], [p.data_ptr()], 0, 0, 1, 0, n, master, m, v, 0, 1e-5, 0.9, 0.999, 1e-8, 0.01,
+                                         0.1, 0.001, 1.0, True)
+    sb = 4 if state == torch.float32 else 2
+    nbytes = n * (2 + 2 + 4 + 2 * sb) + n * (4 + 2 * sb + 2)   # grad read + cleared, state read, state + parameter written
+    return _report(f"fused_rs_adamw_ag_one_rank_{'fp32' if sb == 4 else 'bf16'}_moments", [n], t(fn), nbytes=nbytes)
+
+
+def bench_gemm_ag(t: Timer, m=8192, n=3072, k=4096, b_mn=False):
+    """The all-gather -> GEMM kernel run as rank 0 of two on one GPU: the peer's rows are already in the gathered buffer
+    and its flag is set, the kernel's own push goes into a second local buffer.  Shows the cost of the push warps and the
+    two-source A operand next to the plain GEMM of the same shape (no link is crossed here)."""
+    from . import cuda as cu
+
+    R = m // 2
+    x_loc, x_full, peer_buf = _r(R, k), _r(m, k), _r(m, k)
+    w = _r(k, n) if b_mn else _r(n, k)
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    peer_flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    flags[1] = 1 << 30
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: cu._C.gemm_ag(x_loc, x_full, w, y, [x_full.data_ptr(), peer_buf.data_ptr()], [flags.data_ptr(), peer_flags.data_ptr()],
+                               0, counter, 5, 0, b_mn)
+    return _report("gemm_all_gather_rank0_of_2_" + ("dgrad" if b_mn else "fwd"), [m, n, k], t(fn), flops=2.0 * m * n * k)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "conv1d", "dsa", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "conv1d", "dsa", "fused_adamw", "gemm_ag", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -272,6 +307,11 @@ def main(argv=None):
         bench_conv1d(t, a.tokens, backward=a.backward)
     elif a.what == "dsa":
         bench_dsa(t, backward=a.backward)
+    elif a.what == "fused_adamw":
+        bench_fused_adamw(t)
+        bench_fused_adamw(t, state=torch.bfloat16)
+    elif a.what == "gemm_ag":
+        bench_gemm_ag(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
     else:
         for layout in ("fwd", "dgrad", "wgrad"):
             bench_gemm(t, 8192, 6144, 4096, layout)
@@ -289,6 +329,10 @@ def main(argv=None):
         bench_qkv_rope(t)
         bench_ce(t)
         bench_adamw(t)
+        bench_fused_adamw(t)
+        bench_fused_adamw(t, state=torch.bfloat16)
+        bench_gemm_ag(t, 8192, 3072, 4096)
+        bench_gemm_ag(t, 8192, 2048, 4096, b_mn=True)
         bench_moe(t)
         for docs in (1, 16):
             bench_gdn_scan(t, 16384, docs)
