@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the number of decoder layers (result is not a bench value)")
     ap.add_argument("--opt-state", default="auto", choices=["auto", "fp32", "bf16"])
     ap.add_argument("--vit-ac", default="auto", choices=["auto", "off", "full"])
+    ap.add_argument("--reshard", action="store_true", help="shard parameters and gradients too (ZeRO-3 residency); not the default layout")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file (not a bench run)")
     return ap.parse_args()
@@ -115,6 +116,7 @@ def build_config(args, world: int):
     # parameter; the same precision at every N keeps the scaling curve a like-for-like comparison
     t.optimizer_state_dtype = args.opt_state if args.opt_state != "auto" else "bf16"
     t.fused_comm = os.environ.get("VLMT_FUSED_COMM", "1") == "1"
+    t.reshard_params = bool(args.reshard)
     t.output_dir = "/tmp/vlmt_bench"
     cfg.data.synthetic = "vlm" if "vl" in args.model else "text-loguniform"
     cfg.data.seq_len = args.seq_len
@@ -272,7 +274,8 @@ def run_ours(args):
                                       + (f"+ep{args.ep}" if args.ep > 1 else ""),
                        "ac_mode": cfg.training.ac_mode, "optimizer": f"AdamW, fp32 master + {cfg.training.optimizer_state_dtype} moments, sharded over dp", "vit_ac": vit_ac,
                        "l2": "not flushed: every step streams >17 GB of weights, far above the 126 MB L2",
-                       "layers_override": args.layers or None, "ce_chunk": args.ce_chunk},
+                       "layers_override": args.layers or None, "ce_chunk": args.ce_chunk,
+                       "reshard_params": bool(args.reshard)},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem, "final_loss": float(loss.item()),
         }
         print(json.dumps(line))

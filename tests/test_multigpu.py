@@ -201,3 +201,16 @@ def test_expert_parallel_peer_store_transport_matches_all_to_all(tmp_path):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("EP FUSED OK") == 2, res.stdout[-2000:]
+
+
+def test_sharded_parameters_match_whole_parameters_on_gpus(tmp_path):
+    """ZeRO-3 residency on 2 GPUs (data parallel): parameters gathered per unit by the own peer-pull kernel from symmetric
+    shards (fused_comm on) or by the library all-gather (off), gradients reduce-scattered into shards, against the engine
+    that keeps parameters and gradients whole."""
+    whole = _run(tmp_path, 2, ["--training.fused_comm", "false"], 29721)
+    probe_whole = torch.tensor(_run.last_probe)
+    for port, fused in ((29722, "true"), (29723, "false")):
+        sharded = _run(tmp_path, 2, ["--training.fused_comm", fused, "--training.reshard_params", "true"], port, {"VLMT_NO_MULTIMEM": "1"})
+        assert sharded == pytest.approx(whole, rel=2e-3, abs=2e-3)
+        frac_off = ((torch.tensor(_run.last_probe) - probe_whole).abs() > 5e-4).float().mean().item()
+        assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ (fused_comm {fused})"

@@ -168,3 +168,39 @@ def test_vlm_dp2_tp2_matches_dp2(tmp_path):
     dp2tp2 = _run_ranks(tmp_path, 4, ["--training.data_parallel", "fsdp", "--training.tp_size", "2",
                                       "--training.sequence_parallel", "true"], 29630, **kw)
     assert dp2tp2 == pytest.approx(dp2, rel=5e-4, abs=5e-4)
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("ac", ["off", "full"])
+def test_sharded_parameters_match_whole_parameters(tmp_path, ac):
+    """ZeRO-3 residency (parameters and gradients sharded; a layer's parameters gathered for its forward / recomputation /
+    backward and released afterwards; gradients reduce-scattered per micro-batch) against the engine that keeps them whole:
+    same losses on 2 gloo ranks, with and without activation checkpointing, with gradient accumulation."""
+    common = ["--training.data_parallel", "fsdp", "--training.ac_mode", ac, "--training.tpi_multiplier", "1.5"]
+    whole = _run_ranks(tmp_path, 2, common, 29631)
+    sharded = _run_ranks(tmp_path, 2, common + ["--training.reshard_params", "true"], 29632)
+    assert sharded == pytest.approx(whole, rel=1e-5, abs=1e-5)
+    keep = _run_ranks(tmp_path, 2, common + ["--training.reshard_params", "true", "--training.reshard_after_forward", "false"], 29633)
+    assert keep == pytest.approx(whole, rel=1e-5, abs=1e-5)
+
+
+@pytest.mark.slow
+def test_sharded_parameters_under_dp2_tp2_and_checkpoint_resume(tmp_path):
+    """Sharded parameters with two reduction domains (dp 2 x tp 2, VLM with image-parallel ViT), and a checkpoint written
+    and resumed with parameters sharded."""
+    kw = dict(preset="tiny-qwen3-vl-gpu", synthetic="vlm", seq_len="1024")
+    tp = ["--training.data_parallel", "fsdp", "--training.tp_size", "2", "--training.sequence_parallel", "true"]
+    whole = _run_ranks(tmp_path, 4, tp, 29634, **kw)
+    sharded = _run_ranks(tmp_path, 4, tp + ["--training.reshard_params", "true"], 29635, **kw)
+    assert sharded == pytest.approx(whole, rel=5e-5, abs=5e-5)
+    # 2 steps and a checkpoint, then a fresh job resumes from it (parameters are gathered for the state dict and
+    # re-sharded after the load)
+    base = ["--training.data_parallel", "fsdp", "--training.reshard_params", "true"]
+    (tmp_path / "full").mkdir()
+    (tmp_path / "part").mkdir()
+    full = _run_ranks(tmp_path / "full", 2, base, 29636)
+    first = _run_ranks(tmp_path / "part", 2, base + ["--training.total_steps", "2", "--training.save_steps", "2"], 29637)
+    assert first == pytest.approx(full[:2], rel=1e-6, abs=1e-6)
+    assert os.path.exists(tmp_path / "part" / "out2" / "checkpoint-step-2" / ".metadata")
+    rest = _run_ranks(tmp_path / "part", 2, base + ["--training.resume_checkpoint", "true"], 29638)
+    assert len(rest) == 2 and all(l == l and l < 20 for l in rest)

@@ -102,6 +102,13 @@ class TrainingSection:
     clip_grad: bool = False
     # one-kernel NVLink paths (reduce-scatter+AdamW+all-gather, TP GEMM+collective)
     fused_comm: bool = True
+    # with data_parallel = "fsdp": also shard the bf16 parameters and gradients over the data-parallel ranks (ZeRO-3:
+    # a layer's parameters are gathered for its forward / backward and released afterwards).  Off: parameters and
+    # gradients stay whole on every rank and only the optimizer state is sharded, which is faster while the model fits.
+    reshard_params: bool = False
+    # release a unit's gathered parameters right after its forward pass (and gather again for backward);
+    # false keeps them until the unit's backward pass is done (the reference's default FSDP policy)
+    reshard_after_forward: bool = True
     beta1: float = 0.9
     beta2: float = 0.999
     seed: int = 42

@@ -212,12 +212,16 @@ class _CausalLMBase(nn.Module):
             merged, deep = self.visual(pix, None, plan)
             feats = torch.cat([merged] + list(deep), dim=-1)
         else:
-            n_out = 1 + len(self.config.vision.deepstack_visual_indexes)
-            # a rank without images still takes part in the exchange; its tower gradients stay zero in the flat buffer
-            feats = pixel_values.new_zeros((0, n_out * self.config.vision.out_hidden_size),
-                                           dtype=self.decoder.embed_tokens.weight.dtype)
-            if torch.is_grad_enabled():
-                feats.requires_grad_()  # keeps the exchange's backward collective in this rank's autograd graph too
+            # A rank without images still runs the tower, on one dummy image of 2 x 2 patches whose features are dropped:
+            # every rank then executes the same modules in the same order, so the collectives that belong to the tower's
+            # parameters (bucket reductions from the gradient hooks, parameter gathers of sharded units) line up across
+            # ranks, and the exchange's backward collective stays in this rank's autograd graph.
+            ms = self.config.vision.spatial_merge_size
+            dummy = [[1, ms, ms]]
+            plan = VisionPlan.build(dummy, self.config.vision, dev)
+            pix = pixel_values.new_zeros((ms * ms, pixel_values.shape[1]))
+            merged, deep = self.visual(pix, None, plan)
+            feats = torch.cat([merged] + list(deep), dim=-1)[:0]
         sizes = [sum(n_patch[i] for i in ix) // merge2 for ix in assign]
         allf = gather_uneven(feats, sizes, tp, grad_identical=not tp.sequence_parallel)
         # the gathered rows are rank-major; put the images back in their order of appearance in the row

@@ -65,6 +65,9 @@ def _gemm(a, b, a_mn=False, b_mn=False, bias=None, epilogue=0, out=None, accumul
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    if b.untyped_storage().size() == 0 or out.untyped_storage().size() == 0:
+        # a sharded parameter (or its gradient bucket) whose storage is released: an error here, never a kernel on freed memory
+        raise RuntimeError("GEMM operand without storage: a sharded parameter was used outside the forward / backward of its unit")
     _C.gemm(a, b, out, a_mn, b_mn, bias, epilogue, accumulate)
     _tick()
     return out

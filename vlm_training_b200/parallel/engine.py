@@ -20,6 +20,14 @@ layout chosen for 180 GB GPUs on NVSwitch:
 * with ``fused_comm`` the three steps (reduce-scatter, AdamW, all-gather) run as ONE
   kernel over NVLink peer memory (see :mod:`vlm_training_b200.parallel.fused`).
 
+``reshard`` (``training.reshard_params``, the ZeRO-3 form of ``fsdp``): bf16 parameters and gradients are sharded too.
+Every rank keeps only its 1/dp shard of each bucket between uses; buckets are cut at the boundaries of "units" (a
+decoder layer, a ViT block; everything else forms an always-resident root unit).  A unit's parameter buckets are
+all-gathered into buffers that exist only while the unit runs (before its forward, before its recomputation / backward)
+and their storage is released afterwards; its gradient buckets exist from the unit's backward until their reduce-scatter
+into the gradient shard has been issued.  Autograd keeps references to a bucket's storage object, not to its bytes, so
+the storage can be emptied and refilled between forward and backward.
+
 Two reduction domains exist under tensor parallelism: parameters that are split
 across TP ranks reduce over the data-parallel group only; parameters replicated
 across TP ranks reduce over the whole (dp x tp) world, because with sequence
@@ -68,13 +76,15 @@ class _Bucket:
     reduced: bool = False
     gather_event: object = None
     reduce_event: object = None
+    unit: int = -1          # reshard mode: index of the unit whose parameters this bucket holds (-1: root, always resident)
+    index: int = 0
 
 
 class _Domain:
     """Flat buffers + process group for one reduction domain."""
 
     def __init__(self, name, entries, group, grad_scale, shard, device, param_dtype, bucket_elems, state_dtype,
-                 symmetric=False):
+                 symmetric=False, reshard=False, unit_of=None):
         self.name, self.group, self.shard, self.device = name, group, shard, device
         self.size = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if (group is not None and dist.is_initialized()) else 0
@@ -85,14 +95,21 @@ class _Domain:
         off = 0
         cur = _Bucket(start=0, end=0)
         self.slots = []  # (param, offset, numel, group_idx)
+        self.reshard = bool(reshard) and self.shard and self.size > 1
+        unit_of = unit_of if (self.reshard and unit_of is not None) else {}
+        if self.reshard:   # the root unit first, then the units in order: a bucket never mixes units
+            entries = sorted(entries, key=lambda pg: unit_of.get(pg[0], -1))
         for p, gi in entries:
             n = p.numel()
             off = _round_up(off, 8)  # every parameter starts on a 16-byte boundary (bf16)
-            if cur.params and (off - cur.start) + n > bucket_elems:
+            u = unit_of.get(p, -1)
+            if cur.params and ((off - cur.start) + n > bucket_elems or (self.reshard and u != cur.unit)):
                 off = _round_up(off, unit)
                 cur.end = off
                 self.buckets.append(cur)
                 cur = _Bucket(start=off, end=off)
+            if not cur.params:
+                cur.unit = u
             self.slots.append((p, off, n, gi))
             if cur.segments and cur.segments[-1].group == gi:
                 cur.segments[-1].end = off + n
@@ -105,6 +122,16 @@ class _Domain:
         if cur.params:
             self.buckets.append(cur)
         self.total = off
+        for i, b in enumerate(self.buckets):
+            b.index = i
+        self.param_bucket = {}
+        for b in self.buckets:
+            for p in b.params:
+                self.param_bucket[p] = b
+        self.param_dtype = param_dtype
+        if self.reshard:
+            self._init_resharded(param_dtype, state_dtype, symmetric)
+            return
         # ---- buffers
         alloc = _symmetric_empty if symmetric else (lambda n, dt, dev, grp: torch.zeros(n, dtype=dt, device=dev))
         self.flat_param = alloc(self.total, param_dtype, device, group)
@@ -118,10 +145,6 @@ class _Domain:
                 # weight-gradient GEMMs may add into this view directly (ops/cuda.py:_wgrad); valid because every
                 # such parameter enters exactly one linear per forward pass
                 p._vlmt_grad_in_place = True
-        self.param_bucket = {}
-        for b in self.buckets:
-            for p in b.params:
-                self.param_bucket[p] = b
         # ---- optimizer state on the local shard of every bucket
         self.master, self.exp_avg, self.exp_avg_sq = [], [], []
         for b in self.buckets:
@@ -129,6 +152,121 @@ class _Domain:
             self.master.append(self.flat_param[lo:hi].float().clone())
             self.exp_avg.append(torch.zeros(hi - lo, dtype=state_dtype, device=device))
             self.exp_avg_sq.append(torch.zeros(hi - lo, dtype=state_dtype, device=device))
+
+    # ------------------------------------------------------------------ sharded parameters and gradients (ZeRO-3)
+    def _init_resharded(self, param_dtype, state_dtype, symmetric):
+        device, group = self.device, self.group
+        alloc = _symmetric_empty if symmetric else (lambda n, dt, dev, grp: torch.zeros(n, dtype=dt, device=dev))
+        self.flat_param = self.flat_grad = None
+        self.symmetric_shards = bool(symmetric)
+        self.bucket_param, self.bucket_grad, self.param_shard, self.grad_shard = [], [], [], []
+        self.master, self.exp_avg, self.exp_avg_sq = [], [], []
+        self.resident, self.grad_live = [], []
+        with torch.no_grad():
+            for b in self.buckets:
+                n = b.end - b.start
+                full = torch.zeros(n, dtype=param_dtype, device=device)
+                grad = torch.zeros(n, dtype=param_dtype, device=device)
+                for p in b.params:
+                    o = self._offset_of(p) - b.start
+                    full[o:o + p.numel()].copy_(p.detach().reshape(-1))
+                    p.data = full[o:o + p.numel()].view(p.shape)
+                    p.grad = grad[o:o + p.numel()].view(p.shape)
+                    p._vlmt_grad_in_place = True
+                lo, hi = self.shard_range(b)
+                shard = alloc(hi - lo, param_dtype, device, group)
+                shard.copy_(full[lo - b.start:hi - b.start])
+                self.param_shard.append(shard)
+                self.grad_shard.append(torch.zeros(hi - lo, dtype=param_dtype, device=device))
+                self.master.append(shard.float().clone())
+                self.exp_avg.append(torch.zeros(hi - lo, dtype=state_dtype, device=device))
+                self.exp_avg_sq.append(torch.zeros(hi - lo, dtype=state_dtype, device=device))
+                self.bucket_param.append(full)
+                self.bucket_grad.append(grad)
+                self.resident.append(True)
+                self.grad_live.append(True)
+        self._nbytes = [(b.end - b.start) * self.bucket_param[0].element_size() for b in self.buckets]
+        for b in self.buckets:
+            if b.unit >= 0:
+                self.release_params(b)
+                self.release_grads(b)
+
+    def _offset_of(self, p):
+        if not hasattr(self, "_slot_offset"):
+            self._slot_offset = {q: o for q, o, _, _ in self.slots}
+        return self._slot_offset[p]
+
+    def materialize_params(self, b: _Bucket):
+        """Make the bucket's parameters usable: give its storage its bytes back and all-gather the shards into it."""
+        i = b.index
+        if self.resident[i]:
+            return
+        full = self.bucket_param[i]
+        full.untyped_storage().resize_(self._nbytes[i])
+        self.resident[i] = True
+        self.gather_params(b)
+
+    def gather_params(self, b: _Bucket):
+        i = b.index
+        full, shard = self.bucket_param[i], self.param_shard[i]
+        if self.symmetric_shards and full.is_cuda:
+            from . import symm
+            from ..ops import cuda as cu
+
+            if not hasattr(self, "_no_flags"):
+                self._no_flags = torch.zeros(64, dtype=torch.int32, device=self.device)
+            # peers' shards are stable between optimizer steps (the engine ends a step with a barrier on the device): a
+            # plain peer pull with nothing to wait for (collective number 0 is always "there")
+            cu._C.pull_gather(symm.peer_ptrs(shard), full, shard.numel(), self._no_flags.data_ptr(), 0)
+            cu._tick()
+        else:
+            dist.all_gather_into_tensor(full, shard if full.is_cuda else shard.clone(), group=self.group)
+
+    def release_params(self, b: _Bucket):
+        i = b.index
+        if not self.resident[i] or b.unit < 0:
+            return
+        t = self.bucket_param[i]
+        if t.is_cuda:
+            t.record_stream(torch.cuda.current_stream())
+        t.untyped_storage().resize_(0)
+        self.resident[i] = False
+
+    def materialize_grads(self, b: _Bucket):
+        i = b.index
+        if self.grad_live[i]:
+            return
+        g = self.bucket_grad[i]
+        g.untyped_storage().resize_(self._nbytes[i])
+        g.zero_()
+        self.grad_live[i] = True
+
+    def release_grads(self, b: _Bucket, stream=None):
+        i = b.index
+        if not self.grad_live[i] or b.unit < 0:
+            return
+        g = self.bucket_grad[i]
+        if g.is_cuda and stream is not None:
+            g.record_stream(stream)   # the reduce-scatter on that stream may still be reading
+        g.untyped_storage().resize_(0)
+        self.grad_live[i] = False
+
+    # ------------------------------------------------------------------ layout-independent accessors
+    def bucket_grad_view(self, b: _Bucket):
+        return self.bucket_grad[b.index] if self.reshard else self.flat_grad[b.start:b.end]
+
+    def shard_grad_view(self, b: _Bucket, s: int, e: int):
+        """Elements [s, e) (domain offsets, inside this rank's shard of ``b``) of the reduced gradient."""
+        if self.reshard:
+            lo, _ = self.shard_range(b)
+            return self.grad_shard[b.index][s - lo:e - lo]
+        return self.flat_grad[s:e]
+
+    def shard_param_view(self, b: _Bucket, s: int, e: int):
+        if self.reshard:
+            lo, _ = self.shard_range(b)
+            return self.param_shard[b.index][s - lo:e - lo]
+        return self.flat_param[s:e]
 
     def shard_range(self, b: _Bucket):
         if not self.shard or self.size == 1:
@@ -147,6 +285,25 @@ def _symmetric_empty(n, dtype, device, group):
     return symmetric_zeros(n, dtype, device, group)
 
 
+def _find_units(model, group_of):
+    """Units of parameter residency: every element of an ``nn.ModuleList`` that holds trainable parameters (decoder
+    layers, ViT blocks, DeepStack mergers).  Returns ``(modules, {parameter: unit index})``; parameters outside any
+    unit belong to the root unit (-1), which stays resident."""
+    import torch.nn as nn
+
+    units, unit_of = [], {}
+    for mod in model.modules():
+        if isinstance(mod, nn.ModuleList):
+            for child in mod:
+                ps = [p for p in child.parameters() if p in group_of and p not in unit_of]
+                if not ps:
+                    continue
+                for p in ps:
+                    unit_of[p] = len(units)
+                units.append(child)
+    return units, unit_of
+
+
 class ShardedOptimizerEngine(torch.optim.Optimizer):
     """Owns the model's trainable parameters as flat buffers and performs
     gradient synchronisation + AdamW + parameter redistribution.
@@ -158,7 +315,8 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
 
     def __init__(self, model, groups: list[GroupSpec], *, dp_group=None, world_group=None, tp_size: int = 1,
                  mode: str = "fsdp", betas=(0.9, 0.999), eps: float = 1e-8, max_grad_norm: float | None = None,
-                 bucket_mb: float = 256.0, state_dtype=torch.float32, fused_comm: bool = False, overlap: bool = True):
+                 bucket_mb: float = 256.0, state_dtype=torch.float32, fused_comm: bool = False, overlap: bool = True,
+                 reshard: bool = False, reshard_after_forward: bool = True):
         pgs = [{"params": list(g.params), "lr": g.lr, "weight_decay": g.weight_decay, "name": g.name} for g in groups]
         super().__init__(pgs, defaults={"lr": groups[0].lr, "weight_decay": 0.0})
         self.model = model
@@ -190,6 +348,17 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         self.domains: list[_Domain] = []
         self.comm_path = "local" if not dist.is_initialized() else "nccl"
         reason = ""
+        self.reshard = bool(reshard) and shard and dist.is_initialized() and dp_size > 1
+        self.reshard_after_forward = reshard_after_forward
+        self.units, unit_of = [], {}
+        symmetric_shards = False
+        if self.reshard:
+            self.units, unit_of = _find_units(model, group_of)
+            # with `fused_comm` the parameter shards live in symmetric memory and a unit's parameters are gathered by
+            # our own peer-pull kernel; the gradient side is a reduce-scatter into the shard in both cases
+            symmetric_shards = bool(fused_comm) and self.is_cuda
+            if fused_comm:
+                fused_comm, reason = False, "sharded parameters and gradients use reduce-scatter into shards, not the one-kernel step"
         if fused_comm and self.is_cuda and dist.is_initialized():
             # decided before the buffers are allocated: the one-kernel path needs them in symmetric memory
             if state_dtype not in (torch.float32, torch.bfloat16):
@@ -208,17 +377,18 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         if tp_size > 1:
             if sharded:
                 self.domains.append(_Domain("tp_sharded", sharded, dp_group, 1.0 / dp_size, shard, device, pdtype,
-                                            bucket_elems, state_dtype, symmetric))
+                                            bucket_elems, state_dtype, symmetric or symmetric_shards, self.reshard, unit_of))
             if replicated:
                 with torch.no_grad():
                     self._identical = [p for p, _ in replicated if getattr(p, "_tp_grad", "partial") == "identical"]
                 self.domains.append(_Domain("tp_replicated", replicated, world_group, 1.0 / dp_size, shard, device, pdtype,
-                                            bucket_elems, state_dtype, symmetric))
+                                            bucket_elems, state_dtype, symmetric or symmetric_shards, self.reshard, unit_of))
             self._identical_scale = 1.0 / tp_size
         else:
             self._identical = []
             self.domains.append(_Domain("all", replicated + sharded, dp_group if dp_group is not None else world_group,
-                                        1.0 / dp_size, shard, device, pdtype, bucket_elems, state_dtype, symmetric))
+                                        1.0 / dp_size, shard, device, pdtype, bucket_elems, state_dtype,
+                                        symmetric or symmetric_shards, self.reshard, unit_of))
         self.comm_stream = torch.cuda.Stream(device=device) if self.is_cuda else None
         self._hooks = []
         self._sync_grads = True
@@ -230,23 +400,41 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
             if ok:
                 self._fused = fused.FusedStepState(self)
                 self.comm_path = "fused"
+        if self.reshard:
+            import logging
+
+            logging.getLogger("vlm_training_b200").info(
+                f"parameters and gradients are sharded over {dp_size} data-parallel ranks: {len(self.units)} units, "
+                f"{sum(len(d.buckets) for d in self.domains if d.reshard)} buckets, "
+                f"{'own peer-pull' if symmetric_shards else 'library all-gather'} for the parameter gathers")
         if dist.is_initialized() and self.is_cuda:
             import logging
 
             logging.getLogger("vlm_training_b200").info(
                 "optimizer step: " + ("reduce-scatter + AdamW + all-gather in one NVLink kernel per bucket" if self._fused is not None
                                       else f"NCCL reduce-scatter / all-gather around the AdamW kernel ({reason or 'fused_comm is off'})"))
-        if self.is_cuda and overlap and dist.is_initialized():
+        if (self.is_cuda and overlap and dist.is_initialized()) or self.reshard:
             self._install_hooks()
+        if self.reshard:
+            self._install_unit_hooks()
         if self.is_cuda:
             self._install_forward_waits()
         self._clip_buf = torch.zeros(1, dtype=torch.float32, device=device)
+        self._barrier_buf = torch.zeros(1, dtype=torch.float32, device=device)
         self.last_grad_norm = None
 
     # ------------------------------------------------------------------ torch.optim surface
     def zero_grad(self, set_to_none: bool = False):
         for d in self.domains:
-            if getattr(d, "grads_clean", False):
+            if d.reshard:
+                clean = getattr(d, "grads_clean", False)
+                d.grads_clean = False
+                for b in d.buckets:
+                    if not clean:
+                        d.grad_shard[b.index].zero_()
+                    if b.unit < 0:
+                        d.bucket_grad[b.index].zero_()
+            elif getattr(d, "grads_clean", False):
                 d.grads_clean = False  # the AdamW kernel of the last step() cleared every gradient it consumed
             elif self.is_cuda:
                 from ..ops import cuda as cu
@@ -276,7 +464,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
 
     def _make_hook(self, d, b):
         def hook(p):
-            if not self._sync_grads:
+            if not self._sync_grads and not d.reshard:
                 return
             # once per parameter and step: a weight-gradient GEMM that adds into the flat buffer itself reports the
             # parameter by hand (`_vlmt_grad_ready`), and autograd may report it again with nothing to accumulate
@@ -310,6 +498,56 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
             if any(p is not None for p in mod._parameters.values()):
                 self._hooks.append(mod.register_forward_pre_hook(pre_hook))
 
+    # ------------------------------------------------------------------ residency of sharded parameters (reshard mode)
+    def _unit_buckets(self, u: int):
+        for d in self.domains:
+            if d.reshard:
+                for b in d.buckets:
+                    if b.unit == u:
+                        yield d, b
+
+    def _enter_unit(self, u: int, backward: bool):
+        """Unit ``u`` is about to run: its parameters become resident (and, before a backward pass, its gradient buckets);
+        the other units' parameters are released unless forward passes keep them (``reshard_after_forward`` off)."""
+        if backward or self.reshard_after_forward:
+            for d in self.domains:
+                if d.reshard:
+                    for b in d.buckets:
+                        if b.unit >= 0 and b.unit != u:
+                            d.release_params(b)
+        for d, b in self._unit_buckets(u):
+            d.materialize_params(b)
+            if backward:
+                d.materialize_grads(b)
+
+    def _install_unit_hooks(self):
+        for u, mod in enumerate(self.units):
+            self._hooks.append(mod.register_forward_pre_hook(lambda m, a, u=u: self._enter_unit(u, False)))
+            self._hooks.append(mod.register_full_backward_pre_hook(lambda m, g, u=u: self._enter_unit(u, True)))
+
+    def release_all(self):
+        for d in self.domains:
+            if d.reshard:
+                for b in d.buckets:
+                    d.release_params(b)
+
+    def all_resident(self):
+        """Context manager: every parameter is whole while it is active (checkpoints, evaluation, weight surgery)."""
+        engine = self
+
+        class _Ctx:
+            def __enter__(self_inner):
+                for d in engine.domains:
+                    if d.reshard:
+                        for b in d.buckets:
+                            d.materialize_params(b)
+                return engine
+
+            def __exit__(self_inner, *exc):
+                engine.release_all()
+                return False
+        return _Ctx()
+
     def wait_all_gathers(self):
         if not self.is_cuda:
             return
@@ -324,7 +562,9 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         b.reduced = True
         if d.size == 1 or not dist.is_initialized():
             return
-        g = d.flat_grad[b.start:b.end]
+        if d.reshard:
+            d.materialize_grads(b)   # a bucket none of whose parameters got a gradient this pass: zeros
+        g = d.bucket_grad_view(b)
         if self._identical and d.name == "tp_replicated":
             for p in b.params:
                 if getattr(p, "_tp_grad", "partial") == "identical":
@@ -337,10 +577,33 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                 self._collective_reduce(d, b, g)
                 b.reduce_event = torch.cuda.Event()
                 b.reduce_event.record(self.comm_stream)
+            if d.reshard:
+                d.release_grads(b, stream=self.comm_stream)
         else:
             self._collective_reduce(d, b, g)
+            if d.reshard:
+                d.release_grads(b)
+        if d.reshard:   # ready for the next micro-batch of the accumulation window
+            b.pending = len(b.params)
+            b.seen.clear()
+            b.reduced = False
 
     def _collective_reduce(self, d, b, g):
+        if d.reshard:
+            # reduce-scatter into a temporary, added to the gradient shard (micro-batches of an accumulation window
+            # are reduced one by one: the full-size gradients do not outlive their unit's backward pass)
+            lo, hi = d.shard_range(b)
+            shard = d.grad_shard[b.index]
+            if g.is_cuda:
+                tmp = torch.empty_like(shard)
+                dist.reduce_scatter_tensor(tmp, g, op=dist.ReduceOp.SUM, group=d.group)
+                shard.add_(tmp)
+            else:
+                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=d.group)
+                shard.add_(g[lo - b.start:hi - b.start])
+            if b.unit < 0:
+                g.zero_()   # the root unit's gradient buckets stay allocated: ready for the next pass
+            return
         if d.shard and g.is_cuda:
             lo, hi = d.shard_range(b)
             dist.reduce_scatter_tensor(d.flat_grad[lo:hi], g, op=dist.ReduceOp.SUM, group=d.group)
@@ -351,6 +614,8 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
     def finish_grad_sync(self):
         for d in self.domains:
             for b in d.buckets:
+                if d.reshard and not b.seen:
+                    continue   # nothing left to reduce: complete buckets were reduced (and reset) by the gradient hooks
                 if not b.reduced:
                     self._reduce_bucket(d, b)
         if self.is_cuda:
@@ -382,12 +647,25 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                     if e <= s:
                         continue
                     pg = self.param_groups[seg.group]
-                    self._adamw(d, bi, s - lo, e - lo, d.flat_grad[s:e], d.flat_param[s:e], pg["lr"], pg["weight_decay"],
-                                b1, b2, d.grad_scale * clip)
-                self._gather_bucket(d, b)
+                    self._adamw(d, bi, s - lo, e - lo, d.shard_grad_view(b, s, e), d.shard_param_view(b, s, e), pg["lr"],
+                                pg["weight_decay"], b1, b2, d.grad_scale * clip)
+                if not d.reshard:
+                    self._gather_bucket(d, b)
+            if d.reshard:
+                # every rank's shards are final before anybody gathers from them again (one tiny stream-ordered collective),
+                # then the always-resident root unit gets its new parameters
+                if dist.is_initialized() and d.size > 1:
+                    dist.all_reduce(self._barrier_buf, group=d.group)
+                for b in d.buckets:
+                    if b.unit < 0:
+                        d.gather_params(b)
+                d.grads_clean = self.is_cuda and d.param_dtype == torch.bfloat16
+                continue
             # on this path every rank's kernel clears the gradients it consumed; when each rank consumes the whole
             # buffer (one rank, or unsharded data parallelism) the next zero_grad() has nothing left to do
             d.grads_clean = self.is_cuda and d.flat_param.dtype == torch.bfloat16 and (d.size == 1 or not d.shard)
+        if self.reshard:
+            self.release_all()
 
     def _adamw(self, d, bi, s, e, grad, param, lr, wd, b1, b2, grad_scale):
         master, m, v = d.master[bi][s:e], d.exp_avg[bi][s:e], d.exp_avg_sq[bi][s:e]
@@ -429,7 +707,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         for d in self.domains:
             for b in d.buckets:
                 lo, hi = d.shard_range(b)
-                g = d.flat_grad[lo:hi]
+                g = d.shard_grad_view(b, lo, hi)
                 if self.is_cuda and g.dtype in (torch.bfloat16, torch.float32):
                     from ..ops import cuda as cu
 
@@ -467,24 +745,41 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                 for t in dst:
                     t.copy_(s[name][off:off + t.numel()])
                     off += t.numel()
-            # parameters follow the master copy
-            for bi, b in enumerate(d.buckets):
-                lo, hi = d.shard_range(b)
-                d.flat_param[lo:hi].copy_(d.master[bi])
-                self._gather_bucket(d, b)
-        self.wait_all_gathers()
+        self.params_from_master()
 
-    def resync_master_from_params(self):
-        """Re-read the master weights from the (bf16) parameters, e.g. after loading a model checkpoint."""
+    def params_from_master(self):
+        """The bf16 parameters follow the fp32 master copy (after loading optimizer state)."""
         with torch.no_grad():
             for d in self.domains:
                 for bi, b in enumerate(d.buckets):
                     lo, hi = d.shard_range(b)
-                    d.master[bi].copy_(d.flat_param[lo:hi])
+                    d.shard_param_view(b, lo, hi).copy_(d.master[bi])
+                    if d.reshard:
+                        if d.resident[b.index]:
+                            d.gather_params(b)
+                    else:
+                        self._gather_bucket(d, b)
+        self.wait_all_gathers()
+
+    def resync_master_from_params(self):
+        """Re-read the master weights from the (bf16) parameters, e.g. after loading a model checkpoint (in reshard mode
+        inside ``all_resident()``: the parameters must be whole to be read)."""
+        with torch.no_grad():
+            for d in self.domains:
+                for bi, b in enumerate(d.buckets):
+                    lo, hi = d.shard_range(b)
+                    if d.reshard:
+                        d.param_shard[b.index].copy_(d.bucket_param[b.index][lo - b.start:hi - b.start])
+                    d.master[bi].copy_(d.shard_param_view(b, lo, hi))
 
     def memory_bytes(self) -> dict:
         tot = {"param": 0, "grad": 0, "optimizer": 0}
         for d in self.domains:
+            if d.reshard:   # what is held right now: shards plus the buckets whose storage is live
+                for i in range(len(d.buckets)):
+                    tot["param"] += d.param_shard[i].numel() * d.param_shard[i].element_size() + d.bucket_param[i].untyped_storage().size()
+                    tot["grad"] += d.grad_shard[i].numel() * d.grad_shard[i].element_size() + d.bucket_grad[i].untyped_storage().size()
+                continue
             tot["param"] += d.flat_param.numel() * d.flat_param.element_size()
             tot["grad"] += d.flat_grad.numel() * d.flat_grad.element_size()
             for t in d.master + d.exp_avg + d.exp_avg_sq:

@@ -198,13 +198,7 @@ def load_optimizer_state_from_dcp(engine, state: dict, tp_rank: int = 0):
         pg.update({k: v for k, v in saved.items() if k in ("lr", "initial_lr", "weight_decay")})
     # tensors were loaded in place (by DCP through the DTensors that wrap the engine's own buffers, or by the
     # resharding loader); the bf16 parameters follow the master copy
-    with torch.no_grad():
-        for d in engine.domains:
-            for bi, b in enumerate(d.buckets):
-                lo, hi = d.shard_range(b)
-                d.flat_param[lo:hi].copy_(d.master[bi])
-                engine._gather_bucket(d, b)
-    engine.wait_all_gathers()
+    engine.params_from_master()
 
 
 # ----------------------------------------------------------------------------- save / load

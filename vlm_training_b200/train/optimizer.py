@@ -47,4 +47,5 @@ def create_optimizer(model, tcfg, mesh, *, fused_comm: bool = False) -> ShardedO
         mode="fsdp" if tcfg.data_parallel == "fsdp" else "ddp", betas=(tcfg.beta1, tcfg.beta2), eps=tcfg.eps,
         max_grad_norm=tcfg.max_grad_norm if tcfg.clip_grad else None,
         state_dtype=torch.bfloat16 if tcfg.optimizer_state_dtype == "bf16" else torch.float32,
-        fused_comm=fused_comm)
+        fused_comm=fused_comm, reshard=bool(getattr(tcfg, "reshard_params", False)),
+        reshard_after_forward=bool(getattr(tcfg, "reshard_after_forward", True)))

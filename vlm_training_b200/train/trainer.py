@@ -349,13 +349,15 @@ class Trainer:
         m = self.flush_metrics()  # counters are final and the device status word of the last step has been checked
         if m is not None:
             self._flushed.append(m)
-        return ckpt.save_checkpoint(self.cfg.training.output_dir, self.global_step, self.model, self.optimizer, self.scheduler,
-                                    {"tokens_seen": self.tokens_seen, "tokens_seen_assistant": self.tokens_seen_assistant},
-                                    tp_rank=self.mesh.tp_rank)
+        with self.optimizer.all_resident():   # sharded parameters are gathered for the model's state dict
+            return ckpt.save_checkpoint(self.cfg.training.output_dir, self.global_step, self.model, self.optimizer, self.scheduler,
+                                        {"tokens_seen": self.tokens_seen, "tokens_seen_assistant": self.tokens_seen_assistant},
+                                        tp_rank=self.mesh.tp_rank)
 
     def load_checkpoint(self, step: int):
-        c = ckpt.load_checkpoint(self.cfg.training.output_dir, step, self.model, self.optimizer, self.scheduler,
-                                 tp_rank=self.mesh.tp_rank)
+        with self.optimizer.all_resident():
+            c = ckpt.load_checkpoint(self.cfg.training.output_dir, step, self.model, self.optimizer, self.scheduler,
+                                     tp_rank=self.mesh.tp_rank)
         self.global_step = c["step"]
         self.tokens_seen, self.tokens_seen_assistant = c["tokens_seen"], c["tokens_seen_assistant"]
 
