@@ -226,6 +226,8 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     launches = cu.LAUNCHES["count"] - launches0
     peak_mem = torch.cuda.max_memory_allocated() / 2 ** 30
+    free_b, total_b = torch.cuda.mem_get_info()
+    dev_used = (total_b - free_b) / 2 ** 30   # includes symmetric-memory buffers, which the caching allocator does not count
     global_tokens = sum_over_dp(tokens_per_step)
     value = global_tokens * args.steps / (ms / 1e3)
     cu.check_status()
@@ -276,7 +278,7 @@ def run_ours(args):
                        "l2": "not flushed: every step streams >17 GB of weights, far above the 126 MB L2",
                        "layers_override": args.layers or None, "ce_chunk": args.ce_chunk,
                        "reshard_params": bool(args.reshard)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem, "final_loss": float(loss.item()),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem, "device_mem_used_gib": dev_used, "final_loss": float(loss.item()),
         }
         print(json.dumps(line))
     if dist.is_initialized():

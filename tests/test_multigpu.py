@@ -21,12 +21,14 @@ from vlm_training_b200.train.trainer import Trainer
 cfg = ConfigManager(Config).parse_args(sys.argv[1:])
 tr = Trainer(cfg)
 hist = tr.train()
-if tr.rank == 0:
-    os.makedirs(cfg.training.output_dir, exist_ok=True)
-    json.dump([m["train/loss"] for m in hist], open(os.path.join(cfg.training.output_dir, "losses.json"), "w"))
+with tr.optimizer.all_resident():      # sharded parameters are gathered (a collective: every rank enters)
     # a sample of updated weights: Adam hides a wrong gradient SCALE, but a wrongly weighted sum flips update signs
     probe = torch.cat([p.detach().float().flatten()[:512] for n, p in tr.model.named_parameters()
                        if n.endswith("down_proj.weight") or n.endswith("lm_head.weight") or "merger.linear_fc2.weight" in n])
+    torch.cuda.synchronize()
+if tr.rank == 0:
+    os.makedirs(cfg.training.output_dir, exist_ok=True)
+    json.dump([m["train/loss"] for m in hist], open(os.path.join(cfg.training.output_dir, "losses.json"), "w"))
     json.dump(probe.tolist(), open(os.path.join(cfg.training.output_dir, "probe.json"), "w"))
 if torch.distributed.is_initialized():
     torch.distributed.destroy_process_group()
@@ -46,7 +48,10 @@ def _run(tmp_path, nproc, extra, port, env_extra=None):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", VLMT_PG_TIMEOUT_S="120")
     env.update(env_extra or {})
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env, cwd=ROOT)
-    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    if res.returncode != 0:
+        err = res.stderr
+        cut = err.find("Traceback")
+        raise AssertionError(res.stdout[-1500:] + err[max(0, cut - 200):cut + 3500])
     _run.last_probe = json.load(open(out / "probe.json"))
     return json.load(open(out / "losses.json"))
 

@@ -390,6 +390,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                                         1.0 / dp_size, shard, device, pdtype, bucket_elems, state_dtype,
                                         symmetric or symmetric_shards, self.reshard, unit_of))
         self.comm_stream = torch.cuda.Stream(device=device) if self.is_cuda else None
+        self.gather_stream = torch.cuda.Stream(device=device) if self.is_cuda else None
         self._hooks = []
         self._sync_grads = True
         self._fused = None
@@ -415,6 +416,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                                       else f"NCCL reduce-scatter / all-gather around the AdamW kernel ({reason or 'fused_comm is off'})"))
         if (self.is_cuda and overlap and dist.is_initialized()) or self.reshard:
             self._install_hooks()
+        self._bwd_phase, self._prefetched = False, -1
         if self.reshard:
             self._install_unit_hooks()
         if self.is_cuda:
@@ -508,17 +510,38 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
 
     def _enter_unit(self, u: int, backward: bool):
         """Unit ``u`` is about to run: its parameters become resident (and, before a backward pass, its gradient buckets);
-        the other units' parameters are released unless forward passes keep them (``reshard_after_forward`` off)."""
+        the other units' parameters are released unless forward passes keep them (``reshard_after_forward`` off); the
+        unit that runs next (the following one in a forward pass, the preceding one in a backward pass) is gathered on
+        the communication stream meanwhile."""
+        if backward:
+            self._bwd_phase = True
         if backward or self.reshard_after_forward:
             for d in self.domains:
                 if d.reshard:
                     for b in d.buckets:
-                        if b.unit >= 0 and b.unit != u:
+                        if b.unit >= 0 and b.unit != u and not (b.gather_event is not None and b.unit == self._prefetched):
                             d.release_params(b)
         for d, b in self._unit_buckets(u):
+            if b.gather_event is not None:   # gathered ahead of time on the communication stream
+                if self.is_cuda:
+                    torch.cuda.current_stream().wait_event(b.gather_event)
+                    d.bucket_param[b.index].record_stream(torch.cuda.current_stream())
+                b.gather_event = None
             d.materialize_params(b)
             if backward:
                 d.materialize_grads(b)
+        nxt = u - 1 if self._bwd_phase else u + 1
+        if self.is_cuda and 0 <= nxt < len(self.units) and (backward or not self._bwd_phase):
+            self._prefetched = nxt
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            with torch.cuda.stream(self.gather_stream):   # its own stream: never queued behind a gradient reduce-scatter
+                self.gather_stream.wait_event(ev)
+                for d, b in self._unit_buckets(nxt):
+                    if not d.resident[b.index]:
+                        d.materialize_params(b)
+                        b.gather_event = torch.cuda.Event()
+                        b.gather_event.record(self.gather_stream)
 
     def _install_unit_hooks(self):
         for u, mod in enumerate(self.units):
@@ -529,6 +552,9 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         for d in self.domains:
             if d.reshard:
                 for b in d.buckets:
+                    if b.gather_event is not None and self.is_cuda:
+                        torch.cuda.current_stream().wait_event(b.gather_event)
+                    b.gather_event = None
                     d.release_params(b)
 
     def all_resident(self):
@@ -666,6 +692,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
             d.grads_clean = self.is_cuda and d.flat_param.dtype == torch.bfloat16 and (d.size == 1 or not d.shard)
         if self.reshard:
             self.release_all()
+            self._bwd_phase, self._prefetched = False, -1
 
     def _adamw(self, d, bi, s, e, grad, param, lr, wd, b1, b2, grad_scale):
         master, m, v = d.master[bi][s:e], d.exp_avg[bi][s:e], d.exp_avg_sq[bi][s:e]
