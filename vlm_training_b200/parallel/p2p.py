@@ -68,6 +68,12 @@ class P2PComm:
         if old is not None:
             symm.release(old)
 
+    def reserve(self, n: int):
+        """Make every staging slot hold at least ``n`` elements now (at set-up, from the model's sizes), so that no
+        collective of the training loop has to grow the ring, which costs a device synchronisation and a barrier."""
+        if n > self.slot_elems:
+            self._alloc(n)
+
     def _slot(self, n: int):
         if n > self.slot_elems:
             self._alloc(n)

@@ -100,6 +100,11 @@ class Trainer:
         # ---------------- parallelism (order matters: TP → AC → data parallel)
         tp_backend = "p2p" if (t.fused_comm and self.device.type == "cuda" and t.tp_size > 1) else "dist"
         self.tp_ctx = apply_tp(model, self.mesh, sequence_parallel=t.sequence_parallel, backend=tp_backend)
+        if getattr(self.tp_ctx, "p2p", None) is not None:
+            # largest message of the layer collectives: a gathered [T, hidden] activation gradient, or the vision
+            # features of a row whose tokens are all image tokens (merged + DeepStack features side by side)
+            n_feat = (1 + len(mcfg.vision.deepstack_visual_indexes)) * mcfg.vision.out_hidden_size if mcfg.vision is not None else 0
+            self.tp_ctx.p2p.reserve(self.seq_len * max(mcfg.text.hidden_size, n_feat))
         if t.ep_size > 1:
             from ..parallel.ep import apply_ep
 
