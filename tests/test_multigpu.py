@@ -219,3 +219,17 @@ def test_sharded_parameters_match_whole_parameters_on_gpus(tmp_path):
         assert sharded == pytest.approx(whole, rel=2e-3, abs=2e-3)
         frac_off = ((torch.tensor(_run.last_probe) - probe_whole).abs() > 5e-4).float().mean().item()
         assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ (fused_comm {fused})"
+
+
+def test_fused_optimizer_with_gradient_clipping_matches_nccl(tmp_path):
+    """Clipping at a norm small enough to be active every step: the two-kernel form of the NVLink optimizer step (reduced
+    shard + sum of squares, one scalar all-reduce, AdamW + parameter push with the clip factor read on the device) against
+    the NCCL path, data parallel and tensor parallel."""
+    clip = ["--training.clip_grad", "true", "--training.max_grad_norm", "0.05"]
+    for extra, ports in (([], (29731, 29732)), (["--training.tp_size", "2", "--training.sequence_parallel", "true"], (29733, 29734))):
+        nccl = _run(tmp_path, 2, clip + extra + ["--training.fused_comm", "false"], ports[0])
+        probe_nccl = torch.tensor(_run.last_probe)
+        fused = _run(tmp_path, 2, clip + extra + ["--training.fused_comm", "true"], ports[1], {"VLMT_NO_MULTIMEM": "1"})
+        assert fused == pytest.approx(nccl, rel=3e-3, abs=3e-3)
+        frac_off = ((torch.tensor(_run.last_probe) - probe_nccl).abs() > 5e-4).float().mean().item()
+        assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ"

@@ -34,6 +34,36 @@ static void fused_rs_adamw_ag(const std::vector<int64_t>& grad_ptrs, const std::
   TORCH_CHECK(r == 0, "vlmt_fused_rs_adamw_ag failed with code ", r);
 }
 
+static void rs_reduce_sumsq(const std::vector<int64_t>& grad_ptrs, int64_t grad_mc, int64_t lo, int64_t hi, Tensor& red, int64_t red_off,
+                            Tensor& sumsq) {
+  const int world = (int)grad_ptrs.size();
+  TORCH_CHECK(world <= 16 && red.scalar_type() == at::kFloat && sumsq.scalar_type() == at::kFloat && lo % 8 == 0 && hi % 8 == 0);
+  c10::cuda::CUDAGuard guard(red.device());
+  void* g[16];
+  for (int i = 0; i < world; ++i) g[i] = reinterpret_cast<void*>(grad_ptrs[i]);
+  int r = vlmt_rs_reduce_sumsq(g, reinterpret_cast<void*>(grad_mc), world, lo, hi, red.data_ptr<float>() + red_off, sumsq.data_ptr<float>(),
+                               vlmt_status_tensor().data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_rs_reduce_sumsq failed with code ", r);
+}
+static void adamw_push(const Tensor& red, int64_t red_off, const Tensor& sumsq, double max_norm, const std::vector<int64_t>& param_ptrs,
+                       int64_t param_mc, int64_t lo, int64_t hi, Tensor& master, Tensor& m, Tensor& v, int64_t state_off, double lr,
+                       double b1, double b2, double eps, double wd, double bc1, double bc2, double grad_scale) {
+  const int world = (int)param_ptrs.size();
+  TORCH_CHECK(world <= 16 && master.scalar_type() == at::kFloat && m.scalar_type() == v.scalar_type());
+  TORCH_CHECK(m.scalar_type() == at::kFloat || m.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(master.device());
+  void* p[16];
+  for (int i = 0; i < world; ++i) p[i] = reinterpret_cast<void*>(param_ptrs[i]);
+  const bool sb = m.scalar_type() == at::kBFloat16;
+  const int64_t esz = sb ? 2 : 4;
+  int r = vlmt_adamw_push(red.data_ptr<float>() + red_off, sumsq.data_ptr<float>(), (float)max_norm, p, reinterpret_cast<void*>(param_mc),
+                          world, lo, hi, master.data_ptr<float>() + state_off, static_cast<char*>(m.data_ptr()) + state_off * esz,
+                          static_cast<char*>(v.data_ptr()) + state_off * esz, sb ? 1 : 0, (float)lr, (float)b1, (float)b2, (float)eps,
+                          (float)wd, (float)bc1, (float)bc2, (float)grad_scale, vlmt_status_tensor().data_ptr<int>(),
+                          at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_adamw_push failed with code ", r);
+}
+
 static void peer_sum_rows(const std::vector<int64_t>& partial_ptrs, int64_t row0, const c10::optional<Tensor>& residual, Tensor& out) {
   c10::cuda::CUDAGuard guard(out.device());
   void* p[16];
@@ -103,5 +133,7 @@ void bind_comm(pybind11::module_& m) {
   m.def("pull_gather", &pull_gather);
   m.def("pull_reduce", &pull_reduce);
   m.def("fused_rs_adamw_ag", &fused_rs_adamw_ag);
+  m.def("rs_reduce_sumsq", &rs_reduce_sumsq);
+  m.def("adamw_push", &adamw_push);
   m.def("peer_sum_rows", &peer_sum_rows);
 }

@@ -126,6 +126,85 @@ __global__ void fused_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, void* 
   }
 }
 
+// ---- the same step in two kernels, for gradient clipping (the global norm must be known before the first update) ----
+// reduce: red[i] = sum over ranks of grad_r[lo + i] (kept in fp32), sumsq += sum red[i]^2 (one atomicAdd per block)
+template <bool MULTIMEM>
+__global__ void rs_reduce_sumsq_kernel(PeerPtrs grads, void* grad_mc, int world, long lo, long hi, float* __restrict__ red,
+                                       float* __restrict__ sumsq, const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
+  const long nvec = (hi - lo) >> 3;
+  float local = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    const long e = lo + (i << 3);
+    float g[8];
+    if (MULTIMEM) {
+      unpack8(multimem_ld_reduce_bf16x8(reinterpret_cast<const bf16*>(grad_mc) + e), g);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        float t[8];
+        unpack8(ld_peer_16B(reinterpret_cast<const bf16*>(grads.p[r]) + e), t);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] += t[k];
+      }
+    }
+    store_state8(red + (i << 3), g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) local += g[k] * g[k];
+  }
+  __shared__ float warp_part[8];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += warp_part[w];
+    atomicAdd(sumsq, t);
+  }
+}
+
+// update: AdamW on the shard from the reduced gradient `red`, scaled by grad_scale and by the clip factor
+// min(1, max_norm / (grad_scale * sqrt(*sumsq) + 1e-6)) read from device memory; new parameters go to every rank
+template <bool MULTIMEM, typename ST>
+__global__ void adamw_push_kernel(const float* __restrict__ red, const float* __restrict__ sumsq, float max_norm, PeerPtrs params,
+                                  void* param_mc, int world, long lo, long hi, float* __restrict__ master, ST* __restrict__ m,
+                                  ST* __restrict__ v, AdamArgs a, const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
+  const float norm = a.grad_scale * sqrtf(*sumsq);
+  const float clip = fminf(1.f, max_norm / (norm + 1e-6f));
+  const float gs = a.grad_scale * clip;
+  const long nvec = (hi - lo) >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    const long e = lo + (i << 3);
+    const long s = i << 3;
+    float g[8], pm[8], mm[8], vv[8];
+    load_state8(red + s, g);
+    load_state8(master + s, pm);
+    load_state8(m + s, mm);
+    load_state8(v + s, vv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = g[k] * gs;
+      mm[k] = a.b1 * mm[k] + (1.f - a.b1) * gk;
+      vv[k] = a.b2 * vv[k] + (1.f - a.b2) * gk * gk;
+      float p = pm[k] * (1.f - a.lr * a.wd);
+      p -= a.lr * (mm[k] / a.bc1) / (sqrtf(vv[k] / a.bc2) + a.eps);
+      pm[k] = p;
+    }
+    store_state8(master + s, pm);
+    store_state8(m + s, mm);
+    store_state8(v + s, vv);
+    const uint4 packed = pack8(pm);
+    if (MULTIMEM) {
+      multimem_st_16B(reinterpret_cast<bf16*>(param_mc) + e, packed);
+    } else {
+      for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(params.p[r]) + e) = packed;
+    }
+  }
+}
+
 // out[row, :] = (residual ? residual[row, :] : 0) + sum_r partial_r[row0 + row, :]   (bf16, fp32 accumulation)
 __global__ void peer_sum_rows_kernel(PeerPtrs partials, int world, long row0, long rows, int D, const bf16* __restrict__ residual,
                                      bf16* __restrict__ out) {
@@ -311,6 +390,38 @@ int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void
                                                                 master, reinterpret_cast<ST*>(m), reinterpret_cast<ST*>(v), a, status, zero_own)
   if (state_bf16) { if (mc) LAUNCH(true, bf16); else LAUNCH(false, bf16); }
   else { if (mc) LAUNCH(true, float); else LAUNCH(false, float); }
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+int vlmt_rs_reduce_sumsq(void* const* grad_ptrs, void* grad_mc, int world, long lo, long hi, float* red, float* sumsq, const int* status,
+                         cudaStream_t st) {
+  if (world > MAX_PEERS) return -1;
+  if ((lo & 7) || (hi & 7)) return -2;
+  if (hi <= lo) return 0;
+  PeerPtrs g;
+  for (int r = 0; r < world; ++r) g.p[r] = grad_ptrs[r];
+  long blocks = (((hi - lo) >> 3) + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (grad_mc) rs_reduce_sumsq_kernel<true><<<(int)blocks, 256, 0, st>>>(g, grad_mc, world, lo, hi, red, sumsq, status);
+  else rs_reduce_sumsq_kernel<false><<<(int)blocks, 256, 0, st>>>(g, nullptr, world, lo, hi, red, sumsq, status);
+  return (int)cudaGetLastError();
+}
+int vlmt_adamw_push(const float* red, const float* sumsq, float max_norm, void* const* param_ptrs, void* param_mc, int world, long lo,
+                    long hi, float* master, void* m, void* v, int state_bf16, float lr, float b1, float b2, float eps, float wd, float bc1,
+                    float bc2, float grad_scale, const int* status, cudaStream_t st) {
+  if (world > MAX_PEERS) return -1;
+  if ((lo & 7) || (hi & 7)) return -2;
+  if (hi <= lo) return 0;
+  PeerPtrs p;
+  for (int r = 0; r < world; ++r) p.p[r] = param_ptrs[r];
+  AdamArgs a{lr, b1, b2, eps, wd, bc1, bc2, grad_scale};
+  long blocks = (((hi - lo) >> 3) + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+#define LAUNCH(MC, ST)                                                                                                   \
+  adamw_push_kernel<MC, ST><<<(int)blocks, 256, 0, st>>>(red, sumsq, max_norm, p, MC ? param_mc : nullptr, world, lo, hi, master, \
+                                                         reinterpret_cast<ST*>(m), reinterpret_cast<ST*>(v), a, status)
+  if (state_bf16) { if (param_mc) LAUNCH(true, bf16); else LAUNCH(false, bf16); }
+  else { if (param_mc) LAUNCH(true, float); else LAUNCH(false, float); }
 #undef LAUNCH
   return (int)cudaGetLastError();
 }

@@ -15,6 +15,15 @@ extern "C" {
 int vlmt_fused_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* grad_mc, void* param_mc, int world, long lo, long hi,
                            float* master, void* m, void* v, int state_bf16, float lr, float b1, float b2, float eps, float wd, float bc1,
                            float bc2, float grad_scale, int zero_own, const int* status, cudaStream_t st);
+// The same step split in two for gradient clipping.  Pass 1: red[0 : hi - lo] (fp32) = sum over ranks of the gradients of this
+// rank's shard, *sumsq += sum red^2.  Pass 2 (after the ranks' partial sums of squares have been added up into *sumsq):
+// AdamW from `red` with the gradients scaled by grad_scale * min(1, max_norm / (grad_scale * sqrt(*sumsq) + 1e-6)), new
+// parameters stored to every rank.  Both return at once when *status is non-zero.
+int vlmt_rs_reduce_sumsq(void* const* grad_ptrs, void* grad_mc, int world, long lo, long hi, float* red, float* sumsq, const int* status,
+                         cudaStream_t st);
+int vlmt_adamw_push(const float* red, const float* sumsq, float max_norm, void* const* param_ptrs, void* param_mc, int world, long lo,
+                    long hi, float* master, void* m, void* v, int state_bf16, float lr, float b1, float b2, float eps, float wd, float bc1,
+                    float bc2, float grad_scale, const int* status, cudaStream_t st);
 // out[rows, D] = residual + sum over ranks of partial_r[row0 : row0 + rows, :]
 int vlmt_peer_sum_rows(void* const* partial_ptrs, int world, long row0, long rows, int D, const void* residual, void* out, cudaStream_t st);
 // Signalled peer-to-peer collectives over symmetric staging slots (protocol: comm_kernels.cu).

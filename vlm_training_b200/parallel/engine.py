@@ -363,8 +363,6 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
             # decided before the buffers are allocated: the one-kernel path needs them in symmetric memory
             if state_dtype not in (torch.float32, torch.bfloat16):
                 fused_comm, reason = False, f"the fused kernel keeps fp32 or bf16 Adam moments, optimizer_state_dtype is {state_dtype}"
-            elif max_grad_norm is not None:
-                fused_comm, reason = False, "gradient clipping needs the global norm before the first update"
         symmetric = fused_comm and self.is_cuda and dist.is_initialized()
         if experts:
             # expert-parallel parameters: each rank owns different experts, whose gradients already hold the

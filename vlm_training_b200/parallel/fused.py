@@ -18,6 +18,11 @@ optimizer step number:
   rank waits for all ``DONE`` signals: all pushes have landed and nobody still reads this step's gradients.
 
 Every wait is bounded (``VLMT_FLAG_WAIT_MS``, default 20 s) and reports through the status word instead of hanging.
+
+Gradient clipping needs the global norm before the first update, so with ``max_grad_norm`` the step is two kernels per
+bucket: the reduce-scatter half runs from the gradient hooks as above (it keeps the reduced shard in fp32 and adds its
+sum of squares to a device scalar), then one small all-reduce of that scalar, then the AdamW + all-gather half of every
+bucket, which reads the clip factor from device memory — still no host read and no library collective on the buckets.
 """
 from __future__ import annotations
 
@@ -57,6 +62,12 @@ class FusedStepState:
                 dist.barrier(group=d.group)
         self.step = 0          # number of the optimizer step whose buckets are being processed
         self.processed = set()
+        self.clip = engine.max_grad_norm is not None
+        if self.clip:
+            self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+            for info in self.domains:
+                d = info["domain"]
+                info["red"] = [torch.empty(d.shard_range(b)[1] - d.shard_range(b)[0], dtype=torch.float32, device=dev) for b in d.buckets]
 
     def info_of(self, d):
         for info in self.domains:
@@ -120,20 +131,45 @@ def process_bucket(engine, d, bi: int):
         else:
             g_ptrs, p_ptrs, g_mc, p_mc = [d.flat_grad.data_ptr()], [d.flat_param.data_ptr()], 0, 0
         lo, hi = d.shard_range(b)
-        for seg in b.segments:
-            s, e = max(seg.start, lo), min(seg.end, hi)
-            if e <= s:
-                continue
-            # parameters start on 8-element boundaries; a segment's tail may not end on one: the padding behind it
-            # holds zero gradients, so rounding the end up is harmless
-            e = min(hi, (e + 7) // 8 * 8)
-            pg = engine.param_groups[seg.group]
+        if st.clip:
+            # first half only: the reduced shard (fp32) and its sum of squares; the update follows in finish_step
+            cu._C.rs_reduce_sumsq([p + b.start * esz for p in g_ptrs], (g_mc + b.start * esz) if g_mc else 0, lo - b.start, hi - b.start,
+                                  info["red"][bi], 0, st.sumsq)
+            cu._tick()
+            return
+        _update_segments(engine, d, bi, g_ptrs, p_ptrs, g_mc, p_mc, world)
+
+
+def _update_segments(engine, d, bi, g_ptrs, p_ptrs, g_mc, p_mc, world, red=None, sumsq=None):
+    """AdamW (+ all-gather) on this rank's shard of bucket ``bi``, one launch per learning-rate group segment."""
+    from ..ops import cuda as cu
+
+    st: FusedStepState = engine._fused
+    b = d.buckets[bi]
+    esz = d.flat_grad.element_size()
+    step = st.step
+    b1, b2 = engine.betas
+    bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+    lo, hi = d.shard_range(b)
+    for seg in b.segments:
+        s, e = max(seg.start, lo), min(seg.end, hi)
+        if e <= s:
+            continue
+        # parameters start on 8-element boundaries; a segment's tail may not end on one: the padding behind it
+        # holds zero gradients, so rounding the end up is harmless
+        e = min(hi, (e + 7) // 8 * 8)
+        pg = engine.param_groups[seg.group]
+        if red is not None:
+            cu._C.adamw_push(red, s - lo, sumsq, float(engine.max_grad_norm), [p + b.start * esz for p in p_ptrs],
+                             (p_mc + b.start * esz) if p_mc else 0, s - b.start, e - b.start, d.master[bi], d.exp_avg[bi],
+                             d.exp_avg_sq[bi], s - lo, pg["lr"], b1, b2, engine.eps, pg["weight_decay"], bc1, bc2, d.grad_scale)
+        else:
             cu._C.fused_rs_adamw_ag(
                 [p + b.start * esz for p in g_ptrs], [p + b.start * esz for p in p_ptrs],
                 (g_mc + b.start * esz) if g_mc else 0, (p_mc + b.start * esz) if p_mc else 0,
                 world, s - b.start, e - b.start, d.master[bi], d.exp_avg[bi], d.exp_avg_sq[bi], s - lo,
                 pg["lr"], b1, b2, engine.eps, pg["weight_decay"], bc1, bc2, d.grad_scale, world == 1)
-            cu._tick()
+        cu._tick()
 
 
 def finish_step(engine):
@@ -147,6 +183,19 @@ def finish_step(engine):
             process_bucket(engine, d, bi)
     step = st.step
     with torch.cuda.stream(engine.comm_stream):
+        if st.clip:
+            # every rank's shards are disjoint: the global sum of squares is one all-reduce of a scalar, then the update
+            if dist.is_initialized():
+                dist.all_reduce(st.sumsq)
+            for info in st.domains:
+                d = info["domain"]
+                for bi in range(len(d.buckets)):
+                    if d.size > 1:
+                        _update_segments(engine, d, bi, None, info["p_ptrs"], 0, info["p_mc"], d.size, info["red"][bi], st.sumsq)
+                    else:
+                        _update_segments(engine, d, bi, None, [d.flat_param.data_ptr()], 0, 0, 1, info["red"][bi], st.sumsq)
+            engine.last_grad_norm = st.sumsq.sqrt() * engine.domains[0].grad_scale   # a device tensor: no host read here
+            st.sumsq = torch.zeros_like(st.sumsq)
         for info in st.domains:
             d = info["domain"]
             if d.size > 1:
@@ -159,4 +208,4 @@ def finish_step(engine):
     for d in engine.domains:
         # a domain of one rank consumed (and cleared) every gradient of its buffer; with peers, each rank read only its
         # shard of every buffer, and clearing a buffer is one local pass in zero_grad() instead of stores over NVLink
-        d.grads_clean = d.size == 1
+        d.grads_clean = d.size == 1 and not st.clip
