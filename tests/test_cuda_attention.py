@@ -30,7 +30,12 @@ CASES = [
     ([700], 8, 2, 128, False),
     ([1500, 260, 40], 2, 1, 128, True),
     ([900, 130], 2, 2, 64, False),
-    ([300, 200], 4, 2, 256, True),         # head dims above 128 take the library path
+    ([128], 1, 1, 256, True),              # head size 256: the single-tile kernels (Qwen3.5 full-attention layers)
+    ([300, 200], 4, 2, 256, True),
+    ([700], 4, 1, 256, False),
+    ([1500, 260, 40, 1, 65], 2, 1, 256, True),
+    ([384, 640], 4, 4, 256, False),
+    ([500], 2, 2, 192, True),              # padded to 256
 ]
 
 
@@ -57,8 +62,9 @@ def test_attention_fwd_bwd(lens, Hq, Hkv, D, causal):
     _close(v.grad, vr.grad, 0.05, 3e-2, "dv")
 
 
-def test_attention_is_repeatable():
-    T, Hq, Hkv, D = 1000, 4, 2, 128
+@pytest.mark.parametrize("D", [128, 256])
+def test_attention_is_repeatable(D):
+    T, Hq, Hkv = 1000, 4, 2
     cu_seq = torch.tensor([0, 300, 1000], dtype=torch.int32, device=DEV)
     q, k, v = (torch.randn(T, h, D, device=DEV).bfloat16().requires_grad_() for h in (Hq, Hkv, Hkv))
     g = torch.randn(T, Hq, D, device=DEV).bfloat16()
@@ -72,14 +78,15 @@ def test_attention_is_repeatable():
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("D", [128, 256])
 @pytest.mark.parametrize("causal", [True, False])
-def test_attention_growing_scores(causal):
+def test_attention_growing_scores(causal, D):
     """Scores that keep growing along the keys make the running row max jump by far more than the lazy-rescale
     threshold several times per row, so the in-TMEM rescale of the output accumulator is exercised."""
     from vlm_training_b200.ops import cuda as cu
 
     torch.manual_seed(1)
-    lens, Hq, Hkv, D = [1100, 300], 2, 1, 128
+    lens, Hq, Hkv = [1100, 300], 2, 1
     T = sum(lens)
     cu_seq = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
     ramp = torch.linspace(0.2, 6.0, T, device=DEV)[:, None, None]

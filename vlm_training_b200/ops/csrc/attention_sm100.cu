@@ -970,9 +970,17 @@ int set_smem(K kern, int bytes) {
 
 }  // namespace
 
+// head size 256: the single-tile kernels of attention256_sm100.cu
+extern "C" int vlmt_attn256_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu, int n_docs, int T, int Hq,
+                                int Hkv, long ldq, long ldk, long ldv, float scale, int causal, int* status, cudaStream_t st);
+extern "C" int vlmt_attn256_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse, float* delta,
+                                void* dq, void* dk, void* dv, const int* cu, int n_docs, int T, int Hq, int Hkv, float scale, int causal,
+                                int* status, cudaStream_t st);
+
 extern "C" int vlmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu, int n_docs, int T, int Hq,
                              int Hkv, int D, int d_eff, long ldq, long ldk, long ldv, float scale, int causal, int* status, cudaStream_t st) {
   if (T <= 0 || n_docs <= 0) return 0;
+  if (D == 256) return vlmt_attn256_fwd(q, k, v, o, lse, cu, n_docs, T, Hq, Hkv, ldq, ldk, ldv, scale, causal, status, st);
   CUtensorMap tq, tk, tv;
   int r;
   if ((r = make_act_tmap(&tq, q, T, Hq * D, ldq))) return 1000 + r;
@@ -999,6 +1007,7 @@ extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, con
                              void* dq, void* dk, void* dv, const int* cu, int n_docs, int T, int Hq, int Hkv, int D, int d_eff, float scale,
                              int causal, int* status, cudaStream_t st) {
   if (T <= 0 || n_docs <= 0) return 0;
+  if (D == 256) return vlmt_attn256_bwd(dout, q, k, v, o, lse, delta, dq, dk, dv, cu, n_docs, T, Hq, Hkv, scale, causal, status, st);
   {
     const int warps = T * Hq;
     attn_delta_kernel<<<(warps * 32 + 255) / 256, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(dout),

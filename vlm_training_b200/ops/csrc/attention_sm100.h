@@ -8,7 +8,7 @@
 extern "C" {
 #endif
 // q [T,Hq,D], k/v [T,Hkv,D] bf16 with token strides ldq/ldk/ldv (elements); o [T,Hq,D]; lse [Hq,T] (natural log).
-// cu: int32 [n_docs+1] device pointer.  D in {64, 128}.  d_eff (<= D) says that channels >= d_eff are zero padding in
+// cu: int32 [n_docs+1] device pointer.  D in {64, 128, 256} (256: the single-tile kernels of attention256_sm100.cu; d_eff unused).  d_eff (<= D) says that channels >= d_eff are zero padding in
 // q/k/v (head dims such as 72 are stored padded to D): the contractions over the head dim (Q.K^T, dO.V^T) skip the
 // 16-channel steps that lie entirely in the padding; the MMAs whose N dimension is the head dim stay full width
 // (narrower ones measured slower).

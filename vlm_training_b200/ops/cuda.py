@@ -574,20 +574,18 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None, v
     if not hasattr(_C, "attn_fwd"):
         raise RuntimeError("the attention kernel is not part of this build of the extension")
     cu = cu_seqlens.to(torch.int32)
-    if D in (64, 128):
+    if D in (64, 128, 256):
         return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale), _mma_width(valid_dim or D, D))
     if D < 128:
         # pad the head dim with zeros to the kernel's tile width (ViT head_dim 72); the MMAs skip the padding
         o = _AttentionVarlen.apply(_pad_heads(q, 128), _pad_heads(k, 128), _pad_heads(v, 128), cu, int(max_seqlen),
                                    bool(causal), float(scale), _mma_width(D, 128))
         return o[..., :D]
-    # head dims above 128 (Qwen3.5 full-attention layers use 256) exceed the tensor-memory budget of the kernels above
-    # (two 128-row score tiles plus two output accumulators of D columns each); they run through torch's library
-    # varlen attention until a single-tile variant exists
-    from torch.nn.attention.varlen import varlen_attn
-
-    return varlen_attn(q, k, v, cu, cu, int(max_seqlen), int(max_seqlen), scale=float(scale),
-                       window_size=(-1, 0) if causal else (-1, -1))
+    if D < 256:
+        o = _AttentionVarlen.apply(_pad_heads(q, 256), _pad_heads(k, 256), _pad_heads(v, 256), cu, int(max_seqlen),
+                                   bool(causal), float(scale), 256)
+        return o[..., :D]
+    raise NotImplementedError(f"attention_varlen: head size {D} is beyond the tcgen05 kernels (64, 128, 256 and what pads to them)")
 
 
 def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None):

@@ -85,7 +85,8 @@ def bench_gemm(t: Timer, m, n, k, layout="fwd"):
     return _report(f"gemm_{layout}", [m, n, k], t(fn), flops=2.0 * m * n * k)
 
 
-def bench_attention(t: Timer, tokens, docs, hq=32, hkv=8, d=128, causal=True, backward=False):
+def bench_attention(t: Timer, tokens, docs, hq=32, hkv=8, d=128, causal=True, backward=False, library=False):
+    """``library``: time torch's varlen attention (the reference's kernel) on the same inputs instead of ours."""
     from .. import ops
 
     lens = [tokens // docs] * docs
@@ -93,14 +94,22 @@ def bench_attention(t: Timer, tokens, docs, hq=32, hkv=8, d=128, causal=True, ba
     q, k, v = (_r(tokens, h, d).requires_grad_() for h in (hq, hkv, hkv))
     g = _r(tokens, hq, d)
     fl = sum(4.0 * L * L * d * hq * (0.5 if causal else 1.0) for L in lens)
+    if library:
+        from torch.nn.attention.varlen import varlen_attn
+
+        fn = lambda: varlen_attn(q, k, v, cu_seq, cu_seq, max(lens), max(lens), window_size=(-1, 0) if causal else (-1, -1))
+        tag = "library_varlen_attn"
+    else:
+        fn = lambda: ops.attention_varlen(q, k, v, cu_seq, max(lens), causal, None)
+        tag = "attention"
     if not backward:
         with torch.no_grad():
-            ms = t(lambda: ops.attention_varlen(q, k, v, cu_seq, max(lens), causal, None))
-        return _report("attention_fwd", [tokens, docs, hq, hkv, d, int(causal)], ms, flops=fl)
+            ms = t(fn)
+        return _report(tag + "_fwd", [tokens, docs, hq, hkv, d, int(causal)], ms, flops=fl)
 
     def fb():
-        ops.attention_varlen(q, k, v, cu_seq, max(lens), causal, None).backward(g)
-    return _report("attention_fwd_bwd", [tokens, docs, hq, hkv, d, int(causal)], t(fb), flops=3.5 * fl)
+        fn().backward(g)
+    return _report(tag + "_fwd_bwd", [tokens, docs, hq, hkv, d, int(causal)], t(fb), flops=3.5 * fl)
 
 
 def bench_rmsnorm(t: Timer, rows=8192, dim=4096):
@@ -279,6 +288,9 @@ def main(argv=None):
     ap.add_argument("--docs", type=int, default=1)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--non-causal", action="store_true")
+    ap.add_argument("--heads", type=int, default=0, help="query heads of the attention benchmark (0: 32, or 16 at head size 256)")
+    ap.add_argument("--kv-heads", type=int, default=0)
+    ap.add_argument("--library", action="store_true", help="attention: time torch's varlen attention on the same inputs")
     ap.add_argument("--backward", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -288,7 +300,9 @@ def main(argv=None):
     if a.what == "gemm":
         bench_gemm(t, a.m, a.n, a.k, a.layout)
     elif a.what == "attention":
-        bench_attention(t, a.tokens, a.docs, d=a.head_dim, causal=not a.non_causal, backward=a.backward)
+        hq = a.heads or (16 if a.head_dim == 256 else 32)
+        bench_attention(t, a.tokens, a.docs, hq=hq, hkv=a.kv_heads or hq // 4, d=a.head_dim, causal=not a.non_causal,
+                        backward=a.backward, library=a.library)
     elif a.what == "rmsnorm":
         bench_rmsnorm(t, rows=a.rows)
     elif a.what == "swiglu":
@@ -324,6 +338,9 @@ def main(argv=None):
             bench_attention(t, 8192, docs)
             bench_attention(t, 8192, docs, backward=True)
         bench_attention(t, 16384, 8, hq=16, hkv=16, d=128, causal=False)
+        for docs in (1, 16):
+            bench_attention(t, 16384, docs, hq=16, hkv=4, d=256)
+            bench_attention(t, 16384, docs, hq=16, hkv=4, d=256, backward=True)
         bench_rmsnorm(t)
         bench_swiglu(t)
         bench_qkv_rope(t)
