@@ -49,6 +49,7 @@ def parse():
     ap.add_argument("--vit-ac", default="auto", choices=["auto", "off", "full"])
     ap.add_argument("--reshard", action="store_true", help="shard parameters and gradients too (ZeRO-3 residency); not the default layout")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--sync-debug", action="store_true", help="warn on every host<->device synchronisation inside the end-to-end loop")
     ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file (not a bench run)")
     return ap.parse_args()
 
@@ -191,6 +192,31 @@ def run_ours(args):
         tr.scheduler.step()
         return out.loss.detach()
 
+    # ---------------------------------------------------------------- correctness of the NVLink layer collectives (untimed)
+    tp_check = None
+    tp_ctx = getattr(tr, "tp_ctx", None)
+    if tp_ctx is not None and getattr(tp_ctx, "p2p", None) is not None:
+        # one forward + backward on the same row and weights through our own kernels (all-gather fused into the GEMM,
+        # GEMM + reduce-scatter) and through torch.distributed's NCCL collectives: loss and gradient norm must agree
+        def fwd_bwd_norm():
+            tr.optimizer.set_requires_gradient_sync(False)   # no reduction, no update: the local gradients are compared
+            out = tr.model(**staged[0])
+            out.loss.backward()
+            sq = sum(d.flat_grad.float().pow(2).sum() for d in tr.optimizer.domains)
+            dist.all_reduce(sq)
+            res = (float(out.loss.detach().item()), float(sq.sqrt().item()))
+            for d in tr.optimizer.domains:
+                d.flat_grad.zero_()
+            return res
+        p2p = tp_ctx.p2p
+        own = fwd_bwd_norm()
+        tp_ctx.p2p = None
+        lib = fwd_bwd_norm()
+        tp_ctx.p2p = p2p
+        tr.optimizer.zero_grad()
+        tp_check = {"loss_own_kernels": own[0], "loss_nccl": lib[0], "grad_norm_own_kernels": own[1], "grad_norm_nccl": lib[1],
+                    "rel_diff_loss": abs(own[0] - lib[0]) / max(abs(lib[0]), 1e-9),
+                    "rel_diff_grad_norm": abs(own[1] - lib[1]) / max(abs(lib[1]), 1e-9)}
     for i in range(args.warmup):
         one_step(staged[i % len(staged)])
     barrier()
@@ -246,12 +272,21 @@ def run_ours(args):
         barrier()
         e0.record()
         got = []
+        if args.sync_debug:
+            torch.cuda.set_sync_debug_mode("warn")
+        t_host = []
         for _ in range(args.steps):
             # every step: H2D of its batch from pinned memory, and a D2H copy of its loss / reductions / status word;
             # the host reads step k's numbers when step k + 1 has been enqueued, so the device never waits for it
+            th = time.perf_counter()
             m = tr.train_step(data_it)
+            t_host.append(round((time.perf_counter() - th) * 1e3, 1))
             if m is not None:
                 got.append(m)
+        if args.sync_debug:
+            torch.cuda.set_sync_debug_mode("default")
+            if rank == 0:
+                print(f"host ms per train_step call: {t_host}", file=sys.stderr)
         got.append(tr.flush_metrics())  # the last step's numbers: all K read-backs end inside the timed region
         e1.record()
         barrier()
@@ -280,7 +315,7 @@ def run_ours(args):
                        "l2": "not flushed: every step streams >17 GB of weights, far above the 126 MB L2",
                        "layers_override": args.layers or None, "ce_chunk": args.ce_chunk,
                        "reshard_params": bool(args.reshard)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem, "device_mem_used_gib": dev_used, "final_loss": float(loss.item()),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem, "device_mem_used_gib": dev_used, "tp_path_check": tp_check, "final_loss": float(loss.item()),
         }
         print(json.dumps(line))
     if dist.is_initialized():

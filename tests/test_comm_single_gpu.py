@@ -169,3 +169,21 @@ def test_gemm_all_gather_gives_up_when_the_peer_never_signals(short_waits):
     ref = x_loc.float() @ w.float().t()
     assert ((y[:R].float() - ref).abs().max() / ref.abs().max()).item() < 2e-2
     _still_works(cu)
+
+
+def test_debug_validation_of_index_tensors_sets_the_status_word(short_waits):
+    """``VLMT_DEBUG_CHECKS``: bad ``cu_seqlens`` / image rows / expert ids are reported through the status word (no host read
+    at the point of the check), good ones leave it alone."""
+    cu = short_waits
+    good = torch.tensor([0, 5, 5, 12], dtype=torch.int32, device="cuda")
+    cu.validate_row_indices(good, 12, torch.tensor([0, 11], device="cuda"), torch.tensor([[0, 7]], device="cuda"), 8)
+    assert cu.check_status() == 0
+    cu.validate_row_indices(torch.tensor([0, 7, 5, 12], dtype=torch.int32, device="cuda"), 12)
+    with pytest.raises(RuntimeError, match="cu_seqlens"):
+        cu.check_status()
+    cu.validate_row_indices(good, 12, torch.tensor([3, 12], device="cuda"))
+    with pytest.raises(RuntimeError, match="image-token row"):
+        cu.check_status()
+    cu.validate_row_indices(None, 12, experts=torch.tensor([[0, 8]], device="cuda"), n_experts=8)
+    with pytest.raises(RuntimeError, match="expert id"):
+        cu.check_status()

@@ -129,6 +129,16 @@ for it, (R, K, N) in enumerate([(256, 512, 384), (1024, 1024, 2048), (256, 512, 
     err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
     assert err < 2e-2, f"gemm_reduce_scatter: relative error {{err}}"
 cu.check_status()
+from vlm_training_b200.parallel import symm
+assert symm.guards_enabled() and len(symm._GUARDED) >= 3
+symm.check_guards()                      # every canary band around the peer-visible buffers is intact
+label, raw, payload = symm._GUARDED[0]
+raw[symm.GUARD_BYTES + payload + 5] = 0  # damage one byte behind a buffer (our own allocation: a legal store)
+try:
+    symm.check_guards()
+    raise SystemExit("a damaged guard band was not reported")
+except RuntimeError as exc:
+    assert "out-of-bounds store" in str(exc)
 print(f"rank {{rank}} PRIMITIVES OK worst {{worst:.2e}}", flush=True)
 dist.destroy_process_group()
 """
@@ -142,7 +152,8 @@ def test_fused_gemm_collectives_match_torch(tmp_path):
     script.write_text(PRIMITIVES.format(root=ROOT))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29711", str(script)]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", VLMT_NO_MULTIMEM="1", VLMT_PG_TIMEOUT_S="120", VLMT_FLAG_WAIT_MS="5000")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", VLMT_NO_MULTIMEM="1", VLMT_PG_TIMEOUT_S="120", VLMT_FLAG_WAIT_MS="5000",
+               VLMT_DEBUG_GUARDS="1")   # canary bands around every symmetric buffer, checked at the end
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("PRIMITIVES OK") == 2, res.stdout[-2000:]

@@ -138,6 +138,11 @@ class _CausalLMBase(nn.Module):
             raise ValueError("the vision token ids lie outside the vocabulary; an embedding lookup with them would be out of range")
         if batch_plan is None:
             batch_plan = BatchPlan.build(cfg, ids, attention_mask, image_grid_thw if pixel_values is not None else None, dev)
+        if ids.is_cuda:
+            from ..ops import cuda as _cu
+
+            if _cu.debug_checks_enabled():
+                _cu.validate_row_indices(batch_plan.cu_seqlens, T, batch_plan.image_rows)
         tp = getattr(self, "tp", None)
         sp = tp is not None and tp.enabled and tp.sequence_parallel
         if tp is not None and tp.p2p is not None and torch.is_grad_enabled():

@@ -59,6 +59,30 @@ def check_status(raise_on_error: bool = True) -> int:
     return code
 
 
+def debug_checks_enabled() -> bool:
+    return os.environ.get("VLMT_DEBUG_CHECKS", "0") == "1"
+
+
+def flag_if(bad: torch.Tensor, code: int):
+    """Record ``code`` in the device status word where ``bad`` (a boolean device scalar) is true and no earlier code is set:
+    no host read; the code surfaces with the step's metrics like a bounded wait that ran out."""
+    st = status_word()
+    st.copy_(torch.where(bad.reshape(1) & (st == 0), torch.full_like(st, code), st))
+
+
+def validate_row_indices(cu_seqlens, n_tokens: int, image_rows=None, experts=None, n_experts: int = 0):
+    """Debug aid (``VLMT_DEBUG_CHECKS=1``): the tensors from which kernels derive addresses.  ``cu_seqlens`` must start at
+    0, be non-decreasing and end within the row (status 300); image rows must lie inside the row (301); expert ids inside
+    ``[0, n_experts)`` (302).  Kernels index with these values unchecked, so a bad batch would otherwise be a stray access."""
+    if cu_seqlens is not None:
+        c = cu_seqlens.long()
+        flag_if((c[0] != 0) | (c[1:] < c[:-1]).any() | (c[-1] > n_tokens), 300)
+    if image_rows is not None and image_rows.numel():
+        flag_if((image_rows < 0).any() | (image_rows >= n_tokens).any(), 301)
+    if experts is not None and experts.numel():
+        flag_if((experts < 0).any() | (experts >= n_experts).any(), 302)
+
+
 # ------------------------------------------------------------------------------- GEMM
 def _gemm(a, b, a_mn=False, b_mn=False, bias=None, epilogue=0, out=None, accumulate=False, out_dtype=torch.bfloat16):
     M = a.shape[1] if a_mn else a.shape[0]

@@ -145,6 +145,8 @@ def moe_experts_cuda(x, gate_up, down, weights, experts):
     k = experts.shape[1]
     if not grouped_usable(x, gate_up, down):
         return _moe_experts_loop(x, gate_up, down, weights, experts)
+    if cu.debug_checks_enabled():
+        cu.validate_row_indices(None, T, experts=experts, n_experts=E)
     plan = MoePlan(experts, E, k)
     xs = _Dispatch.apply(x, plan)
     h = _GroupedLinear.apply(xs, gate_up, plan.prefix)

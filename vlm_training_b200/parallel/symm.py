@@ -15,21 +15,75 @@ import torch
 import torch.distributed as dist
 
 _HANDLES: dict[int, object] = {}
+# Debug aid (VLMT_DEBUG_GUARDS=1): every symmetric buffer is allocated with a canary band in front of and behind the
+# part that is handed out.  Peers reach these buffers by raw pointer arithmetic inside kernels, so a wrong offset or
+# count on ANY rank shows up as a damaged band on the victim; `check_guards()` (called by the trainer after every step in
+# this mode) names the buffer.  Bands cost 2 x 4 KiB per buffer and a device read per check; off by default.
+GUARD_BYTES = 4096
+_GUARD_PATTERN = 0x5A
+_GUARDED: list = []  # (label, whole uint8 view, payload bytes)
+
+
+def guards_enabled() -> bool:
+    return os.environ.get("VLMT_DEBUG_GUARDS", "0") == "1"
 
 
 def available(device) -> bool:
     return torch.device(device).type == "cuda" and dist.is_initialized()
 
 
-def symmetric_zeros(n: int, dtype, device, group) -> torch.Tensor:
+def symmetric_zeros(n: int, dtype, device, group, label: str = "") -> torch.Tensor:
     import torch.distributed._symmetric_memory as symm_mem
 
-    t = symm_mem.empty(n, dtype=dtype, device=device)
-    t.zero_()
     grp = group if group is not None else dist.group.WORLD
-    hdl = symm_mem.rendezvous(t, group=grp)
-    _HANDLES[t.data_ptr()] = hdl
+    if not guards_enabled():
+        t = symm_mem.empty(n, dtype=dtype, device=device)
+        t.zero_()
+        hdl = symm_mem.rendezvous(t, group=grp)
+        _HANDLES[t.data_ptr()] = hdl
+        return t
+    esz = torch.empty((), dtype=dtype).element_size()
+    payload = (n * esz + 255) // 256 * 256
+    raw = symm_mem.empty(payload + 2 * GUARD_BYTES, dtype=torch.uint8, device=device)
+    raw.zero_()
+    raw[:GUARD_BYTES].fill_(_GUARD_PATTERN)
+    raw[GUARD_BYTES + payload:].fill_(_GUARD_PATTERN)
+    hdl = symm_mem.rendezvous(raw, group=grp)
+    t = raw[GUARD_BYTES:GUARD_BYTES + n * esz].view(dtype)
+    _HANDLES[t.data_ptr()] = _OffsetHandle(hdl, GUARD_BYTES)
+    _GUARDED.append((label or f"symmetric buffer of {n} x {dtype}", raw, payload))
     return t
+
+
+class _OffsetHandle:
+    """A rendezvous handle whose buffer addresses point behind the leading guard band."""
+
+    def __init__(self, hdl, offset: int):
+        self._hdl, self._offset = hdl, offset
+
+    @property
+    def buffer_ptrs(self):
+        return [int(p) + self._offset for p in self._hdl.buffer_ptrs]
+
+    @property
+    def multicast_ptr(self):
+        mc = int(self._hdl.multicast_ptr)
+        return mc + self._offset if mc else 0
+
+    def __getattr__(self, name):
+        return getattr(self._hdl, name)
+
+
+def check_guards():
+    """Raise if a canary band of any guarded symmetric buffer on THIS rank has been written to (debug mode only)."""
+    for label, raw, payload in _GUARDED:
+        front = raw[:GUARD_BYTES]
+        back = raw[GUARD_BYTES + payload:]
+        bad_f = int((front != _GUARD_PATTERN).sum().item())
+        bad_b = int((back != _GUARD_PATTERN).sum().item())
+        if bad_f or bad_b:
+            raise RuntimeError(f"out-of-bounds store into peer-visible memory: {label}: {bad_f} bytes damaged in front of the "
+                               f"buffer, {bad_b} behind it")
 
 
 def handle_of(t: torch.Tensor):

@@ -312,6 +312,11 @@ class Trainer:
             cu.status_word().zero_()
             raise RuntimeError(f"step {pend['step']}: a kernel gave up on a bounded wait: {st.describe(int(status))} "
                                f"(status {int(status)}); the optimizer state of this step may be incomplete")
+        if self.device.type == "cuda" and self.world > 1:
+            from ..parallel import symm
+
+            if symm.guards_enabled():
+                symm.check_guards()   # debug mode: canary bands around every peer-visible buffer
         self.tokens_seen += int(tok_sum)
         self.tokens_seen_assistant += int(lab_sum)
         self.samples_seen += int(samp_sum)
