@@ -574,8 +574,14 @@ def test_gdn_scan_kernel_matches_loop(reverse, head_major):
     assert torch.equal(y, y2) and torch.equal(states, states2)
 
 
-def test_gated_delta_rule_scan_path_matches_reference():
-    """Head size 128 takes the scan-kernel path; outputs and all five gradients against the fp32 reference."""
+@pytest.mark.parametrize("native_chunks", [True, False])
+def test_gated_delta_rule_scan_path_matches_reference(native_chunks, monkeypatch):
+    """Head size 128 takes the scan-kernel path, with the work inside the chunks as tcgen05 kernels too or as tensor
+    operations; outputs and all five gradients against the fp32 reference."""
+    from vlm_training_b200.ops import gdn_scan
+
+    monkeypatch.setenv("VLMT_GDN_CHUNK", "1" if native_chunks else "0")
+    calls0 = dict(gdn_scan.NATIVE_CALLS)
     torch.manual_seed(11)
     T, H, D = 700, 2, 128
     cu_list = [0, 130, 130, 200, 641, 700]
@@ -599,3 +605,39 @@ def test_gated_delta_rule_scan_path_matches_reference():
     for name, a, b in zip("qkvgb", ins, ins_ref):
         scale = float(b.grad.abs().max())
         _close(a.grad, b.grad, atol=0.03 * scale + 1e-3, rtol=6e-2, what=f"gdn d{name}")
+    ran = gdn_scan.NATIVE_CALLS["forward"] - calls0["forward"], gdn_scan.NATIVE_CALLS["backward"] - calls0["backward"]
+    assert ran == ((1, 1) if native_chunks else (0, 0))
+
+
+@pytest.mark.parametrize("cu_list,H", [([0, 64, 128, 129, 512], 4), ([0, 1, 3, 1000], 3), ([0, 2048], 8), ([0, 300, 300, 900], 2)])
+def test_gated_delta_rule_native_chunks_shapes(cu_list, H):
+    """Chunk boundaries that coincide with document ends, documents of one token, a long document, rows that end before
+    the tensor does (trailing tokens belong to no document) and strided q / k / v (slices of one projection)."""
+    from vlm_training_b200.ops import gdn_scan
+
+    torch.manual_seed(5)
+    T, D = cu_list[-1] + (24 if len(cu_list) == 4 and H == 2 else 0), 128
+    cu_t = torch.tensor(cu_list, device=DEV, dtype=torch.int32)
+    proj = _rand(T, 3 * H * D).requires_grad_()
+    g = (-torch.rand(T, H, device=DEV) * 0.2).float().requires_grad_()
+    b = torch.rand(T, H, device=DEV).requires_grad_()
+    proj_ref, g_ref, b_ref = (t.detach().float().requires_grad_() for t in (proj, g, b))
+
+    def split(p):
+        q, k, v = p.split(H * D, dim=-1)
+        return q.reshape(T, H, D), k.reshape(T, H, D), v.reshape(T, H, D)
+
+    calls0 = gdn_scan.NATIVE_CALLS["forward"]
+    got = ops.gated_delta_rule(*split(proj), g, b, cu_t, None, 64, cu_host=cu_list)
+    assert gdn_scan.NATIVE_CALLS["forward"] == calls0 + 1
+    want = ref.gated_delta_rule(*split(proj_ref), g_ref, b_ref, cu_t)
+    go = _rand(T, H, D, scale=0.5)
+    got.backward(go)
+    want.backward(go.float())
+    _cu().check_status()
+    Tc = cu_list[-1]
+    _close(got[:Tc], want[:Tc], atol=0.03, rtol=4e-2, what="gdn out")
+    assert Tc == T or float(got[Tc:].detach().abs().max()) == 0.0
+    for name, a, r in (("proj", proj, proj_ref), ("g", g, g_ref), ("beta", b, b_ref)):
+        scale = float(r.grad.abs().max())
+        _close(a.grad, r.grad, atol=0.03 * scale + 1e-3, rtol=6e-2, what=f"gdn d{name}")

@@ -78,7 +78,7 @@ struct FwdParams {
   int n_docs, T, Hq, Hkv;
   float scale_log2;   // softmax scale * log2(e)
   int causal;
-  int k_steps;        // 16-channel steps of the Q.K contraction (channels beyond 16 * k_steps are zero padding)
+  int k_steps;        // 16-channel steps of the Q.K contraction and width of the P.V product (channels beyond 16 * k_steps are zero padding)
   int* status;
 };
 
@@ -171,7 +171,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(BM, D, false, true);
+      const uint32_t idesc_pv = make_idesc_bf16(BM, 16 * p.k_steps, false, true);   // only the channels that are not padding
       // S_t(j) = Q_t K_j^T.  It overwrites P_t(j-1), whose consumer P_t(j-1).V was issued earlier by this thread.
       const SmemDesc dQ0 = make_desc(smem_u32(smem + L::offQ), 16, 1024);
       const SmemDesc dK0 = make_desc(smem_u32(smem + L::offK), 16, 1024);
@@ -268,6 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           l *= alpha;
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
+            if (c * 2 >= p.k_steps) break;   // channels beyond 16 * k_steps are never accumulated
             uint32_t o[32];
             tmem_ld_32x32(o_addr + c * 32, o);
             tmem_ld_wait();
@@ -304,10 +305,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const size_t tok = (size_t)(ti.doc_start + qi);
       __nv_bfloat16* dst = p.O + (tok * p.Hq + hq) * D;
 #pragma unroll
+      const int n_out = 16 * p.k_steps;
+#pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
         tmem_ld_32x32(o_addr + c * 32, o);
         tmem_ld_wait();
+        if (c * 32 + 32 > n_out) {   // the padding channels were not accumulated: they are written as zeros
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (c * 32 + i >= n_out) o[i] = 0u;
+        }
         if (qi < ti.doc_len) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -362,7 +369,7 @@ struct BwdParams {
   int n_docs, T, Hq, Hkv;
   float scale, scale_log2;
   int causal;
-  int k_steps;        // 16-channel steps of the contractions over the head dim (Q.K and dO.V); the rest is zero padding
+  int k_steps;        // 16-channel steps of the contractions over the head dim (Q.K and dO.V) and width of dQ / dK / dV; the rest is zero padding
   int* status;
   long long* trace;  // timeline dump of CTA (0,0) (only with -DVLMT_ATTN_TRACE; nullptr otherwise)
 };
@@ -499,7 +506,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // [128 keys] x [128 queries], contraction over d
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);       // [128 keys] x [D], contraction over 128 queries
+      const uint32_t idesc_g = make_idesc_bf16(128, 16 * p.k_steps, false, true);  // [128 keys] x [channels], contraction over 128 queries
       const SmemDesc dK = make_desc(smem_u32(smem + L::offA), 16, 1024), dV = make_desc(smem_u32(smem + L::offB), 16, 1024);
       const SmemDesc dQk = make_desc(smem_u32(smem + L::offC), 16, 1024), dOk = make_desc(smem_u32(smem + L::offD), 16, 1024);         // K-major views
       const SmemDesc dQm = make_desc(smem_u32(smem + L::offC), 16384, 1024), dOm = make_desc(smem_u32(smem + L::offD), 16384, 1024);   // MN-major views
@@ -670,6 +677,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             uint32_t rr[16];
             tmem_ld_32x16(tmem_base + col + lane_addr + c0, rr);
             tmem_ld_wait();
+            if (c0 >= 16 * p.k_steps) {   // padding channels: not accumulated, written as zeros
+#pragma unroll
+              for (int u = 0; u < 16; ++u) rr[u] = 0u;
+            }
             if (key_ok) {
               __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * D + c0;
 #pragma unroll
@@ -782,7 +793,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_q = make_idesc_bf16(128, D, false, true);  // dQ = dS K: A [128 q x 128 kv] from TMEM, B = K_j [128 kv x D] MN-major
+      const uint32_t idesc_q = make_idesc_bf16(128, 16 * p.k_steps, false, true);  // dQ = dS K: A [128 q x 128 kv] from TMEM, B = K_j [128 kv x channels] MN-major
       const SmemDesc dQ = make_desc(smem_u32(smem + L::offA), 16, 1024), dO = make_desc(smem_u32(smem + L::offB), 16, 1024);
       const SmemDesc dKk = make_desc(smem_u32(smem + L::offC), 16, 1024), dVk = make_desc(smem_u32(smem + L::offD), 16, 1024);   // K-major views
       const SmemDesc dKm = make_desc(smem_u32(smem + L::offC), 16384, 1024);                                                     // MN-major view
@@ -928,6 +939,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         uint32_t rr[16];
         tmem_ld_32x16(tmem_base + DQ_COL + lane_addr + c0, rr);
         tmem_ld_wait();
+        if (c0 >= 16 * p.k_steps) {   // padding channels: not accumulated, written as zeros
+#pragma unroll
+          for (int u = 0; u < 16; ++u) rr[u] = 0u;
+        }
         if (row_ok && J > 0) {
           __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * D + c0;
           const float f = p.scale;

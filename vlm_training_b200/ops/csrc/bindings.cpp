@@ -450,6 +450,7 @@ torch::Tensor vlmt_status_tensor() { return status_tensor(); }
 void bind_attention(pybind11::module_& m);
 void bind_comm(pybind11::module_& m);
 void bind_moe(pybind11::module_& m);
+void bind_gdn(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
@@ -496,4 +497,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   bind_attention(m);
   bind_comm(m);
   bind_moe(m);
+  bind_gdn(m);
 }

@@ -119,6 +119,83 @@ class _Scan(torch.autograd.Function):
         return dw.to(wt), dv_tot.to(ut), dkdec.to(kt), ddecay.to(dt), None
 
 
+def chunk_table(cu_host, chunk: int = CHUNK):
+    """Per chunk slot (the order :func:`doc_chunk_ranges` lays them out in): first token and number of rows, ``int32 [N, 2]``."""
+    cu = np.asarray(cu_host, dtype=np.int64)
+    lens = np.diff(cu)
+    n_per = (lens + chunk - 1) // chunk
+    doc = np.repeat(np.arange(len(lens)), n_per)
+    first_all = np.concatenate(([0], np.cumsum(n_per)))[:-1]
+    idx = np.arange(int(n_per.sum())) - np.repeat(first_all, n_per)
+    tok0 = cu[doc] + idx * chunk
+    rows = np.minimum(chunk, cu[doc + 1] - tok0)
+    return np.stack((tok0, rows), 1).astype(np.int32)
+
+
+_TABLES: dict = {}
+NATIVE_CALLS = {"forward": 0, "backward": 0}   # how often the all-kernel path ran (tests assert on it)
+
+
+def _device_tables(cu_host, device):
+    """Chunk table and document ranges on the device, kept for the last few packed rows (every linear-attention layer
+    of a step, and its recomputation, asks for the same one)."""
+    key = (tuple(int(x) for x in cu_host), str(device))
+    hit = _TABLES.get(key)
+    if hit is None:
+        _dst, n_slots, first, count = doc_chunk_ranges(cu_host)
+        chunks = torch.from_numpy(chunk_table(cu_host)).to(device, non_blocking=True)
+        ranges = (first, count, torch.from_numpy(np.stack((first, count), 1).copy()).to(device, non_blocking=True))
+        hit = (chunks, ranges, n_slots)
+        if len(_TABLES) >= 8:
+            _TABLES.pop(next(iter(_TABLES)))
+        _TABLES[key] = hit
+    return hit
+
+
+class _ChunkedNative(torch.autograd.Function):
+    """The whole rule on a GPU: prepare -> scan -> output, each one kernel launch (``csrc/gdn_chunk_sm100.cu``,
+    ``csrc/gdn_scan_sm100.cu``), and the same three stages in reverse for the gradients.  Saved for backward: the scan
+    operands and results, ``P``, the triangular inverse and the cumulative decays (all bf16 tile stacks)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, chunks, ranges, scale):
+        from . import cuda as cu
+
+        NATIVE_CALLS["forward"] += 1
+        gf, bf = g.float().contiguous(), beta.float().contiguous()
+        w, u, kdec, qg, P, Tm, gc, decay = cu._C.gdn_prepare_fwd(q, k, v, gf, bf, chunks, scale, 1e-6)
+        vnew, states = cu.gdn_scan(w, kdec, u, decay, None, ranges, False, head_major=True)
+        o = cu._C.gdn_output_fwd(qg, P, states, vnew, chunks, q.shape[0])
+        cu._tick(2)
+        ctx.save_for_backward(q, k, v, bf, gc, decay, w, kdec, qg, P, Tm, vnew, states, chunks)
+        ctx.ranges, ctx.scale = ranges, scale
+        ctx.dtypes = (g.dtype, beta.dtype)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from . import cuda as cu
+
+        NATIVE_CALLS["backward"] += 1
+        q, k, v, bf, gc, decay, w, kdec, qg, P, Tm, vnew, states, chunks = ctx.saved_tensors
+        dqg, dP, dvn, dS = cu._C.gdn_output_bwd(do.contiguous(), qg, P, states, vnew, chunks)
+        du, adj = cu.gdn_scan(kdec, w, dvn, decay, dS, ctx.ranges, True, head_major=True)
+        dq, dk, dv, dg, dbeta = cu._C.gdn_prepare_bwd(q, k, v, bf, gc, chunks, ctx.scale, 1e-6, states, adj, vnew, du, dqg, dP, P, Tm)
+        cu._tick(2)
+        return dq, dk, dv, dg.to(ctx.dtypes[0]), dbeta.to(ctx.dtypes[1]), None, None, None
+
+
+def native_usable(q, k, v, chunk) -> bool:
+    import os
+
+    def tokens_ok(t):
+        return t.dim() == 3 and t.stride(2) == 1 and t.stride(1) == 128 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+    return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and chunk == CHUNK
+            and q.shape[-1] == 128 and v.shape[-1] == 128 and q.shape == k.shape == v.shape and all(tokens_ok(t) for t in (q, k, v))
+            and os.environ.get("VLMT_GDN_CHUNK", "1") != "0")
+
+
 def gated_delta_rule_scan(q, k, v, g, beta, cu_host, scale=None, chunk: int = CHUNK, work_dtype=None):
     """``q, k [T,H,Dk]``, ``v [T,H,Dv]``, ``g, beta [T,H]``; ``cu_host`` the document boundaries as a host sequence.
     ``work_dtype``: dtype of the scan's operands and states (bf16 on a GPU, float32 on CPU)."""
@@ -128,6 +205,9 @@ def gated_delta_rule_scan(q, k, v, g, beta, cu_host, scale=None, chunk: int = CH
     if work_dtype is None:
         work_dtype = torch.bfloat16 if q.is_cuda else torch.float32
     scale = scale if scale is not None else Dk ** -0.5
+    if work_dtype is torch.bfloat16 and native_usable(q, k, v, chunk):
+        chunks, ranges, _n = _device_tables(cu_host, dev)
+        return _ChunkedNative.apply(q, k, v, g, beta, chunks, ranges, float(scale))
     dst_np, n_slots, first, count = doc_chunk_ranges(cu_host, chunk)
     Tc = int(np.asarray(cu_host)[-1])
     dst = torch.from_numpy(dst_np).to(dev, non_blocking=True)
