@@ -107,7 +107,7 @@ def test_attention_growing_scores(causal, D):
     _close(v.grad, vr.grad, 0.08, 5e-2, "dv")
 
 
-@pytest.mark.parametrize("D,Hkv,rep,L,B,kk", [(256, 2, 8, 700, 96, 300), (64, 2, 2, 300, 50, 64), (128, 1, 4, 513, 33, 2048)])
+@pytest.mark.parametrize("D,Hkv,rep,L,B,kk", [(256, 2, 8, 700, 96, 300), (256, 1, 8, 3000, 40, 2048), (64, 2, 2, 300, 50, 64), (128, 1, 4, 513, 33, 2048)])
 def test_dsa_selected_attention_kernels(D, Hkv, rep, L, B, kk):
     """Selected-key attention kernels (forward and backward) against the gathered dense softmax in float32."""
     from vlm_training_b200.ops import dsa_cuda
@@ -135,7 +135,7 @@ def test_dsa_selected_attention_kernels(D, Hkv, rep, L, B, kk):
     mask = torch.ones(B, 1, 1, device="cuda")
     mask[1] = 0
     (want * mask).backward(go.float())
-    assert float(got[1].abs().max()) == 0.0
+    assert float(got[1].detach().abs().max()) == 0.0
     torch.testing.assert_close(got.float() * mask, want * mask, atol=2e-2, rtol=2e-2)
     for name, a, t in zip("qkv", grads, (q, k, v)):
         ref = t.grad.float()

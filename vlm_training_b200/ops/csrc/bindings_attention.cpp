@@ -46,7 +46,10 @@ static std::vector<Tensor> attn_bwd(const Tensor& dout, const Tensor& q, const T
 }
 
 // selected-key attention of one query block (dsa_attention.h): q [B, Hq, D], k / v [L, Hkv, D], sel [B, kk] int32
-static std::vector<Tensor> dsa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& sel, double scale) {
+torch::Tensor vlmt_status_tensor();
+
+// ``tensor_cores``: the tcgen05 kernel (head size 256, 8 query heads per kv head) instead of the CUDA-core one
+static std::vector<Tensor> dsa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& sel, double scale, bool tensor_cores) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16);
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.is_contiguous() && k.is_contiguous() && v.is_contiguous());
   TORCH_CHECK(sel.scalar_type() == at::kInt && sel.is_cuda() && sel.is_contiguous() && sel.dim() == 2 && sel.size(0) == q.size(0));
@@ -55,6 +58,13 @@ static std::vector<Tensor> dsa_fwd(const Tensor& q, const Tensor& k, const Tenso
   TORCH_CHECK(Hq % Hkv == 0 && k.size(2) == D && v.sizes() == k.sizes());
   Tensor o = torch::empty_like(q);
   Tensor lse = torch::empty({B, Hq}, q.options().dtype(torch::kFloat));
+  if (tensor_cores && D == 256 && Hq / Hkv == 8) {
+    Tensor st = vlmt_status_tensor();
+    int r = vlmt_dsa_fwd_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), sel.data_ptr<int>(), o.data_ptr(), lse.data_ptr<float>(), B, Hkv,
+                            (int)sel.size(1), (float)scale, st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(r == 0, "vlmt_dsa_fwd_tc failed with code ", r);
+    return {o, lse};
+  }
   int r = vlmt_dsa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), sel.data_ptr<int>(), o.data_ptr(), lse.data_ptr<float>(), B, Hkv, Hq / Hkv,
                        D, (int)sel.size(1), (float)scale, at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(r == 0, "vlmt_dsa_fwd failed with code ", r);
@@ -63,13 +73,21 @@ static std::vector<Tensor> dsa_fwd(const Tensor& q, const Tensor& k, const Tenso
 
 // dk / dv are float32 [L, Hkv, D] accumulators owned by the caller (one per document, shared by its query blocks)
 static Tensor dsa_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& sel, const Tensor& o,
-                      const Tensor& lse, Tensor& dk, Tensor& dv, double scale) {
+                      const Tensor& lse, Tensor& dk, Tensor& dv, double scale, bool tensor_cores) {
   TORCH_CHECK(d_o.is_contiguous() && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && o.is_contiguous() && sel.is_contiguous());
   TORCH_CHECK(d_o.scalar_type() == at::kBFloat16 && dk.scalar_type() == at::kFloat && dv.scalar_type() == at::kFloat);
   TORCH_CHECK(dk.is_contiguous() && dv.is_contiguous() && dk.numel() == k.numel() && dv.numel() == v.numel());
   c10::cuda::CUDAGuard guard(q.device());
   const int B = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
   Tensor dq = torch::empty({B, Hq, D}, q.options().dtype(torch::kFloat));
+  if (tensor_cores && D == 256 && Hq / Hkv == 8) {
+    Tensor st = vlmt_status_tensor();
+    int r = vlmt_dsa_bwd_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), sel.data_ptr<int>(), o.data_ptr(), lse.data_ptr<float>(), d_o.data_ptr(),
+                            dq.data_ptr<float>(), dk.data_ptr<float>(), dv.data_ptr<float>(), B, Hkv, (int)sel.size(1), (float)scale,
+                            st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(r == 0, "vlmt_dsa_bwd_tc failed with code ", r);
+    return dq;
+  }
   int r = vlmt_dsa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), sel.data_ptr<int>(), o.data_ptr(), lse.data_ptr<float>(), d_o.data_ptr(),
                        dq.data_ptr<float>(), dk.data_ptr<float>(), dv.data_ptr<float>(), B, Hkv, Hq / Hkv, D, (int)sel.size(1), (float)scale,
                        at::cuda::getCurrentCUDAStream().stream());

@@ -10,6 +10,11 @@ extern "C" {
 int vlmt_dsa_supported(int D, int rep);
 int vlmt_dsa_fwd(const void* q, const void* k, const void* v, const int* sel, void* o, float* lse, int B, int Hkv, int rep, int D,
                  int kk, float scale, cudaStream_t st);
+// forward on the tensor cores (dsa_attention_sm100.cu): D = 256, 8 query heads per kv head; `status`: the device status word
+int vlmt_dsa_fwd_tc(const void* q, const void* k, const void* v, const int* sel, void* o, float* lse, int B, int Hkv, int kk, float scale,
+                    int* status, cudaStream_t st);
+int vlmt_dsa_bwd_tc(const void* q, const void* k, const void* v, const int* sel, const void* o, const float* lse, const void* d_o,
+                    float* dq, float* dk, float* dv, int B, int Hkv, int kk, float scale, int* status, cudaStream_t st);
 int vlmt_dsa_bwd(const void* q, const void* k, const void* v, const int* sel, const void* o, const float* lse, const void* d_o,
                  float* dq, float* dk, float* dv, int B, int Hkv, int rep, int D, int kk, float scale, cudaStream_t st);
 #ifdef __cplusplus

@@ -29,7 +29,7 @@ class _SelectedAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qb, kd, vd, sel, scale):
         qb, kd, vd = qb.contiguous(), kd.contiguous(), vd.contiguous()
-        o, lse = cu._C.dsa_fwd(qb, kd, vd, sel, scale)
+        o, lse = cu._C.dsa_fwd(qb, kd, vd, sel, scale, os.environ.get("VLMT_DSA_TC", "1") != "0")
         cu._tick()
         ctx.save_for_backward(qb, kd, vd, sel, o, lse)
         ctx.scale = scale
@@ -40,7 +40,7 @@ class _SelectedAttention(torch.autograd.Function):
         qb, kd, vd, sel, o, lse = ctx.saved_tensors
         dk = torch.zeros(kd.shape, dtype=torch.float32, device=kd.device)
         dv = torch.zeros(vd.shape, dtype=torch.float32, device=vd.device)
-        dq = cu._C.dsa_bwd(d_o.contiguous(), qb, kd, vd, sel, o, lse, dk, dv, ctx.scale)
+        dq = cu._C.dsa_bwd(d_o.contiguous(), qb, kd, vd, sel, o, lse, dk, dv, ctx.scale, os.environ.get("VLMT_DSA_TC", "1") != "0")
         cu._tick()
         return dq.to(qb.dtype), dk.to(kd.dtype), dv.to(vd.dtype), None, None
 
