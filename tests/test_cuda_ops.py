@@ -434,10 +434,15 @@ def test_adamw_bf16_moments_close_to_fp32():
     torch.testing.assert_close(ma, mb, atol=2e-4, rtol=1e-3)
 
 
-def test_bias_colsum():
+@pytest.mark.parametrize("rows,cols", [(3000, 1152), (28672, 4304), (7, 8), (257, 264)])
+def test_bias_colsum(rows, cols):
     cu = _cu()
-    x = _rand(3000, 1152)
-    torch.testing.assert_close(cu._C.colsum(x), x.float().sum(0), atol=1e-2, rtol=1e-3)
+    x = _rand(rows, cols)
+    torch.testing.assert_close(cu._C.colsum(x), x.float().sum(0), atol=2e-2, rtol=1e-3)
+    wide = _rand(rows, cols + 16)
+    view = wide[:, 8:8 + cols]                    # a column slice: row stride larger than the width
+    if view.data_ptr() % 16 == 0:
+        torch.testing.assert_close(cu._colsum(view), view.float().sum(0), atol=2e-2, rtol=1e-3)
 
 
 def test_layer_norm_linear_and_gelu_linear_match_unfused():

@@ -432,12 +432,14 @@ void sumsq_(const Tensor& x, Tensor& out) {
 // column sums of a 2-D bf16 tensor in fp32 (bias gradients)
 Tensor colsum(const Tensor& x) {
   check_bf16(x, "x");
-  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 2 == 0);
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 8 == 0 && x.stride(0) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "colsum: bf16 [rows, cols], cols and row stride multiples of 8");
   c10::cuda::CUDAGuard guard(x.device());
   const int rows = x.size(0), cols = x.size(1);
   Tensor partial = torch::empty({vlmt_colsum_slabs(rows), cols}, x.options().dtype(torch::kFloat));
-  vlmt_colsum(x.data_ptr(), x.stride(0), rows, cols, partial.data_ptr<float>(), cur_stream());
-  return partial.sum(0);
+  Tensor out = torch::empty({cols}, x.options().dtype(torch::kFloat));
+  vlmt_colsum(x.data_ptr(), x.stride(0), rows, cols, partial.data_ptr<float>(), out.data_ptr<float>(), cur_stream());
+  return out;
 }
 
 Tensor status() { return status_tensor(); }

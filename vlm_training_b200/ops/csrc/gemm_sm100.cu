@@ -24,6 +24,8 @@
 // loads the first tile of that peer's rows from the LOCAL gathered buffer, so remote rows cross NVLink once and the
 // transfer hides behind the own rows' tiles.
 #include "sm100.cuh"
+
+#include <stdlib.h>
 #include "gemm_sm100.h"
 
 #include <cuda_runtime.h>
@@ -63,6 +65,10 @@ struct Params {
   float* Dacc32;       // optional fp32 destination (wgrad into fp32 main grads) or null
   int epilogue;        // GemmEpilogue
   int accumulate;      // D += result
+  // split-K (needs accumulate + tma_store): the K range is cut into k_splits parts of kb_per_split k-blocks; every part is
+  // a work item of its own whose tile is ADDED to D by the memory system, so a GEMM with few output tiles but a long K
+  // (weight gradients) fills all SMs
+  int k_splits, kb_per_split;
   int tma_store;       // bf16 output goes through smem staging + TMA stores (coalesced, clipped at the edges)
   // GEMM -> reduce-scatter: output rows are owned by ranks in blocks of rs_rows; the tile for owner o is stored straight
   // into rs_dst[o] (a buffer in rank o's memory, reached over NVLink), so the transfer overlaps the remaining tiles
@@ -144,6 +150,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int tiles_per_group = tiles_m * tiles_n;                       // grp_mode 2: one [M, N] output per group
   const int num_tiles = p.grp_mode == 2 ? tiles_per_group * p.grp_count : tiles_per_group;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int num_items = num_tiles * p.k_splits;
   const int m_limit = p.grp_mode == 1 ? tiles_m * BM : p.M;           // rows that exist
   constexpr int TMEM_COLS = 2 * BN;  // 256 or 512: a power of two >= 32
 
@@ -172,8 +179,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       uint32_t ag_ready = 0;  // AG: peers whose flag has been seen
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn, kb_lo = 0, kb_hi = num_kb, b_row = 0;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        int tile = item, tm, tn, kb_lo = 0, kb_hi = num_kb, b_row = 0;
+        if (p.k_splits > 1) {
+          const int ks = item / num_tiles;
+          tile = item - ks * num_tiles;
+          kb_lo = ks * p.kb_per_split;
+          kb_hi = min(num_kb, kb_lo + p.kb_per_split);
+        }
         if (p.grp_mode == 2) {
           const int g = tile / tiles_per_group;
           tile_coords(tile - g * tiles_per_group, tiles_m, tiles_n, tm, tn);
@@ -243,13 +256,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kErrTimeoutTmemEmpty, wait_ns)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        int kb_lo = 0, kb_hi = num_kb;
+        int tile = item, kb_lo = 0, kb_hi = num_kb;
+        if (p.k_splits > 1) {
+          const int ks = item / num_tiles;
+          tile = item - ks * num_tiles;
+          kb_lo = ks * p.kb_per_split;
+          kb_hi = min(num_kb, kb_lo + p.kb_per_split);
+        }
         if (p.grp_mode == 2) {
           const int g = tile / tiles_per_group;
           kb_lo = p.grp_prefix[g] * (BM / BK);
@@ -309,7 +328,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++it) {
+      const int tile = p.k_splits > 1 ? item % num_tiles : item;
       int tm, tn, d_row0 = 0;
       bool empty_group = false;   // grp_mode 2: no rows for this group, the accumulator was never written -> zeros
       if (p.grp_mode == 2) {
@@ -567,6 +587,11 @@ struct GemmExtras {
   unsigned* ag_counter = nullptr;
 };
 
+bool split_k_enabled() {
+  static const bool on = [] { const char* e = getenv("VLMT_GEMM_SPLITK"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
 template <int BN, bool A_MN, bool B_MN, bool AG>
 int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const CUtensorMap& ta2, const RsMaps& rsm,
                    const Params& p, int num_sms, cudaStream_t stream) {
@@ -578,7 +603,7 @@ int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.grp_mode == 2 ? p.grp_count : 1);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * (p.grp_mode == 2 ? p.grp_count : 1) * p.k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;   // grp_mode 1: p.M is the row capacity, an upper bound
   kern<<<grid, AG ? NUM_THREADS + AG_PUSH_THREADS : NUM_THREADS, L::kTotal, stream>>>(ta, tb, td, ta2, rsm, p);
   return (int)cudaGetLastError();
@@ -640,6 +665,25 @@ int gemm_launch(const void* A, const void* B, void* D, float* Dacc32, const void
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.Dacc32 = Dacc32;
   p.epilogue = epilogue; p.accumulate = accumulate; p.status = status;
+  p.k_splits = 1; p.kb_per_split = 0;
+  if (accumulate && p.tma_store && x.grp_mode == 0 && x.rs_world == 0 && x.ag_world == 0 && bias == nullptr && epilogue == GEMM_EPI_NONE &&
+      Dacc32 == nullptr && split_k_enabled()) {
+    // few output tiles and a long K: cut K so that the work items fill whole waves of SMs (at least 1024 of K per part)
+    const long tiles = (long)((M + BM - 1) / BM) * ((N + (bn256 ? 256 : 128) - 1) / (bn256 ? 256 : 128));
+    const int num_kb = (K + BK - 1) / BK;
+    auto wave_eff = [&](long items) { return (double)items / (double)(((items + num_sms - 1) / num_sms) * num_sms); };
+    int best = 1;
+    double best_eff = wave_eff(tiles);
+    for (int sp : {2, 3, 4, 6, 8}) {
+      if (num_kb / sp < 16) break;
+      const double e = wave_eff(tiles * sp);
+      if (e > best_eff + 0.04) { best = sp; best_eff = e; }
+    }
+    if (best > 1) {
+      p.kb_per_split = (num_kb + best - 1) / best;
+      p.k_splits = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    }
+  }
   p.ag_world = 0; p.ag_rank = 0; p.ag_rows = 0; p.ag_epoch = 0;
   p.ag_src = nullptr; p.ag_flags = nullptr; p.ag_counter = nullptr;
   if (x.ag_world > 0) {

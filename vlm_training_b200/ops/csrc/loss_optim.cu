@@ -185,18 +185,63 @@ __global__ void adamw_vec8_kernel(GT* __restrict__ grad, float* __restrict__ mas
 }
 
 // out[c] = sum_r x[r, c]  (bf16 in, fp32 accumulate): one thread per column pair inside a row slab, partials per slab
-__global__ void colsum_kernel(const bf16* __restrict__ x, long ld, int rows, int cols, float* __restrict__ partial, int rows_per_slab) {
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(256) colsum_kernel(const bf16* __restrict__ x, long ld, int rows, int cols, float* __restrict__ partial,
+                                                      int rows_per_slab) {
+  // block = 8 warps on the same 256 columns (lane <-> 8 columns, one 16-byte load per row); warp w takes rows w, w + 8, ...
+  // of the slab, eight loads in flight; the warps' sums meet in shared memory
+  __shared__ float red[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 256 + lane * 8;
   const int r0 = blockIdx.y * rows_per_slab;
   const int r1 = min(rows, r0 + rows_per_slab);
-  float a0 = 0.f, a1 = 0.f;
-  for (int r = r0; r < r1; ++r) {
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(x + (long)r * ld + c));
-    a0 += f.x; a1 += f.y;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (c < cols) {   // cols is a multiple of 8: a thread's 8 columns are all inside or all outside
+    int r = r0 + warp;
+    for (; r + 56 < r1; r += 64) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(x + (long)(r + 8 * u) * ld + c);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += __uint_as_float(w4[j] << 16);
+          acc[2 * j + 1] += __uint_as_float(w4[j] & 0xffff0000u);
+        }
+      }
+    }
+    for (; r < r1; r += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(x + (long)r * ld + c);
+      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w4[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w4[j] & 0xffff0000u);
+      }
+    }
   }
-  partial[(long)blockIdx.y * cols + c] = a0;
-  partial[(long)blockIdx.y * cols + c + 1] = a1;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = acc[i];
+  __syncthreads();
+  const int cc = blockIdx.x * 256 + threadIdx.x;
+  if (cc < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+    partial[(long)blockIdx.y * cols + cc] = t;
+  }
+}
+
+// out[c] = sum of the slabs' partial sums
+__global__ void colsum_finish_kernel(const float* __restrict__ partial, int slabs, int cols, float* __restrict__ out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float t = 0.f;
+  for (int sl = 0; sl < slabs; ++sl) t += partial[(long)sl * cols + c];
+  out[c] = t;
 }
 
 // sum of squares of a flat bf16/fp32 range -> out[0] (atomic; used for gradient clipping)
@@ -256,11 +301,16 @@ void vlmt_adamw(void* grad, int grad_fp32, float* master, void* m, void* v, int 
 #undef PICK
 #undef LAUNCH
 }
-int vlmt_colsum_slabs(int rows) { int s = (rows + 511) / 512; return s < 1 ? 1 : s; }
-void vlmt_colsum(const void* x, long ld, int rows, int cols, float* partial, cudaStream_t st) {
-  if (rows <= 0 || cols <= 0) return;
-  dim3 grid((cols / 2 + 127) / 128, vlmt_colsum_slabs(rows));
-  colsum_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const bf16*>(x), ld, rows, cols, partial, 512);
+int vlmt_colsum_slabs(int rows) { int s = (rows + 255) / 256; return s < 1 ? 1 : s; }
+// column sums of x [rows, cols] (cols a multiple of 8, 16-byte aligned rows): `partial` holds vlmt_colsum_slabs(rows) x cols floats
+void vlmt_colsum(const void* x, long ld, int rows, int cols, float* partial, float* out, cudaStream_t st) {
+  if (cols <= 0) return;
+  const int slabs = rows > 0 ? vlmt_colsum_slabs(rows) : 0;
+  if (slabs > 0) {
+    dim3 grid((cols + 255) / 256, slabs);
+    colsum_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const bf16*>(x), ld, rows, cols, partial, 256);
+  }
+  colsum_finish_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, slabs, cols, out);
 }
 void vlmt_sumsq(const void* x, int fp32, long n, float* out, cudaStream_t st) {
   if (n <= 0) return;

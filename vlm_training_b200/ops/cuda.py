@@ -97,6 +97,14 @@ def _gemm(a, b, a_mn=False, b_mn=False, bias=None, epilogue=0, out=None, accumul
     return out
 
 
+def _colsum(x2):
+    """Column sums (a bias gradient) of a 2-D bf16 tensor in fp32; shapes the kernel does not take go through torch."""
+    if x2.shape[1] % 8 == 0 and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0 and x2.dtype == torch.bfloat16:
+        _tick(2)
+        return _C.colsum(x2)
+    return x2.float().sum(0)
+
+
 def _as_gemm_operand(t):
     """2-D, unit inner stride, 16-byte aligned row stride and base (TMA requirements)."""
     if t.stride(-1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
@@ -158,7 +166,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = _wgrad(dy2, x2, ctx.w_param)  # dW[N,K] = dY^T[N,M] . X[M,K]
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = _C.colsum(dy2).to(dy.dtype) if dy2.shape[1] % 2 == 0 else dy2.float().sum(0).to(dy.dtype)
+            db = _colsum(dy2).to(dy.dtype)
             _tick()
         return dx, dw, db, None
 
@@ -411,7 +419,7 @@ class _LNLinear(torch.autograd.Function):
         dx, dlw, dlb = _C.layernorm_bwd(dh, x, ln_w, mean, rstd)
         db = None
         if ctx.has_bias:
-            db = _C.colsum(dy2).to(dy.dtype) if dy2.shape[1] % 2 == 0 else dy2.float().sum(0).to(dy.dtype)
+            db = _colsum(dy2).to(dy.dtype)
         _tick(4)
         return dx, dlw.to(ln_w.dtype), dlb.to(ln_w.dtype) if ln_b is not None else None, dw, db, None
 
@@ -449,7 +457,7 @@ class _GeluLinear(torch.autograd.Function):
         dpre = _C.gelu_bwd(dact, pre, ctx.tanh_approx)
         db = None
         if ctx.has_bias:
-            db = _C.colsum(dy2).to(dy.dtype) if dy2.shape[1] % 2 == 0 else dy2.float().sum(0).to(dy.dtype)
+            db = _colsum(dy2).to(dy.dtype)
         _tick(3)
         return dpre, dw, db, None
 

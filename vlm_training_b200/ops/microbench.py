@@ -79,6 +79,10 @@ def bench_gemm(t: Timer, m, n, k, layout="fwd"):
     elif layout == "dgrad":  # dX[m,n] = dY[m,k] W[k,n]
         a, b = _r(m, k), _r(k, n)
         fn = lambda: cu._gemm(a, b, b_mn=True)
+    elif layout == "wgrad_acc":  # the product is added into an existing gradient (TMA reduce-add; split over K where that fills the SMs)
+        a, b = _r(k, m), _r(k, n)
+        out = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: cu._gemm(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)
     else:  # wgrad: dW[m,n] = dY[k,m]^T X[k,n]
         a, b = _r(k, m), _r(k, n)
         fn = lambda: cu._gemm(a, b, a_mn=True, b_mn=True)
@@ -282,7 +286,7 @@ def main(argv=None):
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
+    ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad", "wgrad_acc"])
     ap.add_argument("--rows", type=int, default=8192, help="rows / tokens of the row-wise kernels (rmsnorm, swiglu, qkv_rope)")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--docs", type=int, default=1)
