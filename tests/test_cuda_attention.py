@@ -26,7 +26,11 @@ CASES = [
     ([256], 2, 1, 128, True),
     ([100, 1, 300, 57], 4, 2, 128, True),
     ([513, 127, 129], 4, 1, 64, True),
-    ([196, 196, 1024], 4, 4, 72, False),   # ViT: head_dim 72 is zero-padded to the kernel tile
+    ([196, 196, 1024], 4, 4, 72, False),   # ViT: head_dim 72 runs in a 128-wide tile whose channels 72.. TMA zero-fills
+    ([300, 90], 2, 1, 40, True),           # 64-wide tile, 24 channels zero-filled
+    ([260, 513], 4, 2, 96, True),
+    ([129, 700], 2, 2, 120, False),
+    ([333], 2, 1, 100, True),              # not a multiple of 8: padded to 104 by a copy
     ([700], 8, 2, 128, False),
     ([1500, 260, 40], 2, 1, 128, True),
     ([900, 130], 2, 2, 64, False),
@@ -105,6 +109,30 @@ def test_attention_growing_scores(causal, D):
     _close(q.grad, qr.grad, 0.08, 5e-2, "dq")
     _close(k.grad, kr.grad, 0.08, 5e-2, "dk")
     _close(v.grad, vr.grad, 0.08, 5e-2, "dv")
+
+
+def test_attention_reads_strided_heads_in_place():
+    """q, k, v as slices of one fused projection ``[T, 3, H, 72]`` (the ViT layout): read through strided tensor maps,
+    no padded or contiguous copies; gradients come back through the slices."""
+    from vlm_training_b200.ops import cuda as cu
+
+    torch.manual_seed(3)
+    lens, H, D = [196, 1024, 77], 4, 72
+    T = sum(lens)
+    cu_seq = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    qkv = torch.randn(T, 3 * H * D, device=DEV).bfloat16().requires_grad_()
+    q, k, v = qkv.view(T, 3, H, D).unbind(1)
+    assert not v.is_contiguous()
+    o = ops.attention_varlen(q, k, v, cu_seq, max(lens), False, None)
+    g = torch.randn(T, H, D, device=DEV).bfloat16()
+    o.backward(g)
+    cu.check_status()
+    ref_in = qkv.detach().float().requires_grad_()
+    qr, kr, vr = ref_in.view(T, 3, H, D).unbind(1)
+    o_r = ref.attention_varlen(qr, kr, vr, cu_seq, max(lens), False, None)
+    o_r.backward(g.float())
+    _close(o, o_r, 0.02, 2e-2, "out")
+    _close(qkv.grad, ref_in.grad, 0.05, 3e-2, "dqkv")
 
 
 @pytest.mark.parametrize("D,Hkv,rep,L,B,kk", [(256, 2, 8, 700, 96, 300), (256, 1, 8, 3000, 40, 2048), (64, 2, 2, 300, 50, 64), (128, 1, 4, 513, 33, 2048)])

@@ -81,15 +81,10 @@ class VisionAttention(nn.Module):
         qkv = qkv.view(S, 3, self.n_heads, self.head_dim)
         q, k, v = qkv.unbind(1)
         D = self.head_dim
-        if x.is_cuda and D not in (64, 128) and D < 128:
-            # the attention kernel works on 64- or 128-wide heads: emit q, k already zero-padded from the rotary
-            # kernel, pad v, and tell the kernel how many channels are real so its MMAs skip the padding
-            q, k = ops.rope_vision(q, k, plan.cos, plan.sin, pad_to=128)
-            v = torch.nn.functional.pad(v, (0, 128 - D))
-            o = ops.attention_varlen(q, k, v, plan.cu_seqlens, plan.max_seqlen, False, D ** -0.5, valid_dim=D)[..., :D]
-        else:
-            q, k = ops.rope_vision(q, k, plan.cos, plan.sin)
-            o = ops.attention_varlen(q, k, v, plan.cu_seqlens, plan.max_seqlen, False, D ** -0.5)
+        # q and k leave the rotary kernel as contiguous [S, H, D]; v is read in place from the fused projection (the
+        # attention kernels take strided heads and any head size that is a multiple of 8, 72 here)
+        q, k = ops.rope_vision(q, k, plan.cos, plan.sin)
+        o = ops.attention_varlen(q, k, v, plan.cu_seqlens, plan.max_seqlen, False, D ** -0.5)
         return self.proj(o.reshape(S, -1))
 
 

@@ -166,13 +166,9 @@ def rope_vision(q, k, cos, sin, pad_to=None):
 
 
 # --- attention ---------------------------------------------------------------
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: float | None = None,
-                     valid_dim: int | None = None):
-    """``valid_dim``: the inputs carry zero padding beyond this many channels (see ``rope_vision(pad_to=...)``)."""
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: float | None = None):
     if _use_cuda(q):
-        return _cu().attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale, valid_dim)
-    if scale is None and valid_dim:
-        scale = valid_dim ** -0.5
+        return _cu().attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
     return ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
 
 

@@ -79,6 +79,7 @@ struct FwdParams {
   float scale_log2;   // softmax scale * log2(e)
   int causal;
   int k_steps;        // 16-channel steps of the Q.K contraction and width of the P.V product (channels beyond 16 * k_steps are zero padding)
+  int d_mem;          // head size in memory (<= D): TMA zero-fills the tile's channels beyond it, the output has this width
   int* status;
 };
 
@@ -153,7 +154,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int t = 0; t < 2; ++t)
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offQ + t * L::kQ + b * 16384, &tmQ, q_full, hq * D + 64 * b, row0 + t * BM);
+        for (int b = 0; b < DB; ++b) tma_load_3d(smem + L::offQ + t * L::kQ + b * 16384, &tmQ, q_full, 64 * b, hq, row0 + t * BM);
       for (int j = 0; j < J; ++j) {
         const int s = j & 1;
         const uint32_t ph = ((j >> 1) & 1) ^ 1;
@@ -161,11 +162,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&k_empty[s], ph, abort_flag, p.status, kErrTimeoutEmpty)) break;
         mbar_expect_tx(&k_full[s], L::kKV);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offK + s * L::kKV + b * 16384, &tmK, &k_full[s], hkv * D + 64 * b, krow);
+        for (int b = 0; b < DB; ++b) tma_load_3d(smem + L::offK + s * L::kKV + b * 16384, &tmK, &k_full[s], 64 * b, hkv, krow);
         if (!mbar_wait(&v_empty[s], ph, abort_flag, p.status, kErrTimeoutEmpty)) break;
         mbar_expect_tx(&v_full[s], L::kKV);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offV + s * L::kKV + b * 16384, &tmV, &v_full[s], hkv * D + 64 * b, krow);
+        for (int b = 0; b < DB; ++b) tma_load_3d(smem + L::offV + s * L::kKV + b * 16384, &tmV, &v_full[s], 64 * b, hkv, krow);
       }
     }
   } else if (warp == 1) {
@@ -303,21 +304,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const size_t tok = (size_t)(ti.doc_start + qi);
-      __nv_bfloat16* dst = p.O + (tok * p.Hq + hq) * D;
-#pragma unroll
-      const int n_out = 16 * p.k_steps;
+      __nv_bfloat16* dst = p.O + (tok * p.Hq + hq) * p.d_mem;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
+        if (c * 32 >= p.d_mem) break;
         uint32_t o[32];
         tmem_ld_32x32(o_addr + c * 32, o);
         tmem_ld_wait();
-        if (c * 32 + 32 > n_out) {   // the padding channels were not accumulated: they are written as zeros
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (c * 32 + i >= n_out) o[i] = 0u;
-        }
         if (qi < ti.doc_len) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
+            if (c * 32 + u * 8 >= p.d_mem) break;   // channels beyond the head size exist only in the tile
             uint4 pk;
             pk.x = pack_bf16x2(__uint_as_float(o[u * 8 + 0]) * inv, __uint_as_float(o[u * 8 + 1]) * inv);
             pk.y = pack_bf16x2(__uint_as_float(o[u * 8 + 2]) * inv, __uint_as_float(o[u * 8 + 3]) * inv);
@@ -370,6 +367,7 @@ struct BwdParams {
   float scale, scale_log2;
   int causal;
   int k_steps;        // 16-channel steps of the contractions over the head dim (Q.K and dO.V) and width of dQ / dK / dV; the rest is zero padding
+  int d_mem;          // head size in memory (<= D)
   int* status;
   long long* trace;  // timeline dump of CTA (0,0) (only with -DVLMT_ATTN_TRACE; nullptr otherwise)
 };
@@ -483,8 +481,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_expect_tx(kv_full, 2 * L::kTile);
 #pragma unroll
       for (int b = 0; b < DB; ++b) {
-        tma_load_2d(smem + L::offA + b * 16384, &tmK, kv_full, hkv * D + 64 * b, krow);
-        tma_load_2d(smem + L::offB + b * 16384, &tmV, kv_full, hkv * D + 64 * b, krow);
+        tma_load_3d(smem + L::offA + b * 16384, &tmK, kv_full, 64 * b, hkv, krow);
+        tma_load_3d(smem + L::offB + b * 16384, &tmV, kv_full, 64 * b, hkv, krow);
       }
       int qs = 0;             // stage / phase of the Q ring (3 stages) ; the dO ring (2 stages) follows `it`
       uint32_t qph = 1;
@@ -495,11 +493,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (!mbar_wait(&q_empty[qs], qph, abort_flag, p.status, kErrTimeoutEmpty)) break;
         mbar_expect_tx(&q_full[qs], L::kTile);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offC + qs * L::kTile + b * 16384, &tmQ, &q_full[qs], hq * D + 64 * b, qrow);
+        for (int b = 0; b < DB; ++b) tma_load_3d(smem + L::offC + qs * L::kTile + b * 16384, &tmQ, &q_full[qs], 64 * b, hq, qrow);
         if (!mbar_wait(&do_empty[ds], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
         mbar_expect_tx(&do_full[ds], L::kTile);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offD + ds * L::kTile + b * 16384, &tmdO, &do_full[ds], hq * D + 64 * b, qrow);
+        for (int b = 0; b < DB; ++b) tma_load_3d(smem + L::offD + ds * L::kTile + b * 16384, &tmdO, &do_full[ds], 64 * b, hq, qrow);
         if (++qs == 3) { qs = 0; qph ^= 1; }
       }
     }
@@ -677,14 +675,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             uint32_t rr[16];
             tmem_ld_32x16(tmem_base + col + lane_addr + c0, rr);
             tmem_ld_wait();
-            if (c0 >= 16 * p.k_steps) {   // padding channels: not accumulated, written as zeros
-#pragma unroll
-              for (int u = 0; u < 16; ++u) rr[u] = 0u;
-            }
             if (key_ok) {
-              __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * D + c0;
+              __nv_bfloat16* dst = base + ((size_t)(ti.doc_start + kvi) * p.Hkv + hkv) * p.d_mem + c0;
 #pragma unroll
               for (int t = 0; t < 2; ++t) {
+                if (c0 + t * 8 >= p.d_mem) break;
                 uint4 pk;
                 pk.x = pack_bf16x2(__uint_as_float(rr[t * 8 + 0]) * f, __uint_as_float(rr[t * 8 + 1]) * f);
                 pk.y = pack_bf16x2(__uint_as_float(rr[t * 8 + 2]) * f, __uint_as_float(rr[t * 8 + 3]) * f);
@@ -771,8 +766,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_expect_tx(qdo_full, 2 * L::kTile);
 #pragma unroll
       for (int b = 0; b < DB; ++b) {
-        tma_load_2d(smem + L::offA + b * 16384, &tmQ, qdo_full, hq * D + 64 * b, qrow);
-        tma_load_2d(smem + L::offB + b * 16384, &tmdO, qdo_full, hq * D + 64 * b, qrow);
+        tma_load_3d(smem + L::offA + b * 16384, &tmQ, qdo_full, 64 * b, hq, qrow);
+        tma_load_3d(smem + L::offB + b * 16384, &tmdO, qdo_full, 64 * b, hq, qrow);
       }
       int ks = 0;             // stage / phase of the K ring (3 stages); the V ring (2 stages) follows j
       uint32_t kph = 1;
@@ -782,11 +777,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!mbar_wait(&k_empty[ks], kph, abort_flag, p.status, kErrTimeoutEmpty)) break;
         mbar_expect_tx(&k_full[ks], L::kTile);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offC + ks * L::kTile + b * 16384, &tmK, &k_full[ks], hkv * D + 64 * b, krow);
+        for (int b = 0; b < DB; ++b) tma_load_3d(smem + L::offC + ks * L::kTile + b * 16384, &tmK, &k_full[ks], 64 * b, hkv, krow);
         if (!mbar_wait(&v_empty[vs], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kErrTimeoutEmpty)) break;
         mbar_expect_tx(&v_full[vs], L::kTile);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) tma_load_2d(smem + L::offD + vs * L::kTile + b * 16384, &tmV, &v_full[vs], hkv * D + 64 * b, krow);
+        for (int b = 0; b < DB; ++b) tma_load_3d(smem + L::offD + vs * L::kTile + b * 16384, &tmV, &v_full[vs], 64 * b, hkv, krow);
         if (++ks == 3) { ks = 0; kph ^= 1; }
       }
     }
@@ -939,15 +934,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         uint32_t rr[16];
         tmem_ld_32x16(tmem_base + DQ_COL + lane_addr + c0, rr);
         tmem_ld_wait();
-        if (c0 >= 16 * p.k_steps) {   // padding channels: not accumulated, written as zeros
-#pragma unroll
-          for (int u = 0; u < 16; ++u) rr[u] = 0u;
-        }
         if (row_ok && J > 0) {
-          __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * D + c0;
+          __nv_bfloat16* dst = p.dQ + (tok * p.Hq + hq) * p.d_mem + c0;
           const float f = p.scale;
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
+            if (c0 + t * 8 >= p.d_mem) break;
             uint4 pk;
             pk.x = pack_bf16x2(__uint_as_float(rr[t * 8 + 0]) * f, __uint_as_float(rr[t * 8 + 1]) * f);
             pk.y = pack_bf16x2(__uint_as_float(rr[t * 8 + 2]) * f, __uint_as_float(rr[t * 8 + 3]) * f);
@@ -973,9 +965,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-// tensor map over a [T, H*D] bf16 activation with row stride `ld` elements, boxes of {64 channels, 128 tokens}
-int make_act_tmap(CUtensorMap* m, const void* base, int T, int HD, long ld, int box_rows = 128) {
-  return vlmt_make_tmap_2d_bf16(m, base, (uint64_t)HD, (uint64_t)T, (uint64_t)ld * 2, 64, (uint32_t)box_rows);
+// tensor map over a [T, H, d] bf16 activation with token stride `ld` and head stride `hs` (elements), boxes of
+// {64 channels, 1 head, 128 tokens}; channels of a box beyond d read as zeros
+int make_act_tmap(CUtensorMap* m, const void* base, int T, int H, int d, long ld, long hs) {
+  return vlmt_make_tmap_3d_bf16(m, base, (uint64_t)d, (uint64_t)H, (uint64_t)T, (uint64_t)hs * 2, (uint64_t)ld * 2, 64, 1, 128);
 }
 
 template <typename K>
@@ -993,53 +986,64 @@ extern "C" int vlmt_attn256_bwd(const void* dout, const void* q, const void* k, 
                                 int* status, cudaStream_t st);
 
 extern "C" int vlmt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu, int n_docs, int T, int Hq,
-                             int Hkv, int D, int d_eff, long ldq, long ldk, long ldv, float scale, int causal, int* status, cudaStream_t st) {
+                             int Hkv, int d, long ldq, long hsq, long ldk, long hsk, long ldv, long hsv, float scale, int causal, int* status,
+                             cudaStream_t st) {
   if (T <= 0 || n_docs <= 0) return 0;
-  if (D == 256) return vlmt_attn256_fwd(q, k, v, o, lse, cu, n_docs, T, Hq, Hkv, ldq, ldk, ldv, scale, causal, status, st);
+  if (d == 256) {
+    if (hsq != 256 || hsk != 256 || hsv != 256) return -11;
+    return vlmt_attn256_fwd(q, k, v, o, lse, cu, n_docs, T, Hq, Hkv, ldq, ldk, ldv, scale, causal, status, st);
+  }
+  if (d <= 0 || d > 128 || (d & 7)) return -10;
+  const int D = d <= 64 ? 64 : 128;   // tile width; TMA zero-fills the channels between d and D
   CUtensorMap tq, tk, tv;
   int r;
-  if ((r = make_act_tmap(&tq, q, T, Hq * D, ldq))) return 1000 + r;
-  if ((r = make_act_tmap(&tk, k, T, Hkv * D, ldk))) return 2000 + r;
-  if ((r = make_act_tmap(&tv, v, T, Hkv * D, ldv))) return 3000 + r;
+  if ((r = make_act_tmap(&tq, q, T, Hq, d, ldq, hsq))) return 1000 + r;
+  if ((r = make_act_tmap(&tk, k, T, Hkv, d, ldk, hsk))) return 2000 + r;
+  if ((r = make_act_tmap(&tv, v, T, Hkv, d, ldv, hsv))) return 3000 + r;
   FwdParams p;
   p.O = reinterpret_cast<__nv_bfloat16*>(o); p.LSE = lse; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
-  p.k_steps = (d_eff <= 0 || d_eff > D) ? D / 16 : (d_eff + 15) / 16;
+  p.k_steps = (d + 15) / 16;
+  p.d_mem = d;
   dim3 grid(T / (2 * BM) + n_docs + 1, Hq);
   if (D == 128) {
     if ((r = set_smem(attn_fwd_kernel<128>, FwdSmem<128>::kTotal))) return r;
     attn_fwd_kernel<128><<<grid, ATT_THREADS, FwdSmem<128>::kTotal, st>>>(tq, tk, tv, p);
-  } else if (D == 64) {
+  } else {
     if ((r = set_smem(attn_fwd_kernel<64>, FwdSmem<64>::kTotal))) return r;
     attn_fwd_kernel<64><<<grid, ATT_THREADS, FwdSmem<64>::kTotal, st>>>(tq, tk, tv, p);
-  } else {
-    return -10;
   }
   return (int)cudaGetLastError();
 }
 
 extern "C" int vlmt_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse, float* delta,
-                             void* dq, void* dk, void* dv, const int* cu, int n_docs, int T, int Hq, int Hkv, int D, int d_eff, float scale,
-                             int causal, int* status, cudaStream_t st) {
+                             void* dq, void* dk, void* dv, const int* cu, int n_docs, int T, int Hq, int Hkv, int d, long ldq, long hsq,
+                             long ldk, long hsk, long ldv, long hsv, float scale, int causal, int* status, cudaStream_t st) {
   if (T <= 0 || n_docs <= 0) return 0;
-  if (D == 256) return vlmt_attn256_bwd(dout, q, k, v, o, lse, delta, dq, dk, dv, cu, n_docs, T, Hq, Hkv, scale, causal, status, st);
+  if (d == 256) {
+    if (hsq != 256 || hsk != 256 || hsv != 256 || ldq != (long)Hq * 256 || ldk != (long)Hkv * 256 || ldv != (long)Hkv * 256) return -11;
+    return vlmt_attn256_bwd(dout, q, k, v, o, lse, delta, dq, dk, dv, cu, n_docs, T, Hq, Hkv, scale, causal, status, st);
+  }
+  if (d <= 0 || d > 128 || (d & 7)) return -10;
+  const int D = d <= 64 ? 64 : 128;
   {
     const int warps = T * Hq;
     attn_delta_kernel<<<(warps * 32 + 255) / 256, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
-                                                                reinterpret_cast<const __nv_bfloat16*>(o), delta, T, Hq, D);
+                                                                reinterpret_cast<const __nv_bfloat16*>(o), delta, T, Hq, d);
   }
   CUtensorMap tq, tk, tv, tdo;
   int r;
-  if ((r = make_act_tmap(&tq, q, T, Hq * D, (long)Hq * D))) return 1000 + r;
-  if ((r = make_act_tmap(&tk, k, T, Hkv * D, (long)Hkv * D))) return 2000 + r;
-  if ((r = make_act_tmap(&tv, v, T, Hkv * D, (long)Hkv * D))) return 3000 + r;
-  if ((r = make_act_tmap(&tdo, dout, T, Hq * D, (long)Hq * D))) return 4000 + r;
+  if ((r = make_act_tmap(&tq, q, T, Hq, d, ldq, hsq))) return 1000 + r;
+  if ((r = make_act_tmap(&tk, k, T, Hkv, d, ldk, hsk))) return 2000 + r;
+  if ((r = make_act_tmap(&tv, v, T, Hkv, d, ldv, hsv))) return 3000 + r;
+  if ((r = make_act_tmap(&tdo, dout, T, Hq, d, (long)Hq * d, d))) return 4000 + r;
   BwdParams p;
   p.dQ = reinterpret_cast<__nv_bfloat16*>(dq); p.dK = reinterpret_cast<__nv_bfloat16*>(dk); p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   p.LSE = lse; p.delta = delta; p.cu = cu; p.n_docs = n_docs; p.T = T; p.Hq = Hq; p.Hkv = Hkv;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.causal = causal; p.status = status;
   p.trace = nullptr;
-  p.k_steps = (d_eff <= 0 || d_eff > D) ? D / 16 : (d_eff + 15) / 16;
+  p.k_steps = (d + 15) / 16;
+  p.d_mem = d;
 #ifdef VLMT_ATTN_TRACE
   static long long* trace_buf = nullptr;
   if (!trace_buf) cudaMalloc(&trace_buf, 256 * 16 * sizeof(long long));

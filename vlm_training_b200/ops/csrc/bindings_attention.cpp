@@ -9,37 +9,45 @@
 using torch::Tensor;
 Tensor vlmt_status_tensor();
 
+// [T, H, d] bf16 with unit channel stride; token and head strides multiples of 8 elements, 16-byte aligned base
+static void check_heads(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 3 && t.stride(2) == 1 && t.stride(1) % 8 == 0 &&
+                  t.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+              name, " must be bf16 [T, H, d] with unit channel stride and 16-byte aligned head / token strides");
+}
+
 static std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu, int64_t max_seqlen, bool causal,
-                                    double scale, int64_t d_eff) {
-  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 3 && k.dim() == 3 && v.dim() == 3);
-  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous(), "q, k, v must be contiguous [T, H, D]");
+                                    double scale) {
+  check_heads(q, "q"); check_heads(k, "k"); check_heads(v, "v");
   TORCH_CHECK(cu.scalar_type() == at::kInt && cu.is_cuda() && cu.is_contiguous());
   c10::cuda::CUDAGuard guard(q.device());
   const int T = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
-  TORCH_CHECK(Hq % Hkv == 0 && k.size(2) == D && v.size(2) == D && k.size(0) == T && v.size(0) == T);
+  TORCH_CHECK(Hq % Hkv == 0 && k.size(2) == D && v.size(2) == D && k.size(0) == T && v.size(0) == T && v.size(1) == Hkv);
   // cu_seqlens must cover [0, T): every row then belongs to exactly one tile and is written by the kernel
-  Tensor o = torch::empty_like(q);
+  Tensor o = torch::empty({T, Hq, D}, q.options());
   Tensor lse = torch::empty({Hq, T}, q.options().dtype(torch::kFloat));
   Tensor st = vlmt_status_tensor();
   int r = vlmt_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), cu.data_ptr<int>(),
-                        (int)cu.numel() - 1, T, Hq, Hkv, D, (int)d_eff, (long)Hq * D, (long)Hkv * D, (long)Hkv * D, (float)scale, causal,
-                        st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+                        (int)cu.numel() - 1, T, Hq, Hkv, D, q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+                        (float)scale, causal, st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(r == 0, "vlmt_attn_fwd failed with code ", r, " (head_dim ", D, ")");
   (void)max_seqlen;
   return {o, lse};
 }
 
 static std::vector<Tensor> attn_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse,
-                                    const Tensor& cu, int64_t max_seqlen, bool causal, double scale, int64_t d_eff) {
-  TORCH_CHECK(dout.is_contiguous() && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && o.is_contiguous());
+                                    const Tensor& cu, int64_t max_seqlen, bool causal, double scale) {
+  check_heads(q, "q"); check_heads(k, "k"); check_heads(v, "v");
+  TORCH_CHECK(dout.is_contiguous() && o.is_contiguous() && dout.scalar_type() == at::kBFloat16 && dout.sizes() == o.sizes());
   c10::cuda::CUDAGuard guard(q.device());
   const int T = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
-  Tensor dq = torch::empty_like(q), dk = torch::empty_like(k), dv = torch::empty_like(v);
+  Tensor dq = torch::empty({T, Hq, D}, q.options()), dk = torch::empty({T, Hkv, D}, q.options()), dv = torch::empty({T, Hkv, D}, q.options());
   Tensor delta = torch::empty({Hq, T}, q.options().dtype(torch::kFloat));
   Tensor st = vlmt_status_tensor();
   int r = vlmt_attn_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
                         delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr<int>(), (int)cu.numel() - 1, T, Hq,
-                        Hkv, D, (int)d_eff, (float)scale, causal, st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+                        Hkv, D, q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1), (float)scale, causal,
+                        st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(r == 0, "vlmt_attn_bwd failed with code ", r);
   (void)max_seqlen;
   return {dq, dk, dv};

@@ -232,15 +232,15 @@ __global__ void __launch_bounds__(THREADS, 1) dsa_tc_fwd_kernel(Params p) {
     for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
       for (int h = 0; h < REP; ++h) l_thread[h] += __shfl_xor_sync(0xffffffffu, l_thread[h], o);
-    if (lane == 0) {
+    if (lane == 0) {   // the four warps' sums meet in a fixed order: the result is bit-reproducible
 #pragma unroll
-      for (int h = 0; h < REP; ++h) atomicAdd(&lsum[h], l_thread[h]);
+      for (int h = 0; h < REP; ++h) wm[warp * 8 + h] = l_thread[h];
     }
     bar_sync_128();
     float inv[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) {
-      const float l = lsum[h];
+      const float l = (wm[h] + wm[8 + h]) + (wm[16 + h] + wm[24 + h]);
       inv[h] = l > 0.f ? 1.f / l : 0.f;
       if (tid == h) p.lse[(size_t)b * Hq + g * REP + h] = l > 0.f ? (m_run[h] + log2f(l)) * kLn2 : -INFINITY;
     }

@@ -569,6 +569,29 @@ extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t 
   return (int)r;
 }
 
+// 3-D tensor map [d2][d1][d0] (d0 innermost, contiguous) with byte strides for d1 and d2, 128-byte swizzle, zero fill
+// outside the tensor.  Not cached: the callers (attention) build a handful per launch.
+extern "C" int vlmt_make_tmap_3d_bf16(void* out_map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                                      uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -4;
+    ctx_bound = true;
+  }
+  if ((stride1_bytes & 15) || (stride2_bytes & 15) || (reinterpret_cast<uintptr_t>(base) & 15)) return -5;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {box0, box1, box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
 namespace {
 // Everything one launch needs besides the plain GEMM arguments; passed explicitly down to the launcher.
 struct GemmExtras {

@@ -571,53 +571,55 @@ def _pad_heads(t, d_to):
     return torch.nn.functional.pad(t, (0, d_to - t.shape[-1]))
 
 
+def _heads_in_place(t):
+    """``[T, H, d]`` as the attention kernels' tensor maps can read it: unit channel stride, 16-byte aligned head and token
+    strides and base (a slice of a fused projection qualifies); anything else is copied."""
+    if t.stride(2) == 1 and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
 class _AttentionVarlen(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale, d_eff):
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse = _C.attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale, d_eff)
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
+        q, k, v = _heads_in_place(q), _heads_in_place(k), _heads_in_place(v)
+        o, lse = _C.attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale)
         ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
-        ctx.cfg = (max_seqlen, causal, scale, d_eff)
+        ctx.cfg = (max_seqlen, causal, scale)
         _tick()
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse, cu = ctx.saved_tensors
-        max_seqlen, causal, scale, d_eff = ctx.cfg
-        dq, dk, dv = _C.attn_bwd(do.contiguous(), q, k, v, o, lse, cu, max_seqlen, causal, scale, d_eff)
+        max_seqlen, causal, scale = ctx.cfg
+        dq, dk, dv = _C.attn_bwd(do.contiguous(), q, k, v, o, lse, cu, max_seqlen, causal, scale)
         _tick(3)
-        return dq, dk, dv, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
-def _mma_width(valid: int, padded: int) -> int:
-    """Channels the head-dim contractions of the attention kernels cover: the padding beyond ``valid`` (rounded up to
-    the MMA's 16-channel step) is skipped."""
-    return min(padded, (valid + 15) // 16 * 16)
-
-
-def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None, valid_dim=None):
-    """``valid_dim``: q/k/v are zero-padded beyond this many channels (they were padded to the kernel's tile
-    width by the caller); the output keeps the padded width."""
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None):
+    """Varlen attention over packed rows.  Head sizes that are a multiple of 8 up to 128 run as they are (the kernels' tiles
+    are 64 or 128 wide and TMA zero-fills the rest), 256 on the single-tile kernels; sizes in between are zero-padded."""
     D = q.shape[-1]
-    scale = scale if scale is not None else 1.0 / math.sqrt(valid_dim or D)
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if q.dtype != torch.bfloat16:
         return ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
     if not hasattr(_C, "attn_fwd"):
         raise RuntimeError("the attention kernel is not part of this build of the extension")
     cu = cu_seqlens.to(torch.int32)
-    if D in (64, 128, 256):
-        return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale), _mma_width(valid_dim or D, D))
+    if D == 256 or (D <= 128 and D % 8 == 0):
+        if D == 256:
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        return _AttentionVarlen.apply(q, k, v, cu, int(max_seqlen), bool(causal), float(scale))
     if D < 128:
-        # pad the head dim with zeros to the kernel's tile width (ViT head_dim 72); the MMAs skip the padding
-        o = _AttentionVarlen.apply(_pad_heads(q, 128), _pad_heads(k, 128), _pad_heads(v, 128), cu, int(max_seqlen),
-                                   bool(causal), float(scale), _mma_width(D, 128))
+        pad = (D + 7) // 8 * 8
+        o = _AttentionVarlen.apply(_pad_heads(q, pad), _pad_heads(k, pad), _pad_heads(v, pad), cu, int(max_seqlen), bool(causal), float(scale))
         return o[..., :D]
     if D < 256:
-        o = _AttentionVarlen.apply(_pad_heads(q, 256), _pad_heads(k, 256), _pad_heads(v, 256), cu, int(max_seqlen),
-                                   bool(causal), float(scale), 256)
+        o = _AttentionVarlen.apply(_pad_heads(q, 256), _pad_heads(k, 256), _pad_heads(v, 256), cu, int(max_seqlen), bool(causal), float(scale))
         return o[..., :D]
-    raise NotImplementedError(f"attention_varlen: head size {D} is beyond the tcgen05 kernels (64, 128, 256 and what pads to them)")
+    raise NotImplementedError(f"attention_varlen: head size {D} is beyond the tcgen05 kernels (up to 128, 256 and what pads to them)")
 
 
 def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None):
