@@ -135,6 +135,41 @@ def test_attention_reads_strided_heads_in_place():
     _close(qkv.grad, ref_in.grad, 0.05, 3e-2, "dqkv")
 
 
+@pytest.mark.parametrize("L,b0,B,kk", [(3000, 1024, 1024, 512), (700, 0, 700, 64), (5000, 4096, 904, 2048), (300, 256, 44, 128)])
+def test_dsa_indexer_scores_and_topk(L, b0, B, kk):
+    """Indexer scores on the tensor cores + radix-select top-k against fp32 scores and torch.topk: the selected sets are
+    compared through their scores (ties may be broken differently), indices must be causal and distinct."""
+    from vlm_training_b200.ops import cuda as cu
+
+    torch.manual_seed(4)
+    pre = 37                                     # the document starts in the middle of the packed row
+    T = pre + L + 11
+    iq = (torch.randn(T, 4, 64, device="cuda") * 0.3).bfloat16()
+    ik = (torch.randn(T, 64, device="cuda") * 0.3).bfloat16()
+    w = torch.randn(T, 4, device="cuda")
+    sel = cu._C.dsa_select(iq, ik, w, pre + b0, b0, pre, B, min(kk, b0 + B))
+    cu.check_status()
+    kq = min(kk, b0 + B)
+    assert sel.shape == (B, kq)
+    sc = torch.einsum("thd,sd->ths", iq[pre + b0:pre + b0 + B].float(), ik[pre:pre + b0 + B].float()).relu()
+    sc = (sc * w[pre + b0:pre + b0 + B].unsqueeze(-1)).sum(1)
+    qpos = torch.arange(b0, b0 + B, device="cuda").unsqueeze(1)
+    kpos = torch.arange(b0 + B, device="cuda").unsqueeze(0)
+    sc = sc.masked_fill(kpos > qpos, float("-inf"))
+    want = sc.topk(kq, dim=-1).values                                    # [B, kq], descending, -inf where fewer causal keys
+    valid = sel >= 0
+    assert bool(((sel <= qpos) | ~valid).all()), "a selected key lies after its query"
+    n_causal = (qpos.squeeze(1) + 1).clamp(max=kq)
+    assert torch.equal(valid.sum(1), n_causal)
+    srt = torch.where(valid, sel, torch.full_like(sel, -1)).sort(dim=1).values
+    dup = (srt[:, 1:] == srt[:, :-1]) & (srt[:, 1:] >= 0)
+    assert not bool(dup.any()), "an index was selected twice"
+    got = torch.where(valid, sc.gather(1, sel.clamp(min=0).long()), torch.full_like(want, float("-inf"))).sort(dim=1, descending=True).values
+    finite = torch.isfinite(want)
+    assert torch.equal(finite, torch.isfinite(got))
+    torch.testing.assert_close(got[finite], want[finite], atol=2e-3, rtol=1e-3)
+
+
 @pytest.mark.parametrize("D,Hkv,rep,L,B,kk", [(256, 2, 8, 700, 96, 300), (256, 1, 8, 3000, 40, 2048), (64, 2, 2, 300, 50, 64), (128, 1, 4, 513, 33, 2048)])
 def test_dsa_selected_attention_kernels(D, Hkv, rep, L, B, kk):
     """Selected-key attention kernels (forward and backward) against the gathered dense softmax in float32."""

@@ -190,7 +190,7 @@ class SelfAttention(nn.Module):
             xin = column_input(x, self.qkv.tp) if self.qkv.tp.enabled else x
             iq = self.idx_q(xin).view(T, self.cfg.dsa_index_heads, self.cfg.dsa_index_dim)
             o = ops.dsa_attention(q, k, v, iq, self.idx_k(xin), self.idx_w(xin), ctx.cu_seqlens,
-                                  self.cfg.dsa_topk, self.scale)
+                                  self.cfg.dsa_topk, self.scale, cu_host=ctx.extras.get("cu_host"))
         else:
             o = ops.attention_varlen(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True, self.scale)
         o = o.reshape(T, self.n_q * self.head_dim)

@@ -172,9 +172,10 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, 
     return ref.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, scale)
 
 
-def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk: int, scale: float | None = None):
+def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk: int, scale: float | None = None, cu_host=None):
+    """``cu_host``: the document boundaries as a host sequence, if the caller has them (no device read then)."""
     if _use_cuda(q):
-        return _cu().dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale)
+        return _cu().dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale, cu_host)
     return ref.dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale)
 
 

@@ -103,7 +103,33 @@ static Tensor dsa_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const
   return dq;
 }
 
+// indexer scores + top-k of one query block: iq [T, 4, 64] / ik [T, 64] bf16, w [T, 4] fp32; queries are the tokens
+// [q_tok0, q_tok0 + B) at document positions q_pos0.., keys the document's tokens from k_tok0.  -> sel int32 [B, kk]
+static Tensor dsa_select(const Tensor& iq, const Tensor& ik, const Tensor& w, int64_t q_tok0, int64_t q_pos0, int64_t k_tok0, int64_t B,
+                         int64_t kk) {
+  TORCH_CHECK(iq.is_cuda() && iq.scalar_type() == at::kBFloat16 && iq.is_contiguous() && iq.dim() == 3 && iq.size(1) == 4 && iq.size(2) == 64,
+              "indexer queries must be contiguous bf16 [T, 4, 64]");
+  TORCH_CHECK(ik.scalar_type() == at::kBFloat16 && ik.is_contiguous() && ik.dim() == 2 && ik.size(1) == 64 && ik.size(0) == iq.size(0));
+  TORCH_CHECK(w.scalar_type() == at::kFloat && w.is_contiguous() && w.dim() == 2 && w.size(1) == 4 && w.size(0) == iq.size(0));
+  c10::cuda::CUDAGuard guard(iq.device());
+  const int T = iq.size(0);
+  const int n_keys = (int)(q_pos0 + B);
+  TORCH_CHECK(q_tok0 >= 0 && q_tok0 + B <= T && k_tok0 >= 0 && k_tok0 + n_keys <= T && q_tok0 == k_tok0 + q_pos0, "block outside the row");
+  const int ld = (n_keys + 3) & ~3;
+  Tensor scores = torch::empty({B, ld}, iq.options().dtype(torch::kFloat));
+  Tensor sel = torch::empty({B, kk}, iq.options().dtype(torch::kInt));
+  Tensor st = vlmt_status_tensor();
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  int r = vlmt_dsa_index_scores(iq.data_ptr(), ik.data_ptr(), w.data_ptr<float>(), T, (int)q_tok0, (int)q_pos0, (int)k_tok0, (int)B, n_keys,
+                                scores.data_ptr<float>(), ld, st.data_ptr<int>(), stream);
+  TORCH_CHECK(r == 0, "vlmt_dsa_index_scores failed with code ", r);
+  r = vlmt_dsa_topk(scores.data_ptr<float>(), (int)B, ld, (int)q_pos0, (int)kk, sel.data_ptr<int>(), stream);
+  TORCH_CHECK(r == 0, "vlmt_dsa_topk failed with code ", r);
+  return sel;
+}
+
 void bind_attention(pybind11::module_& m) {
+  m.def("dsa_select", &dsa_select);
   m.def("dsa_fwd", &dsa_fwd);
   m.def("dsa_bwd", &dsa_bwd);
   m.def("dsa_supported", [](int64_t D, int64_t rep) { return vlmt_dsa_supported((int)D, (int)rep) != 0; });

@@ -17,6 +17,10 @@ int vlmt_dsa_bwd_tc(const void* q, const void* k, const void* v, const int* sel,
                     float* dq, float* dk, float* dv, int B, int Hkv, int kk, float scale, int* status, cudaStream_t st);
 int vlmt_dsa_bwd(const void* q, const void* k, const void* v, const int* sel, const void* o, const float* lse, const void* d_o,
                  float* dq, float* dk, float* dv, int B, int Hkv, int rep, int D, int kk, float scale, cudaStream_t st);
+// lightning indexer (dsa_indexer_sm100.cu): scores of one query block and the per-query top-k selection
+int vlmt_dsa_index_scores(const void* iq, const void* ik, const float* w, int T, int q_tok0, int q_pos0, int k_tok0, int B, int n_keys,
+                          float* scores, int ld, int* status, cudaStream_t st);
+int vlmt_dsa_topk(const float* scores, int B, int ld, int q_pos0, int kk, int* sel, cudaStream_t st);
 #ifdef __cplusplus
 }
 #endif

@@ -622,10 +622,10 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal=True, scale=None):
     raise NotImplementedError(f"attention_varlen: head size {D} is beyond the tcgen05 kernels (up to 128, 256 and what pads to them)")
 
 
-def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None):
+def dsa_attention(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None, cu_host=None):
     from .dsa_cuda import dsa_attention_cuda
 
-    return dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale)
+    return dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale, cu_host)
 
 
 # ------------------------------------------------------------------------------- loss

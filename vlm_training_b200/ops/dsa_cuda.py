@@ -68,15 +68,26 @@ def _block_attention(qb, kd, vd, sel, valid, scale, rep):
     return out.transpose(0, 1).reshape(B, Hq, D)
 
 
-def dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None):
+def _native_indexer(idx_q, idx_k) -> bool:
+    return (hasattr(cu._C, "dsa_select") and idx_q.dtype == torch.bfloat16 and idx_k.dtype == torch.bfloat16 and idx_q.dim() == 3
+            and idx_q.shape[1:] == (4, 64) and idx_k.shape[-1] == 64 and os.environ.get("VLMT_DSA_INDEXER", "1") != "0")
+
+
+def dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=None, cu_host=None):
+    """``cu_host``: the document boundaries as a host sequence (saves the device read of ``cu_seqlens``)."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     rep = Hq // Hkv
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    bounds = cu_seqlens.tolist()
+    bounds = [int(x) for x in cu_host] if cu_host is not None else cu_seqlens.tolist()
     native = _native(q, k)
+    fused_select = native and _native_indexer(idx_q, idx_k)
+    if fused_select:
+        with torch.no_grad():
+            iq_c, ik_c, iw_c = idx_q.contiguous(), idx_k.contiguous(), idx_w.float().contiguous()
     if max(b - a for a, b in zip(bounds[:-1], bounds[1:])) <= topk:
         return cu.attention_varlen(q, k, v, cu_seqlens, 0, True, scale)
+    # documents end where the packed row ends: tokens behind the last boundary are padding
     outs = []
     for s, e in zip(bounds[:-1], bounds[1:]):
         L = e - s
@@ -87,11 +98,17 @@ def dsa_attention_cuda(q, k, v, idx_q, idx_k, idx_w, cu_seqlens, topk, scale=Non
             outs.append(cu.attention_varlen(q[s:e], k[s:e], v[s:e], c, L, True, scale))
             continue
         kd, vd = k[s:e], v[s:e]
-        ik = idx_k[s:e].float()
+        ik = None if fused_select else idx_k[s:e].float()
         doc_out = []
         for b0 in range(0, L, _QBLOCK):
             b1 = min(L, b0 + _QBLOCK)
             n_keys = b1  # causal: keys [0, b1)
+            if fused_select:
+                # scores on the tensor cores and a radix-select top-k, two launches per block, -1 in unused slots
+                sel32 = cu._C.dsa_select(iq_c, ik_c, iw_c, s + b0, b0, s, b1 - b0, min(topk, n_keys))
+                cu._tick(2)
+                doc_out.append(_SelectedAttention.apply(q[s + b0:s + b1], kd, vd, sel32, scale))
+                continue
             with torch.no_grad():  # the selection is an index set: nothing of it is kept for backward
                 sc = torch.einsum("thd,sd->ths", idx_q[s + b0:s + b1].float(), ik[:n_keys]).relu_()
                 sc = (sc * idx_w[s + b0:s + b1].float().unsqueeze(-1)).sum(1)  # [B, n_keys]
