@@ -208,6 +208,31 @@ def bench_gdn_scan(t: Timer, tokens=16384, docs=1, heads=32, reverse=False):
     return out
 
 
+def bench_gdn(t: Timer, tokens=16384, docs=16, heads=32, backward=False):
+    """The whole gated delta rule (prepare -> scan -> output, and back) on one packed row; ``VLMT_GDN_CHUNK=0`` times the
+    form with tensor operations inside the chunks.  The byte count is the op's inputs and outputs once (q, k, v, o and, with
+    the backward pass, their gradients), so the fraction says how far the op is from a pass over its own tensors."""
+    from .. import ops
+
+    per = tokens // docs
+    cu_list = [i * per for i in range(docs)] + [tokens]
+    cu_t = torch.tensor(cu_list, device="cuda", dtype=torch.int32)
+    q, k, v = (_r(tokens, heads, 128, scale=0.5).requires_grad_() for _ in range(3))
+    g = (-torch.rand(tokens, heads, device="cuda") * 0.2).requires_grad_()
+    b = torch.rand(tokens, heads, device="cuda").requires_grad_()
+    go = _r(tokens, heads, 128, scale=0.5)
+    io = 4.0 * tokens * heads * 128 * 2
+    if not backward:
+        with torch.no_grad():
+            ms = t(lambda: ops.gated_delta_rule(q, k, v, g, b, cu_t, None, 64, cu_host=cu_list))
+        return _report("gated_delta_rule_fwd", [tokens, docs, heads], ms, nbytes=io)
+
+    def fb():
+        o = ops.gated_delta_rule(q, k, v, g, b, cu_t, None, 64, cu_host=cu_list)
+        torch.autograd.grad(o, (q, k, v, g, b), go)
+    return _report("gated_delta_rule_fwd_bwd", [tokens, docs, heads], t(fb), nbytes=2.0 * io)
+
+
 def bench_conv1d(t: Timer, tokens=16384, channels=8192, backward=False):
     from .. import ops
     from . import reference as ref
@@ -282,7 +307,7 @@ def bench_gemm_ag(t: Timer, m=8192, n=3072, k=4096, b_mn=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "conv1d", "dsa", "fused_adamw", "gemm_ag", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -319,6 +344,8 @@ def main(argv=None):
         bench_adamw(t)
     elif a.what == "moe":
         bench_moe(t)
+    elif a.what == "gdn":
+        bench_gdn(t, a.tokens, a.docs, heads=a.heads or 32, backward=a.backward)
     elif a.what == "gdn_scan":
         bench_gdn_scan(t, a.tokens, a.docs, reverse=a.backward)
     elif a.what == "conv1d":
