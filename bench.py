@@ -48,6 +48,7 @@ def parse():
     ap.add_argument("--opt-state", default="auto", choices=["auto", "fp32", "bf16"])
     ap.add_argument("--vit-ac", default="auto", choices=["auto", "off", "full"])
     ap.add_argument("--reshard", action="store_true", help="shard parameters and gradients too (ZeRO-3 residency); not the default layout")
+    ap.add_argument("--no-fuse-first-gemm", action="store_true", help="with --reshard: gather every weight by the block's parameter gather")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--sync-debug", action="store_true", help="warn on every host<->device synchronisation inside the end-to-end loop")
     ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file (not a bench run)")
@@ -118,6 +119,7 @@ def build_config(args, world: int):
     t.optimizer_state_dtype = args.opt_state if args.opt_state != "auto" else "bf16"
     t.fused_comm = os.environ.get("VLMT_FUSED_COMM", "1") == "1"
     t.reshard_params = bool(args.reshard)
+    t.reshard_fuse_first_gemm = not args.no_fuse_first_gemm
     t.output_dir = "/tmp/vlmt_bench"
     cfg.data.synthetic = "vlm" if "vl" in args.model else "text-loguniform"
     cfg.data.seq_len = args.seq_len

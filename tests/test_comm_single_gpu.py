@@ -171,6 +171,43 @@ def test_gemm_all_gather_gives_up_when_the_peer_never_signals(short_waits):
     _still_works(cu)
 
 
+@pytest.mark.parametrize("rank,world", [(0, 2), (1, 2), (2, 4)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_with_the_weight_gather_inside_as_one_rank(short_waits, rank, world, with_bias):
+    """The parameter all-gather -> GEMM kernel with every rank's shard staged in local memory: the weight sits in the middle
+    of a flat bucket, its region of the local whole bucket starts as NaN, and after the launch the product is right and
+    the region holds the gathered weight (the rest of the bucket is untouched)."""
+    cu = short_waits
+    torch.manual_seed(7)
+    M, N, K = 1024, 768, 512
+    shard = (N * K + 4096) // world // 8 * 8 + 8           # the weight straddles every shard boundary
+    total = shard * world
+    w_lo = 1000 // 8 * 8
+    assert w_lo + N * K <= total
+    flat = (torch.randn(total, device="cuda") * 0.05).bfloat16()
+    shards = [flat[r * shard:(r + 1) * shard].clone() for r in range(world)]
+    bucket = torch.full((total,), float("nan"), device="cuda", dtype=torch.bfloat16)
+    bucket[:w_lo] = 7.0
+    bucket[w_lo + N * K:] = 7.0
+    w = bucket[w_lo:w_lo + N * K].view(N, K)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16() if with_bias else None
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    sync = torch.zeros(2 * world, dtype=torch.int32, device="cuda")
+    for epoch in (1, 2):                                    # a second call reuses the flags and counters
+        if epoch == 2:
+            bucket[w_lo:w_lo + N * K] = float("nan")
+        cu._C.gemm_wgather(x, w, out, bias, bucket, [t.data_ptr() for t in shards], shard, rank, sync, epoch)
+        torch.cuda.synchronize()
+        assert cu.check_status() == 0
+        w_ref = flat[w_lo:w_lo + N * K].view(N, K)
+        assert torch.equal(w, w_ref)
+        assert bool((bucket[:w_lo] == 7.0).all()) and bool((bucket[w_lo + N * K:] == 7.0).all())
+        ref = x.float() @ w_ref.float().t() + (bias.float() if with_bias else 0.0)
+        torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-1)
+    _still_works(cu)
+
+
 def test_debug_validation_of_index_tensors_sets_the_status_word(short_waits):
     """``VLMT_DEBUG_CHECKS``: bad ``cu_seqlens`` / image rows / expert ids are reported through the status word (no host read
     at the point of the check), good ones leave it alone."""

@@ -30,6 +30,8 @@ if tr.rank == 0:
     os.makedirs(cfg.training.output_dir, exist_ok=True)
     json.dump([m["train/loss"] for m in hist], open(os.path.join(cfg.training.output_dir, "losses.json"), "w"))
     json.dump(probe.tolist(), open(os.path.join(cfg.training.output_dir, "probe.json"), "w"))
+    from vlm_training_b200.parallel.engine import _PendingWeightGather
+    json.dump(_PendingWeightGather.RUNS, open(os.path.join(cfg.training.output_dir, "wgather.json"), "w"))
 if torch.distributed.is_initialized():
     torch.distributed.destroy_process_group()
 """
@@ -53,6 +55,7 @@ def _run(tmp_path, nproc, extra, port, env_extra=None):
         cut = err.find("Traceback")
         raise AssertionError(res.stdout[-1500:] + err[max(0, cut - 200):cut + 3500])
     _run.last_probe = json.load(open(out / "probe.json"))
+    _run.last_wgather = json.load(open(out / "wgather.json"))
     return json.load(open(out / "losses.json"))
 
 
@@ -230,6 +233,13 @@ def test_sharded_parameters_match_whole_parameters_on_gpus(tmp_path):
         assert sharded == pytest.approx(whole, rel=2e-3, abs=2e-3)
         frac_off = ((torch.tensor(_run.last_probe) - probe_whole).abs() > 5e-4).float().mean().item()
         assert frac_off < 0.02, f"{frac_off:.3f} of the sampled weights differ (fused_comm {fused})"
+        # with our own gathers the qkv weight of every decoder layer (4 layers x 4 steps) and of the ViT blocks arrives inside
+        # its GEMM; with the library all-gather never
+        assert (_run.last_wgather["gemm"] >= 16) if fused == "true" else (_run.last_wgather["gemm"] == 0), _run.last_wgather
+    plain = _run(tmp_path, 2, ["--training.fused_comm", "true", "--training.reshard_params", "true",
+                               "--training.reshard_fuse_first_gemm", "false"], 29724, {"VLMT_NO_MULTIMEM": "1"})
+    assert _run.last_wgather["gemm"] == 0
+    assert plain == pytest.approx(whole, rel=2e-3, abs=2e-3)
 
 
 def test_fused_optimizer_with_gradient_clipping_matches_nccl(tmp_path):

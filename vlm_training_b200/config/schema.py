@@ -109,6 +109,9 @@ class TrainingSection:
     # release a unit's gathered parameters right after its forward pass (and gather again for backward);
     # false keeps them until the unit's backward pass is done (the reference's default FSDP policy)
     reshard_after_forward: bool = True
+    # with reshard_params on GPUs (fused_comm, no tensor parallelism): a block's first weight (qkv / in_proj) is gathered by
+    # the GEMM that reads it instead of by the block's parameter gather
+    reshard_fuse_first_gemm: bool = True
     beta1: float = 0.9
     beta2: float = 0.999
     seed: int = 42

@@ -105,6 +105,32 @@ void gemm_ag(const Tensor& x_local, Tensor& x_full, const Tensor& b, Tensor& out
   TORCH_CHECK(r == 0, "vlmt_gemm_bf16_ag failed with code ", r);
 }
 
+// Y = X W^T (+ bias) with the weight's all-gather inside the kernel: `w` is the [N, K] view of the weight inside the local
+// whole bucket `bucket` (flat bf16), `shard_ptrs` the shard base of every rank, `sync` an int32 tensor of 2 * world entries
+// (flags, then counters; zero before the first use), `epoch` growing with every call that shares `sync`.
+void gemm_wgather(const Tensor& x, const Tensor& w, Tensor& out, const c10::optional<Tensor>& bias, Tensor& bucket,
+                  const std::vector<int64_t>& shard_ptrs, int64_t shard, int64_t rank, Tensor& sync, int64_t epoch) {
+  check_bf16(x, "x"); check_bf16(w, "w"); check_bf16(out, "out"); check_bf16(bucket, "bucket");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && w.is_contiguous() && out.stride(1) == 1 &&
+              bucket.is_contiguous());
+  const int world = (int)shard_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world && sync.scalar_type() == at::kInt && sync.is_cuda() &&
+              sync.numel() >= 2 * world);
+  const int M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == M && out.size(1) == N, "gemm_wgather: bad shapes");
+  const int64_t w_lo = (reinterpret_cast<char*>(w.data_ptr()) - reinterpret_cast<char*>(bucket.data_ptr())) / 2;
+  TORCH_CHECK(w_lo >= 0 && w_lo + (int64_t)N * K <= bucket.numel() && shard * world >= bucket.numel(), "gemm_wgather: the weight is not inside the bucket");
+  c10::cuda::CUDAGuard guard(x.device());
+  const void* sp[8];
+  for (int i = 0; i < world; ++i) sp[i] = reinterpret_cast<const void*>(shard_ptrs[i]);
+  Tensor st = status_tensor();
+  int r = vlmt_gemm_bf16_wgather(x.data_ptr(), out.data_ptr(), optptr(bias), M, N, K, (int)x.stride(0), (int)out.stride(0), bucket.data_ptr(),
+                                 (long)w_lo, sp, (long)shard, world, (int)rank, sync.data_ptr<int>(),
+                                 reinterpret_cast<unsigned*>(sync.data_ptr<int>() + world), (int)epoch, st.data_ptr<int>(), num_sms(),
+                                 cur_stream());
+  TORCH_CHECK(r == 0, "vlmt_gemm_bf16_wgather failed with code ", r);
+}
+
 // grouped GEMM over padded row groups (see gemm_sm100.h); prefix: int32 device tensor [groups + 1]
 void gemm_grouped(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& prefix, int64_t mode, bool b_mn) {
   check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(out, "out");
@@ -464,6 +490,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("gemm_rs_push", &gemm_rs_push);
   m.def("gemm_ag", &gemm_ag);
+  m.def("gemm_wgather", &gemm_wgather);
   m.def("gemm_set_flag_wait_ms", [](int64_t ms) {
     int r = vlmt_gemm_set_flag_wait_ms((long)ms);
     TORCH_CHECK(r == 0, "vlmt_gemm_set_flag_wait_ms failed with code ", r);

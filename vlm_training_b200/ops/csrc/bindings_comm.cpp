@@ -109,6 +109,14 @@ static void pull_gather(const std::vector<int64_t>& slot_ptrs, Tensor& out, int6
                            st.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(r == 0, "vlmt_pull_gather failed with code ", r);
 }
+static void pull_gather_range(const std::vector<int64_t>& slot_ptrs, Tensor& out, int64_t n_per_rank, int64_t lo, int64_t hi) {
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kBFloat16 && lo >= 0 && hi <= out.numel());
+  c10::cuda::CUDAGuard guard(out.device());
+  void* s[16];
+  fill_ptrs(slot_ptrs, s);
+  int r = vlmt_pull_gather_range(s, out.data_ptr(), n_per_rank, (int)slot_ptrs.size(), lo, hi, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(r == 0, "vlmt_pull_gather_range failed with code ", r);
+}
 static void pull_reduce(const std::vector<int64_t>& slot_ptrs, Tensor& out, const c10::optional<Tensor>& residual, int64_t n_per_rank,
                         int64_t my_rank, int64_t my_flags, int64_t epoch) {
   TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kBFloat16);
@@ -131,6 +139,7 @@ void bind_comm(pybind11::module_& m) {
   m.def("signal_peers_at", &signal_peers_at);
   m.def("wait_flags", &wait_flags);
   m.def("pull_gather", &pull_gather);
+  m.def("pull_gather_range", &pull_gather_range);
   m.def("pull_reduce", &pull_reduce);
   m.def("fused_rs_adamw_ag", &fused_rs_adamw_ag);
   m.def("rs_reduce_sumsq", &rs_reduce_sumsq);

@@ -311,6 +311,25 @@ __global__ void pull_gather_kernel(PeerPtrs slots, bf16* __restrict__ out, long 
   }
 }
 
+// the elements [lo, hi) of the gathered array only (out[r * n + j] = slot_r[j]); no flags: the slots do not change meanwhile
+__global__ void pull_gather_range_kernel(PeerPtrs slots, bf16* __restrict__ out, long n, int world, long lo, long hi) {
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (int r = 0; r < world; ++r) {
+    const long a = max(lo, (long)r * n), b = min(hi, (long)(r + 1) * n);
+    if (b <= a) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(slots.p[r]) + (a - (long)r * n));
+    uint4* dst = reinterpret_cast<uint4*>(out + a);
+    const long nvec = (b - a) >> 3;
+    long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      const uint4 v0 = ld_peer_16B(src + i), v1 = ld_peer_16B(src + i + stride), v2 = ld_peer_16B(src + i + 2 * stride),
+                  v3 = ld_peer_16B(src + i + 3 * stride);
+      dst[i] = v0; dst[i + stride] = v1; dst[i + 2 * stride] = v2; dst[i + 3 * stride] = v3;
+    }
+    for (; i < nvec; i += stride) dst[i] = ld_peer_16B(src + i);
+  }
+}
+
 // reduce-scatter: out[0:n] = (residual) + sum_r slot_r[me * n : (me + 1) * n]   (own slot included; fp32 accumulation)
 // With `pushed` the producers already stored their blocks into THIS rank's slot (block r from rank r): slots.p[r] then
 // points at local memory and the reads stay on this GPU.
@@ -360,6 +379,16 @@ int vlmt_pull_gather(void* const* slot_ptrs, void* out, long n_per_rank, int wor
   long blocks = ((n_per_rank >> 3) + 255) / 256;
   if (blocks > 148 * 2) blocks = 148 * 2;
   pull_gather_kernel<<<(int)blocks, 256, 0, st>>>(s, reinterpret_cast<bf16*>(out), n_per_rank, world, my_flags, epoch, status);
+  return (int)cudaGetLastError();
+}
+int vlmt_pull_gather_range(void* const* slot_ptrs, void* out, long n_per_rank, int world, long lo, long hi, cudaStream_t st) {
+  if (world > MAX_PEERS || (n_per_rank & 7) || (lo & 7) || (hi & 7)) return -1;
+  if (hi <= lo) return 0;
+  PeerPtrs s;
+  for (int r = 0; r < world; ++r) s.p[r] = slot_ptrs[r];
+  long blocks = (((hi - lo) >> 3) + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  pull_gather_range_kernel<<<(int)blocks, 256, 0, st>>>(s, reinterpret_cast<bf16*>(out), n_per_rank, world, lo, hi);
   return (int)cudaGetLastError();
 }
 int vlmt_pull_reduce(void* const* slot_ptrs, void* out, const void* residual, long n_per_rank, int world, int my_rank,

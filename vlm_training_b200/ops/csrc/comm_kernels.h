@@ -37,6 +37,8 @@ int vlmt_wait_flags(const int* my_flags, int world, int epoch, int skip_rank, in
 // out[r*n:(r+1)*n] = rank r's slot (bf16 elements); waits (bounded) for every rank's signal `epoch`
 int vlmt_pull_gather(void* const* slot_ptrs, void* out, long n_per_rank, int world, const int* my_flags, int epoch, int* status,
                      cudaStream_t st);
+// the same for the elements [lo, hi) of the gathered array only (multiples of 8); no flags
+int vlmt_pull_gather_range(void* const* slot_ptrs, void* out, long n_per_rank, int world, long lo, long hi, cudaStream_t st);
 // out[0:n] = residual + sum_r slot_r[me*n:(me+1)*n]
 int vlmt_pull_reduce(void* const* slot_ptrs, void* out, const void* residual, long n_per_rank, int world, int my_rank,
                      const int* my_flags, int epoch, int* status, cudaStream_t st);

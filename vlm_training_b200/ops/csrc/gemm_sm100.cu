@@ -82,6 +82,16 @@ struct Params {
   int* ag_flag_dst[MAX_RANKS];  // flag array of every rank
   const int* ag_flags;          // this rank's flag array
   unsigned* ag_counter;         // local: CTAs that have finished their share of the push (reset by the last one)
+  // parameter all-gather -> GEMM (AG variant, wg_world > 0): B is a weight [N, K] that lives at element wg_lo of a flat
+  // parameter bucket sharded over wg_world ranks (wg_shard elements each).  Warps 6 and 7 copy every owner's part of the
+  // weight from that owner's shard (peer loads) into the local whole bucket, owner by owner starting with this rank; the
+  // TMA producer waits for the owners of a tile's weight rows before it loads them from LOCAL memory.
+  int wg_world, wg_rank, wg_epoch;
+  long wg_shard, wg_lo;
+  const __nv_bfloat16* wg_src[MAX_RANKS];   // shard base of every rank
+  __nv_bfloat16* wg_dst;                    // local bucket base
+  int* wg_flags;                            // local: wg_flags[o] = wg_epoch once owner o's part is here
+  unsigned* wg_counters;                    // local, one per owner
   // Grouped GEMM (one launch for all experts of a MoE layer).  Rows of every group are padded to whole 128-row tiles
   // and laid out back to back; grp_prefix[g] (device memory, G + 1 ints) is the first tile of group g.
   //   grp_mode 1 (forward / dgrad): groups partition the M dimension; group g multiplies its rows with its own B
@@ -125,6 +135,11 @@ __device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint4 ld_volatile_16B(const void* p) {   // peer memory: never through a stale L1 line
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ void st_release_sys_s32(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -164,7 +179,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (AG) tma_prefetch_desc(&tmap_a2);
   }
   // AG: M tiles are visited starting with this rank's own block, so the peers' rows are needed as late as possible
-  const int ag_rot = AG ? p.ag_rank * (p.ag_rows / BM) : 0;
+  const int ag_rot = (AG && p.ag_world > 0) ? p.ag_rank * (p.ag_rows / BM) : 0;
+  // weight gather: N tiles are visited starting with the first tile of this rank's own part of the weight
+  int wg_rot = 0;
+  if (AG && p.wg_world > 0) {
+    const long own = (long)p.wg_rank * p.wg_shard - p.wg_lo;       // first element of the weight inside this rank's shard
+    const long row = own <= 0 ? 0 : (own + p.K - 1) / p.K;
+    wg_rot = (int)min((long)(tiles_n - 1), row / BN);
+  }
   // the MMA thread and the epilogue depend on a producer that may be waiting for a peer: their own bound covers that wait
   const unsigned long long wait_ns = AG ? kWaitLimitNs + g_gemm_flag_wait_ns : kWaitLimitNs;
   if (warp == 1) tmem_alloc<TMEM_COLS>(tmem_slot);
@@ -196,10 +218,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tile_coords(tile, tiles_m, tiles_n, tm, tn);
           if (p.grp_mode == 1) b_row = group_of_tile(p.grp_prefix, p.grp_count, tm) * p.grp_b_rows;
         }
-        if (AG) { tm += ag_rot; if (tm >= tiles_m) tm -= tiles_m; }
+        if (AG) { tm += ag_rot; if (tm >= tiles_m) tm -= tiles_m; tn += wg_rot; if (tn >= tiles_n) tn -= tiles_n; }
         const int m0 = tm * BM, n0 = tn * BN;
         bool own_rows = false;
-        if (AG) {
+        if (AG && p.wg_world > 0) {
+          // owners of the weight rows [n0, n0 + BN): wait (bounded) until their parts are in the local bucket
+          const long f_lo = p.wg_lo + (long)n0 * p.K, f_hi = p.wg_lo + (long)min(n0 + BN, p.N) * p.K;
+          const int o_lo = (int)(f_lo / p.wg_shard), o_hi = (int)((f_hi - 1) / p.wg_shard);
+          for (int o = o_lo; o <= o_hi && ok; ++o) {
+            if ((ag_ready >> o) & 1u) continue;
+            const unsigned long long t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_sys_s32(p.wg_flags + o) < p.wg_epoch) {
+              if ((++spins & 0xff) == 0) {
+                if (*abort_flag) { ok = false; break; }
+                if (globaltimer_ns() - t0 > g_gemm_flag_wait_ns) {
+                  *abort_flag = 1;
+                  atomicCAS(p.status, 0, 100 + o);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (ok) ag_ready |= 1u << o;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");  // written by ordinary stores of other CTAs, read through TMA
+        }
+        if (AG && p.ag_world > 0) {
           const int owner = m0 / p.ag_rows;
           own_rows = owner == p.ag_rank;
           if (!own_rows && !((ag_ready >> owner) & 1u)) {
@@ -293,6 +339,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (ok) umma_commit(&tmem_full[acc]);
       }
     }
+  } else if (AG && warp >= 6 && p.wg_world > 0) {
+    // ------------------------------------------------------------ weight gather (warps 6, 7): peer shards -> local bucket
+    const int t = threadIdx.x - NUM_THREADS;
+    const long stride = (long)gridDim.x * AG_PUSH_THREADS;
+    const long w_hi = p.wg_lo + (long)p.N * p.K;
+    for (int step = 0; step < p.wg_world; ++step) {
+      const int o = (p.wg_rank + step) % p.wg_world;
+      const long lo = max(p.wg_lo, (long)o * p.wg_shard), hi = min(w_hi, (long)(o + 1) * p.wg_shard);
+      if (hi > lo) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.wg_src[o] + (lo - (long)o * p.wg_shard));
+        uint4* dst = reinterpret_cast<uint4*>(p.wg_dst + lo);
+        const long nvec = (hi - lo) >> 3;
+        long i = (long)blockIdx.x * AG_PUSH_THREADS + t;
+        for (; i + 7 * stride < nvec; i += 8 * stride) {   // eight 16-byte loads in flight per thread: the link's latency is long
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = ld_volatile_16B(src + i + u * stride);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) dst[i + u * stride] = v[u];
+        }
+        for (; i < nvec; i += stride) dst[i] = ld_volatile_16B(src + i);
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(AG_PUSH_THREADS) : "memory");
+      if (t == 0) {
+        const unsigned done = atomicAdd(p.wg_counters + o, 1u);
+        if (done == gridDim.x - 1) {                           // every CTA's share of this owner's part has been stored
+          p.wg_counters[o] = 0;                                // ready for the next launch (stream-ordered)
+          __threadfence();
+          st_release_sys_s32(p.wg_flags + o, p.wg_epoch);
+        }
+      }
+    }
   } else if (AG && warp >= 6) {
     // ------------------------------------------------------------ all-gather push (warps 6, 7)
     // this rank's rows -> the gathered buffer of every rank; 16-byte vectors, four loads in flight per thread
@@ -340,7 +419,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       } else {
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
       }
-      if (AG) { tm += ag_rot; if (tm >= tiles_m) tm -= tiles_m; }
+      if (AG) { tm += ag_rot; if (tm >= tiles_m) tm -= tiles_m; tn += wg_rot; if (tn >= tiles_n) tn -= tiles_n; }
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kErrTimeoutTmemFull, wait_ns)) { ok = false; break; }
@@ -608,6 +687,13 @@ struct GemmExtras {
   void* const* ag_flag_dst = nullptr;
   const int* ag_flags = nullptr;
   unsigned* ag_counter = nullptr;
+  // parameter all-gather -> GEMM
+  int wg_world = 0, wg_rank = 0, wg_epoch = 0;
+  long wg_shard = 0, wg_lo = 0;
+  const void* const* wg_src = nullptr;
+  void* wg_dst = nullptr;
+  int* wg_flags = nullptr;
+  unsigned* wg_counters = nullptr;
 };
 
 bool split_k_enabled() {
@@ -709,6 +795,18 @@ int gemm_launch(const void* A, const void* B, void* D, float* Dacc32, const void
   }
   p.ag_world = 0; p.ag_rank = 0; p.ag_rows = 0; p.ag_epoch = 0;
   p.ag_src = nullptr; p.ag_flags = nullptr; p.ag_counter = nullptr;
+  p.wg_world = 0; p.wg_rank = 0; p.wg_epoch = 0; p.wg_shard = 0; p.wg_lo = 0; p.wg_dst = nullptr; p.wg_flags = nullptr; p.wg_counters = nullptr;
+  if (x.wg_world > 0) {
+    // the weight's rows are gathered inside the kernel: K-major B only, every owner's part a whole number of 16-byte vectors
+    if (a_mn_major || b_mn_major || !bn256 || x.wg_world > MAX_RANKS || (x.wg_shard & 7) || (x.wg_lo & 7) || (((long)N * K) & 7) || ldb != K ||
+        x.ag_world > 0 || x.rs_world > 0 || x.grp_mode != 0)
+      return -41;
+    p.wg_world = x.wg_world; p.wg_rank = x.wg_rank; p.wg_epoch = x.wg_epoch; p.wg_shard = x.wg_shard; p.wg_lo = x.wg_lo;
+    for (int i = 0; i < x.wg_world; ++i) p.wg_src[i] = reinterpret_cast<const __nv_bfloat16*>(x.wg_src[i]);
+    p.wg_dst = reinterpret_cast<__nv_bfloat16*>(x.wg_dst);
+    p.wg_flags = x.wg_flags; p.wg_counters = x.wg_counters;
+    return launch_variant<256, false, false, true>(ta, tb, td, ta2, *rsm, p, num_sms, stream);
+  }
   if (x.ag_world > 0) {
     if (a_mn_major || !bn256 || x.ag_world > MAX_RANKS || x.ag_rows % BM != 0 || x.ag_rows * x.ag_world != M || (K & 7) ||
         (reinterpret_cast<uintptr_t>(x.ag_src) & 15))
@@ -794,4 +892,18 @@ extern "C" int vlmt_gemm_bf16_ag(const void* src, void* A_full, const void* B, v
 extern "C" int vlmt_gemm_set_flag_wait_ms(long ms) {
   const unsigned long long ns = (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
   return (int)cudaMemcpyToSymbol(g_gemm_flag_wait_ns, &ns, sizeof(ns));
+}
+
+// Y[M, N] = X[M, K] . W^T where W [N, K] sits at element `w_lo` of a flat parameter bucket that is sharded over `world`
+// ranks (`shard` elements each): the kernel copies every owner's part of W from `shard_ptrs[o]` (peer memory) into the
+// local bucket `bucket` while its first tiles run on this rank's own part.  `flags` / `counters`: local int32 / uint32
+// arrays of `world` entries (zero before the first use); `epoch` grows with every call that uses them.
+extern "C" int vlmt_gemm_bf16_wgather(const void* X, void* D, const void* bias, int M, int N, int K, int ldx, int ldd, void* bucket, long w_lo,
+                                      const void* const* shard_ptrs, long shard, int world, int rank, int* flags, unsigned* counters,
+                                      int epoch, int* status, int num_sms, cudaStream_t stream) {
+  GemmExtras x;
+  x.wg_world = world; x.wg_rank = rank; x.wg_epoch = epoch; x.wg_shard = shard; x.wg_lo = w_lo;
+  x.wg_src = shard_ptrs; x.wg_dst = bucket; x.wg_flags = flags; x.wg_counters = counters;
+  const void* W = reinterpret_cast<const __nv_bfloat16*>(bucket) + w_lo;
+  return gemm_launch(X, W, D, nullptr, bias, M, N, K, ldx, K, ldd, 0, 0, GEMM_EPI_NONE, 0, x, status, num_sms, stream);
 }

@@ -32,6 +32,11 @@ int vlmt_gemm_bf16_grouped(const void* A, const void* B, void* D, const int* pre
 // `epoch` into flag_dst[r][rank] of every peer when the copy is complete, computes the tiles of its own rows from `src`
 // meanwhile and reads a peer's block of A_full once flags[peer] >= epoch (bounded wait -> status 100 + peer).
 // counter: one zero-initialised unsigned in local device memory.  B K-major or MN-major; N > 128; rows % 128 == 0.
+// parameter all-gather inside the consuming GEMM: Y = X W^T with W [N, K] at element w_lo of a flat parameter bucket that is
+// sharded over `world` ranks (`shard` elements each, peer-readable at shard_ptrs[o]); see gemm_sm100.cu
+int vlmt_gemm_bf16_wgather(const void* X, void* D, const void* bias, int M, int N, int K, int ldx, int ldd, void* bucket, long w_lo,
+                           const void* const* shard_ptrs, long shard, int world, int rank, int* flags, unsigned* counters, int epoch,
+                           int* status, int num_sms, cudaStream_t stream);
 int vlmt_gemm_bf16_ag(const void* src, void* A_full, const void* B, void* D, void* const* gathered, void* const* flag_dst,
                       const int* flags, unsigned* counter, int epoch, int world, int rank, int rows, int N, int K, int ldb, int ldd,
                       int b_mn_major, int* status, int num_sms, cudaStream_t stream);

@@ -89,6 +89,15 @@ def _gemm(a, b, a_mn=False, b_mn=False, bias=None, epilogue=0, out=None, accumul
     N = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    pending = getattr(b, "_vlmt_wgather", None)
+    if pending is not None:
+        # a sharded weight whose gather was left to this GEMM (parallel/engine.py): its owners' parts arrive inside the kernel
+        if (not a_mn and not b_mn and epilogue == 0 and not accumulate and out.dtype == torch.bfloat16 and a.dtype == torch.bfloat16
+                and a.dim() == 2 and a.stride(1) == 1 and b.is_contiguous() and b.shape[0] > 128):
+            pending.run(a, b, out, bias)
+            _tick()
+            return out
+        pending.finish()
     if b.untyped_storage().size() == 0 or out.untyped_storage().size() == 0:
         # a sharded parameter (or its gradient bucket) whose storage is released: an error here, never a kernel on freed memory
         raise RuntimeError("GEMM operand without storage: a sharded parameter was used outside the forward / backward of its unit")

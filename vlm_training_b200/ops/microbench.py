@@ -233,6 +233,29 @@ def bench_gdn(t: Timer, tokens=16384, docs=16, heads=32, backward=False):
     return _report("gated_delta_rule_fwd_bwd", [tokens, docs, heads], t(fb), nbytes=2.0 * io)
 
 
+def bench_gemm_wgather(t: Timer, m=8192, n=6144, k=4096, world=2):
+    """The parameter all-gather -> GEMM kernel run as rank 0 of ``world`` on one GPU: the peers' shards are staged in local
+    memory, so no link is crossed; shows what the copy warps and the gated B tiles cost next to the plain GEMM."""
+    from . import cuda as cu
+
+    shard = (n * k // world + 4096) // 8 * 8
+    flat = _r(shard * world, scale=0.05)
+    shards = [flat[r * shard:(r + 1) * shard].clone() for r in range(world)]
+    bucket = torch.zeros_like(flat)
+    w = bucket[1024:1024 + n * k].view(n, k)
+    x = _r(m, k)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    sync = torch.zeros(2 * world, dtype=torch.int32, device="cuda")
+    ptrs = [s_.data_ptr() for s_ in shards]
+    epoch = [0]
+
+    def fn():
+        epoch[0] += 1
+        cu._C.gemm_wgather(x, w, out, None, bucket, ptrs, shard, 0, sync, epoch[0])
+    _report(f"gemm_weight_gather_rank0_of_{world}", [m, n, k], t(fn), flops=2.0 * m * n * k)
+    return _report("gemm_fwd_same_shape", [m, n, k], t(lambda: cu._gemm(x, w)), flops=2.0 * m * n * k)
+
+
 def bench_conv1d(t: Timer, tokens=16384, channels=8192, backward=False):
     from .. import ops
     from . import reference as ref
@@ -307,7 +330,7 @@ def bench_gemm_ag(t: Timer, m=8192, n=3072, k=4096, b_mn=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_wgather", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -344,6 +367,8 @@ def main(argv=None):
         bench_adamw(t)
     elif a.what == "moe":
         bench_moe(t)
+    elif a.what == "gemm_wgather":
+        bench_gemm_wgather(t, a.m, a.n, a.k)
     elif a.what == "gdn":
         bench_gdn(t, a.tokens, a.docs, heads=a.heads or 32, backward=a.backward)
     elif a.what == "gdn_scan":

@@ -80,6 +80,36 @@ class _Bucket:
     index: int = 0
 
 
+class _PendingWeightGather:
+    """A weight whose part of the unit's parameter gather was left out because the GEMM that consumes it first gathers it
+    itself (``gemm_sm100.cu``, weight-gather mode: peer loads of every owner's part into the local bucket, under the tiles
+    that run on this rank's own part).  ``run`` is that GEMM; ``finish`` is the plain pull for a consumer that cannot
+    take it (another layout, an epilogue)."""
+
+    RUNS = {"gemm": 0, "pull": 0}   # how often a weight arrived inside its GEMM / by the plain pull (tests read it)
+
+    def __init__(self, domain, index, param, lo, ptrs, shard_numel, epoch):
+        self.domain, self.index, self.param, self.lo = domain, index, param, lo
+        self.ptrs, self.shard_numel, self.epoch = ptrs, shard_numel, epoch
+
+    def run(self, x, w, out, bias):
+        from ..ops import cuda as cu
+
+        d = self.domain
+        cu._C.gemm_wgather(x, w, out, bias, d.bucket_param[self.index], self.ptrs, self.shard_numel, d.rank, d.f1_sync, self.epoch)
+        self.param._vlmt_wgather = None
+        self.RUNS["gemm"] += 1
+
+    def finish(self):
+        from ..ops import cuda as cu
+
+        d = self.domain
+        cu._C.pull_gather_range(self.ptrs, d.bucket_param[self.index], self.shard_numel, self.lo, self.lo + self.param.numel())
+        cu._tick()
+        self.param._vlmt_wgather = None
+        self.RUNS["pull"] += 1
+
+
 class _Domain:
     """Flat buffers + process group for one reduction domain."""
 
@@ -186,6 +216,9 @@ class _Domain:
                 self.resident.append(True)
                 self.grad_live.append(True)
         self._nbytes = [(b.end - b.start) * self.bucket_param[0].element_size() for b in self.buckets]
+        # bucket index -> (weight, offset inside the bucket) of the weights gathered inside their first GEMM (set by the engine)
+        self.f1, self.f1_epoch = {}, 0
+        self.f1_sync = torch.zeros(2 * max(self.size, 1), dtype=torch.int32, device=device) if torch.device(device).type == "cuda" else None
         for b in self.buckets:
             if b.unit >= 0:
                 self.release_params(b)
@@ -196,19 +229,33 @@ class _Domain:
             self._slot_offset = {q: o for q, o, _, _ in self.slots}
         return self._slot_offset[p]
 
-    def materialize_params(self, b: _Bucket):
-        """Make the bucket's parameters usable: give its storage its bytes back and all-gather the shards into it."""
+    def materialize_params(self, b: _Bucket, fuse: bool = False):
+        """Make the bucket's parameters usable: give its storage its bytes back and all-gather the shards into it.
+        ``fuse``: leave the bucket's first-consumed weight to the GEMM that reads it (forward passes only)."""
         i = b.index
         if self.resident[i]:
             return
         full = self.bucket_param[i]
         full.untyped_storage().resize_(self._nbytes[i])
         self.resident[i] = True
-        self.gather_params(b)
+        self.gather_params(b, fuse)
 
-    def gather_params(self, b: _Bucket):
+    def gather_params(self, b: _Bucket, fuse: bool = False):
         i = b.index
         full, shard = self.bucket_param[i], self.param_shard[i]
+        ent = self.f1.get(i) if (fuse and self.symmetric_shards and full.is_cuda) else None
+        if ent is not None:
+            from . import symm
+            from ..ops import cuda as cu
+
+            p, lo = ent
+            ptrs, n = symm.peer_ptrs(shard), shard.numel()
+            cu._C.pull_gather_range(ptrs, full, n, 0, lo)
+            cu._C.pull_gather_range(ptrs, full, n, lo + p.numel(), full.numel())
+            cu._tick(2)
+            self.f1_epoch += 1
+            p._vlmt_wgather = _PendingWeightGather(self, i, p, lo, ptrs, n, self.f1_epoch)
+            return
         if self.symmetric_shards and full.is_cuda:
             from . import symm
             from ..ops import cuda as cu
@@ -316,7 +363,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
     def __init__(self, model, groups: list[GroupSpec], *, dp_group=None, world_group=None, tp_size: int = 1,
                  mode: str = "fsdp", betas=(0.9, 0.999), eps: float = 1e-8, max_grad_norm: float | None = None,
                  bucket_mb: float = 256.0, state_dtype=torch.float32, fused_comm: bool = False, overlap: bool = True,
-                 reshard: bool = False, reshard_after_forward: bool = True):
+                 reshard: bool = False, reshard_after_forward: bool = True, fuse_first_gemm: bool = True):
         pgs = [{"params": list(g.params), "lr": g.lr, "weight_decay": g.weight_decay, "name": g.name} for g in groups]
         super().__init__(pgs, defaults={"lr": groups[0].lr, "weight_decay": 0.0})
         self.model = model
@@ -415,7 +462,10 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         if (self.is_cuda and overlap and dist.is_initialized()) or self.reshard:
             self._install_hooks()
         self._bwd_phase, self._prefetched = False, -1
+        self.fuse_first_gemm = False
         if self.reshard:
+            if fuse_first_gemm and symmetric_shards and tp_size == 1:
+                self._pick_fused_weights()
             self._install_unit_hooks()
         if self.is_cuda:
             self._install_forward_waits()
@@ -525,7 +575,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                     torch.cuda.current_stream().wait_event(b.gather_event)
                     d.bucket_param[b.index].record_stream(torch.cuda.current_stream())
                 b.gather_event = None
-            d.materialize_params(b)
+            d.materialize_params(b, fuse=self.fuse_first_gemm and not self._bwd_phase)
             if backward:
                 d.materialize_grads(b)
         nxt = u - 1 if self._bwd_phase else u + 1
@@ -537,12 +587,49 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                 self.gather_stream.wait_event(ev)
                 for d, b in self._unit_buckets(nxt):
                     if not d.resident[b.index]:
-                        d.materialize_params(b)
+                        d.materialize_params(b, fuse=self.fuse_first_gemm and not self._bwd_phase)
                         b.gather_event = torch.cuda.Event()
                         b.gather_event.record(self.gather_stream)
 
+    # weights gathered by the GEMM that consumes them first (the fused projections at the top of a block)
+    FIRST_GEMM_SUFFIXES = ("qkv.weight", "in_proj.weight")
+
+    def _pick_fused_weights(self):
+        """Per unit, the weight of its first GEMM: its part of the unit's parameter gather moves into that GEMM."""
+        names = {p: n for n, p in self.model.named_parameters()}
+        picked = 0
+        for d in self.domains:
+            if not d.reshard or d.f1_sync is None:
+                continue
+            units_done = set()
+            for b in d.buckets:
+                if b.unit < 0 or b.unit in units_done:
+                    continue
+                for p in b.params:
+                    n = names.get(p, "")
+                    if (n.endswith(self.FIRST_GEMM_SUFFIXES) and p.dim() == 2 and p.dtype == torch.bfloat16 and p.shape[0] > 128
+                            and p.shape[1] % 8 == 0 and p.numel() % 8 == 0):
+                        d.f1[b.index] = (p, d._offset_of(p) - b.start)
+                        units_done.add(b.unit)
+                        picked += 1
+                        break
+        self.fuse_first_gemm = picked > 0
+        if picked:
+            import logging
+
+            logging.getLogger("vlm_training_b200").info(f"{picked} units gather the weight of their first GEMM inside that GEMM")
+
+    def _check_consumed(self, u: int):
+        for d, b in self._unit_buckets(u):
+            ent = d.f1.get(b.index)
+            if ent is not None and getattr(ent[0], "_vlmt_wgather", None) is not None:
+                raise RuntimeError("a weight that was left to its first GEMM to gather was not read by a GEMM in this forward pass; "
+                                   "switch training.reshard_fuse_first_gemm off for this model")
+
     def _install_unit_hooks(self):
         for u, mod in enumerate(self.units):
+            if self.fuse_first_gemm:
+                self._hooks.append(mod.register_forward_hook(lambda m, a, o, u=u: self._check_consumed(u)))
             self._hooks.append(mod.register_forward_pre_hook(lambda m, a, u=u: self._enter_unit(u, False)))
             self._hooks.append(mod.register_full_backward_pre_hook(lambda m, g, u=u: self._enter_unit(u, True)))
 

@@ -10,6 +10,8 @@ GEMM peak and copy bandwidth come from ``MEASURED_PEAKS.json`` (else 1590 TFLOP/
 is the measured peer-copy rate of this machine type, 770 GB/s per direction (900 nominal).
 
 Paths (tensor-parallel group = all ranks):
+  wgather_gemm parameter all-gather -> GEMM in one kernel: the weight's shards are pulled from their owners into the local
+               bucket by two extra warps per CTA while the first tiles run on this rank's own part
   ag_gemm      all-gather -> GEMM in one kernel (column-parallel forward: qkv, gate/up; gather of dY + input
                gradient of the row-parallel linears: o_proj, down_proj)
   gemm_rs      GEMM -> reduce-scatter: tile stores into the owner's memory from the epilogue, then the local sum
@@ -110,6 +112,27 @@ def main(argv=None):
         k = x.shape[1]
         ms = _time(lambda: comm.gemm_reduce_scatter(x, w, b_mn=b_mn), a.iters)
         _report(rank, name, [T, H, k], ms, 2.0 * T * H * k, frac * T * H * 2, hbm_bytes=(world + 1) * R * H * 2)
+
+    # ---- parameter all-gather -> GEMM (the first GEMM of a block whose parameters are sharded over the ranks)
+    for name, n_out in (("wgather_gemm qkv", Q), ("wgather_gemm gate_up", 2 * I)):
+        shard_n = (n_out * H // world + 8 * world) // 8 * 8
+        shard = symm.symmetric_zeros(shard_n, torch.bfloat16, dev, dist.group.WORLD)
+        shard.normal_(0, 0.05)
+        bucket = torch.zeros(shard_n * world, dtype=torch.bfloat16, device=dev)
+        w_view = bucket[:n_out * H].view(n_out, H)
+        x_full = r(T, H)
+        out = torch.empty(T, n_out, dtype=torch.bfloat16, device=dev)
+        sync = torch.zeros(2 * world, dtype=torch.int32, device=dev)
+        ptrs = symm.peer_ptrs(shard)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ep = [0]
+
+        def wg():
+            ep[0] += 1
+            cu._C.gemm_wgather(x_full, w_view, out, None, bucket, ptrs, shard_n, rank, sync, ep[0])
+        ms = _time(wg, a.iters)
+        _report(rank, name, [T, n_out, H], ms, 2.0 * T * n_out * H, frac * n_out * H * 2)
 
     # ---- plain peer collectives
     x = r(R, H)

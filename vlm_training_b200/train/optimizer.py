@@ -48,4 +48,5 @@ def create_optimizer(model, tcfg, mesh, *, fused_comm: bool = False) -> ShardedO
         max_grad_norm=tcfg.max_grad_norm if tcfg.clip_grad else None,
         state_dtype=torch.bfloat16 if tcfg.optimizer_state_dtype == "bf16" else torch.float32,
         fused_comm=fused_comm, reshard=bool(getattr(tcfg, "reshard_params", False)),
-        reshard_after_forward=bool(getattr(tcfg, "reshard_after_forward", True)))
+        reshard_after_forward=bool(getattr(tcfg, "reshard_after_forward", True)),
+        fuse_first_gemm=bool(getattr(tcfg, "reshard_fuse_first_gemm", True)))
