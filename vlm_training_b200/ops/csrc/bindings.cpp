@@ -200,6 +200,12 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& re
   if (res.has_value()) return {y, rstd, r_out};
   return {y, rstd};
 }
+// column sums of the per-block partial rows [blocks, D] (one small kernel; the order of the additions is fixed)
+static Tensor sum_partials(const Tensor& partial) {
+  Tensor out = torch::empty({partial.size(1)}, partial.options());
+  vlmt_sum_rows_f32(partial.data_ptr<float>(), (int)partial.size(0), (int)partial.size(1), out.data_ptr<float>(), cur_stream());
+  return out;
+}
 std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, const c10::optional<Tensor>& dres,
                                 bool offset) {
   check_bf16(dy, "dy"); check_contig(dy, "dy"); check_contig(x, "x");
@@ -212,7 +218,7 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   if (dres.has_value()) check_contig(*dres, "dres");
   vlmt_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), w.scalar_type() == at::kFloat, rstd.data_ptr<float>(), optptr(dres),
                    dx.data_ptr(), partial.data_ptr<float>(), rows, D, offset, cur_stream());
-  return {dx, partial.sum(0)};
+  return {dx, sum_partials(partial)};
 }
 std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b, double eps) {
   check_bf16(x, "x"); check_contig(x, "x"); check_bf16(w, "w");
@@ -236,7 +242,7 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tenso
   Tensor pw = torch::empty({blocks, D}, x.options().dtype(torch::kFloat)), pb = torch::empty_like(pw);
   vlmt_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr(),
                      pw.data_ptr<float>(), pb.data_ptr<float>(), rows, D, cur_stream());
-  return {dx, pw.sum(0), pb.sum(0)};
+  return {dx, sum_partials(pw), sum_partials(pb)};
 }
 std::vector<Tensor> rmsnorm_gated_fwd(const Tensor& x, const Tensor& z, const Tensor& w, double eps) {
   check_bf16(x, "x"); check_contig(x, "x"); check_contig(z, "z"); check_bf16(w, "w");
@@ -258,7 +264,7 @@ std::vector<Tensor> rmsnorm_gated_bwd(const Tensor& dy, const Tensor& x, const T
   Tensor pw = torch::empty({blocks, D}, x.options().dtype(torch::kFloat));
   vlmt_rmsnorm_gated_bwd(dy.data_ptr(), x.data_ptr(), z.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dz.data_ptr(),
                          pw.data_ptr<float>(), rows, D, cur_stream());
-  return {dx, dz, pw.sum(0)};
+  return {dx, dz, sum_partials(pw)};
 }
 
 // ------------------------------------------------------------------ activations
@@ -348,7 +354,7 @@ std::vector<Tensor> qkv_norm_rope_bwd(const Tensor& dq, const Tensor& dk, const 
                                  cosv.data_ptr<float>(), sinv.data_ptr<float>(), rstd.data_ptr<float>(), dqkv.data_ptr(),
                                  partial.data_ptr<float>(), T, n_q, n_kv, D, R, offset, gated, qw.has_value(), cur_stream());
   TORCH_CHECK(r >= 0, "qkv_norm_rope_bwd failed");
-  Tensor dw = partial.sum(0);
+  Tensor dw = sum_partials(partial.view({blocks, 2 * D})).view({2, D});
   return {dqkv, dw[0], dw[1]};
 }
 // generic rotary on a strided [S, H, D] view -> contiguous [S, H, Dout>=D] (zero padded when Dout > D)

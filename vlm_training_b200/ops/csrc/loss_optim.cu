@@ -312,6 +312,11 @@ void vlmt_colsum(const void* x, long ld, int rows, int cols, float* partial, flo
   }
   colsum_finish_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, slabs, cols, out);
 }
+// out[c] = sum over `rows` partial rows (the per-block weight-gradient sums of the norm kernels)
+void vlmt_sum_rows_f32(const float* partial, int rows, int cols, float* out, cudaStream_t st) {
+  if (cols <= 0) return;
+  colsum_finish_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, rows, cols, out);
+}
 void vlmt_sumsq(const void* x, int fp32, long n, float* out, cudaStream_t st) {
   if (n <= 0) return;
   long blocks = (n + 1023) / 1024;

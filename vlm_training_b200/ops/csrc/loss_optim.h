@@ -12,6 +12,7 @@ void vlmt_ce_fwd_bwd(void* logits, long ld, const long* targets, float* loss, fl
 void vlmt_adamw(void* grad, int grad_fp32, float* master, void* m, void* v, int state_bf16, void* param, long n, float lr, float b1,
                 float b2, float eps, float wd, float bc1, float bc2, float grad_scale, int zero_grad, cudaStream_t st);
 // partial[slab, c] = sum of rows of the slab (512 rows each) of column c; cols must be even
+void vlmt_sum_rows_f32(const float* partial, int rows, int cols, float* out, cudaStream_t st);
 int vlmt_colsum_slabs(int rows);
 void vlmt_colsum(const void* x, long ld, int rows, int cols, float* partial, float* out, cudaStream_t st);
 void vlmt_sumsq(const void* x, int fp32, long n, float* out, cudaStream_t st);
