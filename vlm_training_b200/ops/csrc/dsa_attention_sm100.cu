@@ -9,8 +9,8 @@
 //
 // One CTA per (query, kv head), 256 threads.  All warps gather: every selected row is 512 contiguous bytes, copied with
 // 16-byte cp.async into the 128-byte-swizzle layout the MMA descriptors expect (one warp per row and instruction).  The
-// key tile and the value tile have one buffer each and alternate, so a gather is always in flight: K(t+1) streams in
-// while the softmax and the P.V product of tile t run, V(t+1) while S(t+1) is computed.  Warps 0-3 own the TMEM lanes:
+// key tile has two buffers and the value tile one, so a gather is always in flight: K(t+1) streams in from the moment
+// tile t starts, V(t+1) while S(t+1) and its softmax are computed.  Warps 0-3 own the TMEM lanes:
 // they read S^T (lane = key), keep a running maximum per head across the CTA (online softmax; the accumulator O^T has
 // only 16 columns, so rescaling it costs 32 values per thread), write P^T as the next B operand and, at the end, divide
 // O^T (lane = channel) by the row sums.  Rows 8-15 of both B operands are whatever follows in shared memory: they only
@@ -57,7 +57,8 @@ struct Params {
 };
 
 struct Smem {
-  static constexpr int offK = 0, offV = offK + kTile, offQ = offV + kTile;   // q block: 4 channel blocks x [8 rows x 128 B]
+  // two key buffers (the next tile's keys stream in while this tile's scores are computed), one value buffer
+  static constexpr int offK = 0, offV = offK + 2 * kTile, offQ = offV + kTile;   // q block: 4 channel blocks x [8 rows x 128 B]
   static constexpr int offP = offQ + 4 * 1024;                                  // P^T: 2 key blocks x [8 rows x 128 B]
   static constexpr int offF = offP + 2 * 1024 + 1024;                           // floats: wm [4][8], m_run [8], alpha [8], lsum [8]
   static constexpr int offCtl = offF + (32 + 24) * 4;
@@ -124,12 +125,14 @@ __global__ void __launch_bounds__(THREADS, 1) dsa_tc_fwd_kernel(Params p) {
   gather(p.v, smem + Smem::offV, 0);
   bool ok = true;
   for (int t = 0; t < nt && ok; ++t) {
-    cp_async_wait<1>();          // K(t) has landed; V(t) may still be in flight
+    // K(t+1) goes into the other key buffer, last read by the scores of tile t-1 (complete: their barrier was waited for)
+    if (t + 1 < nt) gather(p.k, smem + Smem::offK + ((t + 1) & 1) * kTile, t + 1); else cp_async_commit();
+    cp_async_wait<2>();          // K(t) has landed; V(t) and K(t+1) may still be in flight
     fence_async_proxy();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const SmemDesc a0 = make_desc(smem_u32(smem + Smem::offK), 16, 1024), b0 = make_desc(smem_u32(smem + Smem::offQ), 16, 1024);
+      const SmemDesc a0 = make_desc(smem_u32(smem + Smem::offK + (t & 1) * kTile), 16, 1024), b0 = make_desc(smem_u32(smem + Smem::offQ), 16, 1024);
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const SmemDesc a = desc_off(a0, (kk >> 2) * kRowBlk + (kk & 3) * 32), bb = desc_off(b0, (kk >> 2) * 1024 + (kk & 3) * 32);
@@ -141,7 +144,6 @@ __global__ void __launch_bounds__(THREADS, 1) dsa_tc_fwd_kernel(Params p) {
     ok = __syncthreads_and(ok);
     if (!ok) break;
     tc_fence_after();
-    if (t + 1 < nt) gather(p.k, smem + Smem::offK, t + 1); else cp_async_commit();
     if (warp < 4) {
       // ---- online softmax of this tile: thread <-> key
       const int r = tid;
