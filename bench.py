@@ -297,7 +297,11 @@ def run_ours(args):
         e2e = {"value": global_tokens * args.steps / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                "h2d_bytes_per_step": sum(int(m["perf/h2d_bytes"]) for m in got) // args.steps,
                "d2h_bytes_per_step": sum(int(m["perf/d2h_bytes"]) for m in got) // args.steps,
-               "losses": [round(float(m["train/loss"]), 4) for m in got[-4:]]}
+               "losses": [round(float(m["train/loss"]), 4) for m in got[-4:]],
+               # where the difference to the device-timed loop comes from: the steps' own device time (CUDA events inside
+               # train_step; every step sees a new row with its own image mix) and the share of wall time spent waiting for data
+               "device_ms_per_step_by_events": round(1e3 * sum(float(m["perf/step_time"]) for m in got) / len(got), 2),
+               "data_wait_pct": round(sum(float(m["perf/data_time_pct"]) for m in got) / len(got), 2)}
     tr.end_run()
     flops_tok = tr.flops_per_token * tr.mesh.tp  # whole-model FLOPs per token
     if rank == 0:
