@@ -818,6 +818,8 @@ __device__ __forceinline__ void ldF(const float* p, int j, int limit, bool vec, 
   }
 }
 
+constexpr int kQkvGroup = 12;   // heads of one token handled by one warp (the token's angles are loaded once per group)
+
 template <int E>
 __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
                                          const float* __restrict__ cosv, const float* __restrict__ sinv, bf16* __restrict__ q,
@@ -829,15 +831,24 @@ __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf1
   const int slots = n_q + 2 * n_kv;
   const int qstride = gated ? 2 * D : D;
   const int W = n_q * qstride + 2 * n_kv * D;
-  const long total = (long)T * slots;
+  const int groups = (slots + kQkvGroup - 1) / kQkvGroup;
+  const long total = (long)T * groups;
   const int half = R >> 1;
   const int plane = half / E;  // partner lane distance
   const bool vec_cs = (R % E) == 0 && (R % 4) == 0;  // a lane's E angles are all inside or all outside [0, R), 16-byte aligned rows
-  // Four (token, head) items per warp and iteration, all loads first: a single 256-byte item in flight per warp leaves
+  // A warp takes a group of heads of ONE token, so the token's angles are loaded once and stay in registers (they are four
+  // times the bytes of a head); four heads per iteration, all loads first: a single 256-byte item in flight per warp leaves
   // the kernel latency-bound.
   constexpr int U = 4;
   using Raw = typename VecE<E>::T;
-  for (long base = (blockIdx.x * (long)kWarpsPerBlock + warp) * U; base < total; base += (long)gridDim.x * kWarpsPerBlock * U) {
+  for (long task = blockIdx.x * (long)kWarpsPerBlock + warp; task < total; task += (long)gridDim.x * kWarpsPerBlock) {
+    const int t = (int)(task / groups);
+    const int s_begin = (int)(task - (long)t * groups) * kQkvGroup, s_end = min(slots, s_begin + kQkvGroup);
+    float c[E], sn[E];
+    ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
+    ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
+    const bf16* row = qkv + (size_t)t * W;
+   for (int s0 = s_begin; s0 < s_end; s0 += U) {
     const bf16* src[U];
     bf16* dst[U];
     const bf16* wn[U];
@@ -845,12 +856,9 @@ __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf1
     Raw raw[U], graw[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const long item = base + u;
+      const int s = s0 + u;
       kind[u] = -1;
-      if (item >= total) continue;
-      const int t = (int)(item / slots);
-      const int s = (int)(item - (long)t * slots);
-      const bf16* row = qkv + (size_t)t * W;
+      if (s >= s_end) continue;
       tt[u] = t; sl[u] = s; wn[u] = nullptr;
       if (s < n_q) { src[u] = row + s * qstride; dst[u] = q + ((size_t)t * n_q + s) * D; wn[u] = qw; kind[u] = 0; }
       else if (s < n_q + n_kv) { const int h = s - n_q; src[u] = row + n_q * qstride + h * D; dst[u] = k + ((size_t)t * n_kv + h) * D; wn[u] = kw; kind[u] = 1; }
@@ -888,9 +896,7 @@ __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf1
         }
       }
       // rotary on channels [0, R)
-      float c[E], sn[E], o[E];
-      ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
-      ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
+      float o[E];
 #pragma unroll
       for (int i = 0; i < E; ++i) {
         const int j = lane * E + i;
@@ -899,6 +905,7 @@ __global__ void qkv_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf1
       }
       stE<E>(dst[u] + lane * E, o);
     }
+   }
   }
 }
 
@@ -914,18 +921,24 @@ __global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16
   const int slots = n_q + 2 * n_kv;
   const int qstride = gated ? 2 * D : D;
   const int W = n_q * qstride + 2 * n_kv * D;
-  const long total = (long)T * slots;
+  const int groups = (slots + kQkvGroup - 1) / kQkvGroup;
+  const long total = (long)T * groups;
   const int half = R >> 1;
   const int plane = half / E;
   const bool vec_cs = (R % E) == 0 && (R % 4) == 0;
   float acc_q[E], acc_k[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) acc_q[i] = acc_k[i] = 0.f;
-  for (long item = blockIdx.x * (long)kWarpsPerBlock + warp; item < total; item += (long)gridDim.x * kWarpsPerBlock) {
-    const int t = (int)(item / slots);
-    const int s = (int)(item - (long)t * slots);
+  for (long task = blockIdx.x * (long)kWarpsPerBlock + warp; task < total; task += (long)gridDim.x * kWarpsPerBlock) {
+    const int t = (int)(task / groups);
+    const int s_begin = (int)(task - (long)t * groups) * kQkvGroup, s_end = min(slots, s_begin + kQkvGroup);
+    float c[E], sn[E];   // the token's angles: once per group of heads
+    ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
+    ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
     const bf16* row = qkv + (size_t)t * W;
     bf16* drow = dqkv + (size_t)t * W;
+#pragma unroll 4
+   for (int s = s_begin; s < s_end; ++s) {
     int kind, off;
     const bf16* g;
     const bf16* wn = nullptr;
@@ -938,10 +951,8 @@ __global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16
     }
     if (kind == 0 && gated) cpE<E>(drow + off + D + lane * E, dgate + ((size_t)t * n_q + s) * D + lane * E);
     // rotary transpose: dn[j] = do[j] c[j] + (j < half ? do[j+half] s[j+half] : -do[j-half] s[j-half])
-    float d[E], c[E], sn[E], dn[E];
+    float d[E], dn[E];
     ldE<E>(g + lane * E, d);
-    ldF<E>(cosv + (size_t)t * R, lane * E, R, vec_cs, c);
-    ldF<E>(sinv + (size_t)t * R, lane * E, R, vec_cs, sn);
 #pragma unroll
     for (int i = 0; i < E; ++i) {
       const int j = lane * E + i;
@@ -969,6 +980,7 @@ __global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16
 #pragma unroll
     for (int i = 0; i < E; ++i) out[i] = rs * (dn[i] * wv[i] - xh[i] * dot);
     stE<E>(drow + off + lane * E, out);
+   }
   }
 #pragma unroll
   for (int i = 0; i < E; ++i) { sm_dw[warp][0][lane * E + i] = acc_q[i]; sm_dw[warp][1][lane * E + i] = acc_k[i]; }
@@ -1412,7 +1424,7 @@ int vlmt_qkv_norm_rope_fwd(const void* qkv, const void* qw, const void* kw, cons
                            int has_norm, cudaStream_t st) {
   const int E = D / 32;
   if (D % 32 || R > D || (R / 2) % E || (((R / 2) / E) & ((R / 2) / E - 1)) || (R / 2) / E >= 32) return -1;
-  const int grid = vlmt_qkv_blocks(((long)T * (n_q + 2 * n_kv) + 3) / 4);  // four items per warp and iteration
+  const int grid = vlmt_qkv_blocks((long)T * ((n_q + 2 * n_kv + kQkvGroup - 1) / kQkvGroup));  // one warp per token and group of heads
 #define LAUNCH(E_)                                                                                                              \
   qkv_norm_rope_fwd_kernel<E_><<<grid, kThreads, 0, st>>>(BF(qkv), BF(qw), BF(kw), cosv, sinv, BFM(q), BFM(k), BFM(v), BFM(gate), \
                                                           rstd, T, n_q, n_kv, R, eps, offset, gated, has_norm)
