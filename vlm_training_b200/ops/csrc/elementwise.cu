@@ -266,7 +266,7 @@ __device__ __forceinline__ void block_sum(float (&v)[K], float* sm, int& parity)
   for (int k = 0; k < K; ++k) {
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < kRT / 32; ++w) t += buf[k * 8 + w];
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += buf[k * 8 + w];   // blocks may be narrower than kRT
     v[k] = t;
   }
   parity ^= 1;
@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(kRT) rmsnorm_fwd_tile_kernel(const bf16* __res
   float wv[VPT][8];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int v = threadIdx.x + k * kRT;
+    const int v = threadIdx.x + k * (int)blockDim.x;
     if (v < nvec) {
       ld_w8(w, v, wv[k]);
       if (offset) {
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(kRT) rmsnorm_fwd_tile_kernel(const bf16* __res
       const int row = g * kRR + r;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (row < rows && v < nvec) {
           const size_t o = (size_t)row * nvec + v;
           uint4 u = reinterpret_cast<const uint4*>(x)[o];
@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(kRT) rmsnorm_fwd_tile_kernel(const bf16* __res
       if (threadIdx.x == 0 && rstd) rstd[row] = rs;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (v < nvec) {
           float f[8];
           unpack8(xv[r][k], f);
@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __res
   float wv[VPT][8], dw[VPT][8];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int v = threadIdx.x + k * kRT;
+    const int v = threadIdx.x + k * (int)blockDim.x;
 #pragma unroll
     for (int i = 0; i < 8; ++i) dw[k][i] = 0.f;
     if (v < nvec) {
@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __res
       rs[r] = row < rows ? rstd[row] : 0.f;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (row < rows && v < nvec) {
           const size_t o = (size_t)row * nvec + v;
           xv[r][k] = reinterpret_cast<const uint4*>(x)[o];
@@ -407,7 +407,7 @@ __global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __res
       const float dt = dot[r] / (float)D;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (v < nvec) {
           const size_t o = (size_t)row * nvec + v;
           float xf[8], gf[8], out[8];
@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __res
   }
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int v = threadIdx.x + k * kRT;
+    const int v = threadIdx.x + k * (int)blockDim.x;
     if (v < nvec) {
       float4* dst = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * D + (size_t)v * 8);
       dst[0] = make_float4(dw[k][0], dw[k][1], dw[k][2], dw[k][3]);
@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
   float wv[VPT][8], bv[VPT][8];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int v = threadIdx.x + k * kRT;
+    const int v = threadIdx.x + k * (int)blockDim.x;
 #pragma unroll
     for (int i = 0; i < 8; ++i) bv[k][i] = 0.f;
     if (v < nvec) {
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
       const int row = g * kRR + r;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (row < rows && v < nvec) {
           xv[r][k] = reinterpret_cast<const uint4*>(x)[(size_t)row * nvec + v];
           float f[8];
@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
       const int row = g * kRR + r;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (row < rows && v < nvec) {
           float f[8];
           unpack8(xv[r][k], f);
@@ -503,7 +503,7 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
       if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (v < nvec) {
           float f[8];
           unpack8(xv[r][k], f);
@@ -527,7 +527,7 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
   float wv[VPT][8], dw[VPT][8], db[VPT][8];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int v = threadIdx.x + k * kRT;
+    const int v = threadIdx.x + k * (int)blockDim.x;
 #pragma unroll
     for (int i = 0; i < 8; ++i) { dw[k][i] = 0.f; db[k][i] = 0.f; }
     if (v < nvec) ld_w8(w, v, wv[k]);
@@ -545,7 +545,7 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
       rs[r] = row < rows ? rstd[row] : 0.f;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (row < rows && v < nvec) {
           const size_t o = (size_t)row * nvec + v;
           xv[r][k] = reinterpret_cast<const uint4*>(x)[o];
@@ -573,7 +573,7 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
       const float s1 = s12[2 * r] / (float)D, s2 = s12[2 * r + 1] / (float)D;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * kRT;
+        const int v = threadIdx.x + k * (int)blockDim.x;
         if (v < nvec) {
           float xf[8], gf[8], out[8];
           unpack8(xv[r][k], xf);
@@ -590,7 +590,7 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
   }
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int v = threadIdx.x + k * kRT;
+    const int v = threadIdx.x + k * (int)blockDim.x;
     if (v < nvec) {
       float4* d1 = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * D + (size_t)v * 8);
       float4* d2 = reinterpret_cast<float4*>(db_partial + (size_t)blockIdx.x * D + (size_t)v * 8);
@@ -1285,9 +1285,9 @@ inline int grid_for(long work_items, int per_block, int cap) {
 
 // grid of a forward row-tile kernel: one wave of resident blocks (a second, partly filled wave costs a whole pass)
 template <typename K>
-static int tile_grid(K kernel, int rows) {
+static int tile_grid(K kernel, int rows, int threads = kRT) {
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRT, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   return grid_for(rows, kRR, sms * per_sm);
@@ -1309,6 +1309,13 @@ static int tile_vpt(int D) {
   if ((D & 7) || nvec > 4 * kRT) return 0;
   return nvec <= kRT ? 1 : (nvec <= 2 * kRT ? 2 : 4);
 }
+// threads per block of a row-tile launch: with one column group per thread a narrow row (1152 channels = 144 groups) gets a
+// block of just enough warps instead of 256 threads of which 112 idle
+static int tile_threads(int D, int vpt) {
+  if (vpt != 1) return kRT;
+  const int t = (((D >> 3) + 31) / 32) * 32;
+  return t < 64 ? 64 : (t > kRT ? kRT : t);
+}
 #define TILE_DISPATCH(VPT, CALL1, CALL2, CALL4) do { if ((VPT) == 1) { CALL1; } else if ((VPT) == 2) { CALL2; } else { CALL4; } } while (0)
 
 void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32, void* y, void* r_out, float* rstd, int rows, int D,
@@ -1316,7 +1323,7 @@ void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32,
   if (rows <= 0) return;
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define RF(WT, V) rmsnorm_fwd_tile_kernel<WT, V><<<tile_grid(rmsnorm_fwd_tile_kernel<WT, V>, rows), kRT, 0, st>>>(BF(x), BF(res), (const WT*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset)
+#define RF(WT, V) rmsnorm_fwd_tile_kernel<WT, V><<<tile_grid(rmsnorm_fwd_tile_kernel<WT, V>, rows, tile_threads(D, vpt)), tile_threads(D, vpt), 0, st>>>(BF(x), BF(res), (const WT*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset)
     if (w_fp32) TILE_DISPATCH(vpt, RF(float, 1), RF(float, 2), RF(float, 4));
     else TILE_DISPATCH(vpt, RF(bf16, 1), RF(bf16, 2), RF(bf16, 4));
 #undef RF
@@ -1335,7 +1342,7 @@ int vlmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, int w_fp32, c
   const int grid = vlmt_norm_blocks(rows);
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define RB(WT, V) rmsnorm_bwd_tile_kernel<WT, V><<<grid, kRT, 0, st>>>(BF(dy), BF(x), (const WT*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset)
+#define RB(WT, V) rmsnorm_bwd_tile_kernel<WT, V><<<grid, tile_threads(D, vpt), 0, st>>>(BF(dy), BF(x), (const WT*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset)
     if (w_fp32) TILE_DISPATCH(vpt, RB(float, 1), RB(float, 2), RB(float, 4));
     else TILE_DISPATCH(vpt, RB(bf16, 1), RB(bf16, 2), RB(bf16, 4));
 #undef RB
@@ -1362,7 +1369,7 @@ void vlmt_layernorm_fwd(const void* x, const void* w, const void* b, void* y, fl
   if (rows <= 0) return;
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define LF(V) layernorm_fwd_tile_kernel<V><<<tile_grid(layernorm_fwd_tile_kernel<V>, rows), kRT, 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps)
+#define LF(V) layernorm_fwd_tile_kernel<V><<<tile_grid(layernorm_fwd_tile_kernel<V>, rows, tile_threads(D, vpt)), tile_threads(D, vpt), 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps)
     TILE_DISPATCH(vpt, LF(1), LF(2), LF(4));
 #undef LF
     return;
@@ -1374,7 +1381,7 @@ int vlmt_layernorm_bwd(const void* dy, const void* x, const void* w, const float
   const int grid = vlmt_norm_blocks(rows);
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define LB(V) layernorm_bwd_tile_kernel<V><<<grid, kRT, 0, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D)
+#define LB(V) layernorm_bwd_tile_kernel<V><<<grid, tile_threads(D, vpt), 0, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D)
     TILE_DISPATCH(vpt, LB(1), LB(2), LB(4));
 #undef LB
     return grid;
