@@ -100,3 +100,70 @@ def test_device_status_word_raises_on_host():
     with pytest.raises(RuntimeError, match="test kernel.*TMEM"):
         status.raise_if_set(word, "test kernel")
     assert int(word[0]) == 0
+
+
+# ----------------------------------------------------------------------------- data worker processes
+def _pool_args(tmp_path, synthetic="text-uniform", data_path=""):
+    from vlm_training_b200.config import Config
+    from vlm_training_b200.models.config import ModelConfig
+
+    cfg = Config()
+    cfg.data.synthetic = synthetic
+    cfg.data.seq_len = 256
+    cfg.data.doc_len_min, cfg.data.doc_len_max = 16, 64
+    cfg.data.data_path = data_path
+    cfg.training.seed = 3
+    return (cfg.data, cfg.training, ModelConfig.preset("tiny-qwen3"), 0, 1)
+
+
+def test_worker_processes_deliver_rows_in_a_fixed_order(tmp_path):
+    """Two worker processes, rows taken in round-robin order: two pools give the same sequence, and it interleaves the two
+    workers' own streams."""
+    from vlm_training_b200.data.loader import WorkerPool, make_dataset
+
+    args = _pool_args(tmp_path)
+    seqs = []
+    for _ in range(2):
+        pool = WorkerPool(args, 2, depth=2)
+        try:
+            seqs.append([next(pool)["input_ids"].clone() for _ in range(6)])
+        finally:
+            pool.close()
+    for a, b in zip(*seqs):
+        assert torch.equal(a, b)
+    w0 = iter(make_dataset(*args, worker=(0, 2)))
+    w1 = iter(make_dataset(*args, worker=(1, 2)))
+    want = [next(w0 if i % 2 == 0 else w1)["input_ids"] for i in range(6)]
+    for a, b in zip(seqs[0], want):
+        assert torch.equal(a, b)
+    assert not torch.equal(seqs[0][0], seqs[0][1])
+
+
+def test_a_failing_data_worker_process_is_reported_in_the_training_process(tmp_path):
+    """A worker that cannot build its dataset (a data path that does not exist) raises here, with the worker's traceback."""
+    from vlm_training_b200.data.loader import WorkerPool
+
+    args = _pool_args(tmp_path, synthetic="no-such-kind")
+    pool = WorkerPool(args, 2, depth=2)
+    try:
+        with pytest.raises(RuntimeError, match="data worker [01] failed: ValueError"):
+            next(pool)
+    finally:
+        pool.close()
+
+
+def test_a_data_worker_process_that_dies_silently_is_noticed(tmp_path):
+    """The worker is killed by the test between two rows (a host-side failure: nothing runs on a GPU); the next read
+    that finds its queue empty reports the exit code instead of waiting for ever."""
+    from vlm_training_b200.data.loader import WorkerPool
+
+    pool = WorkerPool(_pool_args(tmp_path), 2, depth=1)
+    try:
+        next(pool)
+        pool.procs[1].kill()
+        pool.procs[1].join(timeout=10)
+        with pytest.raises(RuntimeError, match="data worker 1 exited with code"):
+            for _ in range(8):       # rows already queued by the dead worker may still arrive first
+                next(pool)
+    finally:
+        pool.close()

@@ -65,6 +65,22 @@ def test_single_process_loss_decreases(tmp_path, monkeypatch):
     assert losses[-1] < losses[0]
 
 
+def test_trainer_reads_rows_from_worker_processes(tmp_path):
+    """``data.worker_processes = 2``: the rows come from two spawned processes in a fixed order, so two runs give the same
+    loss curve; the workers are gone after ``end_run``."""
+    from vlm_training_b200.train.trainer import Trainer
+
+    curves = []
+    for run in range(2):
+        tr = Trainer(_cfg(tmp_path / f"w{run}", training__total_steps=3, data__worker_processes=2))
+        pool = tr.loader.source
+        hist = tr.train()
+        tr.end_run()
+        curves.append([m["train/loss"] for m in hist])
+        assert len(hist) == 3 and all(not p.is_alive() for p in pool.procs)
+    assert curves[0] == curves[1]
+
+
 def test_checkpoint_resume_reproduces_curve(tmp_path, monkeypatch):
     _shrink_vocab(monkeypatch)
     from vlm_training_b200.train.trainer import Trainer

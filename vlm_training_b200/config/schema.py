@@ -142,6 +142,9 @@ class DataSection:
     doc_len_min: int = 128
     doc_len_max: int = 8192
     num_workers: int = 2
+    # rows are produced by this many worker processes per rank (0: by one thread of the training process); a worker reads its
+    # own 1/n of the rank's samples, the training process takes the workers' rows in round-robin order
+    worker_processes: int = 0
     # cooker for crude webdataset samples: "auto" (from the sample's fields) or a name of data.cookers.COOKERS
     cooker: str = "auto"
 

@@ -21,12 +21,111 @@ from ..models.vision import VisionPlan
 _TENSOR_KEYS = ("input_ids", "labels", "cu_seqlens", "pixel_values", "image_grid_thw", "attention_mask", "mm_token_type_ids")
 
 
+def make_dataset(data_cfg, training_cfg, model_cfg, dp_rank: int, dp_size: int, worker=(0, 1)):
+    """The packed-row iterator of one data-parallel rank (module-level, so worker processes can build their own).
+    ``worker = (w, n)``: this is worker ``w`` of ``n`` of that rank and reads / draws its own 1/n of the rank's rows."""
+    w, n = worker
+    if data_cfg.synthetic:
+        from .synthetic import SyntheticDataset, spec_from_config
+
+        spec = spec_from_config(data_cfg, model_cfg, seed=training_cfg.seed)
+        return SyntheticDataset(spec, model_cfg, dp_rank=dp_rank, dp_size=dp_size, worker=worker)
+    from .task_encoders import build_dataset
+
+    return build_dataset(data_cfg, training_cfg, model_cfg, dp_rank=dp_rank * n + w, dp_size=dp_size * n)
+
+
+def _worker_main(args, wid: int, n: int, out_q, stop):
+    """Body of one data worker process: builds its dataset and feeds rows until told to stop.  Failures travel through
+    the queue as exceptions; the end of the data as ``None``."""
+    import traceback
+
+    try:
+        torch.set_num_threads(1)
+        it = iter(make_dataset(*args, worker=(wid, n)))
+        while not stop.is_set():
+            item = next(it)
+            while not stop.is_set():
+                try:
+                    out_q.put(item, timeout=0.2)
+                    break
+                except queue.Full:
+                    continue
+    except StopIteration:
+        out_q.put(None)
+    except BaseException as exc:  # noqa: BLE001 - everything is reported to the training process
+        out_q.put(RuntimeError(f"data worker {wid} failed: {type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+
+
+class WorkerPool:
+    """Rows from ``n`` worker processes, taken in round-robin order (worker 0, 1, ..., n-1, 0, ...), so the sequence of
+    rows is the same from run to run.  The reference reads through an energon loader with worker processes (reference:
+    train/train_qwen.py:227-250); here a worker owns 1/n of the rank's samples (real data) or its own random stream
+    (synthetic data).  A worker that raises is re-raised here; a worker that dies without a word is noticed by its exit
+    code while its queue stays empty."""
+
+    def __init__(self, args, n: int, depth: int = 2, start_method: str = "spawn"):
+        import torch.multiprocessing as mp
+
+        ctx = mp.get_context(start_method)
+        self.n = int(n)
+        self.stop = ctx.Event()
+        self.queues = [ctx.Queue(maxsize=max(1, depth)) for _ in range(self.n)]
+        self.procs = [ctx.Process(target=_worker_main, args=(args, w, self.n, self.queues[w], self.stop), daemon=True)
+                      for w in range(self.n)]
+        for p in self.procs:
+            p.start()
+        self.done = [False] * self.n
+        self.turn = 0
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        while not all(self.done):
+            w = self.turn
+            if self.done[w]:
+                self.turn = (w + 1) % self.n
+                continue
+            try:
+                item = self.queues[w].get(timeout=0.5)
+            except queue.Empty:
+                if not self.procs[w].is_alive() and self.queues[w].empty():
+                    self.close()
+                    raise RuntimeError(f"data worker {w} exited with code {self.procs[w].exitcode} without reporting")
+                continue
+            self.turn = (w + 1) % self.n
+            if item is None:
+                self.done[w] = True
+                continue
+            if isinstance(item, Exception):
+                self.close()
+                raise item
+            return item
+        raise StopIteration
+
+    def close(self):
+        self.stop.set()
+        for q_ in self.queues:
+            try:
+                while True:
+                    q_.get_nowait()
+            except (queue.Empty, OSError, ValueError):
+                pass
+        for p in self.procs:
+            p.join(timeout=5)
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=5)
+
+
 class PrefetchLoader:
     """``transfer``: optional ``batch -> kwargs`` callable (see :func:`to_device`) run by the worker thread on its own
     CUDA stream, so the host→device copies and the plan construction of step n+1 overlap step n; ``__next__`` then
     returns the device-side kwargs and makes the consumer's stream wait for the copies."""
 
     def __init__(self, dataset, depth: int = 2, pin: bool = True, transfer=None, device=None):
+        self.source = dataset
         self.dataset = iter(dataset)
         self.pin = pin and torch.cuda.is_available()
         self.transfer = transfer
@@ -92,6 +191,8 @@ class PrefetchLoader:
     def close(self):
         """Stop the worker and wait for it, so no thread touches CUDA (pinned allocations) during interpreter exit."""
         self._stop = True
+        if hasattr(self.source, "close"):
+            self.source.close()
         try:
             while True:
                 self.q.get_nowait()

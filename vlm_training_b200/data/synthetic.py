@@ -175,9 +175,12 @@ class SyntheticDataset:
     (tensor-parallel peers pass the same ``dp_rank`` and so see identical data, as with the
     reference's energon ``WorkerConfig``, reference: train/train_qwen.py:227-232)."""
 
-    def __init__(self, spec: SyntheticSpec, cfg: ModelConfig, dp_rank: int = 0, dp_size: int = 1, pad_token_id: int = 151643):
+    def __init__(self, spec: SyntheticSpec, cfg: ModelConfig, dp_rank: int = 0, dp_size: int = 1, pad_token_id: int = 151643,
+                 worker=(0, 1)):
         self.spec, self.cfg = spec, cfg
-        self.rng = np.random.default_rng([spec.seed, dp_rank, dp_size])
+        # one random stream per (rank, worker); a single worker keeps the stream of the in-thread loader
+        key = [spec.seed, dp_rank, dp_size] + ([int(worker[0]), int(worker[1])] if worker[1] > 1 else [])
+        self.rng = np.random.default_rng(key)
         self.pad_token_id = pad_token_id
 
     def __iter__(self):

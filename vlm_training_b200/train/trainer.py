@@ -155,16 +155,14 @@ class Trainer:
         return create_optimizer(self.model, t, self.mesh, fused_comm=fused)
 
     def _build_loader(self):
+        from ..data.loader import WorkerPool, make_dataset
+
         d = self.cfg.data
-        if d.synthetic:
-            from ..data.synthetic import SyntheticDataset, spec_from_config
-
-            spec = spec_from_config(d, self.model_config, seed=self.cfg.training.seed)
-            ds = SyntheticDataset(spec, self.model_config, dp_rank=self.mesh.dp_rank, dp_size=self.mesh.dp)
+        args = (d, self.cfg.training, self.model_config, self.mesh.dp_rank, self.mesh.dp)
+        if int(getattr(d, "worker_processes", 0)) > 0:
+            ds = WorkerPool(args, int(d.worker_processes), depth=max(2, d.num_workers))
         else:
-            from ..data.task_encoders import build_dataset
-
-            ds = build_dataset(d, self.cfg.training, self.model_config, dp_rank=self.mesh.dp_rank, dp_size=self.mesh.dp)
+            ds = make_dataset(*args)
         pixel_dtype = next(self.model.parameters()).dtype
         transfer = lambda b: to_device(b, self.model_config, self.device, pixel_dtype=pixel_dtype)
         return PrefetchLoader(ds, depth=max(2, d.num_workers), transfer=transfer, device=self.device)
