@@ -26,7 +26,10 @@ class _GroupedLinear(torch.autograd.Function):
     def forward(ctx, x, w, prefix):
         E, N, K = w.shape
         x = x.contiguous()
-        y = torch.zeros(x.shape[0], N, dtype=x.dtype, device=x.device)  # rows beyond the last used tile stay zero
+        # every row of a used tile is written by the kernel (padding rows of a tile are zero in x, so zero in y); the rows
+        # beyond the last used tile are written by nobody and read by nobody: the combine walks the slot -> row map, the
+        # grouped weight gradient contracts over the groups' own rows only.  No fill of the whole capacity.
+        y = torch.empty(x.shape[0], N, dtype=x.dtype, device=x.device)
         cu._C.gemm_grouped(x, w.reshape(E * N, K), y, prefix, 1, False)
         cu._tick()
         ctx.save_for_backward(x, w, prefix)
@@ -39,7 +42,7 @@ class _GroupedLinear(torch.autograd.Function):
         dy = dy.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = torch.zeros_like(x)
+            dx = torch.empty_like(x)   # as above: rows of unused tiles are never read
             cu._C.gemm_grouped(dy, w.reshape(E * N, K), dx, prefix, 1, True)     # dX = dY . W_e  (W_e read MN-major)
             cu._tick()
         if ctx.needs_input_grad[1]:
