@@ -55,7 +55,9 @@ static Tensor moe_rows_from_tokens(const Tensor& src, const Tensor& slot_of_row,
   c10::cuda::CUDAGuard guard(src.device());
   const long cap = slot_of_row.numel();
   const int H = src.size(1);
-  Tensor rows = torch::zeros({cap, H}, src.options());   // rows of tiles that are not in use stay zero
+  // the kernel writes every row of the tiles in use (padding rows as zeros); the rows of unused tiles are read by nobody
+  // (the grouped GEMMs stop at the last used tile), so the capacity is not filled
+  Tensor rows = torch::empty({cap, H}, src.options());
   int r = vlmt_moe_rows_from_tokens(src.data_ptr(), slot_of_row.data_ptr<int>(), prefix.data_ptr<int>(), (int)prefix.numel() - 1, (int)k, H,
                                     scale.has_value() ? scale->data_ptr<float>() : nullptr, rows.data_ptr(), cap, cur());
   TORCH_CHECK(r == 0, "vlmt_moe_rows_from_tokens failed with code ", r);
