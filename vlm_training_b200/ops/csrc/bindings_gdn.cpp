@@ -50,13 +50,15 @@ static std::vector<Tensor> gdn_prepare_fwd(const Tensor& q, const Tensor& k, con
 }
 
 // o [T, H, 128]: rows of tokens that belong to no chunk are zero
-static Tensor gdn_output_fwd(const Tensor& qg, const Tensor& P, const Tensor& states, const Tensor& vnew, const Tensor& chunks, int64_t T) {
+// `covered`: the chunks cover all T tokens (no trailing tokens outside every document), so nothing needs a zero fill
+static Tensor gdn_output_fwd(const Tensor& qg, const Tensor& P, const Tensor& states, const Tensor& vnew, const Tensor& chunks, int64_t T,
+                             bool covered) {
   check_chunks(chunks);
   const int64_t H = qg.size(0), N = chunks.size(0);
   check_stack(qg, H, N, 64, 128, "qg"); check_stack(P, H, N, 64, 64, "P"); check_stack(states, H, N, 128, 128, "states");
   check_stack(vnew, H, N, 64, 128, "vnew");
   c10::cuda::CUDAGuard guard(qg.device());
-  Tensor o = torch::zeros({T, H, 128}, qg.options());
+  Tensor o = covered ? torch::empty({T, H, 128}, qg.options()) : torch::zeros({T, H, 128}, qg.options());
   Tensor st = vlmt_status_tensor();
   int r = vlmt_gdn_output_fwd(qg.data_ptr(), P.data_ptr(), states.data_ptr(), vnew.data_ptr(), chunks.data_ptr<int>(), (int)H, (int)N,
                               o.data_ptr(), st.data_ptr<int>(), cur());
@@ -88,7 +90,7 @@ static std::vector<Tensor> gdn_output_bwd(const Tensor& dout, const Tensor& qg, 
 static std::vector<Tensor> gdn_prepare_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& beta, const Tensor& gc,
                                            const Tensor& chunks, double scale, double eps, const Tensor& states, const Tensor& adj,
                                            const Tensor& vnew, const Tensor& du, const Tensor& dqg, const Tensor& dP, const Tensor& P,
-                                           const Tensor& Tm) {
+                                           const Tensor& Tm, bool covered) {
   check_tokens(q, "q"); check_tokens(k, "k"); check_tokens(v, "v"); check_chunks(chunks);
   const int64_t T = q.size(0), H = q.size(1), N = chunks.size(0);
   check_stack(states, H, N, 128, 128, "states"); check_stack(adj, H, N, 128, 128, "adj"); check_stack(vnew, H, N, 64, 128, "vnew");
@@ -99,8 +101,9 @@ static std::vector<Tensor> gdn_prepare_bwd(const Tensor& q, const Tensor& k, con
   c10::cuda::CUDAGuard guard(q.device());
   auto bo = q.options();
   auto fo = q.options().dtype(torch::kFloat);
-  Tensor dq = torch::zeros({T, H, 128}, bo), dk = torch::zeros({T, H, 128}, bo), dv = torch::zeros({T, H, 128}, bo);
-  Tensor dg = torch::zeros({T, H}, fo), dbeta = torch::zeros({T, H}, fo);
+  auto alloc = [&](std::vector<int64_t> shape, const torch::TensorOptions& o) { return covered ? torch::empty(shape, o) : torch::zeros(shape, o); };
+  Tensor dq = alloc({T, H, 128}, bo), dk = alloc({T, H, 128}, bo), dv = alloc({T, H, 128}, bo);
+  Tensor dg = alloc({T, H}, fo), dbeta = alloc({T, H}, fo);
   Tensor st = vlmt_status_tensor();
   int r = vlmt_gdn_prepare_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0), beta.data_ptr<float>(),
                                gc.data_ptr<float>(), chunks.data_ptr<int>(), (int)T, (int)H, (int)N, (float)scale, (float)eps,

@@ -158,17 +158,17 @@ class _ChunkedNative(torch.autograd.Function):
     operands and results, ``P``, the triangular inverse and the cumulative decays (all bf16 tile stacks)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, chunks, ranges, scale):
+    def forward(ctx, q, k, v, g, beta, chunks, ranges, scale, covered):
         from . import cuda as cu
 
         NATIVE_CALLS["forward"] += 1
         gf, bf = g.float().contiguous(), beta.float().contiguous()
         w, u, kdec, qg, P, Tm, gc, decay = cu._C.gdn_prepare_fwd(q, k, v, gf, bf, chunks, scale, 1e-6)
         vnew, states = cu.gdn_scan(w, kdec, u, decay, None, ranges, False, head_major=True)
-        o = cu._C.gdn_output_fwd(qg, P, states, vnew, chunks, q.shape[0])
+        o = cu._C.gdn_output_fwd(qg, P, states, vnew, chunks, q.shape[0], covered)
         cu._tick(2)
         ctx.save_for_backward(q, k, v, bf, gc, decay, w, kdec, qg, P, Tm, vnew, states, chunks)
-        ctx.ranges, ctx.scale = ranges, scale
+        ctx.ranges, ctx.scale, ctx.covered = ranges, scale, covered
         ctx.dtypes = (g.dtype, beta.dtype)
         return o
 
@@ -180,9 +180,10 @@ class _ChunkedNative(torch.autograd.Function):
         q, k, v, bf, gc, decay, w, kdec, qg, P, Tm, vnew, states, chunks = ctx.saved_tensors
         dqg, dP, dvn, dS = cu._C.gdn_output_bwd(do.contiguous(), qg, P, states, vnew, chunks)
         du, adj = cu.gdn_scan(kdec, w, dvn, decay, dS, ctx.ranges, True, head_major=True)
-        dq, dk, dv, dg, dbeta = cu._C.gdn_prepare_bwd(q, k, v, bf, gc, chunks, ctx.scale, 1e-6, states, adj, vnew, du, dqg, dP, P, Tm)
+        dq, dk, dv, dg, dbeta = cu._C.gdn_prepare_bwd(q, k, v, bf, gc, chunks, ctx.scale, 1e-6, states, adj, vnew, du, dqg, dP, P, Tm,
+                                                      ctx.covered)
         cu._tick(2)
-        return dq, dk, dv, dg.to(ctx.dtypes[0]), dbeta.to(ctx.dtypes[1]), None, None, None
+        return dq, dk, dv, dg.to(ctx.dtypes[0]), dbeta.to(ctx.dtypes[1]), None, None, None, None
 
 
 def native_usable(q, k, v, chunk) -> bool:
@@ -207,7 +208,8 @@ def gated_delta_rule_scan(q, k, v, g, beta, cu_host, scale=None, chunk: int = CH
     scale = scale if scale is not None else Dk ** -0.5
     if work_dtype is torch.bfloat16 and native_usable(q, k, v, chunk):
         chunks, ranges, _n = _device_tables(cu_host, dev)
-        return _ChunkedNative.apply(q, k, v, g, beta, chunks, ranges, float(scale))
+        covered = int(np.asarray(cu_host)[-1]) == T and int(np.asarray(cu_host)[0]) == 0   # every token belongs to a chunk
+        return _ChunkedNative.apply(q, k, v, g, beta, chunks, ranges, float(scale), covered)
     dst_np, n_slots, first, count = doc_chunk_ranges(cu_host, chunk)
     Tc = int(np.asarray(cu_host)[-1])
     dst = torch.from_numpy(dst_np).to(dev, non_blocking=True)
