@@ -1,12 +1,17 @@
 """DSA sparse attention on CUDA.
 
-Indexer scores → per-query top-k key selection → attention restricted to the selected keys.  This build
-computes the selection with batched library kernels per document (scores by one GEMM per indexer head
-block, ``topk``) in query blocks so the ``[L, L]`` score matrix is never larger than ``block x L``, and
-runs the attention over the selected keys in the same blocks: with the CUDA kernels of ``csrc/dsa_attention.cu``
-(one CTA per query and kv head reads each selected key / value row once for the query heads that share it) for the
-supported head shapes, else as a gathered dense softmax of tensor operations.  Documents no longer than ``topk``
-take the dense tcgen05 attention kernel directly (the selection keeps every causal key).
+Indexer scores -> per-query top-k key selection -> attention restricted to the selected keys, per document and in query
+blocks of 1024 so the score matrix is never larger than ``block x L``.  The documents and blocks are walked from the host
+copy of the boundaries (no device read).  Per block:
+
+* selection: ``csrc/dsa_indexer_sm100.cu`` (indexer heads' products on the tensor cores folded into fp32 scores, then a
+  radix-select top-k; -1 in unused slots) for 4 indexer heads of 64 channels in bf16, else ``einsum`` / ``topk`` under
+  ``no_grad`` — the selection is an index set, nothing of it is kept for backward;
+* attention over the selected keys: the tcgen05 kernels of ``csrc/dsa_attention_sm100.cu`` (head size 256, 8 query heads
+  per kv head), else the CUDA-core kernels of ``csrc/dsa_attention.cu`` (one CTA per query and kv head reads each selected
+  key / value row once for the query heads that share it), else a gathered dense softmax of tensor operations.
+
+Documents no longer than ``topk`` take the dense tcgen05 attention kernel directly (the selection keeps every causal key).
 """
 from __future__ import annotations
 

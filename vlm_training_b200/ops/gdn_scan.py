@@ -5,7 +5,8 @@ at every document boundary; reference: models/qwen3_5/model.py:180-186 calls fla
 split by what can run in parallel:
 
 * inside a chunk (decay matrices, the 64x64 triangular solve, ``w``, ``u``, the local attention matrix ``P``):
-  batched over all chunks of all documents and heads, plain tensor operations with autograd;
+  batched over all chunks of all documents and heads: on a GPU the kernels of ``csrc/gdn_chunk_sm100.cu`` (one CTA per chunk
+  and head; :class:`_ChunkedNative`), else plain tensor operations with autograd;
 * between chunks: ``vnew_c = u_c - w_c S_c`` and ``S_{c+1} = S_c exp(g_last) + kdec_c^T vnew_c``.  This is the only
   sequential part and runs as :func:`scan` — on a GPU one tcgen05 kernel launch for all documents and heads
   (``csrc/gdn_scan_sm100.cu``), which also writes the state entering every chunk;
