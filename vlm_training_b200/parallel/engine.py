@@ -36,6 +36,7 @@ parallelism every TP rank holds a partial gradient for them.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -459,7 +460,14 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
             logging.getLogger("vlm_training_b200").info(
                 "optimizer step: " + ("reduce-scatter + AdamW + all-gather in one NVLink kernel per bucket" if self._fused is not None
                                       else f"NCCL reduce-scatter / all-gather around the AdamW kernel ({reason or 'fused_comm is off'})"))
-        if (self.is_cuda and overlap and dist.is_initialized()) or self.reshard:
+        # one process on a GPU, no clipping: a bucket's AdamW runs on the side stream as soon as backward has finished the bucket
+        # AFTER it (one bucket of lag: every kernel that reads the bucket's weights has been enqueued by then), so the
+        # memory-bound update hides under the compute-bound rest of backward instead of running after it
+        tied = bool(getattr(getattr(getattr(model, "config", None), "text", None), "tie_word_embeddings", False))
+        self._early = (self.is_cuda and overlap and not dist.is_initialized() and max_grad_norm is None and not self.reshard
+                       and not tied and pdtype == torch.bfloat16 and os.environ.get("VLMT_EARLY_ADAMW", "1") != "0")
+        self._early_prev = None     # (domain, bucket) complete but not yet updated
+        if (self.is_cuda and overlap and dist.is_initialized()) or self.reshard or self._early:
             self._install_hooks()
         self._bwd_phase, self._prefetched = False, -1
         self.fuse_first_gemm = False
@@ -522,6 +530,12 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                 return
             b.seen.add(id(p))
             b.pending -= 1
+            if b.pending == 0 and not b.reduced and self._early:
+                b.reduced = True
+                prev, self._early_prev = self._early_prev, (d, b)
+                if prev is not None:
+                    self._early_update(*prev)
+                return
             if b.pending == 0 and not b.reduced:
                 if self._fused is not None:
                     from . import fused
@@ -750,8 +764,13 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         if self.max_grad_norm is not None:
             clip = self._clip_coefficient()
         b1, b2 = self.betas
+        if self._early:
+            self._early_prev = None   # the last complete bucket and the buckets backward never completed: updated below
         for d in self.domains:
             for bi, b in enumerate(d.buckets):
+                if getattr(b, "early_done", False):
+                    b.early_done = False
+                    continue
                 lo, hi = d.shard_range(b)
                 for seg in b.segments:
                     s, e = max(seg.start, lo), min(seg.end, hi)
@@ -778,19 +797,40 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
         if self.reshard:
             self.release_all()
             self._bwd_phase, self._prefetched = False, -1
+        if self._early:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)   # the updates that ran under backward
 
-    def _adamw(self, d, bi, s, e, grad, param, lr, wd, b1, b2, grad_scale):
+    def _early_update(self, d, b):
+        """AdamW of a bucket whose gradients are final, on the side stream, ordered after everything enqueued so far."""
+        b1, b2 = self.betas
+        bi = b.index
+        lo, hi = d.shard_range(b)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ev)
+            for seg in b.segments:
+                s, e = max(seg.start, lo), min(seg.end, hi)
+                if e <= s:
+                    continue
+                pg = self.param_groups[seg.group]
+                self._adamw(d, bi, s - lo, e - lo, d.shard_grad_view(b, s, e), d.shard_param_view(b, s, e), pg["lr"],
+                            pg["weight_decay"], b1, b2, d.grad_scale, step=self.step_count + 1)
+        b.early_done = True
+
+    def _adamw(self, d, bi, s, e, grad, param, lr, wd, b1, b2, grad_scale, step=None):
         master, m, v = d.master[bi][s:e], d.exp_avg[bi][s:e], d.exp_avg_sq[bi][s:e]
+        step = self.step_count if step is None else step
         if self.is_cuda and param.dtype == torch.bfloat16:
             from ..ops import cuda as cu
 
-            cu.adamw_step_(grad, master, m, v, param, lr, b1, b2, self.eps, wd, self.step_count, grad_scale, zero_grad=True)
+            cu.adamw_step_(grad, master, m, v, param, lr, b1, b2, self.eps, wd, step, grad_scale, zero_grad=True)
             return
         g = grad.float() * grad_scale
         mf, vf = m.float(), v.float()
         mf.mul_(b1).add_(g, alpha=1 - b1)
         vf.mul_(b2).addcmul_(g, g, value=1 - b2)
-        bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+        bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
         master.mul_(1 - lr * wd)
         master.addcdiv_(mf / bc1, (vf / bc2).sqrt_().add_(self.eps), value=-lr)
         m.copy_(mf)
