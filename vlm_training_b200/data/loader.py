@@ -94,6 +94,13 @@ class WorkerPool:
                     self.close()
                     raise RuntimeError(f"data worker {w} exited with code {self.procs[w].exitcode} without reporting")
                 continue
+            except (ConnectionError, EOFError, OSError) as exc:
+                # a queued row whose tensors were still owned by the worker: they cannot be received once it is gone
+                if not self.procs[w].is_alive():
+                    code = self.procs[w].exitcode
+                    self.close()
+                    raise RuntimeError(f"data worker {w} exited with code {code} without reporting") from exc
+                raise
             self.turn = (w + 1) % self.n
             if item is None:
                 self.done[w] = True
