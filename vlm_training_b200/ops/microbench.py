@@ -328,9 +328,24 @@ def bench_gemm_ag(t: Timer, m=8192, n=3072, k=4096, b_mn=False):
     return _report("gemm_all_gather_rank0_of_2_" + ("dgrad" if b_mn else "fwd"), [m, n, k], t(fn), flops=2.0 * m * n * k)
 
 
+def bench_gemm_rs_push(t: Timer, m=8192, n=4096, k=6144, b_mn=False):
+    """The GEMM -> reduce-scatter-push kernel run as rank 0 of two on one GPU: the epilogue stores the rows of each owner
+    into that owner's staging block, both of which are local buffers here (no link is crossed), so the figure is the
+    kernel's own cost next to the plain GEMM of the same shape."""
+    from . import cuda as cu
+
+    rows = m // 2
+    x = _r(m, k)
+    w = _r(k, n) if b_mn else _r(n, k)
+    mine = torch.empty(2, rows, n, dtype=torch.bfloat16, device="cuda")
+    peer = torch.empty(2, rows, n, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: cu._C.gemm_rs_push(x, w, [mine.data_ptr(), peer.data_ptr()], rows, b_mn)
+    return _report("gemm_rs_push_rank0_of_2_" + ("dgrad" if b_mn else "fwd"), [m, n, k], t(fn), flops=2.0 * m * n * k)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_wgather", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -382,6 +397,8 @@ def main(argv=None):
         bench_fused_adamw(t, state=torch.bfloat16)
     elif a.what == "gemm_ag":
         bench_gemm_ag(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
+    elif a.what == "gemm_rs_push":
+        bench_gemm_rs_push(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
     else:
         for layout in ("fwd", "dgrad", "wgrad"):
             bench_gemm(t, 8192, 6144, 4096, layout)
