@@ -1,0 +1,204 @@
+"""FP8 training of linear layers: quantisation kernels and the FP8 GEMM against their plain-PyTorch statement (GPU), the
+emulation and the model-level switch (CPU)."""
+import copy
+import math
+
+import pytest
+import torch
+
+from vlm_training_b200 import ops
+from vlm_training_b200.ops import float8
+from vlm_training_b200.ops.float8 import E4M3, E5M2
+
+
+def _deq(q_u8, fmt):
+    return q_u8.view(float8._DTYPE[fmt]).float()
+
+
+# ------------------------------------------------------------------------------------------------ CPU
+def test_emulated_linear_is_close_to_the_exact_one_and_has_gradients():
+    torch.manual_seed(0)
+    x = torch.randn(96, 128, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.nn.Parameter(torch.randn(64, 128, dtype=torch.bfloat16) * 0.05)
+    b = torch.nn.Parameter(torch.randn(64, dtype=torch.bfloat16) * 0.1)
+    exact = ops.linear(x, w, b)
+    exact.float().pow(2).sum().backward()
+    gx, gw, gb = x.grad.clone(), w.grad.clone(), b.grad.clone()
+    x.grad = w.grad = b.grad = None
+    w._vlmt_fp8 = True
+    before = float8.CALLS["linear"]
+    got = ops.linear(x, w, b)
+    assert float8.CALLS["linear"] == before + 1
+    got.float().pow(2).sum().backward()
+    rel = lambda a, c: float((a.float() - c.float()).norm() / c.float().norm())
+    assert rel(got, exact) < 0.05
+    assert rel(x.grad, gx) < 0.08 and rel(w.grad, gw) < 0.08 and rel(b.grad, gb) < 0.05
+
+
+def test_apply_float8_tags_language_model_linears_only():
+    from vlm_training_b200.models import ModelConfig, build_model
+    from vlm_training_b200.parallel.float8 import apply_float8, remove_float8
+
+    cfg = ModelConfig.preset("tiny-qwen3-vl")
+    model = build_model(cfg, dtype=torch.float32, device="cpu")
+    names = apply_float8(model)
+    assert names and not any("visual" in n for n in names)
+    tagged = {n for n, p in model.named_parameters() if getattr(p, "_vlmt_fp8", False)}
+    assert tagged == {n + ".weight" for n in names}
+    for n in tagged:
+        p = dict(model.named_parameters())[n]
+        assert p.shape[0] % 16 == 0 and p.shape[1] % 16 == 0
+    assert not any(n.startswith("lm_head") or "embed" in n for n in tagged)
+    remove_float8(model)
+    assert not any(getattr(p, "_vlmt_fp8", False) for p in model.parameters())
+
+
+def test_fused_ops_take_the_fp8_linear_for_a_tagged_weight():
+    torch.manual_seed(1)
+    x = torch.randn(32, 64)
+    nw = torch.ones(64)
+    w = torch.nn.Parameter(torch.randn(48, 64) * 0.1)
+    w._vlmt_fp8 = True
+    before = float8.CALLS["linear"]
+    y, r = ops.rms_norm_linear(x, nw, w, residual=torch.zeros_like(x))
+    gu = torch.randn(32, 128)
+    w2 = torch.nn.Parameter(torch.randn(48, 64) * 0.1)
+    w2._vlmt_fp8 = True
+    ops.swiglu_linear(gu, w2)
+    assert float8.CALLS["linear"] == before + 2
+    w._vlmt_fp8 = False
+    y0, _ = ops.rms_norm_linear(x, nw, w, residual=torch.zeros_like(x))
+    assert float((y - y0).norm() / y0.norm()) < 0.05
+
+
+# ------------------------------------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols,fmt", [(256, 128, E4M3), (1000 // 8 * 8, 208, E5M2), (16, 16, E4M3), (4096, 1024, E5M2), (136, 4304 // 16 * 16, E4M3)])
+def test_quantize_matches_reference_bit_for_bit(rows, cols, fmt):
+    from vlm_training_b200.ops import cuda as cu
+
+    torch.manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, device="cuda") * 3).to(torch.bfloat16)
+    x[0, 0] = 37.5   # the maximum is a single element
+    rm, tr, rec = cu._C.fp8_quantize(x, fmt, True, True)
+    q, inv = float8.quantize_ref(x, fmt)
+    assert float(rec[0]) == float(x.abs().max())
+    assert abs(float(rec[1]) - float(inv)) <= 1e-7 * float(inv)
+    want = q.view(torch.uint8)
+    assert torch.equal(rm, want)
+    assert tr.shape == (cols, rows) and torch.equal(tr, want.t())
+    only_t = cu._C.fp8_quantize(x, fmt, False, True)
+    assert only_t[0].numel() == 0 and torch.equal(only_t[1], want.t())
+    cu.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K,fa,fb", [(128, 256, 128, E4M3, E4M3), (256, 512, 512, E4M3, E4M3), (1000 // 8 * 8, 1152, 1536, E5M2, E4M3),
+                                         (384, 4304 // 16 * 16, 1152, E4M3, E4M3), (2048, 4096, 4096, E4M3, E4M3), (144, 144, 208, E5M2, E4M3),
+                                         (16, 16, 16, E4M3, E4M3)])
+def test_gemm_fp8_matches_fp32_product_of_the_quantised_operands(M, N, K, fa, fb):
+    from vlm_training_b200.ops import cuda as cu
+
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda")).to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    a8, _, ra = cu._C.fp8_quantize(a, fa, True, False)
+    b8, _, rb = cu._C.fp8_quantize(b, fb, True, False)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    cu._C.gemm_fp8(a8, b8, out, ra, rb, fa, fb, False)
+    want = (_deq(a8, fa) @ _deq(b8, fb).t()) * (ra[1] * rb[1])
+    err = (out.float() - want).abs()
+    tol = 1e-3 * math.sqrt(K) + 1e-2 * want.abs()   # bf16 rounding of the result + accumulation order
+    assert bool((err <= tol).all()), (float(err.max()), float(want.abs().max()))
+    # and close to the exact product: the quantisation error of two fp8 operands
+    exact = a.float() @ b.float().t()
+    assert float((out.float() - exact).norm() / exact.norm()) < 0.06
+    cu.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,N,K", [(512, 256, 384), (8192, 1024, 512), (1024, 4096, 4096)])
+def test_gemm_fp8_adds_a_weight_gradient_into_an_existing_one(T, N, K):
+    """accumulate: the tiles are added by TMA reduce-adds, a long contraction is cut into parts; the old content survives."""
+    from vlm_training_b200.ops import cuda as cu
+
+    torch.manual_seed(T)
+    dy = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    _, d8t, rd = cu._C.fp8_quantize(dy, E5M2, False, True)
+    _, x8t, rx = cu._C.fp8_quantize(x, E4M3, False, True)
+    before = (torch.randn(N, K, device="cuda") * 3).to(torch.bfloat16)
+    acc = before.clone()
+    cu._C.gemm_fp8(d8t, x8t, acc, rd, rx, E5M2, E4M3, True)
+    want = before.float() + (_deq(d8t, E5M2) @ _deq(x8t, E4M3).t()) * (rd[1] * rx[1])
+    err = (acc.float() - want).abs()
+    # bf16 additions of the old content and up to four partial tiles, each of the size of a random walk over its part of T
+    tol = 0.05 + 4e-2 * math.sqrt(T) + 2e-2 * want.abs()
+    assert bool((err <= tol).all()), (float(err.max()), float(want.abs().max()))
+    cu.check_status()
+
+
+@pytest.mark.gpu
+def test_linear_fp8_forward_backward_matches_the_emulation():
+    from vlm_training_b200.ops import cuda as cu
+
+    torch.manual_seed(5)
+    T, K, N = 1024, 512, 768
+    x = (torch.randn(T, K, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    w = torch.nn.Parameter((torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16))
+    b = torch.nn.Parameter((torch.randn(N, device="cuda") * 0.1).to(torch.bfloat16))
+    w._vlmt_fp8 = True
+    dy = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+    before = float8.CALLS["linear"]
+    y = ops.linear(x, w, b)
+    assert float8.CALLS["linear"] == before + 1
+    y.backward(dy)
+    got = (y.detach().clone(), x.grad.clone(), w.grad.clone(), b.grad.clone())
+    x.grad = w.grad = b.grad = None
+    yr = float8.linear_ref(x, w, b)
+    yr.backward(dy)
+    rel = lambda a, c: float((a.float() - c.float()).norm() / c.float().norm())
+    assert rel(got[0], yr) < 5e-3 and rel(got[1], x.grad) < 5e-3 and rel(got[2], w.grad) < 5e-3 and rel(got[3], b.grad) < 5e-3
+    cu.check_status()
+
+
+@pytest.mark.gpu
+def test_model_with_float8_linears_trains_like_the_bf16_model():
+    from vlm_training_b200.data.synthetic import SyntheticDataset, SyntheticSpec
+    from vlm_training_b200.models import BatchPlan, ModelConfig, build_model
+    from vlm_training_b200.models.init import init_normal_
+    from vlm_training_b200.ops import cuda as cu
+    from vlm_training_b200.parallel.float8 import apply_float8
+
+    torch.manual_seed(0)
+    cfg = ModelConfig.preset("tiny-qwen3")
+    cfg.text.vocab_size = min(cfg.text.vocab_size, 8192)
+    base = build_model(cfg, dtype=torch.float32, device="cpu")
+    init_normal_(base, seed=1)
+    m16 = copy.deepcopy(base).to(device="cuda", dtype=torch.bfloat16)
+    m8 = copy.deepcopy(m16)
+    assert apply_float8(m8)
+    spec = SyntheticSpec(kind="text-uniform", seq_len=512, vocab_size=cfg.text.vocab_size, doc_len_min=32, doc_len_max=256, seed=3)
+    batch = next(SyntheticDataset(spec, cfg))
+
+    def run(model):
+        plan = BatchPlan.build(cfg, batch["input_ids"], batch["cu_seqlens"], None, "cuda")
+        out = model(batch["input_ids"].cuda(), attention_mask=batch["cu_seqlens"].cuda(), labels=batch["labels"].cuda(), batch_plan=plan)
+        out.loss.backward()
+        return float(out.loss)
+
+    before = float8.CALLS["linear"]
+    l8 = run(m8)
+    assert float8.CALLS["linear"] > before
+    l16 = run(m16)
+    cu.check_status()
+    assert math.isfinite(l8) and abs(l8 - l16) < 3e-2 * max(1.0, abs(l16)), (l8, l16)
+    checked = 0
+    for (n, p8), (_, p16) in zip(m8.named_parameters(), m16.named_parameters()):
+        if p16.grad is None or p16.numel() < 4096:
+            continue
+        g, c = p8.grad.float().flatten(), p16.grad.float().flatten()
+        if float(c.norm()) > 1e-6:
+            assert float(torch.dot(g, c) / (g.norm() * c.norm() + 1e-12)) > 0.95, n
+            checked += 1
+    assert checked > 0

@@ -112,6 +112,9 @@ class TrainingSection:
     # with reshard_params on GPUs (fused_comm, no tensor parallelism): a block's first weight (qkv / in_proj) is gathered by
     # the GEMM that reads it instead of by the block's parameter gather
     reshard_fuse_first_gemm: bool = True
+    # FP8 GEMMs (tensor-wise dynamic scaling; e4m3 forward, e5m2 output gradients) for the language model's linear layers
+    # whose dimensions are multiples of 16; the vision tower, the LM head and MoE experts stay bf16
+    float8: bool = False
     beta1: float = 0.9
     beta2: float = 0.999
     seed: int = 42

@@ -59,17 +59,27 @@ def rms_norm_gated(x, z, weight, eps: float = 1e-6):
 
 
 # --- GEMM --------------------------------------------------------------------
+def _ref_linear(x, weight, bias=None):
+    """The CPU linear; a weight tagged for FP8 training (``parallel/float8.py``) goes through the FP8 emulation."""
+    if getattr(weight, "_vlmt_fp8", False):
+        from . import float8
+
+        float8.CALLS["linear"] += 1
+        return float8.linear_ref(x, weight, bias)
+    return ref.linear(x, weight, bias)
+
+
 def linear(x, weight, bias=None):
     if _use_cuda(x):
         return _cu().linear(x, weight, bias)
-    return ref.linear(x, weight, bias)
+    return _ref_linear(x, weight, bias)
 
 
 def linear_gelu(x, weight, bias, approximate: str = "tanh"):
     """``gelu(x @ W.T + b)`` — bias and activation run in the GEMM epilogue on CUDA."""
     if _use_cuda(x):
         return _cu().linear_gelu(x, weight, bias, approximate)
-    y = ref.linear(x, weight, bias)
+    y = _ref_linear(x, weight, bias)
     return ref.gelu_tanh(y) if approximate == "tanh" else ref.gelu_erf(y)
 
 
@@ -79,16 +89,16 @@ def rms_norm_linear(x, norm_weight, weight, eps: float = 1e-6, offset: bool = Fa
     if _use_cuda(x):
         return _cu().rms_norm_linear(x, norm_weight, weight, eps, offset, residual)
     if residual is None:
-        return ref.linear(ref.rms_norm(x, norm_weight, eps, offset), weight)
+        return _ref_linear(ref.rms_norm(x, norm_weight, eps, offset), weight)
     r = x + residual
-    return ref.linear(ref.rms_norm(r, norm_weight, eps, offset), weight), r
+    return _ref_linear(ref.rms_norm(r, norm_weight, eps, offset), weight), r
 
 
 def layer_norm_linear(x, ln_weight, ln_bias, weight, bias=None, eps: float = 1e-6):
     """``linear(layer_norm(x), weight, bias)``; on CUDA the normalised activation is recomputed in backward."""
     if _use_cuda(x):
         return _cu().layer_norm_linear(x, ln_weight, ln_bias, weight, bias, eps)
-    return ref.linear(ref.layer_norm(x, ln_weight, ln_bias, eps), weight, bias)
+    return _ref_linear(ref.layer_norm(x, ln_weight, ln_bias, eps), weight, bias)
 
 
 def gelu_linear(pre, weight, bias=None, approximate: str = "tanh"):
@@ -96,7 +106,7 @@ def gelu_linear(pre, weight, bias=None, approximate: str = "tanh"):
     if _use_cuda(pre):
         return _cu().gelu_linear(pre, weight, bias, approximate)
     act = ref.gelu_tanh(pre) if approximate == "tanh" else ref.gelu_erf(pre)
-    return ref.linear(act, weight, bias)
+    return _ref_linear(act, weight, bias)
 
 
 def swiglu_linear(gate_up, weight):
@@ -104,7 +114,7 @@ def swiglu_linear(gate_up, weight):
     if _use_cuda(gate_up):
         return _cu().swiglu_linear(gate_up, weight)
     g, u = gate_up.chunk(2, dim=-1)
-    return ref.linear(ref.swiglu(g, u), weight)
+    return _ref_linear(ref.swiglu(g, u), weight)
 
 
 # --- activations -------------------------------------------------------------

@@ -485,6 +485,7 @@ void bind_attention(pybind11::module_& m);
 void bind_comm(pybind11::module_& m);
 void bind_moe(pybind11::module_& m);
 void bind_gdn(pybind11::module_& m);
+void bind_fp8(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
@@ -533,4 +534,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   bind_comm(m);
   bind_moe(m);
   bind_gdn(m);
+  bind_fp8(m);
 }

@@ -597,9 +597,10 @@ namespace {
 struct TmapKey {
   uint64_t base, inner, outer, stride;
   uint32_t box_inner, box_outer;
+  int dtype;
   bool operator==(const TmapKey& o) const {
     return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box_inner == o.box_inner &&
-           box_outer == o.box_outer;
+           box_outer == o.box_outer && dtype == o.dtype;
   }
 };
 struct TmapKeyHash {
@@ -609,15 +610,17 @@ struct TmapKeyHash {
     h ^= (k.outer + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
     h ^= (k.stride + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
     h ^= (((uint64_t)k.box_inner << 32 | k.box_outer) + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= ((uint64_t)k.dtype + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
     return (size_t)h;
   }
 };
 }  // namespace
 
-extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
-                                      uint32_t box_inner, uint32_t box_outer) {
+namespace {
+int make_tmap_2d(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                 uint32_t box_outer, CUtensorMapDataType dtype) {
   static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-  const TmapKey key{reinterpret_cast<uint64_t>(base), inner, outer, row_stride_bytes, box_inner, box_outer};
+  const TmapKey key{reinterpret_cast<uint64_t>(base), inner, outer, row_stride_bytes, box_inner, box_outer, (int)dtype};
   auto it = cache.find(key);
   if (it != cache.end()) {
     *reinterpret_cast<CUtensorMap*>(out_map) = it->second;
@@ -638,7 +641,7 @@ extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t 
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), dtype, 2, const_cast<void*>(base), dims,
                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r == CUDA_SUCCESS) {
@@ -646,6 +649,18 @@ extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t 
     cache.emplace(key, *reinterpret_cast<CUtensorMap*>(out_map));
   }
   return (int)r;
+}
+}  // namespace
+
+extern "C" int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                                      uint32_t box_inner, uint32_t box_outer) {
+  return make_tmap_2d(out_map, base, inner, outer, row_stride_bytes, box_inner, box_outer, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+}
+
+// one byte per element (fp8 operands): inner extent, stride and box_inner are bytes
+extern "C" int vlmt_make_tmap_2d_u8(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                                    uint32_t box_inner, uint32_t box_outer) {
+  return make_tmap_2d(out_map, base, inner, outer, row_stride_bytes, box_inner, box_outer, CU_TENSOR_MAP_DATA_TYPE_UINT8);
 }
 
 // 3-D tensor map [d2][d1][d0] (d0 innermost, contiguous) with byte strides for d1 and d2, 128-byte swizzle, zero fill

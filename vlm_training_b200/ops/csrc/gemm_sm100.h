@@ -45,6 +45,9 @@ int vlmt_gemm_set_flag_wait_ms(long ms);
 // 2-D bf16 tensor map with 128-byte swizzle; `out_map` points at 128 bytes (CUtensorMap).
 int vlmt_make_tmap_2d_bf16(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer);
+// the same for one-byte elements (fp8 operands)
+int vlmt_make_tmap_2d_u8(void* out_map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                         uint32_t box_inner, uint32_t box_outer);
 // [d2][d1][d0] bf16 (d0 contiguous) with byte strides for d1 and d2 (multiples of 16); boxes are zero-filled outside the tensor
 int vlmt_make_tmap_3d_bf16(void* out_map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                            uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2);

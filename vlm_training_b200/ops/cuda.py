@@ -184,7 +184,16 @@ def _small_or_odd(x, w) -> bool:
     return (not _tma_ok(x, w)) or w.shape[0] < 16 or w.shape[0] % 8 != 0
 
 
+def _fp8(weight) -> bool:
+    """The weight was marked for FP8 training (``parallel/float8.py``): its linear goes through ``ops/float8.py``."""
+    return getattr(weight, "_vlmt_fp8", False)
+
+
 def linear(x, weight, bias=None):
+    if _fp8(weight):
+        from . import float8
+
+        return float8.linear(x, weight, bias)
     if _GEMM_BACKEND == "cublas" or x.dtype != torch.bfloat16 or _small_or_odd(x, weight):
         return torch.nn.functional.linear(x, weight, bias)
     return _Linear.apply(x, weight, bias, 0)
@@ -393,7 +402,7 @@ class _NormLinear(torch.autograd.Function):
 
 def rms_norm_linear(x, norm_weight, weight, eps=1e-6, offset=False, residual=None):
     """``linear(rms_norm(x + residual))``; returns ``y`` or ``(y, x + residual)``."""
-    ok = x.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and not _small_or_odd(x, weight) and x.dim() == 2
+    ok = x.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and not _small_or_odd(x, weight) and x.dim() == 2 and not _fp8(weight)
     if not ok:
         if residual is None:
             return linear(rms_norm(x, norm_weight, eps, offset), weight)
@@ -434,7 +443,7 @@ class _LNLinear(torch.autograd.Function):
 
 
 def layer_norm_linear(x, ln_weight, ln_bias, weight, bias=None, eps=1e-6):
-    ok = x.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and x.dim() == 2 and not _small_or_odd(x, weight)
+    ok = x.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and x.dim() == 2 and not _small_or_odd(x, weight) and not _fp8(weight)
     if not ok:
         return linear(layer_norm(x, ln_weight, ln_bias, eps), weight, bias)
     return _LNLinear.apply(x, ln_weight, ln_bias, weight, bias, eps)
@@ -473,7 +482,7 @@ class _GeluLinear(torch.autograd.Function):
 
 def gelu_linear(pre, weight, bias=None, approximate="tanh"):
     ok = (pre.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and pre.dim() == 2 and pre.numel() % 8 == 0
-          and not _small_or_odd(pre, weight))
+          and not _small_or_odd(pre, weight) and not _fp8(weight))
     if not ok:
         return linear(gelu(pre, approximate), weight, bias)
     return _GeluLinear.apply(pre, weight, bias, approximate == "tanh")
@@ -508,7 +517,7 @@ class _SwiGLULinear(torch.autograd.Function):
 
 def swiglu_linear(gate_up, weight):
     ok = (gate_up.dtype == torch.bfloat16 and _GEMM_BACKEND != "cublas" and gate_up.dim() == 2 and gate_up.shape[-1] % 16 == 0
-          and not _small_or_odd(gate_up[:, : gate_up.shape[-1] // 2], weight))
+          and not _small_or_odd(gate_up[:, : gate_up.shape[-1] // 2], weight) and not _fp8(weight))
     if not ok:
         return linear(swiglu(gate_up), weight)
     return _SwiGLULinear.apply(gate_up, weight)

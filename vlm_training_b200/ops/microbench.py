@@ -328,6 +328,40 @@ def bench_gemm_ag(t: Timer, m=8192, n=3072, k=4096, b_mn=False):
     return _report("gemm_all_gather_rank0_of_2_" + ("dgrad" if b_mn else "fwd"), [m, n, k], t(fn), flops=2.0 * m * n * k)
 
 
+def bench_gemm_fp8(t: Timer, m=8192, n=6144, k=4096, accumulate=False):
+    """The FP8 GEMM alone (operands already quantised) next to the bf16 GEMM of the same shape."""
+    from . import cuda as cu
+
+    a8, _, ra = cu._C.fp8_quantize(_r(m, k), 0, True, False)
+    b8, _, rb = cu._C.fp8_quantize(_r(n, k), 0, True, False)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: cu._C.gemm_fp8(a8, b8, out, ra, rb, 0, 0, accumulate)
+    return _report("gemm_fp8" + ("_acc" if accumulate else ""), [m, n, k], t(fn), flops=2.0 * m * n * k)
+
+
+def bench_linear_fp8(t: Timer, m=8192, n=6144, k=4096):
+    """Forward + backward of one linear layer (three GEMMs) in FP8, quantisation kernels included, and in bf16."""
+    from . import cuda as cu
+
+    x = _r(m, k).requires_grad_(True)
+    dy = _r(m, n)
+    out = []
+    for fp8 in (True, False):
+        w = torch.nn.Parameter(_r(n, k))
+        w._vlmt_fp8 = fp8
+
+        def fn():
+            x.grad = None
+            w.grad = None
+            cu.linear(x, w).backward(dy)
+
+        out.append(_report("linear_fwd_bwd_" + ("fp8" if fp8 else "bf16"), [m, n, k], t(fn), flops=6.0 * m * n * k))
+    nb = (m * k + n * k + m * n) * 2
+    fnq = lambda: cu._C.fp8_quantize(x.detach(), 0, True, True)
+    out.append(_report("fp8_quantize_both_layouts", [m, k], t(fnq), nbytes=m * k * (2 + 2 + 1 + 1)))
+    return out
+
+
 def bench_gemm_rs_push(t: Timer, m=8192, n=4096, k=6144, b_mn=False):
     """The GEMM -> reduce-scatter-push kernel run as rank 0 of two on one GPU: the epilogue stores the rows of each owner
     into that owner's staging block, both of which are local buffers here (no link is crossed), so the figure is the
@@ -345,7 +379,7 @@ def bench_gemm_rs_push(t: Timer, m=8192, n=4096, k=6144, b_mn=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "gemm_fp8", "linear_fp8", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -397,6 +431,10 @@ def main(argv=None):
         bench_fused_adamw(t, state=torch.bfloat16)
     elif a.what == "gemm_ag":
         bench_gemm_ag(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
+    elif a.what == "gemm_fp8":
+        bench_gemm_fp8(t, a.m, a.n, a.k, accumulate=a.layout == "wgrad_acc")
+    elif a.what == "linear_fp8":
+        bench_linear_fp8(t, a.m, a.n, a.k)
     elif a.what == "gemm_rs_push":
         bench_gemm_rs_push(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
     else:

@@ -622,7 +622,7 @@ class ShardedOptimizerEngine(torch.optim.Optimizer):
                 for p in b.params:
                     n = names.get(p, "")
                     if (n.endswith(self.FIRST_GEMM_SUFFIXES) and p.dim() == 2 and p.dtype == torch.bfloat16 and p.shape[0] > 128
-                            and p.shape[1] % 8 == 0 and p.numel() % 8 == 0):
+                            and p.shape[1] % 8 == 0 and p.numel() % 8 == 0 and not getattr(p, "_vlmt_fp8", False)):
                         d.f1[b.index] = (p, d._offset_of(p) - b.start)
                         units_done.add(b.unit)
                         picked += 1

@@ -273,7 +273,7 @@ def column_linear(x, weight, bias, ctx: TPContext, site=None):
     """``linear(column_input(x), weight, bias)``; on the peer-to-peer backend with sequence parallelism the all-gather
     runs inside the GEMM kernel.  ``site``: the calling module; its gathered input is kept in a persistent symmetric
     buffer of that site for the backward pass."""
-    if gather_linear_usable(x, weight, bias, ctx):
+    if not getattr(weight, "_vlmt_fp8", False) and gather_linear_usable(x, weight, bias, ctx):   # FP8 linears: plain collectives
         return _GatherLinear.apply(x, weight, ctx, site)
     from .. import ops
 
@@ -309,7 +309,8 @@ class _RowLinearReduceScatter(torch.autograd.Function):
 def row_linear(x, weight, ctx: TPContext):
     """``row_output(linear(x, weight))``; on the peer-to-peer backend with sequence parallelism the collective runs
     inside the GEMM kernel's epilogue."""
-    if ctx.enabled and ctx.sequence_parallel and ctx.p2p is not None and ctx.p2p.gemm_rs_usable(x, weight):
+    if (ctx.enabled and ctx.sequence_parallel and ctx.p2p is not None and not getattr(weight, "_vlmt_fp8", False)
+            and ctx.p2p.gemm_rs_usable(x, weight)):
         return _RowLinearReduceScatter.apply(x, weight, ctx)
     from .. import ops
 

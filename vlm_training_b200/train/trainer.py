@@ -110,6 +110,10 @@ class Trainer:
 
             self.ep_ctx = apply_ep(model, self.mesh, t.ep_size, fused=t.fused_comm and self.device.type == "cuda")
         apply_ac(model, t.ac_mode)
+        if t.float8:
+            from ..parallel.float8 import apply_float8
+
+            apply_float8(model)
         self.model = model
         self.optimizer = self.create_optimizer()
         self.scheduler = build_scheduler(self.optimizer, t.scheduler_type, t.total_steps, t.warmup_steps,
