@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--opt-state", default="auto", choices=["auto", "fp32", "bf16"])
     ap.add_argument("--vit-ac", default="auto", choices=["auto", "off", "full"])
     ap.add_argument("--reshard", action="store_true", help="shard parameters and gradients too (ZeRO-3 residency); not the default layout")
+    ap.add_argument("--float8", action="store_true",
+                    help="FP8 GEMMs for the language model's linear layers (training.float8); not the benchmark of record, which is bf16")
     ap.add_argument("--no-fuse-first-gemm", action="store_true", help="with --reshard: gather every weight by the block's parameter gather")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--sync-debug", action="store_true", help="warn on every host<->device synchronisation inside the end-to-end loop")
@@ -120,6 +122,7 @@ def build_config(args, world: int):
     t.fused_comm = os.environ.get("VLMT_FUSED_COMM", "1") == "1"
     t.reshard_params = bool(args.reshard)
     t.reshard_fuse_first_gemm = not args.no_fuse_first_gemm
+    t.float8 = args.float8
     t.output_dir = "/tmp/vlmt_bench"
     cfg.data.synthetic = "vlm" if "vl" in args.model else "text-loguniform"
     cfg.data.seq_len = args.seq_len
@@ -310,7 +313,7 @@ def run_ours(args):
             "metric": f"tokens/sec (whole job), {cfg.model.model_name}-shaped {'VLM ' if cfg.data.synthetic == 'vlm' else ''}training step", "value": value, "unit": "tokens/s",
             "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (value / n / BASELINE_TOKENS_PER_SEC_PER_GPU) if BASELINE_TOKENS_PER_SEC_PER_GPU else None,
-            "dtype": "bf16", "data": ("synthetic packed multimodal rows" if cfg.data.synthetic == "vlm" else "synthetic packed text rows")
+            "dtype": "bf16 with fp8 (e4m3 / e5m2) linear GEMMs in the language model" if args.float8 else "bf16", "data": ("synthetic packed multimodal rows" if cfg.data.synthetic == "vlm" else "synthetic packed text rows")
                                      + ", random-init weights", "impl": "ours",
             "tokens_per_sec_per_gpu": value / n,
             "mfu_vs_measured_sustained": value * flops_tok / n / tr.peak_flops,

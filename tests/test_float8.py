@@ -202,3 +202,31 @@ def test_model_with_float8_linears_trains_like_the_bf16_model():
             assert float(torch.dot(g, c) / (g.norm() * c.norm() + 1e-12)) > 0.95, n
             checked += 1
     assert checked > 0
+
+
+def test_trainer_with_float8_switch_learns_a_fixed_row_on_cpu(tmp_path, monkeypatch):
+    """``training.float8``: the tagged linears run through the FP8 emulation inside the trainer and the loss still falls."""
+    from test_trainer_cpu import _cfg, _shrink_vocab
+
+    _shrink_vocab(monkeypatch)
+    from vlm_training_b200.train.trainer import Trainer
+
+    tr = Trainer(_cfg(tmp_path, training__total_steps=6, training__lr_llm=2e-3, training__float8=True))
+    assert any(getattr(p, "_vlmt_fp8", False) for p in tr.model.parameters())
+    fixed = next(tr.loader)
+    tr.loader.close()
+
+    class Same:
+        def __next__(self):
+            return fixed
+
+        def close(self):
+            pass
+
+    tr.loader = Same()
+    before = float8.CALLS["linear"]
+    hist = tr.train()
+    tr.end_run()
+    losses = [m["train/loss"] for m in hist]
+    assert float8.CALLS["linear"] > before
+    assert len(losses) == 6 and all(l == l for l in losses) and losses[-1] < losses[0]
