@@ -243,11 +243,60 @@ for (int wi = 0; wi < nwarps; ++wi) { a += sm_acc[(size_t)wi * 2 * D + i]; c += 
 // ----------------------------------------------------------------------------------- row-tile norm kernels
 // The kernels above give a warp a whole row (re-reading it for every pass and, in backward, accumulating the weight
 // gradient through shared memory); they measured 16-40 % of copy bandwidth.  The row-tile forms below are used whenever
-// D <= 8192: a block of 256 threads works on kRR rows at a time, every thread owns the same VPT 8-element column
-// groups of every row, so the rows stay in registers between the passes, the weights are loaded once per thread, and
-// the weight gradient of a thread's columns accumulates in its own registers (no shared memory, no cross-warp sum).
-constexpr int kRT = 256;  // threads per block
-constexpr int kRR = 4;    // rows in flight per block
+// D <= 8192: a block of up to 256 threads works on a group of rows at a time, every thread owns the same VPT 8-element
+// column groups of every row, so the rows stay in registers between the passes, the weights are loaded once per thread,
+// and the weight gradient of a thread's columns accumulates in its own registers (no shared memory, no cross-warp sum).
+//
+// The inputs stream through a ring of kPipe stages in shared memory.  A stage holds the rows of one group for every input
+// tensor; a thread copies (cp.async) exactly the 16-byte vectors it will read itself, so the ring needs no barrier.  While
+// a block sums, computes and stores group g, the copies of the next kPipe - 1 groups are in flight: a block keeps the
+// memory system busy all the time instead of alternating between a load phase and a store phase (the version that loaded
+// straight into registers reached 0.33-0.48 of copy bandwidth on 8192 x 4096).
+constexpr int kRT = 256;   // threads per block
+constexpr int kRR = 4;     // most rows per group (sizes the scratch of the block-wide sums)
+constexpr int kPipe = 3;   // stages of the copy ring
+
+// rows per group: four for narrow rows (one column group per thread), one where a thread owns several column groups of a row
+template <int VPT> struct TileRows { static constexpr int value = VPT == 1 ? 4 : 1; };
+
+__device__ __forceinline__ void cp16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// slot of (stage, tensor) inside the ring: RR rows of nvec vectors
+template <int RR>
+__device__ __forceinline__ uint4* ring_slot(uint4* ring, int stage, int tensor, int n_tensors, int nvec) {
+  return ring + (size_t)(stage * n_tensors + tensor) * RR * nvec;
+}
+// start the copies of this thread's vectors of group g (nothing for rows or columns outside the matrix)
+template <int RR, int VPT>
+__device__ __forceinline__ void ring_issue(uint4* slot, const bf16* __restrict__ src, int g, int rows, int nvec) {
+#pragma unroll
+  for (int r = 0; r < RR; ++r) {
+    const int row = g * RR + r;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = threadIdx.x + k * (int)blockDim.x;
+      if (row < rows && v < nvec) cp16(slot + r * nvec + v, reinterpret_cast<const uint4*>(src) + (size_t)row * nvec + v);
+    }
+  }
+}
+// this thread's vectors of group g out of a finished stage; positions outside the matrix read as zeros
+template <int RR, int VPT>
+__device__ __forceinline__ void ring_read(const uint4* slot, int g, int rows, int nvec, uint4 (&dst)[RR][VPT]) {
+#pragma unroll
+  for (int r = 0; r < RR; ++r) {
+    const int row = g * RR + r;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = threadIdx.x + k * (int)blockDim.x;
+      dst[r][k] = (row < rows && v < nvec) ? slot[r * nvec + v] : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
 
 // Sum K per-thread values over the block; every thread gets the totals.  `sm` holds 2 x K x 8 floats and is used
 // alternately (`parity`), which makes one __syncthreads per call sufficient.
@@ -281,12 +330,17 @@ template <typename WT, int VPT>
 __global__ void __launch_bounds__(kRT) rmsnorm_fwd_tile_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
                                                               const WT* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ r_out,
                                                               float* __restrict__ rstd, int rows, int D, float eps, int offset) {
+  constexpr int RR = TileRows<VPT>::value;
+  extern __shared__ uint4 ring[];
   __shared__ float sm[2 * kRR * 8];
   const int nvec = D >> 3;
+  const int nt = res ? 2 : 1;
   float wv[VPT][8];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * (int)blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wv[k][i] = 0.f;
     if (v < nvec) {
       ld_w8(w, v, wv[k]);
       if (offset) {
@@ -296,41 +350,49 @@ __global__ void __launch_bounds__(kRT) rmsnorm_fwd_tile_kernel(const bf16* __res
     }
   }
   int parity = 0;
-  const int n_groups = (rows + kRR - 1) / kRR;
-  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
-    uint4 xv[kRR][VPT];
-    float ss[kRR];
+  const int n_groups = (rows + RR - 1) / RR;
+  auto issue = [&](int g, int stage) {
+    if (g < n_groups) {
+      ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 0, nt, nvec), x, g, rows, nvec);
+      if (res) ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 1, nt, nvec), res, g, rows, nvec);
+    }
+    cp_commit();   // one group per call, empty or not: the wait below counts groups
+  };
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
+  for (int s = 0; s < kPipe; ++s) issue(blockIdx.x + s * gridDim.x, s);
+  int stage = 0;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    cp_wait<kPipe - 1>();
+    uint4 xv[RR][VPT], ev[RR][VPT];
+    ring_read<RR, VPT>(ring_slot<RR>(ring, stage, 0, nt, nvec), g, rows, nvec, xv);
+    if (res) ring_read<RR, VPT>(ring_slot<RR>(ring, stage, 1, nt, nvec), g, rows, nvec, ev);
+    float ss[RR];
+#pragma unroll
+    for (int r = 0; r < RR; ++r) {
       ss[r] = 0.f;
-      const int row = g * kRR + r;
+      const int row = g * RR + r;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = threadIdx.x + k * (int)blockDim.x;
-        if (row < rows && v < nvec) {
-          const size_t o = (size_t)row * nvec + v;
-          uint4 u = reinterpret_cast<const uint4*>(x)[o];
-          float f[8];
-          unpack8(u, f);
-          if (res) {
-            float e[8];
-            unpack8(reinterpret_cast<const uint4*>(res)[o], e);
+        float f[8];
+        unpack8(xv[r][k], f);
+        if (res) {
+          float e[8];
+          unpack8(ev[r][k], e);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] += e[i];
-            u = pack8(f);
-            reinterpret_cast<uint4*>(r_out)[o] = u;
-            unpack8(u, f);  // normalise the rounded residual stream, as the unfused sequence does
-          }
-          xv[r][k] = u;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) ss[r] += f[i] * f[i];
+          for (int i = 0; i < 8; ++i) f[i] += e[i];
+          xv[r][k] = pack8(f);
+          if (row < rows && v < nvec) reinterpret_cast<uint4*>(r_out)[(size_t)row * nvec + v] = xv[r][k];
+          unpack8(xv[r][k], f);  // normalise the rounded residual stream, as the unfused sequence does
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss[r] += f[i] * f[i];
       }
     }
-    block_sum<kRR>(ss, sm, parity);
+    block_sum<RR>(ss, sm, parity);
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
-      const int row = g * kRR + r;
+    for (int r = 0; r < RR; ++r) {
+      const int row = g * RR + r;
       if (row >= rows) continue;
       const float rs = rsqrtf(ss[r] / (float)D + eps);
       if (threadIdx.x == 0 && rstd) rstd[row] = rs;
@@ -346,7 +408,10 @@ __global__ void __launch_bounds__(kRT) rmsnorm_fwd_tile_kernel(const bf16* __res
         }
       }
     }
+    issue(g + kPipe * gridDim.x, stage);   // the stage just read is free again (only this thread touches its slots)
+    stage = stage + 1 == kPipe ? 0 : stage + 1;
   }
+  cp_wait<0>();
 }
 
 template <typename WT, int VPT>
@@ -354,14 +419,17 @@ __global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __res
                                                               const WT* __restrict__ w, const float* __restrict__ rstd,
                                                               const bf16* __restrict__ dres, bf16* __restrict__ dx,
                                                               float* __restrict__ dw_partial, int rows, int D, int offset) {
+  constexpr int RR = TileRows<VPT>::value;
+  extern __shared__ uint4 ring[];
   __shared__ float sm[2 * kRR * 8];
   const int nvec = D >> 3;
+  const int nt = dres ? 3 : 2;
   float wv[VPT][8], dw[VPT][8];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * (int)blockDim.x;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dw[k][i] = 0.f;
+    for (int i = 0; i < 8; ++i) { dw[k][i] = 0.f; wv[k][i] = 0.f; }
     if (v < nvec) {
       ld_w8(w, v, wv[k]);
       if (offset) {
@@ -371,45 +439,53 @@ __global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __res
     }
   }
   int parity = 0;
-  const int n_groups = (rows + kRR - 1) / kRR;
-  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
-    uint4 xv[kRR][VPT], gv[kRR][VPT];
-    float dot[kRR], rs[kRR];
+  const int n_groups = (rows + RR - 1) / RR;
+  auto issue = [&](int g, int stage) {
+    if (g < n_groups) {
+      ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 0, nt, nvec), x, g, rows, nvec);
+      ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 1, nt, nvec), dy, g, rows, nvec);
+      if (dres) ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 2, nt, nvec), dres, g, rows, nvec);
+    }
+    cp_commit();
+  };
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
+  for (int s = 0; s < kPipe; ++s) issue(blockIdx.x + s * gridDim.x, s);
+  int stage = 0;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    cp_wait<kPipe - 1>();
+    uint4 xv[RR][VPT], gv[RR][VPT];
+    ring_read<RR, VPT>(ring_slot<RR>(ring, stage, 0, nt, nvec), g, rows, nvec, xv);
+    ring_read<RR, VPT>(ring_slot<RR>(ring, stage, 1, nt, nvec), g, rows, nvec, gv);
+    float dot[RR], rs[RR];
+#pragma unroll
+    for (int r = 0; r < RR; ++r) {
       dot[r] = 0.f;
-      const int row = g * kRR + r;
+      const int row = g * RR + r;
       rs[r] = row < rows ? rstd[row] : 0.f;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * (int)blockDim.x;
-        if (row < rows && v < nvec) {
-          const size_t o = (size_t)row * nvec + v;
-          xv[r][k] = reinterpret_cast<const uint4*>(x)[o];
-          gv[r][k] = reinterpret_cast<const uint4*>(dy)[o];
-          float xf[8], gf[8];
-          unpack8(xv[r][k], xf);
-          unpack8(gv[r][k], gf);
+        float xf[8], gf[8];
+        unpack8(xv[r][k], xf);
+        unpack8(gv[r][k], gf);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float xh = xf[i] * rs[r];
-            dot[r] += gf[i] * wv[k][i] * xh;
-            dw[k][i] += gf[i] * xh;
-          }
+        for (int i = 0; i < 8; ++i) {
+          const float xh = xf[i] * rs[r];
+          dot[r] += gf[i] * wv[k][i] * xh;
+          dw[k][i] += gf[i] * xh;
         }
       }
     }
-    block_sum<kRR>(dot, sm, parity);
+    block_sum<RR>(dot, sm, parity);
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
-      const int row = g * kRR + r;
+    for (int r = 0; r < RR; ++r) {
+      const int row = g * RR + r;
       if (row >= rows) continue;
       const float dt = dot[r] / (float)D;
+      const uint4* dslot = ring_slot<RR>(ring, stage, 2, nt, nvec);
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = threadIdx.x + k * (int)blockDim.x;
         if (v < nvec) {
-          const size_t o = (size_t)row * nvec + v;
           float xf[8], gf[8], out[8];
           unpack8(xv[r][k], xf);
           unpack8(gv[r][k], gf);
@@ -417,15 +493,18 @@ __global__ void __launch_bounds__(kRT) rmsnorm_bwd_tile_kernel(const bf16* __res
           for (int i = 0; i < 8; ++i) out[i] = rs[r] * (gf[i] * wv[k][i] - xf[i] * rs[r] * dt);
           if (dres) {
             float e[8];
-            unpack8(reinterpret_cast<const uint4*>(dres)[o], e);
+            unpack8(dslot[r * nvec + v], e);
 #pragma unroll
             for (int i = 0; i < 8; ++i) out[i] += e[i];
           }
-          reinterpret_cast<uint4*>(dx)[o] = pack8(out);
+          reinterpret_cast<uint4*>(dx)[(size_t)row * nvec + v] = pack8(out);
         }
       }
     }
+    issue(g + kPipe * gridDim.x, stage);
+    stage = stage + 1 == kPipe ? 0 : stage + 1;
   }
+  cp_wait<0>();
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * (int)blockDim.x;
@@ -442,6 +521,8 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
                                                                 const bf16* __restrict__ b, bf16* __restrict__ y,
                                                                 float* __restrict__ mean, float* __restrict__ rstd, int rows, int D,
                                                                 float eps) {
+  constexpr int RR = TileRows<VPT>::value;
+  extern __shared__ uint4 ring[];
   __shared__ float sm[2 * kRR * 8];
   const int nvec = D >> 3;
   float wv[VPT][8], bv[VPT][8];
@@ -449,44 +530,47 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * (int)blockDim.x;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) bv[k][i] = 0.f;
+    for (int i = 0; i < 8; ++i) { bv[k][i] = 0.f; wv[k][i] = 0.f; }
     if (v < nvec) {
       ld_w8(w, v, wv[k]);
       if (b) ld_w8(b, v, bv[k]);
     }
   }
   int parity = 0;
-  const int n_groups = (rows + kRR - 1) / kRR;
-  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
-    uint4 xv[kRR][VPT];
-    float s[kRR];
+  const int n_groups = (rows + RR - 1) / RR;
+  auto issue = [&](int g, int stage) {
+    if (g < n_groups) ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 0, 1, nvec), x, g, rows, nvec);
+    cp_commit();
+  };
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
+  for (int s = 0; s < kPipe; ++s) issue(blockIdx.x + s * gridDim.x, s);
+  int stage = 0;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    cp_wait<kPipe - 1>();
+    uint4 xv[RR][VPT];
+    ring_read<RR, VPT>(ring_slot<RR>(ring, stage, 0, 1, nvec), g, rows, nvec, xv);
+    float s[RR];
+#pragma unroll
+    for (int r = 0; r < RR; ++r) {
       s[r] = 0.f;
-      const int row = g * kRR + r;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        const int v = threadIdx.x + k * (int)blockDim.x;
-        if (row < rows && v < nvec) {
-          xv[r][k] = reinterpret_cast<const uint4*>(x)[(size_t)row * nvec + v];
-          float f[8];
-          unpack8(xv[r][k], f);
+        float f[8];
+        unpack8(xv[r][k], f);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) s[r] += f[i];
-        }
+        for (int i = 0; i < 8; ++i) s[r] += f[i];
       }
     }
-    block_sum<kRR>(s, sm, parity);
-    float ss[kRR];
+    block_sum<RR>(s, sm, parity);
+    float ss[RR];
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
+    for (int r = 0; r < RR; ++r) {
       s[r] /= (float)D;  // mean
       ss[r] = 0.f;
-      const int row = g * kRR + r;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = threadIdx.x + k * (int)blockDim.x;
-        if (row < rows && v < nvec) {
+        if (v < nvec) {
           float f[8];
           unpack8(xv[r][k], f);
 #pragma unroll
@@ -494,10 +578,10 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
         }
       }
     }
-    block_sum<kRR>(ss, sm, parity);
+    block_sum<RR>(ss, sm, parity);
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
-      const int row = g * kRR + r;
+    for (int r = 0; r < RR; ++r) {
+      const int row = g * RR + r;
       if (row >= rows) continue;
       const float mu = s[r], rs = rsqrtf(ss[r] / (float)D + eps);
       if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
@@ -513,7 +597,10 @@ __global__ void __launch_bounds__(kRT) layernorm_fwd_tile_kernel(const bf16* __r
         }
       }
     }
+    issue(g + kPipe * gridDim.x, stage);
+    stage = stage + 1 == kPipe ? 0 : stage + 1;
   }
+  cp_wait<0>();
 }
 
 template <int VPT>
@@ -522,6 +609,8 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
                                                                 const float* __restrict__ rstd, bf16* __restrict__ dx,
                                                                 float* __restrict__ dw_partial, float* __restrict__ db_partial, int rows,
                                                                 int D) {
+  constexpr int RR = TileRows<VPT>::value;
+  extern __shared__ uint4 ring[];
   __shared__ float sm[2 * 2 * kRR * 8];
   const int nvec = D >> 3;
   float wv[VPT][8], dw[VPT][8], db[VPT][8];
@@ -529,27 +618,37 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * (int)blockDim.x;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { dw[k][i] = 0.f; db[k][i] = 0.f; }
+    for (int i = 0; i < 8; ++i) { dw[k][i] = 0.f; db[k][i] = 0.f; wv[k][i] = 0.f; }
     if (v < nvec) ld_w8(w, v, wv[k]);
   }
   int parity = 0;
-  const int n_groups = (rows + kRR - 1) / kRR;
-  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
-    uint4 xv[kRR][VPT], gv[kRR][VPT];
-    float s12[2 * kRR], mu[kRR], rs[kRR];
+  const int n_groups = (rows + RR - 1) / RR;
+  auto issue = [&](int g, int stage) {
+    if (g < n_groups) {
+      ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 0, 2, nvec), x, g, rows, nvec);
+      ring_issue<RR, VPT>(ring_slot<RR>(ring, stage, 1, 2, nvec), dy, g, rows, nvec);
+    }
+    cp_commit();
+  };
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
+  for (int s = 0; s < kPipe; ++s) issue(blockIdx.x + s * gridDim.x, s);
+  int stage = 0;
+  for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    cp_wait<kPipe - 1>();
+    uint4 xv[RR][VPT], gv[RR][VPT];
+    ring_read<RR, VPT>(ring_slot<RR>(ring, stage, 0, 2, nvec), g, rows, nvec, xv);
+    ring_read<RR, VPT>(ring_slot<RR>(ring, stage, 1, 2, nvec), g, rows, nvec, gv);
+    float s12[2 * RR], mu[RR], rs[RR];
+#pragma unroll
+    for (int r = 0; r < RR; ++r) {
       s12[2 * r] = s12[2 * r + 1] = 0.f;
-      const int row = g * kRR + r;
+      const int row = g * RR + r;
       mu[r] = row < rows ? mean[row] : 0.f;
       rs[r] = row < rows ? rstd[row] : 0.f;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = threadIdx.x + k * (int)blockDim.x;
         if (row < rows && v < nvec) {
-          const size_t o = (size_t)row * nvec + v;
-          xv[r][k] = reinterpret_cast<const uint4*>(x)[o];
-          gv[r][k] = reinterpret_cast<const uint4*>(dy)[o];
           float xf[8], gf[8];
           unpack8(xv[r][k], xf);
           unpack8(gv[r][k], gf);
@@ -565,10 +664,10 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
         }
       }
     }
-    block_sum<2 * kRR>(s12, sm, parity);
+    block_sum<2 * RR>(s12, sm, parity);
 #pragma unroll
-    for (int r = 0; r < kRR; ++r) {
-      const int row = g * kRR + r;
+    for (int r = 0; r < RR; ++r) {
+      const int row = g * RR + r;
       if (row >= rows) continue;
       const float s1 = s12[2 * r] / (float)D, s2 = s12[2 * r + 1] / (float)D;
 #pragma unroll
@@ -587,7 +686,10 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
         }
       }
     }
+    issue(g + kPipe * gridDim.x, stage);
+    stage = stage + 1 == kPipe ? 0 : stage + 1;
   }
+  cp_wait<0>();
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * (int)blockDim.x;
@@ -1283,18 +1385,26 @@ inline int grid_for(long work_items, int per_block, int cap) {
 #define BF(p) reinterpret_cast<const bf16*>(p)
 #define BFM(p) reinterpret_cast<bf16*>(p)
 
+// bytes of the copy ring of a row-tile launch: kPipe stages of `tensors` inputs, `rr` rows each
+static size_t ring_bytes(int D, int rr, int tensors) { return (size_t)kPipe * tensors * rr * (D >> 3) * sizeof(uint4); }
+// a kernel whose ring plus its static scratch exceeds the default 48 KB of shared memory has to be told so
+template <typename K>
+static void allow_smem(K kernel, size_t bytes) {
+  if (bytes > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
 // grid of a forward row-tile kernel: one wave of resident blocks (a second, partly filled wave costs a whole pass)
 template <typename K>
-static int tile_grid(K kernel, int rows, int threads = kRT) {
+static int tile_grid(K kernel, int rows, int threads, int rr, size_t smem) {
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return grid_for(rows, kRR, sms * per_sm);
+  return grid_for(rows, rr, sms * per_sm);
 }
 extern "C" {
 
-int vlmt_norm_blocks(int rows) { return grid_for(rows, kWarpsPerBlock, 148 * 4); }
+// three blocks per SM: what the backward row-tile kernels keep resident (registers and copy ring), so the grid is one wave
+int vlmt_norm_blocks(int rows) { return grid_for(rows, kWarpsPerBlock, 148 * 3); }
 
 // warps per block of the backward norm kernels: each warp owns `floats_per_warp` fp32 accumulators in smem
 static int bwd_warps(size_t floats_per_warp) {
@@ -1323,7 +1433,8 @@ void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32,
   if (rows <= 0) return;
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define RF(WT, V) rmsnorm_fwd_tile_kernel<WT, V><<<tile_grid(rmsnorm_fwd_tile_kernel<WT, V>, rows, tile_threads(D, vpt)), tile_threads(D, vpt), 0, st>>>(BF(x), BF(res), (const WT*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset)
+#define RF(WT, V) do { const size_t sb = ring_bytes(D, TileRows<V>::value, res ? 2 : 1); auto kf = rmsnorm_fwd_tile_kernel<WT, V>; allow_smem(kf, sb); \
+    kf<<<tile_grid(kf, rows, tile_threads(D, vpt), TileRows<V>::value, sb), tile_threads(D, vpt), sb, st>>>(BF(x), BF(res), (const WT*)w, BFM(y), BFM(r_out), rstd, rows, D, eps, offset); } while (0)
     if (w_fp32) TILE_DISPATCH(vpt, RF(float, 1), RF(float, 2), RF(float, 4));
     else TILE_DISPATCH(vpt, RF(bf16, 1), RF(bf16, 2), RF(bf16, 4));
 #undef RF
@@ -1342,7 +1453,8 @@ int vlmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, int w_fp32, c
   const int grid = vlmt_norm_blocks(rows);
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define RB(WT, V) rmsnorm_bwd_tile_kernel<WT, V><<<grid, tile_threads(D, vpt), 0, st>>>(BF(dy), BF(x), (const WT*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset)
+#define RB(WT, V) do { const size_t sb = ring_bytes(D, TileRows<V>::value, dres ? 3 : 2); auto kb = rmsnorm_bwd_tile_kernel<WT, V>; allow_smem(kb, sb); \
+    kb<<<grid, tile_threads(D, vpt), sb, st>>>(BF(dy), BF(x), (const WT*)w, rstd, BF(dres), BFM(dx), dw_partial, rows, D, offset); } while (0)
     if (w_fp32) TILE_DISPATCH(vpt, RB(float, 1), RB(float, 2), RB(float, 4));
     else TILE_DISPATCH(vpt, RB(bf16, 1), RB(bf16, 2), RB(bf16, 4));
 #undef RB
@@ -1369,7 +1481,8 @@ void vlmt_layernorm_fwd(const void* x, const void* w, const void* b, void* y, fl
   if (rows <= 0) return;
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define LF(V) layernorm_fwd_tile_kernel<V><<<tile_grid(layernorm_fwd_tile_kernel<V>, rows, tile_threads(D, vpt)), tile_threads(D, vpt), 0, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps)
+#define LF(V) do { const size_t sb = ring_bytes(D, TileRows<V>::value, 1); auto kf = layernorm_fwd_tile_kernel<V>; allow_smem(kf, sb); \
+    kf<<<tile_grid(kf, rows, tile_threads(D, vpt), TileRows<V>::value, sb), tile_threads(D, vpt), sb, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps); } while (0)
     TILE_DISPATCH(vpt, LF(1), LF(2), LF(4));
 #undef LF
     return;
@@ -1381,7 +1494,8 @@ int vlmt_layernorm_bwd(const void* dy, const void* x, const void* w, const float
   const int grid = vlmt_norm_blocks(rows);
   const int vpt = tile_vpt(D);
   if (vpt) {
-#define LB(V) layernorm_bwd_tile_kernel<V><<<grid, tile_threads(D, vpt), 0, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D)
+#define LB(V) do { const size_t sb = ring_bytes(D, TileRows<V>::value, 2); auto kb = layernorm_bwd_tile_kernel<V>; allow_smem(kb, sb); \
+    kb<<<grid, tile_threads(D, vpt), sb, st>>>(BF(dy), BF(x), BF(w), mean, rstd, BFM(dx), dw_partial, db_partial, rows, D); } while (0)
     TILE_DISPATCH(vpt, LB(1), LB(2), LB(4));
 #undef LB
     return grid;

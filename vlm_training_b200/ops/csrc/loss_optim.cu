@@ -244,6 +244,34 @@ __global__ void colsum_finish_kernel(const float* __restrict__ partial, int slab
   out[c] = t;
 }
 
+// out[c] = sum over many partial rows (the per-block weight-gradient sums of the norm kernels: a few hundred rows).
+// A block owns 16 columns; its 256 threads are 16 row lanes x 16 columns, lane j adds rows j, j + 16, ... and the 16 lane
+// sums are added in lane order, so the result does not depend on timing.
+__global__ void __launch_bounds__(256) sum_rows_kernel(const float* __restrict__ partial, int rows, int cols, float* __restrict__ out) {
+  __shared__ float sm[16][17];
+  const int cl = threadIdx.x & 15, lane = threadIdx.x >> 4;
+  const int c = blockIdx.x * 16 + cl;
+  float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+  if (c < cols) {
+    int r = lane;
+    for (; r + 48 < rows; r += 64) {   // four independent loads in flight per thread
+      t0 += partial[(long)r * cols + c];
+      t1 += partial[(long)(r + 16) * cols + c];
+      t2 += partial[(long)(r + 32) * cols + c];
+      t3 += partial[(long)(r + 48) * cols + c];
+    }
+    for (; r < rows; r += 16) t0 += partial[(long)r * cols + c];
+  }
+  sm[lane][cl] = (t0 + t1) + (t2 + t3);
+  __syncthreads();
+  if (lane == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) t += sm[j][cl];
+    out[c] = t;
+  }
+}
+
 // sum of squares of a flat bf16/fp32 range -> out[0] (atomic; used for gradient clipping)
 template <typename GT>
 __global__ void sumsq_kernel(const GT* __restrict__ x, long n, float* __restrict__ out) {
@@ -315,7 +343,7 @@ void vlmt_colsum(const void* x, long ld, int rows, int cols, float* partial, flo
 // out[c] = sum over `rows` partial rows (the per-block weight-gradient sums of the norm kernels)
 void vlmt_sum_rows_f32(const float* partial, int rows, int cols, float* out, cudaStream_t st) {
   if (cols <= 0) return;
-  colsum_finish_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, rows, cols, out);
+  sum_rows_kernel<<<(cols + 15) / 16, 256, 0, st>>>(partial, rows, cols, out);
 }
 void vlmt_sumsq(const void* x, int fp32, long n, float* out, cudaStream_t st) {
   if (n <= 0) return;

@@ -127,6 +127,17 @@ def bench_rmsnorm(t: Timer, rows=8192, dim=4096):
     return _report("rmsnorm_bwd", [rows, dim], ms, nbytes=3.0 * rows * dim * 2)
 
 
+def bench_layernorm(t: Timer, rows=28672, dim=1152):
+    from . import cuda as cu
+
+    x, w, b = _r(rows, dim), _r(dim), _r(dim)
+    ms = t(lambda: cu._C.layernorm_fwd(x, w, b, 1e-6))
+    _report("layernorm_fwd", [rows, dim], ms, nbytes=2.0 * rows * dim * 2)
+    y, mean, rstd = cu._C.layernorm_fwd(x, w, b, 1e-6)
+    ms = t(lambda: cu._C.layernorm_bwd(y, x, w, mean, rstd))
+    return _report("layernorm_bwd", [rows, dim], ms, nbytes=3.0 * rows * dim * 2)
+
+
 def bench_swiglu(t: Timer, rows=8192, inter=12288):
     from . import cuda as cu
 
@@ -379,7 +390,7 @@ def bench_gemm_rs_push(t: Timer, m=8192, n=4096, k=6144, b_mn=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "gemm_fp8", "linear_fp8", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "layernorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "gemm_fp8", "linear_fp8", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -431,6 +442,8 @@ def main(argv=None):
         bench_fused_adamw(t, state=torch.bfloat16)
     elif a.what == "gemm_ag":
         bench_gemm_ag(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
+    elif a.what == "layernorm":
+        bench_layernorm(t, a.rows if a.rows != 8192 else 28672)
     elif a.what == "gemm_fp8":
         bench_gemm_fp8(t, a.m, a.n, a.k, accumulate=a.layout == "wgrad_acc")
     elif a.what == "linear_fp8":
