@@ -1099,16 +1099,20 @@ __global__ void qkv_norm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16
 // x [S, H, D] with strides (ss, hs, 1) -> contiguous out; cos/sin [S, D] fp32; transpose=1 gives the backward map.
 // the same rotation on groups of 4 channels (8-byte bf16 accesses, 16-byte angle loads): needs D/2, every stride and
 // every base address to be multiples of 4 elements
+// IdxT: unsigned (the usual case: S * H * D / 8 items fit 32 bits, and the index arithmetic is three cheap 32-bit divisions
+// instead of three 64-bit ones, which cost more than the rest of the loop body) or long
+template <typename IdxT>
 __global__ void rope_generic_vec4_kernel(const bf16* __restrict__ x, long ss, long hs, const float* __restrict__ cosv,
                                          const float* __restrict__ sinv, bf16* __restrict__ out, long oss, long ohs, int S, int H, int D,
                                          int transpose) {
-  const int half = D >> 1, hq = half >> 2;
-  const long total = (long)S * H * hq;
-  for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+  const int half = D >> 1;
+  const IdxT hq = (IdxT)(half >> 2), nh = (IdxT)H;
+  const IdxT total = (IdxT)S * nh * hq;
+  for (IdxT idx = (IdxT)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (IdxT)gridDim.x * blockDim.x) {
     const int j = (int)(idx % hq) * 4;
-    const long sh = idx / hq;
-    const int h = (int)(sh % H);
-    const long s = sh / H;
+    const IdxT sh = idx / hq;
+    const int h = (int)(sh % nh);
+    const long s = (long)(sh / nh);
     const bf16* p = x + s * ss + h * hs;
     float a[4], b[4], o0[4], o1[4];
     ldE<4>(p + j, a);
@@ -1584,8 +1588,12 @@ void vlmt_rope_generic(const void* x, long ss, long hs, const float* cosv, const
   const bool vec4 = half % 4 == 0 && ss % 4 == 0 && hs % 4 == 0 && oss % 4 == 0 && ohs % 4 == 0 && ((uintptr_t)x & 7) == 0 &&
                     ((uintptr_t)out & 7) == 0 && ((uintptr_t)cosv & 15) == 0 && ((uintptr_t)sinv & 15) == 0;
   if (vec4) {
-    rope_generic_vec4_kernel<<<grid_for((long)S * H * (half / 4), 256, 148 * 16), 256, 0, st>>>(BF(x), ss, hs, cosv, sinv, BFM(out), oss,
-                                                                                           ohs, S, H, D, transpose);
+    const long items = (long)S * H * (half / 4);
+    const int grid = grid_for(items, 256, 148 * 16);
+    if (items + (long)grid * 256 < (1l << 32))   // the loop's last increment must not wrap
+      rope_generic_vec4_kernel<unsigned><<<grid, 256, 0, st>>>(BF(x), ss, hs, cosv, sinv, BFM(out), oss, ohs, S, H, D, transpose);
+    else
+      rope_generic_vec4_kernel<long><<<grid, 256, 0, st>>>(BF(x), ss, hs, cosv, sinv, BFM(out), oss, ohs, S, H, D, transpose);
     return;
   }
   rope_generic_kernel<<<grid_for((long)S * H * (D / 2), 256, 148 * 16), 256, 0, st>>>(BF(x), ss, hs, cosv, sinv, BFM(out), oss, ohs, S, H, D,

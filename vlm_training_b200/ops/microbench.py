@@ -138,6 +138,18 @@ def bench_layernorm(t: Timer, rows=28672, dim=1152):
     return _report("layernorm_bwd", [rows, dim], ms, nbytes=3.0 * rows * dim * 2)
 
 
+def bench_rope_vision(t: Timer, tokens=28672, heads=16, d=72):
+    """The ViT's rotary embedding on the q slice of a fused qkv projection (strided input, contiguous output)."""
+    from . import cuda as cu
+
+    qkv = _r(tokens, 3 * heads * d)
+    q = qkv[:, : heads * d].view(tokens, heads, d)
+    ang = torch.rand(tokens, d, device="cuda") * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    ms = t(lambda: cu._C.rope_generic(q, cos, sin, False, d))
+    return _report("rope_vision_fwd", [tokens, heads, d], ms, nbytes=2.0 * tokens * heads * d * 2)
+
+
 def bench_swiglu(t: Timer, rows=8192, inter=12288):
     from . import cuda as cu
 
@@ -390,7 +402,7 @@ def bench_gemm_rs_push(t: Timer, m=8192, n=4096, k=6144, b_mn=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "layernorm", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "gemm_fp8", "linear_fp8", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "layernorm", "rope_vision", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "gemm_fp8", "linear_fp8", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -442,6 +454,8 @@ def main(argv=None):
         bench_fused_adamw(t, state=torch.bfloat16)
     elif a.what == "gemm_ag":
         bench_gemm_ag(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
+    elif a.what == "rope_vision":
+        bench_rope_vision(t)
     elif a.what == "layernorm":
         bench_layernorm(t, a.rows if a.rows != 8192 else 28672)
     elif a.what == "gemm_fp8":
