@@ -150,6 +150,16 @@ def bench_rope_vision(t: Timer, tokens=28672, heads=16, d=72):
     return _report("rope_vision_fwd", [tokens, heads, d], ms, nbytes=2.0 * tokens * heads * d * 2)
 
 
+def bench_gelu(t: Timer, rows=28672, dim=4304):
+    from . import cuda as cu
+
+    x, dy = _r(rows, dim), _r(rows, dim)
+    ms = t(lambda: cu._C.gelu_fwd(x, True))
+    _report("gelu_tanh_fwd", [rows, dim], ms, nbytes=2.0 * rows * dim * 2)
+    ms = t(lambda: cu._C.gelu_bwd(dy, x, True))
+    return _report("gelu_tanh_bwd", [rows, dim], ms, nbytes=3.0 * rows * dim * 2)
+
+
 def bench_swiglu(t: Timer, rows=8192, inter=12288):
     from . import cuda as cu
 
@@ -402,7 +412,7 @@ def bench_gemm_rs_push(t: Timer, m=8192, n=4096, k=6144, b_mn=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "layernorm", "rope_vision", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "gemm_fp8", "linear_fp8", "all"])
+    ap.add_argument("what", choices=["gemm", "attention", "rmsnorm", "layernorm", "rope_vision", "gelu", "swiglu", "qkv_rope", "ce", "adamw", "moe", "gdn_scan", "gdn", "conv1d", "dsa", "fused_adamw", "gemm_ag", "gemm_rs_push", "gemm_wgather", "gemm_fp8", "linear_fp8", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -454,6 +464,8 @@ def main(argv=None):
         bench_fused_adamw(t, state=torch.bfloat16)
     elif a.what == "gemm_ag":
         bench_gemm_ag(t, a.m, a.n, a.k, b_mn=a.layout == "dgrad")
+    elif a.what == "gelu":
+        bench_gelu(t)
     elif a.what == "rope_vision":
         bench_rope_vision(t)
     elif a.what == "layernorm":
