@@ -117,7 +117,8 @@ class WorkerPool:
             try:
                 while True:
                     q_.get_nowait()
-            except (queue.Empty, OSError, ValueError):
+            except (queue.Empty, OSError, ValueError, EOFError):
+                # empty, closed, or a queued row whose tensor storage belonged to a worker that has already left
                 pass
         for p in self.procs:
             p.join(timeout=5)
