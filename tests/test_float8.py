@@ -230,3 +230,16 @@ def test_trainer_with_float8_switch_learns_a_fixed_row_on_cpu(tmp_path, monkeypa
     losses = [m["train/loss"] for m in hist]
     assert float8.CALLS["linear"] > before
     assert len(losses) == 6 and all(l == l for l in losses) and losses[-1] < losses[0]
+
+
+@pytest.mark.slow
+def test_float8_under_tp2_sequence_parallel_follows_single_rank(tmp_path):
+    """With tensor parallelism every rank quantises its own shard of a weight (its own scale), so the losses are close to the
+    single-rank FP8 run, not equal to it; both stay close to the exact run."""
+    from test_trainer_cpu import _run_ranks
+
+    exact = _run_ranks(tmp_path, 1, [], 29641)
+    one = _run_ranks(tmp_path, 1, ["--training.float8", "true"], 29642)
+    tp2 = _run_ranks(tmp_path, 2, ["--training.float8", "true", "--training.tp_size", "2", "--training.sequence_parallel", "true"], 29643)
+    assert one == pytest.approx(exact, rel=2e-2, abs=2e-2) and one != exact
+    assert tp2 == pytest.approx(one, rel=2e-2, abs=2e-2)
