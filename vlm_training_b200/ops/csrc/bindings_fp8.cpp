@@ -11,14 +11,7 @@ torch::Tensor vlmt_status_tensor();
 
 static inline cudaStream_t cur() { return at::cuda::getCurrentCUDAStream().stream(); }
 
-static int sm_count() {
-  static thread_local int n[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  if (n[dev] == 0) n[dev] = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  return n[dev];
-}
+static int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
 
 // x: bf16 [rows, cols] (unit inner stride).  -> (q [rows, cols] uint8 or empty, q^T [cols, rows rounded up to 16] uint8 or
 // empty, rec [2] float: max |x| and the factor that undoes the scaling)
