@@ -166,7 +166,7 @@ def test_add_rms_norm_fwd_bwd():
     _close(w.grad, wr.grad, 0.5, 2e-2, "dw")
 
 
-@pytest.mark.parametrize("D", [1152, 4608])
+@pytest.mark.parametrize("D", [1152, 4608, 1024, 1032, 776, 768])
 def test_layer_norm_fwd_bwd(D):
     x = _rand(500, D).requires_grad_()
     w, b = _rand(D, scale=0.5).requires_grad_(), _rand(D, scale=0.5).requires_grad_()

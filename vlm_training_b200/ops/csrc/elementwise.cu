@@ -704,6 +704,95 @@ __global__ void __launch_bounds__(kRT) layernorm_bwd_tile_kernel(const bf16* __r
   }
 }
 
+// ----------------------------------------------------------------------------------- LayerNorm forward, one warp per row
+// Rows of 776 to 1280 channels (the ViT's 1152).  The row-tile kernels spend about 200 instructions per thread and row
+// on eight elements there (three conversions of the same vector, two block-wide sums with a barrier each) and are bound
+// by instruction issue at a quarter of the memory bandwidth.  Here a warp owns a whole row: lane l holds the vectors
+// l, l + 32, ... (VL of them) as floats, both sums are five shuffles, the weights are read from shared memory, and the
+// rows arrive through the same kind of per-thread `cp.async` ring (every lane copies exactly the vectors it reads itself).
+// 28672 x 1152: 0.0349 ms against 0.0451 ms.  The backward pass stays on the row-tile kernel: a warp-per-row form needs
+// 2 x VL x 8 gradient accumulators per lane (184 registers, two blocks of four warps per SM) and measured 0.097 ms against
+// 0.083 ms.
+constexpr int kLnWarpsFwd = 8, kLnPipeFwd = 3;
+
+template <int VL>
+__global__ void __launch_bounds__(kLnWarpsFwd * 32) layernorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                                             const bf16* __restrict__ b, bf16* __restrict__ y,
+                                                                             float* __restrict__ mean, float* __restrict__ rstd, int rows,
+                                                                             int D, float eps) {
+  extern __shared__ uint4 dyn[];
+  float* sw = reinterpret_cast<float*>(dyn);        // weights and bias as floats, [D] each
+  float* sb = sw + D;
+  uint4* ring = reinterpret_cast<uint4*>(sb + D);   // [warp][stage][nvec]
+  const int nvec = D >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    sw[i] = __bfloat162float(w[i]);
+    sb[i] = b ? __bfloat162float(b[i]) : 0.f;
+  }
+  __syncthreads();
+  uint4* my = ring + (size_t)warp * kLnPipeFwd * nvec;
+  const int row_step = gridDim.x * kLnWarpsFwd;
+  auto issue = [&](int row, int stage) {
+    if (row < rows) {
+#pragma unroll
+      for (int k = 0; k < VL; ++k) {
+        const int v = lane + 32 * k;
+        if (v < nvec) cp16(my + stage * nvec + v, reinterpret_cast<const uint4*>(x) + (size_t)row * nvec + v);
+      }
+    }
+    cp_commit();   // one group per call, empty or not: the wait below counts groups
+  };
+  const int row0 = blockIdx.x * kLnWarpsFwd + warp;
+#pragma unroll
+  for (int s = 0; s < kLnPipeFwd; ++s) issue(row0 + s * row_step, s);
+  int stage = 0;
+  for (int row = row0; row < rows; row += row_step) {
+    cp_wait<kLnPipeFwd - 1>();
+    float f[VL][8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+      const int v = lane + 32 * k;
+      if (v < nvec) {
+        unpack8(my[stage * nvec + v], f[k]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += f[k][i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[k][i] = 0.f;
+      }
+    }
+    const float mu = warp_sum(s) / (float)D;
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+      if (lane + 32 * k < nvec) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { f[k][i] -= mu; ss += f[k][i] * f[k][i]; }
+      }
+    }
+    const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+#pragma unroll
+    for (int k = 0; k < VL; ++k) {
+      const int v = lane + 32 * k;
+      if (v < nvec) {
+        const float4 w0 = *reinterpret_cast<const float4*>(sw + v * 8), w1 = *reinterpret_cast<const float4*>(sw + v * 8 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(sb + v * 8), b1 = *reinterpret_cast<const float4*>(sb + v * 8 + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = f[k][i] * rs * wv[i] + bv[i];
+        reinterpret_cast<uint4*>(y)[(size_t)row * nvec + v] = pack8(o);
+      }
+    }
+    issue(row + kLnPipeFwd * row_step, stage);   // the stage just read is free again (only this lane touches its slots)
+    stage = stage + 1 == kLnPipeFwd ? 0 : stage + 1;
+  }
+  cp_wait<0>();
+}
+
 // ----------------------------------------------------------------------------------- gated RMSNorm (GDN output)
 // y = x * rstd * w * z * sigmoid(z), rows of D (<= 256), one warp per row
 __global__ void rmsnorm_gated_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, const bf16* __restrict__ w,
@@ -1468,6 +1557,11 @@ static int tile_threads(int D, int vpt) {
   const int t = (((D >> 3) + 31) / 32) * 32;
   return t < 64 ? 64 : (t > kRT ? kRT : t);
 }
+// vectors per lane of the warp-per-row LayerNorm kernels (0: the width is outside their range)
+static int ln_warp_vl(int D) {
+  if ((D & 7) || D <= 768 || D > 1280) return 0;
+  return ((D >> 3) + 31) / 32 <= 4 ? 4 : 5;
+}
 #define TILE_DISPATCH(VPT, CALL1, CALL2, CALL4) do { if ((VPT) == 1) { CALL1; } else if ((VPT) == 2) { CALL2; } else { CALL4; } } while (0)
 
 void vlmt_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_fp32, void* y, void* r_out, float* rstd, int rows, int D,
@@ -1521,6 +1615,15 @@ int vlmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, int w_fp32, c
 void vlmt_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int D, float eps,
                         cudaStream_t st) {
   if (rows <= 0) return;
+  const int vl = ln_warp_vl(D);
+  if (vl) {
+    const size_t sb = 2 * (size_t)D * sizeof(float) + (size_t)kLnWarpsFwd * kLnPipeFwd * (D >> 3) * sizeof(uint4);
+#define LW(V) do { auto kf = layernorm_fwd_warp_kernel<V>; allow_smem(kf, sb); \
+    kf<<<tile_grid(kf, rows, kLnWarpsFwd * 32, kLnWarpsFwd, sb), kLnWarpsFwd * 32, sb, st>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, rows, D, eps); } while (0)
+    if (vl == 4) LW(4); else LW(5);
+#undef LW
+    return;
+  }
   const int vpt = tile_vpt(D);
   if (vpt) {
 #define LF(V) do { const size_t sb = ring_bytes(D, TileRows<V>::value, 1); auto kf = layernorm_fwd_tile_kernel<V>; allow_smem(kf, sb); \
