@@ -238,8 +238,8 @@ def test_float8_under_tp2_sequence_parallel_follows_single_rank(tmp_path):
     single-rank FP8 run, not equal to it; both stay close to the exact run."""
     from test_trainer_cpu import _run_ranks
 
-    exact = _run_ranks(tmp_path, 1, [], 29641)
-    one = _run_ranks(tmp_path, 1, ["--training.float8", "true"], 29642)
-    tp2 = _run_ranks(tmp_path, 2, ["--training.float8", "true", "--training.tp_size", "2", "--training.sequence_parallel", "true"], 29643)
+    exact = _run_ranks(tmp_path, 1, [], 29651)
+    one = _run_ranks(tmp_path, 1, ["--training.float8", "true"], 29652)
+    tp2 = _run_ranks(tmp_path, 2, ["--training.float8", "true", "--training.tp_size", "2", "--training.sequence_parallel", "true"], 29653)
     assert one == pytest.approx(exact, rel=2e-2, abs=2e-2) and one != exact
     assert tp2 == pytest.approx(one, rel=2e-2, abs=2e-2)
