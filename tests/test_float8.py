@@ -243,3 +243,34 @@ def test_float8_under_tp2_sequence_parallel_follows_single_rank(tmp_path):
     tp2 = _run_ranks(tmp_path, 2, ["--training.float8", "true", "--training.tp_size", "2", "--training.sequence_parallel", "true"], 29653)
     assert one == pytest.approx(exact, rel=2e-2, abs=2e-2) and one != exact
     assert tp2 == pytest.approx(one, rel=2e-2, abs=2e-2)
+
+
+def test_apply_float8_on_the_hybrid_moe_dsa_model_leaves_experts_router_and_indexer_alone():
+    from vlm_training_b200.models import ModelConfig, build_model
+    from vlm_training_b200.parallel.float8 import apply_float8
+
+    cfg = ModelConfig.preset("tiny-qwen3.5-moe")
+    cfg.text.dsa = True
+    cfg.text.dsa_topk = 64
+    model = build_model(cfg, dtype=torch.float32, device="cpu")
+    names = apply_float8(model)
+    assert names
+    leaves = {n.split(".")[-1] for n in names}
+    assert not any(leaf.startswith("idx_") or leaf == "lm_head" for leaf in leaves)
+    tagged = {n for n, p in model.named_parameters() if getattr(p, "_vlmt_fp8", False)}
+    assert all(p.dim() == 2 for n, p in model.named_parameters() if n in tagged)
+    assert not any("experts" in n or "router" in n or n.endswith("gate.weight") for n in tagged), sorted(tagged)[:8]
+    # the tagged model still runs forward and backward on CPU through the emulation
+    from vlm_training_b200.data.synthetic import SyntheticDataset, SyntheticSpec
+    from vlm_training_b200.models import BatchPlan
+
+    cfg.text.vocab_size = min(cfg.text.vocab_size, 2048)
+    spec = SyntheticSpec(kind="text-uniform", seq_len=256, vocab_size=cfg.text.vocab_size, doc_len_min=32, doc_len_max=128, seed=3)
+    model = build_model(cfg, dtype=torch.float32, device="cpu")
+    apply_float8(model)
+    batch = next(SyntheticDataset(spec, cfg))
+    plan = BatchPlan.build(cfg, batch["input_ids"], batch["cu_seqlens"], None, "cpu")
+    before = float8.CALLS["linear"]
+    out = model(batch["input_ids"], attention_mask=batch["cu_seqlens"], labels=batch["labels"], batch_plan=plan)
+    out.loss.backward()
+    assert float8.CALLS["linear"] > before and torch.isfinite(out.loss)
